@@ -1,0 +1,174 @@
+"""Seeded synthetic Magpie-shaped decoder weights and inputs.
+
+The real Magpie checkpoint is not available offline, so every test and
+benchmark runs on random-init weights with the reference's tensor names, shapes
+and layer structure (src/graph.c:2978-3079 in mynah-tts): per layer four
+gain-only LayerNorms, qkv_net [3W,W], o_net [W,W], cross q_net [xw,W],
+kv_net [2xw,W], o_net [W,xw], FFN proj [4W,W,1] and o_net [W,4W,1]; plus
+position embeddings, the output norm, one embedding table and one logit head
+(weight + bias) per stacked codebook stream.
+
+Distributions: linear weights, embeddings and position rows ~ N(0, 0.02);
+LayerNorm gains ~ N(1, 0.01); head biases ~ N(0, 0.01); text-encoder memory
+~ N(0, 1).  numpy's default_rng(seed) is bit-reproducible across machines, so
+the same seed gives the same model here and on the GPU box.
+"""
+from __future__ import annotations
+
+import json
+import struct
+from dataclasses import dataclass, field
+
+import numpy as np
+
+
+@dataclass(frozen=True)
+class DecoderShape:
+    layers: int = 12
+    width: int = 768
+    heads: int = 12            # fixed at 12 in the reference (src/graph.c:2971)
+    xattn_width: int = 128     # q_net.shape[0] of the real checkpoint
+    memory_length: int = 128   # text-encoder states
+    max_positions: int = 2048  # rows of decoder.position_embeddings.weight
+    tables: int = 8            # stacked codebook streams (stacking * codebooks)
+    vocab: int = 2048
+    codebook_size: int = 2016
+    eos_id: int = 2017
+
+    @property
+    def head_width(self) -> int:
+        return self.width // self.heads
+
+    @property
+    def ffn_width(self) -> int:
+        return 4 * self.width   # src/graph.c:2973
+
+
+MAGPIE_357M = DecoderShape()
+# Small shape for fast CPU tests: same structure, 12 heads of 16.
+TINY = DecoderShape(layers=2, width=192, xattn_width=32, memory_length=24,
+                    max_positions=96, tables=4, vocab=64, codebook_size=56, eos_id=57)
+
+LAYER_TENSORS = (
+    ("norm_self.weight", "gain"),
+    ("norm_xattn_query.weight", "gain"),
+    ("norm_xattn_memory.weight", "gain"),
+    ("norm_pos_ff.weight", "gain"),
+    ("self_attention.qkv_net.weight", "qkv"),
+    ("self_attention.o_net.weight", "o_self"),
+    ("cross_attention.q_net.weight", "q_cross"),
+    ("cross_attention.kv_net.weight", "kv_cross"),
+    ("cross_attention.o_net.weight", "o_cross"),
+    ("pos_ff.proj.conv.weight", "ffn_up"),
+    ("pos_ff.o_net.conv.weight", "ffn_down"),
+)
+
+
+def _layer_shapes(s: DecoderShape) -> dict[str, tuple[int, ...]]:
+    w, xw, f = s.width, s.xattn_width, s.ffn_width
+    return {
+        "gain": (w,),
+        "qkv": (3 * w, w),
+        "o_self": (w, w),
+        "q_cross": (xw, w),
+        "kv_cross": (2 * xw, w),
+        "o_cross": (w, xw),
+        "ffn_up": (f, w, 1),
+        "ffn_down": (w, f, 1),
+    }
+
+
+@dataclass
+class SynthModel:
+    shape: DecoderShape
+    seed: int
+    tensors: dict[str, np.ndarray] = field(default_factory=dict)
+
+    def layer(self, index: int, suffix: str) -> np.ndarray:
+        return self.tensors[f"decoder.layers.{index}.{suffix}"]
+
+    def embedding(self, table: int) -> np.ndarray:
+        return self.tensors[f"audio_embeddings.{table}.weight"]
+
+    def head_weight(self, table: int) -> np.ndarray:
+        return self.tensors[f"local_transformer_out_projections.{table}.weight"]
+
+    def head_bias(self, table: int) -> np.ndarray:
+        return self.tensors[f"local_transformer_out_projections.{table}.bias"]
+
+    @property
+    def position(self) -> np.ndarray:
+        return self.tensors["decoder.position_embeddings.weight"]
+
+    @property
+    def norm_out(self) -> np.ndarray:
+        return self.tensors["decoder.norm_out.weight"]
+
+
+def make_model(shape: DecoderShape = MAGPIE_357M, seed: int = 0) -> SynthModel:
+    rng = np.random.default_rng(seed)
+    t: dict[str, np.ndarray] = {}
+
+    def normal(mean, std, dims):
+        return np.ascontiguousarray(rng.normal(mean, std, size=dims).astype(np.float32))
+
+    t["decoder.position_embeddings.weight"] = normal(0.0, 0.02, (shape.max_positions, shape.width))
+    t["decoder.norm_out.weight"] = normal(1.0, 0.01, (shape.width,))
+    shapes = _layer_shapes(shape)
+    for layer in range(shape.layers):
+        for suffix, kind in LAYER_TENSORS:
+            name = f"decoder.layers.{layer}.{suffix}"
+            if kind == "gain":
+                t[name] = normal(1.0, 0.01, shapes[kind])
+            else:
+                t[name] = normal(0.0, 0.02, shapes[kind])
+    for table in range(shape.tables):
+        t[f"audio_embeddings.{table}.weight"] = normal(0.0, 0.02, (shape.vocab, shape.width))
+        t[f"local_transformer_out_projections.{table}.weight"] = normal(
+            0.0, 0.02, (shape.vocab, shape.width))
+        t[f"local_transformer_out_projections.{table}.bias"] = normal(0.0, 0.01, (shape.vocab,))
+    return SynthModel(shape=shape, seed=seed, tensors=t)
+
+
+def make_memory(shape: DecoderShape, seed: int) -> np.ndarray:
+    """Text-encoder output for one request: [memory_length, width] ~ N(0,1)."""
+    rng = np.random.default_rng([seed, 0x6D656D])
+    return np.ascontiguousarray(
+        rng.normal(0.0, 1.0, size=(shape.memory_length, shape.width)).astype(np.float32))
+
+
+def make_codes(shape: DecoderShape, seed: int, frames: int = 1) -> np.ndarray:
+    """Uniform code ids in [0, codebook_size): [frames, tables] uint32."""
+    rng = np.random.default_rng([seed, 0x636F64])
+    return np.ascontiguousarray(
+        rng.integers(0, shape.codebook_size, size=(frames, shape.tables), dtype=np.uint32))
+
+
+def make_linear_case(seed: int, n: int = 3072, k: int = 768):
+    """The single-op case: x ~ N(0,1) [1,k]; W ~ N(0,0.02) [n,k]; LayerNorm gain
+    ~ N(1,0.01); bias ~ N(0,0.01)."""
+    rng = np.random.default_rng([seed, 0x6C696E])
+    x = rng.normal(0.0, 1.0, size=(1, k)).astype(np.float32)
+    w = rng.normal(0.0, 0.02, size=(n, k)).astype(np.float32)
+    gain = rng.normal(1.0, 0.01, size=(k,)).astype(np.float32)
+    bias = rng.normal(0.0, 0.01, size=(n,)).astype(np.float32)
+    return x, w, gain, bias
+
+
+def write_safetensors(path: str, tensors: dict[str, np.ndarray]) -> None:
+    """Minimal safetensors writer (F32 only): 8-byte little-endian header
+    length, JSON header, then the raw tensors back to back."""
+    header: dict[str, dict] = {}
+    offset = 0
+    for name, array in tensors.items():
+        assert array.dtype == np.float32 and array.flags["C_CONTIGUOUS"]
+        header[name] = {"dtype": "F32", "shape": list(array.shape),
+                        "data_offsets": [offset, offset + array.nbytes]}
+        offset += array.nbytes
+    blob = json.dumps(header, separators=(",", ":")).encode()
+    blob += b" " * ((8 - len(blob) % 8) % 8)
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(blob)))
+        f.write(blob)
+        for array in tensors.values():
+            f.write(array.tobytes())

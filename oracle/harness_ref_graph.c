@@ -1,0 +1,212 @@
+/* Harness around the reference's own decoder step.  TEST INFRASTRUCTURE ONLY.
+ *
+ * This translation unit textually includes the reference's src/graph.c (from
+ * the read-only reference checkout named by -I on the compile line) so that
+ * its `static` decoder functions -- decoder_cache_init, decoder_step_batch,
+ * decoder_run, embed_audio_frame -- can be driven on a synthetic safetensors
+ * file without a model pack.  Nothing of the reference is copied here: the
+ * wrappers below only marshal arguments.  The result is built into
+ * oracle/_ref/ and is used to validate oracle/mynah_oracle.c and as the timed
+ * CPU baseline.
+ */
+#include "graph.c"
+
+#include <stdlib.h>
+
+typedef struct {
+    mynah_tts_model model;
+} ref_model;
+
+typedef struct {
+    decoder_cache cache;
+    size_t full_layers;
+} ref_decoder;
+
+#define REF_EXPORT __attribute__((visibility("default")))
+
+/* hidden_dim/layers fill mynah_tts_model_info the way model.json would
+ * (src/mynah_tts.c:214-266); qtype is the enum of src/qmat.c:36
+ * (0 f32, 1 int8, 2 int4, 3 f16). */
+REF_EXPORT ref_model *ref_model_open(const char *safetensors_path, unsigned hidden_dim,
+                                     unsigned layers, unsigned codebooks, unsigned stacking,
+                                     unsigned codebook_size, unsigned vocab, unsigned eos_id,
+                                     int qtype, char *error, size_t cap) {
+    ref_model *r = (ref_model *)calloc(1, sizeof(*r));
+    if (r == NULL) return NULL;
+    r->model.info.hidden_dim = hidden_dim;
+    r->model.info.decoder_layers = layers;
+    r->model.info.codebook_count = codebooks;
+    r->model.info.frame_stacking_factor = stacking;
+    r->model.info.codebook_size = codebook_size;
+    r->model.info.audio_vocab_size = vocab;
+    r->model.info.audio_eos_id = eos_id;
+    if (mynah_weights_open(safetensors_path, &r->model.tts, error, cap) != 0 ||
+        mynah_backend_open(MYNAH_TTS_DEVICE_CPU, &r->model.backend, error, cap) != 0) {
+        free(r);
+        return NULL;
+    }
+    r->model.qcache = mynah_qmat_cache_new(qtype);
+    if (r->model.qcache == NULL) {
+        free(r);
+        return NULL;
+    }
+    return r;
+}
+
+REF_EXPORT void ref_model_close(ref_model *r) {
+    if (r == NULL) return;
+    mynah_qmat_cache_free(r->model.qcache);
+    mynah_backend_close(r->model.backend);
+    mynah_weights_close(r->model.tts);
+    free(r);
+}
+
+REF_EXPORT int ref_num_threads(void) { return mynah_num_threads(); }
+
+REF_EXPORT ref_decoder *ref_decoder_new(ref_model *r, const float *memory, size_t memory_length,
+                                        size_t capacity, char *error, size_t cap) {
+    ref_decoder *d = (ref_decoder *)calloc(1, sizeof(*d));
+    if (d == NULL) return NULL;
+    if (decoder_cache_init(&r->model, &d->cache, memory, memory_length, capacity, error, cap) != 0) {
+        free(d);
+        return NULL;
+    }
+    d->full_layers = d->cache.layers;
+    return d;
+}
+
+REF_EXPORT void ref_decoder_free(ref_decoder *d) {
+    if (d == NULL) return;
+    decoder_cache_free(&d->cache);
+    free(d);
+}
+
+REF_EXPORT size_t ref_decoder_length(const ref_decoder *d) { return d->cache.length; }
+REF_EXPORT void ref_decoder_set_length(ref_decoder *d, size_t n) { d->cache.length = n; }
+/* Run only the first n layers: per-layer hidden states without touching the
+ * reference's arithmetic. */
+REF_EXPORT void ref_decoder_set_layers(ref_decoder *d, size_t n) {
+    d->cache.layers = n <= d->full_layers ? n : d->full_layers;
+}
+REF_EXPORT size_t ref_decoder_xattn_width(const ref_decoder *d) { return d->cache.xattn_width; }
+REF_EXPORT float *ref_decoder_self_k(ref_decoder *d) { return d->cache.self_k; }
+REF_EXPORT float *ref_decoder_self_v(ref_decoder *d) { return d->cache.self_v; }
+REF_EXPORT float *ref_decoder_cross_k(ref_decoder *d) { return d->cache.cross_k; }
+REF_EXPORT float *ref_decoder_cross_v(ref_decoder *d) { return d->cache.cross_v; }
+
+/* inputs/outs are [batch][width] contiguous; the reference takes pointer
+ * arrays (src/graph.c:3127-3131). */
+REF_EXPORT int ref_decoder_step_batch(ref_model *r, ref_decoder **decoders, const float *inputs,
+                                      float *outs, size_t batch, char *error, size_t cap) {
+    if (batch == 0u || batch > MYNAH_MAX_BATCH) return -1;
+    const size_t width = r->model.info.hidden_dim;
+    decoder_cache *caches[MYNAH_MAX_BATCH];
+    const float *in[MYNAH_MAX_BATCH];
+    float *out[MYNAH_MAX_BATCH];
+    for (size_t b = 0; b < batch; ++b) {
+        caches[b] = &decoders[b]->cache;
+        in[b] = inputs + b * width;
+        out[b] = outs + b * width;
+    }
+    batch_scratch scratch;
+    if (batch_scratch_init(&scratch, batch, caches[0]->ffn_width, error, cap) != 0) return -1;
+    const int rc = decoder_step_batch(&r->model, caches, in, out, batch,
+                                      batch > 1u ? &scratch : NULL, error, cap);
+    batch_scratch_free(&scratch);
+    return rc;
+}
+
+REF_EXPORT int ref_decoder_run(ref_model *r, ref_decoder *d, const float *rows, size_t count,
+                               float *out_last, char *error, size_t cap) {
+    return decoder_run(&r->model, &d->cache, rows, count, out_last, NULL, error, cap);
+}
+
+/* codes are [codebooks][code_stride] as in src/graph.c:760-766. */
+REF_EXPORT int ref_embed_audio_frame(ref_model *r, const unsigned *codes, size_t code_stride,
+                                     size_t frame, float *row, char *error, size_t cap) {
+    return embed_audio_frame(&r->model, codes, code_stride, frame, row, error, cap);
+}
+
+/* Logit heads in the form of src/graph.c:1538-1566: the per-stream projection
+ * `local_transformer_out_projections.N.{weight,bias}` through the quantized
+ * linear, then the masked first-on-ties pick.  The mask-and-pick loop is
+ * restated here because the reference has it inline in a larger function. */
+REF_EXPORT int ref_heads_argmax(ref_model *r, const float *hidden, size_t streams, int allow_eos,
+                                unsigned *tokens, float *logits_out, char *error, size_t cap) {
+    const size_t width = r->model.info.hidden_dim;
+    const size_t vocab = r->model.info.audio_vocab_size;
+    const size_t codebook_size = r->model.info.codebook_size;
+    const unsigned eos_id = r->model.info.audio_eos_id;
+    float *logits = (float *)malloc(vocab * sizeof(float));
+    if (logits == NULL) return -1;
+    for (size_t stream = 0; stream < streams; ++stream) {
+        char name[128];
+        mynah_tensor weight, bias;
+        snprintf(name, sizeof(name), "local_transformer_out_projections.%zu.bias", stream);
+        if (tensor(r->model.tts, name, &bias, error, cap) != 0) { free(logits); return -1; }
+        snprintf(name, sizeof(name), "local_transformer_out_projections.%zu.weight", stream);
+        if (tensor(r->model.tts, name, &weight, error, cap) != 0) { free(logits); return -1; }
+        if (mynah_qmat_linear_resolved(r->model.qcache, r->model.backend, name, weight.data,
+                                       hidden, logits, 1u, width, vocab, bias.data,
+                                       error, cap) != 0) { free(logits); return -1; }
+        float best = -FLT_MAX;
+        unsigned argmax = 0;
+        for (size_t candidate = 0; candidate < vocab; ++candidate) {
+            const int is_code = candidate < codebook_size;
+            const int is_eos = candidate == eos_id;
+            if (!is_code && !(is_eos && allow_eos)) continue;
+            if (logits[candidate] > best) {
+                best = logits[candidate];
+                argmax = (unsigned)candidate;
+            }
+        }
+        tokens[stream] = argmax;
+        if (logits_out != NULL) memcpy(logits_out + stream * vocab, logits, vocab * sizeof(float));
+    }
+    free(logits);
+    return 0;
+}
+
+/* Greedy frames for `batch` requests stepped together (<= 16, the reference's
+ * cap): embed each request's stored codes, one decoder_step_batch, heads per
+ * request.  codes is [batch][streams] with stream = fs * codebooks + codebook;
+ * tokens_out is [frames][batch][streams].  Every request runs all frames (EOS
+ * allowed from min_frames on is reported in eos_frame[b], first occurrence,
+ * else -1) so the timing is a fixed amount of work. */
+REF_EXPORT int ref_greedy_decode(ref_model *r, ref_decoder **decoders, size_t batch,
+                                 unsigned *codes, size_t frames, size_t min_frames,
+                                 unsigned *tokens_out, long *eos_frame, char *error, size_t cap) {
+    const size_t width = r->model.info.hidden_dim;
+    const size_t codebooks = r->model.info.codebook_count;
+    const size_t stacking = r->model.info.frame_stacking_factor;
+    const size_t streams = codebooks * stacking;
+    const unsigned eos_id = r->model.info.audio_eos_id;
+    if (batch == 0u || batch > MYNAH_MAX_BATCH) return -1;
+    float *rows = (float *)malloc(2u * batch * width * sizeof(float));
+    unsigned *frame_codes = (unsigned *)malloc(streams * sizeof(unsigned));
+    if (rows == NULL || frame_codes == NULL) { free(rows); free(frame_codes); return -1; }
+    float *hidden = rows + batch * width;
+    int rc = 0;
+    for (size_t b = 0; b < batch; ++b) eos_frame[b] = -1;
+    for (size_t f = 0; f < frames && rc == 0; ++f) {
+        for (size_t b = 0; b < batch && rc == 0; ++b) {
+            /* embed_audio_frame reads codes[codebook * stride + frame * stacking + fs] */
+            for (size_t fs = 0; fs < stacking; ++fs)
+                for (size_t c = 0; c < codebooks; ++c)
+                    frame_codes[c * stacking + fs] = codes[b * streams + fs * codebooks + c];
+            rc = embed_audio_frame(&r->model, frame_codes, stacking, 0u, rows + b * width, error, cap);
+        }
+        if (rc == 0) rc = ref_decoder_step_batch(r, decoders, rows, hidden, batch, error, cap);
+        for (size_t b = 0; b < batch && rc == 0; ++b) {
+            unsigned *tok = tokens_out + (f * batch + b) * streams;
+            rc = ref_heads_argmax(r, hidden + b * width, streams, f >= min_frames, tok, NULL, error, cap);
+            for (size_t s = 0; s < streams && rc == 0; ++s) {
+                if (tok[s] == eos_id && eos_frame[b] < 0) eos_frame[b] = (long)f;
+                codes[b * streams + s] = tok[s] < r->model.info.codebook_size ? tok[s] : 0u;
+            }
+        }
+    }
+    free(rows);
+    free(frame_codes);
+    return rc;
+}

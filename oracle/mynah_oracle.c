@@ -1,0 +1,717 @@
+/* CPU restatement of the Magpie decoder-step hot path of mynah-tts.
+ *
+ * TEST INFRASTRUCTURE ONLY.  This file is the parity checker for the CUDA
+ * library: tests, the smoke check and the benchmark's CPU-baseline leg may call
+ * it; no product code path links, loads or falls back to it.
+ *
+ * Every function restates, in plain scalar C11, what the reference computes
+ * when its host code is built the way its own CUDA variant builds it
+ * (`-std=c11 -O2`, no SIMD, no -ffast-math; Makefile:261): all reductions run
+ * in source order, products and sums are rounded separately (no contraction).
+ * Build this file with exactly those flags; anything else changes rounding.
+ *
+ * Parity pins: the reference's known answers (src/kernels.c:439-517,
+ * src/qmat.c:904-1179, src/backend.c:290-310, gpu/metal/backend_metal_ops.m:
+ * 1049-1079) and bit-equality with the reference's own sources compiled into
+ * oracle/_ref (checked in tests/ wherever that library exists, and through
+ * committed fixtures generated from it).
+ *
+ * f16 weights: the reference has no x86 implementation (src/qmat.c:22-28,
+ * 580-583), so that mode restates the aarch64 kernel (src/qmat.c:319-377) and
+ * is pinned only by the reference's own 1e-3 bound (src/qmat.c:1064-1104):
+ * "parity unpinned" beyond that bound.
+ */
+#include <float.h>
+#include <math.h>
+#include <stddef.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#define ORC_F32 0
+#define ORC_INT8 1
+#define ORC_INT4 2
+#define ORC_F16 3
+#define ORC_Q4_GROUP 32u
+#define ORC_K_MAX 8192u
+
+/* ------------------------------------------------------------ half floats */
+/* IEEE binary16 <-> binary32, round to nearest even: the `(__fp16)w[i]` cast
+ * of src/qmat.c:655. */
+uint16_t orc_f32_to_f16(float f) {
+    uint32_t x;
+    memcpy(&x, &f, 4);
+    const uint32_t sign = (x >> 16) & 0x8000u;
+    const uint32_t absx = x & 0x7fffffffu;
+    if (absx >= 0x7f800000u) { /* inf / nan */
+        return (uint16_t)(sign | 0x7c00u | (absx > 0x7f800000u ? 0x200u | ((absx >> 13) & 0x3ffu) : 0u));
+    }
+    if (absx >= 0x477ff000u) return (uint16_t)(sign | 0x7c00u); /* rounds to inf */
+    if (absx < 0x33000001u) return (uint16_t)sign;               /* rounds to zero */
+    int exp = (int)(absx >> 23) - 127;
+    uint32_t mant = (absx & 0x7fffffu) | 0x800000u;
+    uint32_t half;
+    if (exp < -14) { /* subnormal half */
+        const int shift = -14 - exp + 13;
+        const uint32_t rem_mask = (1u << shift) - 1u;
+        const uint32_t rem = mant & rem_mask;
+        const uint32_t halfway = 1u << (shift - 1);
+        half = mant >> shift;
+        if (rem > halfway || (rem == halfway && (half & 1u))) half += 1u;
+    } else {
+        half = ((uint32_t)(exp + 15) << 10) | ((mant >> 13) & 0x3ffu);
+        const uint32_t rem = mant & 0x1fffu;
+        if (rem > 0x1000u || (rem == 0x1000u && (half & 1u))) half += 1u;
+    }
+    return (uint16_t)(sign | half);
+}
+
+float orc_f16_to_f32(uint16_t h) {
+    const uint32_t sign = ((uint32_t)h & 0x8000u) << 16;
+    uint32_t exp = (h >> 10) & 0x1fu;
+    uint32_t mant = h & 0x3ffu;
+    uint32_t x;
+    if (exp == 0) {
+        if (mant == 0) x = sign;
+        else {
+            int e = -1;
+            do { mant <<= 1; ++e; } while ((mant & 0x400u) == 0);
+            x = sign | ((uint32_t)(127 - 15 - e) << 23) | ((mant & 0x3ffu) << 13);
+        }
+    } else if (exp == 31) {
+        x = sign | 0x7f800000u | (mant << 13);
+    } else {
+        x = sign | ((exp + 127 - 15) << 23) | (mant << 13);
+    }
+    float f;
+    memcpy(&f, &x, 4);
+    return f;
+}
+
+/* -------------------------------------------------------------- quantizers */
+/* src/qmat.c:39-57 */
+void orc_quantize_weight_int8(const float *w, size_t n, size_t k, int8_t *q, float *scales) {
+    for (size_t i = 0; i < n; ++i) {
+        const float *row = w + i * k;
+        float amax = 0.0f;
+        for (size_t j = 0; j < k; ++j) {
+            const float a = fabsf(row[j]);
+            if (a > amax) amax = a;
+        }
+        const float scale = amax > 0.0f ? amax / 127.0f : 1.0f;
+        scales[i] = scale;
+        const float inv = 1.0f / scale;
+        for (size_t j = 0; j < k; ++j) {
+            const float v = row[j] * inv;
+            q[i * k + j] = (int8_t)(v >= 0.0f ? v + 0.5f : v - 0.5f);
+        }
+    }
+}
+
+/* src/qmat.c:59-91: groups of 32 along k, low nibble = even index, +8 offset */
+void orc_quantize_weight_int4(const float *w, size_t n, size_t k, uint8_t *q, float *scales) {
+    const size_t groups = k / ORC_Q4_GROUP;
+    for (size_t i = 0; i < n; ++i) {
+        for (size_t g = 0; g < groups; ++g) {
+            const float *grp = w + i * k + g * ORC_Q4_GROUP;
+            float amax = 0.0f;
+            for (size_t j = 0; j < ORC_Q4_GROUP; ++j) {
+                const float a = fabsf(grp[j]);
+                if (a > amax) amax = a;
+            }
+            const float scale = amax > 0.0f ? amax / 7.0f : 1.0f;
+            scales[i * groups + g] = scale;
+            const float inv = 1.0f / scale;
+            for (size_t j = 0; j < ORC_Q4_GROUP; j += 2) {
+                const float v0 = grp[j] * inv;
+                const float v1 = grp[j + 1] * inv;
+                int q0 = (int)(v0 >= 0.0f ? v0 + 0.5f : v0 - 0.5f);
+                int q1 = (int)(v1 >= 0.0f ? v1 + 0.5f : v1 - 0.5f);
+                if (q0 < -8) q0 = -8;
+                if (q0 > 7) q0 = 7;
+                if (q1 < -8) q1 = -8;
+                if (q1 > 7) q1 = 7;
+                q[i * (k / 2u) + (g * ORC_Q4_GROUP + j) / 2u] = (uint8_t)((q0 + 8) | ((q1 + 8) << 4));
+            }
+        }
+    }
+}
+
+/* src/qmat.c:650-655 */
+void orc_quantize_weight_f16(const float *w, size_t count, uint16_t *h) {
+    for (size_t i = 0; i < count; ++i) h[i] = orc_f32_to_f16(w[i]);
+}
+
+/* src/qmat.c:93-113 */
+float orc_quantize_act_int8(int8_t *qx, const float *x, size_t k) {
+    float amax = 0.0f;
+    for (size_t i = 0; i < k; ++i) {
+        const float a = fabsf(x[i]);
+        if (a > amax) amax = a;
+    }
+    if (amax == 0.0f) {
+        memset(qx, 0, k);
+        return 0.0f;
+    }
+    const float inv = 127.0f / amax;
+    for (size_t i = 0; i < k; ++i) {
+        const float v = x[i] * inv;
+        int q = (int)(v >= 0.0f ? v + 0.5f : v - 0.5f);
+        if (q > 127) q = 127;
+        if (q < -127) q = -127;
+        qx[i] = (int8_t)q;
+    }
+    return amax / 127.0f;
+}
+
+/* ------------------------------------------------------------ dot kernels */
+/* src/qmat.c:136-152 (portable branch); the int32 sum is exact. */
+int32_t orc_dot_q8_i32(const int8_t *qx, const int8_t *w, size_t k) {
+    int32_t s = 0;
+    for (size_t j = 0; j < k; ++j) s += (int32_t)w[j] * (int32_t)qx[j];
+    return s;
+}
+
+float orc_dot_q8(const int8_t *qx, float sx, const int8_t *w, float ws, size_t k) {
+    return (float)orc_dot_q8_i32(qx, w, k) * ws * sx;
+}
+
+/* src/qmat.c:156-185 (portable branch): per group an exact int32 sum, then a
+ * float accumulation in group order. */
+float orc_dot_q4(const int8_t *qx, float sx, const uint8_t *q, const float *scales, size_t k) {
+    const size_t groups = k / ORC_Q4_GROUP;
+    float acc = 0.0f;
+    for (size_t g = 0; g < groups; ++g) {
+        int32_t gi = 0;
+        for (size_t j = 0; j < ORC_Q4_GROUP; j += 2) {
+            const uint8_t b = q[g * 16 + j / 2];
+            const int lo = (int)(b & 0x0F) - 8;
+            const int hi = (int)(b >> 4) - 8;
+            gi += lo * (int32_t)qx[g * 32 + j] + hi * (int32_t)qx[g * 32 + j + 1];
+        }
+        acc += (float)gi * scales[g];
+    }
+    return acc * sx;
+}
+
+/* src/qmat.c:364-376: two 4-lane fused accumulators (j%8 in 0..3 and 4..7),
+ * summed lane-wise, then a pairwise horizontal add, then the scalar tail. */
+float orc_dot_f16(const float *x, const uint16_t *w, size_t k) {
+    float a[4] = {0, 0, 0, 0}, b[4] = {0, 0, 0, 0};
+    size_t j = 0;
+    for (; j + 8u <= k; j += 8u) {
+        for (int l = 0; l < 4; ++l) {
+            a[l] = fmaf(orc_f16_to_f32(w[j + l]), x[j + l], a[l]);
+            b[l] = fmaf(orc_f16_to_f32(w[j + 4 + l]), x[j + 4 + l], b[l]);
+        }
+    }
+    const float c0 = a[0] + b[0], c1 = a[1] + b[1], c2 = a[2] + b[2], c3 = a[3] + b[3];
+    float s = (c0 + c1) + (c2 + c3);
+    for (; j < k; ++j) s += orc_f16_to_f32(w[j]) * x[j];
+    return s;
+}
+
+/* src/kernels.c:39-44 (portable branch) */
+float orc_dot_f32(const float *a, const float *b, size_t n) {
+    float sum = 0.0f;
+    for (size_t i = 0; i < n; ++i) sum += a[i] * b[i];
+    return sum;
+}
+
+/* -------------------------------------------------------------- layer ops */
+/* src/kernels.c:186-244 (portable branch).  Magpie passes bias NULL and
+ * epsilon 1e-5 (src/graph.c:147-150). */
+void orc_layernorm(const float *input, const float *weight, const float *bias,
+                   float *output, size_t rows, size_t width, float epsilon) {
+    for (size_t row = 0; row < rows; ++row) {
+        const float *x = input + row * width;
+        float *y = output + row * width;
+        float mean = 0.0f;
+        for (size_t i = 0; i < width; ++i) mean += x[i];
+        mean /= (float)width;
+        float variance = 0.0f;
+        for (size_t i = 0; i < width; ++i) {
+            const float d = x[i] - mean;
+            variance += d * d;
+        }
+        const float scale = 1.0f / sqrtf(variance / (float)width + epsilon);
+        for (size_t i = 0; i < width; ++i) {
+            y[i] = (x[i] - mean) * scale * weight[i] + (bias == NULL ? 0.0f : bias[i]);
+        }
+    }
+}
+
+/* src/kernels.c:382-389 */
+void orc_gelu_scalar(float *data, size_t n) {
+    for (size_t i = 0; i < n; ++i) {
+        const float x = data[i];
+        const float cubic = x * x * x;
+        const float c = 0.7978845608f * (x + 0.044715f * cubic);
+        data[i] = 0.5f * x * (1.0f + tanhf(c));
+    }
+}
+
+/* src/kernels.c:246-257 */
+void orc_residual_add(float *output, const float *input, size_t n) {
+    for (size_t i = 0; i < n; ++i) output[i] += input[i];
+}
+
+/* src/kernels.c:391-420 */
+int orc_softmax(const float *logits, float *probabilities, size_t n) {
+    if (n == 0) return -1;
+    float maximum = logits[0];
+    if (!isfinite(maximum)) return -1;
+    for (size_t i = 1; i < n; ++i) {
+        if (!isfinite(logits[i])) return -1;
+        if (logits[i] > maximum) maximum = logits[i];
+    }
+    float total = 0.0f;
+    for (size_t i = 0; i < n; ++i) {
+        probabilities[i] = expf(logits[i] - maximum);
+        total += probabilities[i];
+    }
+    if (!(total > 0.0f) || !isfinite(total)) return -1;
+    const float inverse_total = 1.0f / total;
+    for (size_t i = 0; i < n; ++i) probabilities[i] *= inverse_total;
+    return 0;
+}
+
+/* Constrained greedy pick, first index wins ties: src/backend.c:825-847 and
+ * src/graph.c:1551-1566.  Candidates: ids below codebook_size, plus eos_id
+ * when allow_eos. */
+unsigned orc_argmax_constrained(const float *logits, size_t vocab, size_t codebook_size,
+                                size_t eos_id, int allow_eos) {
+    float best = -FLT_MAX;
+    unsigned result = 0u;
+    for (size_t i = 0; i < vocab; ++i) {
+        if (!(i < codebook_size || (allow_eos && i == eos_id))) continue;
+        if (logits[i] > best) {
+            best = logits[i];
+            result = (unsigned)i;
+        }
+    }
+    return result;
+}
+
+/* ------------------------------------------------------- quantized linear */
+typedef struct {
+    int qtype;          /* effective type of this tensor (may fall back to f32) */
+    size_t n, k;
+    const float *w;     /* borrowed f32 weight [n,k] */
+    int8_t *q8;
+    uint8_t *q4;
+    uint16_t *f16;
+    float *scales;
+} orc_qweight;
+
+/* The get-or-create of src/qmat.c:627-679: INT4 refuses k not a multiple of 32
+ * and the caller then uses the exact f32 product. */
+int orc_qweight_init(orc_qweight *e, int qtype, const float *w, size_t n, size_t k) {
+    memset(e, 0, sizeof(*e));
+    e->n = n;
+    e->k = k;
+    e->w = w;
+    e->qtype = qtype;
+    if (k > ORC_K_MAX) e->qtype = ORC_F32;                        /* src/qmat.c:773-774 */
+    if (qtype == ORC_INT4 && (k % ORC_Q4_GROUP) != 0) e->qtype = ORC_F32;
+    if (e->qtype == ORC_INT8) {
+        e->q8 = (int8_t *)malloc(n * k);
+        e->scales = (float *)malloc(n * sizeof(float));
+        if (!e->q8 || !e->scales) return -1;
+        orc_quantize_weight_int8(w, n, k, e->q8, e->scales);
+    } else if (e->qtype == ORC_INT4) {
+        e->q4 = (uint8_t *)malloc(n * (k / 2u));
+        e->scales = (float *)malloc(n * (k / ORC_Q4_GROUP) * sizeof(float));
+        if (!e->q4 || !e->scales) return -1;
+        orc_quantize_weight_int4(w, n, k, e->q4, e->scales);
+    } else if (e->qtype == ORC_F16) {
+        e->f16 = (uint16_t *)malloc(n * k * sizeof(uint16_t));
+        if (!e->f16) return -1;
+        orc_quantize_weight_f16(w, n * k, e->f16);
+    }
+    return 0;
+}
+
+void orc_qweight_free(orc_qweight *e) {
+    free(e->q8);
+    free(e->q4);
+    free(e->f16);
+    free(e->scales);
+    memset(e, 0, sizeof(*e));
+}
+
+/* One activation row through a (possibly quantized) weight:
+ * src/qmat.c:768-818 with the portable kernels; the f32 case is the scalar
+ * backend product of src/backend.c:283-291. */
+void orc_linear_row(const orc_qweight *e, const float *x, float *out, const float *bias) {
+    const size_t n = e->n, k = e->k;
+    if (e->qtype == ORC_F32) {
+        for (size_t r = 0; r < n; ++r) out[r] = orc_dot_f32(e->w + r * k, x, k);
+        if (bias != NULL) for (size_t r = 0; r < n; ++r) out[r] += bias[r];
+        return;
+    }
+    if (e->qtype == ORC_F16) {
+        for (size_t r = 0; r < n; ++r)
+            out[r] = orc_dot_f16(x, e->f16 + r * k, k) + (bias == NULL ? 0.0f : bias[r]);
+        return;
+    }
+    int8_t qx[ORC_K_MAX];
+    const float sx = orc_quantize_act_int8(qx, x, k);
+    for (size_t r = 0; r < n; ++r) {
+        float value = e->qtype == ORC_INT8
+                          ? orc_dot_q8(qx, sx, e->q8 + r * k, e->scales[r], k)
+                          : orc_dot_q4(qx, sx, e->q4 + r * (k / 2u),
+                                       e->scales + r * (k / ORC_Q4_GROUP), k);
+        if (bias != NULL) value += bias[r];
+        out[r] = value;
+    }
+}
+
+/* Stand-alone form used by the single-op tests: y = LN(x) W^T + b when gain is
+ * given, else y = x W^T + b.  rows are independent (src/qmat.c:790-816). */
+int orc_qmat_linear(int qtype, const float *w, const float *x, float *out, size_t count,
+                    size_t k, size_t n, const float *bias, const float *ln_gain) {
+    orc_qweight e;
+    if (orc_qweight_init(&e, qtype, w, n, k) != 0) return -1;
+    float *nrm = (float *)malloc(k * sizeof(float));
+    if (nrm == NULL) { orc_qweight_free(&e); return -1; }
+    for (size_t t = 0; t < count; ++t) {
+        const float *xr = x + t * k;
+        if (ln_gain != NULL) {
+            orc_layernorm(xr, ln_gain, NULL, nrm, 1u, k, 1.0e-5f);
+            xr = nrm;
+        }
+        orc_linear_row(&e, xr, out + t * n, bias);
+    }
+    free(nrm);
+    orc_qweight_free(&e);
+    return 0;
+}
+
+/* --------------------------------------------------------------- attention */
+/* Single-query attention of one head over `valid` cached rows:
+ * src/graph.c:3182-3202 (self, stride = width) and 3221-3244 (cross). */
+void orc_attend_head(const float *q, const float *kbase, const float *vbase, size_t valid,
+                     size_t stride, size_t hw, float scale, float *scores, float *out) {
+    float maxv = -FLT_MAX;
+    for (size_t s = 0; s < valid; ++s) {
+        const float *k = kbase + s * stride;
+        float sc = 0.0f;
+        for (size_t d = 0; d < hw; ++d) sc += q[d] * k[d];
+        sc *= scale;
+        scores[s] = sc;
+        if (sc > maxv) maxv = sc;
+    }
+    float denom = 0.0f;
+    for (size_t s = 0; s < valid; ++s) {
+        scores[s] = expf(scores[s] - maxv);
+        denom += scores[s];
+    }
+    memset(out, 0, hw * sizeof(float));
+    for (size_t s = 0; s < valid; ++s) {
+        const float weight = scores[s] / denom;
+        const float *v = vbase + s * stride;
+        for (size_t d = 0; d < hw; ++d) out[d] += weight * v[d];
+    }
+}
+
+/* The resident-attention contract of src/backend.h:135-154: append K/V at
+ * `position`, attend rows below `valid`, `heads` heads of `head_width`. */
+void orc_self_attention(const float *qkv, float *k_cache, float *v_cache, size_t position,
+                        size_t cache_stride, size_t valid, size_t heads, size_t head_width,
+                        float scale, float *out, float *scores) {
+    const size_t width = heads * head_width;
+    memcpy(k_cache + position * cache_stride, qkv + width, width * sizeof(float));
+    memcpy(v_cache + position * cache_stride, qkv + 2u * width, width * sizeof(float));
+    for (size_t h = 0; h < heads; ++h)
+        orc_attend_head(qkv + h * head_width, k_cache + h * head_width,
+                        v_cache + h * head_width, valid, cache_stride, head_width, scale,
+                        scores, out + h * head_width);
+}
+
+void orc_cross_attention(const float *q, const float *k_cache, const float *v_cache,
+                         size_t valid, size_t cache_stride, size_t heads, size_t head_width,
+                         float scale, float *out, float *scores) {
+    for (size_t h = 0; h < heads; ++h)
+        orc_attend_head(q + h * head_width, k_cache + h * head_width,
+                        v_cache + h * head_width, valid, cache_stride, head_width, scale,
+                        scores, out + h * head_width);
+}
+
+/* ------------------------------------------------------------------ model */
+typedef struct {
+    const float *norm_self, *norm_xattn_query, *norm_xattn_memory, *norm_pos_ff;
+    orc_qweight qkv, o_self, q_cross, o_cross, ffn_up, ffn_down;
+    const float *kv_cross_w; /* f32 [2*xw, width], used once per request */
+} orc_layer;
+
+typedef struct {
+    size_t layers, width, heads, head_width, ffn_width, xattn_width;
+    size_t tables, vocab, codebook_size, eos_id;
+    int qtype;
+    const float *position;   /* [max_positions, width] */
+    const float *norm_out;   /* [width] */
+    const float *const *embeddings; /* tables x [vocab, width] */
+    orc_layer *layer;
+    orc_qweight *head;       /* tables x [vocab, width] */
+    const float *const *head_bias;
+} orc_model;
+
+/* The caller passes flat arrays of pointers, one entry per layer, in the field
+ * order of decoder_layer_resolved (src/graph.c:2795-2811) plus the two
+ * cross-memory tensors decoder_cache_init reads (src/graph.c:3002-3016). */
+orc_model *orc_model_new(size_t layers, size_t width, size_t heads, size_t xattn_width,
+                         int qtype, const float *position, const float *norm_out,
+                         const float *const *norm_self, const float *const *norm_xattn_query,
+                         const float *const *norm_xattn_memory, const float *const *norm_pos_ff,
+                         const float *const *qkv_w, const float *const *o_self_w,
+                         const float *const *q_cross_w, const float *const *kv_cross_w,
+                         const float *const *o_cross_w, const float *const *ffn_up_w,
+                         const float *const *ffn_down_w,
+                         size_t tables, size_t vocab, size_t codebook_size, size_t eos_id,
+                         const float *const *embeddings, const float *const *head_w,
+                         const float *const *head_b) {
+    orc_model *m = (orc_model *)calloc(1, sizeof(*m));
+    if (m == NULL) return NULL;
+    m->layers = layers;
+    m->width = width;
+    m->heads = heads;
+    m->head_width = width / heads;
+    m->ffn_width = width * 4u;                      /* src/graph.c:2973 */
+    m->xattn_width = xattn_width;
+    m->qtype = qtype;
+    m->position = position;
+    m->norm_out = norm_out;
+    m->tables = tables;
+    m->vocab = vocab;
+    m->codebook_size = codebook_size;
+    m->eos_id = eos_id;
+    m->embeddings = embeddings;
+    m->head_bias = head_b;
+    m->layer = (orc_layer *)calloc(layers, sizeof(orc_layer));
+    m->head = (orc_qweight *)calloc(tables ? tables : 1u, sizeof(orc_qweight));
+    if (m->layer == NULL || m->head == NULL) return NULL;
+    const size_t w = width, f = m->ffn_width, xw = xattn_width;
+    for (size_t l = 0; l < layers; ++l) {
+        orc_layer *L = &m->layer[l];
+        L->norm_self = norm_self[l];
+        L->norm_xattn_query = norm_xattn_query[l];
+        L->norm_xattn_memory = norm_xattn_memory[l];
+        L->norm_pos_ff = norm_pos_ff[l];
+        L->kv_cross_w = kv_cross_w[l];
+        if (orc_qweight_init(&L->qkv, qtype, qkv_w[l], 3u * w, w) != 0 ||
+            orc_qweight_init(&L->o_self, qtype, o_self_w[l], w, w) != 0 ||
+            orc_qweight_init(&L->q_cross, qtype, q_cross_w[l], xw, w) != 0 ||
+            orc_qweight_init(&L->o_cross, qtype, o_cross_w[l], w, xw) != 0 ||
+            orc_qweight_init(&L->ffn_up, qtype, ffn_up_w[l], f, w) != 0 ||
+            orc_qweight_init(&L->ffn_down, qtype, ffn_down_w[l], w, f) != 0)
+            return NULL;
+    }
+    for (size_t t = 0; t < tables; ++t)
+        if (head_w != NULL && orc_qweight_init(&m->head[t], qtype, head_w[t], vocab, w) != 0)
+            return NULL;
+    return m;
+}
+
+void orc_model_free(orc_model *m) {
+    if (m == NULL) return;
+    for (size_t l = 0; l < m->layers; ++l) {
+        orc_layer *L = &m->layer[l];
+        orc_qweight_free(&L->qkv);
+        orc_qweight_free(&L->o_self);
+        orc_qweight_free(&L->q_cross);
+        orc_qweight_free(&L->o_cross);
+        orc_qweight_free(&L->ffn_up);
+        orc_qweight_free(&L->ffn_down);
+    }
+    for (size_t t = 0; t < m->tables; ++t) orc_qweight_free(&m->head[t]);
+    free(m->layer);
+    free(m->head);
+    free(m);
+}
+
+/* One request's decoder state: the KV layout of src/graph.c:2813-2826. */
+typedef struct {
+    const orc_model *m;
+    size_t memory_length, capacity, length, layers_run;
+    float *self_k, *self_v;   /* [layers][capacity][width] */
+    float *cross_k, *cross_v; /* [layers][memory_length][xattn_width] */
+    float *x, *nrm, *qkv, *attn, *proj, *q_x, *xctx, *hidden, *scores;
+} orc_stream;
+
+void orc_stream_free(orc_stream *s) {
+    if (s == NULL) return;
+    free(s->self_k); free(s->self_v); free(s->cross_k); free(s->cross_v);
+    free(s->x); free(s->nrm); free(s->qkv); free(s->attn); free(s->proj);
+    free(s->q_x); free(s->xctx); free(s->hidden); free(s->scores);
+    free(s);
+}
+
+/* src/graph.c:2963-3030: cross K/V = LN_memory(memory) @ kv_net^T, K in the
+ * first xw columns, V in the next xw; f32 product (the prefill is never
+ * quantized for more than 16 rows, and this restatement keeps it f32 for any
+ * row count, which equals the reference whenever memory_length > 16 or the
+ * cache is f32).  Self KV starts empty. */
+orc_stream *orc_stream_new(const orc_model *m, const float *memory, size_t memory_length,
+                           size_t capacity) {
+    orc_stream *s = (orc_stream *)calloc(1, sizeof(*s));
+    if (s == NULL) return NULL;
+    const size_t w = m->width, xw = m->xattn_width;
+    s->m = m;
+    s->memory_length = memory_length;
+    s->capacity = capacity;
+    s->layers_run = m->layers;
+    s->self_k = (float *)calloc(m->layers * capacity * w, sizeof(float));
+    s->self_v = (float *)calloc(m->layers * capacity * w, sizeof(float));
+    s->cross_k = (float *)calloc(m->layers * memory_length * xw, sizeof(float));
+    s->cross_v = (float *)calloc(m->layers * memory_length * xw, sizeof(float));
+    s->x = (float *)calloc(w, sizeof(float));
+    s->nrm = (float *)calloc(w, sizeof(float));
+    s->qkv = (float *)calloc(3u * w, sizeof(float));
+    s->attn = (float *)calloc(w, sizeof(float));
+    s->proj = (float *)calloc(w, sizeof(float));
+    s->q_x = (float *)calloc(xw, sizeof(float));
+    s->xctx = (float *)calloc(xw, sizeof(float));
+    s->hidden = (float *)calloc(m->ffn_width, sizeof(float));
+    s->scores = (float *)calloc(capacity > memory_length ? capacity : memory_length, sizeof(float));
+    float *mem_norm = (float *)calloc(memory_length * w, sizeof(float));
+    float *kv = (float *)calloc(2u * xw, sizeof(float));
+    if (!s->self_k || !s->self_v || !s->cross_k || !s->cross_v || !s->x || !s->nrm ||
+        !s->qkv || !s->attn || !s->proj || !s->q_x || !s->xctx || !s->hidden ||
+        !s->scores || !mem_norm || !kv) {
+        free(mem_norm); free(kv); orc_stream_free(s);
+        return NULL;
+    }
+    for (size_t l = 0; l < m->layers; ++l) {
+        const orc_layer *L = &m->layer[l];
+        orc_layernorm(memory, L->norm_xattn_memory, NULL, mem_norm, memory_length, w, 1.0e-5f);
+        float *ck = s->cross_k + l * memory_length * xw;
+        float *cv = s->cross_v + l * memory_length * xw;
+        for (size_t t = 0; t < memory_length; ++t) {
+            for (size_t r = 0; r < 2u * xw; ++r)
+                kv[r] = orc_dot_f32(L->kv_cross_w + r * w, mem_norm + t * w, w);
+            memcpy(ck + t * xw, kv, xw * sizeof(float));
+            memcpy(cv + t * xw, kv + xw, xw * sizeof(float));
+        }
+    }
+    free(mem_norm);
+    free(kv);
+    return s;
+}
+
+float *orc_stream_self_k(orc_stream *s) { return s->self_k; }
+float *orc_stream_self_v(orc_stream *s) { return s->self_v; }
+float *orc_stream_cross_k(orc_stream *s) { return s->cross_k; }
+float *orc_stream_cross_v(orc_stream *s) { return s->cross_v; }
+size_t orc_stream_length(const orc_stream *s) { return s->length; }
+void orc_stream_set_length(orc_stream *s, size_t n) { s->length = n; }
+/* Run only the first `n` layers (then the output norm): gives per-layer hidden
+ * states for the parity ladder without touching the arithmetic. */
+void orc_stream_set_layers(orc_stream *s, size_t n) { s->layers_run = n; }
+
+/* src/graph.c:3127-3284 for one slot.  The reference's batched form runs the
+ * same arithmetic per (weight row, activation) pair and asserts bit-equality
+ * with the single-slot form (src/qmat.c:1107-1179), so a batch is a loop. */
+int orc_decoder_step(orc_stream *s, const float *input, float *out) {
+    const orc_model *m = s->m;
+    const size_t w = m->width, heads = m->heads, hw = m->head_width;
+    const size_t ffn = m->ffn_width, xw = m->xattn_width;
+    if (s->length >= s->capacity) return -1;
+    const float self_scale = 1.0f / sqrtf((float)hw);
+    const float cross_scale = 1.0f / sqrtf((float)xw);
+    const float *pe = m->position + s->length * w;
+    for (size_t d = 0; d < w; ++d) s->x[d] = input[d] + pe[d];
+    for (size_t l = 0; l < s->layers_run; ++l) {
+        const orc_layer *L = &m->layer[l];
+        orc_layernorm(s->x, L->norm_self, NULL, s->nrm, 1u, w, 1.0e-5f);
+        orc_linear_row(&L->qkv, s->nrm, s->qkv, NULL);
+        orc_self_attention(s->qkv, s->self_k + l * s->capacity * w,
+                           s->self_v + l * s->capacity * w, s->length, w, s->length + 1u,
+                           heads, hw, self_scale, s->attn, s->scores);
+        orc_linear_row(&L->o_self, s->attn, s->proj, NULL);
+        for (size_t d = 0; d < w; ++d) s->x[d] += s->proj[d];
+        orc_layernorm(s->x, L->norm_xattn_query, NULL, s->nrm, 1u, w, 1.0e-5f);
+        orc_linear_row(&L->q_cross, s->nrm, s->q_x, NULL);
+        orc_cross_attention(s->q_x, s->cross_k + l * s->memory_length * xw,
+                            s->cross_v + l * s->memory_length * xw, s->memory_length, xw,
+                            1u, xw, cross_scale, s->xctx, s->scores);
+        orc_linear_row(&L->o_cross, s->xctx, s->proj, NULL);
+        for (size_t d = 0; d < w; ++d) s->x[d] += s->proj[d];
+        orc_layernorm(s->x, L->norm_pos_ff, NULL, s->nrm, 1u, w, 1.0e-5f);
+        orc_linear_row(&L->ffn_up, s->nrm, s->hidden, NULL);
+        orc_gelu_scalar(s->hidden, ffn);
+        orc_linear_row(&L->ffn_down, s->hidden, s->proj, NULL);
+        for (size_t d = 0; d < w; ++d) s->x[d] += s->proj[d];
+    }
+    orc_layernorm(s->x, m->norm_out, NULL, out, 1u, w, 1.0e-5f);
+    s->length += 1u;
+    return 0;
+}
+
+/* src/graph.c:760-804 with the table index flattened: the reference walks
+ * stream = fs * codebooks + codebook over stacking * codebooks tables and
+ * divides the sum by their count. */
+int orc_embed_frame(const orc_model *m, const unsigned *codes, float *row) {
+    const size_t w = m->width;
+    memset(row, 0, w * sizeof(float));
+    for (size_t t = 0; t < m->tables; ++t) {
+        if (codes[t] >= m->vocab) return -1;
+        const float *e = m->embeddings[t] + (size_t)codes[t] * w;
+        for (size_t d = 0; d < w; ++d) row[d] += e[d];
+    }
+    for (size_t d = 0; d < w; ++d) row[d] /= (float)m->tables;
+    return 0;
+}
+
+/* Per-table logits through the (quantized) projection with bias, then the
+ * masked first-on-ties pick: src/graph.c:1538-1566.  `logits` may be NULL. */
+void orc_heads_argmax(const orc_model *m, const float *hidden, int allow_eos,
+                      unsigned *tokens, float *logits) {
+    float *tmp = logits != NULL ? NULL : (float *)malloc(m->vocab * sizeof(float));
+    for (size_t t = 0; t < m->tables; ++t) {
+        float *lg = logits != NULL ? logits + t * m->vocab : tmp;
+        orc_linear_row(&m->head[t], hidden, lg, m->head_bias[t]);
+        tokens[t] = orc_argmax_constrained(lg, m->vocab, m->codebook_size, m->eos_id, allow_eos);
+    }
+    free(tmp);
+}
+
+/* One greedy frame for one request: embed the previous frame's stored codes,
+ * step the decoder, pick one token per table.  The stored code collapses
+ * non-code picks to 0 (src/graph.c:3900, 1626-1630); the frame reports EOS if
+ * any table picked it (src/graph.c:3893-3897).  Returns 1 on EOS, 0 otherwise,
+ * -1 on error. */
+int orc_greedy_frame(orc_stream *s, unsigned *codes, int allow_eos, unsigned *tokens,
+                     float *hidden_out) {
+    const orc_model *m = s->m;
+    float *row = (float *)malloc(2u * m->width * sizeof(float));
+    if (row == NULL) return -1;
+    float *hidden = row + m->width;
+    int eos = 0;
+    if (orc_embed_frame(m, codes, row) != 0 || orc_decoder_step(s, row, hidden) != 0) {
+        free(row);
+        return -1;
+    }
+    orc_heads_argmax(m, hidden, allow_eos, tokens, NULL);
+    for (size_t t = 0; t < m->tables; ++t) {
+        if (tokens[t] == m->eos_id) eos = 1;
+        codes[t] = tokens[t] < m->codebook_size ? tokens[t] : 0u;
+    }
+    if (hidden_out != NULL) memcpy(hidden_out, hidden, m->width * sizeof(float));
+    free(row);
+    return eos;
+}
+
+/* Greedy decode of `frames` frames; tokens_out is [frames][tables].  EOS is
+ * allowed from frame `min_frames` on and ends the request; returns the number
+ * of frames produced (the EOS frame included). */
+long orc_greedy_decode(orc_stream *s, unsigned *codes, size_t frames, size_t min_frames,
+                       unsigned *tokens_out) {
+    const size_t tables = s->m->tables;
+    for (size_t f = 0; f < frames; ++f) {
+        const int eos = orc_greedy_frame(s, codes, f >= min_frames, tokens_out + f * tables, NULL);
+        if (eos < 0) return -1;
+        if (eos) return (long)(f + 1u);
+    }
+    return (long)frames;
+}

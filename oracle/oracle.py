@@ -1,0 +1,528 @@
+"""ctypes front end of the parity checkers.  TEST INFRASTRUCTURE ONLY.
+
+Two libraries sit behind this module:
+
+* ``liboracle_port.so`` -- the C restatement in ``mynah_oracle.c`` (class
+  ``Port`` / ``PortModel`` / ``PortStream``); built by ``make -C oracle port``.
+* ``_ref/libmynah_ref_{strict,fast}.so`` -- the reference's own sources compiled
+  around the harness (class ``Ref`` / ``RefModel`` / ``RefDecoder``); present
+  only where ``make -C oracle ref`` could see a reference checkout.
+
+Only tests, the smoke check and the benchmark's CPU-baseline leg import this.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+import tempfile
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+PORT_SO = os.path.join(HERE, "liboracle_port.so")
+REF_SO = {kind: os.path.join(HERE, "_ref", f"libmynah_ref_{kind}.so") for kind in ("strict", "fast")}
+
+F32, INT8, INT4, F16 = 0, 1, 2, 3
+QTYPES = {"f32": F32, "int8": INT8, "int4": INT4, "f16": F16}
+
+c_float_p = C.POINTER(C.c_float)
+c_uint_p = C.POINTER(C.c_uint)
+
+
+def build_port() -> str:
+    subprocess.run(["make", "-C", HERE, "port"], check=True, capture_output=True)
+    return PORT_SO
+
+
+def have_ref(kind: str = "strict") -> bool:
+    return os.path.exists(REF_SO[kind])
+
+
+def _fp(a: np.ndarray):
+    assert a.dtype == np.float32 and a.flags["C_CONTIGUOUS"]
+    return a.ctypes.data_as(c_float_p)
+
+
+def _ptr_array(arrays):
+    arr = (c_float_p * len(arrays))()
+    for i, a in enumerate(arrays):
+        arr[i] = _fp(a)
+    return arr
+
+
+class Port:
+    """Typed access to liboracle_port.so."""
+
+    _instance = None
+
+    def __init__(self):
+        if not os.path.exists(PORT_SO) or os.path.getmtime(PORT_SO) < os.path.getmtime(
+                os.path.join(HERE, "mynah_oracle.c")):
+            build_port()
+        self.lib = lib = C.CDLL(PORT_SO)
+        sz = C.c_size_t
+        lib.orc_f32_to_f16.restype = C.c_uint16
+        lib.orc_f32_to_f16.argtypes = [C.c_float]
+        lib.orc_f16_to_f32.restype = C.c_float
+        lib.orc_f16_to_f32.argtypes = [C.c_uint16]
+        lib.orc_quantize_act_int8.restype = C.c_float
+        lib.orc_quantize_act_int8.argtypes = [C.c_void_p, c_float_p, sz]
+        lib.orc_dot_q8.restype = C.c_float
+        lib.orc_dot_q4.restype = C.c_float
+        lib.orc_dot_f16.restype = C.c_float
+        lib.orc_dot_f32.restype = C.c_float
+        lib.orc_dot_f32.argtypes = [c_float_p, c_float_p, sz]
+        lib.orc_layernorm.argtypes = [c_float_p, c_float_p, c_float_p, c_float_p, sz, sz, C.c_float]
+        lib.orc_qmat_linear.argtypes = [C.c_int, c_float_p, c_float_p, c_float_p, sz, sz, sz,
+                                        c_float_p, c_float_p]
+        lib.orc_argmax_constrained.restype = C.c_uint
+        lib.orc_argmax_constrained.argtypes = [c_float_p, sz, sz, sz, C.c_int]
+        lib.orc_self_attention.argtypes = [c_float_p, c_float_p, c_float_p, sz, sz, sz, sz, sz,
+                                           C.c_float, c_float_p, c_float_p]
+        lib.orc_cross_attention.argtypes = [c_float_p, c_float_p, c_float_p, sz, sz, sz, sz,
+                                            C.c_float, c_float_p, c_float_p]
+        lib.orc_model_new.restype = C.c_void_p
+        lib.orc_model_free.argtypes = [C.c_void_p]
+        lib.orc_stream_new.restype = C.c_void_p
+        lib.orc_stream_new.argtypes = [C.c_void_p, c_float_p, sz, sz]
+        lib.orc_stream_free.argtypes = [C.c_void_p]
+        for name in ("self_k", "self_v", "cross_k", "cross_v"):
+            fn = getattr(lib, f"orc_stream_{name}")
+            fn.restype = c_float_p
+            fn.argtypes = [C.c_void_p]
+        lib.orc_stream_length.restype = sz
+        lib.orc_stream_length.argtypes = [C.c_void_p]
+        lib.orc_stream_set_length.argtypes = [C.c_void_p, sz]
+        lib.orc_stream_set_layers.argtypes = [C.c_void_p, sz]
+        lib.orc_decoder_step.argtypes = [C.c_void_p, c_float_p, c_float_p]
+        lib.orc_embed_frame.argtypes = [C.c_void_p, c_uint_p, c_float_p]
+        lib.orc_heads_argmax.argtypes = [C.c_void_p, c_float_p, C.c_int, c_uint_p, c_float_p]
+        lib.orc_greedy_frame.argtypes = [C.c_void_p, c_uint_p, C.c_int, c_uint_p, c_float_p]
+        lib.orc_greedy_decode.restype = C.c_long
+        lib.orc_greedy_decode.argtypes = [C.c_void_p, c_uint_p, sz, sz, c_uint_p]
+
+    @classmethod
+    def get(cls) -> "Port":
+        if cls._instance is None:
+            cls._instance = cls()
+        return cls._instance
+
+    # ---- single ops -----------------------------------------------------
+    def quantize_weight_int8(self, w: np.ndarray):
+        n, k = w.shape
+        q = np.empty((n, k), np.int8)
+        s = np.empty((n,), np.float32)
+        self.lib.orc_quantize_weight_int8(_fp(w), C.c_size_t(n), C.c_size_t(k),
+                                          q.ctypes.data_as(C.c_void_p), _fp(s))
+        return q, s
+
+    def quantize_weight_int4(self, w: np.ndarray):
+        n, k = w.shape
+        q = np.empty((n, k // 2), np.uint8)
+        s = np.empty((n, k // 32), np.float32)
+        self.lib.orc_quantize_weight_int4(_fp(w), C.c_size_t(n), C.c_size_t(k),
+                                          q.ctypes.data_as(C.c_void_p), _fp(s))
+        return q, s
+
+    def quantize_weight_f16(self, w: np.ndarray):
+        h = np.empty(w.shape, np.uint16)
+        self.lib.orc_quantize_weight_f16(_fp(w), C.c_size_t(w.size), h.ctypes.data_as(C.c_void_p))
+        return h
+
+    def quantize_act_int8(self, x: np.ndarray):
+        q = np.empty(x.shape, np.int8)
+        sx = self.lib.orc_quantize_act_int8(q.ctypes.data_as(C.c_void_p), _fp(x), x.size)
+        return q, np.float32(sx)
+
+    def layernorm(self, x: np.ndarray, gain: np.ndarray, eps: float = 1e-5) -> np.ndarray:
+        x2 = np.ascontiguousarray(x.reshape(-1, x.shape[-1]))
+        y = np.empty_like(x2)
+        self.lib.orc_layernorm(_fp(x2), _fp(gain), None, _fp(y), x2.shape[0], x2.shape[1], eps)
+        return y.reshape(x.shape)
+
+    def gelu(self, x: np.ndarray) -> np.ndarray:
+        y = np.ascontiguousarray(x.copy())
+        self.lib.orc_gelu_scalar(_fp(y), C.c_size_t(y.size))
+        return y
+
+    def qmat_linear(self, qtype: int, w: np.ndarray, x: np.ndarray, bias=None, ln_gain=None):
+        x2 = np.ascontiguousarray(x.reshape(-1, x.shape[-1]))
+        n, k = w.shape[0], w.shape[1]
+        out = np.empty((x2.shape[0], n), np.float32)
+        rc = self.lib.orc_qmat_linear(qtype, _fp(w), _fp(x2), _fp(out), x2.shape[0], k, n,
+                                      None if bias is None else _fp(bias),
+                                      None if ln_gain is None else _fp(ln_gain))
+        assert rc == 0
+        return out
+
+    def argmax_constrained(self, logits, codebook_size, eos_id, allow_eos) -> int:
+        return int(self.lib.orc_argmax_constrained(_fp(logits), logits.size, codebook_size, eos_id,
+                                                   int(allow_eos)))
+
+    def self_attention(self, qkv, k_cache, v_cache, position, stride, valid, heads, hw, scale):
+        out = np.empty((heads * hw,), np.float32)
+        scores = np.empty((max(valid, 1),), np.float32)
+        self.lib.orc_self_attention(_fp(qkv), _fp(k_cache), _fp(v_cache), position, stride, valid,
+                                    heads, hw, scale, _fp(out), _fp(scores))
+        return out
+
+    def cross_attention(self, q, k_cache, v_cache, valid, stride, heads, hw, scale):
+        out = np.empty((heads * hw,), np.float32)
+        scores = np.empty((max(valid, 1),), np.float32)
+        self.lib.orc_cross_attention(_fp(q), _fp(k_cache), _fp(v_cache), valid, stride, heads, hw,
+                                     scale, _fp(out), _fp(scores))
+        return out
+
+
+class PortModel:
+    """orc_model over a mynah_tts_b200.synth.SynthModel (weights are borrowed:
+    the SynthModel must outlive this object)."""
+
+    def __init__(self, synth, qtype: int):
+        self.port = Port.get()
+        self.synth = synth
+        self.qtype = qtype
+        s = synth.shape
+        L = range(s.layers)
+
+        def col(suffix):
+            return [synth.layer(i, suffix) for i in L]
+
+        self._keep = [
+            _ptr_array(col("norm_self.weight")), _ptr_array(col("norm_xattn_query.weight")),
+            _ptr_array(col("norm_xattn_memory.weight")), _ptr_array(col("norm_pos_ff.weight")),
+            _ptr_array(col("self_attention.qkv_net.weight")),
+            _ptr_array(col("self_attention.o_net.weight")),
+            _ptr_array(col("cross_attention.q_net.weight")),
+            _ptr_array(col("cross_attention.kv_net.weight")),
+            _ptr_array(col("cross_attention.o_net.weight")),
+            _ptr_array(col("pos_ff.proj.conv.weight")), _ptr_array(col("pos_ff.o_net.conv.weight")),
+            _ptr_array([synth.embedding(t) for t in range(s.tables)]),
+            _ptr_array([synth.head_weight(t) for t in range(s.tables)]),
+            _ptr_array([synth.head_bias(t) for t in range(s.tables)]),
+        ]
+        k = self._keep
+        sz = C.c_size_t
+        self.handle = C.c_void_p(self.port.lib.orc_model_new(
+            sz(s.layers), sz(s.width), sz(s.heads), sz(s.xattn_width), C.c_int(qtype),
+            _fp(synth.position), _fp(synth.norm_out),
+            k[0], k[1], k[2], k[3], k[4], k[5], k[6], k[7], k[8], k[9], k[10],
+            sz(s.tables), sz(s.vocab), sz(s.codebook_size), sz(s.eos_id), k[11], k[12], k[13]))
+        assert self.handle.value
+
+    def close(self):
+        if self.handle:
+            self.port.lib.orc_model_free(self.handle)
+            self.handle = None
+
+    def new_stream(self, memory: np.ndarray, capacity: int) -> "PortStream":
+        return PortStream(self, memory, capacity)
+
+    def embed_frame(self, codes: np.ndarray) -> np.ndarray:
+        row = np.empty((self.synth.shape.width,), np.float32)
+        codes = np.ascontiguousarray(codes, np.uint32)
+        assert self.port.lib.orc_embed_frame(self.handle, codes.ctypes.data_as(c_uint_p), _fp(row)) == 0
+        return row
+
+    def heads_argmax(self, hidden: np.ndarray, allow_eos: bool):
+        s = self.synth.shape
+        tokens = np.empty((s.tables,), np.uint32)
+        logits = np.empty((s.tables, s.vocab), np.float32)
+        self.port.lib.orc_heads_argmax(self.handle, _fp(hidden), int(allow_eos),
+                                       tokens.ctypes.data_as(c_uint_p), _fp(logits))
+        return tokens, logits
+
+
+class PortStream:
+    def __init__(self, model: PortModel, memory: np.ndarray, capacity: int):
+        self.model = model
+        self.lib = model.port.lib
+        self.capacity = capacity
+        self.memory_length = memory.shape[0]
+        self.handle = C.c_void_p(self.lib.orc_stream_new(model.handle, _fp(memory),
+                                                         memory.shape[0], capacity))
+        assert self.handle.value
+
+    def close(self):
+        if self.handle:
+            self.lib.orc_stream_free(self.handle)
+            self.handle = None
+
+    def _view(self, name, shape):
+        ptr = getattr(self.lib, f"orc_stream_{name}")(self.handle)
+        return np.ctypeslib.as_array(ptr, shape=shape)
+
+    @property
+    def self_k(self):
+        s = self.model.synth.shape
+        return self._view("self_k", (s.layers, self.capacity, s.width))
+
+    @property
+    def self_v(self):
+        s = self.model.synth.shape
+        return self._view("self_v", (s.layers, self.capacity, s.width))
+
+    @property
+    def cross_k(self):
+        s = self.model.synth.shape
+        return self._view("cross_k", (s.layers, self.memory_length, s.xattn_width))
+
+    @property
+    def cross_v(self):
+        s = self.model.synth.shape
+        return self._view("cross_v", (s.layers, self.memory_length, s.xattn_width))
+
+    @property
+    def length(self) -> int:
+        return int(self.lib.orc_stream_length(self.handle))
+
+    @length.setter
+    def length(self, n: int):
+        self.lib.orc_stream_set_length(self.handle, n)
+
+    def set_layers(self, n: int):
+        self.lib.orc_stream_set_layers(self.handle, n)
+
+    def step(self, row: np.ndarray) -> np.ndarray:
+        out = np.empty_like(row)
+        assert self.lib.orc_decoder_step(self.handle, _fp(row), _fp(out)) == 0
+        return out
+
+    def greedy_frame(self, codes: np.ndarray, allow_eos: bool):
+        s = self.model.synth.shape
+        tokens = np.empty((s.tables,), np.uint32)
+        hidden = np.empty((s.width,), np.float32)
+        eos = self.lib.orc_greedy_frame(self.handle, codes.ctypes.data_as(c_uint_p), int(allow_eos),
+                                        tokens.ctypes.data_as(c_uint_p), _fp(hidden))
+        assert eos >= 0
+        return tokens, hidden, bool(eos)
+
+    def greedy_decode(self, codes: np.ndarray, frames: int, min_frames: int):
+        s = self.model.synth.shape
+        codes = np.ascontiguousarray(codes, np.uint32).copy()
+        tokens = np.zeros((frames, s.tables), np.uint32)
+        n = self.lib.orc_greedy_decode(self.handle, codes.ctypes.data_as(c_uint_p), frames,
+                                       min_frames, tokens.ctypes.data_as(c_uint_p))
+        assert n >= 0
+        return tokens[:n]
+
+
+# --------------------------------------------------------------------- Ref
+class Ref:
+    """Typed access to one of the compiled-reference libraries."""
+
+    _instances: dict = {}
+
+    def __init__(self, kind: str):
+        self.kind = kind
+        self.lib = lib = C.CDLL(REF_SO[kind])
+        sz = C.c_size_t
+        lib.ref_model_open.restype = C.c_void_p
+        lib.ref_model_open.argtypes = [C.c_char_p, C.c_uint, C.c_uint, C.c_uint, C.c_uint, C.c_uint,
+                                       C.c_uint, C.c_uint, C.c_int, C.c_char_p, sz]
+        lib.ref_model_close.argtypes = [C.c_void_p]
+        lib.ref_decoder_new.restype = C.c_void_p
+        lib.ref_decoder_new.argtypes = [C.c_void_p, c_float_p, sz, sz, C.c_char_p, sz]
+        lib.ref_decoder_free.argtypes = [C.c_void_p]
+        lib.ref_decoder_length.restype = sz
+        lib.ref_decoder_length.argtypes = [C.c_void_p]
+        lib.ref_decoder_set_length.argtypes = [C.c_void_p, sz]
+        lib.ref_decoder_set_layers.argtypes = [C.c_void_p, sz]
+        for name in ("self_k", "self_v", "cross_k", "cross_v"):
+            fn = getattr(lib, f"ref_decoder_{name}")
+            fn.restype = c_float_p
+            fn.argtypes = [C.c_void_p]
+        lib.ref_decoder_step_batch.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), c_float_p,
+                                               c_float_p, sz, C.c_char_p, sz]
+        lib.ref_decoder_run.argtypes = [C.c_void_p, C.c_void_p, c_float_p, sz, c_float_p,
+                                        C.c_char_p, sz]
+        lib.ref_heads_argmax.argtypes = [C.c_void_p, c_float_p, sz, C.c_int, c_uint_p, c_float_p,
+                                         C.c_char_p, sz]
+        lib.ref_greedy_decode.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), sz, c_uint_p, sz, sz,
+                                          c_uint_p, C.POINTER(C.c_long), C.c_char_p, sz]
+        lib.ref_quantize_act_int8.restype = C.c_float
+        lib.ref_quantize_act_int8.argtypes = [C.c_void_p, c_float_p, sz]
+        lib.ref_qmat_linear.argtypes = [C.c_int, c_float_p, c_float_p, c_float_p, sz, sz, sz,
+                                        c_float_p, C.c_char_p, sz]
+        lib.ref_qmat_linear_batched.argtypes = lib.ref_qmat_linear.argtypes
+        lib.ref_self_tests.argtypes = [C.c_char_p, sz]
+        lib.mynah_layernorm_f32.argtypes = [c_float_p, c_float_p, c_float_p, c_float_p, sz, sz,
+                                            C.c_float]
+        lib.mynah_gelu_f32_scalar.argtypes = [c_float_p, sz]
+
+    @classmethod
+    def get(cls, kind: str = "strict") -> "Ref":
+        if kind not in cls._instances:
+            cls._instances[kind] = cls(kind)
+        return cls._instances[kind]
+
+    def self_tests(self):
+        err = C.create_string_buffer(256)
+        return self.lib.ref_self_tests(err, 256), err.value.decode()
+
+    def quantize_weight_int8(self, w):
+        n, k = w.shape
+        q = np.empty((n, k), np.int8)
+        s = np.empty((n,), np.float32)
+        self.lib.ref_quantize_weight_int8(_fp(w), C.c_size_t(n), C.c_size_t(k),
+                                          q.ctypes.data_as(C.c_void_p), _fp(s))
+        return q, s
+
+    def quantize_weight_int4(self, w):
+        n, k = w.shape
+        q = np.empty((n, k // 2), np.uint8)
+        s = np.empty((n, k // 32), np.float32)
+        self.lib.ref_quantize_weight_int4(_fp(w), C.c_size_t(n), C.c_size_t(k),
+                                          q.ctypes.data_as(C.c_void_p), _fp(s))
+        return q, s
+
+    def quantize_act_int8(self, x):
+        q = np.empty(x.shape, np.int8)
+        sx = self.lib.ref_quantize_act_int8(q.ctypes.data_as(C.c_void_p), _fp(x), x.size)
+        return q, np.float32(sx)
+
+    def layernorm(self, x, gain, eps=1e-5):
+        x2 = np.ascontiguousarray(x.reshape(-1, x.shape[-1]))
+        y = np.empty_like(x2)
+        self.lib.mynah_layernorm_f32(_fp(x2), _fp(gain), None, _fp(y), x2.shape[0], x2.shape[1], eps)
+        return y.reshape(x.shape)
+
+    def gelu(self, x):
+        y = np.ascontiguousarray(x.copy())
+        self.lib.mynah_gelu_f32_scalar(_fp(y), y.size)
+        return y
+
+    def qmat_linear(self, qtype, w, x, bias=None, batched=False):
+        x2 = np.ascontiguousarray(x.reshape(-1, x.shape[-1]))
+        n, k = w.shape[0], w.shape[1]
+        out = np.empty((x2.shape[0], n), np.float32)
+        err = C.create_string_buffer(256)
+        fn = self.lib.ref_qmat_linear_batched if batched else self.lib.ref_qmat_linear
+        rc = fn(qtype, _fp(w), _fp(x2), _fp(out), x2.shape[0], k, n,
+                None if bias is None else _fp(bias), err, 256)
+        assert rc == 0, err.value
+        return out
+
+
+class RefModel:
+    """The reference's model struct over a synthetic safetensors file.
+
+    `tables` stacked streams are presented to the reference as
+    frame_stacking_factor 2 x codebook_count tables/2, the only stacking its
+    embed_audio_frame accepts (src/graph.c:767-770)."""
+
+    def __init__(self, synth, qtype: int, kind: str = "strict", threads: int | None = None):
+        from mynah_tts_b200.synth import write_safetensors
+        if threads is not None:
+            os.environ["MYNAH_THREADS"] = str(threads)
+        self.ref = Ref.get(kind)
+        self.synth = synth
+        s = synth.shape
+        assert s.tables % 2 == 0
+        self._dir = tempfile.TemporaryDirectory(prefix="mynah_ref_")
+        path = os.path.join(self._dir.name, "tts.safetensors")
+        write_safetensors(path, synth.tensors)
+        err = C.create_string_buffer(512)
+        self.handle = C.c_void_p(self.ref.lib.ref_model_open(
+            path.encode(), s.width, s.layers, s.tables // 2, 2, s.codebook_size, s.vocab,
+            s.eos_id, qtype, err, 512))
+        assert self.handle.value, err.value
+
+    def close(self):
+        if self.handle:
+            self.ref.lib.ref_model_close(self.handle)
+            self.handle = None
+            self._dir.cleanup()
+
+    def new_decoder(self, memory: np.ndarray, capacity: int) -> "RefDecoder":
+        return RefDecoder(self, memory, capacity)
+
+    def step_batch(self, decoders, rows: np.ndarray) -> np.ndarray:
+        rows = np.ascontiguousarray(rows, np.float32)
+        outs = np.empty_like(rows)
+        arr = (C.c_void_p * len(decoders))(*[d.handle for d in decoders])
+        err = C.create_string_buffer(256)
+        rc = self.ref.lib.ref_decoder_step_batch(self.handle, arr, _fp(rows), _fp(outs),
+                                                 len(decoders), err, 256)
+        assert rc == 0, err.value
+        return outs
+
+    def heads_argmax(self, hidden, allow_eos):
+        s = self.synth.shape
+        tokens = np.empty((s.tables,), np.uint32)
+        logits = np.empty((s.tables, s.vocab), np.float32)
+        err = C.create_string_buffer(256)
+        rc = self.ref.lib.ref_heads_argmax(self.handle, _fp(hidden), s.tables, int(allow_eos),
+                                           tokens.ctypes.data_as(c_uint_p), _fp(logits), err, 256)
+        assert rc == 0, err.value
+        return tokens, logits
+
+    def greedy_decode(self, decoders, codes: np.ndarray, frames: int, min_frames: int):
+        """codes [batch, tables] -> tokens [frames, batch, tables], eos_frame [batch]."""
+        s = self.synth.shape
+        batch = len(decoders)
+        codes = np.ascontiguousarray(codes, np.uint32).copy()
+        tokens = np.zeros((frames, batch, s.tables), np.uint32)
+        eos = (C.c_long * batch)()
+        arr = (C.c_void_p * batch)(*[d.handle for d in decoders])
+        err = C.create_string_buffer(256)
+        rc = self.ref.lib.ref_greedy_decode(self.handle, arr, batch, codes.ctypes.data_as(c_uint_p),
+                                            frames, min_frames, tokens.ctypes.data_as(c_uint_p),
+                                            eos, err, 256)
+        assert rc == 0, err.value
+        return tokens, np.array(list(eos))
+
+
+class RefDecoder:
+    def __init__(self, model: RefModel, memory: np.ndarray, capacity: int):
+        self.model = model
+        self.lib = model.ref.lib
+        self.capacity = capacity
+        self.memory_length = memory.shape[0]
+        err = C.create_string_buffer(256)
+        self.handle = C.c_void_p(self.lib.ref_decoder_new(model.handle, _fp(memory),
+                                                          memory.shape[0], capacity, err, 256))
+        assert self.handle.value, err.value
+
+    def close(self):
+        if self.handle:
+            self.lib.ref_decoder_free(self.handle)
+            self.handle = None
+
+    def _view(self, name, shape):
+        return np.ctypeslib.as_array(getattr(self.lib, f"ref_decoder_{name}")(self.handle), shape=shape)
+
+    @property
+    def self_k(self):
+        s = self.model.synth.shape
+        return self._view("self_k", (s.layers, self.capacity, s.width))
+
+    @property
+    def self_v(self):
+        s = self.model.synth.shape
+        return self._view("self_v", (s.layers, self.capacity, s.width))
+
+    @property
+    def cross_k(self):
+        s = self.model.synth.shape
+        return self._view("cross_k", (s.layers, self.memory_length, s.xattn_width))
+
+    @property
+    def cross_v(self):
+        s = self.model.synth.shape
+        return self._view("cross_v", (s.layers, self.memory_length, s.xattn_width))
+
+    @property
+    def length(self):
+        return int(self.lib.ref_decoder_length(self.handle))
+
+    @length.setter
+    def length(self, n):
+        self.lib.ref_decoder_set_length(self.handle, n)
+
+    def set_layers(self, n):
+        self.lib.ref_decoder_set_layers(self.handle, n)
+
+    def step(self, row: np.ndarray) -> np.ndarray:
+        return self.model.step_batch([self], row.reshape(1, -1))[0]
