@@ -1,0 +1,283 @@
+/* C ABI of libmynah_b200: a B200 (sm_100a) backend for the Magpie decoder step
+ * of mynah-tts.
+ *
+ * Part 1 is the drop-in seam: the symbols mynah-tts's src/backend.c binds for
+ * its CUDA device (declared there at src/backend.c:105-135, defined by
+ * gpu/cuda/backend_cuda.cu in the reference), with the same names, argument
+ * order and error convention -- 0 on success, -1 on failure with a message
+ * written to (error, error_capacity); nothing prints, nothing aborts.  Linking
+ * this library in place of backend_cuda.o needs no change to the callers.
+ * Five further `mynah_cuda_*` entries implement the resident-attention ops of
+ * src/backend.h:135-179 that the reference wires only for its Metal device
+ * (src/backend.c:404-428); assigning them in the CUDA branch of
+ * mynah_backend_open lights up the resident decode step of
+ * src/graph.c:3363-3488 unchanged.
+ *
+ * Part 2 is an extension the reference's seam has no counterpart for: weight
+ * quantization behind the seam (the reference's quantized products bypass the
+ * backend, src/qmat.c:773-788), a whole-step batched decoder object, and a
+ * device-resident greedy loop.
+ *
+ * All pointers named dev_* are device pointers obtained from this library;
+ * `weight`/`bias`/`gain` arguments of part 1 are HOST pointers that stay valid
+ * and unchanged for the life of the backend: they key an internal device cache,
+ * as in the reference (gpu/cuda/backend_cuda.cu:205-219).
+ */
+#ifndef MYNAH_B200_H
+#define MYNAH_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+/* Every declaration below is an exported symbol of the shared library. */
+#pragma GCC visibility push(default)
+
+/* ===================================================================== *
+ * Part 1: the backend seam (src/backend.h of mynah-tts)
+ * ===================================================================== */
+
+/* src/backend.h:10-25 */
+typedef int (*mynah_backend_matmul_fn)(void *, const float *, float *, size_t, size_t, size_t,
+                                       const float *, const float *, char *, size_t);
+typedef void (*mynah_backend_close_fn)(void *);
+typedef int (*mynah_backend_self_test_fn)(void *, char *, size_t);
+typedef int (*mynah_backend_sgemm_fn)(void *, int trans_a, int trans_b, size_t m, size_t n,
+                                      size_t k, float alpha, const float *a, size_t lda,
+                                      const float *b, size_t ldb, float beta, float *c,
+                                      size_t ldc, char *, size_t);
+
+/* Replaces mynah_backend_cuda_open (src/backend.c:106-109,
+ * gpu/cuda/backend_cuda.cu:543-568).  Device = MYNAH_B200_DEVICE (default 0);
+ * weight format = MYNAH_QUANT (f32 default | f16 | int8 | int4, the values of
+ * src/qmat.c:571-576); MYNAH_B200_STRICT=1 selects reference-order reductions.
+ * The returned matmul/sgemm take HOST buffers and synchronize. */
+int mynah_backend_cuda_open(void **state, mynah_backend_matmul_fn *matmul,
+                            mynah_backend_sgemm_fn *sgemm, mynah_backend_close_fn *close,
+                            mynah_backend_self_test_fn *self_test, char *error,
+                            size_t error_capacity);
+
+/* src/backend.h:78-93,181-186 / src/backend.c:111-123 */
+int mynah_cuda_upload(void *state, const float *host, size_t n, float **dev_ptr, char *error, size_t cap);
+int mynah_cuda_download(void *state, const float *dev_ptr, float *host, size_t n, char *error, size_t cap);
+int mynah_cuda_sync(void *state, char *error, size_t cap);
+int mynah_cuda_dev_alloc(void *state, size_t n, float **dev_ptr, char *error, size_t cap);
+void mynah_cuda_dev_free(void *state, float *dev_ptr);
+int mynah_cuda_h2d(void *state, const float *host, float *dev_ptr, size_t n, char *error, size_t cap);
+int mynah_cuda_d2h(void *state, const float *dev_ptr, float *host, size_t n, char *error, size_t cap);
+
+/* Element-wise and normalization ops on device rows (src/backend.h:54-56,
+ * 103-127; kernels gpu/cuda/backend_cuda.cu:33-108 in the reference). */
+int mynah_cuda_gelu_dev(void *state, float *dev_data, size_t n, char *error, size_t cap);
+int mynah_cuda_gelu_inplace(void *state, float *dev_data, size_t n, char *error, size_t cap);
+int mynah_cuda_layer_norm_dev(void *state, const float *dev_in, float *dev_out, const float *gain,
+                              const float *bias, size_t rows, size_t width, char *error, size_t cap);
+int mynah_cuda_layer_norm_inplace(void *state, const float *dev_in, float *dev_out,
+                                  const float *gain, size_t rows, size_t width, char *error,
+                                  size_t cap);
+int mynah_cuda_residual_add_dev(void *state, float *dev_out, const float *dev_in, size_t n,
+                                char *error, size_t cap);
+int mynah_cuda_residual_inplace(void *state, float *dev_out, const float *dev_in, size_t n,
+                                char *error, size_t cap);
+
+/* out[rows,ow] = in[rows,iw] @ W[ow,iw]^T + bias (src/backend.h:58,95-101,
+ * 66-71).  With MYNAH_QUANT set, products of at most 16 rows and iw <= 8192
+ * use the packed weight with per-row int8 activations exactly as
+ * mynah_qmat_linear_resolved does on the CPU (src/qmat.c:768-818); larger
+ * calls and int4 with iw not a multiple of 32 stay f32. */
+int mynah_cuda_matmul_dev(void *state, const float *dev_in, float *dev_out, size_t rows, size_t iw,
+                          size_t ow, const float *weight, const float *bias, char *error, size_t cap);
+int mynah_cuda_matmul_d2d(void *state, const float *dev_in, float *dev_out, size_t rows, size_t iw,
+                          size_t ow, const float *weight, const float *bias, char *error, size_t cap);
+int mynah_cuda_matmul_to_dev(void *state, const float *host_in, float *dev_out, size_t rows,
+                             size_t iw, size_t ow, const float *weight, const float *bias,
+                             char *error, size_t cap);
+int mynah_cuda_matmul_graph(void *state, const float *host_in, float *host_out, size_t rows,
+                            size_t iw, size_t ow, const float *weight, const float *bias,
+                            char *error, size_t cap);
+int mynah_cuda_matvec_dev(void *state, const float *dev_in, float *dev_out, size_t K, size_t N,
+                          const float *weight, const float *bias, char *error, size_t cap);
+int mynah_cuda_sgemm_dev(void *state, int trans_a, int trans_b, size_t m, size_t n, size_t k,
+                         float alpha, const float *dev_a, size_t lda, const float *dev_b,
+                         size_t ldb, float beta, float *dev_c, size_t ldc, char *error, size_t cap);
+
+/* Resident single-token attention and helpers: src/backend.h:135-179.  The
+ * reference's CUDA file has no counterpart (its vtable leaves them NULL). */
+int mynah_cuda_batch_begin(void *state, char *error, size_t cap);
+int mynah_cuda_self_attention_dev(void *state, const float *dev_qkv, float *dev_k_cache,
+                                  float *dev_v_cache, size_t position, size_t cache_stride,
+                                  size_t valid, size_t heads, size_t head_width, float scale,
+                                  float *dev_out, char *error, size_t cap);
+int mynah_cuda_cross_attention_dev(void *state, const float *dev_q, const float *dev_k_cache,
+                                   const float *dev_v_cache, size_t valid, size_t cache_stride,
+                                   size_t heads, size_t head_width, float scale, float *dev_out,
+                                   char *error, size_t cap);
+int mynah_cuda_copy_dev(void *state, float *dev_dst, const float *dev_src, size_t n, char *error, size_t cap);
+int mynah_cuda_scale_dev(void *state, float *dev_data, size_t n, float scale, char *error, size_t cap);
+int mynah_cuda_clip_dev(void *state, float *dev_data, size_t n, char *error, size_t cap);
+int mynah_cuda_argmax_dev(void *state, const float *dev_logits, size_t vocab, size_t codebook_size,
+                          size_t eos_id, int allow_eos, unsigned *argmax, char *error, size_t cap);
+
+/* Host-side GELU helpers the reference exports for calibration
+ * (src/backend.h:63-64): data is a HOST buffer, processed on the device. */
+int mynah_cuda_gelu_host(void *state, float *host_data, size_t n, char *error, size_t cap);
+int mynah_cuda_gelu_host_f64(void *state, float *host_data, size_t n, char *error, size_t cap);
+
+/* NanoCodec ops (src/backend.h:59-62,128-133) are outside this library's
+ * scope; they return -1 with a message so the caller keeps its CPU path. */
+int mynah_cuda_snake_dev(void *state, float *dev_data, const float *alpha, size_t channels,
+                         size_t length, size_t snake_channels, char *error, size_t cap);
+int mynah_cuda_im2col(void *state, const float *in, float *cols, int in_ch, int length, int kernel,
+                      int dilation, char *error, size_t cap);
+int mynah_cuda_conv1d(void *state, const float *in, float *out, int in_ch, int out_ch, int length,
+                      int kernel, int dilation, const float *weight, const float *bias,
+                      char *error, size_t cap);
+
+/* ===================================================================== *
+ * Part 2: extensions (no counterpart in the reference's seam)
+ * ===================================================================== */
+
+enum { MYNAH_B200_F32 = 0, MYNAH_B200_INT8 = 1, MYNAH_B200_INT4 = 2, MYNAH_B200_F16 = 3 };
+
+/* Explicit open: device ordinal, weight format (MYNAH_B200_*), strict flag.
+ * mynah_backend_cuda_open is this with values taken from the environment. */
+int mynah_b200_open(void **state, int device, int quant, int strict, char *error, size_t cap);
+void mynah_b200_close(void *state);
+/* Run all work of this backend on the caller's CUDA stream (cudaStream_t). */
+int mynah_b200_set_stream(void *state, void *cuda_stream, char *error, size_t cap);
+int mynah_b200_quant(const void *state);
+int mynah_b200_strict(const void *state);
+/* Number of kernels this library has launched on `state` (graph replays count
+ * their kernel nodes). */
+unsigned long long mynah_b200_launch_count(const void *state);
+
+/* Pack a HOST f32 weight [n,k] on the device with the reference's quantizers
+ * (src/qmat.c:39-91,650-655) and copy the packed bytes and scales back:
+ * int8 -> q[n*k] + scales[n]; int4 -> q[n*k/2] + scales[n*k/32]; f16 ->
+ * q[n*k] halves, scales untouched. */
+int mynah_b200_pack_weight(void *state, int quant, const float *host_w, size_t n, size_t k,
+                           void *host_q, float *host_scales, char *error, size_t cap);
+/* Per-row int8 activation quantization of HOST rows (src/qmat.c:93-113). */
+int mynah_b200_quantize_act(void *state, const float *host_x, size_t rows, size_t k,
+                            int8_t *host_q, float *host_sx, char *error, size_t cap);
+/* HOST-buffer single op: out[count,n] = LN(x)[count,k] @ W[n,k]^T + bias, the
+ * LayerNorm (gain only, eps 1e-5) skipped when ln_gain is NULL; W, bias and
+ * ln_gain are cached by host pointer.  The reference's counterpart is
+ * layer_norm + mynah_qmat_linear_resolved (src/graph.c:147-150,
+ * src/qmat.c:768-818). */
+int mynah_b200_qmat_linear(void *state, const float *weight, const float *x, float *out,
+                           size_t count, size_t k, size_t n, const float *bias,
+                           const float *ln_gain, char *error, size_t cap);
+/* Device-resident form of the same op over `groups` independent problems laid
+ * out back to back (weights from mynah_b200_pool_*): used to stream a pool of
+ * distinct matrices larger than L2 through the product kernel in one launch
+ * sequence.  dev_x is [groups][k], dev_out [groups][n]. */
+int mynah_b200_pool_create(void *state, const float *host_w, size_t n, size_t k, size_t groups,
+                           const float *host_bias, const float *host_gain, void **pool,
+                           char *error, size_t cap);
+void mynah_b200_pool_destroy(void *pool);
+int mynah_b200_pool_linear(void *pool, const float *dev_x, float *dev_out, char *error, size_t cap);
+size_t mynah_b200_pool_bytes_per_pass(const void *pool);
+
+/* ---- whole-step decoder --------------------------------------------------- */
+/* Host weight pointers of one decoder layer, in the order of
+ * decoder_layer_resolved (src/graph.c:2795-2804). */
+typedef struct {
+    const float *norm_self;         /* [width] */
+    const float *norm_xattn_query;  /* [width] */
+    const float *norm_pos_ff;       /* [width] */
+    const float *qkv_w;             /* [3*width, width] */
+    const float *o_self_w;          /* [width, width] */
+    const float *q_cross_w;         /* [xattn_width, width] */
+    const float *o_cross_w;         /* [width, xattn_width] */
+    const float *ffn_up_w;          /* [4*width, width] */
+    const float *ffn_down_w;        /* [width, 4*width] */
+} mynah_b200_layer_weights;
+
+typedef struct {
+    size_t layers, width, heads, xattn_width; /* head_width = width/heads, ffn = 4*width */
+    size_t memory_length;  /* rows of cross K/V per slot */
+    size_t capacity;       /* self-KV rows per slot (src/graph.c:3804-3806) */
+    size_t slots;          /* resident requests (each owns KV) */
+    size_t max_batch;      /* most slots stepped together */
+    size_t max_positions;  /* rows of the position table */
+    const mynah_b200_layer_weights *layer; /* [layers] */
+    const float *position;  /* decoder.position_embeddings.weight [max_positions, width] */
+    const float *norm_out;  /* decoder.norm_out.weight [width] */
+    /* optional greedy front/back ends (tables == 0 disables them) */
+    size_t tables, vocab, codebook_size, eos_id;
+    const float *const *embeddings; /* tables x [vocab, width]  (audio_embeddings.N.weight) */
+    const float *const *head_w;     /* tables x [vocab, width] */
+    const float *const *head_b;     /* tables x [vocab] */
+} mynah_b200_decoder_desc;
+
+/* Uploads and packs every weight once (format and strictness of `state`) and
+ * allocates KV for `slots` requests.  Weight host pointers need only be valid
+ * during this call. */
+int mynah_b200_decoder_create(void *state, const mynah_b200_decoder_desc *desc, void **decoder,
+                              char *error, size_t cap);
+void mynah_b200_decoder_destroy(void *decoder);
+
+/* Load one request into a slot: cross K/V [layers][memory_length][xattn_width]
+ * as decoder_cache_init leaves them (src/graph.c:3012-3027), and optionally
+ * `length` rows of existing self K/V [layers][capacity][width] (what
+ * decoder_gpu_attention_init uploads, src/graph.c:2929-2953). */
+int mynah_b200_decoder_slot_load(void *decoder, size_t slot, const float *cross_k,
+                                 const float *cross_v, const float *self_k, const float *self_v,
+                                 size_t length, char *error, size_t cap);
+int mynah_b200_decoder_slot_length(void *decoder, size_t slot, size_t *length, char *error, size_t cap);
+int mynah_b200_decoder_slot_set_length(void *decoder, size_t slot, size_t length, char *error, size_t cap);
+/* Copy a slot's self K/V back: host arrays [layers][capacity][width]. */
+int mynah_b200_decoder_slot_read_kv(void *decoder, size_t slot, float *self_k, float *self_v,
+                                    char *error, size_t cap);
+/* Run only the first n layers (then the output norm); n = layers restores. */
+int mynah_b200_decoder_set_layers(void *decoder, size_t n, char *error, size_t cap);
+
+/* One decoder step for `batch` slots: the contract of decoder_step_batch
+ * (src/graph.c:3127-3284) with HOST rows -- inputs[b] and outs[b] are `width`
+ * floats; position embedding, all layers, output norm; each slot's length
+ * advances by one.  Synchronous. */
+int mynah_b200_decoder_step_batch(void *decoder, const unsigned *slots,
+                                  const float *const *inputs, float *const *outs, size_t batch,
+                                  char *error, size_t cap);
+/* One greedy frame for `batch` slots with HOST buffers: codes [batch][tables]
+ * in, tokens [batch][tables] out (optionally the output-norm rows
+ * [batch][width]): embedding mean (src/graph.c:760-804), decoder step, logit
+ * heads with the constrained first-on-ties pick (src/graph.c:1538-1566).
+ * Synchronous; the caller applies its own EOS policy. */
+int mynah_b200_decoder_frame_batch(void *decoder, const unsigned *slots, const unsigned *codes,
+                                   const int *allow_eos, unsigned *tokens, float *hidden,
+                                   size_t batch, char *error, size_t cap);
+/* Device-resident greedy decode: lane b runs frames[b] frames starting from
+ * codes[b][tables] (HOST, updated to the last stored codes); tokens
+ * [max_frames][batch][tables] (HOST) receives every picked token (rows of
+ * lanes that already finished are left zero); EOS is allowed from frame
+ * min_frames on and is reported in eos_frame[b] (first frame, -1 if none) but
+ * does not stop a lane.  One CUDA graph launch per frame, no host round trip
+ * inside the loop.  elapsed_ms (optional) receives the device time of the
+ * loop measured with events on the backend's stream. */
+int mynah_b200_decoder_greedy(void *decoder, const unsigned *slots, size_t batch, unsigned *codes,
+                              const size_t *frames, size_t min_frames, unsigned *tokens,
+                              long *eos_frame, float *elapsed_ms, char *error, size_t cap);
+/* Bytes of weights one step reads, and of KV one slot at `length` reads. */
+size_t mynah_b200_decoder_weight_bytes(const void *decoder);
+size_t mynah_b200_decoder_kv_bytes(const void *decoder, size_t length);
+
+/* Per-call-site device timing of the step (the reference's MYNAH_TIMING=1
+ * phase report, src/graph.c:83-88, is the nearest counterpart).  While enabled
+ * every step runs as individual launches, each bracketed by two CUDA events on
+ * the backend's stream, instead of a graph replay; _read synchronizes and
+ * returns, per class, the launches seen and their summed device time. */
+#define MYNAH_B200_PROFILE_CLASSES 14
+int mynah_b200_decoder_profile(void *decoder, int enable, char *error, size_t cap);
+int mynah_b200_decoder_profile_read(void *decoder, unsigned long long *launches, double *ms,
+                                    size_t n, char *error, size_t cap);
+const char *mynah_b200_profile_class_name(size_t cls);
+
+#pragma GCC visibility pop
+#ifdef __cplusplus
+}
+#endif
+#endif

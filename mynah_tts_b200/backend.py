@@ -1,0 +1,345 @@
+"""Host-side mirror of the reference's backend and decoder interfaces over the
+C ABI: method names and argument meaning follow mynah-tts's src/backend.h
+(`matmul_d2d`, `layer_norm_inplace`, `self_attention_dev`, ...) and
+src/graph.c's decoder step (`step_batch`), so parity tests read like the
+reference's own.  Every call goes through libmynah_b200.so; nothing here
+computes.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import capi
+from .capi import F16, F32, INT4, INT8, QUANT, MynahB200Error, call, fp  # noqa: F401
+
+
+class DeviceBuffer:
+    """n floats on the device, owned through dev_alloc/dev_free (src/backend.h:181-186)."""
+
+    def __init__(self, backend: "Backend", n: int):
+        self.backend = backend
+        self.n = n
+        ptr = C.c_void_p()
+        call(capi.lib().mynah_cuda_dev_alloc, backend.state, n, C.byref(ptr))
+        self.ptr = ptr
+
+    def at(self, offset: int) -> C.c_void_p:
+        return C.c_void_p(self.ptr.value + 4 * offset)
+
+    def free(self):
+        if self.ptr:
+            capi.lib().mynah_cuda_dev_free(self.backend.state, self.ptr)
+            self.ptr = None
+
+
+class Backend:
+    def __init__(self, quant="f32", strict: bool = False, device: int = 0, from_env: bool = False):
+        self.lib = capi.lib()
+        self.state = C.c_void_p()
+        self._keep = []   # host arrays whose addresses key the device caches
+        if from_env:
+            self.matmul_fn, self.sgemm_fn = capi.MATMUL_FN(), capi.SGEMM_FN()
+            self.close_fn, self.self_test_fn = capi.CLOSE_FN(), capi.SELF_TEST_FN()
+            call(self.lib.mynah_backend_cuda_open, C.byref(self.state), C.byref(self.matmul_fn),
+                 C.byref(self.sgemm_fn), C.byref(self.close_fn), C.byref(self.self_test_fn))
+        else:
+            q = QUANT[quant] if isinstance(quant, str) else int(quant)
+            call(self.lib.mynah_b200_open, C.byref(self.state), device, q, int(strict))
+        self.quant = self.lib.mynah_b200_quant(self.state)
+        self.strict = bool(self.lib.mynah_b200_strict(self.state))
+
+    def close(self):
+        if self.state:
+            self.lib.mynah_b200_close(self.state)
+            self.state = None
+
+    def keep(self, a: np.ndarray | None):
+        """Pin a host array's lifetime to the backend (host pointers are cache keys)."""
+        if a is not None:
+            self._keep.append(a)
+        return a
+
+    def set_stream(self, cuda_stream: int):
+        call(self.lib.mynah_b200_set_stream, self.state, C.c_void_p(cuda_stream))
+
+    @property
+    def launch_count(self) -> int:
+        return int(self.lib.mynah_b200_launch_count(self.state))
+
+    # ---- memory ----------------------------------------------------------
+    def dev_alloc(self, n: int) -> DeviceBuffer:
+        return DeviceBuffer(self, n)
+
+    def h2d(self, host: np.ndarray, dev, n: int | None = None):
+        host = np.ascontiguousarray(host, np.float32)
+        call(self.lib.mynah_cuda_h2d, self.state, fp(host), _p(dev), host.size if n is None else n)
+
+    def d2h(self, dev, n: int) -> np.ndarray:
+        out = np.empty((n,), np.float32)
+        call(self.lib.mynah_cuda_d2h, self.state, _p(dev), fp(out), n)
+        return out
+
+    def to_device(self, host: np.ndarray) -> DeviceBuffer:
+        buf = self.dev_alloc(host.size)
+        self.h2d(host, buf)
+        return buf
+
+    def sync(self):
+        call(self.lib.mynah_cuda_sync, self.state)
+
+    # ---- seam ops on device rows -------------------------------------------
+    def matmul(self, x: np.ndarray, weight: np.ndarray, bias=None) -> np.ndarray:
+        """Host-buffer product through the function pointer mynah_backend_cuda_open returns."""
+        rows, iw = x.shape
+        ow = weight.shape[0]
+        out = np.empty((rows, ow), np.float32)
+        self.keep(weight), self.keep(bias)
+        call(self.lib.mynah_cuda_matmul_graph, self.state, fp(x), fp(out), rows, iw, ow, fp(weight),
+             None if bias is None else fp(bias))
+        return out
+
+    def matmul_d2d(self, din, dout, rows, iw, ow, weight: np.ndarray, bias=None):
+        self.keep(weight), self.keep(bias)
+        call(self.lib.mynah_cuda_matmul_d2d, self.state, _p(din), _p(dout), rows, iw, ow, fp(weight),
+             None if bias is None else fp(bias))
+
+    def layer_norm_inplace(self, din, dout, gain: np.ndarray, rows, width):
+        self.keep(gain)
+        call(self.lib.mynah_cuda_layer_norm_inplace, self.state, _p(din), _p(dout), fp(gain), rows, width)
+
+    def gelu_inplace(self, dev, n):
+        call(self.lib.mynah_cuda_gelu_inplace, self.state, _p(dev), n)
+
+    def residual_inplace(self, dout, din, n):
+        call(self.lib.mynah_cuda_residual_inplace, self.state, _p(dout), _p(din), n)
+
+    def self_attention_dev(self, dqkv, dk, dv, position, cache_stride, valid, heads, head_width,
+                           scale, dout):
+        call(self.lib.mynah_cuda_self_attention_dev, self.state, _p(dqkv), _p(dk), _p(dv), position,
+             cache_stride, valid, heads, head_width, C.c_float(scale), _p(dout))
+
+    def cross_attention_dev(self, dq, dk, dv, valid, cache_stride, heads, head_width, scale, dout):
+        call(self.lib.mynah_cuda_cross_attention_dev, self.state, _p(dq), _p(dk), _p(dv), valid,
+             cache_stride, heads, head_width, C.c_float(scale), _p(dout))
+
+    def argmax_dev(self, dlogits, vocab, codebook_size, eos_id, allow_eos) -> int:
+        out = C.c_uint(0)
+        call(self.lib.mynah_cuda_argmax_dev, self.state, _p(dlogits), vocab, codebook_size, eos_id,
+             int(allow_eos), C.byref(out))
+        return int(out.value)
+
+    def copy_dev(self, dst, src, n):
+        call(self.lib.mynah_cuda_copy_dev, self.state, _p(dst), _p(src), n)
+
+    def scale_dev(self, dev, n, scale):
+        call(self.lib.mynah_cuda_scale_dev, self.state, _p(dev), n, C.c_float(scale))
+
+    def clip_dev(self, dev, n):
+        call(self.lib.mynah_cuda_clip_dev, self.state, _p(dev), n)
+
+    def sgemm(self, trans_a, trans_b, m, n, k, alpha, a, lda, b, ldb, beta, c, ldc):
+        call(self.sgemm_fn, self.state, trans_a, trans_b, m, n, k, C.c_float(alpha), fp(a), lda, fp(b),
+             ldb, C.c_float(beta), fp(c), ldc)
+
+    def self_test(self):
+        call(self.self_test_fn, self.state)
+
+    # ---- extensions ---------------------------------------------------------
+    def pack_weight(self, quant: int, w: np.ndarray):
+        n, k = w.shape
+        if quant == INT8:
+            q, s = np.empty((n, k), np.int8), np.empty((n,), np.float32)
+        elif quant == INT4:
+            q, s = np.empty((n, k // 2), np.uint8), np.empty((n, k // 32), np.float32)
+        elif quant == F16:
+            q, s = np.empty((n, k), np.uint16), np.empty((0,), np.float32)
+        else:
+            q, s = np.empty((n, k), np.float32), np.empty((0,), np.float32)
+        call(self.lib.mynah_b200_pack_weight, self.state, quant, fp(w), n, k,
+             q.ctypes.data_as(C.c_void_p), fp(s) if s.size else None)
+        return q, s
+
+    def quantize_act(self, x: np.ndarray):
+        x2 = np.ascontiguousarray(x.reshape(-1, x.shape[-1]))
+        q = np.empty(x2.shape, np.int8)
+        sx = np.empty((x2.shape[0],), np.float32)
+        call(self.lib.mynah_b200_quantize_act, self.state, fp(x2), x2.shape[0], x2.shape[1],
+             q.ctypes.data_as(C.c_void_p), fp(sx))
+        return q.reshape(x.shape), sx
+
+    def qmat_linear(self, weight: np.ndarray, x: np.ndarray, bias=None, ln_gain=None,
+                    out: np.ndarray | None = None) -> np.ndarray:
+        x2 = x.reshape(-1, x.shape[-1])
+        n, k = weight.shape[0], weight.shape[1]
+        if out is None:
+            out = np.empty((x2.shape[0], n), np.float32)
+        self.keep(weight), self.keep(bias), self.keep(ln_gain)
+        call(self.lib.mynah_b200_qmat_linear, self.state, fp(weight), fp(x2), fp(out), x2.shape[0], k,
+             n, None if bias is None else fp(bias), None if ln_gain is None else fp(ln_gain))
+        return out
+
+
+def _p(dev):
+    if isinstance(dev, DeviceBuffer):
+        return dev.ptr
+    return dev
+
+
+class MatrixPool:
+    """`groups` distinct matrices (row rotations of one seeded matrix) resident
+    on the device, for streaming more weight bytes than L2 holds through the
+    product kernel."""
+
+    def __init__(self, backend: Backend, w: np.ndarray, groups: int, bias=None, gain=None):
+        self.backend = backend
+        self.n, self.k = w.shape
+        self.groups = groups
+        self.handle = C.c_void_p()
+        call(capi.lib().mynah_b200_pool_create, backend.state, fp(w), self.n, self.k, groups,
+             None if bias is None else fp(bias), None if gain is None else fp(gain),
+             C.byref(self.handle))
+
+    @property
+    def bytes_per_pass(self) -> int:
+        return int(capi.lib().mynah_b200_pool_bytes_per_pass(self.handle))
+
+    def linear(self, dev_x, dev_out):
+        call(capi.lib().mynah_b200_pool_linear, self.handle, _p(dev_x), _p(dev_out))
+
+    def close(self):
+        if self.handle:
+            capi.lib().mynah_b200_pool_destroy(self.handle)
+            self.handle = None
+
+
+class Decoder:
+    """The whole-step decoder over a synth.SynthModel (or any object with the
+    same accessors)."""
+
+    def __init__(self, backend: Backend, model, capacity: int, slots: int, max_batch: int | None = None,
+                 with_heads: bool = True):
+        self.backend = backend
+        self.model = model
+        s = model.shape
+        self.shape = s
+        self.capacity = capacity
+        self.slots = slots
+        self.max_batch = max_batch or slots
+        layers = (capi.LayerWeights * s.layers)()
+        for i in range(s.layers):
+            L = layers[i]
+            L.norm_self = fp(model.layer(i, "norm_self.weight"))
+            L.norm_xattn_query = fp(model.layer(i, "norm_xattn_query.weight"))
+            L.norm_pos_ff = fp(model.layer(i, "norm_pos_ff.weight"))
+            L.qkv_w = fp(model.layer(i, "self_attention.qkv_net.weight"))
+            L.o_self_w = fp(model.layer(i, "self_attention.o_net.weight"))
+            L.q_cross_w = fp(model.layer(i, "cross_attention.q_net.weight"))
+            L.o_cross_w = fp(model.layer(i, "cross_attention.o_net.weight"))
+            L.ffn_up_w = fp(model.layer(i, "pos_ff.proj.conv.weight"))
+            L.ffn_down_w = fp(model.layer(i, "pos_ff.o_net.conv.weight"))
+        desc = capi.DecoderDesc()
+        desc.layers, desc.width, desc.heads, desc.xattn_width = s.layers, s.width, s.heads, s.xattn_width
+        desc.memory_length, desc.capacity, desc.slots = s.memory_length, capacity, slots
+        desc.max_batch, desc.max_positions = self.max_batch, s.max_positions
+        desc.layer = layers
+        desc.position, desc.norm_out = fp(model.position), fp(model.norm_out)
+        if with_heads:
+            tabs = (capi.c_float_p * s.tables)(*[fp(model.embedding(t)) for t in range(s.tables)])
+            hw = (capi.c_float_p * s.tables)(*[fp(model.head_weight(t)) for t in range(s.tables)])
+            hb = (capi.c_float_p * s.tables)(*[fp(model.head_bias(t)) for t in range(s.tables)])
+            desc.tables, desc.vocab = s.tables, s.vocab
+            desc.codebook_size, desc.eos_id = s.codebook_size, s.eos_id
+            desc.embeddings, desc.head_w, desc.head_b = tabs, hw, hb
+        self.handle = C.c_void_p()
+        call(capi.lib().mynah_b200_decoder_create, backend.state, C.byref(desc), C.byref(self.handle))
+
+    def close(self):
+        if self.handle:
+            capi.lib().mynah_b200_decoder_destroy(self.handle)
+            self.handle = None
+
+    @property
+    def weight_bytes(self) -> int:
+        return int(capi.lib().mynah_b200_decoder_weight_bytes(self.handle))
+
+    def kv_bytes(self, length: int) -> int:
+        return int(capi.lib().mynah_b200_decoder_kv_bytes(self.handle, length))
+
+    def profile(self, enable: bool):
+        call(capi.lib().mynah_b200_decoder_profile, self.handle, int(enable))
+
+    def profile_read(self) -> dict:
+        """{call site: (launches, total device ms)} since profiling was enabled."""
+        n = capi.PROFILE_CLASSES
+        launches = (C.c_ulonglong * n)()
+        ms = (C.c_double * n)()
+        call(capi.lib().mynah_b200_decoder_profile_read, self.handle, launches, ms, n)
+        names = [capi.lib().mynah_b200_profile_class_name(i).decode() for i in range(n)]
+        return {names[i]: (int(launches[i]), float(ms[i])) for i in range(n)}
+
+    def slot_load(self, slot: int, cross_k, cross_v, self_k=None, self_v=None, length: int = 0):
+        ck = np.ascontiguousarray(cross_k, np.float32)
+        cv = np.ascontiguousarray(cross_v, np.float32)
+        sk = None if self_k is None else np.ascontiguousarray(self_k, np.float32)
+        sv = None if self_v is None else np.ascontiguousarray(self_v, np.float32)
+        call(capi.lib().mynah_b200_decoder_slot_load, self.handle, slot, fp(ck), fp(cv),
+             None if sk is None else fp(sk), None if sv is None else fp(sv), length)
+
+    def slot_length(self, slot: int) -> int:
+        n = capi.sz(0)
+        call(capi.lib().mynah_b200_decoder_slot_length, self.handle, slot, C.byref(n))
+        return int(n.value)
+
+    def slot_set_length(self, slot: int, length: int):
+        call(capi.lib().mynah_b200_decoder_slot_set_length, self.handle, slot, length)
+
+    def slot_read_kv(self, slot: int):
+        s = self.shape
+        k = np.empty((s.layers, self.capacity, s.width), np.float32)
+        v = np.empty_like(k)
+        call(capi.lib().mynah_b200_decoder_slot_read_kv, self.handle, slot, fp(k), fp(v))
+        return k, v
+
+    def set_layers(self, n: int):
+        call(capi.lib().mynah_b200_decoder_set_layers, self.handle, n)
+
+    def step_batch(self, slots, rows: np.ndarray, outs: np.ndarray | None = None) -> np.ndarray:
+        rows = np.ascontiguousarray(rows, np.float32)
+        batch = len(slots)
+        if outs is None:
+            outs = np.empty_like(rows)
+        slot_arr = (C.c_uint * batch)(*slots)
+        ins = (capi.c_float_p * batch)(*[fp(rows[b]) for b in range(batch)])
+        out_ptrs = (capi.c_float_p * batch)(*[fp(outs[b]) for b in range(batch)])
+        call(capi.lib().mynah_b200_decoder_step_batch, self.handle, slot_arr, ins, out_ptrs, batch)
+        return outs
+
+    def frame_batch(self, slots, codes: np.ndarray, allow_eos=None, want_hidden: bool = False,
+                    tokens: np.ndarray | None = None):
+        batch = len(slots)
+        codes = np.ascontiguousarray(codes, np.uint32)
+        if tokens is None:
+            tokens = np.empty((batch, self.shape.tables), np.uint32)
+        hidden = np.empty((batch, self.shape.width), np.float32) if want_hidden else None
+        slot_arr = (C.c_uint * batch)(*slots)
+        allow = None if allow_eos is None else (C.c_int * batch)(*[int(a) for a in allow_eos])
+        call(capi.lib().mynah_b200_decoder_frame_batch, self.handle, slot_arr,
+             codes.ctypes.data_as(capi.c_uint_p), allow, tokens.ctypes.data_as(capi.c_uint_p),
+             None if hidden is None else fp(hidden), batch)
+        return (tokens, hidden) if want_hidden else tokens
+
+    def greedy(self, slots, codes: np.ndarray, frames, min_frames: int = 0):
+        """codes [batch, tables]; frames: int or per-lane list.  Returns
+        (tokens [max_frames, batch, tables], eos_frame [batch], device ms)."""
+        batch = len(slots)
+        frames = [frames] * batch if isinstance(frames, int) else list(frames)
+        codes = np.ascontiguousarray(codes, np.uint32).copy()
+        tokens = np.zeros((max(frames), batch, self.shape.tables), np.uint32)
+        eos = (C.c_long * batch)()
+        ms = C.c_float(0.0)
+        call(capi.lib().mynah_b200_decoder_greedy, self.handle, (C.c_uint * batch)(*slots), batch,
+             codes.ctypes.data_as(capi.c_uint_p), (capi.sz * batch)(*frames), min_frames,
+             tokens.ctypes.data_as(capi.c_uint_p), eos, C.byref(ms))
+        return tokens, np.array(list(eos)), float(ms.value), codes

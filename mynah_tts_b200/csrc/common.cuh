@@ -1,0 +1,86 @@
+// Device helpers shared by the sm_100a kernels.
+//
+// All translation units are compiled with -fmad=false: the reference rounds
+// every product and sum separately (C11, no contraction), and a silently fused
+// multiply-add would move activation-quantization rounding boundaries.  Where
+// a fused multiply-add is wanted for speed it is written as fmaf explicitly.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define MB_WARP 32
+#define MB_FULL 0xffffffffu
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(MB_FULL, v, o);
+    return v;
+}
+__device__ __forceinline__ int warp_sum_i(int v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(MB_FULL, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(MB_FULL, v, o));
+    return v;
+}
+
+// Block-wide reductions; `red` is shared scratch of at least 33 floats.  Every
+// thread receives the result.  The summation order is fixed (lanes by
+// butterfly, then warps in index order) so results do not depend on timing.
+__device__ __forceinline__ float block_sum(float v, float *red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nw ? red[lane] : 0.0f;
+        t = warp_sum(t);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+}
+__device__ __forceinline__ float block_max(float v, float *red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nw ? red[lane] : -3.402823466e+38f;
+        t = warp_max(t);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+}
+
+// Round-half-away-from-zero to int with C truncation semantics:
+// (int)(v >= 0 ? v + 0.5f : v - 0.5f)   (src/qmat.c:54, 107 in mynah-tts)
+__device__ __forceinline__ int round_half_away(float v) {
+    return __float2int_rz(v >= 0.0f ? __fadd_rn(v, 0.5f) : __fsub_rn(v, 0.5f));
+}
+
+// tanh-form GELU of the reference's decode step (src/kernels.c:382-389):
+// 0.5*x*(1+tanhf(0.7978845608*(x+0.044715*x^3))), every operation rounded to
+// f32 in source order.  STRICT evaluates tanh in double and rounds once, which
+// agrees with a correctly rounded tanhf; the fast form uses CUDA's tanhf.
+template <bool STRICT>
+__device__ __forceinline__ float gelu_tanh(float x) {
+    const float cubic = __fmul_rn(__fmul_rn(x, x), x);
+    const float c = __fmul_rn(0.7978845608f, __fadd_rn(x, __fmul_rn(0.044715f, cubic)));
+    const float t = STRICT ? (float)tanh((double)c) : tanhf(c);
+    return __fmul_rn(__fmul_rn(0.5f, x), __fadd_rn(1.0f, t));
+}
+
+template <bool STRICT>
+__device__ __forceinline__ float exp_ref(float x) {
+    return STRICT ? (float)exp((double)x) : expf(x);
+}
+
+static inline int mb_check_launch() { return (int)cudaGetLastError(); }

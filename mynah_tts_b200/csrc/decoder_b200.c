@@ -1,0 +1,873 @@
+/* Whole-step Magpie decoder on one B200 (extension of the backend seam), C11.
+ *
+ * Restates decoder_step_batch of mynah-tts (src/graph.c:3127-3284) as one
+ * device-resident sequence per step -- position add, per layer LayerNorm ->
+ * qkv -> KV append + self-attention -> o -> residual -> LayerNorm -> cross q ->
+ * cross-attention -> o -> residual -> LayerNorm -> FFN up + GELU -> FFN down ->
+ * residual, then the output norm -- for `batch` independent requests ("slots")
+ * that each own a KV cache in the layout of src/graph.c:2823-2826.  The
+ * sequence is captured once per batch bucket into a CUDA graph and replayed;
+ * positions, slot ids and the live lane count are read from device memory so
+ * one graph serves every step.  The greedy front/back ends (embedding mean,
+ * logit heads, constrained argmax) follow src/graph.c:760-804 and 1538-1566.
+ */
+#include "host_common.h"
+#include "../../include/mynah_b200.h"
+
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+
+enum { MODE_STEP = 0, MODE_FRAME = 1 };
+#define MAX_BUCKETS 12
+
+typedef struct {
+    float *norm_self, *norm_xattn_query, *norm_pos_ff;
+    mb_dev_weight qkv, o_self, q_cross, o_cross, ffn_up, ffn_down;
+} dec_layer;
+
+typedef struct mb_decoder {
+    mb_state *st;
+    size_t layers, layers_run, width, heads, hw, ffn, xw, T, capacity, slots, max_batch;
+    size_t max_positions, tables, vocab, codebook_size, eos_id;
+    dec_layer *L;
+    float *position, *norm_out;
+    float *emb;                 /* [tables][vocab][width] */
+    const float **d_tables;     /* device array of table pointers */
+    mb_dev_weight heads_w;      /* [tables*vocab, width] */
+    float *heads_b;
+    float *self_k, *self_v, *cross_k, *cross_v;
+    /* activations, [max_batch][...] */
+    float *x, *nrm, *qkv, *attn, *q_x, *xctx, *hidden, *out, *rows_in, *logits;
+    int8_t *qx;
+    float *sx;
+    float *partials;
+    unsigned *counters;
+    size_t self_splits[MAX_BUCKETS], cross_splits[MAX_BUCKETS];
+    /* lane state */
+    int *d_lens, *d_slots, *d_n_active, *d_allow_eos, *d_eos_flag, *d_eos_frame, *d_frame_idx, *d_status;
+    int *d_min_frames;
+    unsigned *d_codes, *d_tokens, *d_history;
+    size_t history_frames;
+    /* pinned host staging */
+    float *h_rows, *h_out;
+    int *h_lens, *h_slots, *h_ints, *h_table;
+    unsigned *h_codes, *h_tokens;
+    size_t *slot_len;           /* host mirror of every slot's length */
+    cudaGraphExec_t graph[2][MAX_BUCKETS];
+    unsigned graph_launches[2][MAX_BUCKETS];
+    size_t bucket_size[MAX_BUCKETS];
+    size_t n_buckets;
+    int use_graphs;
+    cudaEvent_t ev0, ev1;
+    size_t weight_bytes;
+    /* per-call-site timing (profile mode: eager launches bracketed by events) */
+    int profiling;
+    cudaEvent_t *prof_ev;          /* PROF_POOL pairs */
+    int *prof_cls;
+    size_t prof_used;
+    unsigned long long prof_launches[MYNAH_B200_PROFILE_CLASSES];
+    double prof_ms[MYNAH_B200_PROFILE_CLASSES];
+} mb_decoder;
+
+#define PROF_POOL 4096u
+enum { PC_INPUT = 0, PC_NORM, PC_QKV, PC_ATTN_SELF, PC_O_SELF, PC_Q_CROSS, PC_ATTN_CROSS,
+       PC_O_CROSS, PC_FFN_UP, PC_QUANT, PC_FFN_DOWN, PC_HEADS, PC_ARGMAX, PC_ADVANCE };
+static const char *const prof_names[MYNAH_B200_PROFILE_CLASSES] = {
+    "input(embed|position)", "layernorm(+quant)", "qkv product", "self attention", "o_self product",
+    "q_cross product", "cross attention", "o_cross product", "ffn_up product(+gelu)",
+    "hidden quant", "ffn_down product", "heads product", "argmax", "advance"};
+
+static void prof_drain(mb_decoder *d) {
+    if (d->prof_used == 0) return;
+    cudaStreamSynchronize(d->st->stream);
+    for (size_t i = 0; i < d->prof_used; ++i) {
+        float ms = 0.0f;
+        if (cudaEventElapsedTime(&ms, d->prof_ev[2 * i], d->prof_ev[2 * i + 1]) == cudaSuccess) {
+            d->prof_ms[d->prof_cls[i]] += ms;
+            d->prof_launches[d->prof_cls[i]] += 1u;
+        }
+    }
+    d->prof_used = 0;
+}
+static void prof_begin(mb_decoder *d, int cls) {
+    if (!d->profiling) return;
+    if (d->prof_used == PROF_POOL) prof_drain(d);
+    d->prof_cls[d->prof_used] = cls;
+    cudaEventRecord(d->prof_ev[2 * d->prof_used], d->st->stream);
+}
+static void prof_end(mb_decoder *d) {
+    if (!d->profiling) return;
+    cudaEventRecord(d->prof_ev[2 * d->prof_used + 1], d->st->stream);
+    d->prof_used += 1u;
+}
+
+static int quantized_mode(const mb_decoder *d) {
+    return d->st->quant == MB_INT8 || d->st->quant == MB_INT4;
+}
+
+static int dmalloc(void **p, size_t bytes, char *error, size_t cap) {
+    *p = NULL;
+    return mb_cuda((int)cudaMalloc(p, bytes ? bytes : 4u), "cudaMalloc(decoder)", error, cap);
+}
+
+static int upload_vec(float **dst, const float *host, size_t n, char *error, size_t cap) {
+    if (dmalloc((void **)dst, n * sizeof(float), error, cap) != 0) return -1;
+    return mb_cuda((int)cudaMemcpy(*dst, host, n * sizeof(float), cudaMemcpyHostToDevice),
+                   "upload", error, cap);
+}
+
+static void destroy_graphs(mb_decoder *d) {
+    for (int m = 0; m < 2; ++m)
+        for (size_t i = 0; i < MAX_BUCKETS; ++i)
+            if (d->graph[m][i] != NULL) {
+                cudaGraphExecDestroy(d->graph[m][i]);
+                d->graph[m][i] = NULL;
+            }
+}
+
+void mynah_b200_decoder_destroy(void *decoder) {
+    mb_decoder *d = (mb_decoder *)decoder;
+    if (d == NULL) return;
+    cudaSetDevice(d->st->device);
+    cudaStreamSynchronize(d->st->stream);
+    destroy_graphs(d);
+    if (d->L != NULL) {
+        for (size_t l = 0; l < d->layers; ++l) {
+            dec_layer *L = &d->L[l];
+            cudaFree(L->norm_self); cudaFree(L->norm_xattn_query); cudaFree(L->norm_pos_ff);
+            mb_weight_release(&L->qkv); mb_weight_release(&L->o_self);
+            mb_weight_release(&L->q_cross); mb_weight_release(&L->o_cross);
+            mb_weight_release(&L->ffn_up); mb_weight_release(&L->ffn_down);
+        }
+        free(d->L);
+    }
+    mb_weight_release(&d->heads_w);
+    void *dev[] = {d->position, d->norm_out, d->emb, (void *)d->d_tables, d->heads_b, d->self_k,
+                   d->self_v, d->cross_k, d->cross_v, d->x, d->nrm, d->qkv, d->attn, d->q_x,
+                   d->xctx, d->hidden, d->out, d->rows_in, d->logits, d->qx, d->sx, d->partials,
+                   d->counters, d->d_lens, d->d_slots, d->d_n_active, d->d_allow_eos,
+                   d->d_eos_flag, d->d_eos_frame, d->d_frame_idx, d->d_status, d->d_min_frames, d->d_codes,
+                   d->d_tokens, d->d_history};
+    for (size_t i = 0; i < sizeof(dev) / sizeof(dev[0]); ++i) cudaFree(dev[i]);
+    void *pinned[] = {d->h_rows, d->h_out, d->h_lens, d->h_slots, d->h_ints, d->h_table,
+                      d->h_codes, d->h_tokens};
+    for (size_t i = 0; i < sizeof(pinned) / sizeof(pinned[0]); ++i)
+        if (pinned[i] != NULL) cudaFreeHost(pinned[i]);
+    if (d->prof_ev != NULL) {
+        for (size_t i = 0; i < 2u * PROF_POOL; ++i)
+            if (d->prof_ev[i] != NULL) cudaEventDestroy(d->prof_ev[i]);
+        free(d->prof_ev);
+    }
+    free(d->prof_cls);
+    if (d->ev0 != NULL) cudaEventDestroy(d->ev0);
+    if (d->ev1 != NULL) cudaEventDestroy(d->ev1);
+    free(d->slot_len);
+    free(d);
+}
+
+static size_t pick_bucket(const mb_decoder *d, size_t batch) {
+    for (size_t i = 0; i < d->n_buckets; ++i)
+        if (d->bucket_size[i] >= batch) return i;
+    return d->n_buckets - 1u;
+}
+
+static size_t splits_for(const mb_decoder *d, size_t batch, size_t heads, size_t positions) {
+    size_t splits = (2u * (size_t)d->st->sm_count + batch * heads - 1u) / (batch * heads);
+    const size_t by_len = (positions + 31u) / 32u;
+    if (splits > by_len) splits = by_len;
+    if (splits > 16u) splits = 16u;
+    if (splits < 1u) splits = 1u;
+    return splits;
+}
+
+int mynah_b200_decoder_create(void *state, const mynah_b200_decoder_desc *desc, void **decoder,
+                              char *error, size_t cap) {
+    mb_state *st = (mb_state *)state;
+    if (st == NULL || desc == NULL || decoder == NULL) {
+        mb_set_error(error, cap, "invalid decoder arguments");
+        return -1;
+    }
+    *decoder = NULL;
+    if (desc->layers == 0 || desc->width == 0 || desc->heads == 0 || desc->width % desc->heads != 0 ||
+        desc->xattn_width == 0 || desc->memory_length == 0 || desc->capacity == 0 ||
+        desc->slots == 0 || desc->max_batch == 0 || desc->max_batch > desc->slots ||
+        desc->max_batch > 1024u || desc->layer == NULL || desc->position == NULL ||
+        desc->norm_out == NULL || desc->max_positions < desc->capacity) {
+        mb_set_error(error, cap, "invalid decoder shape");
+        return -1;
+    }
+    if (desc->tables != 0 && (desc->embeddings == NULL || desc->head_w == NULL ||
+                              desc->head_b == NULL || desc->vocab == 0 ||
+                              desc->codebook_size > desc->vocab)) {
+        mb_set_error(error, cap, "invalid decoder head description");
+        return -1;
+    }
+    MB_TRY(cudaSetDevice(st->device), "cudaSetDevice");
+    mb_decoder *d = (mb_decoder *)calloc(1, sizeof(*d));
+    if (d == NULL) {
+        mb_set_error(error, cap, "out of memory creating decoder");
+        return -1;
+    }
+    d->st = st;
+    d->layers = d->layers_run = desc->layers;
+    d->width = desc->width;
+    d->heads = desc->heads;
+    d->hw = desc->width / desc->heads;
+    d->ffn = 4u * desc->width;                     /* src/graph.c:2973 */
+    d->xw = desc->xattn_width;
+    d->T = desc->memory_length;
+    d->capacity = desc->capacity;
+    d->slots = desc->slots;
+    d->max_batch = desc->max_batch;
+    d->max_positions = desc->max_positions;
+    d->tables = desc->tables;
+    d->vocab = desc->vocab;
+    d->codebook_size = desc->codebook_size;
+    d->eos_id = desc->eos_id;
+    const char *ng = getenv("MYNAH_B200_NO_GRAPH");
+    d->use_graphs = !(ng != NULL && strcmp(ng, "0") != 0);
+    const size_t W = d->width, F = d->ffn, XW = d->xw, MB = d->max_batch;
+    const int q = st->quant;
+    int ok = 1;
+#define D_TRY(expr) do { if (ok && (expr) != 0) ok = 0; } while (0)
+    d->L = (dec_layer *)calloc(d->layers, sizeof(dec_layer));
+    d->slot_len = (size_t *)calloc(d->slots, sizeof(size_t));
+    if (d->L == NULL || d->slot_len == NULL) { mb_set_error(error, cap, "out of memory"); ok = 0; }
+    for (size_t l = 0; ok && l < d->layers; ++l) {
+        const mynah_b200_layer_weights *s = &desc->layer[l];
+        dec_layer *L = &d->L[l];
+        D_TRY(upload_vec(&L->norm_self, s->norm_self, W, error, cap));
+        D_TRY(upload_vec(&L->norm_xattn_query, s->norm_xattn_query, W, error, cap));
+        D_TRY(upload_vec(&L->norm_pos_ff, s->norm_pos_ff, W, error, cap));
+        D_TRY(mb_weight_build(st, s->qkv_w, 3u * W, W, q, &L->qkv, error, cap));
+        D_TRY(mb_weight_build(st, s->o_self_w, W, W, q, &L->o_self, error, cap));
+        D_TRY(mb_weight_build(st, s->q_cross_w, XW, W, q, &L->q_cross, error, cap));
+        D_TRY(mb_weight_build(st, s->o_cross_w, W, XW, q, &L->o_cross, error, cap));
+        D_TRY(mb_weight_build(st, s->ffn_up_w, F, W, q, &L->ffn_up, error, cap));
+        D_TRY(mb_weight_build(st, s->ffn_down_w, W, F, q, &L->ffn_down, error, cap));
+        if (ok)
+            d->weight_bytes += L->qkv.bytes + L->o_self.bytes + L->q_cross.bytes + L->o_cross.bytes +
+                               L->ffn_up.bytes + L->ffn_down.bytes + 3u * W * sizeof(float);
+    }
+    D_TRY(upload_vec(&d->position, desc->position, d->max_positions * W, error, cap));
+    D_TRY(upload_vec(&d->norm_out, desc->norm_out, W, error, cap));
+    d->weight_bytes += W * sizeof(float);
+    if (ok && d->tables != 0) {
+        const size_t per = d->vocab * W;
+        float *joined = (float *)malloc(d->tables * per * sizeof(float));
+        float *joined_b = (float *)malloc(d->tables * d->vocab * sizeof(float));
+        const float **ptrs = (const float **)malloc(d->tables * sizeof(*ptrs));
+        if (joined == NULL || joined_b == NULL || ptrs == NULL) {
+            mb_set_error(error, cap, "out of memory joining heads");
+            ok = 0;
+        }
+        D_TRY(dmalloc((void **)&d->emb, d->tables * per * sizeof(float), error, cap));
+        D_TRY(dmalloc((void **)&d->d_tables, d->tables * sizeof(float *), error, cap));
+        for (size_t t = 0; ok && t < d->tables; ++t) {
+            D_TRY(mb_cuda((int)cudaMemcpy(d->emb + t * per, desc->embeddings[t], per * sizeof(float),
+                                          cudaMemcpyHostToDevice), "upload embeddings", error, cap));
+            ptrs[t] = d->emb + t * per;
+            memcpy(joined + t * per, desc->head_w[t], per * sizeof(float));
+            memcpy(joined_b + t * d->vocab, desc->head_b[t], d->vocab * sizeof(float));
+        }
+        D_TRY(mb_cuda((int)cudaMemcpy((void *)d->d_tables, ptrs, d->tables * sizeof(float *),
+                                      cudaMemcpyHostToDevice), "upload table pointers", error, cap));
+        /* per-row / per-group quantization makes the joined pack identical to
+         * packing each head alone */
+        D_TRY(mb_weight_build(st, joined, d->tables * d->vocab, W, q, &d->heads_w, error, cap));
+        D_TRY(upload_vec(&d->heads_b, joined_b, d->tables * d->vocab, error, cap));
+        free(joined);
+        free(joined_b);
+        free(ptrs);
+    }
+    /* KV pools */
+    const size_t self_n = d->slots * d->layers * d->capacity * W;
+    const size_t cross_n = d->slots * d->layers * d->T * XW;
+    D_TRY(dmalloc((void **)&d->self_k, self_n * sizeof(float), error, cap));
+    D_TRY(dmalloc((void **)&d->self_v, self_n * sizeof(float), error, cap));
+    D_TRY(dmalloc((void **)&d->cross_k, cross_n * sizeof(float), error, cap));
+    D_TRY(dmalloc((void **)&d->cross_v, cross_n * sizeof(float), error, cap));
+    /* activations */
+    D_TRY(dmalloc((void **)&d->x, MB * W * sizeof(float), error, cap));
+    D_TRY(dmalloc((void **)&d->nrm, MB * W * sizeof(float), error, cap));
+    D_TRY(dmalloc((void **)&d->qkv, MB * 3u * W * sizeof(float), error, cap));
+    D_TRY(dmalloc((void **)&d->attn, MB * W * sizeof(float), error, cap));
+    D_TRY(dmalloc((void **)&d->q_x, MB * XW * sizeof(float), error, cap));
+    D_TRY(dmalloc((void **)&d->xctx, MB * XW * sizeof(float), error, cap));
+    D_TRY(dmalloc((void **)&d->hidden, MB * F * sizeof(float), error, cap));
+    D_TRY(dmalloc((void **)&d->out, MB * W * sizeof(float), error, cap));
+    D_TRY(dmalloc((void **)&d->rows_in, MB * W * sizeof(float), error, cap));
+    D_TRY(dmalloc((void **)&d->qx, MB * F, error, cap));
+    D_TRY(dmalloc((void **)&d->sx, MB * sizeof(float), error, cap));
+    if (d->tables != 0) {
+        D_TRY(dmalloc((void **)&d->logits, MB * d->tables * d->vocab * sizeof(float), error, cap));
+        D_TRY(dmalloc((void **)&d->d_codes, MB * d->tables * sizeof(unsigned), error, cap));
+        D_TRY(dmalloc((void **)&d->d_tokens, MB * d->tables * sizeof(unsigned), error, cap));
+        d->history_frames = d->capacity;
+        D_TRY(dmalloc((void **)&d->d_history, d->history_frames * MB * d->tables * sizeof(unsigned), error, cap));
+    }
+    /* batch buckets: powers of two up to max_batch, then max_batch itself */
+    for (size_t b = 1; b < MB && d->n_buckets < MAX_BUCKETS - 1u; b *= 2u) d->bucket_size[d->n_buckets++] = b;
+    d->bucket_size[d->n_buckets++] = MB;
+    size_t partial_floats = 0;
+    for (size_t i = 0; i < d->n_buckets; ++i) {
+        const size_t b = d->bucket_size[i];
+        d->self_splits[i] = st->strict ? 1u : splits_for(d, b, d->heads, d->capacity);
+        d->cross_splits[i] = st->strict ? 1u : splits_for(d, b, 1u, d->T);
+        size_t need = mb_attention_partials_floats(b, d->heads, d->self_splits[i], d->hw);
+        if (need > partial_floats) partial_floats = need;
+        need = mb_attention_partials_floats(b, 1u, d->cross_splits[i], XW);
+        if (need > partial_floats) partial_floats = need;
+    }
+    D_TRY(dmalloc((void **)&d->partials, partial_floats * sizeof(float), error, cap));
+    D_TRY(dmalloc((void **)&d->counters, MB * sizeof(unsigned), error, cap));
+    int **ints[] = {&d->d_lens, &d->d_slots, &d->d_allow_eos, &d->d_eos_flag, &d->d_eos_frame};
+    for (size_t i = 0; i < sizeof(ints) / sizeof(ints[0]); ++i)
+        D_TRY(dmalloc((void **)ints[i], MB * sizeof(int), error, cap));
+    D_TRY(dmalloc((void **)&d->d_n_active, sizeof(int), error, cap));
+    D_TRY(dmalloc((void **)&d->d_frame_idx, sizeof(int), error, cap));
+    D_TRY(dmalloc((void **)&d->d_status, sizeof(int), error, cap));
+    D_TRY(dmalloc((void **)&d->d_min_frames, sizeof(int), error, cap));
+    if (ok) {
+        D_TRY(mb_cuda((int)cudaMemset(d->counters, 0, MB * sizeof(unsigned)), "memset", error, cap));
+        D_TRY(mb_cuda((int)cudaMemset(d->d_status, 0, sizeof(int)), "memset", error, cap));
+        D_TRY(mb_cuda((int)cudaMemset(d->d_min_frames, 0, sizeof(int)), "memset", error, cap));
+        D_TRY(mb_cuda((int)cudaMemset(d->d_eos_flag, 0, MB * sizeof(int)), "memset", error, cap));
+        D_TRY(mb_cuda((int)cudaMemset(d->self_k, 0, self_n * sizeof(float)), "memset", error, cap));
+        D_TRY(mb_cuda((int)cudaMemset(d->self_v, 0, self_n * sizeof(float)), "memset", error, cap));
+    }
+    /* pinned staging */
+    D_TRY(mb_cuda((int)cudaMallocHost((void **)&d->h_rows, MB * W * sizeof(float)), "cudaMallocHost", error, cap));
+    D_TRY(mb_cuda((int)cudaMallocHost((void **)&d->h_out, MB * W * sizeof(float)), "cudaMallocHost", error, cap));
+    D_TRY(mb_cuda((int)cudaMallocHost((void **)&d->h_lens, MB * sizeof(int)), "cudaMallocHost", error, cap));
+    D_TRY(mb_cuda((int)cudaMallocHost((void **)&d->h_slots, MB * sizeof(int)), "cudaMallocHost", error, cap));
+    D_TRY(mb_cuda((int)cudaMallocHost((void **)&d->h_ints, 4u * MB * sizeof(int)), "cudaMallocHost", error, cap));
+    D_TRY(mb_cuda((int)cudaMallocHost((void **)&d->h_table, (MB + 1u) * sizeof(int)), "cudaMallocHost", error, cap));
+    if (d->tables != 0) {
+        D_TRY(mb_cuda((int)cudaMallocHost((void **)&d->h_codes, MB * d->tables * sizeof(unsigned)), "cudaMallocHost", error, cap));
+        D_TRY(mb_cuda((int)cudaMallocHost((void **)&d->h_tokens, MB * d->tables * sizeof(unsigned)), "cudaMallocHost", error, cap));
+    }
+    D_TRY(mb_cuda((int)cudaEventCreate(&d->ev0), "cudaEventCreate", error, cap));
+    D_TRY(mb_cuda((int)cudaEventCreate(&d->ev1), "cudaEventCreate", error, cap));
+#undef D_TRY
+    if (!ok) {
+        mynah_b200_decoder_destroy(d);
+        return -1;
+    }
+    for (size_t i = 0; i <= MB; ++i) d->h_table[i] = (int)i;
+    *decoder = d;
+    mb_clear_error(error, cap);
+    return 0;
+}
+
+size_t mynah_b200_decoder_weight_bytes(const void *decoder) {
+    const mb_decoder *d = (const mb_decoder *)decoder;
+    return d == NULL ? 0u : d->weight_bytes;
+}
+
+/* self K+V rows [0, length] of every layer read once, one row of each written,
+ * plus the constant cross K/V */
+size_t mynah_b200_decoder_kv_bytes(const void *decoder, size_t length) {
+    const mb_decoder *d = (const mb_decoder *)decoder;
+    if (d == NULL) return 0u;
+    return d->layers * (2u * (length + 1u) * d->width + 2u * d->width + 2u * d->T * d->xw) * sizeof(float);
+}
+
+/* ------------------------------------------------------------ the sequence */
+static int product(mb_decoder *d, const mb_dev_weight *w, const float *bias, const float *act_f32,
+                   float *out, size_t out_stride, size_t nb, int epilogue, unsigned *count) {
+    mb_gemv_args g;
+    memset(&g, 0, sizeof(g));
+    mb_gemv_bind_weight(&g, w, bias);
+    g.out = out;
+    g.out_stride = out_stride;
+    g.batch = nb;
+    g.n_active = d->d_n_active;
+    g.epilogue = epilogue;
+    g.strict = d->st->strict;
+    if (w->qtype == MB_INT8 || w->qtype == MB_INT4) {
+        g.qx = d->qx;
+        g.sx = d->sx;
+    } else {
+        g.x = act_f32;
+    }
+    *count += 1u;
+    return mb_gemv(&g, d->st->stream);
+}
+
+static int norm(mb_decoder *d, const float *in, float *out, const float *gain, size_t nb,
+                unsigned *count) {
+    const int q = quantized_mode(d);
+    *count += 1u;
+    return mb_layernorm(in, out, gain, NULL, nb, d->width, 1.0e-5f, q ? d->qx : NULL,
+                        q ? d->sx : NULL, d->d_n_active, d->st->strict, d->st->stream);
+}
+
+static int enqueue(mb_decoder *d, size_t bucket, int mode, unsigned *count) {
+    mb_state *st = d->st;
+    mb_stream s = st->stream;
+    const size_t nb = d->bucket_size[bucket];
+    const size_t W = d->width, F = d->ffn, XW = d->xw;
+    const int q = quantized_mode(d);
+    const float self_scale = 1.0f / sqrtf((float)d->hw);   /* src/graph.c:3143-3144 */
+    const float cross_scale = 1.0f / sqrtf((float)XW);
+    int rc = 0;
+#define E_TRY(expr) do { if (rc == 0) rc = (expr); } while (0)
+#define P(cls, expr) do { prof_begin(d, (cls)); E_TRY(expr); prof_end(d); } while (0)
+    prof_begin(d, PC_INPUT);
+    if (mode == MODE_FRAME) {
+        E_TRY(mb_embed_frames(d->d_tables, d->tables, d->vocab, W, d->d_codes, d->position,
+                              d->d_lens, d->x, nb, d->d_n_active, d->d_status, s));
+    } else {
+        E_TRY(mb_add_position(d->rows_in, d->position, d->d_lens, d->x, nb, W, d->d_n_active, s));
+    }
+    prof_end(d);
+    *count += 1u;
+    for (size_t l = 0; l < d->layers_run && rc == 0; ++l) {
+        const dec_layer *L = &d->L[l];
+        P(PC_NORM, norm(d, d->x, d->nrm, L->norm_self, nb, count));
+        P(PC_QKV, product(d, &L->qkv, NULL, d->nrm, d->qkv, 3u * W, nb, MB_EPI_STORE, count));
+        mb_attn_args a;
+        memset(&a, 0, sizeof(a));
+        a.q = d->qkv;
+        a.q_stride = 3u * W;
+        a.k_new = d->qkv + W;
+        a.v_new = d->qkv + 2u * W;
+        a.k_cache = d->self_k + l * d->capacity * W;
+        a.v_cache = d->self_v + l * d->capacity * W;
+        a.slot_stride = d->layers * d->capacity * W;
+        a.slots = d->d_slots;
+        a.lens = d->d_lens;
+        a.valid = d->capacity;
+        a.cache_stride = W;
+        a.heads = d->heads;
+        a.head_width = d->hw;
+        a.scale = self_scale;
+        a.out = d->attn;
+        a.out_stride = W;
+        a.qx = q ? d->qx : NULL;
+        a.sx = q ? d->sx : NULL;
+        a.batch = nb;
+        a.n_active = d->d_n_active;
+        a.strict = st->strict;
+        a.splits = d->self_splits[bucket];
+        a.partials = d->partials;
+        a.counters = d->counters;
+        a.status = d->d_status;
+        P(PC_ATTN_SELF, mb_attention(&a, s));
+        *count += (st->strict && q) ? 2u : 1u;
+        P(PC_O_SELF, product(d, &L->o_self, NULL, d->attn, d->x, W, nb, MB_EPI_RESIDUAL, count));
+        P(PC_NORM, norm(d, d->x, d->nrm, L->norm_xattn_query, nb, count));
+        P(PC_Q_CROSS, product(d, &L->q_cross, NULL, d->nrm, d->q_x, XW, nb, MB_EPI_STORE, count));
+        memset(&a, 0, sizeof(a));
+        a.q = d->q_x;
+        a.q_stride = XW;
+        a.k_cache = d->cross_k + l * d->T * XW;
+        a.v_cache = d->cross_v + l * d->T * XW;
+        a.slot_stride = d->layers * d->T * XW;
+        a.slots = d->d_slots;
+        a.position = 0;
+        a.valid = d->T;
+        a.cache_stride = XW;
+        a.heads = 1;
+        a.head_width = XW;
+        a.scale = cross_scale;
+        a.out = d->xctx;
+        a.out_stride = XW;
+        a.qx = q ? d->qx : NULL;
+        a.sx = q ? d->sx : NULL;
+        a.batch = nb;
+        a.n_active = d->d_n_active;
+        a.strict = st->strict;
+        a.splits = d->cross_splits[bucket];
+        a.partials = d->partials;
+        a.counters = d->counters;
+        a.status = d->d_status;
+        P(PC_ATTN_CROSS, mb_attention(&a, s));
+        *count += (st->strict && q) ? 2u : 1u;
+        P(PC_O_CROSS, product(d, &L->o_cross, NULL, d->xctx, d->x, W, nb, MB_EPI_RESIDUAL, count));
+        P(PC_NORM, norm(d, d->x, d->nrm, L->norm_pos_ff, nb, count));
+        P(PC_FFN_UP, product(d, &L->ffn_up, NULL, d->nrm, d->hidden, F, nb, MB_EPI_GELU, count));
+        if (q) {
+            P(PC_QUANT, mb_quant_rows(d->hidden, nb, F, d->qx, d->sx, d->d_n_active, s));
+            *count += 1u;
+        }
+        P(PC_FFN_DOWN, product(d, &L->ffn_down, NULL, d->hidden, d->x, W, nb, MB_EPI_RESIDUAL, count));
+    }
+    P(PC_NORM, norm(d, d->x, d->out, d->norm_out, nb, count));
+    if (mode == MODE_FRAME) {
+        P(PC_HEADS, product(d, &d->heads_w, d->heads_b, d->out, d->logits, d->tables * d->vocab, nb,
+                            MB_EPI_STORE, count));
+        P(PC_ARGMAX, mb_argmax_rows(d->logits, nb * d->tables, d->vocab, d->codebook_size, d->eos_id,
+                                    d->d_allow_eos, 0, d->d_tokens, d->d_codes, d->d_eos_flag,
+                                    d->tables, d->d_n_active, s));
+        P(PC_ADVANCE, mb_frame_advance(d->d_lens, d->d_tokens, d->d_history, d->d_frame_idx,
+                                       d->d_eos_flag, d->d_eos_frame, d->d_allow_eos, nb,
+                                       d->max_batch, d->tables, d->d_min_frames, d->history_frames,
+                                       d->d_n_active, s));
+        *count += 2u;
+    } else {
+        P(PC_ADVANCE, mb_advance_lens(d->d_lens, nb, d->d_n_active, s));
+        *count += 1u;
+    }
+#undef P
+#undef E_TRY
+    return rc;
+}
+
+/* Launch one step for the bucket that holds `batch` lanes (graph replay, or the
+ * eager sequence when graphs are disabled). */
+static int run(mb_decoder *d, size_t batch, int mode, char *error, size_t cap) {
+    const size_t bucket = pick_bucket(d, batch);
+    mb_state *st = d->st;
+    if (!d->use_graphs || d->profiling) {
+        unsigned count = 0;
+        MB_TRY(enqueue(d, bucket, mode, &count), "decoder step");
+        st->launches += count;
+        return 0;
+    }
+    if (d->graph[mode][bucket] == NULL) {
+        cudaGraph_t graph = NULL;
+        unsigned count = 0;
+        MB_TRY(cudaStreamBeginCapture(st->stream, cudaStreamCaptureModeThreadLocal), "begin capture");
+        const int rc = enqueue(d, bucket, mode, &count);
+        const int rc_end = (int)cudaStreamEndCapture(st->stream, &graph);
+        if (rc != 0 || rc_end != 0) {
+            if (graph != NULL) cudaGraphDestroy(graph);
+            return mb_cuda(rc != 0 ? rc : rc_end, "capture decoder step", error, cap);
+        }
+        const int rc_inst = (int)cudaGraphInstantiate(&d->graph[mode][bucket], graph, 0);
+        cudaGraphDestroy(graph);
+        if (rc_inst != 0) {
+            d->graph[mode][bucket] = NULL;
+            return mb_cuda(rc_inst, "instantiate decoder graph", error, cap);
+        }
+        d->graph_launches[mode][bucket] = count;
+    }
+    MB_TRY(cudaGraphLaunch(d->graph[mode][bucket], st->stream), "launch decoder graph");
+    st->launches += d->graph_launches[mode][bucket];
+    return 0;
+}
+
+/* --------------------------------------------------------------- slot state */
+static int check_slot(const mb_decoder *d, size_t slot, char *error, size_t cap) {
+    if (d == NULL || slot >= d->slots) {
+        mb_set_error(error, cap, "decoder slot out of range");
+        return -1;
+    }
+    return mb_cuda((int)cudaSetDevice(d->st->device), "cudaSetDevice", error, cap);
+}
+
+int mynah_b200_decoder_slot_load(void *decoder, size_t slot, const float *cross_k,
+                                 const float *cross_v, const float *self_k, const float *self_v,
+                                 size_t length, char *error, size_t cap) {
+    mb_decoder *d = (mb_decoder *)decoder;
+    if (check_slot(d, slot, error, cap) != 0) return -1;
+    if (cross_k == NULL || cross_v == NULL || length > d->capacity ||
+        (length > 0 && (self_k == NULL || self_v == NULL))) {
+        mb_set_error(error, cap, "invalid slot contents");
+        return -1;
+    }
+    cudaStream_t s = d->st->stream;
+    const size_t cross_n = d->layers * d->T * d->xw;
+    MB_TRY(cudaMemcpyAsync(d->cross_k + slot * cross_n, cross_k, cross_n * sizeof(float),
+                           cudaMemcpyHostToDevice, s), "upload cross K");
+    MB_TRY(cudaMemcpyAsync(d->cross_v + slot * cross_n, cross_v, cross_n * sizeof(float),
+                           cudaMemcpyHostToDevice, s), "upload cross V");
+    const size_t per_layer = d->capacity * d->width;
+    for (size_t l = 0; l < d->layers && length > 0; ++l) {
+        const size_t off = (slot * d->layers + l) * per_layer;
+        MB_TRY(cudaMemcpyAsync(d->self_k + off, self_k + l * per_layer, length * d->width * sizeof(float),
+                               cudaMemcpyHostToDevice, s), "upload self K");
+        MB_TRY(cudaMemcpyAsync(d->self_v + off, self_v + l * per_layer, length * d->width * sizeof(float),
+                               cudaMemcpyHostToDevice, s), "upload self V");
+    }
+    MB_TRY(cudaStreamSynchronize(s), "cudaStreamSynchronize");
+    d->slot_len[slot] = length;
+    mb_clear_error(error, cap);
+    return 0;
+}
+
+int mynah_b200_decoder_slot_length(void *decoder, size_t slot, size_t *length, char *error, size_t cap) {
+    mb_decoder *d = (mb_decoder *)decoder;
+    if (check_slot(d, slot, error, cap) != 0 || length == NULL) return -1;
+    *length = d->slot_len[slot];
+    mb_clear_error(error, cap);
+    return 0;
+}
+
+int mynah_b200_decoder_slot_set_length(void *decoder, size_t slot, size_t length, char *error, size_t cap) {
+    mb_decoder *d = (mb_decoder *)decoder;
+    if (check_slot(d, slot, error, cap) != 0) return -1;
+    if (length > d->capacity) {
+        mb_set_error(error, cap, "slot length beyond capacity");
+        return -1;
+    }
+    d->slot_len[slot] = length;
+    mb_clear_error(error, cap);
+    return 0;
+}
+
+int mynah_b200_decoder_slot_read_kv(void *decoder, size_t slot, float *self_k, float *self_v,
+                                    char *error, size_t cap) {
+    mb_decoder *d = (mb_decoder *)decoder;
+    if (check_slot(d, slot, error, cap) != 0 || self_k == NULL || self_v == NULL) return -1;
+    const size_t n = d->layers * d->capacity * d->width;
+    MB_TRY(cudaStreamSynchronize(d->st->stream), "cudaStreamSynchronize");
+    MB_TRY(cudaMemcpy(self_k, d->self_k + slot * n, n * sizeof(float), cudaMemcpyDeviceToHost), "read K");
+    MB_TRY(cudaMemcpy(self_v, d->self_v + slot * n, n * sizeof(float), cudaMemcpyDeviceToHost), "read V");
+    mb_clear_error(error, cap);
+    return 0;
+}
+
+int mynah_b200_decoder_set_layers(void *decoder, size_t n, char *error, size_t cap) {
+    mb_decoder *d = (mb_decoder *)decoder;
+    if (d == NULL || n == 0 || n > d->layers) {
+        mb_set_error(error, cap, "layer count out of range");
+        return -1;
+    }
+    MB_TRY(cudaSetDevice(d->st->device), "cudaSetDevice");
+    MB_TRY(cudaStreamSynchronize(d->st->stream), "cudaStreamSynchronize");
+    if (n != d->layers_run) destroy_graphs(d);
+    d->layers_run = n;
+    mb_clear_error(error, cap);
+    return 0;
+}
+
+/* ----------------------------------------------------------------- stepping */
+/* Validate the slot list and stage slot ids and positions for the lanes. */
+static int stage_lanes(mb_decoder *d, const unsigned *slots, size_t batch, char *error, size_t cap) {
+    if (d == NULL || slots == NULL || batch == 0 || batch > d->max_batch) {
+        mb_set_error(error, cap, "decoder batch exceeds max_batch");   /* src/graph.c:3133-3136 */
+        return -1;
+    }
+    MB_TRY(cudaSetDevice(d->st->device), "cudaSetDevice");
+    for (size_t b = 0; b < batch; ++b) {
+        if (slots[b] >= d->slots) {
+            mb_set_error(error, cap, "decoder slot out of range");
+            return -1;
+        }
+        for (size_t o = 0; o < b; ++o)
+            if (slots[o] == slots[b]) {
+                mb_set_error(error, cap, "a slot may appear once per step");
+                return -1;
+            }
+        if (d->slot_len[slots[b]] >= d->capacity || d->slot_len[slots[b]] >= d->max_positions) {
+            mb_set_error(error, cap, "decoder cache capacity exceeded");   /* src/graph.c:3152-3155 */
+            return -1;
+        }
+        d->h_slots[b] = (int)slots[b];
+        d->h_lens[b] = (int)d->slot_len[slots[b]];
+    }
+    cudaStream_t s = d->st->stream;
+    MB_TRY(cudaMemcpyAsync(d->d_slots, d->h_slots, batch * sizeof(int), cudaMemcpyHostToDevice, s), "stage slots");
+    MB_TRY(cudaMemcpyAsync(d->d_lens, d->h_lens, batch * sizeof(int), cudaMemcpyHostToDevice, s), "stage positions");
+    MB_TRY(cudaMemcpyAsync(d->d_n_active, &d->h_table[batch], sizeof(int), cudaMemcpyHostToDevice, s), "stage lane count");
+    return 0;
+}
+
+static int check_status(mb_decoder *d, char *error, size_t cap) {
+    int status = 0;
+    MB_TRY(cudaMemcpy(&status, d->d_status, sizeof(int), cudaMemcpyDeviceToHost), "read status");
+    if (status != 0) {
+        cudaMemset(d->d_status, 0, sizeof(int));
+        mb_set_error(error, cap, "audio token id is outside vocabulary");   /* src/graph.c:794-797 */
+        return -1;
+    }
+    return 0;
+}
+
+int mynah_b200_decoder_step_batch(void *decoder, const unsigned *slots,
+                                  const float *const *inputs, float *const *outs, size_t batch,
+                                  char *error, size_t cap) {
+    mb_decoder *d = (mb_decoder *)decoder;
+    if (d != NULL && batch == 0) return 0;   /* src/graph.c:3132 */
+    if (inputs == NULL || outs == NULL) {
+        mb_set_error(error, cap, "invalid decoder step buffers");
+        return -1;
+    }
+    if (stage_lanes(d, slots, batch, error, cap) != 0) return -1;
+    const size_t W = d->width;
+    cudaStream_t s = d->st->stream;
+    for (size_t b = 0; b < batch; ++b) memcpy(d->h_rows + b * W, inputs[b], W * sizeof(float));
+    MB_TRY(cudaMemcpyAsync(d->rows_in, d->h_rows, batch * W * sizeof(float), cudaMemcpyHostToDevice, s), "stage inputs");
+    if (run(d, batch, MODE_STEP, error, cap) != 0) return -1;
+    MB_TRY(cudaMemcpyAsync(d->h_out, d->out, batch * W * sizeof(float), cudaMemcpyDeviceToHost, s), "read outputs");
+    MB_TRY(cudaStreamSynchronize(s), "cudaStreamSynchronize");
+    for (size_t b = 0; b < batch; ++b) {
+        memcpy(outs[b], d->h_out + b * W, W * sizeof(float));
+        d->slot_len[slots[b]] += 1u;
+    }
+    mb_clear_error(error, cap);
+    return 0;
+}
+
+int mynah_b200_decoder_frame_batch(void *decoder, const unsigned *slots, const unsigned *codes,
+                                   const int *allow_eos, unsigned *tokens, float *hidden,
+                                   size_t batch, char *error, size_t cap) {
+    mb_decoder *d = (mb_decoder *)decoder;
+    if (d != NULL && batch == 0) return 0;
+    if (d == NULL || d->tables == 0 || codes == NULL || tokens == NULL) {
+        mb_set_error(error, cap, "decoder has no embedding tables or heads");
+        return -1;
+    }
+    if (stage_lanes(d, slots, batch, error, cap) != 0) return -1;
+    const size_t nt = batch * d->tables;
+    cudaStream_t s = d->st->stream;
+    memcpy(d->h_codes, codes, nt * sizeof(unsigned));
+    for (size_t b = 0; b < batch; ++b) d->h_ints[b] = allow_eos == NULL ? 1 : (allow_eos[b] != 0);
+    MB_TRY(cudaMemcpyAsync(d->d_codes, d->h_codes, nt * sizeof(unsigned), cudaMemcpyHostToDevice, s), "stage codes");
+    MB_TRY(cudaMemcpyAsync(d->d_allow_eos, d->h_ints, batch * sizeof(int), cudaMemcpyHostToDevice, s), "stage eos rule");
+    MB_TRY(cudaMemsetAsync(d->d_eos_flag, 0, batch * sizeof(int), s), "clear eos flags");
+    /* history row 0 is scratch for this entry point; the allow_eos flags written
+     * by frame_advance are restaged on every call */
+    MB_TRY(cudaMemsetAsync(d->d_frame_idx, 0, sizeof(int), s), "clear frame index");
+    if (run(d, batch, MODE_FRAME, error, cap) != 0) return -1;
+    MB_TRY(cudaMemcpyAsync(d->h_tokens, d->d_tokens, nt * sizeof(unsigned), cudaMemcpyDeviceToHost, s), "read tokens");
+    if (hidden != NULL)
+        MB_TRY(cudaMemcpyAsync(d->h_out, d->out, batch * d->width * sizeof(float), cudaMemcpyDeviceToHost, s), "read hidden");
+    MB_TRY(cudaStreamSynchronize(s), "cudaStreamSynchronize");
+    if (check_status(d, error, cap) != 0) return -1;
+    memcpy(tokens, d->h_tokens, nt * sizeof(unsigned));
+    if (hidden != NULL) memcpy(hidden, d->h_out, batch * d->width * sizeof(float));
+    for (size_t b = 0; b < batch; ++b) d->slot_len[slots[b]] += 1u;
+    mb_clear_error(error, cap);
+    return 0;
+}
+
+int mynah_b200_decoder_greedy(void *decoder, const unsigned *slots, size_t batch, unsigned *codes,
+                              const size_t *frames, size_t min_frames, unsigned *tokens,
+                              long *eos_frame, float *elapsed_ms, char *error, size_t cap) {
+    mb_decoder *d = (mb_decoder *)decoder;
+    if (d == NULL || d->tables == 0 || codes == NULL || frames == NULL || tokens == NULL ||
+        slots == NULL || batch == 0 || batch > d->max_batch) {
+        mb_set_error(error, cap, "invalid greedy decode request");
+        return -1;
+    }
+    /* lanes ordered by frame count, longest first, so live lanes are a prefix */
+    size_t *order = (size_t *)malloc(batch * sizeof(size_t));
+    unsigned *lane_slots = (unsigned *)malloc(batch * sizeof(unsigned));
+    if (order == NULL || lane_slots == NULL) {
+        free(order); free(lane_slots);
+        mb_set_error(error, cap, "out of memory");
+        return -1;
+    }
+    for (size_t i = 0; i < batch; ++i) order[i] = i;
+    for (size_t i = 1; i < batch; ++i) {           /* stable insertion sort, descending */
+        const size_t v = order[i];
+        size_t j = i;
+        while (j > 0 && frames[order[j - 1]] < frames[v]) { order[j] = order[j - 1]; --j; }
+        order[j] = v;
+    }
+    const size_t max_frames = frames[order[0]];
+    int rc = 0;
+    for (size_t i = 0; i < batch; ++i) {
+        lane_slots[i] = slots[order[i]];
+        if (slots[order[i]] < d->slots &&
+            d->slot_len[slots[order[i]]] + frames[order[i]] > d->capacity) rc = -1;
+    }
+    if (rc != 0 || max_frames > d->history_frames) {
+        free(order); free(lane_slots);
+        mb_set_error(error, cap, "decoder cache capacity exceeded");
+        return -1;
+    }
+    if (max_frames == 0) { free(order); free(lane_slots); return 0; }
+    if (stage_lanes(d, lane_slots, batch, error, cap) != 0) { free(order); free(lane_slots); return -1; }
+    const size_t T = d->tables;
+    cudaStream_t s = d->st->stream;
+    for (size_t i = 0; i < batch; ++i) {
+        memcpy(d->h_codes + i * T, codes + order[i] * T, T * sizeof(unsigned));
+        d->h_ints[i] = min_frames == 0 ? 1 : 0;                 /* allow_eos at frame 0 */
+        d->h_ints[d->max_batch + i] = -1;                       /* eos_frame */
+    }
+    d->h_ints[2u * d->max_batch] = min_frames > 0x7fffffffu ? 0x7fffffff : (int)min_frames;
+#define G_TRY(expr, what) do { if (rc == 0 && mb_cuda((int)(expr), (what), error, cap) != 0) rc = -1; } while (0)
+    G_TRY(cudaMemcpyAsync(d->d_codes, d->h_codes, batch * T * sizeof(unsigned), cudaMemcpyHostToDevice, s), "stage codes");
+    G_TRY(cudaMemcpyAsync(d->d_allow_eos, d->h_ints, batch * sizeof(int), cudaMemcpyHostToDevice, s), "stage eos rule");
+    G_TRY(cudaMemcpyAsync(d->d_eos_frame, d->h_ints + d->max_batch, batch * sizeof(int), cudaMemcpyHostToDevice, s), "stage eos frames");
+    G_TRY(cudaMemcpyAsync(d->d_min_frames, d->h_ints + 2u * d->max_batch, sizeof(int), cudaMemcpyHostToDevice, s), "stage min frames");
+    G_TRY(cudaMemsetAsync(d->d_eos_flag, 0, d->max_batch * sizeof(int), s), "clear eos flags");
+    G_TRY(cudaMemsetAsync(d->d_frame_idx, 0, sizeof(int), s), "clear frame index");
+    G_TRY(cudaMemsetAsync(d->d_history, 0, max_frames * d->max_batch * T * sizeof(unsigned), s), "clear history");
+    G_TRY(cudaEventRecord(d->ev0, s), "record event");
+    size_t live = batch;
+    for (size_t f = 0; f < max_frames && rc == 0; ++f) {
+        size_t now = live;
+        while (now > 0 && frames[order[now - 1]] <= f) --now;
+        if (now != live) {
+            live = now;
+            G_TRY(cudaMemcpyAsync(d->d_n_active, &d->h_table[live], sizeof(int), cudaMemcpyHostToDevice, s), "stage lane count");
+        }
+        if (rc == 0 && run(d, live, MODE_FRAME, error, cap) != 0) rc = -1;
+    }
+    G_TRY(cudaEventRecord(d->ev1, s), "record event");
+    unsigned *hist = (unsigned *)malloc(max_frames * d->max_batch * T * sizeof(unsigned));
+    int *eosf = (int *)malloc(batch * sizeof(int));
+    if (hist == NULL || eosf == NULL) { mb_set_error(error, cap, "out of memory"); rc = -1; }
+    G_TRY(cudaMemcpyAsync(hist, d->d_history, max_frames * d->max_batch * T * sizeof(unsigned), cudaMemcpyDeviceToHost, s), "read tokens");
+    G_TRY(cudaMemcpyAsync(eosf, d->d_eos_frame, batch * sizeof(int), cudaMemcpyDeviceToHost, s), "read eos frames");
+    G_TRY(cudaMemcpyAsync(d->h_codes, d->d_codes, batch * T * sizeof(unsigned), cudaMemcpyDeviceToHost, s), "read codes");
+    G_TRY(cudaStreamSynchronize(s), "cudaStreamSynchronize");
+    if (rc == 0 && elapsed_ms != NULL) G_TRY(cudaEventElapsedTime(elapsed_ms, d->ev0, d->ev1), "event time");
+    if (rc == 0 && check_status(d, error, cap) != 0) rc = -1;
+#undef G_TRY
+    if (rc == 0) {
+        memset(tokens, 0, max_frames * batch * T * sizeof(unsigned));
+        for (size_t i = 0; i < batch; ++i) {
+            const size_t b = order[i];
+            for (size_t f = 0; f < frames[b]; ++f)
+                memcpy(tokens + (f * batch + b) * T, hist + (f * d->max_batch + i) * T, T * sizeof(unsigned));
+            memcpy(codes + b * T, d->h_codes + i * T, T * sizeof(unsigned));
+            if (eos_frame != NULL) eos_frame[b] = eosf[i];
+            d->slot_len[slots[b]] += frames[b];
+        }
+        mb_clear_error(error, cap);
+    }
+    free(hist); free(eosf); free(order); free(lane_slots);
+    return rc;
+}
+
+/* ----------------------------------------------------------------- profiling */
+int mynah_b200_decoder_profile(void *decoder, int enable, char *error, size_t cap) {
+    mb_decoder *d = (mb_decoder *)decoder;
+    if (d == NULL) return -1;
+    MB_TRY(cudaSetDevice(d->st->device), "cudaSetDevice");
+    if (enable && d->prof_ev == NULL) {
+        d->prof_ev = (cudaEvent_t *)calloc(2u * PROF_POOL, sizeof(cudaEvent_t));
+        d->prof_cls = (int *)calloc(PROF_POOL, sizeof(int));
+        if (d->prof_ev == NULL || d->prof_cls == NULL) {
+            mb_set_error(error, cap, "out of memory");
+            return -1;
+        }
+        for (size_t i = 0; i < 2u * PROF_POOL; ++i)
+            MB_TRY(cudaEventCreate(&d->prof_ev[i]), "cudaEventCreate");
+    }
+    if (!enable) prof_drain(d);
+    d->profiling = enable != 0;
+    if (enable) {
+        prof_drain(d);
+        memset(d->prof_launches, 0, sizeof(d->prof_launches));
+        memset(d->prof_ms, 0, sizeof(d->prof_ms));
+    }
+    mb_clear_error(error, cap);
+    return 0;
+}
+
+int mynah_b200_decoder_profile_read(void *decoder, unsigned long long *launches, double *ms,
+                                    size_t n, char *error, size_t cap) {
+    mb_decoder *d = (mb_decoder *)decoder;
+    if (d == NULL || launches == NULL || ms == NULL) return -1;
+    MB_TRY(cudaSetDevice(d->st->device), "cudaSetDevice");
+    prof_drain(d);
+    for (size_t i = 0; i < n && i < MYNAH_B200_PROFILE_CLASSES; ++i) {
+        launches[i] = d->prof_launches[i];
+        ms[i] = d->prof_ms[i];
+    }
+    mb_clear_error(error, cap);
+    return 0;
+}
+
+const char *mynah_b200_profile_class_name(size_t cls) {
+    return cls < MYNAH_B200_PROFILE_CLASSES ? prof_names[cls] : "";
+}

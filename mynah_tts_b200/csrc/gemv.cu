@@ -1,0 +1,444 @@
+// Quantized matrix-vector products of the decode step (SIMT path, batch-generic):
+//   out[b][r] = epilogue( dot(W[r,:], act[b,:]) * scales + bias )
+// for int8 per-row weights, int4 group-of-32 weights, f16 and f32 weights, in
+// the byte layouts the reference's quantizers produce.
+//
+// Numerics (reference: src/qmat.c:136-185, 191-304, 319-377):
+//   int8  the int32 sum is exact, so any summation order gives the reference's
+//         bits; then (float)s * ws * sx (+ bias), each product rounded to f32.
+//   int4  per group an exact int32 sum; the f32 accumulation over groups runs in
+//         group order exactly as the reference's scalar kernel, so the result
+//         is bit-identical given the same quantized activation.
+//   f16/f32  tree reduction with fused multiply-adds: agrees with the reference
+//         to rounding error only (its own tolerance for these modes is 1e-3).
+//
+// Work split: a row's packed bytes are cut into 16-byte chunks; LPR lanes
+// (a power of two dividing the chunk count) share one row, so every warp-wide
+// load instruction reads whole contiguous 16-byte pieces of 32/LPR consecutive
+// rows.  Activations of a tile of BT streams are staged in shared memory once
+// per CTA; the weight stream is read once per batch tile.
+#include "common.cuh"
+#include "launch.h"
+
+#include <cuda_fp16.h>
+
+namespace {
+
+constexpr int WARPS = 4;
+constexpr int MAX_PRELOAD = 6;
+
+struct GemvP {
+    const unsigned char *w;
+    const float *scales;
+    const float *bias;
+    const int8_t *qx;
+    const float *sx;
+    const float *x;
+    float *out;
+    const int *n_active;
+    long n, k;
+    long out_stride;
+    int batch;
+    int epilogue;
+    int lpr, cpl;       // lanes per row, 16-byte chunks per lane
+    long row_bytes;
+    long w_gs, scale_gs, act_gs, out_gs;  // group strides (elements of the respective arrays)
+};
+
+template <bool STRICT>
+__device__ __forceinline__ void store_out(const GemvP &p, float *out, long row, int b, float v) {
+    float *dst = out + (long)b * p.out_stride + row;
+    if (p.epilogue == MB_EPI_RESIDUAL) *dst = __fadd_rn(*dst, v);
+    else if (p.epilogue == MB_EPI_GELU) *dst = gelu_tanh<STRICT>(v);
+    else *dst = v;
+}
+
+__device__ __forceinline__ uint4 ldg16(const unsigned char *ptr) {
+    return __ldg(reinterpret_cast<const uint4 *>(ptr));
+}
+
+template <int QT, int BT, bool STRICT>
+__global__ void __launch_bounds__(WARPS * 32) k_gemv(GemvP p) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const long grp = blockIdx.y;
+    const unsigned char *w = p.w + grp * p.w_gs;
+    const float *scales = p.scales == nullptr ? nullptr : p.scales + grp * p.scale_gs;
+    float *out = p.out + grp * p.out_gs;
+    const int nb = p.n_active != nullptr ? min(p.batch, *p.n_active) : p.batch;
+    const int LPR = p.lpr, CPL = p.cpl, RPW = 32 / LPR;
+    const int sub = lane / LPR, li = lane % LPR;
+    const long row = ((long)blockIdx.x * WARPS + warp) * RPW + sub;
+    const bool row_ok = row < p.n;
+    const long k = p.k;
+    constexpr bool QUANT = (QT == MB_INT8 || QT == MB_INT4);
+    const long act_bytes = QUANT ? k : k * 4;
+    unsigned char *act = smem;                         // [BT][act_bytes]
+    float *pbuf = reinterpret_cast<float *>(smem + (size_t)BT * act_bytes);  // int4 only
+    const unsigned char *wrow = w + (row_ok ? row : 0) * p.row_bytes;
+
+    for (int b0 = 0; b0 < nb; b0 += BT) {
+        __syncthreads();
+        // ---- stage the activation tile ------------------------------------
+        if (QUANT) {
+            const int8_t *src = p.qx + grp * p.act_gs;
+            if (QT == MB_INT8) {
+                const int per = (int)(k / 16);
+                for (int i = threadIdx.x; i < BT * per; i += blockDim.x) {
+                    const int b = i / per, c = i % per;
+                    uint4 v = make_uint4(0, 0, 0, 0);
+                    if (b0 + b < nb)
+                        v = *reinterpret_cast<const uint4 *>(src + (long)(b0 + b) * k + c * 16);
+                    reinterpret_cast<uint4 *>(act)[(long)b * per + c] = v;
+                }
+            } else {
+                // de-interleave each 8-byte span into (even bytes, odd bytes): a packed
+                // int4 word holds its even-index weights in the low nibbles.
+                const int per = (int)(k / 8);
+                for (int i = threadIdx.x; i < BT * per; i += blockDim.x) {
+                    const int b = i / per, c = i % per;
+                    uint2 v = make_uint2(0, 0);
+                    if (b0 + b < nb)
+                        v = *reinterpret_cast<const uint2 *>(src + (long)(b0 + b) * k + c * 8);
+                    const uint2 o = make_uint2(__byte_perm(v.x, v.y, 0x6420),
+                                               __byte_perm(v.x, v.y, 0x7531));
+                    reinterpret_cast<uint2 *>(act)[(long)b * per + c] = o;
+                }
+            }
+        } else {
+            const float *src = p.x + grp * p.act_gs;
+            const int per = (int)(k / 4);
+            for (int i = threadIdx.x; i < BT * per; i += blockDim.x) {
+                const int b = i / per, c = i % per;
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (b0 + b < nb)
+                    v = *reinterpret_cast<const float4 *>(src + (long)(b0 + b) * k + c * 4);
+                reinterpret_cast<float4 *>(act)[(long)b * per + c] = v;
+            }
+        }
+        __syncthreads();
+
+        // ---- dot products -----------------------------------------------------
+        if (QT == MB_INT8) {
+            int acc[BT];
+#pragma unroll
+            for (int b = 0; b < BT; ++b) acc[b] = 0;
+            if (row_ok) {
+                for (int i0 = 0; i0 < CPL; i0 += MAX_PRELOAD) {
+                    uint4 wv[MAX_PRELOAD];
+#pragma unroll
+                    for (int u = 0; u < MAX_PRELOAD; ++u)
+                        if (i0 + u < CPL) wv[u] = ldg16(wrow + (long)(li + (i0 + u) * LPR) * 16);
+#pragma unroll
+                    for (int u = 0; u < MAX_PRELOAD; ++u) {
+                        if (i0 + u < CPL) {
+                            const int c = li + (i0 + u) * LPR;
+#pragma unroll
+                            for (int b = 0; b < BT; ++b) {
+                                const uint4 xv = reinterpret_cast<const uint4 *>(act + (long)b * k)[c];
+                                int a = acc[b];
+                                a = __dp4a((int)wv[u].x, (int)xv.x, a);
+                                a = __dp4a((int)wv[u].y, (int)xv.y, a);
+                                a = __dp4a((int)wv[u].z, (int)xv.z, a);
+                                a = __dp4a((int)wv[u].w, (int)xv.w, a);
+                                acc[b] = a;
+                            }
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int b = 0; b < BT; ++b)
+                for (int o = LPR >> 1; o > 0; o >>= 1) acc[b] += __shfl_xor_sync(MB_FULL, acc[b], o);
+            if (row_ok && li == 0) {
+                const float ws = scales[row];
+                const float bias = p.bias == nullptr ? 0.0f : p.bias[row];
+#pragma unroll
+                for (int b = 0; b < BT; ++b) {
+                    if (b0 + b < nb) {
+                        float v = __fmul_rn(__fmul_rn((float)acc[b], ws), p.sx[grp * p.batch + b0 + b]);
+                        if (p.bias != nullptr) v = __fadd_rn(v, bias);
+                        store_out<STRICT>(p, out, row, b0 + b, v);
+                    }
+                }
+            }
+        } else if (QT == MB_INT4) {
+            const long groups = k / 32;
+            float *wp = pbuf + (size_t)warp * 32 * CPL * BT;   // [RPW][groups][BT]
+            if (row_ok) {
+                for (int i0 = 0; i0 < CPL; i0 += MAX_PRELOAD) {
+                    uint4 wv[MAX_PRELOAD];
+#pragma unroll
+                    for (int u = 0; u < MAX_PRELOAD; ++u)
+                        if (i0 + u < CPL) wv[u] = ldg16(wrow + (long)(li + (i0 + u) * LPR) * 16);
+#pragma unroll
+                    for (int u = 0; u < MAX_PRELOAD; ++u) {
+                        if (i0 + u < CPL) {
+                            const int g = li + (i0 + u) * LPR;   // chunk index == group index
+                            const float gs = scales[row * groups + g];
+                            const unsigned ww[4] = {wv[u].x, wv[u].y, wv[u].z, wv[u].w};
+                            int lo[4], hi[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                lo[j] = (int)__vsub4(ww[j] & 0x0f0f0f0fu, 0x08080808u);
+                                hi[j] = (int)__vsub4((ww[j] >> 4) & 0x0f0f0f0fu, 0x08080808u);
+                            }
+#pragma unroll
+                            for (int b = 0; b < BT; ++b) {
+                                const uint4 *xp = reinterpret_cast<const uint4 *>(act + (long)b * k) + 2 * g;
+                                const uint4 x0 = xp[0], x1 = xp[1];
+                                int gi = 0;
+                                gi = __dp4a(lo[0], (int)x0.x, gi);
+                                gi = __dp4a(hi[0], (int)x0.y, gi);
+                                gi = __dp4a(lo[1], (int)x0.z, gi);
+                                gi = __dp4a(hi[1], (int)x0.w, gi);
+                                gi = __dp4a(lo[2], (int)x1.x, gi);
+                                gi = __dp4a(hi[2], (int)x1.y, gi);
+                                gi = __dp4a(lo[3], (int)x1.z, gi);
+                                gi = __dp4a(hi[3], (int)x1.w, gi);
+                                wp[((long)sub * groups + g) * BT + b] = __fmul_rn((float)gi, gs);
+                            }
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            // ordered accumulation over groups, one (row, stream) pair per lane
+            for (int j = lane; j < RPW * BT; j += 32) {
+                const int r = j / BT, b = j % BT;
+                const long orow = ((long)blockIdx.x * WARPS + warp) * RPW + r;
+                if (orow < p.n && b0 + b < nb) {
+                    float a = 0.0f;
+                    for (long g = 0; g < groups; ++g) a = __fadd_rn(a, wp[((long)r * groups + g) * BT + b]);
+                    float v = __fmul_rn(a, p.sx[grp * p.batch + b0 + b]);
+                    if (p.bias != nullptr) v = __fadd_rn(v, p.bias[orow]);
+                    store_out<STRICT>(p, out, orow, b0 + b, v);
+                }
+            }
+            __syncwarp();
+        } else {
+            float acc[BT];
+#pragma unroll
+            for (int b = 0; b < BT; ++b) acc[b] = 0.0f;
+            if (row_ok) {
+                for (int i0 = 0; i0 < CPL; i0 += MAX_PRELOAD) {
+                    uint4 wv[MAX_PRELOAD];
+#pragma unroll
+                    for (int u = 0; u < MAX_PRELOAD; ++u)
+                        if (i0 + u < CPL) wv[u] = ldg16(wrow + (long)(li + (i0 + u) * LPR) * 16);
+#pragma unroll
+                    for (int u = 0; u < MAX_PRELOAD; ++u) {
+                        if (i0 + u < CPL) {
+                            const int c = li + (i0 + u) * LPR;
+                            if (QT == MB_F16) {
+                                const __half2 *h = reinterpret_cast<const __half2 *>(&wv[u]);
+                                const float2 w0 = __half22float2(h[0]), w1 = __half22float2(h[1]);
+                                const float2 w2 = __half22float2(h[2]), w3 = __half22float2(h[3]);
+#pragma unroll
+                                for (int b = 0; b < BT; ++b) {
+                                    const float4 *xp = reinterpret_cast<const float4 *>(act + (long)b * k * 4) + 2 * c;
+                                    const float4 xa = xp[0], xb = xp[1];
+                                    float a = acc[b];
+                                    a = fmaf(w0.x, xa.x, a); a = fmaf(w0.y, xa.y, a);
+                                    a = fmaf(w1.x, xa.z, a); a = fmaf(w1.y, xa.w, a);
+                                    a = fmaf(w2.x, xb.x, a); a = fmaf(w2.y, xb.y, a);
+                                    a = fmaf(w3.x, xb.z, a); a = fmaf(w3.y, xb.w, a);
+                                    acc[b] = a;
+                                }
+                            } else {
+                                const float4 wf = *reinterpret_cast<const float4 *>(&wv[u]);
+#pragma unroll
+                                for (int b = 0; b < BT; ++b) {
+                                    const float4 xa = reinterpret_cast<const float4 *>(act + (long)b * k * 4)[c];
+                                    float a = acc[b];
+                                    a = fmaf(wf.x, xa.x, a); a = fmaf(wf.y, xa.y, a);
+                                    a = fmaf(wf.z, xa.z, a); a = fmaf(wf.w, xa.w, a);
+                                    acc[b] = a;
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int b = 0; b < BT; ++b)
+                for (int o = LPR >> 1; o > 0; o >>= 1) acc[b] += __shfl_xor_sync(MB_FULL, acc[b], o);
+            if (row_ok && li == 0) {
+#pragma unroll
+                for (int b = 0; b < BT; ++b) {
+                    if (b0 + b < nb) {
+                        float v = acc[b];
+                        if (p.bias != nullptr) v = __fadd_rn(v, p.bias[row]);
+                        store_out<STRICT>(p, out, row, b0 + b, v);
+                    }
+                }
+            }
+        }
+    }
+}
+
+// Shapes whose packed rows are not a whole number of 16-byte chunks: one thread
+// per (row, stream), sequential over k.  Cold path (tiny self-test shapes).
+template <int QT, bool STRICT>
+__global__ void k_gemv_generic(GemvP p) {
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    const int nb = p.n_active != nullptr ? min(p.batch, *p.n_active) : p.batch;
+    const long row = idx % p.n;
+    const int b = (int)(idx / p.n);
+    if (b >= nb) return;
+    const long k = p.k;
+    float v;
+    if (QT == MB_INT8) {
+        const int8_t *w = reinterpret_cast<const int8_t *>(p.w) + row * k;
+        const int8_t *q = p.qx + (long)b * k;
+        int s = 0;
+        for (long j = 0; j < k; ++j) s += (int)w[j] * (int)q[j];
+        v = __fmul_rn(__fmul_rn((float)s, p.scales[row]), p.sx[b]);
+    } else if (QT == MB_INT4) {
+        const unsigned char *w = p.w + row * (k / 2);
+        const int8_t *q = p.qx + (long)b * k;
+        float a = 0.0f;
+        for (long g = 0; g < k / 32; ++g) {
+            int gi = 0;
+            for (int j = 0; j < 32; j += 2) {
+                const unsigned char byte = w[g * 16 + j / 2];
+                gi += ((int)(byte & 0x0f) - 8) * (int)q[g * 32 + j] +
+                      ((int)(byte >> 4) - 8) * (int)q[g * 32 + j + 1];
+            }
+            a = __fadd_rn(a, __fmul_rn((float)gi, p.scales[row * (k / 32) + g]));
+        }
+        v = __fmul_rn(a, p.sx[b]);
+    } else if (QT == MB_F16) {
+        const __half *w = reinterpret_cast<const __half *>(p.w) + row * k;
+        const float *x = p.x + (long)b * k;
+        float a = 0.0f;
+        for (long j = 0; j < k; ++j) a = fmaf(__half2float(w[j]), x[j], a);
+        v = a;
+    } else {
+        const float *w = reinterpret_cast<const float *>(p.w) + row * k;
+        const float *x = p.x + (long)b * k;
+        float a = 0.0f;
+        for (long j = 0; j < k; ++j) a = __fadd_rn(a, __fmul_rn(w[j], x[j]));
+        v = a;
+    }
+    if (p.bias != nullptr) v = __fadd_rn(v, p.bias[row]);
+    store_out<STRICT>(p, p.out, row, b, v);
+}
+
+template <int QT, int BT, bool STRICT>
+int launch_tiled(const GemvP &p, size_t groups, cudaStream_t s) {
+    const int rpw = 32 / p.lpr;
+    const long iters = (p.n + rpw - 1) / rpw;
+    const unsigned blocks = (unsigned)((iters + WARPS - 1) / WARPS);
+    const bool quant = (QT == MB_INT8 || QT == MB_INT4);
+    size_t smem = (size_t)BT * (quant ? p.k : p.k * 4);
+    if (QT == MB_INT4) smem += (size_t)WARPS * 32 * p.cpl * BT * sizeof(float);
+    if (smem > 160u * 1024u) return (int)cudaErrorInvalidValue;
+    k_gemv<QT, BT, STRICT><<<dim3(blocks, (unsigned)groups), WARPS * 32, smem, s>>>(p);
+    return mb_check_launch();
+}
+
+template <int QT, bool STRICT>
+int launch_qt(const GemvP &p, size_t groups, bool tiled, cudaStream_t s) {
+    if (!tiled) {
+        if (groups != 1) return (int)cudaErrorInvalidValue;
+        const long total = p.n * p.batch;
+        k_gemv_generic<QT, STRICT><<<(unsigned)((total + 127) / 128), 128, 0, s>>>(p);
+        return mb_check_launch();
+    }
+    const bool quant = (QT == MB_INT8 || QT == MB_INT4);
+    const size_t act_row = quant ? (size_t)p.k : (size_t)p.k * 4;
+    // widest batch tile whose activations fit comfortably in shared memory
+    if (p.batch >= 8 && 8 * act_row <= 64u * 1024u) return launch_tiled<QT, 8, STRICT>(p, groups, s);
+    if (p.batch >= 4 && 4 * act_row <= 64u * 1024u) return launch_tiled<QT, 4, STRICT>(p, groups, s);
+    if (p.batch >= 2 && 2 * act_row <= 64u * 1024u) return launch_tiled<QT, 2, STRICT>(p, groups, s);
+    return launch_tiled<QT, 1, STRICT>(p, groups, s);
+}
+
+template <int QT>
+int set_attrs() {
+    int rc = 0;
+#define MB_ATTR(BT, ST)                                                                         \
+    if (rc == 0)                                                                                \
+        rc = (int)cudaFuncSetAttribute(k_gemv<QT, BT, ST>,                                      \
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024)
+    MB_ATTR(1, false); MB_ATTR(2, false); MB_ATTR(4, false); MB_ATTR(8, false);
+    MB_ATTR(1, true); MB_ATTR(2, true); MB_ATTR(4, true); MB_ATTR(8, true);
+#undef MB_ATTR
+    return rc;
+}
+
+}  // namespace
+
+// Opt every instantiation into large dynamic shared memory on the current
+// device.  Called once per device at backend open, outside any stream capture.
+extern "C" int mb_gemv_init(void) {
+    int rc = set_attrs<MB_INT8>();
+    if (rc == 0) rc = set_attrs<MB_INT4>();
+    if (rc == 0) rc = set_attrs<MB_F16>();
+    if (rc == 0) rc = set_attrs<MB_F32>();
+    return rc;
+}
+
+extern "C" int mb_gemv(const mb_gemv_args *a, mb_stream stream) {
+    if (a == nullptr || a->n == 0 || a->k == 0 || a->batch == 0 || a->w == nullptr ||
+        a->out == nullptr)
+        return (int)cudaErrorInvalidValue;
+    const bool quant = a->qtype == MB_INT8 || a->qtype == MB_INT4;
+    if (quant && (a->qx == nullptr || a->sx == nullptr || a->scales == nullptr))
+        return (int)cudaErrorInvalidValue;
+    if (!quant && a->x == nullptr) return (int)cudaErrorInvalidValue;
+    if (a->qtype == MB_INT4 && (a->k % 32u) != 0) return (int)cudaErrorInvalidValue;
+    GemvP p;
+    p.w = static_cast<const unsigned char *>(a->w);
+    p.scales = a->scales;
+    p.bias = a->bias;
+    p.qx = a->qx;
+    p.sx = a->sx;
+    p.x = a->x;
+    p.out = a->out;
+    p.n_active = a->n_active;
+    p.n = (long)a->n;
+    p.k = (long)a->k;
+    p.out_stride = (long)a->out_stride;
+    p.batch = (int)a->batch;
+    p.epilogue = a->epilogue;
+    switch (a->qtype) {
+        case MB_INT8: p.row_bytes = (long)a->k; break;
+        case MB_INT4: p.row_bytes = (long)a->k / 2; break;
+        case MB_F16: p.row_bytes = (long)a->k * 2; break;
+        default: p.row_bytes = (long)a->k * 4; break;
+    }
+    const size_t groups = a->groups > 1 ? a->groups : 1;
+    p.w_gs = (long)a->w_group_stride;
+    p.scale_gs = (long)a->scale_group_stride;
+    p.act_gs = (long)a->act_group_stride;
+    p.out_gs = (long)a->out_group_stride;
+    // activations are staged in 16-byte pieces: k must allow it, and the packed
+    // row must be whole 16-byte chunks, else the scalar kernel takes the shape.
+    const bool act_ok = quant ? (a->k % 16u) == 0 : (a->k % 4u) == 0;
+    const bool tiled = act_ok && (p.row_bytes % 16) == 0;
+    if (tiled) {
+        const long cpr = p.row_bytes / 16;
+        int lpr = 32;
+        while (cpr % lpr != 0) lpr >>= 1;
+        p.lpr = lpr;
+        p.cpl = (int)(cpr / lpr);
+    } else {
+        p.lpr = 1;
+        p.cpl = 0;
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    const bool strict = a->strict != 0;
+#define MB_DISPATCH(QT)                                                         \
+    return strict ? launch_qt<QT, true>(p, groups, tiled, s)                    \
+                  : launch_qt<QT, false>(p, groups, tiled, s)
+    switch (a->qtype) {
+        case MB_INT8: MB_DISPATCH(MB_INT8);
+        case MB_INT4: MB_DISPATCH(MB_INT4);
+        case MB_F16: MB_DISPATCH(MB_F16);
+        case MB_F32: MB_DISPATCH(MB_F32);
+        default: return (int)cudaErrorInvalidValue;
+    }
+#undef MB_DISPATCH
+}

@@ -1,0 +1,138 @@
+/* Internal C ABI between the C11 host code (backend_b200.c, decoder_b200.c)
+ * and the CUDA translation units.  Every function enqueues work on `stream`
+ * and returns a cudaError_t value as int (0 = success); none synchronizes.
+ * All pointers are device pointers unless the name says host.
+ */
+#ifndef MYNAH_B200_LAUNCH_H
+#define MYNAH_B200_LAUNCH_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void *mb_stream; /* cudaStream_t */
+
+/* Weight formats.  Values match the reference's enum (src/qmat.c:36). */
+enum { MB_F32 = 0, MB_INT8 = 1, MB_INT4 = 2, MB_F16 = 3 };
+
+/* GEMV epilogues. */
+enum { MB_EPI_STORE = 0, MB_EPI_RESIDUAL = 1, MB_EPI_GELU = 2 };
+
+/* Per-device one-time kernel attribute setup (call with the device current,
+ * outside stream capture). */
+int mb_gemv_init(void);
+int mb_attention_init(void);
+
+/* ---- weight packing (once per tensor) ---------------------------------- */
+int mb_pack_int8(const float *w, size_t n, size_t k, int8_t *q, float *scales, mb_stream stream);
+int mb_pack_int4(const float *w, size_t n, size_t k, uint8_t *q, float *scales, mb_stream stream);
+int mb_pack_f16(const float *w, size_t count, uint16_t *h, mb_stream stream);
+
+/* ---- glue --------------------------------------------------------------- */
+/* LayerNorm over `rows` rows of `width`; bias may be NULL.  When qx != NULL
+ * the normalized row is also quantized per row (int8, scale to sx[row]); out
+ * may then be NULL.  n_active (device int, may be NULL) masks rows >= *n_active.
+ * strict = reference summation order. */
+int mb_layernorm(const float *in, float *out, const float *gain, const float *bias,
+                 size_t rows, size_t width, float eps, int8_t *qx, float *sx,
+                 const int *n_active, int strict, mb_stream stream);
+/* Per-row int8 activation quantization of f32 rows. */
+int mb_quant_rows(const float *in, size_t rows, size_t width, int8_t *qx, float *sx,
+                  const int *n_active, mb_stream stream);
+int mb_gelu(float *data, size_t n, int strict, mb_stream stream);
+int mb_residual_add(float *out, const float *in, size_t n, mb_stream stream);
+int mb_scale(float *data, size_t n, float scale, mb_stream stream);
+int mb_clip(float *data, size_t n, mb_stream stream);
+int mb_bias_add(float *out, const float *bias, size_t rows, size_t cols, mb_stream stream);
+/* Constrained first-on-ties argmax over `rows` logit rows of `vocab`; writes
+ * tokens[row]; when codes != NULL also the stored code (non-codes collapse to
+ * 0) and ORs eos_flag[row / tables_per_stream]. */
+int mb_argmax_rows(const float *logits, size_t rows, size_t vocab, size_t codebook_size,
+                   size_t eos_id, const int *allow_eos, int allow_eos_scalar,
+                   unsigned *tokens, unsigned *codes, int *eos_flag, size_t tables_per_stream,
+                   const int *n_active, mb_stream stream);
+/* x[b] = mean_t(table_t[codes[b][t]]) + position[lens[b]] ; tables is a device
+ * array of table base pointers. */
+int mb_embed_frames(const float *const *tables, size_t n_tables, size_t vocab, size_t width,
+                    const unsigned *codes, const float *position, const int *lens,
+                    float *x, size_t batch, const int *n_active, int *status, mb_stream stream);
+/* x[b] = rows[b] + position[lens[b]] */
+int mb_add_position(const float *rows, const float *position, const int *lens, float *x,
+                    size_t batch, size_t width, const int *n_active, mb_stream stream);
+/* lens[b] += 1 for b < n_active */
+int mb_advance_lens(int *lens, size_t batch, const int *n_active, mb_stream stream);
+/* End of one greedy frame for lanes below n_active: lens[b] += 1; append
+ * tokens_cur[b][:] to history[*frame_idx][b][:] (rows of lane_stride lanes); record the first frame whose
+ * eos_flag[b] is set in eos_frame[b] (-1 = none yet); then (one thread)
+ * *frame_idx += 1 and, when min_frames (device int) is given,
+ * allow_eos[:] = (*frame_idx >= *min_frames). */
+int mb_frame_advance(int *lens, const unsigned *tokens_cur, unsigned *history, int *frame_idx,
+                     const int *eos_flag, int *eos_frame, int *allow_eos, size_t batch,
+                     size_t lane_stride, size_t tables, const int *min_frames, size_t history_frames,
+                     const int *n_active, mb_stream stream);
+
+/* ---- quantized matrix-vector products ---------------------------------- */
+typedef struct {
+    int qtype;            /* MB_* */
+    const void *w;        /* packed weights [n][k] in the reference's layout */
+    const float *scales;  /* int8: [n]; int4: [n][k/32]; else NULL */
+    const float *bias;    /* [n] or NULL */
+    size_t n, k;
+    const int8_t *qx;     /* int8/int4: [batch][k] quantized activations */
+    const float *sx;      /* int8/int4: [batch] activation scales */
+    const float *x;       /* f32/f16: [batch][k] activations */
+    float *out;           /* [batch][out_stride] */
+    size_t out_stride;
+    size_t batch;
+    const int *n_active;  /* device int or NULL */
+    int epilogue;         /* MB_EPI_* */
+    int strict;           /* GELU epilogue: reference-order transcendental */
+    size_t groups;        /* >1: independent problems; pointers advance by the strides below */
+    size_t w_group_stride, scale_group_stride, act_group_stride, out_group_stride;
+} mb_gemv_args;
+int mb_gemv(const mb_gemv_args *args, mb_stream stream);
+
+/* Plain f32 row-major sgemm for the non-hot seam entries (prefill, codec):
+ * C = alpha*op(A)*op(B) + beta*C. */
+int mb_sgemm(int trans_a, int trans_b, size_t m, size_t n, size_t k, float alpha,
+             const float *a, size_t lda, const float *b, size_t ldb, float beta, float *c,
+             size_t ldc, mb_stream stream);
+
+/* ---- attention ----------------------------------------------------------- */
+typedef struct {
+    const float *q;       /* [batch][q_stride], head h at h*head_width */
+    size_t q_stride;
+    const float *k_new;   /* self: new K rows [batch][q_stride] (appended at position); cross: NULL */
+    const float *v_new;
+    float *k_cache;       /* slot 0 base for this layer: [capacity][cache_stride] */
+    float *v_cache;
+    size_t slot_stride;   /* floats between consecutive slots' caches */
+    const int *slots;     /* [batch] slot of each lane, NULL = identity */
+    const int *lens;      /* [batch] position of each lane (valid = len+1); NULL = scalars below */
+    size_t position, valid;
+    size_t cache_stride, heads, head_width;
+    float scale;
+    float *out;           /* [batch][out_stride] */
+    size_t out_stride;
+    int8_t *qx;           /* optional fused per-row quantization of out */
+    float *sx;
+    size_t batch;
+    const int *n_active;
+    int strict;
+    /* scratch for the split-position path (fast mode): partial results and
+     * one arrival counter per lane.  splits == 1 needs none. */
+    size_t splits;
+    float *partials;      /* [batch][heads][splits][head_width + 2] */
+    unsigned *counters;   /* [batch], zero before first use, left zero */
+    int *status;          /* device error word (nonzero = bad argument seen) */
+} mb_attn_args;
+int mb_attention(const mb_attn_args *args, mb_stream stream);
+size_t mb_attention_partials_floats(size_t batch, size_t heads, size_t splits, size_t head_width);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
