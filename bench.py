@@ -1,0 +1,430 @@
+"""Benchmark of the B200 decode path (and, with --impl reference, of the
+reference's own CPU implementation of the same path).
+
+Workload (the data-parallel serving configuration): int8 per-row weights,
+`--streams` concurrent greedy streams per GPU, `--frames` frames each from an
+empty KV cache, on a random-init Magpie-357M-shaped decoder (12 layers, d 768,
+12 heads x 64, cross width 128 over 128 text states, FFN 3072, 8 embedding
+tables and 8 logit heads over a 2048-entry vocabulary).  One "step" is one such
+job: streams x frames frames.  Streams are independent, so with N GPUs every
+rank runs its own streams on a full weight copy (weak scaling, no collective on
+the data path; NCCL is used only for the barrier and the max over ranks).
+
+    python bench.py --gpus 1 --steps 3 --warmup 3
+    python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...
+    python bench.py --impl reference
+
+Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from mynah_tts_b200 import synth  # noqa: E402
+
+FRAME_RATE = 21.533          # audio frames per second of the real model (stacked frames)
+SEED = 21
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f)["hbm_gbs"], "measured"
+    return 6650.0, "fallback"
+
+
+def partition_streams(total_streams: int, world: int, rank: int) -> list[int]:
+    """Stream i runs on rank i mod world (the reference has no scheduler across
+    devices; requests are independent, src/mynah_tts.h:79-91)."""
+    return [i for i in range(total_streams) if i % world == rank]
+
+
+def reduce_max(value: float, world: int, device: str = "cuda") -> float:
+    """Max of a per-rank scalar over all ranks (the only cross-rank exchange of
+    the benchmark; the data path has none)."""
+    if world <= 1:
+        return float(value)
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor([value], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def synthetic_cross_kv(shape, stream: int):
+    """Cross K/V of one request, [layers][memory_length][xattn_width] each: the
+    distribution LayerNorm(memory) @ kv_net^T has for N(0,1) memory and
+    N(0,0.02) weights (std 0.02*sqrt(width))."""
+    rng = np.random.default_rng([SEED, 0x6B76, stream])
+    std = 0.02 * np.sqrt(shape.width)
+    dims = (shape.layers, shape.memory_length, shape.xattn_width)
+    return (rng.normal(0, std, dims).astype(np.float32), rng.normal(0, std, dims).astype(np.float32))
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device: int):
+        self.device = device
+        self.lines: list[str] = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "200", "-i", str(self.device)], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None,
+                "sm_max_mhz": float(max(mx)) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------- reference arm
+def cpu_reference_job(shape, model, streams: int, frames: int, threads: int | None):
+    """`streams` greedy streams x `frames` frames through the reference's own CPU
+    code (oracle/_ref, its default x86 flags) in groups of at most 16 (its batch
+    cap, src/graph.c:12); falls back to the C restatement where the compiled
+    reference is absent.  Returns (frames/s, seconds, kind, cores)."""
+    from oracle import oracle as O
+    cores = threads or os.cpu_count() or 1
+    memory = synth.make_memory(shape, seed=SEED + 100)
+    start = synth.make_codes(shape, seed=SEED + 200, frames=1)
+    if O.have_ref("fast"):
+        rm = O.RefModel(model, O.INT8, "fast", threads=cores)
+        groups = [min(16, streams - g) for g in range(0, streams, 16)]
+        decs = [[rm.new_decoder(memory, frames + 2) for _ in range(n)] for n in groups]
+        rm.greedy_decode(decs[0][:1], start, 1, 10 ** 6)          # packs the weights (first use)
+        for d in decs[0][:1]:
+            d.length = 0
+        t0 = time.perf_counter()
+        for group in decs:
+            rm.greedy_decode(group, np.repeat(start, len(group), axis=0), frames, 10 ** 6)
+        dt = time.perf_counter() - t0
+        for group in decs:
+            for d in group:
+                d.close()
+        rm.close()
+        return streams * frames / dt, dt, "reference", cores
+    pm = O.PortModel(model, O.INT8)
+    ps = [pm.new_stream(memory, frames + 2) for _ in range(streams)]
+    t0 = time.perf_counter()
+    for s in ps:
+        s.greedy_decode(start[0], frames, 10 ** 6)
+    dt = time.perf_counter() - t0
+    for s in ps:
+        s.close()
+    pm.close()
+    return streams * frames / dt, dt, "port", 1
+
+
+def run_reference(args, rank: int):
+    if rank != 0:
+        return
+    shape = synth.MAGPIE_357M
+    model = synth.make_model(shape, seed=SEED)
+    streams, frames = min(args.streams, 16), args.ref_frames
+    times = []
+    value = kind = cores = None
+    for step in range(args.warmup + args.steps):
+        value, dt, kind, cores = cpu_reference_job(shape, model, streams, frames, None)
+        if step >= args.warmup:
+            times.append(dt)
+    ms = 1000.0 * float(np.mean(times))
+    value = streams * frames / (ms / 1000.0)
+    sample = (f"{streams} streams stepped together x {frames} frames from empty KV per step "
+              f"(the reference's batch cap is 16)")
+    print(json.dumps({
+        "impl": "reference", "metric": "frames_per_s", "value": value, "unit": "frames/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
+        "data": "synthetic",
+        "config": workload_config(args, shape),
+        "cpu_baseline": {"value": value, "unit": "frames/s", "cores": cores, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": "frames/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def workload_config(args, shape):
+    return {"workload": (f"C5 data-parallel serving: {args.quant} weights, {args.streams} concurrent greedy "
+                         f"streams per GPU x {args.frames} frames from empty KV, Magpie-357M-shaped decoder "
+                         f"(12L d768 12x64 heads, xw128 over 128 text states, ffn3072, 8 tables/heads x 2048)"),
+            "streams_per_gpu": args.streams, "frames": args.frames, "quant": args.quant,
+            "l2": "working set (weights + f32 KV of all streams) exceeds the 126 MB L2",
+            "parallelism": f"dp{args.gpus} replicas, no collective"}
+
+
+# ------------------------------------------------------------------- own arm
+def algorithmic_bytes(shape, name: str, batch: int, mean_len: float, qbytes: dict) -> float:
+    """Bytes one launch of a call site must move, each counted once."""
+    W, F, XW, T = shape.width, shape.ffn_width, shape.xattn_width, shape.memory_length
+    act = 1 if qbytes["quantized"] else 4
+
+    def product(n, k, wname, out_f32=True):
+        return qbytes[wname] + batch * (k * act + 4 + n * 4 * (2 if wname in ("o_self", "o_cross", "ffn_down") else 1))
+    if name == "self attention":
+        return batch * (2 * (mean_len + 1) * W * 4 + 2 * W * 4 + 3 * W * 4 + W * (4 + act))
+    if name == "cross attention":
+        return batch * (2 * T * XW * 4 + XW * 4 + XW * (4 + act))
+    table = {"qkv product": (3 * W, W, "qkv"), "o_self product": (W, W, "o_self"),
+             "q_cross product": (XW, W, "q_cross"), "o_cross product": (W, XW, "o_cross"),
+             "ffn_up product(+gelu)": (F, W, "ffn_up"), "ffn_down product": (W, F, "ffn_down"),
+             "heads product": (shape.tables * shape.vocab, W, "heads")}
+    if name in table:
+        n, k, wname = table[name]
+        return product(n, k, wname)
+    if name == "layernorm(+quant)":
+        return batch * W * (4 + 4 + act) + W * 4
+    if name == "hidden quant":
+        return batch * F * (4 + 1)
+    return 0.0
+
+
+def weight_bytes_table(shape, quant: str) -> dict:
+    W, F, XW = shape.width, shape.ffn_width, shape.xattn_width
+
+    def wb(n, k):
+        if quant == "int8":
+            return n * k + n * 4
+        if quant == "int4":
+            return n * k // 2 + n * (k // 32) * 4
+        return n * k * (2 if quant == "f16" else 4)
+    return {"qkv": wb(3 * W, W), "o_self": wb(W, W), "q_cross": wb(XW, W), "o_cross": wb(W, XW),
+            "ffn_up": wb(F, W), "ffn_down": wb(W, F), "heads": wb(shape.tables * shape.vocab, W) + shape.tables * shape.vocab * 4,
+            "quantized": quant in ("int8", "int4")}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--streams", type=int, default=64, help="concurrent streams per GPU")
+    ap.add_argument("--total-streams", type=int, default=0,
+                    help="strong scaling: this many streams in all, dealt round-robin to the ranks")
+    ap.add_argument("--frames", type=int, default=512)
+    ap.add_argument("--quant", default="int8", choices=["int8", "int4", "f16", "f32"])
+    ap.add_argument("--ref-frames", type=int, default=24, help="frames per step of the CPU reference arm")
+    ap.add_argument("--cpu-frames", type=int, default=24, help="frames of the CPU baseline sample")
+    ap.add_argument("--no-extras", action="store_true", help="skip batch-1 and matrix-pool measurements")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from mynah_tts_b200.backend import Backend, Decoder, MatrixPool
+
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    shape = synth.MAGPIE_357M
+    model = synth.make_model(shape, seed=SEED)
+    frames = args.frames
+    if args.total_streams:
+        # strong scaling: a fixed set of streams dealt round-robin to the ranks
+        my_streams = partition_streams(args.total_streams, world, rank)
+        scaling, total_streams = "strong", args.total_streams
+    else:
+        my_streams = [rank * args.streams + i for i in range(args.streams)]
+        scaling, total_streams = "weak", world * args.streams
+    B = len(my_streams)
+    backend = Backend(args.quant, strict=False, device=local_rank)
+    dec = Decoder(backend, model, capacity=frames + 8, slots=B, max_batch=B)
+    for slot, gid in enumerate(my_streams):
+        ck, cv = synthetic_cross_kv(shape, gid)
+        dec.slot_load(slot, ck, cv)
+    slots = list(range(B))
+    start_codes = np.stack([synth.make_codes(shape, seed=SEED + 200 + gid, frames=1)[0] for gid in my_streams])
+
+    def reset():
+        for s in slots:
+            dec.slot_set_length(s, 0)
+
+    # ---- device-resident arm: `value` -------------------------------------------
+    for _ in range(args.warmup):
+        reset()
+        dec.greedy(slots, start_codes, frames, min_frames=10 ** 6)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = backend.launch_count
+    total_ms = 0.0
+    tokens = None
+    for _ in range(args.steps):
+        reset()
+        tokens, _, ms, _ = dec.greedy(slots, start_codes, frames, min_frames=10 ** 6)
+        total_ms += ms                       # CUDA events on the launching stream, inside the library
+    barrier()
+    gpu_launches = backend.launch_count - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    ms_per_step = reduce_max(total_ms, world) / args.steps
+    value = total_streams * frames / (ms_per_step / 1000.0)
+
+    # ---- host-buffer arm: `e2e` (one C-ABI call per frame, host codes in, host tokens out)
+    pinned_codes = torch.empty((B, shape.tables), dtype=torch.int32).pin_memory().numpy().view(np.uint32)
+    pinned_tokens = torch.empty((B, shape.tables), dtype=torch.int32).pin_memory().numpy().view(np.uint32)
+    allow = [0] * B
+
+    def e2e_job():
+        reset()
+        pinned_codes[:] = start_codes
+        for _ in range(frames):
+            dec.frame_batch(slots, pinned_codes, allow, tokens=pinned_tokens)
+            pinned_codes[:] = pinned_tokens       # EOS is not allowed here, so every pick is a code
+        return pinned_tokens
+    for _ in range(min(args.warmup, 1) or 1):
+        e2e_job()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_job()
+    barrier()
+    e2e_s = reduce_max(time.perf_counter() - t0, world)
+    e2e_value = total_streams * frames * args.steps / e2e_s
+    h2d = frames * (B * shape.tables * 4 + 3 * B * 4 + 4)
+    d2h = frames * (B * shape.tables * 4)
+
+    result = None
+    if rank == 0:
+        # ---- per-call-site device times over one more job -> roofline of the dominant kernel
+        peak, peak_kind = load_peaks()
+        reset()
+        dec.profile(True)
+        dec.greedy(slots, start_codes, frames, min_frames=10 ** 6)
+        prof = dec.profile_read()
+        dec.profile(False)
+        total = sum(v[1] for v in prof.values()) or 1.0
+        name, (n_launch, t_ms) = max(prof.items(), key=lambda kv: kv[1][1])
+        qbytes = weight_bytes_table(shape, args.quant)
+        bytes_per_launch = algorithmic_bytes(shape, name, B, (frames - 1) / 2.0, qbytes)
+        avg_s = t_ms / 1000.0 / max(n_launch, 1)
+        achieved = bytes_per_launch / avg_s / 1e9
+        roofline = {"bound": "hbm", "kernel": name, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                    "frac": achieved / peak, "of": peak_kind, "traffic": None,
+                    "bytes_per_launch": bytes_per_launch, "avg_launch_us": avg_s * 1e6,
+                    "share_of_step": t_ms / total,
+                    "timing": "CUDA events around each launch, eager replay of one job"}
+        shares = {k: {"launches": v[0], "ms": round(v[1], 3), "share": round(v[1] / total, 4)}
+                  for k, v in prof.items() if v[0]}
+        extras = {}
+        if not args.no_extras:
+            # batch-1 decode (weights stay L2-resident between steps: labelled so)
+            reset()
+            dec.greedy([0], start_codes[:1], frames, min_frames=10 ** 6)
+            dec.slot_set_length(0, 0)
+            _, _, ms1, _ = dec.greedy([0], start_codes[:1], frames, min_frames=10 ** 6)
+            step_us = ms1 * 1000.0 / frames
+            extras["batch1"] = {"frames_per_s": frames / (ms1 / 1000.0), "us_per_frame": step_us,
+                                "rtf": (ms1 / 1000.0 / frames) * FRAME_RATE, "note": "weights L2-resident"}
+            # the single [3072,768] op streamed over 512 distinct matrices (1.2 GB > L2) per pass
+            x, w, gain, bias = synth.make_linear_case(seed=1)
+            groups = 512
+            pool = MatrixPool(backend, w, groups, bias=bias, gain=gain)
+            xs = np.repeat(x, groups, axis=0)
+            dx = backend.to_device(xs)
+            dy = backend.dev_alloc(groups * w.shape[0])
+            for _ in range(3):
+                pool.linear(dx, dy)
+            backend.timer_start()
+            passes = 10
+            for _ in range(passes):
+                pool.linear(dx, dy)
+            pool_ms = backend.timer_stop() / passes
+            gbs = pool.bytes_per_pass / (pool_ms / 1000.0) / 1e9
+            extras["gemv_pool"] = {"matrix": "[3072,768] " + args.quant, "matrices_per_pass": groups,
+                                   "bytes_per_pass": pool.bytes_per_pass, "ms_per_pass": pool_ms,
+                                   "gbs": gbs, "frac_of_measured_hbm": gbs / peak,
+                                   "frac_of_8tbs": gbs / 8000.0,
+                                   "note": "LayerNorm+quant launch plus product launch per pass; cold (pool > L2)"}
+            pool.close(); dx.free(); dy.free()
+        cpu = None
+        if world == 1:
+            v, dt, kind, cores = cpu_reference_job(shape, model, min(B, 16), args.cpu_frames, None)
+            cpu = {"value": v, "unit": "frames/s", "cores": cores, "kind": kind,
+                   "sample": f"{min(B, 16)} streams stepped together x {args.cpu_frames} frames from empty KV "
+                             f"({dt:.1f} s; the reference's batch cap is 16)"}
+        result = {
+            "metric": "frames_per_s", "value": value, "unit": "frames/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
+            "dtype": "int8 weights x int8 activations, int32 accumulate, f32 glue" if args.quant == "int8" else args.quant,
+            "data": "synthetic", "config": workload_config(args, shape),
+            "rtf_per_stream": (ms_per_step / 1000.0 / frames) * FRAME_RATE,
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": "frames/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "call": "mynah_b200_decoder_frame_batch per frame, pinned host codes in / tokens out"},
+            "gpu_launches": int(gpu_launches),
+            "roofline": roofline, "call_sites": shares, "cpu_baseline": cpu,
+            "tokens_checksum": int(np.asarray(tokens, np.uint64).sum()),
+        }
+        result.update(extras)
+    dec.close()
+    backend.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(result))
+
+
+if __name__ == "__main__":
+    main()

@@ -149,6 +149,10 @@ void mynah_b200_close(void *state);
 int mynah_b200_set_stream(void *state, void *cuda_stream, char *error, size_t cap);
 int mynah_b200_quant(const void *state);
 int mynah_b200_strict(const void *state);
+/* Device-time stopwatch: two CUDA events recorded on the backend's stream;
+ * _stop waits for the second and returns the time between them. */
+int mynah_b200_timer_start(void *state, char *error, size_t cap);
+int mynah_b200_timer_stop(void *state, float *elapsed_ms, char *error, size_t cap);
 /* Number of kernels this library has launched on `state` (graph replays count
  * their kernel nodes). */
 unsigned long long mynah_b200_launch_count(const void *state);

@@ -64,6 +64,14 @@ class Backend:
     def set_stream(self, cuda_stream: int):
         call(self.lib.mynah_b200_set_stream, self.state, C.c_void_p(cuda_stream))
 
+    def timer_start(self):
+        call(self.lib.mynah_b200_timer_start, self.state)
+
+    def timer_stop(self) -> float:
+        ms = C.c_float(0.0)
+        call(self.lib.mynah_b200_timer_stop, self.state, C.byref(ms))
+        return float(ms.value)
+
     @property
     def launch_count(self) -> int:
         return int(self.lib.mynah_b200_launch_count(self.state))

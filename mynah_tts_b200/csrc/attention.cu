@@ -14,13 +14,13 @@
 // is evaluated in double and rounded once.  Same bits as the CPU loop except
 // where libm's expf is not correctly rounded.
 //
-// FAST kernel: grid (splits, heads, streams).  Each CTA takes a contiguous
-// range of positions, computes a partial (max, sum, weighted V) and, when the
-// work is split or the output must be quantized across heads, publishes it to
-// a scratch buffer; the last CTA of a stream to arrive (one atomic counter per
-// stream) merges all partials in split order and optionally quantizes the
-// merged row to int8 for the next projection.  Results do not depend on
-// arrival order.
+// FAST kernel: grid (chunks, heads, streams).  Each CTA takes a fixed chunk of
+// 32 positions, computes a partial (max, sum, weighted V) and, when a head spans
+// several chunks, publishes it to a scratch buffer; the last chunk of a head to
+// arrive (an atomic counter per head) merges that head's partials in chunk
+// order; when the next projection wants int8 input, the last head of a stream
+// to finish (a counter per stream) quantizes the merged row.  Results depend
+// neither on arrival order nor on the batch a stream is stepped in.
 #include "common.cuh"
 #include "launch.h"
 
@@ -40,7 +40,7 @@ struct AttnP {
     int *status;
     long q_stride, slot_stride, cache_stride, out_stride;
     long position, valid;
-    int heads, hw, batch, splits, chunk_max;
+    int heads, hw, batch, max_chunks;
     float scale;
 };
 
@@ -108,202 +108,298 @@ __global__ void __launch_bounds__(256) k_attn_strict(AttnP p) {
     }
 }
 
-// -------------------------------------------------------------------- fast
-constexpr int FAST_THREADS = 128;
 
-template <int VEC>
-__global__ void __launch_bounds__(FAST_THREADS) k_attn_fast(AttnP p) {
+// -------------------------------------------------------------------- fast
+// Positions are cut into fixed chunks of CHUNK rows, one CTA per (chunk, head,
+// stream): the partition depends only on the stream's own length, never on how
+// many streams are stepped together, so a stream's result is bit-identical
+// whatever batch it runs in.  A chunk's K and V rows are staged in shared
+// memory by bulk asynchronous copies (one 16-byte-aligned row per copy, all in
+// flight at once, completion counted on an mbarrier).
+constexpr int CHUNK = 32;
+constexpr int FAST_THREADS = 128;
+constexpr unsigned SPIN_LIMIT = 1u << 24;
+
+__device__ __forceinline__ unsigned smem_addr(const void *ptr) {
+    return (unsigned)__cvta_generic_to_shared(ptr);
+}
+__device__ __forceinline__ void mbar_init(void *bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(void *bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)),
+                 "r"(bytes)
+                 : "memory");
+}
+// global -> this CTA's shared memory, size and both addresses multiples of 16 bytes
+__device__ __forceinline__ void bulk_g2s(void *dst, const void *src, unsigned bytes, void *bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+            "r"(smem_addr(dst)), "l"(src), "r"(bytes), "r"(smem_addr(bar))
+        : "memory");
+}
+// Bounded wait for phase `parity`; false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(void *bar, unsigned parity, unsigned limit) {
+    for (unsigned i = 0; i < limit; ++i) {
+        unsigned done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(smem_addr(bar)), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
+// Quantize one merged row (already in `vals`, shared) to int8: shared by the
+// per-stream tail of the kernel below.
+__device__ __forceinline__ void quantize_shared_row(const float *vals, int width, int8_t *qrow,
+                                                    float *sx_out, float *red) {
+    float amax = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) amax = fmaxf(amax, fabsf(vals[i]));
+    amax = block_max(amax, red);
+    const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const int v = round_half_away(__fmul_rn(vals[i], inv));
+        qrow[i] = (int8_t)min(127, max(-127, v));
+    }
+    if (threadIdx.x == 0) *sx_out = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 0.0f;
+}
+
+__global__ void __launch_bounds__(FAST_THREADS) k_attn_chunk(AttnP p) {
     extern __shared__ __align__(16) float sm[];
     __shared__ float red[33];
+    __shared__ float s_ml[2];
     __shared__ unsigned s_last;
+    __shared__ __align__(8) unsigned long long mbar;
     const int sp = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
     long pos, valid;
     float *kc, *vc;
     if (!lane_setup(p, b, pos, valid, kc, vc)) return;
+    const int ns = (int)((valid + CHUNK - 1) / CHUNK);
+    if (sp >= ns) return;
     const int hw = p.hw, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const long chunk = (valid + p.splits - 1) / p.splits;
-    const long s0 = (long)sp * chunk;
-    const long s1 = min(valid, s0 + chunk);
-    const long cnt = s1 > s0 ? s1 - s0 : 0;
+    const long s0 = (long)sp * CHUNK;
+    const int cnt = (int)min((long)CHUNK, valid - s0);
+    const int tpp = hw / 4;                         // float4 lanes per row (power of two <= 32)
+    const int groups = FAST_THREADS / tpp;
     float *qs = sm;                                 // [hw]
-    float *sc = sm + hw;                            // [chunk_max]
-    float *accs = sc + p.chunk_max;                 // [groups][hw]
+    float *Ks = qs + hw;                            // [CHUNK][hw]
+    float *Vs = Ks + CHUNK * hw;                    // [CHUNK][hw]
+    float *sc = Vs + CHUNK * hw;                    // [CHUNK]
+    float *accs = sc + CHUNK;                       // [groups][hw]; reused by the merges
     const long hoff = (long)h * hw;
     const float *knew = p.k_new == nullptr ? nullptr : p.k_new + (long)b * p.q_stride + hoff;
     const float *vnew = p.v_new == nullptr ? nullptr : p.v_new + (long)b * p.q_stride + hoff;
+    const unsigned row_bytes = (unsigned)hw * 4u;
+    if (threadIdx.x == 0) mbar_init(&mbar, 1u);
+    __syncthreads();
+    if (warp == 0) {
+        if (lane == 0) mbar_expect_tx(&mbar, 2u * row_bytes * (unsigned)cnt);
+        __syncwarp();
+        if (lane < cnt) {
+            const long s = s0 + lane;
+            const bool fresh = knew != nullptr && s == pos;   // the row being appended now
+            bulk_g2s(Ks + lane * hw, fresh ? knew : kc + s * p.cache_stride + hoff, row_bytes, &mbar);
+            bulk_g2s(Vs + lane * hw, fresh ? vnew : vc + s * p.cache_stride + hoff, row_bytes, &mbar);
+        }
+    }
     for (int d = threadIdx.x; d < hw; d += blockDim.x) {
         qs[d] = p.q[(long)b * p.q_stride + hoff + d];
-        if (knew != nullptr && sp == 0) {   // one CTA per (stream, head) appends
+        if (knew != nullptr && sp == 0) {   // one CTA per (stream, head) appends; readers of row
+                                            // `pos` take it from the new row, never from the cache
             kc[pos * p.cache_stride + hoff + d] = knew[d];
             vc[pos * p.cache_stride + hoff + d] = vnew[d];
         }
     }
     __syncthreads();
-    // ---- scores ---------------------------------------------------------------
-    float lmax = -FLT_MAX;
-    if (VEC == 4) {
-        const int lpp = hw / 4;            // lanes per position (power of two <= 32)
-        const int ppw = 32 / lpp;          // positions per warp step
-        const int sub = lane / lpp, li = lane % lpp;
+    if (!mbar_wait(&mbar, 0u, SPIN_LIMIT)) {
+        // the copies never landed: flag it, give them one more bounded wait so none
+        // is in flight when this CTA's shared memory is released, and leave.
+        if (threadIdx.x == 0 && p.status != nullptr) atomicOr(p.status, 2);
+        mbar_wait(&mbar, 0u, SPIN_LIMIT);
+        return;
+    }
+    // ---- scores: tpp lanes share a row, 32/tpp rows per warp step -----------------
+    {
+        const int ppw = 32 / tpp, sub = lane / tpp, li = lane % tpp;
         const float4 qv = reinterpret_cast<const float4 *>(qs)[li];
         const int step = (FAST_THREADS / 32) * ppw;
-        // all lanes iterate the same number of times so the shuffles stay converged
-        const long bound = (cnt + step - 1) / step * step;
-        for (long i = warp * ppw + sub; i < bound; i += step) {
+#pragma unroll 4
+        for (int i = warp * ppw + sub; i < CHUNK; i += step) {   // same trip count on every lane
             float a = 0.0f;
-            const bool ok = i < cnt;
-            if (ok) {
-                const long s = s0 + i;
-                const float *src = (knew != nullptr && s == pos) ? knew : kc + s * p.cache_stride + hoff;
-                const float4 kv = reinterpret_cast<const float4 *>(src)[li];
+            if (i < cnt) {
+                const float4 kv = reinterpret_cast<const float4 *>(Ks + i * hw)[li];
                 a = fmaf(qv.x, kv.x, a); a = fmaf(qv.y, kv.y, a);
                 a = fmaf(qv.z, kv.z, a); a = fmaf(qv.w, kv.w, a);
             }
-            for (int o = lpp >> 1; o > 0; o >>= 1) a += __shfl_xor_sync(MB_FULL, a, o);
-            if (ok && li == 0) {
-                a *= p.scale;
-                sc[i] = a;
-                lmax = fmaxf(lmax, a);
-            }
-        }
-    } else {
-        for (long i = warp; i < cnt; i += FAST_THREADS / 32) {
-            const long s = s0 + i;
-            const float *src = (knew != nullptr && s == pos) ? knew : kc + s * p.cache_stride + hoff;
-            float a = 0.0f;
-            for (int d = lane; d < hw; d += 32) a = fmaf(qs[d], src[d], a);
-            a = warp_sum(a);
-            if (lane == 0) {
-                a *= p.scale;
-                sc[i] = a;
-                lmax = fmaxf(lmax, a);
-            }
+            for (int o = tpp >> 1; o > 0; o >>= 1) a += __shfl_xor_sync(MB_FULL, a, o);
+            if (li == 0) sc[i] = i < cnt ? a * p.scale : -FLT_MAX;
         }
     }
-    const float m = block_max(lmax, red);   // includes the barrier that publishes sc[]
+    __syncthreads();
+    if (warp == 0) {   // CHUNK == 32: one lane per row
+        const float v = sc[lane];
+        const float m = warp_max(v);
+        const float e = lane < cnt ? exp_ref<false>(v - m) : 0.0f;
+        sc[lane] = e;
+        const float l = warp_sum(e);
+        if (lane == 0) { s_ml[0] = m; s_ml[1] = l; }
+    }
+    __syncthreads();
+    // ---- weighted V: group g of tpp threads takes rows g, g+groups, ... -----------
+    {
+        const int g = threadIdx.x / tpp, li = threadIdx.x % tpp;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+        for (int i = g; i < cnt; i += groups) {
+            const float4 vv = reinterpret_cast<const float4 *>(Vs + i * hw)[li];
+            const float w = sc[i];
+            acc.x = fmaf(w, vv.x, acc.x); acc.y = fmaf(w, vv.y, acc.y);
+            acc.z = fmaf(w, vv.z, acc.z); acc.w = fmaf(w, vv.w, acc.w);
+        }
+        reinterpret_cast<float4 *>(accs)[g * tpp + li] = acc;
+    }
+    __syncthreads();
+    const float m = s_ml[0], l = s_ml[1];
+    const int width = p.heads * hw;
+    const bool quant = p.qx != nullptr;
+    float *outrow = p.out == nullptr ? nullptr : p.out + (long)b * p.out_stride;
+    // staging row for the merged output when it must be quantized but not stored
+    float *merged = p.partials == nullptr ? nullptr
+                                          : p.partials + (long)p.batch * p.heads * p.max_chunks * (hw + 2) +
+                                                (long)b * width;
+    if (ns == 1) {
+        for (int d = threadIdx.x; d < hw; d += blockDim.x) {
+            float a = 0.0f;
+            for (int g = 0; g < groups; ++g) a += accs[g * hw + d];
+            const float o = l > 0.0f ? a / l : 0.0f;
+            if (outrow != nullptr) outrow[hoff + d] = o;
+            if (quant) merged[hoff + d] = o;
+        }
+    } else {
+        float *part = p.partials + (((long)b * p.heads + h) * p.max_chunks + sp) * (hw + 2);
+        for (int d = threadIdx.x; d < hw; d += blockDim.x) {
+            float a = 0.0f;
+            for (int g = 0; g < groups; ++g) a += accs[g * hw + d];
+            part[2 + d] = a;
+        }
+        if (threadIdx.x == 0) { part[0] = m; part[1] = l; }
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            unsigned *ctr = p.counters + (long)b * p.heads + h;
+            const unsigned prev = atomicAdd(ctr, 1u);
+            s_last = prev == (unsigned)ns - 1u;
+            if (s_last) *ctr = 0u;
+        }
+        __syncthreads();
+        if (!s_last) return;
+        // ---- this head's last chunk merges the head, chunks in index order ----------
+        __threadfence();
+        const float *ph = p.partials + ((long)b * p.heads + h) * p.max_chunks * (hw + 2);
+        float *wts = accs;                   // [ns] merge weights (ns <= max_chunks <= groups*hw)
+        for (int s = threadIdx.x; s < ns; s += blockDim.x) wts[s] = __ldcg(ph + (long)s * (hw + 2));
+        __syncthreads();
+        float M = -FLT_MAX;
+        for (int s = 0; s < ns; ++s) M = fmaxf(M, wts[s]);
+        __syncthreads();
+        for (int s = threadIdx.x; s < ns; s += blockDim.x) wts[s] = exp_ref<false>(wts[s] - M);
+        __syncthreads();
+        float L = 0.0f;
+        for (int s = 0; s < ns; ++s) L = fmaf(__ldcg(ph + (long)s * (hw + 2) + 1), wts[s], L);
+        for (int d = threadIdx.x; d < hw; d += blockDim.x) {
+            float O = 0.0f;
+#pragma unroll 4
+            for (int s = 0; s < ns; ++s) O = fmaf(__ldcg(ph + (long)s * (hw + 2) + 2 + d), wts[s], O);
+            const float o = L > 0.0f ? O / L : 0.0f;
+            if (outrow != nullptr) outrow[hoff + d] = o;
+            if (quant) merged[hoff + d] = o;
+        }
+    }
+    if (!quant) return;
+    // ---- the stream's last head quantizes the whole row --------------------------------
+    if (p.heads > 1) {
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            unsigned *ctr = p.counters + (long)p.batch * p.heads + b;
+            const unsigned prev = atomicAdd(ctr, 1u);
+            s_last = prev == (unsigned)p.heads - 1u;
+            if (s_last) *ctr = 0u;
+        }
+        __syncthreads();
+        if (!s_last) return;
+        __threadfence();
+    } else {
+        __syncthreads();
+    }
+    float *vals = Ks;   // at least CHUNK*hw floats; the launcher checks heads*hw fits
+    for (int i = threadIdx.x; i < width; i += blockDim.x) vals[i] = __ldcg(merged + i);
+    __syncthreads();
+    quantize_shared_row(vals, width, p.qx + (long)b * width, p.sx + b, red);
+}
+
+// Shapes the chunked kernel cannot take (head width not a power-of-two multiple
+// of 4, or unaligned rows): one CTA per (head, stream), plain loads, no split.
+__global__ void __launch_bounds__(FAST_THREADS) k_attn_scalar(AttnP p) {
+    extern __shared__ __align__(16) float sm[];
+    __shared__ float red[33];
+    const int h = blockIdx.x, b = blockIdx.y;
+    long pos, valid;
+    float *kc, *vc;
+    if (!lane_setup(p, b, pos, valid, kc, vc)) return;
+    const int hw = p.hw, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float *qs = sm;
+    float *sc = sm + hw;
+    const long hoff = (long)h * hw;
+    const float *knew = p.k_new == nullptr ? nullptr : p.k_new + (long)b * p.q_stride + hoff;
+    const float *vnew = p.v_new == nullptr ? nullptr : p.v_new + (long)b * p.q_stride + hoff;
+    for (int d = threadIdx.x; d < hw; d += blockDim.x) {
+        qs[d] = p.q[(long)b * p.q_stride + hoff + d];
+        if (knew != nullptr) {
+            kc[pos * p.cache_stride + hoff + d] = knew[d];
+            vc[pos * p.cache_stride + hoff + d] = vnew[d];
+        }
+    }
+    __syncthreads();
+    float lmax = -FLT_MAX;
+    for (long s = warp; s < valid; s += FAST_THREADS / 32) {
+        const float *src = (knew != nullptr && s == pos) ? knew : kc + s * p.cache_stride + hoff;
+        float a = 0.0f;
+        for (int d = lane; d < hw; d += 32) a = fmaf(qs[d], src[d], a);
+        a = warp_sum(a);
+        if (lane == 0) {
+            a *= p.scale;
+            sc[s] = a;
+            lmax = fmaxf(lmax, a);
+        }
+    }
+    const float m = block_max(lmax, red);
     float lsum = 0.0f;
-    for (long i = threadIdx.x; i < cnt; i += blockDim.x) {
-        const float e = exp_ref<false>(sc[i] - m);
-        sc[i] = e;
+    for (long s = threadIdx.x; s < valid; s += blockDim.x) {
+        const float e = exp_ref<false>(sc[s] - m);
+        sc[s] = e;
         lsum += e;
     }
     const float l = block_sum(lsum, red);
-    // ---- weighted V -------------------------------------------------------------
-    const int tpp = hw / VEC;                       // threads per position
-    const int groups = tpp >= FAST_THREADS ? 1 : FAST_THREADS / tpp;
-    if (VEC == 4) {
-        const int g = threadIdx.x / tpp, li = threadIdx.x % tpp;
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (g < groups) {
-            for (long i = g; i < cnt; i += groups) {
-                const long s = s0 + i;
-                const float *src = (vnew != nullptr && s == pos) ? vnew : vc + s * p.cache_stride + hoff;
-                const float4 vv = reinterpret_cast<const float4 *>(src)[li];
-                const float w = sc[i];
-                acc.x = fmaf(w, vv.x, acc.x); acc.y = fmaf(w, vv.y, acc.y);
-                acc.z = fmaf(w, vv.z, acc.z); acc.w = fmaf(w, vv.w, acc.w);
-            }
-            reinterpret_cast<float4 *>(accs)[g * tpp + li] = acc;
-        }
-    } else {
-        // scalar layout: thread t covers d = t, t + blockDim, ...; single group
-        for (int d = threadIdx.x; d < hw; d += blockDim.x) {
-            float a = 0.0f;
-            for (long i = 0; i < cnt; ++i) {
-                const long s = s0 + i;
-                const float *src = (vnew != nullptr && s == pos) ? vnew : vc + s * p.cache_stride + hoff;
-                a = fmaf(sc[i], src[d], a);
-            }
-            accs[d] = a;
-        }
-    }
-    __syncthreads();
-    const int ngroups = VEC == 4 ? groups : 1;
-    const bool publish = p.splits > 1 || (p.qx != nullptr && p.heads > 1);
-    float *part = p.partials == nullptr
-                      ? nullptr
-                      : p.partials + (((long)b * p.heads + h) * p.splits + sp) * (hw + 2);
     for (int d = threadIdx.x; d < hw; d += blockDim.x) {
         float a = 0.0f;
-        for (int g = 0; g < ngroups; ++g) a += accs[g * hw + d];
-        if (publish) part[2 + d] = a;
-        else {
-            const float o = l > 0.0f ? a / l : 0.0f;
-            if (p.out != nullptr) p.out[(long)b * p.out_stride + hoff + d] = o;
-            accs[d] = o;   // kept for the single-CTA quantization below
+        for (long s = 0; s < valid; ++s) {
+            const float *src = (vnew != nullptr && s == pos) ? vnew : vc + s * p.cache_stride + hoff;
+            a = fmaf(sc[s], src[d], a);
         }
+        p.out[(long)b * p.out_stride + hoff + d] = l > 0.0f ? a / l : 0.0f;
     }
-    if (!publish) {
-        if (p.qx == nullptr) return;
-        // heads == 1 and one split: this CTA owns the whole row
-        __syncthreads();
-        float amax = 0.0f;
-        for (int d = threadIdx.x; d < hw; d += blockDim.x) amax = fmaxf(amax, fabsf(accs[d]));
-        amax = block_max(amax, red);
-        int8_t *qrow = p.qx + (long)b * p.heads * hw;
-        const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
-        for (int d = threadIdx.x; d < hw; d += blockDim.x) {
-            int v = round_half_away(__fmul_rn(accs[d], inv));
-            qrow[d] = (int8_t)min(127, max(-127, v));
-        }
-        if (threadIdx.x == 0) p.sx[b] = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 0.0f;
-        return;
-    }
-    if (threadIdx.x == 0) {
-        part[0] = cnt > 0 ? m : -FLT_MAX;
-        part[1] = cnt > 0 ? l : 0.0f;
-    }
-    // ---- last CTA of this stream merges ------------------------------------------
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        const unsigned total = (unsigned)(p.heads * p.splits);
-        const unsigned prev = atomicAdd(&p.counters[b], 1u);
-        s_last = (prev == total - 1u) ? 1u : 0u;
-        if (s_last) p.counters[b] = 0u;   // ready for the next launch
-    }
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    const int width = p.heads * hw;
-    const float *base = p.partials + (long)b * p.heads * p.splits * (hw + 2);
-    float amax = 0.0f;
-    // merged outputs are parked in this stream's first partial slots (each thread
-    // overwrites only what it alone reads) before the quantization pass.
-    for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        const int hh = i / hw, d = i % hw;
-        const float *ph = base + (long)hh * p.splits * (hw + 2);
-        float M = -FLT_MAX;
-        for (int s = 0; s < p.splits; ++s) M = fmaxf(M, __ldcg(ph + (long)s * (hw + 2)));
-        float L = 0.0f, O = 0.0f;
-        for (int s = 0; s < p.splits; ++s) {
-            const float *ps = ph + (long)s * (hw + 2);
-            const float ls = __ldcg(ps + 1);
-            if (ls > 0.0f) {
-                const float wgt = exp_ref<false>(__ldcg(ps) - M);
-                L = fmaf(ls, wgt, L);
-                O = fmaf(__ldcg(ps + 2 + d), wgt, O);
-            }
-        }
-        const float o = L > 0.0f ? O / L : 0.0f;
-        if (p.out != nullptr) p.out[(long)b * p.out_stride + i] = o;
-        if (p.qx != nullptr) {
-            sm[i] = o;   // the launcher sizes shared memory for heads*hw floats
-            amax = fmaxf(amax, fabsf(o));
-        }
-    }
-    if (p.qx == nullptr) return;
-    amax = block_max(amax, red);
-    int8_t *qrow = p.qx + (long)b * width;
-    const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        int v = round_half_away(__fmul_rn(sm[i], inv));
-        qrow[i] = (int8_t)min(127, max(-127, v));
-    }
-    if (threadIdx.x == 0) p.sx[b] = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 0.0f;
 }
 
 bool is_pow2(long v) { return v > 0 && (v & (v - 1)) == 0; }
+
+size_t chunks_for(size_t max_valid) { return (max_valid + CHUNK - 1) / CHUNK; }
 
 }  // namespace
 
@@ -311,15 +407,19 @@ bool is_pow2(long v) { return v > 0 && (v & (v - 1)) == 0; }
 // per device at backend open, outside any stream capture.
 extern "C" int mb_attention_init(void) {
     int rc = (int)cudaFuncSetAttribute(k_attn_strict, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    if (rc == 0) rc = (int)cudaFuncSetAttribute(k_attn_fast<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    if (rc == 0) rc = (int)cudaFuncSetAttribute(k_attn_fast<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (rc == 0) rc = (int)cudaFuncSetAttribute(k_attn_chunk, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (rc == 0) rc = (int)cudaFuncSetAttribute(k_attn_scalar, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     return rc;
 }
 
-extern "C" size_t mb_attention_partials_floats(size_t batch, size_t heads, size_t splits,
-                                               size_t head_width) {
-    return batch * heads * splits * (head_width + 2);
+// Scratch the chunked kernel needs for `batch` lanes that attend at most
+// `max_valid` rows: per-chunk partials, then one merged row per lane.
+extern "C" size_t mb_attention_scratch_floats(size_t batch, size_t heads, size_t max_valid,
+                                              size_t head_width) {
+    return batch * heads * chunks_for(max_valid) * (head_width + 2) + batch * heads * head_width;
 }
+// Arrival counters: one per (lane, head), then one per lane.
+extern "C" size_t mb_attention_counters(size_t batch, size_t heads) { return batch * (heads + 1); }
 
 extern "C" int mb_attention(const mb_attn_args *a, mb_stream stream) {
     if (a == nullptr || a->q == nullptr || a->k_cache == nullptr || a->v_cache == nullptr ||
@@ -343,40 +443,33 @@ extern "C" int mb_attention(const mb_attn_args *a, mb_stream stream) {
     // the cache capacity in `valid`.
     const long max_valid = (long)a->valid;
     if (max_valid <= 0) return (int)cudaErrorInvalidValue;
-    if (a->strict) {
-        if (a->out == nullptr) return (int)cudaErrorInvalidValue;
-        p.splits = 1; p.chunk_max = (int)max_valid;
-        const size_t smem = (size_t)(p.hw + max_valid) * sizeof(float);
-        if (smem > 200u * 1024u) return (int)cudaErrorInvalidValue;
-        k_attn_strict<<<dim3((unsigned)p.heads, (unsigned)p.batch), 256, smem, s>>>(p);
-        int rc = mb_check_launch();
-        if (rc == 0 && a->qx != nullptr)
-            rc = mb_quant_rows(a->out, a->batch, a->heads * a->head_width, a->qx, a->sx,
-                               a->n_active, stream);
-        return rc;
+    p.max_chunks = (int)chunks_for((size_t)max_valid);
+    const size_t width = a->heads * a->head_width;
+    const bool chunked = !a->strict && (p.hw % 4) == 0 && is_pow2(p.hw / 4) && p.hw / 4 <= 32 &&
+                         (p.cache_stride % 4) == 0 && (p.q_stride % 4) == 0 &&
+                         (p.slot_stride % 4) == 0 && width <= (size_t)CHUNK * p.hw &&
+                         (((uintptr_t)a->k_cache | (uintptr_t)a->v_cache | (uintptr_t)a->q |
+                           (uintptr_t)a->k_new | (uintptr_t)a->v_new) & 15u) == 0;
+    if (chunked) {
+        const bool needs_scratch = p.max_chunks > 1 || a->qx != nullptr;
+        if (needs_scratch && (a->partials == nullptr || a->counters == nullptr))
+            return (int)cudaErrorInvalidValue;
+        const int groups = FAST_THREADS / (p.hw / 4);
+        const size_t floats = (size_t)p.hw + 2u * CHUNK * p.hw + CHUNK + (size_t)groups * p.hw;
+        if (floats * sizeof(float) > 200u * 1024u || (size_t)p.max_chunks > (size_t)groups * p.hw)
+            return (int)cudaErrorInvalidValue;
+        dim3 grid((unsigned)p.max_chunks, (unsigned)p.heads, (unsigned)p.batch);
+        k_attn_chunk<<<grid, FAST_THREADS, floats * sizeof(float), s>>>(p);
+        return mb_check_launch();
     }
-    p.splits = (int)(a->splits > 0 ? a->splits : 1);
-    const bool publish = p.splits > 1 || (a->qx != nullptr && p.heads > 1);
-    if (publish && (a->partials == nullptr || a->counters == nullptr))
-        return (int)cudaErrorInvalidValue;
-    p.chunk_max = (int)((max_valid + p.splits - 1) / p.splits);
-    const bool vec4 = (p.hw % 4) == 0 && is_pow2(p.hw / 4) && p.hw / 4 <= 32 &&
-                      (p.cache_stride % 4) == 0 && (p.q_stride % 4) == 0 &&
-                      (p.slot_stride % 4) == 0 &&
-                      (((uintptr_t)a->k_cache | (uintptr_t)a->v_cache | (uintptr_t)a->q |
-                        (uintptr_t)a->k_new | (uintptr_t)a->v_new) & 15u) == 0;
-    const int tpp = vec4 ? p.hw / 4 : p.hw;
-    const int groups = vec4 ? (tpp >= FAST_THREADS ? 1 : FAST_THREADS / tpp) : 1;
-    size_t floats = (size_t)p.hw + p.chunk_max + (size_t)groups * p.hw;
-    // the merging CTA parks heads*hw merged outputs in the same shared buffer
-    if (a->qx != nullptr && publish && floats < (size_t)p.heads * p.hw) {
-        p.chunk_max += (int)((size_t)p.heads * p.hw - floats);
-        floats = (size_t)p.heads * p.hw;
-    }
-    const size_t smem = floats * sizeof(float);
+    if (a->out == nullptr) return (int)cudaErrorInvalidValue;
+    const size_t smem = (size_t)(p.hw + max_valid) * sizeof(float);
     if (smem > 200u * 1024u) return (int)cudaErrorInvalidValue;
-    dim3 grid((unsigned)p.splits, (unsigned)p.heads, (unsigned)p.batch);
-    if (vec4) k_attn_fast<4><<<grid, FAST_THREADS, smem, s>>>(p);
-    else k_attn_fast<1><<<grid, FAST_THREADS, smem, s>>>(p);
-    return mb_check_launch();
+    dim3 grid((unsigned)p.heads, (unsigned)p.batch);
+    if (a->strict) k_attn_strict<<<grid, 256, smem, s>>>(p);
+    else k_attn_scalar<<<grid, FAST_THREADS, smem, s>>>(p);
+    int rc = mb_check_launch();
+    if (rc == 0 && a->qx != nullptr)
+        rc = mb_quant_rows(a->out, a->batch, width, a->qx, a->sx, a->n_active, stream);
+    return rc;
 }

@@ -235,6 +235,8 @@ void mynah_b200_close(void *state) {
     cudaFree(st->d_counters);
     cudaFree(st->d_token);
     cudaFree(st->d_status);
+    if (st->timer0 != NULL) cudaEventDestroy(st->timer0);
+    if (st->timer1 != NULL) cudaEventDestroy(st->timer1);
     if (st->own_stream && st->stream != NULL) cudaStreamDestroy(st->stream);
     free(st);
 }
@@ -255,6 +257,31 @@ int mynah_b200_quant(const void *state) { return state == NULL ? -1 : ((const mb
 int mynah_b200_strict(const void *state) { return state == NULL ? -1 : ((const mb_state *)state)->strict; }
 unsigned long long mynah_b200_launch_count(const void *state) {
     return state == NULL ? 0ull : ((const mb_state *)state)->launches;
+}
+
+/* Device-time stopwatch on the backend's stream (two CUDA events). */
+int mynah_b200_timer_start(void *state, char *error, size_t cap) {
+    mb_state *st = (mb_state *)state;
+    if (st == NULL) return -1;
+    if (use_device(st, error, cap) != 0) return -1;
+    if (st->timer0 == NULL) {
+        MB_TRY(cudaEventCreate(&st->timer0), "cudaEventCreate");
+        MB_TRY(cudaEventCreate(&st->timer1), "cudaEventCreate");
+    }
+    MB_TRY(cudaEventRecord(st->timer0, st->stream), "cudaEventRecord");
+    mb_clear_error(error, cap);
+    return 0;
+}
+
+int mynah_b200_timer_stop(void *state, float *elapsed_ms, char *error, size_t cap) {
+    mb_state *st = (mb_state *)state;
+    if (st == NULL || elapsed_ms == NULL || st->timer0 == NULL) return -1;
+    if (use_device(st, error, cap) != 0) return -1;
+    MB_TRY(cudaEventRecord(st->timer1, st->stream), "cudaEventRecord");
+    MB_TRY(cudaEventSynchronize(st->timer1), "cudaEventSynchronize");
+    MB_TRY(cudaEventElapsedTime(elapsed_ms, st->timer0, st->timer1), "cudaEventElapsedTime");
+    mb_clear_error(error, cap);
+    return 0;
 }
 
 /* --------------------------------------------------------- product dispatch */
@@ -670,16 +697,6 @@ int mynah_cuda_sgemm_dev(void *state, int trans_a, int trans_b, size_t m, size_t
 }
 
 /* ----------------------------------------------------------------- attention */
-static size_t pick_splits(const mb_state *st, size_t batch, size_t heads, size_t valid) {
-    /* enough CTAs to cover the SMs about twice, at least 16 positions each */
-    size_t splits = (2u * (size_t)st->sm_count + batch * heads - 1u) / (batch * heads);
-    const size_t by_len = (valid + 15u) / 16u;
-    if (splits > by_len) splits = by_len;
-    if (splits > 16u) splits = 16u;
-    if (splits < 1u) splits = 1u;
-    return splits;
-}
-
 static int attention_common(mb_state *st, const float *q, size_t q_stride, const float *k_new,
                             const float *v_new, float *kc, float *vc, size_t position,
                             size_t cache_stride, size_t valid, size_t heads, size_t hw, float scale,
@@ -708,14 +725,14 @@ static int attention_common(mb_state *st, const float *q, size_t q_stride, const
     a.batch = 1;
     a.strict = st->strict;
     a.status = st->d_status;
-    a.splits = st->strict ? 1u : pick_splits(st, 1u, heads, valid);
-    if (a.splits > 1u) {
-        const size_t need = mb_attention_partials_floats(1u, heads, a.splits, hw);
-        const int fresh = st->d_counters == NULL;
+    if (!st->strict) {
+        const size_t need = mb_attention_scratch_floats(1u, heads, valid, hw);
+        const size_t ctrs = mb_attention_counters(1u, heads);
+        const size_t had = st->d_counters_cap;
         if (grow((void **)&st->d_partials, &st->d_partials_cap, need, sizeof(float), error, cap) != 0 ||
-            grow((void **)&st->d_counters, &st->d_counters_cap, 1u, sizeof(unsigned), error, cap) != 0)
+            grow((void **)&st->d_counters, &st->d_counters_cap, ctrs, sizeof(unsigned), error, cap) != 0)
             return -1;
-        if (fresh)
+        if (st->d_counters_cap != had)
             MB_TRY(cudaMemsetAsync(st->d_counters, 0, st->d_counters_cap * sizeof(unsigned), st->stream),
                    "cudaMemset");
         a.partials = st->d_partials;

@@ -43,7 +43,6 @@ typedef struct mb_decoder {
     float *sx;
     float *partials;
     unsigned *counters;
-    size_t self_splits[MAX_BUCKETS], cross_splits[MAX_BUCKETS];
     /* lane state */
     int *d_lens, *d_slots, *d_n_active, *d_allow_eos, *d_eos_flag, *d_eos_frame, *d_frame_idx, *d_status;
     int *d_min_frames;
@@ -170,15 +169,6 @@ static size_t pick_bucket(const mb_decoder *d, size_t batch) {
     for (size_t i = 0; i < d->n_buckets; ++i)
         if (d->bucket_size[i] >= batch) return i;
     return d->n_buckets - 1u;
-}
-
-static size_t splits_for(const mb_decoder *d, size_t batch, size_t heads, size_t positions) {
-    size_t splits = (2u * (size_t)d->st->sm_count + batch * heads - 1u) / (batch * heads);
-    const size_t by_len = (positions + 31u) / 32u;
-    if (splits > by_len) splits = by_len;
-    if (splits > 16u) splits = 16u;
-    if (splits < 1u) splits = 1u;
-    return splits;
 }
 
 int mynah_b200_decoder_create(void *state, const mynah_b200_decoder_desc *desc, void **decoder,
@@ -310,18 +300,12 @@ int mynah_b200_decoder_create(void *state, const mynah_b200_decoder_desc *desc, 
     /* batch buckets: powers of two up to max_batch, then max_batch itself */
     for (size_t b = 1; b < MB && d->n_buckets < MAX_BUCKETS - 1u; b *= 2u) d->bucket_size[d->n_buckets++] = b;
     d->bucket_size[d->n_buckets++] = MB;
-    size_t partial_floats = 0;
-    for (size_t i = 0; i < d->n_buckets; ++i) {
-        const size_t b = d->bucket_size[i];
-        d->self_splits[i] = st->strict ? 1u : splits_for(d, b, d->heads, d->capacity);
-        d->cross_splits[i] = st->strict ? 1u : splits_for(d, b, 1u, d->T);
-        size_t need = mb_attention_partials_floats(b, d->heads, d->self_splits[i], d->hw);
-        if (need > partial_floats) partial_floats = need;
-        need = mb_attention_partials_floats(b, 1u, d->cross_splits[i], XW);
-        if (need > partial_floats) partial_floats = need;
-    }
+    size_t partial_floats = mb_attention_scratch_floats(MB, d->heads, d->capacity, d->hw);
+    const size_t cross_floats = mb_attention_scratch_floats(MB, 1u, d->T, XW);
+    if (cross_floats > partial_floats) partial_floats = cross_floats;
+    const size_t n_counters = mb_attention_counters(MB, d->heads);
     D_TRY(dmalloc((void **)&d->partials, partial_floats * sizeof(float), error, cap));
-    D_TRY(dmalloc((void **)&d->counters, MB * sizeof(unsigned), error, cap));
+    D_TRY(dmalloc((void **)&d->counters, n_counters * sizeof(unsigned), error, cap));
     int **ints[] = {&d->d_lens, &d->d_slots, &d->d_allow_eos, &d->d_eos_flag, &d->d_eos_frame};
     for (size_t i = 0; i < sizeof(ints) / sizeof(ints[0]); ++i)
         D_TRY(dmalloc((void **)ints[i], MB * sizeof(int), error, cap));
@@ -330,7 +314,7 @@ int mynah_b200_decoder_create(void *state, const mynah_b200_decoder_desc *desc, 
     D_TRY(dmalloc((void **)&d->d_status, sizeof(int), error, cap));
     D_TRY(dmalloc((void **)&d->d_min_frames, sizeof(int), error, cap));
     if (ok) {
-        D_TRY(mb_cuda((int)cudaMemset(d->counters, 0, MB * sizeof(unsigned)), "memset", error, cap));
+        D_TRY(mb_cuda((int)cudaMemset(d->counters, 0, n_counters * sizeof(unsigned)), "memset", error, cap));
         D_TRY(mb_cuda((int)cudaMemset(d->d_status, 0, sizeof(int)), "memset", error, cap));
         D_TRY(mb_cuda((int)cudaMemset(d->d_min_frames, 0, sizeof(int)), "memset", error, cap));
         D_TRY(mb_cuda((int)cudaMemset(d->d_eos_flag, 0, MB * sizeof(int)), "memset", error, cap));
@@ -451,7 +435,6 @@ static int enqueue(mb_decoder *d, size_t bucket, int mode, unsigned *count) {
         a.batch = nb;
         a.n_active = d->d_n_active;
         a.strict = st->strict;
-        a.splits = d->self_splits[bucket];
         a.partials = d->partials;
         a.counters = d->counters;
         a.status = d->d_status;
@@ -480,7 +463,6 @@ static int enqueue(mb_decoder *d, size_t bucket, int mode, unsigned *count) {
         a.batch = nb;
         a.n_active = d->d_n_active;
         a.strict = st->strict;
-        a.splits = d->cross_splits[bucket];
         a.partials = d->partials;
         a.counters = d->counters;
         a.status = d->d_status;

@@ -46,6 +46,7 @@ typedef struct mb_state {
     unsigned *d_token;               /* 1 element */
     int *d_status;
     int sm_count;
+    cudaEvent_t timer0, timer1;
     unsigned long long launches;
 } mb_state;
 

@@ -122,15 +122,17 @@ typedef struct {
     size_t batch;
     const int *n_active;
     int strict;
-    /* scratch for the split-position path (fast mode): partial results and
-     * one arrival counter per lane.  splits == 1 needs none. */
-    size_t splits;
-    float *partials;      /* [batch][heads][splits][head_width + 2] */
-    unsigned *counters;   /* [batch], zero before first use, left zero */
+    /* scratch of the chunked kernel (fast mode): mb_attention_scratch_floats()
+     * floats and mb_attention_counters() counters, the counters zero before
+     * first use (the kernel leaves them zero).  Launches that share scratch
+     * must not overlap on the device. */
+    float *partials;
+    unsigned *counters;
     int *status;          /* device error word (nonzero = bad argument seen) */
 } mb_attn_args;
 int mb_attention(const mb_attn_args *args, mb_stream stream);
-size_t mb_attention_partials_floats(size_t batch, size_t heads, size_t splits, size_t head_width);
+size_t mb_attention_scratch_floats(size_t batch, size_t heads, size_t max_valid, size_t head_width);
+size_t mb_attention_counters(size_t batch, size_t heads);
 
 #ifdef __cplusplus
 }
