@@ -147,6 +147,12 @@ int mynah_b200_open(void **state, int device, int quant, int strict, char *error
 void mynah_b200_close(void *state);
 /* Run all work of this backend on the caller's CUDA stream (cudaStream_t). */
 int mynah_b200_set_stream(void *state, void *cuda_stream, char *error, size_t cap);
+/* 1 when this (strict) backend reproduces the host libm's expf and tanhf bit
+ * for bit: correction tables are built from the host's own libm the first time
+ * a strict backend is opened on a device (about 220 MB of device memory, a few
+ * seconds; MYNAH_B200_LIBM_TABLES=0 skips them and strict mode then uses the
+ * correctly rounded functions). */
+int mynah_b200_libm_exact(const void *state);
 int mynah_b200_quant(const void *state);
 int mynah_b200_strict(const void *state);
 /* Device-time stopwatch: two CUDA events recorded on the backend's stream;

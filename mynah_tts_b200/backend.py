@@ -49,6 +49,7 @@ class Backend:
             call(self.lib.mynah_b200_open, C.byref(self.state), device, q, int(strict))
         self.quant = self.lib.mynah_b200_quant(self.state)
         self.strict = bool(self.lib.mynah_b200_strict(self.state))
+        self.libm_exact = bool(self.lib.mynah_b200_libm_exact(self.state))
 
     def close(self):
         if self.state:

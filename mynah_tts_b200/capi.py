@@ -111,6 +111,7 @@ SIGNATURES = {
     "mynah_b200_set_stream": (C.c_int, [C.c_void_p, C.c_void_p, _E]),
     "mynah_b200_timer_start": (C.c_int, [C.c_void_p, _E]),
     "mynah_b200_timer_stop": (C.c_int, [C.c_void_p, c_float_p, _E]),
+    "mynah_b200_libm_exact": (C.c_int, [C.c_void_p]),
     "mynah_b200_quant": (C.c_int, [C.c_void_p]),
     "mynah_b200_strict": (C.c_int, [C.c_void_p]),
     "mynah_b200_launch_count": (C.c_ulonglong, [C.c_void_p]),

@@ -38,6 +38,7 @@ struct AttnP {
     float *partials;
     unsigned *counters;
     int *status;
+    const uint32_t *exp_tab;
     long q_stride, slot_stride, cache_stride, out_stride;
     long position, valid;
     int heads, hw, batch, max_chunks;
@@ -89,7 +90,7 @@ __global__ void __launch_bounds__(256) k_attn_strict(AttnP p) {
     }
     const float m = block_max(lmax, red);
     for (long s = threadIdx.x; s < valid; s += blockDim.x)
-        sc[s] = exp_ref<true>(__fsub_rn(sc[s], m));
+        sc[s] = exp_ref<true>(__fsub_rn(sc[s], m), p.exp_tab);
     __syncthreads();
     if (threadIdx.x == 0) {
         float den = 0.0f;
@@ -433,6 +434,7 @@ extern "C" int mb_attention(const mb_attn_args *a, mb_stream stream) {
     p.slots = a->slots; p.lens = a->lens; p.n_active = a->n_active;
     p.out = a->out; p.qx = a->qx; p.sx = a->sx;
     p.partials = a->partials; p.counters = a->counters; p.status = a->status;
+    p.exp_tab = a->exp_tab;
     p.q_stride = (long)a->q_stride; p.slot_stride = (long)a->slot_stride;
     p.cache_stride = (long)a->cache_stride; p.out_stride = (long)a->out_stride;
     p.position = (long)a->position; p.valid = (long)a->valid;

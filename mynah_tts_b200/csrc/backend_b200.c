@@ -12,6 +12,9 @@
 #include "host_common.h"
 #include "../../include/mynah_b200.h"
 
+#include <math.h>
+#include <pthread.h>
+#include <unistd.h>
 #include <stdlib.h>
 #include <string.h>
 
@@ -165,6 +168,113 @@ static int grow(void **ptr, size_t *have, size_t want, size_t elem, char *error,
     return 0;
 }
 
+/* ------------------------------------------------------- libm parity tables */
+/* Tables are per device and shared by every backend opened on it in this
+ * process; they live until the process exits. */
+#define LIBM_MAX_DEVICES 16
+#define TANH_LO_BITS 0x32800000u /* must match libm_parity.cuh */
+#define TANH_HI_BITS 0x41800000u
+#define EXP_LO_BITS 0x38000000u
+#define EXP_HI_BITS 0x43800000u
+static struct { mb_libm_tables tables; int state; /* 0 none, 1 exact, -1 failed */ } g_libm[LIBM_MAX_DEVICES];
+static pthread_mutex_t g_libm_lock = PTHREAD_MUTEX_INITIALIZER;
+
+typedef struct { float *out; uint32_t first_bits; size_t begin, end; int is_exp; } libm_job;
+
+static void *libm_worker(void *arg) {
+    const libm_job *j = (const libm_job *)arg;
+    for (size_t i = j->begin; i < j->end; ++i) {
+        const uint32_t bits = j->first_bits + (uint32_t)i;
+        float a;
+        memcpy(&a, &bits, sizeof(a));
+        j->out[i] = j->is_exp ? expf(-a) : tanhf(a);   /* the HOST libm, which the reference links */
+    }
+    return NULL;
+}
+
+static int build_libm_table(mb_state *st, int is_exp, uint32_t lo, uint32_t hi, uint32_t **table_out,
+                            char *error, size_t cap) {
+    enum { RUN = 1 << 23, MAX_THREADS = 64 };
+    const size_t total = (size_t)(hi - lo);
+    uint32_t *table = NULL;
+    float *host = (float *)malloc((size_t)RUN * sizeof(float));
+    float *dev = NULL;
+    int *status = st->d_status;
+    if (host == NULL) {
+        mb_set_error(error, cap, "out of memory building libm tables");
+        return -1;
+    }
+    int rc = (int)cudaMalloc((void **)&table, total / 8u * sizeof(uint32_t));
+    if (rc == 0) rc = (int)cudaMalloc((void **)&dev, (size_t)RUN * sizeof(float));
+    long ncpu = sysconf(_SC_NPROCESSORS_ONLN);
+    size_t threads = ncpu < 1 ? 1u : (ncpu > MAX_THREADS ? MAX_THREADS : (size_t)ncpu);
+    for (size_t off = 0; off < total && rc == 0; off += RUN) {
+        const size_t count = total - off < RUN ? total - off : RUN;
+        pthread_t tid[MAX_THREADS];
+        libm_job jobs[MAX_THREADS];
+        size_t started = 0;
+        for (size_t t = 0; t < threads; ++t) {
+            jobs[t].out = host;
+            jobs[t].first_bits = lo + (uint32_t)off;
+            jobs[t].begin = count * t / threads;
+            jobs[t].end = count * (t + 1) / threads;
+            jobs[t].is_exp = is_exp;
+            if (t + 1 == threads || pthread_create(&tid[t], NULL, libm_worker, &jobs[t]) != 0) {
+                jobs[t].end = count;           /* this thread takes the rest */
+                libm_worker(&jobs[t]);
+                break;
+            }
+            ++started;
+        }
+        for (size_t t = 0; t < started; ++t) pthread_join(tid[t], NULL);
+        rc = (int)cudaMemcpyAsync(dev, host, count * sizeof(float), cudaMemcpyHostToDevice, st->stream);
+        if (rc == 0) rc = mb_libm_delta(dev, lo + (uint32_t)off, count, is_exp, table + off / 8u, status, st->stream);
+        if (rc == 0) rc = (int)cudaStreamSynchronize(st->stream);   /* host buffer is reused */
+        st->launches += 1;
+    }
+    int flags = 0;
+    if (rc == 0) rc = (int)cudaMemcpy(&flags, status, sizeof(int), cudaMemcpyDeviceToHost);
+    free(host);
+    cudaFree(dev);
+    if (rc != 0 || (flags & 4) != 0) {
+        cudaFree(table);
+        if (rc == 0) cudaMemset(status, 0, sizeof(int));
+        if (rc != 0) return mb_cuda(rc, "build libm tables", error, cap);
+        mb_set_error(error, cap, "host libm differs from the device by more than the tables can express");
+        return -1;
+    }
+    *table_out = table;
+    return 0;
+}
+
+static void libm_tables_for(mb_state *st) {
+    if (st->device < 0 || st->device >= LIBM_MAX_DEVICES) return;
+    pthread_mutex_lock(&g_libm_lock);
+    if (g_libm[st->device].state == 0) {
+        char msg[128];
+        uint32_t *tt = NULL, *et = NULL;
+        if (build_libm_table(st, 0, TANH_LO_BITS, TANH_HI_BITS, &tt, msg, sizeof(msg)) == 0 &&
+            build_libm_table(st, 1, EXP_LO_BITS, EXP_HI_BITS, &et, msg, sizeof(msg)) == 0) {
+            g_libm[st->device].tables.tanh_tab = tt;
+            g_libm[st->device].tables.exp_tab = et;
+            g_libm[st->device].state = 1;
+        } else {
+            cudaFree(tt);
+            g_libm[st->device].state = -1;
+        }
+    }
+    if (g_libm[st->device].state == 1) {
+        st->libm = g_libm[st->device].tables;
+        st->libm_exact = 1;
+    }
+    pthread_mutex_unlock(&g_libm_lock);
+}
+
+/* 1 when strict mode reproduces the host libm's expf/tanhf bit for bit. */
+int mynah_b200_libm_exact(const void *state) {
+    return state == NULL ? 0 : ((const mb_state *)state)->libm_exact;
+}
+
 /* ------------------------------------------------------------ open / close */
 int mynah_b200_open(void **state, int device, int quant, int strict, char *error, size_t cap) {
     if (state == NULL) {
@@ -213,6 +323,10 @@ int mynah_b200_open(void **state, int device, int quant, int strict, char *error
         return -1;
     }
     st->own_stream = 1;
+    if (st->strict) {
+        const char *env = getenv("MYNAH_B200_LIBM_TABLES");
+        if (env == NULL || strcmp(env, "0") != 0) libm_tables_for(st);
+    }
     *state = st;
     mb_clear_error(error, cap);
     return 0;
@@ -320,6 +434,7 @@ static int product_dev(mb_state *st, const float *dev_in, float *dev_out, size_t
     g.batch = rows;
     g.epilogue = MB_EPI_STORE;
     g.strict = st->strict;
+    g.tanh_tab = st->libm.tanh_tab;
     if (w->qtype == MB_INT8 || w->qtype == MB_INT4) {
         if (grow((void **)&st->d_qx, &st->d_qx_cap, rows * iw, 1, error, cap) != 0 ||
             grow((void **)&st->d_sx, &st->d_sx_cap, rows, sizeof(float), error, cap) != 0)
@@ -561,7 +676,7 @@ int mynah_cuda_copy_dev(void *state, float *dev_dst, const float *dev_src, size_
 int mynah_cuda_gelu_inplace(void *state, float *dev_data, size_t n, char *error, size_t cap) {
     SEAM_PROLOGUE();
     if (dev_data == NULL) return -1;
-    MB_TRY(mb_gelu(dev_data, n, st->strict, st->stream), "gelu");
+    MB_TRY(mb_gelu(dev_data, n, st->strict, st->libm.tanh_tab, st->stream), "gelu");
     st->launches += 1;
     mb_clear_error(error, cap);
     return 0;
@@ -641,7 +756,7 @@ static int gelu_host_common(void *state, float *host_data, size_t n, int strict,
     SEAM_PROLOGUE();
     if (host_data == NULL) return -1;
     if (stage_in(st, host_data, n, error, cap) != 0) return -1;
-    MB_TRY(mb_gelu(st->d_in, n, strict, st->stream), "gelu");
+    MB_TRY(mb_gelu(st->d_in, n, strict, st->libm.tanh_tab, st->stream), "gelu");
     st->launches += 1;
     MB_TRY(cudaMemcpyAsync(host_data, st->d_in, n * sizeof(float), cudaMemcpyDeviceToHost, st->stream),
            "device to host copy");
@@ -724,6 +839,7 @@ static int attention_common(mb_state *st, const float *q, size_t q_stride, const
     a.out_stride = heads * hw;
     a.batch = 1;
     a.strict = st->strict;
+    a.exp_tab = st->libm.exp_tab;
     a.status = st->d_status;
     if (!st->strict) {
         const size_t need = mb_attention_scratch_floats(1u, heads, valid, hw);
@@ -880,6 +996,7 @@ int mynah_b200_qmat_linear(void *state, const float *weight, const float *x, flo
         g.out_stride = n;
         g.batch = count;
         g.strict = st->strict;
+    g.tanh_tab = st->libm.tanh_tab;
         if (quantized) { g.qx = st->d_qx; g.sx = st->d_sx; }
         else g.x = act;
         MB_TRY(mb_gemv(&g, st->stream), "matrix-vector product");
@@ -1015,6 +1132,7 @@ int mynah_b200_pool_linear(void *pool, const float *dev_x, float *dev_out, char 
     g.out_stride = p->n;
     g.batch = 1;
     g.strict = st->strict;
+    g.tanh_tab = st->libm.tanh_tab;
     g.groups = p->groups;
     g.w_group_stride = p->w_stride;
     g.scale_group_stride = p->scale_stride;

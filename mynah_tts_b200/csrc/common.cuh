@@ -9,6 +9,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "libm_parity.cuh"
+
 #define MB_WARP 32
 #define MB_FULL 0xffffffffu
 
@@ -68,19 +70,20 @@ __device__ __forceinline__ int round_half_away(float v) {
 
 // tanh-form GELU of the reference's decode step (src/kernels.c:382-389):
 // 0.5*x*(1+tanhf(0.7978845608*(x+0.044715*x^3))), every operation rounded to
-// f32 in source order.  STRICT evaluates tanh in double and rounds once, which
-// agrees with a correctly rounded tanhf; the fast form uses CUDA's tanhf.
+// f32 in source order.  STRICT returns the host libm's tanhf bit for bit when
+// the correction table is given (libm_parity.cuh), else the correctly rounded
+// value; the fast form uses CUDA's tanhf.
 template <bool STRICT>
-__device__ __forceinline__ float gelu_tanh(float x) {
+__device__ __forceinline__ float gelu_tanh(float x, const uint32_t *tanh_tab) {
     const float cubic = __fmul_rn(__fmul_rn(x, x), x);
     const float c = __fmul_rn(0.7978845608f, __fadd_rn(x, __fmul_rn(0.044715f, cubic)));
-    const float t = STRICT ? (float)tanh((double)c) : tanhf(c);
+    const float t = STRICT ? mb_tanhf_host(c, tanh_tab) : tanhf(c);
     return __fmul_rn(__fmul_rn(0.5f, x), __fadd_rn(1.0f, t));
 }
 
 template <bool STRICT>
-__device__ __forceinline__ float exp_ref(float x) {
-    return STRICT ? (float)exp((double)x) : expf(x);
+__device__ __forceinline__ float exp_ref(float x, const uint32_t *exp_tab = nullptr) {
+    return STRICT ? mb_expf_host(x, exp_tab) : expf(x);
 }
 
 static inline int mb_check_launch() { return (int)cudaGetLastError(); }

@@ -370,6 +370,7 @@ static int product(mb_decoder *d, const mb_dev_weight *w, const float *bias, con
     g.n_active = d->d_n_active;
     g.epilogue = epilogue;
     g.strict = d->st->strict;
+    g.tanh_tab = d->st->libm.tanh_tab;
     if (w->qtype == MB_INT8 || w->qtype == MB_INT4) {
         g.qx = d->qx;
         g.sx = d->sx;
@@ -435,6 +436,7 @@ static int enqueue(mb_decoder *d, size_t bucket, int mode, unsigned *count) {
         a.batch = nb;
         a.n_active = d->d_n_active;
         a.strict = st->strict;
+        a.exp_tab = st->libm.exp_tab;
         a.partials = d->partials;
         a.counters = d->counters;
         a.status = d->d_status;
@@ -463,6 +465,7 @@ static int enqueue(mb_decoder *d, size_t bucket, int mode, unsigned *count) {
         a.batch = nb;
         a.n_active = d->d_n_active;
         a.strict = st->strict;
+        a.exp_tab = st->libm.exp_tab;
         a.partials = d->partials;
         a.counters = d->counters;
         a.status = d->d_status;

@@ -36,6 +36,7 @@ struct GemvP {
     const float *x;
     float *out;
     const int *n_active;
+    const uint32_t *tanh_tab;
     long n, k;
     long out_stride;
     int batch;
@@ -49,7 +50,7 @@ template <bool STRICT>
 __device__ __forceinline__ void store_out(const GemvP &p, float *out, long row, int b, float v) {
     float *dst = out + (long)b * p.out_stride + row;
     if (p.epilogue == MB_EPI_RESIDUAL) *dst = __fadd_rn(*dst, v);
-    else if (p.epilogue == MB_EPI_GELU) *dst = gelu_tanh<STRICT>(v);
+    else if (p.epilogue == MB_EPI_GELU) *dst = gelu_tanh<STRICT>(v, p.tanh_tab);
     else *dst = v;
 }
 
@@ -398,6 +399,7 @@ extern "C" int mb_gemv(const mb_gemv_args *a, mb_stream stream) {
     p.x = a->x;
     p.out = a->out;
     p.n_active = a->n_active;
+    p.tanh_tab = a->tanh_tab;
     p.n = (long)a->n;
     p.k = (long)a->k;
     p.out_stride = (long)a->out_stride;

@@ -121,9 +121,9 @@ k_quant_rows(const float *__restrict__ in, int width, int8_t *__restrict__ qx,
 }
 
 template <bool STRICT>
-__global__ void k_gelu(float *data, size_t n) {
+__global__ void k_gelu(float *data, size_t n, const uint32_t *tanh_tab) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) data[i] = gelu_tanh<STRICT>(data[i]);
+    if (i < n) data[i] = gelu_tanh<STRICT>(data[i], tanh_tab);
 }
 
 __global__ void k_residual_add(float *out, const float *in, size_t n) {
@@ -286,10 +286,10 @@ extern "C" int mb_quant_rows(const float *in, size_t rows, size_t width, int8_t 
     return mb_check_launch();
 }
 
-extern "C" int mb_gelu(float *data, size_t n, int strict, mb_stream stream) {
+extern "C" int mb_gelu(float *data, size_t n, int strict, const uint32_t *tanh_tab, mb_stream stream) {
     if (n == 0) return 0;
-    if (strict) k_gelu<true><<<blocks_for(n), 256, 0, (cudaStream_t)stream>>>(data, n);
-    else k_gelu<false><<<blocks_for(n), 256, 0, (cudaStream_t)stream>>>(data, n);
+    if (strict) k_gelu<true><<<blocks_for(n), 256, 0, (cudaStream_t)stream>>>(data, n, tanh_tab);
+    else k_gelu<false><<<blocks_for(n), 256, 0, (cudaStream_t)stream>>>(data, n, nullptr);
     return mb_check_launch();
 }
 

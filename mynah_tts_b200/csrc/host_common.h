@@ -47,6 +47,8 @@ typedef struct mb_state {
     int *d_status;
     int sm_count;
     cudaEvent_t timer0, timer1;
+    mb_libm_tables libm;             /* strict mode: host-libm correction tables */
+    int libm_exact;                  /* 1 when both tables were built */
     unsigned long long launches;
 } mb_state;
 

@@ -21,6 +21,19 @@ enum { MB_F32 = 0, MB_INT8 = 1, MB_INT4 = 2, MB_F16 = 3 };
 /* GEMV epilogues. */
 enum { MB_EPI_STORE = 0, MB_EPI_RESIDUAL = 1, MB_EPI_GELU = 2 };
 
+/* Device tables that make strict-mode expf/tanhf return the host libm's bits
+ * (libm_parity.cuh); either pointer may be NULL (then: correctly rounded). */
+typedef struct {
+    const uint32_t *tanh_tab;
+    const uint32_t *exp_tab;
+} mb_libm_tables;
+/* One run of the table build: host_vals_dev[i] is the host's tanhf(a) (or
+ * expf(-a) when is_exp) for the float a with bit pattern first_bits + i; packs
+ * count/8 words at table_words.  status gets bit 4 if a difference does not fit
+ * 4 bits. */
+int mb_libm_delta(const float *host_vals_dev, uint32_t first_bits, size_t count, int is_exp,
+                  uint32_t *table_words, int *status, mb_stream stream);
+
 /* Per-device one-time kernel attribute setup (call with the device current,
  * outside stream capture). */
 int mb_gemv_init(void);
@@ -42,7 +55,7 @@ int mb_layernorm(const float *in, float *out, const float *gain, const float *bi
 /* Per-row int8 activation quantization of f32 rows. */
 int mb_quant_rows(const float *in, size_t rows, size_t width, int8_t *qx, float *sx,
                   const int *n_active, mb_stream stream);
-int mb_gelu(float *data, size_t n, int strict, mb_stream stream);
+int mb_gelu(float *data, size_t n, int strict, const uint32_t *tanh_tab, mb_stream stream);
 int mb_residual_add(float *out, const float *in, size_t n, mb_stream stream);
 int mb_scale(float *data, size_t n, float scale, mb_stream stream);
 int mb_clip(float *data, size_t n, mb_stream stream);
@@ -90,6 +103,7 @@ typedef struct {
     const int *n_active;  /* device int or NULL */
     int epilogue;         /* MB_EPI_* */
     int strict;           /* GELU epilogue: reference-order transcendental */
+    const uint32_t *tanh_tab; /* strict GELU: host-libm correction table or NULL */
     size_t groups;        /* >1: independent problems; pointers advance by the strides below */
     size_t w_group_stride, scale_group_stride, act_group_stride, out_group_stride;
 } mb_gemv_args;
@@ -122,6 +136,7 @@ typedef struct {
     size_t batch;
     const int *n_active;
     int strict;
+    const uint32_t *exp_tab; /* strict: host-libm correction table or NULL */
     /* scratch of the chunked kernel (fast mode): mb_attention_scratch_floats()
      * floats and mb_attention_counters() counters, the counters zero before
      * first use (the kernel leaves them zero).  Launches that share scratch

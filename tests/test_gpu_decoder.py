@@ -30,6 +30,8 @@ def test_tiny_decoder_per_layer_and_kv(name, strict, tiny_model, tiny_memory):
     pm = O.PortModel(tiny_model, QT[name])
     ps = pm.new_stream(tiny_memory, 64)
     be = Backend(name, strict=strict)
+    assert be.libm_exact == strict
+    exact = strict and name in ("int8", "int4")
     dec = Decoder(be, tiny_model, capacity=64, slots=3)
     dec.slot_load(1, ps.cross_k, ps.cross_v)
     forced = synth.make_codes(shape, seed=7, frames=10)
@@ -38,9 +40,12 @@ def test_tiny_decoder_per_layer_and_kv(name, strict, tiny_model, tiny_memory):
         want = ps.step(row)
         got = dec.step_batch([1], row[None, :])[0]
         assert rel_err(got, want) < tol, (name, strict, f)
+        if exact:
+            assert np.array_equal(got, want), (name, f)
     k, v = dec.slot_read_kv(1)
-    if strict and name in ("int8",):
-        # integer products + reference-order glue: the cache is the reference's, bit for bit
+    if exact:
+        # integer products + reference-order glue + the host's libm: the cache is the
+        # reference's, bit for bit
         assert np.array_equal(k[:, :10], ps.self_k[:, :10]) and np.array_equal(v[:, :10], ps.self_v[:, :10])
     assert rel_err(k[:, :10], ps.self_k[:, :10]) < tol and rel_err(v[:, :10], ps.self_v[:, :10]) < tol
     assert not k[:, 10:].any() and not v[:, 10:].any()          # nothing written past the length
@@ -52,7 +57,10 @@ def test_tiny_decoder_per_layer_and_kv(name, strict, tiny_model, tiny_memory):
         ps.set_layers(n)
         dec.slot_set_length(1, 10)
         dec.set_layers(n)
-        assert rel_err(dec.step_batch([1], row[None, :])[0], ps.step(row)) < tol
+        got, want = dec.step_batch([1], row[None, :])[0], ps.step(row)
+        assert rel_err(got, want) < tol
+        if exact:
+            assert np.array_equal(got, want), (name, n)
     dec.close(); be.close(); ps.close(); pm.close()
 
 
@@ -67,6 +75,8 @@ def test_tiny_decoder_against_reference_fixtures(golden, tiny_model, tiny_memory
         for f in range(10):
             tokens, hidden = dec.frame_batch([0], forced[f:f + 1], [1], want_hidden=True)
             assert rel_err(hidden[0], golden[f"tiny_{name}_forced_hidden"][f]) < STRICT_TOL
+            if name != "f32":
+                assert np.array_equal(hidden[0], golden[f"tiny_{name}_forced_hidden"][f])
             assert np.array_equal(tokens[0], golden[f"tiny_{name}_forced_tokens"][f])
         dec.close(); be.close()
 
@@ -190,8 +200,8 @@ def _full_setup(seed, name, strict, capacity, slots=1):
     pm = O.PortModel(model, QT[name])
     ps = pm.new_stream(memory, 4)            # only for the cross K/V precompute
     be = Backend(name, strict=strict)
-    dec = Decoder(be, model, capacity=capacity, slots=slots)
-    for s in range(slots):
+    dec = Decoder(be, model, capacity=capacity, slots=max(slots, 2))
+    for s in range(max(slots, 2)):
         dec.slot_load(s, ps.cross_k, ps.cross_v)
     ps.close(); pm.close()
     return shape, model, start, be, dec
@@ -214,37 +224,83 @@ def test_full_greedy_512_frames_match_reference(name, seed, golden, record_prope
     record_property("first_divergence", div)
     k, v = dec.slot_read_kv(0)
     dec.close(); be.close()
+    if name != "f32":
+        import zlib
+        kv_crc = np.uint32(zlib.crc32(np.ascontiguousarray(k[:, :512]).tobytes())) ^ \
+            np.uint32(zlib.crc32(np.ascontiguousarray(v[:, :512]).tobytes()))
+        record_property("kv_crc_equal", bool(kv_crc == golden[f"full_{name}_s{seed}_kv_crc"]))
     margin = golden[f"full_{name}_s{seed}_margin"]
     assert div == -1, (f"{name} seed {seed}: token streams part at frame {div}; the reference's "
                        f"top-2 margin there is {margin[div]:.2e}")
+    if name != "f32":
+        # the whole KV cache after 512 frames is the reference's, bit for bit
+        assert kv_crc == golden[f"full_{name}_s{seed}_kv_crc"]
 
 
 @pytest.mark.parametrize("name", ["int8", "f32", "int4"])
-def test_full_hidden_states_teacher_forced(name, golden):
-    """Fast mode, teacher-forced with the reference's tokens: hidden states at
-    frames 0, 1, 63, 64, 255, 256, 511 within the mode's tolerance, and the
-    greedy pick equal to the reference's wherever its top-2 margin exceeds the
-    perturbation that tolerance allows."""
+def test_full_fast_mode_single_steps_and_picks(name, golden, record_property):
+    """Fast (production) mode on the Magpie-357M shape, teacher-forced with the
+    reference's tokens.
+
+    (a) Single steps from the reference's exact state: the strict decoder (which
+    the tests above pin to the reference bit for bit) carries the KV cache; at
+    frames 0, 1, 63, 64, 255, 256, 511 its cache is copied into the fast
+    decoder, which then runs that one frame.  The hidden row must be within the
+    mode's tolerance of the reference's.  For the quantized modes the tolerance
+    is set by activation-rounding flips: a last-bit difference in a LayerNorm
+    sum can move one int8 activation by one step, and twelve random-init layers
+    amplify that to about 1e-2 of the row.
+    (b) Greedy picks of the fast decoder running all 512 frames on its own
+    cache: equal to the reference's wherever the reference's top-2 margin
+    exceeds what that hidden-state tolerance can move a logit by; the drift of
+    the hidden rows is recorded."""
     seed = 21
     shape, model, start, be, dec = _full_setup(seed, name, False, 520)
+    _, _, _, sbe, sdec = _full_setup(seed, name, True, 520)
     want_tokens = golden[f"full_{name}_s{seed}_tokens"].astype(np.uint32)
     want_hidden = golden[f"full_{name}_s{seed}_hidden"]
     margin = golden[f"full_{name}_s{seed}_margin"]
     keep = (0, 1, 63, 64, 255, 256, 511)
+    tol = {"f32": 1e-3, "int8": 2e-2, "int4": 2e-2}[name]
     codes = start.copy()
-    worst, disagree_wide = 0.0, 0
-    # a hidden row off by tol moves a logit by about tol * |h| * |w| = tol * 28 * 0.55
-    eps = FAST_TOL[name] * 16.0
+    single, drift, disagree_wide = [], 0.0, 0
+    # a hidden row off by tol moves a logit by about tol * |h| * |w| * sqrt(width)/sqrt(width)
+    eps = tol * 16.0
     for f in range(512):
+        if f in keep:
+            k, v = sdec.slot_read_kv(0)
+            dec.slot_load(1, golden_cross(sdec, be, model, seed)[0], golden_cross(sdec, be, model, seed)[1],
+                          k, v, length=f)
+            _, h1 = dec.frame_batch([1], codes, [0], want_hidden=True)
+            single.append(rel_err(h1[0], want_hidden[keep.index(f)]))
+        sdec.frame_batch([0], codes, [0])
         tokens, hidden = dec.frame_batch([0], codes, [0], want_hidden=True)
         if f in keep:
-            worst = max(worst, rel_err(hidden[0], want_hidden[keep.index(f)]))
+            drift = max(drift, rel_err(hidden[0], want_hidden[keep.index(f)]))
         if not np.array_equal(tokens[0], want_tokens[f]) and margin[f] > eps:
             disagree_wide += 1
         codes = np.where(want_tokens[f] < shape.codebook_size, want_tokens[f], 0).astype(np.uint32)[None, :]
-    dec.close(); be.close()
-    assert worst < FAST_TOL[name], worst
+    dec.close(); be.close(); sdec.close(); sbe.close()
+    record_property("single_step_rel_err", [float(x) for x in single])
+    record_property("drift_rel_err", drift)
+    print(f"{name}: single-step errors {single}, drift over 512 frames {drift:.3e}")
+    assert max(single) < tol, single
+    assert drift < 5e-2
     assert disagree_wide == 0
+
+
+_cross_cache = {}
+
+
+def golden_cross(sdec, be, model, seed):
+    """Cross K/V of the request (CPU precompute of decoder_cache_init, cached)."""
+    if seed not in _cross_cache:
+        shape = synth.MAGPIE_357M
+        pm = O.PortModel(model, O.F32)
+        ps = pm.new_stream(synth.make_memory(shape, seed=seed + 100), 4)
+        _cross_cache[seed] = (ps.cross_k.copy(), ps.cross_v.copy())
+        ps.close(); pm.close()
+    return _cross_cache[seed]
 
 
 def test_full_size_properties_64_streams(golden):
