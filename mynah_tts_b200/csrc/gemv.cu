@@ -16,7 +16,8 @@
 // (a power of two dividing the chunk count) share one row, so every warp-wide
 // load instruction reads whole contiguous 16-byte pieces of 32/LPR consecutive
 // rows.  Activations of a tile of BT streams are staged in shared memory once
-// per CTA; the weight stream is read once per batch tile.
+// per CTA; batch tiles are spread over grid.z (the weight stream is read once per
+// tile, from L2 after the first).
 #include "common.cuh"
 #include "launch.h"
 
@@ -78,8 +79,8 @@ __global__ void __launch_bounds__(WARPS * 32) k_gemv(GemvP p) {
     float *pbuf = reinterpret_cast<float *>(smem + (size_t)BT * act_bytes);  // int4 only
     const unsigned char *wrow = w + (row_ok ? row : 0) * p.row_bytes;
 
-    for (int b0 = 0; b0 < nb; b0 += BT) {
-        __syncthreads();
+    // one batch tile per CTA (grid.z): tiles past the live lanes leave at once
+    for (int b0 = blockIdx.z * BT; b0 < nb; b0 = nb) {
         // ---- stage the activation tile ------------------------------------
         if (QUANT) {
             const int8_t *src = p.qx + grp * p.act_gs;
@@ -335,7 +336,7 @@ int launch_tiled(const GemvP &p, size_t groups, cudaStream_t s) {
     size_t smem = (size_t)BT * (quant ? p.k : p.k * 4);
     if (QT == MB_INT4) smem += (size_t)WARPS * 32 * p.cpl * BT * sizeof(float);
     if (smem > 160u * 1024u) return (int)cudaErrorInvalidValue;
-    k_gemv<QT, BT, STRICT><<<dim3(blocks, (unsigned)groups), WARPS * 32, smem, s>>>(p);
+    k_gemv<QT, BT, STRICT><<<dim3(blocks, (unsigned)groups, (unsigned)((p.batch + BT - 1) / BT)), WARPS * 32, smem, s>>>(p);
     return mb_check_launch();
 }
 
