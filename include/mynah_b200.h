@@ -286,6 +286,26 @@ int mynah_b200_decoder_profile_read(void *decoder, unsigned long long *launches,
                                     size_t n, char *error, size_t cap);
 const char *mynah_b200_profile_class_name(size_t cls);
 
+/* No counterpart in the reference.  Self-attention with the contract of
+ * mynah_cuda_self_attention_dev for callers that are not allowed to allocate
+ * device memory (a real-time audio thread, a plugin living in a host whose
+ * memory pool is not its own, a context that must not grow): it takes no
+ * backend state and never calls cudaMalloc/cudaFree or any allocating routine.
+ * The kernel's scratch (per-chunk partial results, one merged row, arrival
+ * counters) sits in a fixed ~590 KB array inside the library image that every
+ * GPU loading the library holds until the process exits.
+ * Limits: at most 4096 attended rows, heads*head_width <= 1024, <= 64 heads,
+ * head_width a power-of-two multiple of 4 up to 128, 16-byte aligned buffers;
+ * anything else is refused with a message.  The first call on a device looks
+ * up the array's device address (cudaGetSymbolAddress); make that first call
+ * before any stream capture.  All calls share the one array: calls that overlap
+ * on the GPU race, so serialize them.  cuda_stream is a cudaStream_t (may be
+ * NULL); the work is enqueued, not synchronized. */
+int mynah_b200_self_attention_static(const float *dev_qkv, float *dev_k_cache, float *dev_v_cache,
+                                     size_t position, size_t cache_stride, size_t valid,
+                                     size_t heads, size_t head_width, float scale, float *dev_out,
+                                     void *cuda_stream, char *error, size_t cap);
+
 #pragma GCC visibility pop
 #ifdef __cplusplus
 }

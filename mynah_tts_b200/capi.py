@@ -141,6 +141,8 @@ SIGNATURES = {
     "mynah_b200_decoder_profile_read": (C.c_int, [C.c_void_p, C.POINTER(C.c_ulonglong),
                                                   C.POINTER(C.c_double), sz, _E]),
     "mynah_b200_profile_class_name": (C.c_char_p, [sz]),
+    "mynah_b200_self_attention_static": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, sz, sz, sz, sz, sz,
+                                                   C.c_float, C.c_void_p, C.c_void_p, _E]),
     "mynah_b200_decoder_weight_bytes": (sz, [C.c_void_p]),
     "mynah_b200_decoder_kv_bytes": (sz, [C.c_void_p, sz]),
 }

@@ -25,6 +25,8 @@
 #include "launch.h"
 
 #include <float.h>
+#include <stdio.h>
+#include <string.h>
 
 namespace {
 
@@ -474,4 +476,135 @@ extern "C" int mb_attention(const mb_attn_args *a, mb_stream stream) {
     if (rc == 0 && a->qx != nullptr)
         rc = mb_quant_rows(a->out, a->batch, width, a->qx, a->sx, a->n_active, stream);
     return rc;
+}
+
+// ---------------------------------------------------------------------------
+// Allocation-free self-attention for callers that must not allocate.
+//
+// Some hosts of this library run where device allocation is off the table: a
+// real-time audio thread that may not block in the allocator, a plugin loaded
+// into a process whose memory pool is owned by someone else, or code that runs
+// under a CUDA context it is not allowed to grow.  For them the split-position
+// kernel's scratch (per-chunk partial results, one merged row, arrival
+// counters) lives in the fixed array below instead of in memory obtained with
+// cudaMalloc.  Every GPU that loads this library holds the array until the
+// process exits.
+//
+// Limits: one stream per call, at most MB_STATIC_MAX_VALID attended rows and
+// heads * head_width <= MB_STATIC_MAX_WIDTH; head_width a power-of-two multiple
+// of 4 up to 128 and 16-byte aligned buffers (the chunked kernel's shapes).
+// Every call uses the same array, so two calls that overlap on the GPU (two
+// streams, two threads) race; serialize them.  The array keeps the previous
+// call's partial results, which are always rewritten before they are read; the
+// counters must start at zero and are cleared at the start of each call.
+#define MB_STATIC_MAX_VALID 4096u
+#define MB_STATIC_MAX_WIDTH 1024u
+#define MB_STATIC_MAX_HEADS 64u
+#define MB_STATIC_MAX_DEVICES 16
+// chunks * (width + 2 * heads) partial floats + one merged row, then the counters
+#define MB_STATIC_FLOATS ((MB_STATIC_MAX_VALID / 32u) * (MB_STATIC_MAX_WIDTH + 2u * MB_STATIC_MAX_HEADS) + MB_STATIC_MAX_WIDTH)
+#define MB_STATIC_COUNTERS (MB_STATIC_MAX_HEADS + 1u)
+#define MB_STATIC_BYTES (MB_STATIC_FLOATS * 4u + MB_STATIC_COUNTERS * 4u)
+
+static __device__ __align__(256) unsigned char g_attention_static_scratch[MB_STATIC_BYTES];
+
+// Device address of the array on each device, resolved on first use there.  In
+// host code the array's name is only a handle; a kernel must be given the
+// address cudaGetSymbolAddress returns for the current device.
+static void *g_static_scratch_addr[MB_STATIC_MAX_DEVICES];
+
+static void static_error(char *error, size_t cap, const char *message) {
+    if (error != nullptr && cap > 0) snprintf(error, cap, "%s", message);
+}
+
+// Same contract as mynah_cuda_self_attention_dev (append K/V of dev_qkv at
+// `position`, attend rows below `valid`, `heads` heads of `head_width`), but
+// state-free and allocation-free: no cudaMalloc, cudaFree or allocating library
+// call is made, here or on any later call.  The first call on a device
+// resolves the scratch array's device address; make that first call outside
+// stream capture.  Work is enqueued on `cuda_stream` (a cudaStream_t, may be
+// 0) and is not synchronized.  Returns 0, or -1 with a message.
+extern "C" __attribute__((visibility("default")))
+int mynah_b200_self_attention_static(const float *dev_qkv, float *dev_k_cache, float *dev_v_cache,
+                                     size_t position, size_t cache_stride, size_t valid,
+                                     size_t heads, size_t head_width, float scale, float *dev_out,
+                                     void *cuda_stream, char *error, size_t cap) {
+    if (dev_qkv == nullptr || dev_k_cache == nullptr || dev_v_cache == nullptr || dev_out == nullptr ||
+        heads == 0 || head_width == 0 || valid == 0 || cache_stride < heads * head_width) {
+        static_error(error, cap, "invalid attention request");
+        return -1;
+    }
+    const size_t width = heads * head_width;
+    if (valid > MB_STATIC_MAX_VALID || width > MB_STATIC_MAX_WIDTH || heads > MB_STATIC_MAX_HEADS) {
+        if (error != nullptr && cap > 0)
+            snprintf(error, cap,
+                     "request exceeds the static scratch: at most %u rows, width %u, %u heads",
+                     MB_STATIC_MAX_VALID, MB_STATIC_MAX_WIDTH, MB_STATIC_MAX_HEADS);
+        return -1;
+    }
+    const bool shape_ok = (head_width % 4) == 0 && is_pow2((long)head_width / 4) && head_width <= 128 &&
+                          (cache_stride % 4) == 0 && (width % 4) == 0 && width <= (size_t)CHUNK * head_width &&
+                          (((uintptr_t)dev_k_cache | (uintptr_t)dev_v_cache | (uintptr_t)dev_qkv) & 15u) == 0;
+    if (!shape_ok) {
+        static_error(error, cap, "head width must be a power-of-two multiple of 4 up to 128 and buffers 16-byte aligned");
+        return -1;
+    }
+    int device = -1;
+    cudaError_t rc = cudaGetDevice(&device);
+    if (rc != cudaSuccess || device < 0 || device >= MB_STATIC_MAX_DEVICES) {
+        static_error(error, cap, rc != cudaSuccess ? cudaGetErrorString(rc) : "device ordinal out of range");
+        return -1;
+    }
+    if (g_static_scratch_addr[device] == nullptr) {
+        void *addr = nullptr;
+        rc = cudaGetSymbolAddress(&addr, g_attention_static_scratch);
+        if (rc != cudaSuccess || addr == nullptr) {
+            static_error(error, cap, rc != cudaSuccess ? cudaGetErrorString(rc) : "no address for the static scratch");
+            return -1;
+        }
+        g_static_scratch_addr[device] = addr;
+    }
+    float *scratch = static_cast<float *>(g_static_scratch_addr[device]);
+    unsigned *counters = reinterpret_cast<unsigned *>(scratch + MB_STATIC_FLOATS);
+    cudaStream_t s = (cudaStream_t)cuda_stream;
+    rc = cudaMemsetAsync(counters, 0, MB_STATIC_COUNTERS * sizeof(unsigned), s);
+    if (rc != cudaSuccess) {
+        static_error(error, cap, cudaGetErrorString(rc));
+        return -1;
+    }
+    AttnP p;
+    memset(&p, 0, sizeof(p));
+    p.q = dev_qkv;
+    p.k_new = dev_qkv + width;
+    p.v_new = dev_qkv + 2 * width;
+    p.k_cache = dev_k_cache;
+    p.v_cache = dev_v_cache;
+    p.out = dev_out;
+    p.partials = scratch;
+    p.counters = counters;
+    p.q_stride = (long)(3 * width);
+    p.cache_stride = (long)cache_stride;
+    p.out_stride = (long)width;
+    p.position = (long)position;
+    p.valid = (long)valid;
+    p.heads = (int)heads;
+    p.hw = (int)head_width;
+    p.batch = 1;
+    p.max_chunks = (int)chunks_for(valid);
+    p.scale = scale;
+    const int groups = FAST_THREADS / (p.hw / 4);
+    const size_t floats = (size_t)p.hw + 2u * CHUNK * p.hw + CHUNK + (size_t)groups * p.hw;
+    if (floats * sizeof(float) > 48u * 1024u || (size_t)p.max_chunks > (size_t)groups * p.hw) {
+        static_error(error, cap, "shape needs more shared memory than the allocation-free path uses");
+        return -1;
+    }
+    dim3 grid((unsigned)p.max_chunks, (unsigned)p.heads, 1u);
+    k_attn_chunk<<<grid, FAST_THREADS, floats * sizeof(float), s>>>(p);
+    rc = cudaGetLastError();
+    if (rc != cudaSuccess) {
+        static_error(error, cap, cudaGetErrorString(rc));
+        return -1;
+    }
+    if (error != nullptr && cap > 0) error[0] = '\0';
+    return 0;
 }
