@@ -191,6 +191,13 @@ void mynah_b200_pool_destroy(void *pool);
 int mynah_b200_pool_linear(void *pool, const float *dev_x, float *dev_out, char *error, size_t cap);
 size_t mynah_b200_pool_bytes_per_pass(const void *pool);
 
+/* Diagnostic: mean device time (microseconds) of one int8 product
+ * out[batch,n] = qx[batch,k] W[n,k]^T launched `iters` times back to back on
+ * resident synthetic data; path 0 = SIMT kernel, 1 = tensor-core kernel
+ * (batch >= 16); epilogue 0 store, 1 residual add, 2 GELU. */
+int mynah_b200_time_product(void *state, size_t n, size_t k, size_t batch, int path, int epilogue,
+                            size_t iters, float *us_per_launch, char *error, size_t cap);
+
 /* ---- whole-step decoder --------------------------------------------------- */
 /* Host weight pointers of one decoder layer, in the order of
  * decoder_layer_resolved (src/graph.c:2795-2804). */

@@ -119,6 +119,7 @@ SIGNATURES = {
     "mynah_b200_quantize_act": (C.c_int, [C.c_void_p, c_float_p, sz, sz, C.c_void_p, c_float_p, _E]),
     "mynah_b200_qmat_linear": (C.c_int, [C.c_void_p, c_float_p, c_float_p, c_float_p, sz, sz, sz,
                                          c_float_p, c_float_p, _E]),
+    "mynah_b200_time_product": (C.c_int, [C.c_void_p, sz, sz, sz, C.c_int, C.c_int, sz, c_float_p, _E]),
     "mynah_b200_pool_create": (C.c_int, [C.c_void_p, c_float_p, sz, sz, sz, c_float_p, c_float_p,
                                          C.POINTER(C.c_void_p), _E]),
     "mynah_b200_pool_destroy": (None, [C.c_void_p]),

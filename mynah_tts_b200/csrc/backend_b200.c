@@ -316,6 +316,7 @@ int mynah_b200_open(void **state, int device, int quant, int strict, char *error
                 "cudaStreamCreate", error, cap) != 0 ||
         mb_cuda(mb_gemv_init(), "kernel attributes (gemv)", error, cap) != 0 ||
         mb_cuda(mb_attention_init(), "kernel attributes (attention)", error, cap) != 0 ||
+        mb_cuda(mb_gemm_tc_init(), "kernel attributes (tensor-core product)", error, cap) != 0 ||
         mb_cuda((int)cudaMalloc((void **)&st->d_token, sizeof(unsigned)), "cudaMalloc", error, cap) != 0 ||
         mb_cuda((int)cudaMalloc((void **)&st->d_status, sizeof(int)), "cudaMalloc", error, cap) != 0 ||
         mb_cuda((int)cudaMemset(st->d_status, 0, sizeof(int)), "cudaMemset", error, cap) != 0) {
@@ -1142,6 +1143,54 @@ int mynah_b200_pool_linear(void *pool, const float *dev_x, float *dev_out, char 
     else g.x = act;
     MB_TRY(mb_gemv(&g, st->stream), "matrix-vector product");
     st->launches += 1;
+    mb_clear_error(error, cap);
+    return 0;
+}
+
+/* ---------------------------------------------------------------- diagnostics */
+/* Time one int8 product shape in isolation: `iters` back-to-back launches on the
+ * backend's stream between two events, weights and activations resident.  path:
+ * 0 = SIMT kernel, 1 = tensor-core kernel.  Returns the mean device time per
+ * launch in microseconds. */
+int mynah_b200_time_product(void *state, size_t n, size_t k, size_t batch, int path, int epilogue,
+                            size_t iters, float *us_per_launch, char *error, size_t cap) {
+    SEAM_PROLOGUE();
+    if (n == 0 || k == 0 || batch == 0 || iters == 0 || us_per_launch == NULL) return -1;
+    int8_t *w = NULL, *qx = NULL;
+    float *scales = NULL, *sx = NULL, *out = NULL;
+    cudaEvent_t e0 = NULL, e1 = NULL;
+    int rc = (int)cudaMalloc((void **)&w, n * k);
+    if (rc == 0) rc = (int)cudaMalloc((void **)&qx, batch * k);
+    if (rc == 0) rc = (int)cudaMalloc((void **)&scales, n * sizeof(float));
+    if (rc == 0) rc = (int)cudaMalloc((void **)&sx, batch * sizeof(float));
+    if (rc == 0) rc = (int)cudaMalloc((void **)&out, batch * n * sizeof(float));
+    if (rc == 0) rc = (int)cudaMemset(w, 1, n * k);
+    if (rc == 0) rc = (int)cudaMemset(qx, 1, batch * k);
+    if (rc == 0) rc = (int)cudaMemset(scales, 0, n * sizeof(float));
+    if (rc == 0) rc = (int)cudaMemset(sx, 0, batch * sizeof(float));
+    if (rc == 0) rc = (int)cudaMemset(out, 0, batch * n * sizeof(float));
+    if (rc == 0) rc = (int)cudaEventCreate(&e0);
+    if (rc == 0) rc = (int)cudaEventCreate(&e1);
+    mb_gemv_args g;
+    memset(&g, 0, sizeof(g));
+    g.qtype = MB_INT8; g.w = w; g.scales = scales; g.n = n; g.k = k; g.qx = qx; g.sx = sx;
+    g.out = out; g.out_stride = n; g.batch = batch; g.epilogue = epilogue;
+    for (size_t i = 0; i < iters + 3 && rc == 0; ++i) {
+        if (i == 3) rc = (int)cudaEventRecord(e0, st->stream);
+        if (rc == 0)
+            rc = path == 1 ? mb_gemm_tc(&g, batch, st->d_status, st->stream)
+                           : mb_gemv(&g, st->stream);
+    }
+    if (rc == 0) rc = (int)cudaEventRecord(e1, st->stream);
+    if (rc == 0) rc = (int)cudaEventSynchronize(e1);
+    float ms = 0.0f;
+    if (rc == 0) rc = (int)cudaEventElapsedTime(&ms, e0, e1);
+    st->launches += iters + 3;
+    cudaFree(w); cudaFree(qx); cudaFree(scales); cudaFree(sx); cudaFree(out);
+    if (e0 != NULL) cudaEventDestroy(e0);
+    if (e1 != NULL) cudaEventDestroy(e1);
+    if (rc != 0) return mb_cuda(rc, "time product", error, cap);
+    *us_per_launch = ms * 1000.0f / (float)iters;
     mb_clear_error(error, cap);
     return 0;
 }

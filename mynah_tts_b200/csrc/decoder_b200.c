@@ -43,6 +43,7 @@ typedef struct mb_decoder {
     float *sx;
     float *partials;
     unsigned *counters;
+    int use_tc;
     /* lane state */
     int *d_lens, *d_slots, *d_n_active, *d_allow_eos, *d_eos_flag, *d_eos_frame, *d_frame_idx, *d_status;
     int *d_min_frames;
@@ -304,6 +305,10 @@ int mynah_b200_decoder_create(void *state, const mynah_b200_decoder_desc *desc, 
     const size_t cross_floats = mb_attention_scratch_floats(MB, 1u, d->T, XW);
     if (cross_floats > partial_floats) partial_floats = cross_floats;
     const size_t n_counters = mb_attention_counters(MB, d->heads);
+    {
+        const char *no_tc = getenv("MYNAH_B200_NO_TC");
+        d->use_tc = !(no_tc != NULL && strcmp(no_tc, "0") != 0);
+    }
     D_TRY(dmalloc((void **)&d->partials, partial_floats * sizeof(float), error, cap));
     D_TRY(dmalloc((void **)&d->counters, n_counters * sizeof(unsigned), error, cap));
     int **ints[] = {&d->d_lens, &d->d_slots, &d->d_allow_eos, &d->d_eos_flag, &d->d_eos_frame};
@@ -378,6 +383,8 @@ static int product(mb_decoder *d, const mb_dev_weight *w, const float *bias, con
         g.x = act_f32;
     }
     *count += 1u;
+    if (d->use_tc && mb_gemm_tc_supported(w->qtype, w->n, w->k, nb))
+        return mb_gemm_tc(&g, d->max_batch, d->d_status, d->st->stream);
     return mb_gemv(&g, d->st->stream);
 }
 

@@ -1,0 +1,289 @@
+// Batched int8 weight products on the 5th-generation tensor cores (tcgen05).
+//
+//   out[b][r] = epilogue( (sum_k W[r][k] * qx[b][k]) * scales[r] * sx[b] + bias[r] )
+//
+// for 16 or more streams stepped together: one pass over the weight serves every
+// lane (the weight-stationary batching of src/qmat.c:681-735 in mynah-tts).  The
+// sum is an exact int32, so the result has the same bits as the SIMT kernel in
+// gemv.cu and as the reference, whatever the batch.
+//
+// One CTA = one tile of 128 weight rows x BN lanes over a range of K:
+//   * TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast) brings
+//     [128 rows x 128 K-bytes] of W and [BN lanes x 128 K-bytes] of the quantized
+//     activations into shared memory, one stage per 128-byte K chunk, each
+//     stage completing on its own mbarrier;
+//   * one thread issues tcgen05.mma kind::i8 (M=128, N=BN, K=32), four per
+//     stage, accumulating int32 in tensor memory (TMEM);
+//   * after tcgen05.commit signals completion, the four warps read their 32 TMEM
+//     lanes (= weight rows) with tcgen05.ld and apply the epilogue.
+// Grid: (row tiles, lane tiles).  A CTA walks the whole K range through a ring of
+// eight stages: a stage is refilled as soon as tcgen05.commit reports that the
+// MMAs reading it have finished.  (Splitting K across CTAs with integer atomics
+// was measured at twice the time of an unsplit launch and was dropped.)
+//
+// Every wait is bounded: if a barrier does not complete within the limit the
+// CTA raises a status bit, waits once more for its copies, frees its TMEM and
+// returns.
+#include "common.cuh"
+#include "launch.h"
+
+#include <cuda.h>
+
+namespace {
+
+constexpr int TC_THREADS = 128;
+constexpr int TM = 128;             // weight rows per tile (MMA M)
+constexpr int BN = 16;              // lanes per tile (MMA N)
+constexpr int KC = 128;             // K bytes per stage (one swizzle row)
+constexpr int MAX_STAGES = 8;
+constexpr int A_BYTES = TM * KC;    // 16 KB
+constexpr int B_BYTES = BN * KC;    // 2 KB
+constexpr int TMEM_COLS = 32;       // smallest allocation; BN <= 32 columns used
+constexpr unsigned TC_SPIN = 1u << 24;
+
+struct TcP {
+    const float *scales, *bias, *sx;
+    float *out;
+    const int *n_active;
+    int *status;
+    const uint32_t *tanh_tab;
+    long n, k, out_stride;
+    int batch, epilogue, strict;
+};
+
+__device__ __forceinline__ unsigned saddr(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void bar_init(void *bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(saddr(bar)), "r"(count));
+}
+__device__ __forceinline__ void bar_expect(void *bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(saddr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool bar_wait(void *bar, unsigned parity, unsigned limit) {
+    for (unsigned i = 0; i < limit; ++i) {
+        unsigned done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(saddr(bar)), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, void *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3}], [%4];" ::"r"(saddr(dst)), "l"(map), "r"(x), "r"(y), "r"(saddr(bar))
+        : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of
+// 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_sw128(unsigned addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3ffffu) >> 4);          // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                           // leading byte offset (unused with swizzle)
+    d |= (uint64_t)(1024u >> 4) << 32;                // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                           // descriptor version of this architecture
+    d |= (uint64_t)2 << 61;                           // 128-byte swizzle
+    return d;
+}
+// Instruction descriptor: int32 accumulate, signed 8-bit A and B, both K-major.
+__device__ __forceinline__ uint32_t instr_desc_i8(int m, int n) {
+    return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void mma_i8(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void mma_commit(void *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(saddr(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, int (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__global__ void __launch_bounds__(TC_THREADS)
+k_gemm_i8_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcP p) {
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) unsigned long long full_bar[MAX_STAGES];
+    __shared__ __align__(8) unsigned long long empty_bar[MAX_STAGES];
+    __shared__ __align__(8) unsigned long long done_bar;
+    __shared__ uint32_t s_tmem;
+    __shared__ unsigned s_fail;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nb = p.n_active != nullptr ? min(p.batch, *p.n_active) : p.batch;
+    const int b0 = blockIdx.y * BN;
+    if (b0 >= nb) return;                                   // whole CTA: no live lane in this tile
+    const long m0 = (long)blockIdx.x * TM;
+    const int nchunks = (int)((p.k + KC - 1) / KC);
+    // operands need 1024-byte alignment for the 128-byte swizzle
+    unsigned char *base = smem_raw + ((1024u - (saddr(smem_raw) & 1023u)) & 1023u);
+    unsigned char *As = base;                               // [stage][128 rows][128 B]
+    unsigned char *Bs = base + (size_t)MAX_STAGES * A_BYTES; // [stage][BN rows][128 B]
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < MAX_STAGES; ++s) {
+            bar_init(&full_bar[s], 1u);
+            bar_init(&empty_bar[s], 1u);
+        }
+        bar_init(&done_bar, 1u);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        s_fail = 0u;
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(saddr(&s_tmem)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = s_tmem;
+
+    if (warp == 0 && lane == 0) {
+        // producer: chunk c goes to stage c % 8 once the MMAs of chunk c - 8 released it
+        for (int c = 0; c < nchunks; ++c) {
+            const int s = c % MAX_STAGES;
+            if (c >= MAX_STAGES && !bar_wait(&empty_bar[s], (unsigned)((c / MAX_STAGES - 1) & 1), TC_SPIN)) {
+                s_fail = 1u;
+                if (p.status != nullptr) atomicOr(p.status, 8);
+                break;
+            }
+            bar_expect(&full_bar[s], (unsigned)(A_BYTES + B_BYTES));
+            tma_load_2d(As + (size_t)s * A_BYTES, &map_w, c * KC, (int)m0, &full_bar[s]);
+            tma_load_2d(Bs + (size_t)s * B_BYTES, &map_x, c * KC, b0, &full_bar[s]);
+        }
+    } else if (warp == 1 && lane == 0) {
+        const uint32_t idesc = instr_desc_i8(TM, BN);
+        for (int c = 0; c < nchunks; ++c) {
+            const int s = c % MAX_STAGES;
+            if (!bar_wait(&full_bar[s], (unsigned)((c / MAX_STAGES) & 1), TC_SPIN)) {
+                s_fail = 1u;
+                if (p.status != nullptr) atomicOr(p.status, 8);
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint64_t da = smem_desc_sw128(saddr(As + (size_t)s * A_BYTES));
+            const uint64_t db = smem_desc_sw128(saddr(Bs + (size_t)s * B_BYTES));
+#pragma unroll
+            for (int kk = 0; kk < KC / 32; ++kk)          // 32 K-bytes per instruction: +2 in 16-byte units
+                mma_i8(tmem, da + 2u * kk, db + 2u * kk, idesc, (c | kk) != 0 ? 1u : 0u);
+            mma_commit(&empty_bar[s]);                       // stage s is free once these MMAs are done
+        }
+        mma_commit(&done_bar);                               // arrives when every MMA above has finished
+    }
+    // scale and bias of this thread's row, fetched while the tensor cores work
+    const long row = m0 + warp * 32 + lane;
+    const bool row_ok = row < p.n;
+    const float ws = row_ok ? __ldg(p.scales + row) : 0.0f;
+    const float bias = (row_ok && p.bias != nullptr) ? __ldg(p.bias + row) : 0.0f;
+    const bool done = bar_wait(&done_bar, 0u, TC_SPIN);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    __syncthreads();
+    const bool good = done && s_fail == 0u;
+    if (!done && threadIdx.x == 0 && p.status != nullptr) atomicOr(p.status, 16);
+    if (!good) {
+        // a wait ran out: give copies still in flight one more bounded chance to land
+        // before this CTA's shared memory is released
+        if (threadIdx.x == 0)
+            for (int s = 0; s < MAX_STAGES && s < nchunks; ++s) bar_wait(&full_bar[s], 0u, TC_SPIN >> 4);
+    } else {
+        int v[16];
+        tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16), v);
+        if (row_ok) {
+#pragma unroll
+            for (int j = 0; j < BN; ++j) {
+                const int b = b0 + j;
+                if (b < nb) {
+                    float y = __fmul_rn(__fmul_rn((float)v[j], ws), p.sx[b]);
+                    if (p.bias != nullptr) y = __fadd_rn(y, bias);
+                    float *dst = p.out + (long)b * p.out_stride + row;
+                    if (p.epilogue == MB_EPI_RESIDUAL) *dst = __fadd_rn(*dst, y);
+                    else if (p.epilogue == MB_EPI_GELU)
+                        *dst = p.strict ? gelu_tanh<true>(y, p.tanh_tab) : gelu_tanh<false>(y, nullptr);
+                    else *dst = y;
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+}
+
+typedef CUresult (*encode_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                              const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                              CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                              CUtensorMapFloatOOBfill);
+
+encode_fn get_encoder() {
+    static encode_fn fn = nullptr;
+    if (fn == nullptr) {
+        void *sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<encode_fn>(sym);
+    }
+    return fn;
+}
+
+// [rows][k] bytes, row-major; box = 128 K-bytes x box_rows rows, 128-byte swizzle,
+// out-of-range elements read as zero.
+bool make_map(CUtensorMap *map, const void *ptr, size_t rows, size_t k, unsigned box_rows) {
+    encode_fn enc = get_encoder();
+    if (enc == nullptr) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)k};
+    cuuint32_t box[2] = {(cuuint32_t)KC, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(ptr), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+constexpr size_t TC_SMEM = (size_t)MAX_STAGES * (A_BYTES + B_BYTES) + 1024;
+
+}  // namespace
+
+extern "C" int mb_gemm_tc_init(void) {
+    return (int)cudaFuncSetAttribute(k_gemm_i8_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM);
+}
+
+// Shapes the tensor-core path takes: int8 weights, k a multiple of 16 (TMA row
+// stride), 16-byte aligned operands.
+extern "C" int mb_gemm_tc_supported(int qtype, size_t n, size_t k, size_t batch) {
+    return qtype == MB_INT8 && n > 0 && batch >= 16 && k >= 16 && (k % 16u) == 0;
+}
+
+// qx_rows_alloc: rows the activation buffer really holds (>= batch), so a lane
+// tile never reads past the allocation.
+extern "C" int mb_gemm_tc(const mb_gemv_args *a, size_t qx_rows_alloc, int *status, mb_stream stream) {
+    if (a == nullptr || !mb_gemm_tc_supported(a->qtype, a->n, a->k, a->batch) || a->qx == nullptr ||
+        a->sx == nullptr || a->scales == nullptr || a->out == nullptr ||
+        (((uintptr_t)a->w | (uintptr_t)a->qx) & 15u) != 0)
+        return (int)cudaErrorInvalidValue;
+    CUtensorMap map_w, map_x;
+    if (!make_map(&map_w, a->w, a->n, a->k, TM) ||
+        !make_map(&map_x, a->qx, qx_rows_alloc > a->batch ? qx_rows_alloc : a->batch, a->k, BN))
+        return (int)cudaErrorInvalidValue;
+    TcP p;
+    p.scales = a->scales; p.bias = a->bias; p.sx = a->sx; p.out = a->out;
+    p.n_active = a->n_active; p.status = status;
+    p.tanh_tab = a->tanh_tab;
+    p.n = (long)a->n; p.k = (long)a->k; p.out_stride = (long)a->out_stride;
+    p.batch = (int)a->batch; p.epilogue = a->epilogue; p.strict = a->strict;
+    const unsigned m_tiles = (unsigned)((a->n + TM - 1) / TM);
+    const unsigned b_tiles = (unsigned)((a->batch + BN - 1) / BN);
+    k_gemm_i8_tc<<<dim3(m_tiles, b_tiles), TC_THREADS, TC_SMEM, (cudaStream_t)stream>>>(map_w, map_x, p);
+    return mb_check_launch();
+}
