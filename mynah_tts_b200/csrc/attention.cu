@@ -60,6 +60,8 @@ __device__ __forceinline__ bool lane_setup(const AttnP &p, int b, long &pos, lon
 
 // ------------------------------------------------------------------ strict
 __global__ void __launch_bounds__(256) k_attn_strict(AttnP p) {
+    mb_pdl_wait();
+    mb_pdl_trigger();
     extern __shared__ float sm[];
     __shared__ float red[33];
     __shared__ float s_denom;
@@ -174,6 +176,8 @@ __device__ __forceinline__ void quantize_shared_row(const float *vals, int width
 }
 
 __global__ void __launch_bounds__(FAST_THREADS) k_attn_chunk(AttnP p) {
+    mb_pdl_wait();
+    mb_pdl_trigger();
     extern __shared__ __align__(16) float sm[];
     __shared__ float red[33];
     __shared__ float s_ml[2];
@@ -350,6 +354,8 @@ __global__ void __launch_bounds__(FAST_THREADS) k_attn_chunk(AttnP p) {
 // Shapes the chunked kernel cannot take (head width not a power-of-two multiple
 // of 4, or unaligned rows): one CTA per (head, stream), plain loads, no split.
 __global__ void __launch_bounds__(FAST_THREADS) k_attn_scalar(AttnP p) {
+    mb_pdl_wait();
+    mb_pdl_trigger();
     extern __shared__ __align__(16) float sm[];
     __shared__ float red[33];
     const int h = blockIdx.x, b = blockIdx.y;
@@ -463,15 +469,15 @@ extern "C" int mb_attention(const mb_attn_args *a, mb_stream stream) {
         if (floats * sizeof(float) > 200u * 1024u || (size_t)p.max_chunks > (size_t)groups * p.hw)
             return (int)cudaErrorInvalidValue;
         dim3 grid((unsigned)p.max_chunks, (unsigned)p.heads, (unsigned)p.batch);
-        k_attn_chunk<<<grid, FAST_THREADS, floats * sizeof(float), s>>>(p);
+        mb_launch(k_attn_chunk, dim3(grid), dim3(FAST_THREADS), floats * sizeof(float), s, p);
         return mb_check_launch();
     }
     if (a->out == nullptr) return (int)cudaErrorInvalidValue;
     const size_t smem = (size_t)(p.hw + max_valid) * sizeof(float);
     if (smem > 200u * 1024u) return (int)cudaErrorInvalidValue;
     dim3 grid((unsigned)p.heads, (unsigned)p.batch);
-    if (a->strict) k_attn_strict<<<grid, 256, smem, s>>>(p);
-    else k_attn_scalar<<<grid, FAST_THREADS, smem, s>>>(p);
+    if (a->strict) mb_launch(k_attn_strict, dim3(grid), dim3(256), smem, s, p);
+    else mb_launch(k_attn_scalar, dim3(grid), dim3(FAST_THREADS), smem, s, p);
     int rc = mb_check_launch();
     if (rc == 0 && a->qx != nullptr)
         rc = mb_quant_rows(a->out, a->batch, width, a->qx, a->sx, a->n_active, stream);

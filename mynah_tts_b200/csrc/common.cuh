@@ -87,3 +87,32 @@ __device__ __forceinline__ float exp_ref(float x, const uint32_t *exp_tab = null
 }
 
 static inline int mb_check_launch() { return (int)cudaGetLastError(); }
+
+// ---- programmatic dependent launch -----------------------------------------
+// Every kernel of the step begins with mb_pdl_wait(): when it was launched with
+// the programmatic-serialization attribute it may be scheduled while its
+// predecessor in the stream is still running, and the wait blocks until that
+// predecessor has finished and its writes are visible; without the attribute the
+// instruction does nothing.  mb_pdl_trigger() then lets the next kernel in the
+// stream start its own launch early.  Nothing a predecessor writes may be touched
+// before the wait.
+__device__ __forceinline__ void mb_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void mb_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+extern "C" int mb_pdl_enabled(void);   // glue.cu: MYNAH_B200_PDL, default on
+
+template <typename... KArgs, typename... Args>
+static inline int mb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                            Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = mb_pdl_enabled() ? 1u : 0u;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}

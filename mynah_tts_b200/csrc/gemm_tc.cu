@@ -114,6 +114,8 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, int (&v)[16]) {
 
 __global__ void __launch_bounds__(TC_THREADS)
 k_gemm_i8_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcP p) {
+    mb_pdl_wait();
+    mb_pdl_trigger();
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) unsigned long long full_bar[MAX_STAGES];
     __shared__ __align__(8) unsigned long long empty_bar[MAX_STAGES];
@@ -284,6 +286,6 @@ extern "C" int mb_gemm_tc(const mb_gemv_args *a, size_t qx_rows_alloc, int *stat
     p.batch = (int)a->batch; p.epilogue = a->epilogue; p.strict = a->strict;
     const unsigned m_tiles = (unsigned)((a->n + TM - 1) / TM);
     const unsigned b_tiles = (unsigned)((a->batch + BN - 1) / BN);
-    k_gemm_i8_tc<<<dim3(m_tiles, b_tiles), TC_THREADS, TC_SMEM, (cudaStream_t)stream>>>(map_w, map_x, p);
+    mb_launch(k_gemm_i8_tc, dim3(dim3(m_tiles, b_tiles)), dim3(TC_THREADS), TC_SMEM, (cudaStream_t)stream, map_w, map_x, p);
     return mb_check_launch();
 }

@@ -43,6 +43,7 @@ struct GemvP {
     int batch;
     int epilogue;
     int lpr, cpl;       // lanes per row, 16-byte chunks per lane
+    int iters;          // consecutive row groups one warp walks
     long row_bytes;
     long w_gs, scale_gs, act_gs, out_gs;  // group strides (elements of the respective arrays)
 };
@@ -61,6 +62,8 @@ __device__ __forceinline__ uint4 ldg16(const unsigned char *ptr) {
 
 template <int QT, int BT, bool STRICT>
 __global__ void __launch_bounds__(WARPS * 32) k_gemv(GemvP p) {
+    mb_pdl_wait();
+    mb_pdl_trigger();
     extern __shared__ __align__(16) unsigned char smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const long grp = blockIdx.y;
@@ -70,14 +73,11 @@ __global__ void __launch_bounds__(WARPS * 32) k_gemv(GemvP p) {
     const int nb = p.n_active != nullptr ? min(p.batch, *p.n_active) : p.batch;
     const int LPR = p.lpr, CPL = p.cpl, RPW = 32 / LPR;
     const int sub = lane / LPR, li = lane % LPR;
-    const long row = ((long)blockIdx.x * WARPS + warp) * RPW + sub;
-    const bool row_ok = row < p.n;
     const long k = p.k;
     constexpr bool QUANT = (QT == MB_INT8 || QT == MB_INT4);
     const long act_bytes = QUANT ? k : k * 4;
     unsigned char *act = smem;                         // [BT][act_bytes]
     float *pbuf = reinterpret_cast<float *>(smem + (size_t)BT * act_bytes);  // int4 only
-    const unsigned char *wrow = w + (row_ok ? row : 0) * p.row_bytes;
 
     // one batch tile per CTA (grid.z): tiles past the live lanes leave at once
     for (int b0 = blockIdx.z * BT; b0 < nb; b0 = nb) {
@@ -120,7 +120,14 @@ __global__ void __launch_bounds__(WARPS * 32) k_gemv(GemvP p) {
         }
         __syncthreads();
 
-        // ---- dot products -----------------------------------------------------
+        // ---- dot products: a warp walks `iters` row groups; the unrolled loop keeps
+        // the weight loads of two groups in flight -------------------------------
+#pragma unroll 2
+        for (int it = 0; it < p.iters; ++it) {
+        const long wgroup = ((long)blockIdx.x * p.iters + it) * WARPS + warp;
+        const long row = wgroup * RPW + sub;
+        const bool row_ok = row < p.n;
+        const unsigned char *wrow = w + (row_ok ? row : 0) * p.row_bytes;
         if (QT == MB_INT8) {
             int acc[BT];
 #pragma unroll
@@ -208,7 +215,7 @@ __global__ void __launch_bounds__(WARPS * 32) k_gemv(GemvP p) {
             // ordered accumulation over groups, one (row, stream) pair per lane
             for (int j = lane; j < RPW * BT; j += 32) {
                 const int r = j / BT, b = j % BT;
-                const long orow = ((long)blockIdx.x * WARPS + warp) * RPW + r;
+                const long orow = wgroup * RPW + r;
                 if (orow < p.n && b0 + b < nb) {
                     float a = 0.0f;
                     for (long g = 0; g < groups; ++g) a = __fadd_rn(a, wp[((long)r * groups + g) * BT + b]);
@@ -276,6 +283,7 @@ __global__ void __launch_bounds__(WARPS * 32) k_gemv(GemvP p) {
                 }
             }
         }
+        }   // row groups
     }
 }
 
@@ -283,6 +291,8 @@ __global__ void __launch_bounds__(WARPS * 32) k_gemv(GemvP p) {
 // per (row, stream), sequential over k.  Cold path (tiny self-test shapes).
 template <int QT, bool STRICT>
 __global__ void k_gemv_generic(GemvP p) {
+    mb_pdl_wait();
+    mb_pdl_trigger();
     const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
     const int nb = p.n_active != nullptr ? min(p.batch, *p.n_active) : p.batch;
     const long row = idx % p.n;
@@ -330,13 +340,21 @@ __global__ void k_gemv_generic(GemvP p) {
 template <int QT, int BT, bool STRICT>
 int launch_tiled(const GemvP &p, size_t groups, cudaStream_t s) {
     const int rpw = 32 / p.lpr;
-    const long iters = (p.n + rpw - 1) / rpw;
-    const unsigned blocks = (unsigned)((iters + WARPS - 1) / WARPS);
+    const long wgroups = (p.n + rpw - 1) / rpw;
+    const long blocks1 = (wgroups + WARPS - 1) / WARPS;
+    const long btiles = (p.batch + BT - 1) / BT;
+    // enough CTAs to cover the SMs about four times; beyond that a warp walks several
+    // row groups so a CTA moves tens of KB instead of a few
+    long it = blocks1 * (long)groups * btiles / 600;
+    it = it < 1 ? 1 : (it > 8 ? 8 : it);
+    GemvP q = p;
+    q.iters = (int)it;
+    const unsigned blocks = (unsigned)((blocks1 + it - 1) / it);
     const bool quant = (QT == MB_INT8 || QT == MB_INT4);
     size_t smem = (size_t)BT * (quant ? p.k : p.k * 4);
     if (QT == MB_INT4) smem += (size_t)WARPS * 32 * p.cpl * BT * sizeof(float);
     if (smem > 160u * 1024u) return (int)cudaErrorInvalidValue;
-    k_gemv<QT, BT, STRICT><<<dim3(blocks, (unsigned)groups, (unsigned)((p.batch + BT - 1) / BT)), WARPS * 32, smem, s>>>(p);
+    mb_launch(k_gemv<QT, BT, STRICT>, dim3(blocks, (unsigned)groups, (unsigned)btiles), dim3(WARPS * 32), smem, s, q);
     return mb_check_launch();
 }
 
@@ -345,7 +363,7 @@ int launch_qt(const GemvP &p, size_t groups, bool tiled, cudaStream_t s) {
     if (!tiled) {
         if (groups != 1) return (int)cudaErrorInvalidValue;
         const long total = p.n * p.batch;
-        k_gemv_generic<QT, STRICT><<<(unsigned)((total + 127) / 128), 128, 0, s>>>(p);
+        mb_launch(k_gemv_generic<QT, STRICT>, dim3((unsigned)((total + 127) / 128)), dim3(128), 0, s, p);
         return mb_check_launch();
     }
     const bool quant = (QT == MB_INT8 || QT == MB_INT4);
@@ -430,6 +448,9 @@ extern "C" int mb_gemv(const mb_gemv_args *a, mb_stream stream) {
     } else {
         p.lpr = 1;
         p.cpl = 0;
+    }
+    p.iters = 1;
+    {
     }
     cudaStream_t s = (cudaStream_t)stream;
     const bool strict = a->strict != 0;

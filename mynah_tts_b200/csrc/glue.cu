@@ -11,6 +11,7 @@
 #include "launch.h"
 
 #include <float.h>
+#include <stdlib.h>
 
 namespace {
 
@@ -21,6 +22,8 @@ __global__ void __launch_bounds__(256)
 k_layernorm(const float *__restrict__ in, float *__restrict__ out, const float *__restrict__ gain,
             const float *__restrict__ bias, int width, float eps, int8_t *__restrict__ qx,
             float *__restrict__ sx, const int *__restrict__ n_active) {
+    mb_pdl_wait();
+    mb_pdl_trigger();
     extern __shared__ float row[];
     __shared__ float red[33];
     __shared__ float stat[2];
@@ -98,6 +101,8 @@ k_layernorm(const float *__restrict__ in, float *__restrict__ out, const float *
 __global__ void __launch_bounds__(256)
 k_quant_rows(const float *__restrict__ in, int width, int8_t *__restrict__ qx,
              float *__restrict__ sx, const int *__restrict__ n_active) {
+    mb_pdl_wait();
+    mb_pdl_trigger();
     __shared__ float red[33];
     const int r = blockIdx.x;
     if (n_active != nullptr && r >= *n_active) return;
@@ -122,22 +127,30 @@ k_quant_rows(const float *__restrict__ in, int width, int8_t *__restrict__ qx,
 
 template <bool STRICT>
 __global__ void k_gelu(float *data, size_t n, const uint32_t *tanh_tab) {
+    mb_pdl_wait();
+    mb_pdl_trigger();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) data[i] = gelu_tanh<STRICT>(data[i], tanh_tab);
 }
 
 __global__ void k_residual_add(float *out, const float *in, size_t n) {
+    mb_pdl_wait();
+    mb_pdl_trigger();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) out[i] = __fadd_rn(out[i], in[i]);
 }
 
 __global__ void k_scale(float *data, size_t n, float scale) {
+    mb_pdl_wait();
+    mb_pdl_trigger();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) data[i] = __fmul_rn(data[i], scale);
 }
 
 // Non-finite -> 0, else clamp to [-1, 1] (src/backend.c:815-820).
 __global__ void k_clip(float *data, size_t n) {
+    mb_pdl_wait();
+    mb_pdl_trigger();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const float v = data[i];
@@ -145,6 +158,8 @@ __global__ void k_clip(float *data, size_t n) {
 }
 
 __global__ void k_bias_add(float *out, const float *bias, size_t total, size_t cols) {
+    mb_pdl_wait();
+    mb_pdl_trigger();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < total) out[i] = __fadd_rn(out[i], bias[i % cols]);
 }
@@ -159,6 +174,8 @@ k_argmax_rows(const float *__restrict__ logits, int vocab, int codebook_size, in
               unsigned *__restrict__ tokens, unsigned *__restrict__ codes,
               int *__restrict__ eos_flag, int tables_per_stream,
               const int *__restrict__ n_active) {
+    mb_pdl_wait();
+    mb_pdl_trigger();
     __shared__ float bv[256];
     __shared__ unsigned bi[256];
     const int r = blockIdx.x;
@@ -203,6 +220,8 @@ k_embed_frames(const float *const *__restrict__ tables, int n_tables, int vocab,
                const unsigned *__restrict__ codes, const float *__restrict__ position,
                const int *__restrict__ lens, float *__restrict__ x,
                const int *__restrict__ n_active, int *__restrict__ status) {
+    mb_pdl_wait();
+    mb_pdl_trigger();
     const int b = blockIdx.x;
     if (n_active != nullptr && b >= *n_active) return;
     const float *pe = position + (size_t)lens[b] * width;
@@ -225,6 +244,8 @@ __global__ void __launch_bounds__(256)
 k_add_position(const float *__restrict__ rows, const float *__restrict__ position,
                const int *__restrict__ lens, float *__restrict__ x, int width,
                const int *__restrict__ n_active) {
+    mb_pdl_wait();
+    mb_pdl_trigger();
     const int b = blockIdx.x;
     if (n_active != nullptr && b >= *n_active) return;
     const float *pe = position + (size_t)lens[b] * width;
@@ -233,6 +254,8 @@ k_add_position(const float *__restrict__ rows, const float *__restrict__ positio
 }
 
 __global__ void k_advance_lens(int *lens, int batch, const int *n_active) {
+    mb_pdl_wait();
+    mb_pdl_trigger();
     const int b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b < batch && (n_active == nullptr || b < *n_active)) lens[b] += 1;
 }
@@ -244,6 +267,8 @@ k_frame_advance(int *lens, const unsigned *__restrict__ tokens_cur, unsigned *__
                 int *frame_idx, const int *__restrict__ eos_flag, int *eos_frame, int *allow_eos,
                 int batch, int lane_stride, int tables, const int *__restrict__ min_frames, int history_frames,
                 const int *__restrict__ n_active) {
+    mb_pdl_wait();
+    mb_pdl_trigger();
     const int frame = *frame_idx;
     const int nb = n_active != nullptr ? min(batch, *n_active) : batch;
     __syncthreads();
@@ -260,6 +285,8 @@ k_frame_advance(int *lens, const unsigned *__restrict__ tokens_cur, unsigned *__
     if (threadIdx.x == 0) *frame_idx = frame + 1;
 }
 
+int g_pdl = -1;
+
 inline unsigned blocks_for(size_t n) { return (unsigned)((n + 255) / 256); }
 
 }  // namespace
@@ -271,10 +298,10 @@ extern "C" int mb_layernorm(const float *in, float *out, const float *gain, cons
     if (rows == 0 || width == 0 || smem > 48u * 1024u) return (int)cudaErrorInvalidValue;
     cudaStream_t s = (cudaStream_t)stream;
     if (strict)
-        k_layernorm<true><<<(unsigned)rows, 256, smem, s>>>(in, out, gain, bias, (int)width, eps,
+        mb_launch(k_layernorm<true>, dim3((unsigned)rows), dim3(256), smem, s, in, out, gain, bias, (int)width, eps,
                                                             qx, sx, n_active);
     else
-        k_layernorm<false><<<(unsigned)rows, 256, smem, s>>>(in, out, gain, bias, (int)width, eps,
+        mb_launch(k_layernorm<false>, dim3((unsigned)rows), dim3(256), smem, s, in, out, gain, bias, (int)width, eps,
                                                              qx, sx, n_active);
     return mb_check_launch();
 }
@@ -282,39 +309,39 @@ extern "C" int mb_layernorm(const float *in, float *out, const float *gain, cons
 extern "C" int mb_quant_rows(const float *in, size_t rows, size_t width, int8_t *qx, float *sx,
                              const int *n_active, mb_stream stream) {
     if (rows == 0 || width == 0) return (int)cudaErrorInvalidValue;
-    k_quant_rows<<<(unsigned)rows, 256, 0, (cudaStream_t)stream>>>(in, (int)width, qx, sx, n_active);
+    mb_launch(k_quant_rows, dim3((unsigned)rows), dim3(256), 0, (cudaStream_t)stream, in, (int)width, qx, sx, n_active);
     return mb_check_launch();
 }
 
 extern "C" int mb_gelu(float *data, size_t n, int strict, const uint32_t *tanh_tab, mb_stream stream) {
     if (n == 0) return 0;
-    if (strict) k_gelu<true><<<blocks_for(n), 256, 0, (cudaStream_t)stream>>>(data, n, tanh_tab);
-    else k_gelu<false><<<blocks_for(n), 256, 0, (cudaStream_t)stream>>>(data, n, nullptr);
+    if (strict) mb_launch(k_gelu<true>, dim3(blocks_for(n)), dim3(256), 0, (cudaStream_t)stream, data, n, tanh_tab);
+    else mb_launch(k_gelu<false>, dim3(blocks_for(n)), dim3(256), 0, (cudaStream_t)stream, data, n, nullptr);
     return mb_check_launch();
 }
 
 extern "C" int mb_residual_add(float *out, const float *in, size_t n, mb_stream stream) {
     if (n == 0) return 0;
-    k_residual_add<<<blocks_for(n), 256, 0, (cudaStream_t)stream>>>(out, in, n);
+    mb_launch(k_residual_add, dim3(blocks_for(n)), dim3(256), 0, (cudaStream_t)stream, out, in, n);
     return mb_check_launch();
 }
 
 extern "C" int mb_scale(float *data, size_t n, float scale, mb_stream stream) {
     if (n == 0) return 0;
-    k_scale<<<blocks_for(n), 256, 0, (cudaStream_t)stream>>>(data, n, scale);
+    mb_launch(k_scale, dim3(blocks_for(n)), dim3(256), 0, (cudaStream_t)stream, data, n, scale);
     return mb_check_launch();
 }
 
 extern "C" int mb_clip(float *data, size_t n, mb_stream stream) {
     if (n == 0) return 0;
-    k_clip<<<blocks_for(n), 256, 0, (cudaStream_t)stream>>>(data, n);
+    mb_launch(k_clip, dim3(blocks_for(n)), dim3(256), 0, (cudaStream_t)stream, data, n);
     return mb_check_launch();
 }
 
 extern "C" int mb_bias_add(float *out, const float *bias, size_t rows, size_t cols,
                            mb_stream stream) {
     if (rows * cols == 0) return 0;
-    k_bias_add<<<blocks_for(rows * cols), 256, 0, (cudaStream_t)stream>>>(out, bias, rows * cols,
+    mb_launch(k_bias_add, dim3(blocks_for(rows * cols)), dim3(256), 0, (cudaStream_t)stream, out, bias, rows * cols,
                                                                          cols);
     return mb_check_launch();
 }
@@ -324,7 +351,7 @@ extern "C" int mb_argmax_rows(const float *logits, size_t rows, size_t vocab, si
                               unsigned *tokens, unsigned *codes, int *eos_flag,
                               size_t tables_per_stream, const int *n_active, mb_stream stream) {
     if (rows == 0 || vocab == 0 || tables_per_stream == 0) return (int)cudaErrorInvalidValue;
-    k_argmax_rows<<<(unsigned)rows, 256, 0, (cudaStream_t)stream>>>(
+    mb_launch(k_argmax_rows, dim3((unsigned)rows), dim3(256), 0, (cudaStream_t)stream, 
         logits, (int)vocab, (int)codebook_size, (int)eos_id, allow_eos, allow_eos_scalar, tokens,
         codes, eos_flag, (int)tables_per_stream, n_active);
     return mb_check_launch();
@@ -335,7 +362,7 @@ extern "C" int mb_embed_frames(const float *const *tables, size_t n_tables, size
                                const int *lens, float *x, size_t batch, const int *n_active,
                                int *status, mb_stream stream) {
     if (batch == 0 || n_tables == 0) return (int)cudaErrorInvalidValue;
-    k_embed_frames<<<(unsigned)batch, 256, 0, (cudaStream_t)stream>>>(
+    mb_launch(k_embed_frames, dim3((unsigned)batch), dim3(256), 0, (cudaStream_t)stream, 
         tables, (int)n_tables, (int)vocab, (int)width, codes, position, lens, x, n_active, status);
     return mb_check_launch();
 }
@@ -343,14 +370,14 @@ extern "C" int mb_embed_frames(const float *const *tables, size_t n_tables, size
 extern "C" int mb_add_position(const float *rows, const float *position, const int *lens, float *x,
                                size_t batch, size_t width, const int *n_active, mb_stream stream) {
     if (batch == 0) return (int)cudaErrorInvalidValue;
-    k_add_position<<<(unsigned)batch, 256, 0, (cudaStream_t)stream>>>(rows, position, lens, x,
+    mb_launch(k_add_position, dim3((unsigned)batch), dim3(256), 0, (cudaStream_t)stream, rows, position, lens, x,
                                                                       (int)width, n_active);
     return mb_check_launch();
 }
 
 extern "C" int mb_advance_lens(int *lens, size_t batch, const int *n_active, mb_stream stream) {
     if (batch == 0) return 0;
-    k_advance_lens<<<blocks_for(batch), 256, 0, (cudaStream_t)stream>>>(lens, (int)batch, n_active);
+    mb_launch(k_advance_lens, dim3(blocks_for(batch)), dim3(256), 0, (cudaStream_t)stream, lens, (int)batch, n_active);
     return mb_check_launch();
 }
 
@@ -361,8 +388,16 @@ extern "C" int mb_frame_advance(int *lens, const unsigned *tokens_cur, unsigned 
                                 mb_stream stream) {
     if (batch == 0 || frame_idx == nullptr) return (int)cudaErrorInvalidValue;
     const unsigned threads = batch < 1024 ? (unsigned)((batch + 31) / 32 * 32) : 1024u;
-    k_frame_advance<<<1, threads, 0, (cudaStream_t)stream>>>(
+    mb_launch(k_frame_advance, dim3(1), dim3(threads), 0, (cudaStream_t)stream, 
         lens, tokens_cur, history, frame_idx, eos_flag, eos_frame, allow_eos, (int)batch,
         (int)lane_stride, (int)tables, min_frames, (int)history_frames, n_active);
     return mb_check_launch();
+}
+
+extern "C" int mb_pdl_enabled(void) {
+    if (g_pdl < 0) {
+        const char *env = getenv("MYNAH_B200_PDL");
+        g_pdl = (env != nullptr && env[0] == '0') ? 0 : 1;
+    }
+    return g_pdl;
 }

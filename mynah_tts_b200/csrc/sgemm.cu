@@ -14,6 +14,8 @@ constexpr int TILE = 16;
 __global__ void __launch_bounds__(TILE * TILE)
 k_sgemm(int trans_a, int trans_b, long m, long n, long k, float alpha, const float *__restrict__ a,
         long lda, const float *__restrict__ b, long ldb, float beta, float *__restrict__ c, long ldc) {
+    mb_pdl_wait();
+    mb_pdl_trigger();
     __shared__ float as[TILE][TILE + 1];
     __shared__ float bs[TILE][TILE + 1];
     const int tx = threadIdx.x % TILE, ty = threadIdx.x / TILE;
@@ -44,7 +46,7 @@ extern "C" int mb_sgemm(int trans_a, int trans_b, size_t m, size_t n, size_t k, 
                         size_t ldc, mb_stream stream) {
     if (m == 0 || n == 0 || k == 0) return (int)cudaErrorInvalidValue;
     dim3 grid((unsigned)((n + TILE - 1) / TILE), (unsigned)((m + TILE - 1) / TILE));
-    k_sgemm<<<grid, TILE * TILE, 0, (cudaStream_t)stream>>>(trans_a, trans_b, (long)m, (long)n,
+    mb_launch(k_sgemm, dim3(grid), dim3(TILE * TILE), 0, (cudaStream_t)stream, trans_a, trans_b, (long)m, (long)n,
                                                            (long)k, alpha, a, (long)lda, b,
                                                            (long)ldb, beta, c, (long)ldc);
     return mb_check_launch();
