@@ -299,9 +299,9 @@ const char *mynah_b200_profile_class_name(size_t cls);
  * memory pool is not its own, a context that must not grow): it takes no
  * backend state and never calls cudaMalloc/cudaFree or any allocating routine.
  * The kernel's scratch (per-chunk partial results, one merged row, arrival
- * counters) sits in a fixed ~590 KB array inside the library image that every
+ * counters) sits in a fixed ~450 KB array inside the library image that every
  * GPU loading the library holds until the process exits.
- * Limits: at most 4096 attended rows, heads*head_width <= 1024, <= 64 heads,
+ * Limits: at most 4096 attended rows, heads*head_width <= 768, <= 32 heads,
  * head_width a power-of-two multiple of 4 up to 128, 16-byte aligned buffers;
  * anything else is refused with a message.  The first call on a device looks
  * up the array's device address (cudaGetSymbolAddress); make that first call

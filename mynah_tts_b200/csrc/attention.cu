@@ -14,15 +14,18 @@
 // is evaluated in double and rounded once.  Same bits as the CPU loop except
 // where libm's expf is not correctly rounded.
 //
-// FAST kernel: grid (chunks, heads, streams).  Each CTA takes a fixed chunk of
-// 32 positions, computes a partial (max, sum, weighted V) and, when a head spans
-// several chunks, publishes it to a scratch buffer; the last chunk of a head to
-// arrive (an atomic counter per head) merges that head's partials in chunk
-// order; when the next projection wants int8 input, the last head of a stream
-// to finish (a counter per stream) quantizes the merged row.  Results depend
-// neither on arrival order nor on the batch a stream is stepped in.
+// FAST kernel: grid (CTAs per stream, streams), one warp per head.  Positions are cut
+// into fixed chunks of 32 rows.  A CTA brings a chunk's K rows and V rows -- whole
+// rows, all heads, contiguous in the cache -- into shared memory as TMA tiles
+// (completion on an mbarrier, bounded wait) and each warp computes its head's
+// partial (max, sum, weighted V) of that chunk without leaving the warp.  Partials
+// go to a scratch buffer; the last CTA of a stream to finish (an atomic counter per
+// stream; none when one CTA owns the stream) merges every head's chunks in index
+// order and, when the next projection wants int8 input, quantizes the merged row.
+// Results depend neither on arrival order nor on the batch a stream is stepped in.
 #include "common.cuh"
 #include "launch.h"
+#include "tma.cuh"
 
 #include <float.h>
 #include <stdio.h>
@@ -43,7 +46,9 @@ struct AttnP {
     const uint32_t *exp_tab;
     long q_stride, slot_stride, cache_stride, out_stride;
     long position, valid;
-    int heads, hw, batch, max_chunks;
+    int heads, hw, batch, max_chunks, splits;
+    long slot_rows;      // cache rows between consecutive slots (slot_stride / cache_stride)
+    int box_cols, nbox;  // a 32-row tile is nbox TMA boxes of box_cols columns
     float scale;
 };
 
@@ -115,15 +120,14 @@ __global__ void __launch_bounds__(256) k_attn_strict(AttnP p) {
 
 
 // -------------------------------------------------------------------- fast
-// Positions are cut into fixed chunks of CHUNK rows, one CTA per (chunk, head,
-// stream): the partition depends only on the stream's own length, never on how
-// many streams are stepped together, so a stream's result is bit-identical
-// whatever batch it runs in.  A chunk's K and V rows are staged in shared
-// memory by bulk asynchronous copies (one 16-byte-aligned row per copy, all in
-// flight at once, completion counted on an mbarrier).
+// Positions are cut into fixed chunks of CHUNK rows: the partition depends only on
+// the stream's own length, never on how many streams are stepped together, so a
+// stream's result is bit-identical whatever batch it runs in.
 constexpr int CHUNK = 32;
 constexpr int FAST_THREADS = 128;
+constexpr int MERGE_MAX = 128;      // most chunks one stream may have (4096 rows)
 constexpr unsigned SPIN_LIMIT = 1u << 24;
+constexpr int ROWS_SMEM_MAX = 220 * 1024;
 
 __device__ __forceinline__ unsigned smem_addr(const void *ptr) {
     return (unsigned)__cvta_generic_to_shared(ptr);
@@ -136,13 +140,6 @@ __device__ __forceinline__ void mbar_expect_tx(void *bar, unsigned bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)),
                  "r"(bytes)
                  : "memory");
-}
-// global -> this CTA's shared memory, size and both addresses multiples of 16 bytes
-__device__ __forceinline__ void bulk_g2s(void *dst, const void *src, unsigned bytes, void *bar) {
-    asm volatile(
-        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
-            "r"(smem_addr(dst)), "l"(src), "r"(bytes), "r"(smem_addr(bar))
-        : "memory");
 }
 // Bounded wait for phase `parity`; false when the limit ran out.
 __device__ __forceinline__ bool mbar_wait(void *bar, unsigned parity, unsigned limit) {
@@ -175,178 +172,216 @@ __device__ __forceinline__ void quantize_shared_row(const float *vals, int width
     if (threadIdx.x == 0) *sx_out = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 0.0f;
 }
 
-__global__ void __launch_bounds__(FAST_THREADS) k_attn_chunk(AttnP p) {
+// One CTA = one stream (lane) and a subset of its 32-row chunks, ALL heads: warp h
+// is head h.  A chunk's K rows (32 x width floats, contiguous in the cache) come in
+// as one tile, its V rows as another; reading whole rows keeps DRAM pages open
+// (head-sliced 256-byte reads were measured at 29% of HBM peak).  While the warps
+// score the K tile of chunk c, the V tile of c is landing; while they accumulate
+// V, the K tile of the next chunk is landing.
+__global__ void __launch_bounds__(1024, 1)
+k_attn_rows(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, AttnP p) {
     mb_pdl_wait();
     mb_pdl_trigger();
-    extern __shared__ __align__(16) float sm[];
+    extern __shared__ __align__(128) float sm[];
     __shared__ float red[33];
-    __shared__ float s_ml[2];
     __shared__ unsigned s_last;
-    __shared__ __align__(8) unsigned long long mbar;
-    const int sp = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    __shared__ __align__(8) unsigned long long mbar[2];    // [0] K tile, [1] V tile
+    const int sp = blockIdx.x, b = blockIdx.y;
     long pos, valid;
     float *kc, *vc;
     if (!lane_setup(p, b, pos, valid, kc, vc)) return;
-    const int ns = (int)((valid + CHUNK - 1) / CHUNK);
+    const int ns = (int)((valid + CHUNK - 1) / CHUNK);      // chunks of this stream
+    const int splits = p.splits;                             // CTAs that share a stream
     if (sp >= ns) return;
-    const int hw = p.hw, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const long s0 = (long)sp * CHUNK;
-    const int cnt = (int)min((long)CHUNK, valid - s0);
+    const int hw = p.hw, heads = p.heads, width = heads * hw;
+    const int hg = blockDim.x >> 5;                          // heads (= warps) of this CTA
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int h0 = blockIdx.z * hg, h = h0 + warp;           // this warp's head
+    const int cwidth = hg * hw;                              // columns this CTA covers
     const int tpp = hw / 4;                         // float4 lanes per row (power of two <= 32)
-    const int groups = FAST_THREADS / tpp;
-    float *qs = sm;                                 // [hw]
-    float *Ks = qs + hw;                            // [CHUNK][hw]
-    float *Vs = Ks + CHUNK * hw;                    // [CHUNK][hw]
-    float *sc = Vs + CHUNK * hw;                    // [CHUNK]
-    float *accs = sc + CHUNK;                       // [groups][hw]; reused by the merges
+    const int rps = 32 / tpp;                       // rows a warp covers per step
+    const int sub = lane / tpp, li = lane % tpp;
+    const int tile_floats = CHUNK * cwidth;
+    float *Kt = sm;                                 // [nbox][CHUNK][box_cols]
+    float *Vt = sm + tile_floats;
+    float *qs = Vt + tile_floats;                   // [cwidth]
+    float *wts = qs + cwidth + warp * MERGE_MAX;    // this warp's merge weights
     const long hoff = (long)h * hw;
-    const float *knew = p.k_new == nullptr ? nullptr : p.k_new + (long)b * p.q_stride + hoff;
-    const float *vnew = p.v_new == nullptr ? nullptr : p.v_new + (long)b * p.q_stride + hoff;
-    const unsigned row_bytes = (unsigned)hw * 4u;
-    if (threadIdx.x == 0) mbar_init(&mbar, 1u);
-    __syncthreads();
-    if (warp == 0) {
-        if (lane == 0) mbar_expect_tx(&mbar, 2u * row_bytes * (unsigned)cnt);
-        __syncwarp();
-        if (lane < cnt) {
-            const long s = s0 + lane;
-            const bool fresh = knew != nullptr && s == pos;   // the row being appended now
-            bulk_g2s(Ks + lane * hw, fresh ? knew : kc + s * p.cache_stride + hoff, row_bytes, &mbar);
-            bulk_g2s(Vs + lane * hw, fresh ? vnew : vc + s * p.cache_stride + hoff, row_bytes, &mbar);
-        }
+    const float *knew = p.k_new == nullptr ? nullptr : p.k_new + (long)b * p.q_stride;
+    const float *vnew = p.v_new == nullptr ? nullptr : p.v_new + (long)b * p.q_stride;
+    const long slot = p.slots != nullptr ? p.slots[b] : b;
+    const unsigned tile_bytes = (unsigned)tile_floats * 4u;
+    if (threadIdx.x == 0) {
+        mbar_init(&mbar[0], 1u);
+        mbar_init(&mbar[1], 1u);
     }
-    for (int d = threadIdx.x; d < hw; d += blockDim.x) {
-        qs[d] = p.q[(long)b * p.q_stride + hoff + d];
-        if (knew != nullptr && sp == 0) {   // one CTA per (stream, head) appends; readers of row
-                                            // `pos` take it from the new row, never from the cache
-            kc[pos * p.cache_stride + hoff + d] = knew[d];
-            vc[pos * p.cache_stride + hoff + d] = vnew[d];
+    for (int d = threadIdx.x; d < cwidth; d += blockDim.x) {
+        const long col = (long)h0 * hw + d;
+        qs[d] = p.q[(long)b * p.q_stride + col];
+        if (knew != nullptr && sp == 0) {   // one CTA per (stream, head group) appends; readers
+                                            // of row `pos` take it from the new row, never
+                                            // from the cache
+            kc[pos * p.cache_stride + col] = knew[col];
+            vc[pos * p.cache_stride + col] = vnew[col];
         }
     }
     __syncthreads();
-    if (!mbar_wait(&mbar, 0u, SPIN_LIMIT)) {
-        // the copies never landed: flag it, give them one more bounded wait so none
-        // is in flight when this CTA's shared memory is released, and leave.
-        if (threadIdx.x == 0 && p.status != nullptr) atomicOr(p.status, 2);
-        mbar_wait(&mbar, 0u, SPIN_LIMIT);
-        return;
+    // tile of chunk c: p.nbox boxes of box_cols columns x 32 rows each
+    auto issue = [&](const CUtensorMap *map, float *tile, int c, int which) {
+        const int y = (int)(slot * p.slot_rows + (long)c * CHUNK);
+        mbar_expect_tx(&mbar[which], tile_bytes);
+        for (int bx = 0; bx < p.nbox; ++bx)
+            mb_tma_load_2d(tile + (long)bx * CHUNK * p.box_cols, map, h0 * hw + bx * p.box_cols, y,
+                           &mbar[which]);
+    };
+    if (threadIdx.x == 0) {
+        issue(&kmap, Kt, sp, 0);
+        issue(&vmap, Vt, sp, 1);
     }
-    // ---- scores: tpp lanes share a row, 32/tpp rows per warp step -----------------
-    {
-        const int ppw = 32 / tpp, sub = lane / tpp, li = lane % tpp;
-        const float4 qv = reinterpret_cast<const float4 *>(qs)[li];
-        const int step = (FAST_THREADS / 32) * ppw;
-#pragma unroll 4
-        for (int i = warp * ppw + sub; i < CHUNK; i += step) {   // same trip count on every lane
-            float a = 0.0f;
-            if (i < cnt) {
-                const float4 kv = reinterpret_cast<const float4 *>(Ks + i * hw)[li];
-                a = fmaf(qv.x, kv.x, a); a = fmaf(qv.y, kv.y, a);
-                a = fmaf(qv.z, kv.z, a); a = fmaf(qv.w, kv.w, a);
+    // this head's slice inside a tile: box, column offset, row pitch
+    const long slice = (long)((warp * hw) / p.box_cols) * CHUNK * p.box_cols + (warp * hw) % p.box_cols;
+    const int pitch = p.box_cols;
+    const float4 qv = reinterpret_cast<const float4 *>(qs + warp * hw)[li];
+    int it = 0;
+    for (int c = sp; c < ns; c += splits, ++it) {
+        const unsigned parity = (unsigned)(it & 1);
+        const long s0 = (long)c * CHUNK;
+        const int cnt = (int)min((long)CHUNK, valid - s0);
+        const bool fresh = knew != nullptr && pos >= s0 && pos < s0 + cnt;
+        // ---- K tile ---------------------------------------------------------------------
+        if (__syncthreads_or(mbar_wait(&mbar[0], parity, SPIN_LIMIT) ? 0 : 1)) {
+            // a tile never landed: flag it, give the copies one more bounded wait so none
+            // is in flight when this CTA's shared memory is released, and leave together.
+            if (threadIdx.x == 0) {
+                if (p.status != nullptr) atomicOr(p.status, 2);
+                mbar_wait(&mbar[0], parity, SPIN_LIMIT);
+                mbar_wait(&mbar[1], parity, SPIN_LIMIT);
             }
-            for (int o = tpp >> 1; o > 0; o >>= 1) a += __shfl_xor_sync(MB_FULL, a, o);
-            if (li == 0) sc[i] = i < cnt ? a * p.scale : -FLT_MAX;
+            __syncthreads();
+            return;
         }
-    }
-    __syncthreads();
-    if (warp == 0) {   // CHUNK == 32: one lane per row
-        const float v = sc[lane];
-        const float m = warp_max(v);
-        const float e = lane < cnt ? exp_ref<false>(v - m) : 0.0f;
-        sc[lane] = e;
+        float *Ks = Kt + slice;
+        if (fresh) {
+            // the row being appended now may not have reached the cache when the tile was
+            // read: take it from the new K row itself
+            for (int d = lane; d < hw; d += 32) Ks[(pos - s0) * pitch + d] = knew[hoff + d];
+            __syncwarp();
+        }
+        // scores: tpp lanes share a row, rps rows per step; lane (sub, li) keeps the score
+        // of row li * rps + sub
+        float mine = -FLT_MAX;
+        for (int t = 0; t < tpp; ++t) {
+            const int i = t * rps + sub;
+            const float4 kv = *reinterpret_cast<const float4 *>(Ks + (long)i * pitch + 4 * li);
+            float a = 0.0f;
+            a = fmaf(qv.x, kv.x, a); a = fmaf(qv.y, kv.y, a);
+            a = fmaf(qv.z, kv.z, a); a = fmaf(qv.w, kv.w, a);
+            for (int o = tpp >> 1; o > 0; o >>= 1) a += __shfl_xor_sync(MB_FULL, a, o);
+            if (li == t) mine = i < cnt ? a * p.scale : -FLT_MAX;
+        }
+        const float m = warp_max(mine);
+        const int my_row = li * rps + sub;
+        const float e = my_row < cnt ? exp_ref<false>(mine - m) : 0.0f;
         const float l = warp_sum(e);
-        if (lane == 0) { s_ml[0] = m; s_ml[1] = l; }
-    }
-    __syncthreads();
-    // ---- weighted V: group g of tpp threads takes rows g, g+groups, ... -----------
-    {
-        const int g = threadIdx.x / tpp, li = threadIdx.x % tpp;
+        __syncthreads();                                     // every warp is done with the K tile
+        if (threadIdx.x == 0 && c + splits < ns) issue(&kmap, Kt, c + splits, 0);
+        // ---- V tile ---------------------------------------------------------------------
+        if (__syncthreads_or(mbar_wait(&mbar[1], parity, SPIN_LIMIT) ? 0 : 1)) {
+            if (threadIdx.x == 0) {
+                if (p.status != nullptr) atomicOr(p.status, 2);
+                mbar_wait(&mbar[1], parity, SPIN_LIMIT);
+                if (c + splits < ns) mbar_wait(&mbar[0], parity ^ 1u, SPIN_LIMIT);
+            }
+            __syncthreads();
+            return;
+        }
+        float *Vs = Vt + slice;
+        if (fresh) {
+            for (int d = lane; d < hw; d += 32) Vs[(pos - s0) * pitch + d] = vnew[hoff + d];
+            __syncwarp();
+        }
+        // weighted V: the sub-groups take interleaved rows, then add up
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 4
-        for (int i = g; i < cnt; i += groups) {
-            const float4 vv = reinterpret_cast<const float4 *>(Vs + i * hw)[li];
-            const float w = sc[i];
+        for (int t = 0; t < tpp; ++t) {
+            const int i = t * rps + sub;
+            const float w = __shfl_sync(MB_FULL, e, sub * tpp + t);
+            const float4 vv = *reinterpret_cast<const float4 *>(Vs + (long)i * pitch + 4 * li);
             acc.x = fmaf(w, vv.x, acc.x); acc.y = fmaf(w, vv.y, acc.y);
             acc.z = fmaf(w, vv.z, acc.z); acc.w = fmaf(w, vv.w, acc.w);
         }
-        reinterpret_cast<float4 *>(accs)[g * tpp + li] = acc;
+        for (int o = tpp; o < 32; o <<= 1) {
+            acc.x += __shfl_xor_sync(MB_FULL, acc.x, o); acc.y += __shfl_xor_sync(MB_FULL, acc.y, o);
+            acc.z += __shfl_xor_sync(MB_FULL, acc.z, o); acc.w += __shfl_xor_sync(MB_FULL, acc.w, o);
+        }
+        // this chunk's partial (max, sum, weighted V) of head h
+        float *part = p.partials + (((long)b * heads + h) * p.max_chunks + c) * (hw + 2);
+        if (sub == 0) {
+            part[2 + 4 * li] = acc.x; part[3 + 4 * li] = acc.y;
+            part[4 + 4 * li] = acc.z; part[5 + 4 * li] = acc.w;
+        }
+        if (lane == 0) { part[0] = m; part[1] = l; }
+        __syncthreads();                                     // every warp is done with the V tile
+        if (threadIdx.x == 0 && c + splits < ns) issue(&vmap, Vt, c + splits, 1);
     }
+    // ---- the head group's last CTA merges its heads, chunks in index order -------------
+    __threadfence();
     __syncthreads();
-    const float m = s_ml[0], l = s_ml[1];
-    const int width = p.heads * hw;
-    const bool quant = p.qx != nullptr;
-    float *outrow = p.out == nullptr ? nullptr : p.out + (long)b * p.out_stride;
-    // staging row for the merged output when it must be quantized but not stored
-    float *merged = p.partials == nullptr ? nullptr
-                                          : p.partials + (long)p.batch * p.heads * p.max_chunks * (hw + 2) +
-                                                (long)b * width;
-    if (ns == 1) {
-        for (int d = threadIdx.x; d < hw; d += blockDim.x) {
-            float a = 0.0f;
-            for (int g = 0; g < groups; ++g) a += accs[g * hw + d];
-            const float o = l > 0.0f ? a / l : 0.0f;
-            if (outrow != nullptr) outrow[hoff + d] = o;
-            if (quant) merged[hoff + d] = o;
-        }
-    } else {
-        float *part = p.partials + (((long)b * p.heads + h) * p.max_chunks + sp) * (hw + 2);
-        for (int d = threadIdx.x; d < hw; d += blockDim.x) {
-            float a = 0.0f;
-            for (int g = 0; g < groups; ++g) a += accs[g * hw + d];
-            part[2 + d] = a;
-        }
-        if (threadIdx.x == 0) { part[0] = m; part[1] = l; }
-        __threadfence();
-        __syncthreads();
+    const int groups = (int)gridDim.z;
+    if (min(ns, splits) > 1) {                               // several CTAs shared this head group
         if (threadIdx.x == 0) {
-            unsigned *ctr = p.counters + (long)b * p.heads + h;
+            unsigned *ctr = p.counters + (long)b * groups + blockIdx.z;
             const unsigned prev = atomicAdd(ctr, 1u);
-            s_last = prev == (unsigned)ns - 1u;
+            s_last = prev == (unsigned)min(ns, splits) - 1u;
             if (s_last) *ctr = 0u;
         }
         __syncthreads();
         if (!s_last) return;
-        // ---- this head's last chunk merges the head, chunks in index order ----------
         __threadfence();
-        const float *ph = p.partials + ((long)b * p.heads + h) * p.max_chunks * (hw + 2);
-        float *wts = accs;                   // [ns] merge weights (ns <= max_chunks <= groups*hw)
-        for (int s = threadIdx.x; s < ns; s += blockDim.x) wts[s] = __ldcg(ph + (long)s * (hw + 2));
-        __syncthreads();
+    }
+    const bool quant = p.qx != nullptr;
+    float *outrow = p.out == nullptr ? nullptr : p.out + (long)b * p.out_stride;
+    float *vals = Kt;                                        // merged row, for the quantization pass
+    // staging of the merged row when its head groups sit in different CTAs
+    float *merged = p.partials + (long)p.batch * heads * p.max_chunks * (hw + 2) + (long)b * width;
+    {
+        const float *ph = p.partials + ((long)b * heads + h) * p.max_chunks * (hw + 2);
+        for (int s = lane; s < ns; s += 32) wts[s] = __ldcg(ph + (long)s * (hw + 2));
+        __syncwarp();
         float M = -FLT_MAX;
         for (int s = 0; s < ns; ++s) M = fmaxf(M, wts[s]);
-        __syncthreads();
-        for (int s = threadIdx.x; s < ns; s += blockDim.x) wts[s] = exp_ref<false>(wts[s] - M);
-        __syncthreads();
+        __syncwarp();
+        for (int s = lane; s < ns; s += 32) wts[s] = exp_ref<false>(wts[s] - M);
+        __syncwarp();
         float L = 0.0f;
         for (int s = 0; s < ns; ++s) L = fmaf(__ldcg(ph + (long)s * (hw + 2) + 1), wts[s], L);
-        for (int d = threadIdx.x; d < hw; d += blockDim.x) {
+        for (int d = lane; d < hw; d += 32) {
             float O = 0.0f;
 #pragma unroll 4
             for (int s = 0; s < ns; ++s) O = fmaf(__ldcg(ph + (long)s * (hw + 2) + 2 + d), wts[s], O);
             const float o = L > 0.0f ? O / L : 0.0f;
             if (outrow != nullptr) outrow[hoff + d] = o;
-            if (quant) merged[hoff + d] = o;
+            if (quant) {
+                if (groups == 1) vals[hoff + d] = o;
+                else merged[hoff + d] = o;
+            }
         }
     }
     if (!quant) return;
-    // ---- the stream's last head quantizes the whole row --------------------------------
-    if (p.heads > 1) {
+    // ---- the stream's last head group quantizes the whole row ---------------------------
+    if (groups > 1) {
         __threadfence();
         __syncthreads();
         if (threadIdx.x == 0) {
-            unsigned *ctr = p.counters + (long)p.batch * p.heads + b;
+            unsigned *ctr = p.counters + (long)p.batch * groups + b;
             const unsigned prev = atomicAdd(ctr, 1u);
-            s_last = prev == (unsigned)p.heads - 1u;
+            s_last = prev == (unsigned)groups - 1u;
             if (s_last) *ctr = 0u;
         }
         __syncthreads();
         if (!s_last) return;
         __threadfence();
-    } else {
-        __syncthreads();
+        for (int i = threadIdx.x; i < width; i += blockDim.x) vals[i] = __ldcg(merged + i);
     }
-    float *vals = Ks;   // at least CHUNK*hw floats; the launcher checks heads*hw fits
-    for (int i = threadIdx.x; i < width; i += blockDim.x) vals[i] = __ldcg(merged + i);
     __syncthreads();
     quantize_shared_row(vals, width, p.qx + (long)b * width, p.sx + b, red);
 }
@@ -416,7 +451,7 @@ size_t chunks_for(size_t max_valid) { return (max_valid + CHUNK - 1) / CHUNK; }
 // per device at backend open, outside any stream capture.
 extern "C" int mb_attention_init(void) {
     int rc = (int)cudaFuncSetAttribute(k_attn_strict, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    if (rc == 0) rc = (int)cudaFuncSetAttribute(k_attn_chunk, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (rc == 0) rc = (int)cudaFuncSetAttribute(k_attn_rows, cudaFuncAttributeMaxDynamicSharedMemorySize, ROWS_SMEM_MAX);
     if (rc == 0) rc = (int)cudaFuncSetAttribute(k_attn_scalar, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     return rc;
 }
@@ -455,21 +490,48 @@ extern "C" int mb_attention(const mb_attn_args *a, mb_stream stream) {
     if (max_valid <= 0) return (int)cudaErrorInvalidValue;
     p.max_chunks = (int)chunks_for((size_t)max_valid);
     const size_t width = a->heads * a->head_width;
-    const bool chunked = !a->strict && (p.hw % 4) == 0 && is_pow2(p.hw / 4) && p.hw / 4 <= 32 &&
-                         (p.cache_stride % 4) == 0 && (p.q_stride % 4) == 0 &&
-                         (p.slot_stride % 4) == 0 && width <= (size_t)CHUNK * p.hw &&
+    // heads per CTA (one warp each): all of them when many streams are stepped (whole cache
+    // rows per tile keep DRAM pages open), fewer when few streams must still fill the SMs
+    int hg = p.heads;
+    if (a->sm_count > 0 && p.heads <= 32) {
+        const int want = p.batch >= 32 ? p.heads : (p.batch >= 8 ? (p.heads + 2) / 3 : 1);
+        for (hg = want < 1 ? 1 : want; hg < p.heads && p.heads % hg != 0; ++hg) {}
+    }
+    int hpb = 0;   // heads per TMA box: a box holds whole heads and at most 256 columns
+    for (int c = p.hw > 0 ? 256 / p.hw : 0; c >= 1 && hpb == 0; --c)
+        if (c <= hg && hg % c == 0) hpb = c;
+    const size_t cwidth = (size_t)hg * p.hw;
+    const size_t rows_floats = 2u * CHUNK * cwidth + cwidth + (size_t)hg * MERGE_MAX;
+    const bool chunked = !a->strict && hpb > 0 && (p.hw % 4) == 0 && is_pow2(p.hw / 4) && p.hw / 4 <= 32 &&
+                         p.heads <= 32 && p.max_chunks <= MERGE_MAX &&
+                         rows_floats * sizeof(float) <= (size_t)ROWS_SMEM_MAX && 64u * cwidth >= width &&
+                         (p.cache_stride % 4) == 0 && (p.q_stride % 4) == 0 && (p.slot_stride % 4) == 0 &&
+                         (a->batch == 1 || a->cache_rows != 0) && (p.slot_stride % p.cache_stride) == 0 &&
                          (((uintptr_t)a->k_cache | (uintptr_t)a->v_cache | (uintptr_t)a->q |
                            (uintptr_t)a->k_new | (uintptr_t)a->v_new) & 15u) == 0;
     if (chunked) {
-        const bool needs_scratch = p.max_chunks > 1 || a->qx != nullptr;
-        if (needs_scratch && (a->partials == nullptr || a->counters == nullptr))
+        if (a->partials == nullptr || a->counters == nullptr) return (int)cudaErrorInvalidValue;
+        // CTAs per stream: about one CTA per SM in all; with many streams one CTA walks
+        // all chunks of its stream
+        const long groups = p.heads / hg;
+        long splits = a->sm_count > 0 ? a->sm_count / ((long)p.batch * groups) : p.max_chunks;
+        if (hg < 4) splits = p.max_chunks;        // few warps per CTA: one chunk each, many CTAs
+        if (splits > p.max_chunks) splits = p.max_chunks;
+        if (splits < 1) splits = 1;
+        p.splits = (int)splits;
+        p.box_cols = hpb * p.hw;
+        p.nbox = hg / hpb;
+        p.slot_rows = p.slot_stride / p.cache_stride;
+        size_t rows = a->cache_rows;
+        if (rows == 0) rows = (size_t)(p.valid > p.position + 1 ? p.valid : p.position + 1);
+        CUtensorMap kmap, vmap;
+        if (!mb_make_map_2d(&kmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a->k_cache, rows, (size_t)p.cache_stride,
+                            (size_t)p.cache_stride * 4u, (unsigned)p.box_cols, CHUNK, CU_TENSOR_MAP_SWIZZLE_NONE) ||
+            !mb_make_map_2d(&vmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a->v_cache, rows, (size_t)p.cache_stride,
+                            (size_t)p.cache_stride * 4u, (unsigned)p.box_cols, CHUNK, CU_TENSOR_MAP_SWIZZLE_NONE))
             return (int)cudaErrorInvalidValue;
-        const int groups = FAST_THREADS / (p.hw / 4);
-        const size_t floats = (size_t)p.hw + 2u * CHUNK * p.hw + CHUNK + (size_t)groups * p.hw;
-        if (floats * sizeof(float) > 200u * 1024u || (size_t)p.max_chunks > (size_t)groups * p.hw)
-            return (int)cudaErrorInvalidValue;
-        dim3 grid((unsigned)p.max_chunks, (unsigned)p.heads, (unsigned)p.batch);
-        mb_launch(k_attn_chunk, dim3(grid), dim3(FAST_THREADS), floats * sizeof(float), s, p);
+        mb_launch(k_attn_rows, dim3((unsigned)splits, (unsigned)p.batch, (unsigned)groups),
+                  dim3((unsigned)hg * 32u), rows_floats * sizeof(float), s, kmap, vmap, p);
         return mb_check_launch();
     }
     if (a->out == nullptr) return (int)cudaErrorInvalidValue;
@@ -504,8 +566,8 @@ extern "C" int mb_attention(const mb_attn_args *a, mb_stream stream) {
 // call's partial results, which are always rewritten before they are read; the
 // counters must start at zero and are cleared at the start of each call.
 #define MB_STATIC_MAX_VALID 4096u
-#define MB_STATIC_MAX_WIDTH 1024u
-#define MB_STATIC_MAX_HEADS 64u
+#define MB_STATIC_MAX_WIDTH 768u
+#define MB_STATIC_MAX_HEADS 32u
 #define MB_STATIC_MAX_DEVICES 16
 // chunks * (width + 2 * heads) partial floats + one merged row, then the counters
 #define MB_STATIC_FLOATS ((MB_STATIC_MAX_VALID / 32u) * (MB_STATIC_MAX_WIDTH + 2u * MB_STATIC_MAX_HEADS) + MB_STATIC_MAX_WIDTH)
@@ -527,8 +589,8 @@ static void static_error(char *error, size_t cap, const char *message) {
 // `position`, attend rows below `valid`, `heads` heads of `head_width`), but
 // state-free and allocation-free: no cudaMalloc, cudaFree or allocating library
 // call is made, here or on any later call.  The first call on a device
-// resolves the scratch array's device address; make that first call outside
-// stream capture.  Work is enqueued on `cuda_stream` (a cudaStream_t, may be
+// resolves the scratch array's device address and opts the kernel into its
+// shared-memory size; make that first call outside stream capture.  Work is enqueued on `cuda_stream` (a cudaStream_t, may be
 // 0) and is not synchronized.  Returns 0, or -1 with a message.
 extern "C" __attribute__((visibility("default")))
 int mynah_b200_self_attention_static(const float *dev_qkv, float *dev_k_cache, float *dev_v_cache,
@@ -549,7 +611,7 @@ int mynah_b200_self_attention_static(const float *dev_qkv, float *dev_k_cache, f
         return -1;
     }
     const bool shape_ok = (head_width % 4) == 0 && is_pow2((long)head_width / 4) && head_width <= 128 &&
-                          (cache_stride % 4) == 0 && (width % 4) == 0 && width <= (size_t)CHUNK * head_width &&
+                          (cache_stride % 4) == 0 && (width % 4) == 0 &&
                           (((uintptr_t)dev_k_cache | (uintptr_t)dev_v_cache | (uintptr_t)dev_qkv) & 15u) == 0;
     if (!shape_ok) {
         static_error(error, cap, "head width must be a power-of-two multiple of 4 up to 128 and buffers 16-byte aligned");
@@ -566,6 +628,13 @@ int mynah_b200_self_attention_static(const float *dev_qkv, float *dev_k_cache, f
         rc = cudaGetSymbolAddress(&addr, g_attention_static_scratch);
         if (rc != cudaSuccess || addr == nullptr) {
             static_error(error, cap, rc != cudaSuccess ? cudaGetErrorString(rc) : "no address for the static scratch");
+            return -1;
+        }
+        // the chunk kernel stages two chunks of K and V: above 48 KB of dynamic shared
+        // memory for wide heads, which a kernel must opt into once per device
+        rc = cudaFuncSetAttribute(k_attn_rows, cudaFuncAttributeMaxDynamicSharedMemorySize, ROWS_SMEM_MAX);
+        if (rc != cudaSuccess) {
+            static_error(error, cap, cudaGetErrorString(rc));
             return -1;
         }
         g_static_scratch_addr[device] = addr;
@@ -597,15 +666,29 @@ int mynah_b200_self_attention_static(const float *dev_qkv, float *dev_k_cache, f
     p.hw = (int)head_width;
     p.batch = 1;
     p.max_chunks = (int)chunks_for(valid);
+    p.splits = p.max_chunks;           // one chunk per CTA: partials go through the static scratch
     p.scale = scale;
-    const int groups = FAST_THREADS / (p.hw / 4);
-    const size_t floats = (size_t)p.hw + 2u * CHUNK * p.hw + CHUNK + (size_t)groups * p.hw;
-    if (floats * sizeof(float) > 48u * 1024u || (size_t)p.max_chunks > (size_t)groups * p.hw) {
+    int hpb = 0;
+    for (int c = 256 / p.hw; c >= 1 && hpb == 0; --c)
+        if (c <= p.heads && p.heads % c == 0) hpb = c;
+    const size_t floats = 2u * CHUNK * width + width + (size_t)p.heads * MERGE_MAX;
+    if (hpb == 0 || floats * sizeof(float) > (size_t)ROWS_SMEM_MAX || p.max_chunks > MERGE_MAX) {
         static_error(error, cap, "shape needs more shared memory than the allocation-free path uses");
         return -1;
     }
-    dim3 grid((unsigned)p.max_chunks, (unsigned)p.heads, 1u);
-    k_attn_chunk<<<grid, FAST_THREADS, floats * sizeof(float), s>>>(p);
+    p.box_cols = hpb * p.hw;
+    p.nbox = p.heads / hpb;
+    p.slot_rows = 0;
+    const size_t rows = valid > position + 1 ? valid : position + 1;
+    CUtensorMap kmap, vmap;   // encoded on the host: no device memory involved
+    if (!mb_make_map_2d(&kmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, dev_k_cache, rows, cache_stride,
+                        cache_stride * 4u, (unsigned)p.box_cols, CHUNK, CU_TENSOR_MAP_SWIZZLE_NONE) ||
+        !mb_make_map_2d(&vmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, dev_v_cache, rows, cache_stride,
+                        cache_stride * 4u, (unsigned)p.box_cols, CHUNK, CU_TENSOR_MAP_SWIZZLE_NONE)) {
+        static_error(error, cap, "could not describe the KV cache to the copy engine");
+        return -1;
+    }
+    k_attn_rows<<<dim3((unsigned)p.splits, 1u), (unsigned)p.heads * 32u, floats * sizeof(float), s>>>(kmap, vmap, p);
     rc = cudaGetLastError();
     if (rc != cudaSuccess) {
         static_error(error, cap, cudaGetErrorString(rc));

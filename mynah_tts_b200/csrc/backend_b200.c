@@ -842,6 +842,7 @@ static int attention_common(mb_state *st, const float *q, size_t q_stride, const
     a.strict = st->strict;
     a.exp_tab = st->libm.exp_tab;
     a.status = st->d_status;
+    a.sm_count = st->sm_count;
     if (!st->strict) {
         const size_t need = mb_attention_scratch_floats(1u, heads, valid, hw);
         const size_t ctrs = mb_attention_counters(1u, heads);

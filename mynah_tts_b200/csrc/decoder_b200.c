@@ -432,6 +432,7 @@ static int enqueue(mb_decoder *d, size_t bucket, int mode, unsigned *count) {
         a.slots = d->d_slots;
         a.lens = d->d_lens;
         a.valid = d->capacity;
+        a.cache_rows = (d->slots - 1u) * d->layers * d->capacity + d->capacity;
         a.cache_stride = W;
         a.heads = d->heads;
         a.head_width = d->hw;
@@ -447,6 +448,7 @@ static int enqueue(mb_decoder *d, size_t bucket, int mode, unsigned *count) {
         a.partials = d->partials;
         a.counters = d->counters;
         a.status = d->d_status;
+        a.sm_count = st->sm_count;
         P(PC_ATTN_SELF, mb_attention(&a, s));
         *count += (st->strict && q) ? 2u : 1u;
         P(PC_O_SELF, product(d, &L->o_self, NULL, d->attn, d->x, W, nb, MB_EPI_RESIDUAL, count));
@@ -461,6 +463,7 @@ static int enqueue(mb_decoder *d, size_t bucket, int mode, unsigned *count) {
         a.slots = d->d_slots;
         a.position = 0;
         a.valid = d->T;
+        a.cache_rows = (d->slots - 1u) * d->layers * d->T + d->T;
         a.cache_stride = XW;
         a.heads = 1;
         a.head_width = XW;
@@ -476,6 +479,7 @@ static int enqueue(mb_decoder *d, size_t bucket, int mode, unsigned *count) {
         a.partials = d->partials;
         a.counters = d->counters;
         a.status = d->d_status;
+        a.sm_count = st->sm_count;
         P(PC_ATTN_CROSS, mb_attention(&a, s));
         *count += (st->strict && q) ? 2u : 1u;
         P(PC_O_CROSS, product(d, &L->o_cross, NULL, d->xctx, d->x, W, nb, MB_EPI_RESIDUAL, count));

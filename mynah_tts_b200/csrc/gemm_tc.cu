@@ -27,7 +27,7 @@
 #include "common.cuh"
 #include "launch.h"
 
-#include <cuda.h>
+#include "tma.cuh"
 
 namespace {
 
@@ -222,35 +222,10 @@ k_gemm_i8_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
 }
 
-typedef CUresult (*encode_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                              const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
-                              CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                              CUtensorMapFloatOOBfill);
-
-encode_fn get_encoder() {
-    static encode_fn fn = nullptr;
-    if (fn == nullptr) {
-        void *sym = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<encode_fn>(sym);
-    }
-    return fn;
-}
-
-// [rows][k] bytes, row-major; box = 128 K-bytes x box_rows rows, 128-byte swizzle,
-// out-of-range elements read as zero.
+// [rows][k] bytes, row-major; box = 128 K-bytes x box_rows rows, 128-byte swizzle.
 bool make_map(CUtensorMap *map, const void *ptr, size_t rows, size_t k, unsigned box_rows) {
-    encode_fn enc = get_encoder();
-    if (enc == nullptr) return false;
-    cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)k};
-    cuuint32_t box[2] = {(cuuint32_t)KC, box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(ptr), dims, strides, box, estr,
-               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    return mb_make_map_2d(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, ptr, rows, k, k, (unsigned)KC, box_rows,
+                          CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
 constexpr size_t TC_SMEM = (size_t)MAX_STAGES * (A_BYTES + B_BYTES) + 1024;

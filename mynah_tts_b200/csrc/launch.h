@@ -134,6 +134,7 @@ typedef struct {
     const int *lens;      /* [batch] position of each lane (valid = len+1); NULL = scalars below */
     size_t position, valid;
     size_t cache_stride, heads, head_width;
+    size_t cache_rows;    /* rows addressable from k_cache/v_cache (all slots); 0 = up to valid/position */
     float scale;
     float *out;           /* [batch][out_stride] */
     size_t out_stride;
@@ -149,6 +150,7 @@ typedef struct {
      * must not overlap on the device. */
     float *partials;
     unsigned *counters;
+    int sm_count;         /* SMs of the device (sizes the split); 0 = one chunk per CTA */
     int *status;          /* device error word (nonzero = bad argument seen) */
 } mb_attn_args;
 int mb_attention(const mb_attn_args *args, mb_stream stream);

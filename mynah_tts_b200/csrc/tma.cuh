@@ -1,0 +1,53 @@
+// Tensor-map (TMA) helpers shared by the kernels that stage tiles with
+// cp.async.bulk.tensor: a host-side encoder reached through the runtime's driver
+// entry point (no link-time dependency on the driver library) and the device-side
+// 2-D tile load.  No load here uses cluster multicast.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+typedef CUresult (*mb_encode_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                 const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                 CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                 CUtensorMapFloatOOBfill);
+
+static inline mb_encode_fn mb_tensor_map_encoder() {
+    static mb_encode_fn fn = nullptr;
+    if (fn == nullptr) {
+        void *sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<mb_encode_fn>(sym);
+    }
+    return fn;
+}
+
+// Row-major 2-D array [rows][row_elems] with a row pitch of pitch_bytes; a box
+// of box_cols x box_rows elements; elements outside the array read as zero.
+static inline bool mb_make_map_2d(CUtensorMap *map, CUtensorMapDataType type, const void *ptr, size_t rows,
+                                  size_t row_elems, size_t pitch_bytes, unsigned box_cols, unsigned box_rows,
+                                  CUtensorMapSwizzle swizzle) {
+    mb_encode_fn enc = mb_tensor_map_encoder();
+    if (enc == nullptr) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)row_elems, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)pitch_bytes};
+    cuuint32_t box[2] = {box_cols, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    return enc(map, type, 2, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+#ifdef __CUDACC__
+// Tile whose first element is (x, y) -> this CTA's shared memory; completion is
+// counted in bytes on the mbarrier.  x * element size must be a multiple of 16.
+__device__ __forceinline__ void mb_tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, void *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3}], [%4];" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(map), "r"(x), "r"(y),
+        "r"((unsigned)__cvta_generic_to_shared(bar))
+        : "memory");
+}
+#endif
