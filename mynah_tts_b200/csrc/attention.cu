@@ -172,6 +172,58 @@ __device__ __forceinline__ void quantize_shared_row(const float *vals, int width
     if (threadIdx.x == 0) *sx_out = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 0.0f;
 }
 
+// Scores of one 32-row chunk for one head, one warp.  TPP lanes share a row (a float4 of
+// the head each), 32 / TPP rows per step, TPP steps.  Each lane first forms its four-term
+// partial for all TPP rows it touches, then the TPP lanes of a row group exchange halves
+// (TPP - 1 shuffles in all, independent within a round) so that lane (sub, li) ends with
+// the full dot product of row li * (32 / TPP) + sub.  Returns that score, unscaled.
+template <int TPP>
+__device__ __forceinline__ float chunk_scores(const float *Ks, int pitch, float4 qv, int sub, int li) {
+    constexpr int RPS = 32 / TPP;
+    float a[TPP];
+#pragma unroll
+    for (int t = 0; t < TPP; ++t) {
+        const float4 kv = *reinterpret_cast<const float4 *>(Ks + (long)(t * RPS + sub) * pitch + 4 * li);
+        float x = 0.0f;
+        x = fmaf(qv.x, kv.x, x); x = fmaf(qv.y, kv.y, x);
+        x = fmaf(qv.z, kv.z, x); x = fmaf(qv.w, kv.w, x);
+        a[t] = x;
+    }
+#pragma unroll
+    for (int o = TPP / 2; o >= 1; o >>= 1) {
+        const bool upper = (li & o) != 0;     // this lane keeps the rows whose index has bit o set
+#pragma unroll
+        for (int t = 0; t < o; ++t) {
+            const float send = upper ? a[t] : a[t + o];
+            const float keep = upper ? a[t + o] : a[t];
+            a[t] = keep + __shfl_xor_sync(MB_FULL, send, o);
+        }
+    }
+    return a[0];
+}
+
+// Weighted V rows of one chunk for one head: lane (sub, li) adds rows t * (32 / TPP) + sub
+// for its float4 of the head, weights from the lane that owns each row's score; the row
+// sub-groups are then added up across the warp.
+template <int TPP>
+__device__ __forceinline__ float4 chunk_values(const float *Vs, int pitch, float e, int sub, int li) {
+    constexpr int RPS = 32 / TPP;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int t = 0; t < TPP; ++t) {
+        const float w = __shfl_sync(MB_FULL, e, sub * TPP + t);
+        const float4 vv = *reinterpret_cast<const float4 *>(Vs + (long)(t * RPS + sub) * pitch + 4 * li);
+        acc.x = fmaf(w, vv.x, acc.x); acc.y = fmaf(w, vv.y, acc.y);
+        acc.z = fmaf(w, vv.z, acc.z); acc.w = fmaf(w, vv.w, acc.w);
+    }
+#pragma unroll
+    for (int o = TPP; o < 32; o <<= 1) {
+        acc.x += __shfl_xor_sync(MB_FULL, acc.x, o); acc.y += __shfl_xor_sync(MB_FULL, acc.y, o);
+        acc.z += __shfl_xor_sync(MB_FULL, acc.z, o); acc.w += __shfl_xor_sync(MB_FULL, acc.w, o);
+    }
+    return acc;
+}
+
 // One CTA = one stream (lane) and a subset of its 32-row chunks, ALL heads: warp h
 // is head h.  A chunk's K rows (32 x width floats, contiguous in the cache) come in
 // as one tile, its V rows as another; reading whole rows keeps DRAM pages open
@@ -269,16 +321,16 @@ k_attn_rows(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CU
         }
         // scores: tpp lanes share a row, rps rows per step; lane (sub, li) keeps the score
         // of row li * rps + sub
-        float mine = -FLT_MAX;
-        for (int t = 0; t < tpp; ++t) {
-            const int i = t * rps + sub;
-            const float4 kv = *reinterpret_cast<const float4 *>(Ks + (long)i * pitch + 4 * li);
-            float a = 0.0f;
-            a = fmaf(qv.x, kv.x, a); a = fmaf(qv.y, kv.y, a);
-            a = fmaf(qv.z, kv.z, a); a = fmaf(qv.w, kv.w, a);
-            for (int o = tpp >> 1; o > 0; o >>= 1) a += __shfl_xor_sync(MB_FULL, a, o);
-            if (li == t) mine = i < cnt ? a * p.scale : -FLT_MAX;
+        float dot;
+        switch (tpp) {
+        case 32: dot = chunk_scores<32>(Ks, pitch, qv, sub, li); break;
+        case 16: dot = chunk_scores<16>(Ks, pitch, qv, sub, li); break;
+        case 8: dot = chunk_scores<8>(Ks, pitch, qv, sub, li); break;
+        case 4: dot = chunk_scores<4>(Ks, pitch, qv, sub, li); break;
+        case 2: dot = chunk_scores<2>(Ks, pitch, qv, sub, li); break;
+        default: dot = chunk_scores<1>(Ks, pitch, qv, sub, li); break;
         }
+        const float mine = li * rps + sub < cnt ? dot * p.scale : -FLT_MAX;
         const float m = warp_max(mine);
         const int my_row = li * rps + sub;
         const float e = my_row < cnt ? exp_ref<false>(mine - m) : 0.0f;
@@ -301,17 +353,14 @@ k_attn_rows(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CU
             __syncwarp();
         }
         // weighted V: the sub-groups take interleaved rows, then add up
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int t = 0; t < tpp; ++t) {
-            const int i = t * rps + sub;
-            const float w = __shfl_sync(MB_FULL, e, sub * tpp + t);
-            const float4 vv = *reinterpret_cast<const float4 *>(Vs + (long)i * pitch + 4 * li);
-            acc.x = fmaf(w, vv.x, acc.x); acc.y = fmaf(w, vv.y, acc.y);
-            acc.z = fmaf(w, vv.z, acc.z); acc.w = fmaf(w, vv.w, acc.w);
-        }
-        for (int o = tpp; o < 32; o <<= 1) {
-            acc.x += __shfl_xor_sync(MB_FULL, acc.x, o); acc.y += __shfl_xor_sync(MB_FULL, acc.y, o);
-            acc.z += __shfl_xor_sync(MB_FULL, acc.z, o); acc.w += __shfl_xor_sync(MB_FULL, acc.w, o);
+        float4 acc;
+        switch (tpp) {
+        case 32: acc = chunk_values<32>(Vs, pitch, e, sub, li); break;
+        case 16: acc = chunk_values<16>(Vs, pitch, e, sub, li); break;
+        case 8: acc = chunk_values<8>(Vs, pitch, e, sub, li); break;
+        case 4: acc = chunk_values<4>(Vs, pitch, e, sub, li); break;
+        case 2: acc = chunk_values<2>(Vs, pitch, e, sub, li); break;
+        default: acc = chunk_values<1>(Vs, pitch, e, sub, li); break;
         }
         // this chunk's partial (max, sum, weighted V) of head h
         float *part = p.partials + (((long)b * heads + h) * p.max_chunks + c) * (hw + 2);

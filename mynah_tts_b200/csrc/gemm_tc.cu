@@ -182,11 +182,20 @@ k_gemm_i8_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
         }
         mma_commit(&done_bar);                               // arrives when every MMA above has finished
     }
-    // scale and bias of this thread's row, fetched while the tensor cores work
+    // scale and bias of this thread's row, the lane scales and (residual epilogue) the
+    // values to add to, all fetched while the tensor cores work: loads issued one by one
+    // between the stores below would each pay a full memory round trip
     const long row = m0 + warp * 32 + lane;
     const bool row_ok = row < p.n;
     const float ws = row_ok ? __ldg(p.scales + row) : 0.0f;
     const float bias = (row_ok && p.bias != nullptr) ? __ldg(p.bias + row) : 0.0f;
+    float lane_scale[BN], prior[BN];
+#pragma unroll
+    for (int j = 0; j < BN; ++j) {
+        const int b = b0 + j;
+        lane_scale[j] = b < nb ? p.sx[b] : 0.0f;
+        prior[j] = (p.epilogue == MB_EPI_RESIDUAL && row_ok && b < nb) ? p.out[(long)b * p.out_stride + row] : 0.0f;
+    }
     const bool done = bar_wait(&done_bar, 0u, TC_SPIN);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     __syncthreads();
@@ -205,10 +214,10 @@ k_gemm_i8_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
             for (int j = 0; j < BN; ++j) {
                 const int b = b0 + j;
                 if (b < nb) {
-                    float y = __fmul_rn(__fmul_rn((float)v[j], ws), p.sx[b]);
+                    float y = __fmul_rn(__fmul_rn((float)v[j], ws), lane_scale[j]);
                     if (p.bias != nullptr) y = __fadd_rn(y, bias);
                     float *dst = p.out + (long)b * p.out_stride + row;
-                    if (p.epilogue == MB_EPI_RESIDUAL) *dst = __fadd_rn(*dst, y);
+                    if (p.epilogue == MB_EPI_RESIDUAL) *dst = __fadd_rn(prior[j], y);
                     else if (p.epilogue == MB_EPI_GELU)
                         *dst = p.strict ? gelu_tanh<true>(y, p.tanh_tab) : gelu_tanh<false>(y, nullptr);
                     else *dst = y;
