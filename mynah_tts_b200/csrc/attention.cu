@@ -23,6 +23,7 @@
 // stream; none when one CTA owns the stream) merges every head's chunks in index
 // order and, when the next projection wants int8 input, quantizes the merged row.
 // Results depend neither on arrival order nor on the batch a stream is stepped in.
+#include <cstdlib>
 #include "common.cuh"
 #include "launch.h"
 #include "tma.cuh"
@@ -49,15 +50,20 @@ struct AttnP {
     int heads, hw, batch, max_chunks, splits;
     long slot_rows;      // cache rows between consecutive slots (slot_stride / cache_stride)
     int box_cols, nbox;  // a 32-row tile is nbox TMA boxes of box_cols columns
+    int depth;           // ring slots per tile kind (K, V)
     float scale;
 };
 
 __device__ __forceinline__ bool lane_setup(const AttnP &p, int b, long &pos, long &valid,
-                                           float *&kc, float *&vc) {
-    if (p.n_active != nullptr && b >= *p.n_active) return false;
-    if (p.lens != nullptr) { pos = p.lens[b]; valid = pos + 1; }
+                                           float *&kc, float *&vc, long *slot_out = nullptr) {
+    // the three lane-state words are fetched together: one memory round trip, not three
+    const int live = p.n_active != nullptr ? *p.n_active : 0x7fffffff;
+    const long len = p.lens != nullptr ? (long)p.lens[b] : 0L;
+    const long slot = p.slots != nullptr ? (long)p.slots[b] : (long)b;
+    if (b >= live) return false;
+    if (slot_out != nullptr) *slot_out = slot;
+    if (p.lens != nullptr) { pos = len; valid = pos + 1; }
     else { pos = p.position; valid = p.valid; }
-    const long slot = p.slots != nullptr ? p.slots[b] : b;
     kc = p.k_cache + slot * p.slot_stride;
     vc = p.v_cache + slot * p.slot_stride;
     return true;
@@ -127,7 +133,7 @@ constexpr int CHUNK = 32;
 constexpr int FAST_THREADS = 128;
 constexpr int MERGE_MAX = 128;      // most chunks one stream may have (4096 rows)
 constexpr unsigned SPIN_LIMIT = 1u << 24;
-constexpr int ROWS_SMEM_MAX = 220 * 1024;
+constexpr int ROWS_SMEM_MAX = 225 * 1024;
 
 __device__ __forceinline__ unsigned smem_addr(const void *ptr) {
     return (unsigned)__cvta_generic_to_shared(ptr);
@@ -155,6 +161,30 @@ __device__ __forceinline__ bool mbar_wait(void *bar, unsigned parity, unsigned l
         if (done) return true;
     }
     return false;
+}
+
+// Merge one head's per-chunk partials (max, sum, weighted V[hw]) in chunk index order:
+// M = max m_s, w_s = exp(m_s - M), L = sum l_s w_s, O = sum acc_s w_s, out = O / L, the
+// sums as fma chains over s.  One warp; `ph` is in shared memory unless GLOBAL.
+template <bool GLOBAL, typename Emit>
+__device__ __forceinline__ void merge_chunks(const float *ph, int ns, int hw, int lane, float *wts, Emit emit) {
+    auto ld = [](const float *q) { return GLOBAL ? __ldcg(q) : *q; };
+    const int pitch = hw + 2;
+    for (int s = lane; s < ns; s += 32) wts[s] = ld(ph + (long)s * pitch);
+    __syncwarp();
+    float M = -FLT_MAX;
+    for (int s = 0; s < ns; ++s) M = fmaxf(M, wts[s]);
+    __syncwarp();
+    for (int s = lane; s < ns; s += 32) wts[s] = exp_ref<false>(wts[s] - M);
+    __syncwarp();
+    float L = 0.0f;
+    for (int s = 0; s < ns; ++s) L = fmaf(ld(ph + (long)s * pitch + 1), wts[s], L);
+    for (int d = lane; d < hw; d += 32) {
+        float O = 0.0f;
+#pragma unroll 4
+        for (int s = 0; s < ns; ++s) O = fmaf(ld(ph + (long)s * pitch + 2 + d), wts[s], O);
+        emit(d, L > 0.0f ? O / L : 0.0f);
+    }
 }
 
 // Quantize one merged row (already in `vals`, shared) to int8: shared by the
@@ -224,12 +254,13 @@ __device__ __forceinline__ float4 chunk_values(const float *Vs, int pitch, float
     return acc;
 }
 
-// One CTA = one stream (lane) and a subset of its 32-row chunks, ALL heads: warp h
-// is head h.  A chunk's K rows (32 x width floats, contiguous in the cache) come in
-// as one tile, its V rows as another; reading whole rows keeps DRAM pages open
-// (head-sliced 256-byte reads were measured at 29% of HBM peak).  While the warps
-// score the K tile of chunk c, the V tile of c is landing; while they accumulate
-// V, the K tile of the next chunk is landing.
+// One CTA = one stream (lane), a group of its heads (warp w is head h0 + w) and a subset
+// of its 32-row chunks.  A chunk's K rows (32 rows x the group's columns, whole rows when
+// the group is all heads) come in as one tile, its V rows as another; wide row pieces
+// keep DRAM pages open (head-sliced 256-byte reads were measured at 29% of HBM peak).
+// K and V tiles each go through a ring of p.depth slots, so while the warps work on one
+// tile the next 2 * depth - 1 are landing.
+constexpr int RING_MAX = 4;
 __global__ void __launch_bounds__(1024, 1)
 k_attn_rows(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, AttnP p) {
     mb_pdl_wait();
@@ -237,11 +268,12 @@ k_attn_rows(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CU
     extern __shared__ __align__(128) float sm[];
     __shared__ float red[33];
     __shared__ unsigned s_last;
-    __shared__ __align__(8) unsigned long long mbar[2];    // [0] K tile, [1] V tile
+    __shared__ __align__(8) unsigned long long mbar[2 * RING_MAX];   // K slots, then V slots
     const int sp = blockIdx.x, b = blockIdx.y;
     long pos, valid;
     float *kc, *vc;
-    if (!lane_setup(p, b, pos, valid, kc, vc)) return;
+    long slot;
+    if (!lane_setup(p, b, pos, valid, kc, vc, &slot)) return;
     const int ns = (int)((valid + CHUNK - 1) / CHUNK);      // chunks of this stream
     const int splits = p.splits;                             // CTAs that share a stream
     if (sp >= ns) return;
@@ -254,65 +286,99 @@ k_attn_rows(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CU
     const int rps = 32 / tpp;                       // rows a warp covers per step
     const int sub = lane / tpp, li = lane % tpp;
     const int tile_floats = CHUNK * cwidth;
-    float *Kt = sm;                                 // [nbox][CHUNK][box_cols]
-    float *Vt = sm + tile_floats;
-    float *qs = Vt + tile_floats;                   // [cwidth]
-    float *wts = qs + cwidth + warp * MERGE_MAX;    // this warp's merge weights
+    const int depth = p.depth;
+    float *Kt = sm;                                 // [depth][nbox][CHUNK][box_cols]
+    float *Vt = sm + (long)depth * tile_floats;
+    float *qs = Vt + (long)depth * tile_floats;     // [cwidth]
+    float *wts = qs + cwidth + warp * p.max_chunks; // this warp's merge weights
     const long hoff = (long)h * hw;
     const float *knew = p.k_new == nullptr ? nullptr : p.k_new + (long)b * p.q_stride;
     const float *vnew = p.v_new == nullptr ? nullptr : p.v_new + (long)b * p.q_stride;
-    const long slot = p.slots != nullptr ? p.slots[b] : b;
     const unsigned tile_bytes = (unsigned)tile_floats * 4u;
+    // this CTA's j-th tile (chunk sp + j * splits) goes to ring slot j % depth:
+    // p.nbox boxes of box_cols columns x 32 rows each
+    const int mine_chunks = sp < ns ? (ns - sp + splits - 1) / splits : 0;
+    // cache rows are read once per launch: they must not push weights, activations and
+    // code out of L2
+    const unsigned long long stream_policy = mb_l2_evict_first();
+    auto issue = [&](const CUtensorMap *map, float *ring, int j, int first_bar) {
+        const int c = sp + j * splits, rs = j % depth;
+        const int y = (int)(slot * p.slot_rows + (long)c * CHUNK);
+        float *tile = ring + (long)rs * tile_floats;
+        mbar_expect_tx(&mbar[first_bar + rs], tile_bytes);
+        for (int bx = 0; bx < p.nbox; ++bx)
+            mb_tma_load_2d_hint(tile + (long)bx * CHUNK * p.box_cols, map, h0 * hw + bx * p.box_cols, y,
+                                &mbar[first_bar + rs], stream_policy);
+    };
+    // A wait ran out at this CTA's tile `it`: flag it, give every copy still in flight one
+    // more bounded wait so none lands after this CTA's shared memory is released.
+    auto drain = [&](int it, int k_issued, int v_issued) {
+        if (threadIdx.x == 0) {
+            if (p.status != nullptr) atomicOr(p.status, 2);
+            for (int j = it; j < k_issued; ++j) mbar_wait(&mbar[j % depth], (unsigned)((j / depth) & 1), SPIN_LIMIT);
+            for (int j = it; j < v_issued; ++j)
+                mbar_wait(&mbar[depth + j % depth], (unsigned)((j / depth) & 1), SPIN_LIMIT);
+        }
+        __syncthreads();
+    };
+    // the first tiles start before anything else of the prologue: the copy engine works
+    // while the threads fetch q and append the new row
     if (threadIdx.x == 0) {
-        mbar_init(&mbar[0], 1u);
-        mbar_init(&mbar[1], 1u);
+        for (int i = 0; i < 2 * depth; ++i) mbar_init(&mbar[i], 1u);
+        for (int j = 0; j < depth && j < mine_chunks; ++j) {
+            issue(&kmap, Kt, j, 0);
+            issue(&vmap, Vt, j, depth);
+        }
     }
-    for (int d = threadIdx.x; d < cwidth; d += blockDim.x) {
-        const long col = (long)h0 * hw + d;
-        qs[d] = p.q[(long)b * p.q_stride + col];
-        if (knew != nullptr && sp == 0) {   // one CTA per (stream, head group) appends; readers
-                                            // of row `pos` take it from the new row, never
-                                            // from the cache
-            kc[pos * p.cache_stride + col] = knew[col];
-            vc[pos * p.cache_stride + col] = vnew[col];
+    // q into shared memory and the new K/V row into the cache: all loads of a batch are
+    // issued before its stores, so they overlap instead of queueing behind one another.
+    // One CTA per (stream, head group) appends; readers of row `pos` take it from the new
+    // row, never from the cache.
+    const bool append = knew != nullptr && sp == 0;
+    for (int d0 = threadIdx.x; d0 < cwidth; d0 += 4 * blockDim.x) {
+        float qq[4], kk[4], vv[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int d = d0 + u * blockDim.x;
+            const long col = (long)h0 * hw + d;
+            if (d < cwidth) {
+                qq[u] = p.q[(long)b * p.q_stride + col];
+                if (append) { kk[u] = knew[col]; vv[u] = vnew[col]; }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int d = d0 + u * blockDim.x;
+            const long col = (long)h0 * hw + d;
+            if (d < cwidth) {
+                qs[d] = qq[u];
+                if (append) {
+                    kc[pos * p.cache_stride + col] = kk[u];
+                    vc[pos * p.cache_stride + col] = vv[u];
+                }
+            }
         }
     }
     __syncthreads();
-    // tile of chunk c: p.nbox boxes of box_cols columns x 32 rows each
-    auto issue = [&](const CUtensorMap *map, float *tile, int c, int which) {
-        const int y = (int)(slot * p.slot_rows + (long)c * CHUNK);
-        mbar_expect_tx(&mbar[which], tile_bytes);
-        for (int bx = 0; bx < p.nbox; ++bx)
-            mb_tma_load_2d(tile + (long)bx * CHUNK * p.box_cols, map, h0 * hw + bx * p.box_cols, y,
-                           &mbar[which]);
-    };
-    if (threadIdx.x == 0) {
-        issue(&kmap, Kt, sp, 0);
-        issue(&vmap, Vt, sp, 1);
-    }
     // this head's slice inside a tile: box, column offset, row pitch
     const long slice = (long)((warp * hw) / p.box_cols) * CHUNK * p.box_cols + (warp * hw) % p.box_cols;
     const int pitch = p.box_cols;
     const float4 qv = reinterpret_cast<const float4 *>(qs + warp * hw)[li];
-    int it = 0;
-    for (int c = sp; c < ns; c += splits, ++it) {
-        const unsigned parity = (unsigned)(it & 1);
+    bool failed = false;                                     // a tile never landed (CTA-uniform)
+    for (int it = 0; it < mine_chunks; ++it) {
+        const int c = sp + it * splits, rs = it % depth;
+        const unsigned parity = (unsigned)((it / depth) & 1);
+        const int issued = min(mine_chunks, it + depth);     // tiles of each kind issued so far
         const long s0 = (long)c * CHUNK;
         const int cnt = (int)min((long)CHUNK, valid - s0);
         const bool fresh = knew != nullptr && pos >= s0 && pos < s0 + cnt;
         // ---- K tile ---------------------------------------------------------------------
-        if (__syncthreads_or(mbar_wait(&mbar[0], parity, SPIN_LIMIT) ? 0 : 1)) {
-            // a tile never landed: flag it, give the copies one more bounded wait so none
-            // is in flight when this CTA's shared memory is released, and leave together.
-            if (threadIdx.x == 0) {
-                if (p.status != nullptr) atomicOr(p.status, 2);
-                mbar_wait(&mbar[0], parity, SPIN_LIMIT);
-                mbar_wait(&mbar[1], parity, SPIN_LIMIT);
-            }
-            __syncthreads();
-            return;
+        if (__syncthreads_or(mbar_wait(&mbar[rs], parity, SPIN_LIMIT) ? 0 : 1)) {
+            drain(it, issued, issued);
+            failed = true;
+            break;
         }
-        float *Ks = Kt + slice;
+        float *Ks = Kt + (long)rs * tile_floats + slice;
         if (fresh) {
             // the row being appended now may not have reached the cache when the tile was
             // read: take it from the new K row itself
@@ -336,18 +402,15 @@ k_attn_rows(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CU
         const float e = my_row < cnt ? exp_ref<false>(mine - m) : 0.0f;
         const float l = warp_sum(e);
         __syncthreads();                                     // every warp is done with the K tile
-        if (threadIdx.x == 0 && c + splits < ns) issue(&kmap, Kt, c + splits, 0);
+        const bool more = it + depth < mine_chunks;
+        if (threadIdx.x == 0 && more) issue(&kmap, Kt, it + depth, 0);
         // ---- V tile ---------------------------------------------------------------------
-        if (__syncthreads_or(mbar_wait(&mbar[1], parity, SPIN_LIMIT) ? 0 : 1)) {
-            if (threadIdx.x == 0) {
-                if (p.status != nullptr) atomicOr(p.status, 2);
-                mbar_wait(&mbar[1], parity, SPIN_LIMIT);
-                if (c + splits < ns) mbar_wait(&mbar[0], parity ^ 1u, SPIN_LIMIT);
-            }
-            __syncthreads();
-            return;
+        if (__syncthreads_or(mbar_wait(&mbar[depth + rs], parity, SPIN_LIMIT) ? 0 : 1)) {
+            drain(it, more ? issued + 1 : issued, issued);
+            failed = true;
+            break;
         }
-        float *Vs = Vt + slice;
+        float *Vs = Vt + (long)rs * tile_floats + slice;
         if (fresh) {
             for (int d = lane; d < hw; d += 32) Vs[(pos - s0) * pitch + d] = vnew[hoff + d];
             __syncwarp();
@@ -370,50 +433,71 @@ k_attn_rows(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CU
         }
         if (lane == 0) { part[0] = m; part[1] = l; }
         __syncthreads();                                     // every warp is done with the V tile
-        if (threadIdx.x == 0 && c + splits < ns) issue(&vmap, Vt, c + splits, 1);
+        if (threadIdx.x == 0 && more) issue(&vmap, Vt, it + depth, depth);
     }
-    // ---- the head group's last CTA merges its heads, chunks in index order -------------
-    __threadfence();
-    __syncthreads();
     const int groups = (int)gridDim.z;
-    if (min(ns, splits) > 1) {                               // several CTAs shared this head group
-        if (threadIdx.x == 0) {
-            unsigned *ctr = p.counters + (long)b * groups + blockIdx.z;
-            const unsigned prev = atomicAdd(ctr, 1u);
-            s_last = prev == (unsigned)min(ns, splits) - 1u;
-            if (s_last) *ctr = 0u;
-        }
-        __syncthreads();
-        if (!s_last) return;
-        __threadfence();
-    }
     const bool quant = p.qx != nullptr;
     float *outrow = p.out == nullptr ? nullptr : p.out + (long)b * p.out_stride;
-    float *vals = Kt;                                        // merged row, for the quantization pass
     // staging of the merged row when its head groups sit in different CTAs
-    float *merged = p.partials + (long)p.batch * heads * p.max_chunks * (hw + 2) + (long)b * width;
+    float *merged = p.partials == nullptr
+                        ? nullptr
+                        : p.partials + (long)p.batch * heads * p.max_chunks * (hw + 2) + (long)b * width;
+    const int per_head = ns * (hw + 2);
+    float *vals;                                             // merged row, for the quantization pass
+    if (failed) return;
     {
-        const float *ph = p.partials + ((long)b * heads + h) * p.max_chunks * (hw + 2);
-        for (int s = lane; s < ns; s += 32) wts[s] = __ldcg(ph + (long)s * (hw + 2));
-        __syncwarp();
-        float M = -FLT_MAX;
-        for (int s = 0; s < ns; ++s) M = fmaxf(M, wts[s]);
-        __syncwarp();
-        for (int s = lane; s < ns; s += 32) wts[s] = exp_ref<false>(wts[s] - M);
-        __syncwarp();
-        float L = 0.0f;
-        for (int s = 0; s < ns; ++s) L = fmaf(__ldcg(ph + (long)s * (hw + 2) + 1), wts[s], L);
-        for (int d = lane; d < hw; d += 32) {
-            float O = 0.0f;
-#pragma unroll 4
-            for (int s = 0; s < ns; ++s) O = fmaf(__ldcg(ph + (long)s * (hw + 2) + 2 + d), wts[s], O);
-            const float o = L > 0.0f ? O / L : 0.0f;
+        // ---- the head group's last CTA merges its heads ------------------------------------
+        __threadfence();
+        __syncthreads();
+        if (min(ns, splits) > 1) {                           // several CTAs shared this head group
+            if (threadIdx.x == 0) {
+                unsigned *ctr = p.counters + (long)b * groups + blockIdx.z;
+                const unsigned prev = atomicAdd(ctr, 1u);
+                s_last = prev == (unsigned)min(ns, splits) - 1u;
+                if (s_last) *ctr = 0u;
+            }
+            __syncthreads();
+            if (!s_last) return;
+            __threadfence();
+        }
+        // Every tile has been consumed, so the tile memory is free: bring this head group's
+        // partials into it with one round of independent, coalesced loads (walking them from
+        // global memory inside the ordered sums would pay one memory round trip per chunk),
+        // then merge out of shared memory.  The merged row for the quantization pass sits
+        // behind them.  Streams too long for that keep the partials in global memory.
+        const long tile_room = 2L * depth * tile_floats;
+        const bool staged = (long)hg * per_head + width <= tile_room;
+        float *stage = Kt;
+        vals = staged ? Kt + (long)hg * per_head : Kt;
+        if (staged) {
+            const float *src = p.partials + ((long)b * heads + h0) * p.max_chunks * (hw + 2);
+            const long head_pitch = (long)p.max_chunks * (hw + 2);
+            const int total = hg * per_head;
+            for (int i0 = threadIdx.x; i0 < total; i0 += 8 * blockDim.x) {
+                float v[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int i = i0 + u * blockDim.x;
+                    const int w = i / per_head, o = i - w * per_head;
+                    if (i < total) v[u] = __ldcg(src + w * head_pitch + o);
+                }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int i = i0 + u * blockDim.x;
+                    if (i < total) stage[i] = v[u];
+                }
+            }
+            __syncthreads();
+        }
+        auto emit = [&](int d, float o) {
             if (outrow != nullptr) outrow[hoff + d] = o;
             if (quant) {
-                if (groups == 1) vals[hoff + d] = o;
+                if (groups == 1) vals[hoff + d] = o;         // behind the staged partials
                 else merged[hoff + d] = o;
             }
-        }
+        };
+        if (staged) merge_chunks<false>(stage + (long)warp * per_head, ns, hw, lane, wts, emit);
+        else merge_chunks<true>(p.partials + ((long)b * heads + h) * p.max_chunks * (hw + 2), ns, hw, lane, wts, emit);
     }
     if (!quant) return;
     // ---- the stream's last head group quantizes the whole row ---------------------------
@@ -543,31 +627,39 @@ extern "C" int mb_attention(const mb_attn_args *a, mb_stream stream) {
     // rows per tile keep DRAM pages open), fewer when few streams must still fill the SMs
     int hg = p.heads;
     if (a->sm_count > 0 && p.heads <= 32) {
-        const int want = p.batch >= 32 ? p.heads : (p.batch >= 8 ? (p.heads + 2) / 3 : 1);
+        int want = p.batch >= 8 ? (p.heads + 2) / 3 : 1;
+        if (p.batch >= 32) want = p.heads;   // whole cache rows per tile (measured faster than half rows with a deeper ring)
         for (hg = want < 1 ? 1 : want; hg < p.heads && p.heads % hg != 0; ++hg) {}
     }
     int hpb = 0;   // heads per TMA box: a box holds whole heads and at most 256 columns
     for (int c = p.hw > 0 ? 256 / p.hw : 0; c >= 1 && hpb == 0; --c)
         if (c <= hg && hg % c == 0) hpb = c;
     const size_t cwidth = (size_t)hg * p.hw;
-    const size_t rows_floats = 2u * CHUNK * cwidth + cwidth + (size_t)hg * MERGE_MAX;
+    const size_t tile_bytes = (size_t)CHUNK * cwidth * sizeof(float);
+    // CTAs per stream: about one CTA per SM in all; with many streams one CTA walks
+    // all chunks of its stream
+    const long groups = p.heads / hg;
+    long splits = a->sm_count > 0 ? a->sm_count / ((long)p.batch * groups) : p.max_chunks;
+    if (hg < 4) splits = p.max_chunks;        // few warps per CTA: one chunk each, many CTAs
+    if (splits > p.max_chunks) splits = p.max_chunks;
+    if (splits < 1) splits = 1;
+    const long per_cta = (p.max_chunks + splits - 1) / splits;   // most tiles of a kind one CTA walks
+    const size_t fixed_bytes = (cwidth + (size_t)hg * p.max_chunks) * sizeof(float);
+    long depth = ((long)ROWS_SMEM_MAX - (long)fixed_bytes) / (long)(2u * tile_bytes);
+    if (depth > per_cta) depth = per_cta;
+    if (depth > RING_MAX) depth = RING_MAX;
+    const size_t rows_bytes = 2u * (size_t)(depth < 1 ? 1 : depth) * tile_bytes + fixed_bytes;
     const bool chunked = !a->strict && hpb > 0 && (p.hw % 4) == 0 && is_pow2(p.hw / 4) && p.hw / 4 <= 32 &&
                          p.heads <= 32 && p.max_chunks <= MERGE_MAX &&
-                         rows_floats * sizeof(float) <= (size_t)ROWS_SMEM_MAX && 64u * cwidth >= width &&
+                         depth >= 1 && rows_bytes <= (size_t)ROWS_SMEM_MAX && 64u * cwidth >= width &&
                          (p.cache_stride % 4) == 0 && (p.q_stride % 4) == 0 && (p.slot_stride % 4) == 0 &&
                          (a->batch == 1 || a->cache_rows != 0) && (p.slot_stride % p.cache_stride) == 0 &&
                          (((uintptr_t)a->k_cache | (uintptr_t)a->v_cache | (uintptr_t)a->q |
                            (uintptr_t)a->k_new | (uintptr_t)a->v_new) & 15u) == 0;
     if (chunked) {
         if (a->partials == nullptr || a->counters == nullptr) return (int)cudaErrorInvalidValue;
-        // CTAs per stream: about one CTA per SM in all; with many streams one CTA walks
-        // all chunks of its stream
-        const long groups = p.heads / hg;
-        long splits = a->sm_count > 0 ? a->sm_count / ((long)p.batch * groups) : p.max_chunks;
-        if (hg < 4) splits = p.max_chunks;        // few warps per CTA: one chunk each, many CTAs
-        if (splits > p.max_chunks) splits = p.max_chunks;
-        if (splits < 1) splits = 1;
         p.splits = (int)splits;
+        p.depth = (int)depth;
         p.box_cols = hpb * p.hw;
         p.nbox = hg / hpb;
         p.slot_rows = p.slot_stride / p.cache_stride;
@@ -580,7 +672,7 @@ extern "C" int mb_attention(const mb_attn_args *a, mb_stream stream) {
                             (size_t)p.cache_stride * 4u, (unsigned)p.box_cols, CHUNK, CU_TENSOR_MAP_SWIZZLE_NONE))
             return (int)cudaErrorInvalidValue;
         mb_launch(k_attn_rows, dim3((unsigned)splits, (unsigned)p.batch, (unsigned)groups),
-                  dim3((unsigned)hg * 32u), rows_floats * sizeof(float), s, kmap, vmap, p);
+                  dim3((unsigned)hg * 32u), rows_bytes, s, kmap, vmap, p);
         return mb_check_launch();
     }
     if (a->out == nullptr) return (int)cudaErrorInvalidValue;
@@ -716,6 +808,7 @@ int mynah_b200_self_attention_static(const float *dev_qkv, float *dev_k_cache, f
     p.batch = 1;
     p.max_chunks = (int)chunks_for(valid);
     p.splits = p.max_chunks;           // one chunk per CTA: partials go through the static scratch
+    p.depth = 1;
     p.scale = scale;
     int hpb = 0;
     for (int c = 256 / p.hw; c >= 1 && hpb == 0; --c)

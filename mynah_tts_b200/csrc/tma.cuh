@@ -50,4 +50,26 @@ __device__ __forceinline__ void mb_tma_load_2d(void *dst, const CUtensorMap *map
         "r"((unsigned)__cvta_generic_to_shared(bar))
         : "memory");
 }
+
+// Same copy with an L2 eviction-priority hint.  `mb_l2_evict_first()` marks data read once
+// per launch (a streamed cache), so that it does not push longer-lived lines (weights,
+// activations, code) out of L2.
+__device__ __forceinline__ unsigned long long mb_l2_evict_first() {
+    unsigned long long policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    return policy;
+}
+__device__ __forceinline__ unsigned long long mb_l2_evict_last() {
+    unsigned long long policy;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(policy));
+    return policy;
+}
+__device__ __forceinline__ void mb_tma_load_2d_hint(void *dst, const CUtensorMap *map, int x, int y, void *bar,
+                                                    unsigned long long policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint "
+        "[%0], [%1, {%2, %3}], [%4], %5;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(map), "r"(x), "r"(y),
+        "r"((unsigned)__cvta_generic_to_shared(bar)), "l"(policy)
+        : "memory");
+}
 #endif
