@@ -23,7 +23,6 @@
 // stream; none when one CTA owns the stream) merges every head's chunks in index
 // order and, when the next projection wants int8 input, quantizes the merged row.
 // Results depend neither on arrival order nor on the batch a stream is stepped in.
-#include <cstdlib>
 #include "common.cuh"
 #include "launch.h"
 #include "tma.cuh"
@@ -51,6 +50,7 @@ struct AttnP {
     long slot_rows;      // cache rows between consecutive slots (slot_stride / cache_stride)
     int box_cols, nbox;  // a 32-row tile is nbox TMA boxes of box_cols columns
     int depth;           // ring slots per tile kind (K, V)
+    int early;           // first tiles are requested before the dependency wait
     float scale;
 };
 
@@ -263,8 +263,15 @@ __device__ __forceinline__ float4 chunk_values(const float *Vs, int pitch, float
 constexpr int RING_MAX = 4;
 __global__ void __launch_bounds__(1024, 1)
 k_attn_rows(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, AttnP p) {
-    mb_pdl_wait();
-    mb_pdl_trigger();
+    // With p.early the dependency wait comes AFTER the first tiles are requested.  The caller
+    // then vouches that what is read before it (lane state, cache rows below `pos`) was
+    // written at least two launches back: every launch waits for its predecessor before it
+    // lets its successor start, so all of that is complete, and only q and the new K/V rows
+    // come from the immediate predecessor.
+    if (!p.early) {
+        mb_pdl_wait();
+        mb_pdl_trigger();
+    }
     extern __shared__ __align__(128) float sm[];
     __shared__ float red[33];
     __shared__ unsigned s_last;
@@ -329,6 +336,10 @@ k_attn_rows(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CU
             issue(&kmap, Kt, j, 0);
             issue(&vmap, Vt, j, depth);
         }
+    }
+    if (p.early) {
+        mb_pdl_wait();
+        mb_pdl_trigger();
     }
     // q into shared memory and the new K/V row into the cache: all loads of a batch are
     // issued before its stores, so they overlap instead of queueing behind one another.
@@ -660,6 +671,7 @@ extern "C" int mb_attention(const mb_attn_args *a, mb_stream stream) {
         if (a->partials == nullptr || a->counters == nullptr) return (int)cudaErrorInvalidValue;
         p.splits = (int)splits;
         p.depth = (int)depth;
+        p.early = a->early_prefetch ? 1 : 0;
         p.box_cols = hpb * p.hw;
         p.nbox = hg / hpb;
         p.slot_rows = p.slot_stride / p.cache_stride;
@@ -809,6 +821,7 @@ int mynah_b200_self_attention_static(const float *dev_qkv, float *dev_k_cache, f
     p.max_chunks = (int)chunks_for(valid);
     p.splits = p.max_chunks;           // one chunk per CTA: partials go through the static scratch
     p.depth = 1;
+    p.early = 0;
     p.scale = scale;
     int hpb = 0;
     for (int c = 256 / p.hw; c >= 1 && hpb == 0; --c)

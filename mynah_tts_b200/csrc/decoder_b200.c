@@ -449,6 +449,7 @@ static int enqueue(mb_decoder *d, size_t bucket, int mode, unsigned *count) {
         a.counters = d->counters;
         a.status = d->d_status;
         a.sm_count = st->sm_count;
+        a.early_prefetch = 1;   /* lane state: previous step; cache rows below the position: earlier steps */
         P(PC_ATTN_SELF, mb_attention(&a, s));
         *count += (st->strict && q) ? 2u : 1u;
         P(PC_O_SELF, product(d, &L->o_self, NULL, d->attn, d->x, W, nb, MB_EPI_RESIDUAL, count));
@@ -480,6 +481,7 @@ static int enqueue(mb_decoder *d, size_t bucket, int mode, unsigned *count) {
         a.counters = d->counters;
         a.status = d->d_status;
         a.sm_count = st->sm_count;
+        a.early_prefetch = 1;   /* the cross cache is written once, when the slot is loaded */
         P(PC_ATTN_CROSS, mb_attention(&a, s));
         *count += (st->strict && q) ? 2u : 1u;
         P(PC_O_CROSS, product(d, &L->o_cross, NULL, d->xctx, d->x, W, nb, MB_EPI_RESIDUAL, count));

@@ -21,6 +21,9 @@
 // MMAs reading it have finished.  (Splitting K across CTAs with integer atomics
 // was measured at twice the time of an unsplit launch and was dropped.)
 //
+// The first weight stages are requested BEFORE the programmatic-dependency wait: weights
+// are never written by a preceding launch, so they can land while it finishes.
+//
 // Every wait is bounded: if a barrier does not complete within the limit the
 // CTA raises a status bit, waits once more for its copies, frees its TMEM and
 // returns.
@@ -114,8 +117,6 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, int (&v)[16]) {
 
 __global__ void __launch_bounds__(TC_THREADS)
 k_gemm_i8_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcP p) {
-    mb_pdl_wait();
-    mb_pdl_trigger();
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) unsigned long long full_bar[MAX_STAGES];
     __shared__ __align__(8) unsigned long long empty_bar[MAX_STAGES];
@@ -123,9 +124,7 @@ k_gemm_i8_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
     __shared__ uint32_t s_tmem;
     __shared__ unsigned s_fail;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int nb = p.n_active != nullptr ? min(p.batch, *p.n_active) : p.batch;
     const int b0 = blockIdx.y * BN;
-    if (b0 >= nb) return;                                   // whole CTA: no live lane in this tile
     const long m0 = (long)blockIdx.x * TM;
     const int nchunks = (int)((p.k + KC - 1) / KC);
     // operands need 1024-byte alignment for the 128-byte swizzle
@@ -150,16 +149,46 @@ k_gemm_i8_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = s_tmem;
 
+    // Weights do not depend on the launches before this one: their first stages are
+    // requested before the dependency wait, so they land while the predecessor finishes.
+    const unsigned stage_bytes = (unsigned)(A_BYTES + B_BYTES);
+    const int first = min(nchunks, MAX_STAGES);             // stages that need no release to fill
     if (warp == 0 && lane == 0) {
-        // producer: chunk c goes to stage c % 8 once the MMAs of chunk c - 8 released it
-        for (int c = 0; c < nchunks; ++c) {
+        for (int c = 0; c < first; ++c) {
+            bar_expect(&full_bar[c], stage_bytes);
+            tma_load_2d(As + (size_t)c * A_BYTES, &map_w, c * KC, (int)m0, &full_bar[c]);
+        }
+    }
+    mb_pdl_wait();
+    mb_pdl_trigger();
+    const int nb = p.n_active != nullptr ? min(p.batch, *p.n_active) : p.batch;
+    if (b0 >= nb) {
+        // no live lane in this tile: let the requested weight stages land (the activation
+        // halves are sent too, so each barrier completes), then give the TMEM back
+        if (warp == 0 && lane == 0) {
+            for (int c = 0; c < first; ++c) {
+                tma_load_2d(Bs + (size_t)c * B_BYTES, &map_x, c * KC, b0, &full_bar[c]);
+                bar_wait(&full_bar[c], 0u, TC_SPIN);
+            }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        if (warp == 0)
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+        return;
+    }
+    if (warp == 0 && lane == 0) {
+        // the activation halves of the first stages, then the rest of the K walk:
+        // chunk c goes to stage c % 8 once the MMAs of chunk c - 8 released it
+        for (int c = 0; c < first; ++c) tma_load_2d(Bs + (size_t)c * B_BYTES, &map_x, c * KC, b0, &full_bar[c]);
+        for (int c = first; c < nchunks; ++c) {
             const int s = c % MAX_STAGES;
-            if (c >= MAX_STAGES && !bar_wait(&empty_bar[s], (unsigned)((c / MAX_STAGES - 1) & 1), TC_SPIN)) {
+            if (!bar_wait(&empty_bar[s], (unsigned)((c / MAX_STAGES - 1) & 1), TC_SPIN)) {
                 s_fail = 1u;
                 if (p.status != nullptr) atomicOr(p.status, 8);
                 break;
             }
-            bar_expect(&full_bar[s], (unsigned)(A_BYTES + B_BYTES));
+            bar_expect(&full_bar[s], stage_bytes);
             tma_load_2d(As + (size_t)s * A_BYTES, &map_w, c * KC, (int)m0, &full_bar[s]);
             tma_load_2d(Bs + (size_t)s * B_BYTES, &map_x, c * KC, b0, &full_bar[s]);
         }

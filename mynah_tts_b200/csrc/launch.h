@@ -152,6 +152,9 @@ typedef struct {
     unsigned *counters;
     int sm_count;         /* SMs of the device (sizes the split); 0 = one chunk per CTA */
     int *status;          /* device error word (nonzero = bad argument seen) */
+    int early_prefetch;   /* 1: lane state and cache rows below the position were written at least two
+                           * launches before this one, so the kernel may request its first cache tiles
+                           * before it waits for its predecessor (programmatic dependent launch) */
 } mb_attn_args;
 int mb_attention(const mb_attn_args *args, mb_stream stream);
 size_t mb_attention_scratch_floats(size_t batch, size_t heads, size_t max_valid, size_t head_width);
