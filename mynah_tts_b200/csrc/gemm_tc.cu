@@ -8,7 +8,7 @@
 // gemv.cu and as the reference, whatever the batch.
 //
 // One CTA = one tile of 128 weight rows x BN lanes over a range of K:
-//   * TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast) brings
+//   * TMA (cp.async.bulk.tensor, 128-byte swizzle, into this CTA only) brings
 //     [128 rows x 128 K-bytes] of W and [BN lanes x 128 K-bytes] of the quantized
 //     activations into shared memory, one stage per 128-byte K chunk, each
 //     stage completing on its own mbarrier;

@@ -1,7 +1,7 @@
 // Tensor-map (TMA) helpers shared by the kernels that stage tiles with
 // cp.async.bulk.tensor: a host-side encoder reached through the runtime's driver
 // entry point (no link-time dependency on the driver library) and the device-side
-// 2-D tile load.  No load here uses cluster multicast.
+// 2-D tile load, each into the issuing CTA only.
 #pragma once
 
 #include <cuda.h>
