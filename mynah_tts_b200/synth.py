@@ -6,7 +6,9 @@ and layer structure (src/graph.c:2978-3079 in mynah-tts): per layer four
 gain-only LayerNorms, qkv_net [3W,W], o_net [W,W], cross q_net [xw,W],
 kv_net [2xw,W], o_net [W,xw], FFN proj [4W,W,1] and o_net [W,4W,1]; plus
 position embeddings, the output norm, one embedding table and one logit head
-(weight + bias) per stacked codebook stream.
+(weight + bias) per stacked codebook stream; optionally the local transformer
+(src/graph.c:1021-1056): its position rows and per layer two norms, qkv_net,
+o_net and the two FFN matrices.
 
 Distributions: linear weights, embeddings and position rows ~ N(0, 0.02);
 LayerNorm gains ~ N(1, 0.01); head biases ~ N(0, 0.01); text-encoder memory
@@ -34,6 +36,11 @@ class DecoderShape:
     vocab: int = 2048
     codebook_size: int = 2016
     eos_id: int = 2017
+    local_layers: int = 0      # layers of the local transformer (0: none; the real model has 2)
+
+    @property
+    def local_positions(self) -> int:
+        return self.tables + 1   # rows the local transformer can attend (src/graph.c:1200)
 
     @property
     def head_width(self) -> int:
@@ -48,6 +55,21 @@ MAGPIE_357M = DecoderShape()
 # Small shape for fast CPU tests: same structure, 12 heads of 16.
 TINY = DecoderShape(layers=2, width=192, xattn_width=32, memory_length=24,
                     max_positions=96, tables=4, vocab=64, codebook_size=56, eos_id=57)
+# The same two with a local transformer; the full size has the real model's 16 stacked
+# streams (8 codebooks x 2 frames) and 2 local layers.
+MAGPIE_357M_LOCAL = DecoderShape(tables=16, local_layers=2)
+TINY_LOCAL = DecoderShape(layers=2, width=192, xattn_width=32, memory_length=24,
+                          max_positions=96, tables=4, vocab=64, codebook_size=56, eos_id=57,
+                          local_layers=2)
+
+LOCAL_LAYER_TENSORS = (
+    ("norm_self.weight", "gain"),
+    ("norm_pos_ff.weight", "gain"),
+    ("self_attention.qkv_net.weight", "qkv"),
+    ("self_attention.o_net.weight", "o_self"),
+    ("pos_ff.proj.conv.weight", "ffn_up"),
+    ("pos_ff.o_net.conv.weight", "ffn_down"),
+)
 
 LAYER_TENSORS = (
     ("norm_self.weight", "gain"),
@@ -96,6 +118,13 @@ class SynthModel:
     def head_bias(self, table: int) -> np.ndarray:
         return self.tensors[f"local_transformer_out_projections.{table}.bias"]
 
+    def local_layer(self, index: int, suffix: str) -> np.ndarray:
+        return self.tensors[f"local_transformer.layers.{index}.{suffix}"]
+
+    @property
+    def local_position(self) -> np.ndarray:
+        return self.tensors["local_transformer.position_embeddings.weight"]
+
     @property
     def position(self) -> np.ndarray:
         return self.tensors["decoder.position_embeddings.weight"]
@@ -127,6 +156,14 @@ def make_model(shape: DecoderShape = MAGPIE_357M, seed: int = 0) -> SynthModel:
         t[f"local_transformer_out_projections.{table}.weight"] = normal(
             0.0, 0.02, (shape.vocab, shape.width))
         t[f"local_transformer_out_projections.{table}.bias"] = normal(0.0, 0.01, (shape.vocab,))
+    # Local transformer tensors are drawn last, so a shape with and without them shares every
+    # other tensor (names and shapes: src/graph.c:1021-1056).
+    if shape.local_layers:
+        t["local_transformer.position_embeddings.weight"] = normal(0.0, 0.02, (shape.local_positions, shape.width))
+        for layer in range(shape.local_layers):
+            for suffix, kind in LOCAL_LAYER_TENSORS:
+                name = f"local_transformer.layers.{layer}.{suffix}"
+                t[name] = normal(1.0, 0.01, shapes[kind]) if kind == "gain" else normal(0.0, 0.02, shapes[kind])
     return SynthModel(shape=shape, seed=seed, tensors=t)
 
 

@@ -210,3 +210,111 @@ REF_EXPORT int ref_greedy_decode(ref_model *r, ref_decoder **decoders, size_t ba
     free(frame_codes);
     return rc;
 }
+
+/* ------------------------------------------------------ local transformer */
+typedef struct {
+    local_frame_state state;
+} ref_local;
+
+/* model.json's local_transformer_layers (src/mynah_tts.c:230-231). */
+REF_EXPORT void ref_model_set_local_layers(ref_model *r, unsigned layers) {
+    r->model.info.local_transformer_layers = layers;
+}
+
+REF_EXPORT ref_local *ref_local_new(ref_model *r, size_t top_count, char *error, size_t cap) {
+    ref_local *l = (ref_local *)calloc(1, sizeof(*l));
+    if (l == NULL) return NULL;
+    if (local_frame_state_init(&r->model, &l->state, top_count, error, cap) != 0) {
+        free(l);
+        return NULL;
+    }
+    return l;
+}
+
+REF_EXPORT void ref_local_free(ref_local *l) {
+    if (l == NULL) return;
+    local_frame_state_free(&l->state);
+    free(l);
+}
+
+REF_EXPORT size_t ref_local_length(const ref_local *l) { return l->state.cache.length; }
+REF_EXPORT void ref_local_set_length(ref_local *l, size_t n) { l->state.cache.length = n; }
+REF_EXPORT float *ref_local_k(ref_local *l) { return l->state.cache.k; }
+REF_EXPORT float *ref_local_v(ref_local *l) { return l->state.cache.v; }
+REF_EXPORT size_t ref_local_capacity(const ref_local *l) { return l->state.cache.capacity; }
+
+/* inputs/outs are [batch][width] contiguous (src/graph.c:1234-1238 takes
+ * pointer arrays). */
+REF_EXPORT int ref_local_step_batch(ref_model *r, ref_local **locals, const float *inputs,
+                                    float *outs, size_t batch, char *error, size_t cap) {
+    if (batch == 0u || batch > MYNAH_MAX_BATCH) return -1;
+    const size_t width = r->model.info.hidden_dim;
+    local_cache *caches[MYNAH_MAX_BATCH];
+    local_workspace *workspaces[MYNAH_MAX_BATCH];
+    const float *in[MYNAH_MAX_BATCH];
+    float *out[MYNAH_MAX_BATCH];
+    for (size_t b = 0; b < batch; ++b) {
+        caches[b] = &locals[b]->state.cache;
+        workspaces[b] = &locals[b]->state.workspace;
+        in[b] = inputs + b * width;
+        out[b] = outs + b * width;
+    }
+    batch_scratch scratch;
+    if (batch_scratch_init(&scratch, batch, caches[0]->ffn_width, error, cap) != 0) return -1;
+    const int rc = local_step_batch(&r->model, caches, workspaces, in, out, batch,
+                                    batch > 1u ? &scratch : NULL, error, cap);
+    batch_scratch_free(&scratch);
+    return rc;
+}
+
+/* One stacked frame for `batch` requests through sample_local_frame_batch
+ * (src/graph.c:1374-1656).  decoder_last is [batch][width]; rng_states are
+ * updated in place; allow_eos[b] == 0 forbids EOS the way a request below its
+ * minimum length does.  codes_out is [batch][streams] with stream =
+ * fs * codebooks + codebook (the reference writes codes[codebook * stride +
+ * offset + fs]); saw_eos/eos_frame as the reference reports them (-1: none). */
+REF_EXPORT int ref_local_frame(ref_model *r, ref_local **locals, size_t batch,
+                               const float *decoder_last, const float *temperature,
+                               const unsigned *topk, uint64_t *rng_states, const int *allow_eos,
+                               unsigned *codes_out, int *saw_eos, long *eos_frame,
+                               char *error, size_t cap) {
+    if (batch == 0u || batch > MYNAH_MAX_BATCH) return -1;
+    const size_t width = r->model.info.hidden_dim;
+    const size_t codebooks = r->model.info.codebook_count;
+    const size_t stacking = r->model.info.frame_stacking_factor;
+    const size_t streams = codebooks * stacking;
+    local_batch_item items[MYNAH_MAX_BATCH];
+    unsigned *scratch_codes = (unsigned *)calloc(batch * streams, sizeof(unsigned));
+    if (scratch_codes == NULL) return -1;
+    for (size_t b = 0; b < batch; ++b) {
+        local_batch_item *it = &items[b];
+        memset(it, 0, sizeof(*it));
+        it->state = &locals[b]->state;
+        it->decoder_last = decoder_last + b * width;
+        it->codes = scratch_codes + b * streams;   /* [codebooks][stacking] */
+        it->raw_offset = 0u;
+        it->code_stride = stacking;
+        it->generated_raw_length = allow_eos[b] ? 1u : 0u;
+        it->min_raw_length = 1u;
+        it->temperature = temperature[b];
+        it->topk = topk[b];
+        it->rng_state = &rng_states[b];
+    }
+    batch_scratch scratch;
+    if (batch_scratch_init(&scratch, batch, locals[0]->state.cache.ffn_width, error, cap) != 0) {
+        free(scratch_codes);
+        return -1;
+    }
+    const int rc = sample_local_frame_batch(&r->model, items, batch, batch > 1u ? &scratch : NULL,
+                                            error, cap);
+    batch_scratch_free(&scratch);
+    for (size_t b = 0; b < batch && rc == 0; ++b) {
+        for (size_t fs = 0; fs < stacking; ++fs)
+            for (size_t c = 0; c < codebooks; ++c)
+                codes_out[b * streams + fs * codebooks + c] = scratch_codes[b * streams + c * stacking + fs];
+        saw_eos[b] = items[b].saw_eos;
+        eos_frame[b] = items[b].eos_frame == SIZE_MAX ? -1 : (long)items[b].eos_frame;
+    }
+    free(scratch_codes);
+    return rc;
+}

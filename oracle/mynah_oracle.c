@@ -715,3 +715,231 @@ long orc_greedy_decode(orc_stream *s, unsigned *codes, size_t frames, size_t min
     }
     return (long)frames;
 }
+
+/* ---------------------------------------------------- local transformer ----
+ * The autoregressive local transformer that turns one decoder output row into
+ * the tables of one stacked frame (src/graph.c:806-1656).  It shares the
+ * model's embedding tables (audio_embeddings.N) and per-table projections
+ * (local_transformer_out_projections.N) with the greedy heads above. */
+typedef struct {
+    const float *norm_self, *norm_ff;
+    orc_qweight qkv, o, ffn_up, ffn_down;
+} orc_local_layer;
+
+typedef struct {
+    const orc_model *m;
+    size_t layers, capacity, length;
+    const float *position;          /* local_transformer.position_embeddings.weight */
+    orc_local_layer layer[4];       /* at most 4 layers (src/graph.c:1060) */
+    float *k, *v;                   /* [layers][capacity][width] */
+    float *x, *nrm, *qkv, *attn, *proj, *hidden, *scores, *row_in, *row_out, *logits;
+    size_t top_count;
+    size_t *top_indices;
+    float *top_logits;
+} orc_local;
+
+void orc_local_free(orc_local *s) {
+    if (s == NULL) return;
+    for (size_t l = 0; l < s->layers && l < 4u; ++l) {
+        orc_qweight_free(&s->layer[l].qkv);
+        orc_qweight_free(&s->layer[l].o);
+        orc_qweight_free(&s->layer[l].ffn_up);
+        orc_qweight_free(&s->layer[l].ffn_down);
+    }
+    free(s->k); free(s->v); free(s->x); free(s->nrm); free(s->qkv); free(s->attn);
+    free(s->proj); free(s->hidden); free(s->scores); free(s->row_in); free(s->row_out);
+    free(s->logits); free(s->top_indices); free(s->top_logits);
+    free(s);
+}
+
+/* Per-layer pointer arrays in the order local_cache_init resolves them
+ * (src/graph.c:1031-1056); capacity is tables + 1 (src/graph.c:1200);
+ * top_count > 0 sizes the sampler scratch (src/graph.c:1217-1220). */
+orc_local *orc_local_new(const orc_model *m, size_t layers, const float *position,
+                         const float *const *norm_self, const float *const *qkv_w,
+                         const float *const *o_w, const float *const *norm_ff,
+                         const float *const *ffn_up_w, const float *const *ffn_down_w,
+                         size_t top_count) {
+    if (m == NULL || layers == 0u || layers > 4u) return NULL;
+    orc_local *s = (orc_local *)calloc(1, sizeof(*s));
+    if (s == NULL) return NULL;
+    const size_t w = m->width, f = m->ffn_width;
+    s->m = m;
+    s->layers = layers;
+    s->capacity = m->tables + 1u;
+    s->position = position;
+    s->top_count = top_count;
+    int ok = 1;
+    for (size_t l = 0; l < layers; ++l) {
+        s->layer[l].norm_self = norm_self[l];
+        s->layer[l].norm_ff = norm_ff[l];
+        ok = ok && orc_qweight_init(&s->layer[l].qkv, m->qtype, qkv_w[l], 3u * w, w) == 0;
+        ok = ok && orc_qweight_init(&s->layer[l].o, m->qtype, o_w[l], w, w) == 0;
+        ok = ok && orc_qweight_init(&s->layer[l].ffn_up, m->qtype, ffn_up_w[l], f, w) == 0;
+        ok = ok && orc_qweight_init(&s->layer[l].ffn_down, m->qtype, ffn_down_w[l], w, f) == 0;
+    }
+    s->k = (float *)calloc(layers * s->capacity * w, sizeof(float));
+    s->v = (float *)calloc(layers * s->capacity * w, sizeof(float));
+    s->x = (float *)calloc(w, sizeof(float));
+    s->nrm = (float *)calloc(w, sizeof(float));
+    s->qkv = (float *)calloc(3u * w, sizeof(float));
+    s->attn = (float *)calloc(w, sizeof(float));
+    s->proj = (float *)calloc(w, sizeof(float));
+    s->hidden = (float *)calloc(f, sizeof(float));
+    s->scores = (float *)calloc(s->capacity, sizeof(float));
+    s->row_in = (float *)calloc(w, sizeof(float));
+    s->row_out = (float *)calloc(w, sizeof(float));
+    s->logits = (float *)calloc(m->vocab, sizeof(float));
+    if (top_count > 0u) {
+        s->top_indices = (size_t *)calloc(top_count, sizeof(size_t));
+        s->top_logits = (float *)calloc(top_count, sizeof(float));
+    }
+    if (!ok || !s->k || !s->v || !s->x || !s->nrm || !s->qkv || !s->attn || !s->proj ||
+        !s->hidden || !s->scores || !s->row_in || !s->row_out || !s->logits ||
+        (top_count > 0u && (!s->top_indices || !s->top_logits))) {
+        orc_local_free(s);
+        return NULL;
+    }
+    return s;
+}
+
+size_t orc_local_length(const orc_local *s) { return s->length; }
+void orc_local_set_length(orc_local *s, size_t n) { s->length = n; }
+float *orc_local_k(orc_local *s) { return s->k; }
+float *orc_local_v(orc_local *s) { return s->v; }
+
+/* src/graph.c:1234-1343 for one slot: position row added, then per layer
+ * norm -> qkv -> attention over the rows written so far -> o -> residual ->
+ * norm -> up -> GELU -> down -> residual.  No cross attention, no output norm. */
+int orc_local_step(orc_local *s, const float *input, float *out) {
+    const orc_model *m = s->m;
+    const size_t w = m->width, heads = m->heads, hw = m->head_width, ffn = m->ffn_width;
+    if (s->length >= s->capacity) return -1;
+    const float scale = 1.0f / sqrtf((float)hw);
+    const float *pe = s->position + s->length * w;
+    for (size_t d = 0; d < w; ++d) s->x[d] = input[d] + pe[d];
+    for (size_t l = 0; l < s->layers; ++l) {
+        const orc_local_layer *L = &s->layer[l];
+        orc_layernorm(s->x, L->norm_self, NULL, s->nrm, 1u, w, 1.0e-5f);
+        orc_linear_row(&L->qkv, s->nrm, s->qkv, NULL);
+        orc_self_attention(s->qkv, s->k + l * s->capacity * w, s->v + l * s->capacity * w,
+                           s->length, w, s->length + 1u, heads, hw, scale, s->attn, s->scores);
+        orc_linear_row(&L->o, s->attn, s->proj, NULL);
+        for (size_t d = 0; d < w; ++d) s->x[d] += s->proj[d];
+        orc_layernorm(s->x, L->norm_ff, NULL, s->nrm, 1u, w, 1.0e-5f);
+        orc_linear_row(&L->ffn_up, s->nrm, s->hidden, NULL);
+        orc_gelu_scalar(s->hidden, ffn);
+        orc_linear_row(&L->ffn_down, s->hidden, s->proj, NULL);
+        for (size_t d = 0; d < w; ++d) s->x[d] += s->proj[d];
+    }
+    memcpy(out, s->x, w * sizeof(float));
+    s->length += 1u;
+    return 0;
+}
+
+/* xorshift64 step of the sampler (src/graph.c:1606-1610). */
+uint64_t orc_xorshift64(uint64_t state) {
+    state ^= state << 13;
+    state ^= state >> 7;
+    state ^= state << 17;
+    return state == 0 ? UINT64_C(0x9e3779b97f4a7c15) : state;
+}
+
+/* One stacked frame for one request: src/graph.c:1374-1656.  decoder_last is
+ * the decoder's output row; table t's token comes from position t of the
+ * local transformer, whose input is the decoder row (t = 0) or the embedding
+ * of the previous table's token.  Disallowed candidates are masked to -FLT_MAX
+ * in place, the greedy pick is first-on-ties, and when temperature > 0 and
+ * topk > 1 a token is drawn from the top-k (insertion order: higher logit
+ * first, earlier index first among equals) with weights exp((l - max) / T).
+ * codes[t] gets the stored code (specials collapsed to 0), values[t]
+ * (optional) the token that was fed back.  EOS is seen when the greedy or the
+ * drawn token is EOS; *eos_frame is the smallest t / codebooks where that
+ * happened (SIZE_MAX as -1).  Returns 1 if EOS was seen, 0 if not, -1 on error. */
+int orc_local_frame(orc_local *s, const float *decoder_last, float temperature, unsigned topk,
+                    uint64_t *rng_state, int allow_eos, size_t codebooks, unsigned *codes,
+                    unsigned *values, long *eos_frame) {
+    const orc_model *m = s->m;
+    const size_t w = m->width, vocab = m->vocab;
+    const int sampling = temperature > 0.0f && topk > 1u && rng_state != NULL;
+    const size_t top_count = topk < vocab ? topk : vocab;
+    if (sampling && top_count > s->top_count) return -1;
+    if (codebooks == 0u) return -1;
+    int saw_eos = 0;
+    long first = -1;
+    s->length = 0u;
+    memcpy(s->row_in, decoder_last, w * sizeof(float));
+    for (size_t t = 0; t < m->tables; ++t) {
+        if (orc_local_step(s, s->row_in, s->row_out) != 0) return -1;
+        float *logits = s->logits;
+        orc_linear_row(&m->head[t], s->row_out, logits, m->head_bias[t]);
+        float best = -FLT_MAX;
+        unsigned argmax = 0;
+        for (size_t c = 0; c < vocab; ++c) {
+            const int is_code = c < m->codebook_size;
+            const int is_eos = c == m->eos_id;
+            if (!is_code && !(is_eos && allow_eos)) {
+                logits[c] = -FLT_MAX;
+                continue;
+            }
+            if (logits[c] > best) {
+                best = logits[c];
+                argmax = (unsigned)c;
+            }
+        }
+        unsigned value = argmax;
+        int stream_eos = argmax == m->eos_id;
+        if (sampling) {
+            size_t used = 0;
+            for (size_t c = 0; c < vocab; ++c) {
+                size_t insert = used;
+                while (insert > 0 && logits[c] > s->top_logits[insert - 1u]) --insert;
+                if (used < top_count) {
+                    for (size_t q = used; q > insert; --q) {
+                        s->top_indices[q] = s->top_indices[q - 1u];
+                        s->top_logits[q] = s->top_logits[q - 1u];
+                    }
+                    s->top_indices[insert] = c;
+                    s->top_logits[insert] = logits[c];
+                    ++used;
+                } else if (insert < top_count) {
+                    for (size_t q = top_count - 1u; q > insert; --q) {
+                        s->top_indices[q] = s->top_indices[q - 1u];
+                        s->top_logits[q] = s->top_logits[q - 1u];
+                    }
+                    s->top_indices[insert] = c;
+                    s->top_logits[insert] = logits[c];
+                }
+            }
+            const float maximum = s->top_logits[0];
+            float total = 0.0f;
+            for (size_t q = 0; q < used; ++q) {
+                s->top_logits[q] = expf((s->top_logits[q] - maximum) / temperature);
+                total += s->top_logits[q];
+            }
+            *rng_state = orc_xorshift64(*rng_state);
+            const float draw = ((float)((*rng_state >> 40) & UINT64_C(0xffffff)) /
+                                (float)UINT64_C(0x1000000)) * total;
+            float cumulative = 0.0f;
+            for (size_t q = 0; q < used; ++q) {
+                cumulative += s->top_logits[q];
+                if (draw <= cumulative || q + 1u == used) {
+                    value = (unsigned)s->top_indices[q];
+                    break;
+                }
+            }
+        }
+        if (value == m->eos_id) stream_eos = 1;
+        if (stream_eos) {
+            saw_eos = 1;
+            const long frame = (long)(t / codebooks);
+            if (first < 0 || frame < first) first = frame;
+        }
+        const unsigned emit = value < vocab ? value : 0u;
+        codes[t] = value < m->codebook_size ? value : 0u;
+        if (values != NULL) values[t] = value;
+        memcpy(s->row_in, m->embeddings[t] + (size_t)emit * w, w * sizeof(float));
+    }
+    if (eos_frame != NULL) *eos_frame = first;
+    return saw_eos;
+}

@@ -101,6 +101,21 @@ class Port:
         lib.orc_greedy_frame.argtypes = [C.c_void_p, c_uint_p, C.c_int, c_uint_p, c_float_p]
         lib.orc_greedy_decode.restype = C.c_long
         lib.orc_greedy_decode.argtypes = [C.c_void_p, c_uint_p, sz, sz, c_uint_p]
+        lib.orc_local_new.restype = C.c_void_p
+        lib.orc_local_free.argtypes = [C.c_void_p]
+        lib.orc_local_length.restype = sz
+        lib.orc_local_length.argtypes = [C.c_void_p]
+        lib.orc_local_set_length.argtypes = [C.c_void_p, sz]
+        lib.orc_local_k.restype = c_float_p
+        lib.orc_local_k.argtypes = [C.c_void_p]
+        lib.orc_local_v.restype = c_float_p
+        lib.orc_local_v.argtypes = [C.c_void_p]
+        lib.orc_local_step.argtypes = [C.c_void_p, c_float_p, c_float_p]
+        lib.orc_local_frame.argtypes = [C.c_void_p, c_float_p, C.c_float, C.c_uint,
+                                        C.POINTER(C.c_uint64), C.c_int, sz, c_uint_p, c_uint_p,
+                                        C.POINTER(C.c_long)]
+        lib.orc_xorshift64.restype = C.c_uint64
+        lib.orc_xorshift64.argtypes = [C.c_uint64]
 
     @classmethod
     def get(cls) -> "Port":
@@ -234,6 +249,72 @@ class PortModel:
         return tokens, logits
 
 
+class PortLocal:
+    """orc_local: one request's local-transformer state over a PortModel whose
+    SynthModel has local_layers > 0."""
+
+    def __init__(self, model: PortModel, top_count: int = 0):
+        self.model = model
+        synth = model.synth
+        s = synth.shape
+        assert s.local_layers > 0
+        L = range(s.local_layers)
+
+        def col(suffix):
+            return _ptr_array([synth.local_layer(i, suffix) for i in L])
+        self._keep = [col("norm_self.weight"), col("self_attention.qkv_net.weight"),
+                      col("self_attention.o_net.weight"), col("norm_pos_ff.weight"),
+                      col("pos_ff.proj.conv.weight"), col("pos_ff.o_net.conv.weight")]
+        k = self._keep
+        self.handle = C.c_void_p(model.port.lib.orc_local_new(
+            model.handle, C.c_size_t(s.local_layers), _fp(synth.local_position),
+            k[0], k[1], k[2], k[3], k[4], k[5], C.c_size_t(top_count)))
+        assert self.handle.value
+
+    def close(self):
+        if self.handle:
+            self.model.port.lib.orc_local_free(self.handle)
+            self.handle = None
+
+    @property
+    def length(self) -> int:
+        return self.model.port.lib.orc_local_length(self.handle)
+
+    @length.setter
+    def length(self, n: int):
+        self.model.port.lib.orc_local_set_length(self.handle, n)
+
+    def kv(self):
+        s = self.model.synth.shape
+        shape = (s.local_layers, s.local_positions, s.width)
+        lib = self.model.port.lib
+        n = int(np.prod(shape))
+        return (np.ctypeslib.as_array(lib.orc_local_k(self.handle), shape=(n,)).reshape(shape),
+                np.ctypeslib.as_array(lib.orc_local_v(self.handle), shape=(n,)).reshape(shape))
+
+    def step(self, row: np.ndarray) -> np.ndarray:
+        row = np.ascontiguousarray(row, np.float32)
+        out = np.empty_like(row)
+        assert self.model.port.lib.orc_local_step(self.handle, _fp(row), _fp(out)) == 0
+        return out
+
+    def frame(self, decoder_last: np.ndarray, temperature: float = 0.0, topk: int = 0,
+              rng_state: int = 0, allow_eos: bool = True, codebooks: int | None = None):
+        """-> codes [tables], values [tables], saw_eos, eos_frame, new rng state."""
+        s = self.model.synth.shape
+        codes = np.zeros((s.tables,), np.uint32)
+        values = np.zeros((s.tables,), np.uint32)
+        rng = C.c_uint64(rng_state)
+        eos_frame = C.c_long(-1)
+        row = np.ascontiguousarray(decoder_last, np.float32)
+        rc = self.model.port.lib.orc_local_frame(
+            self.handle, _fp(row), C.c_float(temperature), C.c_uint(topk), C.byref(rng),
+            int(allow_eos), C.c_size_t(codebooks if codebooks else s.tables // 2),
+            codes.ctypes.data_as(c_uint_p), values.ctypes.data_as(c_uint_p), C.byref(eos_frame))
+        assert rc >= 0
+        return codes, values, bool(rc), int(eos_frame.value), int(rng.value)
+
+
 class PortStream:
     def __init__(self, model: PortModel, memory: np.ndarray, capacity: int):
         self.model = model
@@ -341,6 +422,22 @@ class Ref:
                                          C.c_char_p, sz]
         lib.ref_greedy_decode.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), sz, c_uint_p, sz, sz,
                                           c_uint_p, C.POINTER(C.c_long), C.c_char_p, sz]
+        lib.ref_model_set_local_layers.argtypes = [C.c_void_p, C.c_uint]
+        lib.ref_local_new.restype = C.c_void_p
+        lib.ref_local_new.argtypes = [C.c_void_p, sz, C.c_char_p, sz]
+        lib.ref_local_free.argtypes = [C.c_void_p]
+        lib.ref_local_length.restype = sz
+        lib.ref_local_length.argtypes = [C.c_void_p]
+        lib.ref_local_set_length.argtypes = [C.c_void_p, sz]
+        lib.ref_local_k.restype = c_float_p
+        lib.ref_local_k.argtypes = [C.c_void_p]
+        lib.ref_local_v.restype = c_float_p
+        lib.ref_local_v.argtypes = [C.c_void_p]
+        lib.ref_local_step_batch.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), c_float_p, c_float_p,
+                                             sz, C.c_char_p, sz]
+        lib.ref_local_frame.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), sz, c_float_p, c_float_p,
+                                        c_uint_p, C.POINTER(C.c_uint64), C.POINTER(C.c_int), c_uint_p,
+                                        C.POINTER(C.c_int), C.POINTER(C.c_long), C.c_char_p, sz]
         lib.ref_quantize_act_int8.restype = C.c_float
         lib.ref_quantize_act_int8.argtypes = [C.c_void_p, c_float_p, sz]
         lib.ref_qmat_linear.argtypes = [C.c_int, c_float_p, c_float_p, c_float_p, sz, sz, sz,
@@ -428,6 +525,41 @@ class RefModel:
             path.encode(), s.width, s.layers, s.tables // 2, 2, s.codebook_size, s.vocab,
             s.eos_id, qtype, err, 512))
         assert self.handle.value, err.value
+        if s.local_layers:
+            self.ref.lib.ref_model_set_local_layers(self.handle, s.local_layers)
+
+    def new_local(self, top_count: int = 0) -> "RefLocal":
+        return RefLocal(self, top_count)
+
+    def local_step_batch(self, locals_, rows: np.ndarray) -> np.ndarray:
+        rows = np.ascontiguousarray(rows, np.float32)
+        outs = np.empty_like(rows)
+        arr = (C.c_void_p * len(locals_))(*[l.handle for l in locals_])
+        err = C.create_string_buffer(256)
+        rc = self.ref.lib.ref_local_step_batch(self.handle, arr, _fp(rows), _fp(outs), len(locals_), err, 256)
+        assert rc == 0, err.value
+        return outs
+
+    def local_frame(self, locals_, decoder_last: np.ndarray, temperature, topk, rng_states, allow_eos):
+        """One stacked frame for len(locals_) requests (<= 16) ->
+        codes [batch, tables], saw_eos [batch], eos_frame [batch], new rng states."""
+        s = self.synth.shape
+        batch = len(locals_)
+        rows = np.ascontiguousarray(decoder_last, np.float32)
+        temp = np.ascontiguousarray(temperature, np.float32)
+        tk = np.ascontiguousarray(topk, np.uint32)
+        rng = (C.c_uint64 * batch)(*[int(x) for x in rng_states])
+        allow = (C.c_int * batch)(*[int(bool(x)) for x in allow_eos])
+        codes = np.zeros((batch, s.tables), np.uint32)
+        saw = (C.c_int * batch)()
+        eos = (C.c_long * batch)()
+        arr = (C.c_void_p * batch)(*[l.handle for l in locals_])
+        err = C.create_string_buffer(256)
+        rc = self.ref.lib.ref_local_frame(self.handle, arr, batch, _fp(rows), _fp(temp),
+                                          tk.ctypes.data_as(c_uint_p), rng, allow,
+                                          codes.ctypes.data_as(c_uint_p), saw, eos, err, 256)
+        assert rc == 0, err.value
+        return codes, np.array(list(saw)), np.array(list(eos)), [int(x) for x in rng]
 
     def close(self):
         if self.handle:
@@ -472,6 +604,27 @@ class RefModel:
                                             eos, err, 256)
         assert rc == 0, err.value
         return tokens, np.array(list(eos))
+
+
+class RefLocal:
+    def __init__(self, model: RefModel, top_count: int = 0):
+        self.model = model
+        err = C.create_string_buffer(256)
+        self.handle = C.c_void_p(model.ref.lib.ref_local_new(model.handle, top_count, err, 256))
+        assert self.handle.value, err.value
+
+    def close(self):
+        if self.handle:
+            self.model.ref.lib.ref_local_free(self.handle)
+            self.handle = None
+
+    @property
+    def length(self):
+        return self.model.ref.lib.ref_local_length(self.handle)
+
+    @length.setter
+    def length(self, n):
+        self.model.ref.lib.ref_local_set_length(self.handle, n)
 
 
 class RefDecoder:
