@@ -422,6 +422,7 @@ class Ref:
                                          C.c_char_p, sz]
         lib.ref_greedy_decode.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), sz, c_uint_p, sz, sz,
                                           c_uint_p, C.POINTER(C.c_long), C.c_char_p, sz]
+        lib.ref_embed_audio_frame.argtypes = [C.c_void_p, c_uint_p, sz, sz, c_float_p, C.c_char_p, sz]
         lib.ref_model_set_local_layers.argtypes = [C.c_void_p, C.c_uint]
         lib.ref_local_new.restype = C.c_void_p
         lib.ref_local_new.argtypes = [C.c_void_p, sz, C.c_char_p, sz]
@@ -527,6 +528,20 @@ class RefModel:
         assert self.handle.value, err.value
         if s.local_layers:
             self.ref.lib.ref_model_set_local_layers(self.handle, s.local_layers)
+
+    def embed_frame(self, codes: np.ndarray) -> np.ndarray:
+        """codes [tables] with table = fs * codebooks + codebook -> decoder input row
+        (embed_audio_frame, src/graph.c:760-804)."""
+        s = self.synth.shape
+        codebooks = s.tables // 2
+        flat = np.ascontiguousarray(codes, np.uint32).reshape(2, codebooks)   # [fs][codebook]
+        laid = np.ascontiguousarray(flat.T)                                   # [codebook][fs]
+        row = np.empty((s.width,), np.float32)
+        err = C.create_string_buffer(256)
+        rc = self.ref.lib.ref_embed_audio_frame(self.handle, laid.ctypes.data_as(c_uint_p), 2, 0,
+                                                _fp(row), err, 256)
+        assert rc == 0, err.value
+        return row
 
     def new_local(self, top_count: int = 0) -> "RefLocal":
         return RefLocal(self, top_count)
