@@ -278,6 +278,62 @@ int mynah_b200_decoder_frame_batch(void *decoder, const unsigned *slots, const u
 int mynah_b200_decoder_greedy(void *decoder, const unsigned *slots, size_t batch, unsigned *codes,
                               const size_t *frames, size_t min_frames, unsigned *tokens,
                               long *eos_frame, float *elapsed_ms, char *error, size_t cap);
+/* ---- local transformer and sampler (src/graph.c:806-1656) -------------------
+ * The small autoregressive transformer that turns one decoder output row into the
+ * `tables` tokens of a stacked frame: table t's logits come from position t, whose
+ * input is the decoder row (t = 0) or the embedding of table t-1's token.  It uses
+ * the decoder's embedding tables and per-table projections (desc->embeddings,
+ * head_w, head_b: audio_embeddings.N / local_transformer_out_projections.N). */
+typedef struct {
+    const float *norm_self;    /* local_transformer.layers.N.norm_self.weight [width] */
+    const float *norm_pos_ff;  /* ...norm_pos_ff.weight [width] */
+    const float *qkv_w;        /* ...self_attention.qkv_net.weight [3*width, width] */
+    const float *o_w;          /* ...self_attention.o_net.weight [width, width] */
+    const float *ffn_up_w;     /* ...pos_ff.proj.conv.weight [4*width, width] */
+    const float *ffn_down_w;   /* ...pos_ff.o_net.conv.weight [width, 4*width] */
+} mynah_b200_local_layer_weights;
+
+typedef struct {
+    size_t layers;             /* model.json local_transformer_layers, 1..4 (src/graph.c:1060) */
+    const mynah_b200_local_layer_weights *layer;
+    const float *position;     /* local_transformer.position_embeddings.weight [position_rows, width] */
+    size_t position_rows;      /* >= tables */
+    size_t codebooks;          /* tables = codebooks x frame_stacking_factor */
+} mynah_b200_local_desc;
+
+/* Uploads and packs the local transformer's weights and allocates its per-lane
+ * KV (tables + 1 rows, src/graph.c:1200).  Once per decoder. */
+int mynah_b200_decoder_local_attach(void *decoder, const mynah_b200_local_desc *desc, char *error,
+                                    size_t cap);
+
+/* Per-request sampler settings (local_batch_item, src/graph.c:1346-1362): greedy
+ * when temperature <= 0 or topk <= 1, else a draw from the top-k with the
+ * request's xorshift64 state, which the call advances. */
+typedef struct {
+    float temperature;
+    unsigned topk;
+    unsigned long long rng_state;
+    int allow_eos;             /* used by _local_frame only; the loops apply min_frames */
+} mynah_b200_sampler;
+
+/* One stacked frame for `batch` requests: the contract of sample_local_frame_batch
+ * (src/graph.c:1374-1656) with HOST buffers.  decoder_last [batch][width] in;
+ * codes [batch][tables] (stored codes, specials collapsed to 0), values (optional,
+ * the tokens fed back, EOS kept), saw_eos, eos_frame (smallest table / codebooks
+ * where the greedy or drawn token was EOS, -1 if none) out.  Synchronous. */
+int mynah_b200_decoder_local_frame(void *decoder, const float *decoder_last, size_t batch,
+                                   mynah_b200_sampler *samplers, unsigned *codes, unsigned *values,
+                                   int *saw_eos, long *eos_frame, char *error, size_t cap);
+
+/* _greedy with the local transformer in place of the logit heads: per frame embed
+ * the stored codes, step the decoder, run one stacked local frame (the loop of
+ * synthesize_slots, src/graph.c:4083-4183, without the codec).  tokens receives the
+ * fed-back tokens of every frame; samplers [batch] (NULL: all greedy) are advanced. */
+int mynah_b200_decoder_generate(void *decoder, const unsigned *slots, size_t batch, unsigned *codes,
+                                const size_t *frames, size_t min_frames,
+                                mynah_b200_sampler *samplers, unsigned *tokens, long *eos_frame,
+                                float *elapsed_ms, char *error, size_t cap);
+
 /* Bytes of weights one step reads, and of KV one slot at `length` reads. */
 size_t mynah_b200_decoder_weight_bytes(const void *decoder);
 size_t mynah_b200_decoder_kv_bytes(const void *decoder, size_t length);
@@ -287,7 +343,7 @@ size_t mynah_b200_decoder_kv_bytes(const void *decoder, size_t length);
  * every step runs as individual launches, each bracketed by two CUDA events on
  * the backend's stream, instead of a graph replay; _read synchronizes and
  * returns, per class, the launches seen and their summed device time. */
-#define MYNAH_B200_PROFILE_CLASSES 14
+#define MYNAH_B200_PROFILE_CLASSES 15
 int mynah_b200_decoder_profile(void *decoder, int enable, char *error, size_t cap);
 int mynah_b200_decoder_profile_read(void *decoder, unsigned long long *launches, double *ms,
                                     size_t n, char *error, size_t cap);

@@ -263,6 +263,22 @@ class Decoder:
             desc.embeddings, desc.head_w, desc.head_b = tabs, hw, hb
         self.handle = C.c_void_p()
         call(capi.lib().mynah_b200_decoder_create, backend.state, C.byref(desc), C.byref(self.handle))
+        self.has_local = False
+        if with_heads and getattr(s, "local_layers", 0):
+            ll = (capi.LocalLayerWeights * s.local_layers)()
+            for i in range(s.local_layers):
+                ll[i].norm_self = fp(model.local_layer(i, "norm_self.weight"))
+                ll[i].norm_pos_ff = fp(model.local_layer(i, "norm_pos_ff.weight"))
+                ll[i].qkv_w = fp(model.local_layer(i, "self_attention.qkv_net.weight"))
+                ll[i].o_w = fp(model.local_layer(i, "self_attention.o_net.weight"))
+                ll[i].ffn_up_w = fp(model.local_layer(i, "pos_ff.proj.conv.weight"))
+                ll[i].ffn_down_w = fp(model.local_layer(i, "pos_ff.o_net.conv.weight"))
+            ld = capi.LocalDesc()
+            ld.layers, ld.layer = s.local_layers, ll
+            ld.position, ld.position_rows = fp(model.local_position), model.local_position.shape[0]
+            ld.codebooks = s.tables // 2       # stacking factor 2, as the reference requires
+            call(capi.lib().mynah_b200_decoder_local_attach, self.handle, C.byref(ld))
+            self.has_local = True
 
     def close(self):
         if self.handle:
@@ -338,6 +354,48 @@ class Decoder:
              codes.ctypes.data_as(capi.c_uint_p), allow, tokens.ctypes.data_as(capi.c_uint_p),
              None if hidden is None else fp(hidden), batch)
         return (tokens, hidden) if want_hidden else tokens
+
+    @staticmethod
+    def _samplers(batch, samplers):
+        """samplers: None (greedy) or a list of (temperature, topk, rng_state[, allow_eos])."""
+        arr = (capi.Sampler * batch)()
+        for b in range(batch):
+            t = (0.0, 0, 0, 1) if samplers is None else tuple(samplers[b])
+            arr[b].temperature, arr[b].topk, arr[b].rng_state = float(t[0]), int(t[1]), int(t[2])
+            arr[b].allow_eos = int(t[3]) if len(t) > 3 else 1
+        return arr
+
+    def local_frame(self, decoder_last: np.ndarray, samplers=None):
+        """One stacked frame of the local transformer for len(decoder_last) requests ->
+        codes, values [batch, tables], saw_eos, eos_frame [batch], new rng states."""
+        rows = np.ascontiguousarray(decoder_last, np.float32)
+        batch = rows.shape[0]
+        arr = self._samplers(batch, samplers)
+        codes = np.zeros((batch, self.shape.tables), np.uint32)
+        values = np.zeros_like(codes)
+        saw = (C.c_int * batch)()
+        eos = (C.c_long * batch)()
+        call(capi.lib().mynah_b200_decoder_local_frame, self.handle, fp(rows), batch, arr,
+             codes.ctypes.data_as(capi.c_uint_p), values.ctypes.data_as(capi.c_uint_p), saw, eos)
+        return (codes, values, np.array(list(saw)), np.array(list(eos)),
+                [int(arr[b].rng_state) for b in range(batch)])
+
+    def generate(self, slots, codes: np.ndarray, frames, min_frames: int = 0, samplers=None):
+        """greedy() with the local transformer and its sampler in place of the logit
+        heads.  Returns (tokens [max_frames, batch, tables], eos_frame, device ms, last
+        stored codes, new rng states)."""
+        batch = len(slots)
+        frames = [frames] * batch if isinstance(frames, int) else list(frames)
+        codes = np.ascontiguousarray(codes, np.uint32).copy()
+        tokens = np.zeros((max(frames), batch, self.shape.tables), np.uint32)
+        eos = (C.c_long * batch)()
+        ms = C.c_float(0.0)
+        arr = self._samplers(batch, samplers)
+        call(capi.lib().mynah_b200_decoder_generate, self.handle, (C.c_uint * batch)(*slots), batch,
+             codes.ctypes.data_as(capi.c_uint_p), (capi.sz * batch)(*frames), min_frames, arr,
+             tokens.ctypes.data_as(capi.c_uint_p), eos, C.byref(ms))
+        return (tokens, np.array(list(eos)), float(ms.value), codes,
+                [int(arr[b].rng_state) for b in range(batch)])
 
     def greedy(self, slots, codes: np.ndarray, frames, min_frames: int = 0):
         """codes [batch, tables]; frames: int or per-lane list.  Returns

@@ -18,7 +18,7 @@ LIB_PATH = os.path.join(HERE, "libmynah_b200.so")
 F32, INT8, INT4, F16 = 0, 1, 2, 3
 QUANT = {"f32": F32, "int8": INT8, "int4": INT4, "f16": F16}
 ERR_CAP = 512
-PROFILE_CLASSES = 14
+PROFILE_CLASSES = 15
 
 c_float_p = C.POINTER(C.c_float)
 c_uint_p = C.POINTER(C.c_uint)
@@ -54,6 +54,21 @@ class DecoderDesc(C.Structure):
         ("embeddings", C.POINTER(c_float_p)), ("head_w", C.POINTER(c_float_p)),
         ("head_b", C.POINTER(c_float_p)),
     ]
+
+
+class LocalLayerWeights(C.Structure):
+    _fields_ = [(n, c_float_p) for n in (
+        "norm_self", "norm_pos_ff", "qkv_w", "o_w", "ffn_up_w", "ffn_down_w")]
+
+
+class LocalDesc(C.Structure):
+    _fields_ = [("layers", sz), ("layer", C.POINTER(LocalLayerWeights)), ("position", c_float_p),
+                ("position_rows", sz), ("codebooks", sz)]
+
+
+class Sampler(C.Structure):
+    _fields_ = [("temperature", C.c_float), ("topk", C.c_uint), ("rng_state", C.c_ulonglong),
+                ("allow_eos", C.c_int)]
 
 
 MATMUL_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, c_float_p, c_float_p, sz, sz, sz, c_float_p, c_float_p,
@@ -138,6 +153,11 @@ SIGNATURES = {
                                                  c_float_p, sz, _E]),
     "mynah_b200_decoder_greedy": (C.c_int, [C.c_void_p, c_uint_p, sz, c_uint_p, C.POINTER(sz), sz,
                                             c_uint_p, C.POINTER(C.c_long), c_float_p, _E]),
+    "mynah_b200_decoder_local_attach": (C.c_int, [C.c_void_p, C.POINTER(LocalDesc), _E]),
+    "mynah_b200_decoder_local_frame": (C.c_int, [C.c_void_p, c_float_p, sz, C.POINTER(Sampler), c_uint_p,
+                                                 c_uint_p, c_int_p, C.POINTER(C.c_long), _E]),
+    "mynah_b200_decoder_generate": (C.c_int, [C.c_void_p, c_uint_p, sz, c_uint_p, C.POINTER(sz), sz,
+                                              C.POINTER(Sampler), c_uint_p, C.POINTER(C.c_long), c_float_p, _E]),
     "mynah_b200_decoder_profile": (C.c_int, [C.c_void_p, C.c_int, _E]),
     "mynah_b200_decoder_profile_read": (C.c_int, [C.c_void_p, C.POINTER(C.c_ulonglong),
                                                   C.POINTER(C.c_double), sz, _E]),

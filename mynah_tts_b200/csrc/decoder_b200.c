@@ -18,13 +18,35 @@
 #include <stdlib.h>
 #include <string.h>
 
-enum { MODE_STEP = 0, MODE_FRAME = 1 };
+/* STEP: host rows in/out; FRAME: embed + step + logit heads; LOCAL: embed + step + the
+ * local transformer's stacked frame; LOCAL_ONLY: the stacked frame alone, from rows in d->out */
+enum { MODE_STEP = 0, MODE_FRAME = 1, MODE_LOCAL = 2, MODE_LOCAL_ONLY = 3, MODE_COUNT = 4 };
 #define MAX_BUCKETS 12
 
 typedef struct {
     float *norm_self, *norm_xattn_query, *norm_pos_ff;
     mb_dev_weight qkv, o_self, q_cross, o_cross, ffn_up, ffn_down;
 } dec_layer;
+
+typedef struct {
+    float *norm_self, *norm_ff;
+    mb_dev_weight qkv, o, ffn_up, ffn_down;
+} local_layer;
+
+/* The local transformer of src/graph.c:806-1656: at most 4 layers, no cross attention, a KV
+ * of tables + 1 rows per lane that is rewritten every frame (so it belongs to lanes, not to
+ * slots), and the per-lane sampler state. */
+typedef struct {
+    size_t layers, capacity, codebooks;
+    local_layer L[4];
+    float *position;               /* [position_rows][width] */
+    float *k, *v;                  /* [max_batch][layers][capacity][width] */
+    float *row_in;                 /* [max_batch][width]: embedding of the previous table's token */
+    float *d_temp;                 /* [max_batch] */
+    unsigned *d_topk;              /* [max_batch] */
+    unsigned long long *d_rng;     /* [max_batch] xorshift64 states */
+    int *d_eos_sub;                /* [max_batch] first stacked sub-frame with EOS in this frame */
+} mb_local;
 
 typedef struct mb_decoder {
     mb_state *st;
@@ -54,8 +76,9 @@ typedef struct mb_decoder {
     int *h_lens, *h_slots, *h_ints, *h_table;
     unsigned *h_codes, *h_tokens;
     size_t *slot_len;           /* host mirror of every slot's length */
-    cudaGraphExec_t graph[2][MAX_BUCKETS];
-    unsigned graph_launches[2][MAX_BUCKETS];
+    mb_local local;             /* layers == 0: not attached */
+    cudaGraphExec_t graph[MODE_COUNT][MAX_BUCKETS];
+    unsigned graph_launches[MODE_COUNT][MAX_BUCKETS];
     size_t bucket_size[MAX_BUCKETS];
     size_t n_buckets;
     int use_graphs;
@@ -72,11 +95,12 @@ typedef struct mb_decoder {
 
 #define PROF_POOL 4096u
 enum { PC_INPUT = 0, PC_NORM, PC_QKV, PC_ATTN_SELF, PC_O_SELF, PC_Q_CROSS, PC_ATTN_CROSS,
-       PC_O_CROSS, PC_FFN_UP, PC_QUANT, PC_FFN_DOWN, PC_HEADS, PC_ARGMAX, PC_ADVANCE };
+       PC_O_CROSS, PC_FFN_UP, PC_QUANT, PC_FFN_DOWN, PC_HEADS, PC_ARGMAX, PC_ADVANCE, PC_LOCAL };
 static const char *const prof_names[MYNAH_B200_PROFILE_CLASSES] = {
     "input(embed|position)", "layernorm(+quant)", "qkv product", "self attention", "o_self product",
     "q_cross product", "cross attention", "o_cross product", "ffn_up product(+gelu)",
-    "hidden quant", "ffn_down product", "heads product", "argmax", "advance"};
+    "hidden quant", "ffn_down product", "heads product", "argmax", "advance",
+    "local transformer frame (all tables)"};
 
 static void prof_drain(mb_decoder *d) {
     if (d->prof_used == 0) return;
@@ -118,7 +142,7 @@ static int upload_vec(float **dst, const float *host, size_t n, char *error, siz
 }
 
 static void destroy_graphs(mb_decoder *d) {
-    for (int m = 0; m < 2; ++m)
+    for (int m = 0; m < MODE_COUNT; ++m)
         for (size_t i = 0; i < MAX_BUCKETS; ++i)
             if (d->graph[m][i] != NULL) {
                 cudaGraphExecDestroy(d->graph[m][i]);
@@ -143,6 +167,16 @@ void mynah_b200_decoder_destroy(void *decoder) {
         free(d->L);
     }
     mb_weight_release(&d->heads_w);
+    for (size_t l = 0; l < 4u; ++l) {
+        mb_weight_release(&d->local.L[l].qkv); mb_weight_release(&d->local.L[l].o);
+        mb_weight_release(&d->local.L[l].ffn_up); mb_weight_release(&d->local.L[l].ffn_down);
+        cudaFree(d->local.L[l].norm_self); cudaFree(d->local.L[l].norm_ff);
+    }
+    {
+        void *ldev[] = {d->local.position, d->local.k, d->local.v, d->local.row_in, d->local.d_temp,
+                        d->local.d_topk, d->local.d_rng, d->local.d_eos_sub};
+        for (size_t i = 0; i < sizeof(ldev) / sizeof(ldev[0]); ++i) cudaFree(ldev[i]);
+    }
     void *dev[] = {d->position, d->norm_out, d->emb, (void *)d->d_tables, d->heads_b, d->self_k,
                    d->self_v, d->cross_k, d->cross_v, d->x, d->nrm, d->qkv, d->attn, d->q_x,
                    d->xctx, d->hidden, d->out, d->rows_in, d->logits, d->qx, d->sx, d->partials,
@@ -396,6 +430,119 @@ static int norm(mb_decoder *d, const float *in, float *out, const float *gain, s
                         q ? d->sx : NULL, d->d_n_active, d->st->strict, d->st->stream);
 }
 
+/* Rows [row0, row0 + rows) of a packed weight as a weight of its own. */
+static mb_dev_weight weight_rows(const mb_dev_weight *w, size_t row0, size_t rows) {
+    mb_dev_weight v = *w;
+    v.n = rows;
+    unsigned char *base = (unsigned char *)w->w;
+    switch (w->qtype) {
+    case MB_INT8: v.w = base + row0 * w->k; v.scales = w->scales + row0; break;
+    case MB_INT4: v.w = base + row0 * (w->k / 2u); v.scales = w->scales + row0 * (w->k / 32u); break;
+    case MB_F16: v.w = base + row0 * w->k * 2u; break;
+    default: v.w = base + row0 * w->k * 4u; break;
+    }
+    return v;
+}
+
+/* One stacked frame of the local transformer for nb lanes (src/graph.c:1374-1656), fully on
+ * the device: table t's token is made at position t; position 0 reads `first_rows` (the
+ * decoder's output rows), position t > 0 the embedding of the previous table's token, left
+ * in local.row_in by the sampler. */
+static int enqueue_local(mb_decoder *d, const float *first_rows, size_t nb, unsigned *count) {
+    mb_state *st = d->st;
+    mb_stream s = st->stream;
+    mb_local *lt = &d->local;
+    const size_t W = d->width, F = d->ffn;
+    const int q = d->st->quant == MB_INT8 || d->st->quant == MB_INT4;
+    const float scale = 1.0f / sqrtf((float)d->hw);
+    int rc = 0;
+#define L_TRY(expr) do { if (rc == 0) rc = (expr); } while (0)
+    for (size_t t = 0; t < d->tables && rc == 0; ++t) {
+        L_TRY(mb_add_row(t == 0 ? first_rows : lt->row_in, lt->position + t * W, d->x, nb, W, d->d_n_active, s));
+        *count += 1u;
+        for (size_t l = 0; l < lt->layers && rc == 0; ++l) {
+            const local_layer *L = &lt->L[l];
+            L_TRY(norm(d, d->x, d->nrm, L->norm_self, nb, count));
+            L_TRY(product(d, &L->qkv, NULL, d->nrm, d->qkv, 3u * W, nb, MB_EPI_STORE, count));
+            mb_attn_args a;
+            memset(&a, 0, sizeof(a));
+            a.q = d->qkv;
+            a.q_stride = 3u * W;
+            a.k_new = d->qkv + W;
+            a.v_new = d->qkv + 2u * W;
+            a.k_cache = lt->k + l * lt->capacity * W;
+            a.v_cache = lt->v + l * lt->capacity * W;
+            a.slot_stride = lt->layers * lt->capacity * W;     /* lane b owns block b */
+            a.position = t;
+            a.valid = t + 1u;
+            a.cache_rows = (d->max_batch - 1u) * lt->layers * lt->capacity + lt->capacity;
+            a.cache_stride = W;
+            a.heads = d->heads;
+            a.head_width = d->hw;
+            a.scale = scale;
+            a.out = d->attn;
+            a.out_stride = W;
+            a.qx = q ? d->qx : NULL;
+            a.sx = q ? d->sx : NULL;
+            a.batch = nb;
+            a.n_active = d->d_n_active;
+            a.strict = st->strict;
+            a.exp_tab = st->libm.exp_tab;
+            a.partials = d->partials;
+            a.counters = d->counters;
+            a.status = d->d_status;
+            a.sm_count = st->sm_count;
+            a.early_prefetch = 1;   /* rows below t were appended at earlier positions of this frame */
+            L_TRY(mb_attention(&a, s));
+            *count += (st->strict && q) ? 2u : 1u;
+            L_TRY(product(d, &L->o, NULL, d->attn, d->x, W, nb, MB_EPI_RESIDUAL, count));
+            L_TRY(norm(d, d->x, d->nrm, L->norm_ff, nb, count));
+            L_TRY(product(d, &L->ffn_up, NULL, d->nrm, d->hidden, F, nb, MB_EPI_GELU, count));
+            if (q) {
+                L_TRY(mb_quant_rows(d->hidden, nb, F, d->qx, d->sx, d->d_n_active, s));
+                *count += 1u;
+            }
+            L_TRY(product(d, &L->ffn_down, NULL, d->hidden, d->x, W, nb, MB_EPI_RESIDUAL, count));
+        }
+        /* this table's projection (no norm in between: src/graph.c:1339-1341, 1538-1549) */
+        if (q) {
+            L_TRY(mb_quant_rows(d->x, nb, W, d->qx, d->sx, d->d_n_active, s));
+            *count += 1u;
+        }
+        const mb_dev_weight head = weight_rows(&d->heads_w, t * d->vocab, d->vocab);
+        L_TRY(product(d, &head, d->heads_b + t * d->vocab, d->x, d->logits, d->vocab, nb, MB_EPI_STORE, count));
+        mb_sample_args sa;
+        memset(&sa, 0, sizeof(sa));
+        sa.logits = d->logits;
+        sa.logits_stride = d->vocab;
+        sa.vocab = d->vocab;
+        sa.codebook_size = d->codebook_size;
+        sa.eos_id = d->eos_id;
+        sa.batch = nb;
+        sa.allow_eos = d->d_allow_eos;
+        sa.temperature = lt->d_temp;
+        sa.topk = lt->d_topk;
+        sa.rng = lt->d_rng;
+        sa.table = t;
+        sa.tables = d->tables;
+        sa.codebooks = lt->codebooks;
+        sa.tokens = d->d_tokens;
+        sa.codes = d->d_codes;
+        sa.eos_flag = d->d_eos_flag;
+        sa.eos_sub = lt->d_eos_sub;
+        sa.emb_table = d->emb + t * d->vocab * W;
+        sa.row_in = lt->row_in;
+        sa.width = W;
+        sa.strict = st->strict;
+        sa.exp_tab = st->libm.exp_tab;
+        sa.n_active = d->d_n_active;
+        L_TRY(mb_local_sample(&sa, s));
+        *count += 1u;
+    }
+#undef L_TRY
+    return rc;
+}
+
 static int enqueue(mb_decoder *d, size_t bucket, int mode, unsigned *count) {
     mb_state *st = d->st;
     mb_stream s = st->stream;
@@ -407,8 +554,14 @@ static int enqueue(mb_decoder *d, size_t bucket, int mode, unsigned *count) {
     int rc = 0;
 #define E_TRY(expr) do { if (rc == 0) rc = (expr); } while (0)
 #define P(cls, expr) do { prof_begin(d, (cls)); E_TRY(expr); prof_end(d); } while (0)
+    if (mode == MODE_LOCAL_ONLY) {
+        prof_begin(d, PC_LOCAL);
+        rc = enqueue_local(d, d->out, nb, count);
+        prof_end(d);
+        return rc;
+    }
     prof_begin(d, PC_INPUT);
-    if (mode == MODE_FRAME) {
+    if (mode == MODE_FRAME || mode == MODE_LOCAL) {
         E_TRY(mb_embed_frames(d->d_tables, d->tables, d->vocab, W, d->d_codes, d->position,
                               d->d_lens, d->x, nb, d->d_n_active, d->d_status, s));
     } else {
@@ -505,6 +658,13 @@ static int enqueue(mb_decoder *d, size_t bucket, int mode, unsigned *count) {
                                        d->max_batch, d->tables, d->d_min_frames, d->history_frames,
                                        d->d_n_active, s));
         *count += 2u;
+    } else if (mode == MODE_LOCAL) {
+        P(PC_LOCAL, enqueue_local(d, d->out, nb, count));
+        P(PC_ADVANCE, mb_frame_advance(d->d_lens, d->d_tokens, d->d_history, d->d_frame_idx,
+                                       d->d_eos_flag, d->d_eos_frame, d->d_allow_eos, nb,
+                                       d->max_batch, d->tables, d->d_min_frames, d->history_frames,
+                                       d->d_n_active, s));
+        *count += 1u;
     } else {
         P(PC_ADVANCE, mb_advance_lens(d->d_lens, nb, d->d_n_active, s));
         *count += 1u;
@@ -734,13 +894,18 @@ int mynah_b200_decoder_frame_batch(void *decoder, const unsigned *slots, const u
     return 0;
 }
 
-int mynah_b200_decoder_greedy(void *decoder, const unsigned *slots, size_t batch, unsigned *codes,
-                              const size_t *frames, size_t min_frames, unsigned *tokens,
-                              long *eos_frame, float *elapsed_ms, char *error, size_t cap) {
-    mb_decoder *d = (mb_decoder *)decoder;
+static int stage_samplers(mb_decoder *d, const mynah_b200_sampler *samplers, const size_t *order,
+                          size_t batch, char *error, size_t cap);
+
+/* The device-resident frame loop behind _greedy (mode MODE_FRAME: logit heads) and _generate
+ * (mode MODE_LOCAL: the local transformer and its sampler). */
+static int decode_loop(mb_decoder *d, int mode, mynah_b200_sampler *samplers, const unsigned *slots,
+                       size_t batch, unsigned *codes, const size_t *frames, size_t min_frames,
+                       unsigned *tokens, long *eos_frame, float *elapsed_ms, char *error, size_t cap) {
     if (d == NULL || d->tables == 0 || codes == NULL || frames == NULL || tokens == NULL ||
-        slots == NULL || batch == 0 || batch > d->max_batch) {
-        mb_set_error(error, cap, "invalid greedy decode request");
+        slots == NULL || batch == 0 || batch > d->max_batch ||
+        (mode == MODE_LOCAL && d->local.layers == 0)) {
+        mb_set_error(error, cap, "invalid decode request");
         return -1;
     }
     /* lanes ordered by frame count, longest first, so live lanes are a prefix */
@@ -772,6 +937,10 @@ int mynah_b200_decoder_greedy(void *decoder, const unsigned *slots, size_t batch
     }
     if (max_frames == 0) { free(order); free(lane_slots); return 0; }
     if (stage_lanes(d, lane_slots, batch, error, cap) != 0) { free(order); free(lane_slots); return -1; }
+    if (mode == MODE_LOCAL && stage_samplers(d, samplers, order, batch, error, cap) != 0) {
+        free(order); free(lane_slots);
+        return -1;
+    }
     const size_t T = d->tables;
     cudaStream_t s = d->st->stream;
     for (size_t i = 0; i < batch; ++i) {
@@ -797,7 +966,7 @@ int mynah_b200_decoder_greedy(void *decoder, const unsigned *slots, size_t batch
             live = now;
             G_TRY(cudaMemcpyAsync(d->d_n_active, &d->h_table[live], sizeof(int), cudaMemcpyHostToDevice, s), "stage lane count");
         }
-        if (rc == 0 && run(d, live, MODE_FRAME, error, cap) != 0) rc = -1;
+        if (rc == 0 && run(d, live, mode, error, cap) != 0) rc = -1;
     }
     G_TRY(cudaEventRecord(d->ev1, s), "record event");
     unsigned *hist = (unsigned *)malloc(max_frames * d->max_batch * T * sizeof(unsigned));
@@ -806,6 +975,9 @@ int mynah_b200_decoder_greedy(void *decoder, const unsigned *slots, size_t batch
     G_TRY(cudaMemcpyAsync(hist, d->d_history, max_frames * d->max_batch * T * sizeof(unsigned), cudaMemcpyDeviceToHost, s), "read tokens");
     G_TRY(cudaMemcpyAsync(eosf, d->d_eos_frame, batch * sizeof(int), cudaMemcpyDeviceToHost, s), "read eos frames");
     G_TRY(cudaMemcpyAsync(d->h_codes, d->d_codes, batch * T * sizeof(unsigned), cudaMemcpyDeviceToHost, s), "read codes");
+    unsigned long long *rng_back = (unsigned long long *)d->h_rows;
+    if (mode == MODE_LOCAL)
+        G_TRY(cudaMemcpyAsync(rng_back, d->local.d_rng, batch * sizeof(unsigned long long), cudaMemcpyDeviceToHost, s), "read rng");
     G_TRY(cudaStreamSynchronize(s), "cudaStreamSynchronize");
     if (rc == 0 && elapsed_ms != NULL) G_TRY(cudaEventElapsedTime(elapsed_ms, d->ev0, d->ev1), "event time");
     if (rc == 0 && check_status(d, error, cap) != 0) rc = -1;
@@ -818,12 +990,151 @@ int mynah_b200_decoder_greedy(void *decoder, const unsigned *slots, size_t batch
                 memcpy(tokens + (f * batch + b) * T, hist + (f * d->max_batch + i) * T, T * sizeof(unsigned));
             memcpy(codes + b * T, d->h_codes + i * T, T * sizeof(unsigned));
             if (eos_frame != NULL) eos_frame[b] = eosf[i];
+            if (mode == MODE_LOCAL && samplers != NULL) samplers[b].rng_state = rng_back[i];
             d->slot_len[slots[b]] += frames[b];
         }
         mb_clear_error(error, cap);
     }
     free(hist); free(eosf); free(order); free(lane_slots);
     return rc;
+}
+
+int mynah_b200_decoder_greedy(void *decoder, const unsigned *slots, size_t batch, unsigned *codes,
+                              const size_t *frames, size_t min_frames, unsigned *tokens,
+                              long *eos_frame, float *elapsed_ms, char *error, size_t cap) {
+    return decode_loop((mb_decoder *)decoder, MODE_FRAME, NULL, slots, batch, codes, frames, min_frames,
+                       tokens, eos_frame, elapsed_ms, error, cap);
+}
+
+int mynah_b200_decoder_generate(void *decoder, const unsigned *slots, size_t batch, unsigned *codes,
+                                const size_t *frames, size_t min_frames,
+                                mynah_b200_sampler *samplers, unsigned *tokens, long *eos_frame,
+                                float *elapsed_ms, char *error, size_t cap) {
+    return decode_loop((mb_decoder *)decoder, MODE_LOCAL, samplers, slots, batch, codes, frames,
+                       min_frames, tokens, eos_frame, elapsed_ms, error, cap);
+}
+
+/* ------------------------------------------------------- local transformer */
+int mynah_b200_decoder_local_attach(void *decoder, const mynah_b200_local_desc *desc, char *error,
+                                    size_t cap) {
+    mb_decoder *d = (mb_decoder *)decoder;
+    if (d == NULL || desc == NULL || desc->layer == NULL || desc->position == NULL) {
+        mb_set_error(error, cap, "invalid local transformer arguments");
+        return -1;
+    }
+    if (d->tables == 0 || desc->layers == 0 || desc->layers > 4u || desc->codebooks == 0 ||
+        desc->position_rows < d->tables || d->local.layers != 0) {
+        mb_set_error(error, cap, "local transformer needs embedding tables and projections, 1..4 layers, "
+                                 "one position row per table, and may be attached once");
+        return -1;
+    }
+    MB_TRY(cudaSetDevice(d->st->device), "cudaSetDevice");
+    mb_state *st = d->st;
+    mb_local *lt = &d->local;
+    const size_t W = d->width, F = d->ffn, MB = d->max_batch;
+    const int q = st->quant;
+    int ok = 1;
+#define A_TRY(expr) do { if (ok && (expr) != 0) ok = 0; } while (0)
+    lt->capacity = d->tables + 1u;                  /* src/graph.c:1200 */
+    lt->codebooks = desc->codebooks;
+    A_TRY(upload_vec(&lt->position, desc->position, desc->position_rows * W, error, cap));
+    for (size_t l = 0; l < desc->layers; ++l) {
+        const mynah_b200_local_layer_weights *src = &desc->layer[l];
+        local_layer *L = &lt->L[l];
+        A_TRY(upload_vec(&L->norm_self, src->norm_self, W, error, cap));
+        A_TRY(upload_vec(&L->norm_ff, src->norm_pos_ff, W, error, cap));
+        A_TRY(mb_weight_build(st, src->qkv_w, 3u * W, W, q, &L->qkv, error, cap));
+        A_TRY(mb_weight_build(st, src->o_w, W, W, q, &L->o, error, cap));
+        A_TRY(mb_weight_build(st, src->ffn_up_w, F, W, q, &L->ffn_up, error, cap));
+        A_TRY(mb_weight_build(st, src->ffn_down_w, W, F, q, &L->ffn_down, error, cap));
+        if (ok) d->weight_bytes += L->qkv.bytes + L->o.bytes + L->ffn_up.bytes + L->ffn_down.bytes;
+    }
+    const size_t kv = MB * desc->layers * lt->capacity * W;
+    A_TRY(dmalloc((void **)&lt->k, kv * sizeof(float), error, cap));
+    A_TRY(dmalloc((void **)&lt->v, kv * sizeof(float), error, cap));
+    A_TRY(dmalloc((void **)&lt->row_in, MB * W * sizeof(float), error, cap));
+    A_TRY(dmalloc((void **)&lt->d_temp, MB * sizeof(float), error, cap));
+    A_TRY(dmalloc((void **)&lt->d_topk, MB * sizeof(unsigned), error, cap));
+    A_TRY(dmalloc((void **)&lt->d_rng, MB * sizeof(unsigned long long), error, cap));
+    A_TRY(dmalloc((void **)&lt->d_eos_sub, MB * sizeof(int), error, cap));
+    if (ok) {
+        A_TRY(mb_cuda((int)cudaMemset(lt->k, 0, kv * sizeof(float)), "memset", error, cap));
+        A_TRY(mb_cuda((int)cudaMemset(lt->v, 0, kv * sizeof(float)), "memset", error, cap));
+        A_TRY(mb_cuda((int)cudaMemset(lt->d_temp, 0, MB * sizeof(float)), "memset", error, cap));
+        A_TRY(mb_cuda((int)cudaMemset(lt->d_topk, 0, MB * sizeof(unsigned)), "memset", error, cap));
+        A_TRY(mb_cuda((int)cudaMemset(lt->d_rng, 0, MB * sizeof(unsigned long long)), "memset", error, cap));
+    }
+#undef A_TRY
+    if (!ok) return -1;     /* the decoder's destructor releases whatever was built */
+    lt->layers = desc->layers;
+    mb_clear_error(error, cap);
+    return 0;
+}
+
+/* Sampler settings of `batch` lanes (in lane order) to the device. */
+static int stage_samplers(mb_decoder *d, const mynah_b200_sampler *samplers, const size_t *order,
+                          size_t batch, char *error, size_t cap) {
+    mb_local *lt = &d->local;
+    cudaStream_t s = d->st->stream;
+    float *temp = (float *)d->h_rows;                               /* pinned, >= max_batch floats */
+    unsigned *topk = (unsigned *)(d->h_rows + d->max_batch);
+    unsigned long long *rng = (unsigned long long *)(d->h_rows + 2u * d->max_batch);
+    for (size_t i = 0; i < batch; ++i) {
+        const mynah_b200_sampler *sp = samplers == NULL ? NULL : &samplers[order == NULL ? i : order[i]];
+        temp[i] = sp == NULL ? 0.0f : sp->temperature;
+        topk[i] = sp == NULL ? 0u : sp->topk;
+        rng[i] = sp == NULL ? 0ull : sp->rng_state;
+    }
+    MB_TRY(cudaMemcpyAsync(lt->d_temp, temp, batch * sizeof(float), cudaMemcpyHostToDevice, s), "stage temperatures");
+    MB_TRY(cudaMemcpyAsync(lt->d_topk, topk, batch * sizeof(unsigned), cudaMemcpyHostToDevice, s), "stage top-k");
+    MB_TRY(cudaMemcpyAsync(lt->d_rng, rng, batch * sizeof(unsigned long long), cudaMemcpyHostToDevice, s), "stage rng");
+    /* the pinned block is reused by later calls: finish the copies first */
+    MB_TRY(cudaStreamSynchronize(s), "cudaStreamSynchronize");
+    return 0;
+}
+
+int mynah_b200_decoder_local_frame(void *decoder, const float *decoder_last, size_t batch,
+                                   mynah_b200_sampler *samplers, unsigned *codes, unsigned *values,
+                                   int *saw_eos, long *eos_frame, char *error, size_t cap) {
+    mb_decoder *d = (mb_decoder *)decoder;
+    if (d != NULL && batch == 0) return 0;
+    if (d == NULL || d->local.layers == 0 || decoder_last == NULL || codes == NULL ||
+        batch > d->max_batch) {
+        mb_set_error(error, cap, "local frame: no local transformer attached, or bad arguments");
+        return -1;
+    }
+    MB_TRY(cudaSetDevice(d->st->device), "cudaSetDevice");
+    cudaStream_t s = d->st->stream;
+    const size_t W = d->width, T = d->tables;
+    if (stage_samplers(d, samplers, NULL, batch, error, cap) != 0) return -1;
+    memcpy(d->h_rows, decoder_last, batch * W * sizeof(float));
+    for (size_t b = 0; b < batch; ++b) {
+        d->h_ints[b] = samplers == NULL ? 1 : (samplers[b].allow_eos != 0);
+        d->h_ints[d->max_batch + b] = 0x7fffffff;
+    }
+    MB_TRY(cudaMemcpyAsync(d->out, d->h_rows, batch * W * sizeof(float), cudaMemcpyHostToDevice, s), "stage rows");
+    MB_TRY(cudaMemcpyAsync(d->d_allow_eos, d->h_ints, batch * sizeof(int), cudaMemcpyHostToDevice, s), "stage eos rule");
+    MB_TRY(cudaMemcpyAsync(d->local.d_eos_sub, d->h_ints + d->max_batch, batch * sizeof(int), cudaMemcpyHostToDevice, s), "stage eos frames");
+    MB_TRY(cudaMemsetAsync(d->d_eos_flag, 0, batch * sizeof(int), s), "clear eos flags");
+    MB_TRY(cudaMemcpyAsync(d->d_n_active, &d->h_table[batch], sizeof(int), cudaMemcpyHostToDevice, s), "stage lane count");
+    if (run(d, batch, MODE_LOCAL_ONLY, error, cap) != 0) return -1;
+    unsigned long long *rng = (unsigned long long *)d->h_rows;
+    MB_TRY(cudaMemcpyAsync(d->h_codes, d->d_codes, batch * T * sizeof(unsigned), cudaMemcpyDeviceToHost, s), "read codes");
+    MB_TRY(cudaMemcpyAsync(d->h_tokens, d->d_tokens, batch * T * sizeof(unsigned), cudaMemcpyDeviceToHost, s), "read tokens");
+    MB_TRY(cudaMemcpyAsync(d->h_ints, d->d_eos_flag, batch * sizeof(int), cudaMemcpyDeviceToHost, s), "read eos flags");
+    MB_TRY(cudaMemcpyAsync(d->h_ints + d->max_batch, d->local.d_eos_sub, batch * sizeof(int), cudaMemcpyDeviceToHost, s), "read eos frames");
+    MB_TRY(cudaMemcpyAsync(rng, d->local.d_rng, batch * sizeof(unsigned long long), cudaMemcpyDeviceToHost, s), "read rng");
+    MB_TRY(cudaStreamSynchronize(s), "cudaStreamSynchronize");
+    if (check_status(d, error, cap) != 0) return -1;
+    memcpy(codes, d->h_codes, batch * T * sizeof(unsigned));
+    if (values != NULL) memcpy(values, d->h_tokens, batch * T * sizeof(unsigned));
+    for (size_t b = 0; b < batch; ++b) {
+        if (saw_eos != NULL) saw_eos[b] = d->h_ints[b] != 0;
+        if (eos_frame != NULL) eos_frame[b] = d->h_ints[b] != 0 ? (long)d->h_ints[d->max_batch + b] : -1;
+        if (samplers != NULL) samplers[b].rng_state = rng[b];
+    }
+    mb_clear_error(error, cap);
+    return 0;
 }
 
 /* ----------------------------------------------------------------- profiling */

@@ -253,6 +253,146 @@ k_add_position(const float *__restrict__ rows, const float *__restrict__ positio
         x[(size_t)b * width + d] = __fadd_rn(rows[(size_t)b * width + d], pe[d]);
 }
 
+// x[b] = rows[b] + row: the local transformer's input at one position
+// (src/graph.c:1262-1264; every lane is at the same position of its frame).
+__global__ void __launch_bounds__(256)
+k_add_row(const float *__restrict__ rows, const float *__restrict__ row, float *__restrict__ x, int width,
+          const int *__restrict__ n_active) {
+    mb_pdl_wait();
+    mb_pdl_trigger();
+    const int b = blockIdx.x;
+    if (n_active != nullptr && b >= *n_active) return;
+    for (int d = threadIdx.x; d < width; d += blockDim.x)
+        x[(size_t)b * width + d] = __fadd_rn(rows[(size_t)b * width + d], row[d]);
+}
+
+// One table of one stacked frame, one CTA per lane: the tail of the per-stream loop of
+// sample_local_frame_batch (src/graph.c:1538-1652).
+//   * candidates below codebook_size, and EOS when allowed, compete; the rest count as
+//     -FLT_MAX;
+//   * greedy pick: largest logit, first index on ties;
+//   * when temperature > 0 and topk > 1: the top-k in the reference's insertion order
+//     (higher logit first, earlier index first among equals) is produced by a bitonic sort
+//     of (logit, index) keys; weights exp((l - max) / T) are summed in that order by one
+//     thread, the lane's xorshift64 state advances once, and the drawn token is the first
+//     whose running sum reaches draw = (top 24 bits / 2^24) * total (the last one if none);
+//   * EOS is reported if the greedy or the drawn token is EOS; the stored code collapses
+//     specials to 0; the embedding row of the fed-back token becomes the next input.
+// Dynamic shared memory: n2 keys of 8 bytes + n2 floats, n2 = vocab rounded up to a power
+// of two.
+__device__ __forceinline__ unsigned ordered_bits(float v) {
+    const unsigned u = __float_as_uint(v);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float from_ordered_bits(unsigned o) {
+    return __uint_as_float((o & 0x80000000u) ? (o & 0x7fffffffu) : ~o);
+}
+
+template <bool STRICT>
+__global__ void __launch_bounds__(256)
+k_local_sample(const float *__restrict__ logits, int ld, int vocab, int n2, int codebook_size, int eos_id,
+               const int *__restrict__ allow_eos, const float *__restrict__ temperature,
+               const unsigned *__restrict__ topk, unsigned long long *__restrict__ rng, int table, int tables,
+               int codebooks, unsigned *__restrict__ tokens, unsigned *__restrict__ codes,
+               int *__restrict__ eos_flag, int *__restrict__ eos_sub, const float *__restrict__ emb_table,
+               float *__restrict__ row_in, int width, const uint32_t *__restrict__ exp_tab,
+               const int *__restrict__ n_active) {
+    mb_pdl_wait();
+    mb_pdl_trigger();
+    extern __shared__ __align__(8) unsigned char sample_smem[];
+    unsigned long long *keys = reinterpret_cast<unsigned long long *>(sample_smem);
+    float *weights = reinterpret_cast<float *>(keys + n2);
+    __shared__ float s_best[8];
+    __shared__ int s_idx[8];
+    __shared__ unsigned s_emit;
+    const int b = blockIdx.x;
+    if (n_active != nullptr && b >= *n_active) return;
+    const float *lg = logits + (size_t)b * ld;
+    const bool eos_ok = allow_eos == nullptr || allow_eos[b] != 0;
+    const float temp = temperature != nullptr ? temperature[b] : 0.0f;
+    const unsigned k = topk != nullptr ? topk[b] : 0u;
+    const bool sampling = temp > 0.0f && k > 1u && rng != nullptr;
+    float best = -FLT_MAX;
+    int best_i = 0x7fffffff;
+    for (int c = threadIdx.x; c < n2; c += blockDim.x) {
+        unsigned long long key = 0ull;                       // padding sorts after every candidate
+        if (c < vocab) {
+            const bool ok = c < codebook_size || (c == eos_id && eos_ok);
+            float v = ok ? lg[c] : -FLT_MAX;
+            if (ok && v > best) { best = v; best_i = c; }
+            if (v == 0.0f) v = 0.0f;                         // -0 and +0 compare equal: one key for both
+            key = ((unsigned long long)ordered_bits(v) << 32) | (unsigned)(0xffffffffu - (unsigned)c);
+        }
+        if (sampling) keys[c] = key;
+    }
+    // first-on-ties argmax over the block
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(MB_FULL, best, o);
+        const int oi = __shfl_xor_sync(MB_FULL, best_i, o);
+        if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { s_best[threadIdx.x >> 5] = best; s_idx[threadIdx.x >> 5] = best_i; }
+    __syncthreads();
+    if (sampling) {
+        for (int size = 2; size <= n2; size <<= 1)
+            for (int stride = size >> 1; stride > 0; stride >>= 1) {
+                for (int i = threadIdx.x; i < (n2 >> 1); i += blockDim.x) {
+                    const int lo = ((i / stride) * stride * 2) + (i % stride), hi = lo + stride;
+                    const bool descending = ((lo & size) == 0);
+                    const unsigned long long a = keys[lo], c = keys[hi];
+                    if ((a < c) == descending) { keys[lo] = c; keys[hi] = a; }
+                }
+                __syncthreads();
+            }
+        const int used = (int)min(k, (unsigned)vocab);
+        const float maximum = from_ordered_bits((unsigned)(keys[0] >> 32));
+        for (int q = threadIdx.x; q < used; q += blockDim.x) {
+            const float l = from_ordered_bits((unsigned)(keys[q] >> 32));
+            weights[q] = exp_ref<STRICT>(__fdiv_rn(__fsub_rn(l, maximum), temp), exp_tab);
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        float gb = s_best[0];
+        int gi = s_idx[0];
+        for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+            if (s_best[w] > gb || (s_best[w] == gb && s_idx[w] < gi)) { gb = s_best[w]; gi = s_idx[w]; }
+        const unsigned argmax = gi == 0x7fffffff ? 0u : (unsigned)gi;
+        unsigned value = argmax;
+        if (sampling) {
+            const int used = (int)min(k, (unsigned)vocab);
+            float total = 0.0f;
+            for (int q = 0; q < used; ++q) total = __fadd_rn(total, weights[q]);
+            unsigned long long state = rng[b];
+            state ^= state << 13;
+            state ^= state >> 7;
+            state ^= state << 17;
+            if (state == 0ull) state = 0x9e3779b97f4a7c15ull;
+            rng[b] = state;
+            const float draw = __fmul_rn(__fdiv_rn((float)((state >> 40) & 0xffffffull), 16777216.0f), total);
+            float cumulative = 0.0f;
+            for (int q = 0; q < used; ++q) {
+                cumulative = __fadd_rn(cumulative, weights[q]);
+                if (draw <= cumulative || q + 1 == used) {
+                    value = 0xffffffffu - (unsigned)(keys[q] & 0xffffffffull);
+                    break;
+                }
+            }
+        }
+        const bool eos = argmax == (unsigned)eos_id || value == (unsigned)eos_id;
+        if (eos) {
+            if (eos_flag != nullptr) eos_flag[b] = 1;
+            if (eos_sub != nullptr) eos_sub[b] = min(eos_sub[b], table / codebooks);
+        }
+        tokens[(size_t)b * tables + table] = value;
+        codes[(size_t)b * tables + table] = value < (unsigned)codebook_size ? value : 0u;
+        s_emit = value < (unsigned)vocab ? value : 0u;
+    }
+    __syncthreads();
+    const float *e = emb_table + (size_t)s_emit * width;
+    for (int d = threadIdx.x; d < width; d += blockDim.x) row_in[(size_t)b * width + d] = e[d];
+}
+
 __global__ void k_advance_lens(int *lens, int batch, const int *n_active) {
     mb_pdl_wait();
     mb_pdl_trigger();
@@ -372,6 +512,48 @@ extern "C" int mb_add_position(const float *rows, const float *position, const i
     if (batch == 0) return (int)cudaErrorInvalidValue;
     mb_launch(k_add_position, dim3((unsigned)batch), dim3(256), 0, (cudaStream_t)stream, rows, position, lens, x,
                                                                       (int)width, n_active);
+    return mb_check_launch();
+}
+
+extern "C" int mb_add_row(const float *rows, const float *row, float *x, size_t batch, size_t width,
+                          const int *n_active, mb_stream stream) {
+    if (batch == 0 || width == 0) return (int)cudaErrorInvalidValue;
+    mb_launch(k_add_row, dim3((unsigned)batch), dim3(256), 0, (cudaStream_t)stream, rows, row, x, (int)width, n_active);
+    return mb_check_launch();
+}
+
+extern "C" size_t mb_local_sample_smem(size_t vocab) {
+    size_t n2 = 2;
+    while (n2 < vocab) n2 <<= 1;
+    return n2 * (sizeof(unsigned long long) + sizeof(float));
+}
+
+extern "C" int mb_local_sample(const mb_sample_args *a, mb_stream stream) {
+    if (a == nullptr || a->logits == nullptr || a->batch == 0 || a->vocab == 0 || a->tables == 0 ||
+        a->codebooks == 0 || a->tokens == nullptr || a->codes == nullptr || a->emb_table == nullptr ||
+        a->row_in == nullptr)
+        return (int)cudaErrorInvalidValue;
+    size_t n2 = 2;
+    while (n2 < a->vocab) n2 <<= 1;
+    const size_t smem = mb_local_sample_smem(a->vocab);
+    if (smem > 200u * 1024u) return (int)cudaErrorInvalidValue;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaFuncSetAttribute(k_local_sample<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(k_local_sample<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        attr_set = true;
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    if (a->strict)
+        mb_launch(k_local_sample<true>, dim3((unsigned)a->batch), dim3(256), smem, s, a->logits, (int)a->logits_stride,
+                  (int)a->vocab, (int)n2, (int)a->codebook_size, (int)a->eos_id, a->allow_eos, a->temperature, a->topk,
+                  a->rng, (int)a->table, (int)a->tables, (int)a->codebooks, a->tokens, a->codes, a->eos_flag,
+                  a->eos_sub, a->emb_table, a->row_in, (int)a->width, a->exp_tab, a->n_active);
+    else
+        mb_launch(k_local_sample<false>, dim3((unsigned)a->batch), dim3(256), smem, s, a->logits, (int)a->logits_stride,
+                  (int)a->vocab, (int)n2, (int)a->codebook_size, (int)a->eos_id, a->allow_eos, a->temperature, a->topk,
+                  a->rng, (int)a->table, (int)a->tables, (int)a->codebooks, a->tokens, a->codes, a->eos_flag,
+                  a->eos_sub, a->emb_table, a->row_in, (int)a->width, a->exp_tab, a->n_active);
     return mb_check_launch();
 }
 

@@ -76,6 +76,36 @@ int mb_embed_frames(const float *const *tables, size_t n_tables, size_t vocab, s
 int mb_add_position(const float *rows, const float *position, const int *lens, float *x,
                     size_t batch, size_t width, const int *n_active, mb_stream stream);
 /* lens[b] += 1 for b < n_active */
+/* x[b] = rows[b] + row for every live lane. */
+int mb_add_row(const float *rows, const float *row, float *x, size_t batch, size_t width,
+               const int *n_active, mb_stream stream);
+
+/* One table of a stacked local-transformer frame for `batch` lanes: masked
+ * first-on-ties pick, optional top-k draw with the lane's xorshift64 state
+ * (src/graph.c:1551-1625), stored code, EOS report, and the embedding row of the
+ * fed-back token copied to row_in as the next position's input. */
+typedef struct {
+    const float *logits;      /* [batch][logits_stride], vocab used */
+    size_t logits_stride, vocab, codebook_size, eos_id, batch;
+    const int *allow_eos;     /* [batch] or NULL (allowed) */
+    const float *temperature; /* [batch] or NULL (greedy) */
+    const unsigned *topk;     /* [batch] or NULL (greedy) */
+    unsigned long long *rng;  /* [batch] xorshift64 states or NULL (greedy) */
+    size_t table, tables, codebooks;
+    unsigned *tokens;         /* [batch][tables]: the token fed back (EOS kept) */
+    unsigned *codes;          /* [batch][tables]: the stored code (specials -> 0) */
+    int *eos_flag;            /* [batch] set to 1 on EOS, or NULL */
+    int *eos_sub;             /* [batch] min(table / codebooks) over EOS tables, or NULL */
+    const float *emb_table;   /* [vocab][width]: audio_embeddings.<table>.weight */
+    float *row_in;            /* [batch][width] */
+    size_t width;
+    int strict;
+    const uint32_t *exp_tab;  /* strict: host-libm expf correction table or NULL */
+    const int *n_active;
+} mb_sample_args;
+int mb_local_sample(const mb_sample_args *args, mb_stream stream);
+size_t mb_local_sample_smem(size_t vocab);
+
 int mb_advance_lens(int *lens, size_t batch, const int *n_active, mb_stream stream);
 /* End of one greedy frame for lanes below n_active: lens[b] += 1; append
  * tokens_cur[b][:] to history[*frame_idx][b][:] (rows of lane_stride lanes); record the first frame whose
