@@ -163,6 +163,57 @@ def cpu_reference_job(shape, model, streams: int, frames: int, threads: int | No
     return streams * frames / dt, dt, "port", 1
 
 
+def local_generate_extra(backend, streams: int, args) -> dict:
+    """The sampled generation loop with the local transformer (16 stacked streams, 2 local
+    layers): embed -> decoder step -> 16 local positions with top-k draws, per frame, for
+    `streams` requests; plus the same loop through the reference's own CPU functions on a
+    bounded sample."""
+    from mynah_tts_b200.backend import Decoder
+    from oracle import oracle as O
+    shape = synth.MAGPIE_357M_LOCAL
+    model = synth.make_model(shape, seed=SEED + 7)
+    frames = 64
+    dec = Decoder(backend, model, capacity=frames + 8, slots=streams, max_batch=streams)
+    for slot in range(streams):
+        ck, cv = synthetic_cross_kv(shape, slot)
+        dec.slot_load(slot, ck, cv)
+    start = np.stack([synth.make_codes(shape, seed=SEED + 300 + b, frames=1)[0] for b in range(streams)])
+    lanes = [(0.7, 80, 1000 + b, 1) for b in range(streams)]
+    ms = 0.0
+    for _ in range(3):
+        for slot in range(streams):
+            dec.slot_set_length(slot, 0)
+        _, _, ms, _, _ = dec.generate(list(range(streams)), start, frames, 10 ** 6, lanes)
+    out = {"workload": f"{streams} sampled streams x {frames} frames, 16 stacked streams, 2 local layers, "
+                       "temperature 0.7, top-k 80", "frames_per_s": streams * frames / (ms / 1000.0),
+           "us_per_frame": ms * 1000.0 / frames, "rtf_per_stream": (ms / 1000.0 / frames) * FRAME_RATE}
+    dec.close()
+    if O.have_ref("fast"):
+        n, cpu_frames = min(streams, 16), 6
+        rm = O.RefModel(model, O.INT8, "fast", threads=os.cpu_count() or 1)
+        memory = synth.make_memory(shape, seed=SEED + 100)
+        decs = [rm.new_decoder(memory, cpu_frames + 3) for _ in range(n)]
+        locs = [rm.new_local(80) for _ in range(n)]
+        codes = start[:n].copy()
+        rng = [1000 + b for b in range(n)]
+        t0 = 0.0
+        for f in range(cpu_frames + 1):            # frame 0 packs the weights: not timed
+            if f == 1:
+                t0 = time.perf_counter()
+            rows = np.stack([rm.embed_frame(codes[b]) for b in range(n)])
+            hidden = rm.step_batch(decs, rows)
+            codes, _, _, rng = rm.local_frame(locs, hidden, [0.7] * n, [80] * n, rng, [0] * n)
+        dt = time.perf_counter() - t0
+        for d in decs:
+            d.close()
+        for l in locs:
+            l.close()
+        rm.close()
+        out["cpu_reference"] = {"frames_per_s": n * cpu_frames / dt, "cores": os.cpu_count() or 1,
+                                "sample": f"{n} streams stepped together x {cpu_frames} frames ({dt:.1f} s)"}
+    return out
+
+
 def run_reference(args, rank: int):
     if rank != 0:
         return
@@ -412,6 +463,7 @@ def main():
                                    "frac_of_8tbs": gbs / 8000.0,
                                    "note": "LayerNorm+quant launch plus product launch per pass; cold (pool > L2)"}
             pool.close(); dx.free(); dy.free()
+            extras["generate"] = local_generate_extra(backend, B, args)
         cpu = None
         if world == 1:
             v, dt, kind, cores = cpu_reference_job(shape, model, min(B, 16), args.cpu_frames, None)
