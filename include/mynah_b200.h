@@ -211,6 +211,10 @@ typedef struct {
     const float *o_cross_w;         /* [width, xattn_width] */
     const float *ffn_up_w;          /* [4*width, width] */
     const float *ffn_down_w;        /* [width, 4*width] */
+    /* optional (both or neither): the tensors decoder_cache_init uses to make the cross
+     * K/V of a request (src/graph.c:3002-3016); they enable _slot_prefill */
+    const float *norm_xattn_memory; /* [width] */
+    const float *kv_cross_w;        /* cross_attention.kv_net.weight [2*xattn_width, width] */
 } mynah_b200_layer_weights;
 
 typedef struct {
@@ -244,6 +248,14 @@ void mynah_b200_decoder_destroy(void *decoder);
 int mynah_b200_decoder_slot_load(void *decoder, size_t slot, const float *cross_k,
                                  const float *cross_v, const float *self_k, const float *self_v,
                                  size_t length, char *error, size_t cap);
+/* Make a slot's cross K/V on the device from the text-encoder memory
+ * [memory_length][width] (HOST): what decoder_cache_init computes on the CPU
+ * (src/graph.c:3002-3027).  The slot starts at length 0. */
+int mynah_b200_decoder_slot_prefill(void *decoder, size_t slot, const float *memory,
+                                    size_t memory_length, char *error, size_t cap);
+/* Copy a slot's cross K/V back: host arrays [layers][memory_length][xattn_width]. */
+int mynah_b200_decoder_slot_read_cross(void *decoder, size_t slot, float *cross_k, float *cross_v,
+                                       char *error, size_t cap);
 int mynah_b200_decoder_slot_length(void *decoder, size_t slot, size_t *length, char *error, size_t cap);
 int mynah_b200_decoder_slot_set_length(void *decoder, size_t slot, size_t length, char *error, size_t cap);
 /* Copy a slot's self K/V back: host arrays [layers][capacity][width]. */

@@ -248,6 +248,8 @@ class Decoder:
             L.o_cross_w = fp(model.layer(i, "cross_attention.o_net.weight"))
             L.ffn_up_w = fp(model.layer(i, "pos_ff.proj.conv.weight"))
             L.ffn_down_w = fp(model.layer(i, "pos_ff.o_net.conv.weight"))
+            L.norm_xattn_memory = fp(model.layer(i, "norm_xattn_memory.weight"))
+            L.kv_cross_w = fp(model.layer(i, "cross_attention.kv_net.weight"))
         desc = capi.DecoderDesc()
         desc.layers, desc.width, desc.heads, desc.xattn_width = s.layers, s.width, s.heads, s.xattn_width
         desc.memory_length, desc.capacity, desc.slots = s.memory_length, capacity, slots
@@ -311,6 +313,18 @@ class Decoder:
         sv = None if self_v is None else np.ascontiguousarray(self_v, np.float32)
         call(capi.lib().mynah_b200_decoder_slot_load, self.handle, slot, fp(ck), fp(cv),
              None if sk is None else fp(sk), None if sv is None else fp(sv), length)
+
+    def slot_prefill(self, slot: int, memory: np.ndarray):
+        """Cross K/V of a request made on the device from its text-encoder memory."""
+        mem = np.ascontiguousarray(memory, np.float32)
+        call(capi.lib().mynah_b200_decoder_slot_prefill, self.handle, slot, fp(mem), mem.shape[0])
+
+    def slot_read_cross(self, slot: int):
+        s = self.shape
+        k = np.empty((s.layers, s.memory_length, s.xattn_width), np.float32)
+        v = np.empty_like(k)
+        call(capi.lib().mynah_b200_decoder_slot_read_cross, self.handle, slot, fp(k), fp(v))
+        return k, v
 
     def slot_length(self, slot: int) -> int:
         n = capi.sz(0)

@@ -41,7 +41,7 @@ def load_library() -> C.CDLL:
 class LayerWeights(C.Structure):
     _fields_ = [(n, c_float_p) for n in (
         "norm_self", "norm_xattn_query", "norm_pos_ff", "qkv_w", "o_self_w", "q_cross_w",
-        "o_cross_w", "ffn_up_w", "ffn_down_w")]
+        "o_cross_w", "ffn_up_w", "ffn_down_w", "norm_xattn_memory", "kv_cross_w")]
 
 
 class DecoderDesc(C.Structure):
@@ -143,6 +143,8 @@ SIGNATURES = {
     "mynah_b200_decoder_create": (C.c_int, [C.c_void_p, C.POINTER(DecoderDesc), C.POINTER(C.c_void_p), _E]),
     "mynah_b200_decoder_destroy": (None, [C.c_void_p]),
     "mynah_b200_decoder_slot_load": (C.c_int, [C.c_void_p, sz, c_float_p, c_float_p, c_float_p, c_float_p, sz, _E]),
+    "mynah_b200_decoder_slot_prefill": (C.c_int, [C.c_void_p, sz, c_float_p, sz, _E]),
+    "mynah_b200_decoder_slot_read_cross": (C.c_int, [C.c_void_p, sz, c_float_p, c_float_p, _E]),
     "mynah_b200_decoder_slot_length": (C.c_int, [C.c_void_p, sz, C.POINTER(sz), _E]),
     "mynah_b200_decoder_slot_set_length": (C.c_int, [C.c_void_p, sz, sz, _E]),
     "mynah_b200_decoder_slot_read_kv": (C.c_int, [C.c_void_p, sz, c_float_p, c_float_p, _E]),

@@ -26,6 +26,8 @@ enum { MODE_STEP = 0, MODE_FRAME = 1, MODE_LOCAL = 2, MODE_LOCAL_ONLY = 3, MODE_
 typedef struct {
     float *norm_self, *norm_xattn_query, *norm_pos_ff;
     mb_dev_weight qkv, o_self, q_cross, o_cross, ffn_up, ffn_down;
+    float *norm_xattn_memory;   /* optional: with kv_cross, lets a slot's cross K/V be made here */
+    mb_dev_weight kv_cross;     /* f32 [2*xw, width]; the reference runs it unquantized */
 } dec_layer;
 
 typedef struct {
@@ -160,6 +162,7 @@ void mynah_b200_decoder_destroy(void *decoder) {
         for (size_t l = 0; l < d->layers; ++l) {
             dec_layer *L = &d->L[l];
             cudaFree(L->norm_self); cudaFree(L->norm_xattn_query); cudaFree(L->norm_pos_ff);
+            cudaFree(L->norm_xattn_memory); mb_weight_release(&L->kv_cross);
             mb_weight_release(&L->qkv); mb_weight_release(&L->o_self);
             mb_weight_release(&L->q_cross); mb_weight_release(&L->o_cross);
             mb_weight_release(&L->ffn_up); mb_weight_release(&L->ffn_down);
@@ -265,6 +268,10 @@ int mynah_b200_decoder_create(void *state, const mynah_b200_decoder_desc *desc, 
         D_TRY(upload_vec(&L->norm_self, s->norm_self, W, error, cap));
         D_TRY(upload_vec(&L->norm_xattn_query, s->norm_xattn_query, W, error, cap));
         D_TRY(upload_vec(&L->norm_pos_ff, s->norm_pos_ff, W, error, cap));
+        if (s->norm_xattn_memory != NULL && s->kv_cross_w != NULL) {
+            D_TRY(upload_vec(&L->norm_xattn_memory, s->norm_xattn_memory, W, error, cap));
+            D_TRY(mb_weight_build(st, s->kv_cross_w, 2u * XW, W, MB_F32, &L->kv_cross, error, cap));
+        }
         D_TRY(mb_weight_build(st, s->qkv_w, 3u * W, W, q, &L->qkv, error, cap));
         D_TRY(mb_weight_build(st, s->o_self_w, W, W, q, &L->o_self, error, cap));
         D_TRY(mb_weight_build(st, s->q_cross_w, XW, W, q, &L->q_cross, error, cap));
@@ -743,6 +750,80 @@ int mynah_b200_decoder_slot_load(void *decoder, size_t slot, const float *cross_
     }
     MB_TRY(cudaStreamSynchronize(s), "cudaStreamSynchronize");
     d->slot_len[slot] = length;
+    mb_clear_error(error, cap);
+    return 0;
+}
+
+/* decoder_cache_init's cross K/V (src/graph.c:3002-3027) on the device: per layer
+ * LayerNorm(memory, norm_xattn_memory) through kv_net in f32 (the reference calls the
+ * backend's f32 matmul here whatever MYNAH_QUANT says), first xw columns K, next xw V. */
+int mynah_b200_decoder_slot_prefill(void *decoder, size_t slot, const float *memory,
+                                    size_t memory_length, char *error, size_t cap) {
+    mb_decoder *d = (mb_decoder *)decoder;
+    if (check_slot(d, slot, error, cap) != 0) return -1;
+    if (memory == NULL || memory_length != d->T) {
+        mb_set_error(error, cap, "prefill: memory must have the decoder's memory_length rows");
+        return -1;
+    }
+    for (size_t l = 0; l < d->layers; ++l)
+        if (d->L[l].norm_xattn_memory == NULL || d->L[l].kv_cross.w == NULL) {
+            mb_set_error(error, cap, "prefill: the decoder was created without norm_xattn_memory / kv_net weights");
+            return -1;
+        }
+    mb_state *st = d->st;
+    cudaStream_t s = st->stream;
+    const size_t W = d->width, XW = d->xw, T = d->T;
+    float *mem = NULL, *nrm = NULL, *kv = NULL;
+    int rc = 0;
+#define F_TRY(expr, what) do { if (rc == 0 && mb_cuda((int)(expr), (what), error, cap) != 0) rc = -1; } while (0)
+    F_TRY(cudaMalloc((void **)&mem, T * W * sizeof(float)), "cudaMalloc(prefill)");
+    F_TRY(cudaMalloc((void **)&nrm, T * W * sizeof(float)), "cudaMalloc(prefill)");
+    F_TRY(cudaMalloc((void **)&kv, T * 2u * XW * sizeof(float)), "cudaMalloc(prefill)");
+    F_TRY(cudaMemcpyAsync(mem, memory, T * W * sizeof(float), cudaMemcpyHostToDevice, s), "upload memory");
+    const size_t cross_n = d->layers * T * XW;
+    for (size_t l = 0; l < d->layers && rc == 0; ++l) {
+        F_TRY(mb_layernorm(mem, nrm, d->L[l].norm_xattn_memory, NULL, T, W, 1.0e-5f, NULL, NULL, NULL,
+                           st->strict, s), "layer norm of the memory");
+        mb_gemv_args g;
+        memset(&g, 0, sizeof(g));
+        mb_gemv_bind_weight(&g, &d->L[l].kv_cross, NULL);
+        g.x = nrm;
+        g.out = kv;
+        g.out_stride = 2u * XW;
+        g.batch = T;
+        g.epilogue = MB_EPI_STORE;
+        g.strict = st->strict;
+        F_TRY(mb_gemv(&g, s), "kv_net product");
+        float *ck = d->cross_k + slot * cross_n + l * T * XW;
+        float *cv = d->cross_v + slot * cross_n + l * T * XW;
+        F_TRY(cudaMemcpy2DAsync(ck, XW * sizeof(float), kv, 2u * XW * sizeof(float), XW * sizeof(float), T,
+                                cudaMemcpyDeviceToDevice, s), "split K");
+        F_TRY(cudaMemcpy2DAsync(cv, XW * sizeof(float), kv + XW, 2u * XW * sizeof(float), XW * sizeof(float), T,
+                                cudaMemcpyDeviceToDevice, s), "split V");
+        st->launches += 2u;
+    }
+    F_TRY(cudaStreamSynchronize(s), "cudaStreamSynchronize");
+#undef F_TRY
+    cudaFree(mem); cudaFree(nrm); cudaFree(kv);
+    if (rc != 0) return -1;
+    d->slot_len[slot] = 0;
+    mb_clear_error(error, cap);
+    return 0;
+}
+
+/* Copy a slot's cross K/V back: host arrays [layers][memory_length][xattn_width]. */
+int mynah_b200_decoder_slot_read_cross(void *decoder, size_t slot, float *cross_k, float *cross_v,
+                                       char *error, size_t cap) {
+    mb_decoder *d = (mb_decoder *)decoder;
+    if (check_slot(d, slot, error, cap) != 0) return -1;
+    if (cross_k == NULL || cross_v == NULL) {
+        mb_set_error(error, cap, "invalid buffers");
+        return -1;
+    }
+    const size_t cross_n = d->layers * d->T * d->xw;
+    MB_TRY(cudaStreamSynchronize(d->st->stream), "cudaStreamSynchronize");
+    MB_TRY(cudaMemcpy(cross_k, d->cross_k + slot * cross_n, cross_n * sizeof(float), cudaMemcpyDeviceToHost), "read cross K");
+    MB_TRY(cudaMemcpy(cross_v, d->cross_v + slot * cross_n, cross_n * sizeof(float), cudaMemcpyDeviceToHost), "read cross V");
     mb_clear_error(error, cap);
     return 0;
 }

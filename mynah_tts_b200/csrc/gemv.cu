@@ -360,7 +360,9 @@ int launch_tiled(const GemvP &p, size_t groups, cudaStream_t s) {
 
 template <int QT, bool STRICT>
 int launch_qt(const GemvP &p, size_t groups, bool tiled, cudaStream_t s) {
-    if (!tiled) {
+    // Strict f32: the reference's scalar build sums a row's products one after another
+    // (src/kernels.c:40-44); only the one-thread-per-output kernel keeps that order.
+    if (!tiled || (STRICT && QT == MB_F32 && groups == 1)) {
         if (groups != 1) return (int)cudaErrorInvalidValue;
         const long total = p.n * p.batch;
         mb_launch(k_gemv_generic<QT, STRICT>, dim3((unsigned)((total + 127) / 128)), dim3(128), 0, s, p);

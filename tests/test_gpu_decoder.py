@@ -323,3 +323,27 @@ def test_full_size_properties_64_streams(golden):
         assert not tokens2[frames[b]:, b].any()
         assert dec.slot_length(b) == frames[b]
     dec.close(); be.close()
+
+
+@pytest.mark.parametrize("strict", [True, False])
+def test_slot_prefill_makes_the_reference_cross_kv(strict, tiny_model, tiny_memory, golden):
+    """Cross K/V made on the device from the text memory (decoder_cache_init,
+    src/graph.c:3002-3027: LayerNorm then the f32 kv_net product, whatever the
+    weight format of the step) against the fixture taken from the reference, and a
+    greedy decode from the prefilled slot against the reference's token stream."""
+    shape = synth.TINY
+    be = Backend("int8", strict=strict)
+    dec = Decoder(be, tiny_model, capacity=80, slots=2)
+    dec.slot_prefill(1, tiny_memory)
+    k, v = dec.slot_read_cross(1)
+    if strict:
+        assert np.array_equal(k, golden["tiny_cross_k"]) and np.array_equal(v, golden["tiny_cross_v"])
+        want = golden["tiny_int8_greedy_tokens"]
+        start = synth.make_codes(shape, seed=9, frames=1)
+        tokens, _, _, _ = dec.greedy([1], start, 64, min_frames=4)
+        assert np.array_equal(tokens[:len(want), 0], want)
+    else:
+        assert rel_err(k, golden["tiny_cross_k"]) < 1e-5 and rel_err(v, golden["tiny_cross_v"]) < 1e-5
+    with pytest.raises(MynahB200Error):
+        dec.slot_prefill(0, tiny_memory[:-1])
+    dec.close(); be.close()
