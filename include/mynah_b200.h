@@ -346,6 +346,37 @@ int mynah_b200_decoder_generate(void *decoder, const unsigned *slots, size_t bat
                                 mynah_b200_sampler *samplers, unsigned *tokens, long *eos_frame,
                                 float *elapsed_ms, char *error, size_t cap);
 
+/* frame_batch with the local transformer: codes [batch][tables] in (the previous
+ * frame's stored codes), one decoder step, one stacked local frame; codes_out, values
+ * (optional), saw_eos, eos_frame as _local_frame reports them; samplers advanced.
+ * Synchronous. */
+int mynah_b200_decoder_frame_batch_local(void *decoder, const unsigned *slots, const unsigned *codes,
+                                         mynah_b200_sampler *samplers, unsigned *codes_out,
+                                         unsigned *values, int *saw_eos, long *eos_frame,
+                                         size_t batch, char *error, size_t cap);
+
+/* Continuous batching (no counterpart in the reference, whose synthesize_slots steps
+ * at most 16 requests that start together and whose server never admits into a
+ * running batch): `count` requests share the decoder's slots; a waiting request
+ * enters as soon as a slot is free (its cross K/V are made on the device, so the
+ * layer weights must carry norm_xattn_memory / kv_cross_w), every live request
+ * advances one sampled frame per step, and a request leaves when EOS is seen (allowed
+ * once frames_done >= min_frames) or at max_frames (src/graph.c:3912-3913).  Because a
+ * request's result does not depend on its batch, codes equal what the request
+ * produces alone. */
+typedef struct {
+    const float *memory;         /* [memory_length][width] text-encoder states (HOST) */
+    const unsigned *start_codes; /* [tables]: the frame embedded before the first step */
+    size_t max_frames, min_frames;
+    mynah_b200_sampler sampler;  /* advanced; allow_eos is ignored */
+    unsigned *codes;             /* out: [max_frames][tables] stored codes (caller-allocated) */
+    size_t frames_done;          /* out */
+    long eos_frame;              /* out: frame in which EOS was seen, -1 if none */
+    size_t admitted_at;          /* out: step at which the request entered a slot */
+} mynah_b200_request;
+int mynah_b200_decoder_serve(void *decoder, mynah_b200_request *requests, size_t count,
+                             size_t *steps, char *error, size_t cap);
+
 /* Bytes of weights one step reads, and of KV one slot at `length` reads. */
 size_t mynah_b200_decoder_weight_bytes(const void *decoder);
 size_t mynah_b200_decoder_kv_bytes(const void *decoder, size_t length);

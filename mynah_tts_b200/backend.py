@@ -411,6 +411,44 @@ class Decoder:
         return (tokens, np.array(list(eos)), float(ms.value), codes,
                 [int(arr[b].rng_state) for b in range(batch)])
 
+    def frame_batch_local(self, slots, codes: np.ndarray, samplers=None):
+        """One sampled frame for the given slots -> codes, values, saw_eos, eos_frame, rng."""
+        batch = len(slots)
+        codes = np.ascontiguousarray(codes, np.uint32)
+        arr = self._samplers(batch, samplers)
+        out = np.zeros((batch, self.shape.tables), np.uint32)
+        values = np.zeros_like(out)
+        saw = (C.c_int * batch)()
+        eos = (C.c_long * batch)()
+        call(capi.lib().mynah_b200_decoder_frame_batch_local, self.handle, (C.c_uint * batch)(*slots),
+             codes.ctypes.data_as(capi.c_uint_p), arr, out.ctypes.data_as(capi.c_uint_p),
+             values.ctypes.data_as(capi.c_uint_p), saw, eos, batch)
+        return (out, values, np.array(list(saw)), np.array(list(eos)),
+                [int(arr[b].rng_state) for b in range(batch)])
+
+    def serve(self, requests):
+        """Continuous batching.  requests: list of dicts with memory, start_codes,
+        max_frames, min_frames, sampler (temperature, topk, rng).  Returns a list of
+        (codes [frames_done, tables], eos_frame, admitted_at, rng) and the step count."""
+        n = len(requests)
+        arr = (capi.Request * n)()
+        keep = []
+        for i, r in enumerate(requests):
+            mem = np.ascontiguousarray(r["memory"], np.float32)
+            start = np.ascontiguousarray(r["start_codes"], np.uint32)
+            out = np.zeros((r["max_frames"], self.shape.tables), np.uint32)
+            keep.append((mem, start, out))
+            arr[i].memory, arr[i].start_codes = fp(mem), start.ctypes.data_as(capi.c_uint_p)
+            arr[i].max_frames, arr[i].min_frames = r["max_frames"], r.get("min_frames", 0)
+            t = r.get("sampler", (0.0, 0, 0))
+            arr[i].sampler.temperature, arr[i].sampler.topk, arr[i].sampler.rng_state = float(t[0]), int(t[1]), int(t[2])
+            arr[i].codes = out.ctypes.data_as(capi.c_uint_p)
+        steps = capi.sz(0)
+        call(capi.lib().mynah_b200_decoder_serve, self.handle, arr, n, C.byref(steps))
+        results = [(keep[i][2][:arr[i].frames_done].copy(), int(arr[i].eos_frame), int(arr[i].admitted_at),
+                    int(arr[i].sampler.rng_state)) for i in range(n)]
+        return results, int(steps.value)
+
     def greedy(self, slots, codes: np.ndarray, frames, min_frames: int = 0):
         """codes [batch, tables]; frames: int or per-lane list.  Returns
         (tokens [max_frames, batch, tables], eos_frame [batch], device ms)."""

@@ -71,6 +71,12 @@ class Sampler(C.Structure):
                 ("allow_eos", C.c_int)]
 
 
+class Request(C.Structure):
+    _fields_ = [("memory", c_float_p), ("start_codes", c_uint_p), ("max_frames", sz), ("min_frames", sz),
+                ("sampler", Sampler), ("codes", c_uint_p), ("frames_done", sz), ("eos_frame", C.c_long),
+                ("admitted_at", sz)]
+
+
 MATMUL_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, c_float_p, c_float_p, sz, sz, sz, c_float_p, c_float_p,
                         C.c_char_p, sz)
 SGEMM_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_int, C.c_int, sz, sz, sz, C.c_float, c_float_p, sz,
@@ -160,6 +166,9 @@ SIGNATURES = {
                                                  c_uint_p, c_int_p, C.POINTER(C.c_long), _E]),
     "mynah_b200_decoder_generate": (C.c_int, [C.c_void_p, c_uint_p, sz, c_uint_p, C.POINTER(sz), sz,
                                               C.POINTER(Sampler), c_uint_p, C.POINTER(C.c_long), c_float_p, _E]),
+    "mynah_b200_decoder_frame_batch_local": (C.c_int, [C.c_void_p, c_uint_p, c_uint_p, C.POINTER(Sampler),
+                                                       c_uint_p, c_uint_p, c_int_p, C.POINTER(C.c_long), sz, _E]),
+    "mynah_b200_decoder_serve": (C.c_int, [C.c_void_p, C.POINTER(Request), sz, C.POINTER(sz), _E]),
     "mynah_b200_decoder_profile": (C.c_int, [C.c_void_p, C.c_int, _E]),
     "mynah_b200_decoder_profile_read": (C.c_int, [C.c_void_p, C.POINTER(C.c_ulonglong),
                                                   C.POINTER(C.c_double), sz, _E]),

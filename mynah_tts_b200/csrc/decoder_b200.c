@@ -1218,6 +1218,140 @@ int mynah_b200_decoder_local_frame(void *decoder, const float *decoder_last, siz
     return 0;
 }
 
+/* One sampled frame for `batch` slots with HOST buffers: frame_batch with the local
+ * transformer and its sampler in place of the logit heads (one iteration of the loop of
+ * synthesize_slots, src/graph.c:4083-4183). */
+int mynah_b200_decoder_frame_batch_local(void *decoder, const unsigned *slots, const unsigned *codes,
+                                         mynah_b200_sampler *samplers, unsigned *codes_out,
+                                         unsigned *values, int *saw_eos, long *eos_frame,
+                                         size_t batch, char *error, size_t cap) {
+    mb_decoder *d = (mb_decoder *)decoder;
+    if (d != NULL && batch == 0) return 0;
+    if (d == NULL || d->local.layers == 0 || codes == NULL || codes_out == NULL) {
+        mb_set_error(error, cap, "sampled frame: no local transformer attached, or bad arguments");
+        return -1;
+    }
+    if (stage_lanes(d, slots, batch, error, cap) != 0) return -1;
+    if (stage_samplers(d, samplers, NULL, batch, error, cap) != 0) return -1;
+    const size_t T = d->tables, nt = batch * T;
+    cudaStream_t s = d->st->stream;
+    memcpy(d->h_codes, codes, nt * sizeof(unsigned));
+    for (size_t b = 0; b < batch; ++b) {
+        d->h_ints[b] = samplers == NULL ? 1 : (samplers[b].allow_eos != 0);
+        d->h_ints[d->max_batch + b] = 0x7fffffff;
+    }
+    MB_TRY(cudaMemcpyAsync(d->d_codes, d->h_codes, nt * sizeof(unsigned), cudaMemcpyHostToDevice, s), "stage codes");
+    MB_TRY(cudaMemcpyAsync(d->d_allow_eos, d->h_ints, batch * sizeof(int), cudaMemcpyHostToDevice, s), "stage eos rule");
+    MB_TRY(cudaMemcpyAsync(d->local.d_eos_sub, d->h_ints + d->max_batch, batch * sizeof(int), cudaMemcpyHostToDevice, s), "stage eos frames");
+    MB_TRY(cudaMemsetAsync(d->d_eos_flag, 0, batch * sizeof(int), s), "clear eos flags");
+    MB_TRY(cudaMemsetAsync(d->d_frame_idx, 0, sizeof(int), s), "clear frame index");
+    /* frame_advance rewrites the EOS rule for the next frame from min_frames; this entry
+     * point restages it on every call, so park min_frames at 0 */
+    MB_TRY(cudaMemsetAsync(d->d_min_frames, 0, sizeof(int), s), "clear min frames");
+    if (run(d, batch, MODE_LOCAL, error, cap) != 0) return -1;
+    unsigned long long *rng = (unsigned long long *)d->h_rows;
+    MB_TRY(cudaMemcpyAsync(d->h_codes, d->d_codes, nt * sizeof(unsigned), cudaMemcpyDeviceToHost, s), "read codes");
+    MB_TRY(cudaMemcpyAsync(d->h_tokens, d->d_tokens, nt * sizeof(unsigned), cudaMemcpyDeviceToHost, s), "read tokens");
+    MB_TRY(cudaMemcpyAsync(d->h_ints, d->d_eos_flag, batch * sizeof(int), cudaMemcpyDeviceToHost, s), "read eos flags");
+    MB_TRY(cudaMemcpyAsync(d->h_ints + d->max_batch, d->local.d_eos_sub, batch * sizeof(int), cudaMemcpyDeviceToHost, s), "read eos frames");
+    MB_TRY(cudaMemcpyAsync(rng, d->local.d_rng, batch * sizeof(unsigned long long), cudaMemcpyDeviceToHost, s), "read rng");
+    MB_TRY(cudaStreamSynchronize(s), "cudaStreamSynchronize");
+    if (check_status(d, error, cap) != 0) return -1;
+    memcpy(codes_out, d->h_codes, nt * sizeof(unsigned));
+    if (values != NULL) memcpy(values, d->h_tokens, nt * sizeof(unsigned));
+    for (size_t b = 0; b < batch; ++b) {
+        if (saw_eos != NULL) saw_eos[b] = d->h_ints[b] != 0;
+        if (eos_frame != NULL) eos_frame[b] = d->h_ints[b] != 0 ? (long)d->h_ints[d->max_batch + b] : -1;
+        if (samplers != NULL) samplers[b].rng_state = rng[b];
+        d->slot_len[slots[b]] += 1u;
+    }
+    mb_clear_error(error, cap);
+    return 0;
+}
+
+/* Continuous batching over the decoder's slots (the reference steps at most 16 requests
+ * that all start together, src/graph.c:4046-4200, and its server never admits into a
+ * running batch): requests wait in order, a free slot is filled before the next frame
+ * (cross K/V made on the device), every live request advances one frame per step, and a
+ * request leaves on EOS or at its frame limit, as slot_advance decides
+ * (src/graph.c:3912-3913). */
+int mynah_b200_decoder_serve(void *decoder, mynah_b200_request *requests, size_t count,
+                             size_t *steps_out, char *error, size_t cap) {
+    mb_decoder *d = (mb_decoder *)decoder;
+    if (d == NULL || d->local.layers == 0 || (requests == NULL && count > 0)) {
+        mb_set_error(error, cap, "serve: no local transformer attached, or bad arguments");
+        return -1;
+    }
+    const size_t T = d->tables, lanes_max = d->slots < d->max_batch ? d->slots : d->max_batch;
+    size_t *owner = (size_t *)malloc(lanes_max * sizeof(size_t));       /* request in slot s, or SIZE_MAX */
+    unsigned *slot_ids = (unsigned *)malloc(lanes_max * sizeof(unsigned));
+    unsigned *codes = (unsigned *)malloc(lanes_max * T * sizeof(unsigned));
+    unsigned *next = (unsigned *)malloc(lanes_max * T * sizeof(unsigned));
+    mynah_b200_sampler *sp = (mynah_b200_sampler *)malloc(lanes_max * sizeof(mynah_b200_sampler));
+    int *saw = (int *)malloc(lanes_max * sizeof(int));
+    int rc = 0;
+    if (!owner || !slot_ids || !codes || !next || !sp || !saw) {
+        mb_set_error(error, cap, "out of memory");
+        rc = -1;
+    }
+    for (size_t i = 0; rc == 0 && i < count; ++i) {
+        if (requests[i].memory == NULL || requests[i].start_codes == NULL || requests[i].codes == NULL ||
+            requests[i].max_frames > d->capacity) {
+            mb_set_error(error, cap, "serve: a request lacks buffers or exceeds the cache capacity");
+            rc = -1;
+        }
+        requests[i].frames_done = 0;
+        requests[i].eos_frame = -1;
+        requests[i].admitted_at = 0;
+    }
+    for (size_t s = 0; rc == 0 && s < lanes_max; ++s) owner[s] = SIZE_MAX;
+    size_t waiting = 0, live = 0, step = 0;
+    while (rc == 0 && (waiting < count || live > 0)) {
+        for (size_t s = 0; s < lanes_max && waiting < count && rc == 0; ++s) {
+            if (owner[s] != SIZE_MAX) continue;
+            mynah_b200_request *r = &requests[waiting];
+            if (r->max_frames == 0) { ++waiting; --s; continue; }
+            if (mynah_b200_decoder_slot_prefill(d, s, r->memory, d->T, error, cap) != 0) { rc = -1; break; }
+            owner[s] = waiting++;
+            r->admitted_at = step;
+            ++live;
+        }
+        if (rc != 0 || live == 0) break;
+        size_t nb = 0;
+        for (size_t s = 0; s < lanes_max; ++s) {
+            if (owner[s] == SIZE_MAX) continue;
+            mynah_b200_request *r = &requests[owner[s]];
+            slot_ids[nb] = (unsigned)s;
+            memcpy(codes + nb * T, r->frames_done == 0 ? r->start_codes : r->codes + (r->frames_done - 1u) * T,
+                   T * sizeof(unsigned));
+            sp[nb] = r->sampler;
+            sp[nb].allow_eos = r->frames_done >= r->min_frames;
+            ++nb;
+        }
+        if (mynah_b200_decoder_frame_batch_local(d, slot_ids, codes, sp, next, NULL, saw, NULL, nb, error, cap) != 0) {
+            rc = -1;
+            break;
+        }
+        for (size_t b = 0; b < nb; ++b) {
+            const size_t s = slot_ids[b];
+            mynah_b200_request *r = &requests[owner[s]];
+            memcpy(r->codes + r->frames_done * T, next + b * T, T * sizeof(unsigned));
+            r->sampler.rng_state = sp[b].rng_state;
+            if (saw[b] && r->eos_frame < 0) r->eos_frame = (long)r->frames_done;
+            r->frames_done += 1u;
+            if (saw[b] || r->frames_done >= r->max_frames) {
+                owner[s] = SIZE_MAX;
+                --live;
+            }
+        }
+        ++step;
+    }
+    free(owner); free(slot_ids); free(codes); free(next); free(sp); free(saw);
+    if (steps_out != NULL) *steps_out = step;
+    if (rc == 0) mb_clear_error(error, cap);
+    return rc;
+}
+
 /* ----------------------------------------------------------------- profiling */
 int mynah_b200_decoder_profile(void *decoder, int enable, char *error, size_t cap) {
     mb_decoder *d = (mb_decoder *)decoder;

@@ -153,3 +153,43 @@ def test_local_requests_are_refused_without_local_weights(tiny_model):
     with pytest.raises(MynahB200Error):
         dec.generate([0], np.zeros((1, synth.TINY.tables), np.uint32), 2)
     dec.close(); be.close()
+
+
+def test_continuous_batching_gives_each_request_its_solo_result(tiny_local_model):
+    """Eight requests over three slots: a request enters when a slot frees up, leaves on
+    EOS or at its frame limit, and its codes are what the reference's functions give
+    for the request alone (port loop: embed -> decoder step -> local frame)."""
+    from mynah_tts_b200.backend import Backend, Decoder
+    shape = synth.TINY_LOCAL
+    pm = O.PortModel(tiny_local_model, O.INT8)
+    reqs, want = [], []
+    for i in range(8):
+        memory = synth.make_memory(shape, seed=700 + i)
+        start = synth.make_codes(shape, seed=800 + i, frames=1)[0]
+        sampler = (0.9, 12, 5000 + i) if i % 2 else (0.0, 0, 0)
+        max_frames, min_frames = 6 + 3 * i, 2 + (i % 3)
+        reqs.append({"memory": memory, "start_codes": start, "max_frames": max_frames,
+                     "min_frames": min_frames, "sampler": sampler})
+        st = pm.new_stream(memory, max_frames + 2)
+        pl = O.PortLocal(pm, 16)
+        codes, rng, out, eos_at = start.copy(), sampler[2], [], -1
+        for f in range(max_frames):
+            hidden = st.step(pm.embed_frame(codes))
+            codes, _, saw, _, rng = pl.frame(hidden, sampler[0], sampler[1], rng, f >= min_frames)
+            out.append(codes.copy())
+            if saw:
+                eos_at = f
+                break
+        want.append((np.stack(out), eos_at, rng))
+        st.close(); pl.close()
+    pm.close()
+    be = Backend("int8", strict=True)
+    dec = Decoder(be, tiny_local_model, capacity=40, slots=3)
+    results, steps = dec.serve(reqs)
+    for i, (codes, eos_frame, admitted_at, rng) in enumerate(results):
+        assert np.array_equal(codes, want[i][0]), i
+        assert eos_frame == want[i][1] and rng == want[i][2]
+        assert (admitted_at == 0) == (i < 3)
+    total = sum(len(w[0]) for w in want)
+    assert max(len(w[0]) for w in want) <= steps < total      # requests overlapped
+    dec.close(); be.close()
