@@ -214,6 +214,32 @@ def local_generate_extra(backend, streams: int, args) -> dict:
     return out
 
 
+def ragged_int4_extra(shape, model, device: int, streams: int) -> dict:
+    """int4 (group 32) weights, `streams` greedy streams whose lengths are uniform in
+    [128, 1024] from the seed; a stream leaves the batch at its length.  Aggregate frames/s
+    of the device-resident loop."""
+    from mynah_tts_b200.backend import Backend, Decoder
+    rng = np.random.default_rng([SEED, 0x726167])
+    lengths = [int(x) for x in rng.integers(128, 1025, size=streams)]
+    backend = Backend("int4", strict=False, device=device)
+    dec = Decoder(backend, model, capacity=max(lengths) + 8, slots=streams, max_batch=streams)
+    for slot in range(streams):
+        ck, cv = synthetic_cross_kv(shape, slot)
+        dec.slot_load(slot, ck, cv)
+    start = np.stack([synth.make_codes(shape, seed=SEED + 200 + b, frames=1)[0] for b in range(streams)])
+    ms = 0.0
+    for _ in range(2):
+        for slot in range(streams):
+            dec.slot_set_length(slot, 0)
+        _, _, ms, _ = dec.greedy(list(range(streams)), start, lengths, min_frames=10 ** 6)
+    dec.close()
+    backend.close()
+    return {"workload": f"int4 group-32 weights, {streams} greedy streams, lengths uniform[128,1024] "
+                        f"(sum {sum(lengths)}, max {max(lengths)}), a stream leaves at its length",
+            "frames_per_s": sum(lengths) / (ms / 1000.0), "ms": ms,
+            "note": "int4 products run the SIMT kernel at every batch size"}
+
+
 def run_reference(args, rank: int):
     if rank != 0:
         return
@@ -464,6 +490,7 @@ def main():
                                    "note": "LayerNorm+quant launch plus product launch per pass; cold (pool > L2)"}
             pool.close(); dx.free(); dy.free()
             extras["generate"] = local_generate_extra(backend, B, args)
+            extras["ragged_int4"] = ragged_int4_extra(shape, model, local_rank, B)
         cpu = None
         if world == 1:
             v, dt, kind, cores = cpu_reference_job(shape, model, min(B, 16), args.cpu_frames, None)
