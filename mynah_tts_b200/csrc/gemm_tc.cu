@@ -260,6 +260,223 @@ k_gemm_i8_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
 }
 
+// ------------------------------------------------------------------ int4 weights
+// The same tile for int4 weights in groups of 32 (src/qmat.c:154-185): per group an exact
+// int32 dot, scaled by the group's f32 scale and added up in group order.  A group is one
+// K = 32 MMA, so every group gets its own accumulator in tensor memory:
+//   * TMA brings [128 rows x 64 packed bytes] of W (128 elements, 4 groups) and
+//     [16 lanes x 128 B] of the int8 activations per stage;
+//   * the CTA's 512 threads unpack four stages at a time, a quarter of a weight row each:
+//     low nibble = even k, minus 8, written as int8 in the 128-byte-swizzled operand
+//     layout; one proxy fence and one barrier hand them to the MMA thread;
+//   * four MMAs per stage (accumulate off), each into its own 16 columns; the 16 groups of
+//     a pass fill the 256 allocated columns, then all threads read them back with
+//     tcgen05.ld and fold them into f32 sums, group by group, and the next pass reuses
+//     the columns.
+// Same bits as the SIMT kernel's int4 path.
+constexpr int I4_PASS_CHUNKS = 4;         // stages per pass (4 groups each): 16 accumulators
+constexpr int I4_STAGES = 2 * I4_PASS_CHUNKS;   // packed stages in flight: this pass and the next
+constexpr int I4_THREADS = 512;
+constexpr int P_BYTES = TM * 64;          // packed weights of a stage, 8 KB
+constexpr int I4_COLS = 256;              // 16 accumulators of 16 columns
+
+__device__ __forceinline__ void tmem_ld4_nowait(uint32_t taddr, int (&v)[4]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3])
+                 : "r"(taddr)
+                 : "memory");
+}
+
+// Threads: t / 4 is the weight row a thread unpacks (a quarter of a stage's 64 packed bytes
+// each).  Tensor memory is read per warp: warp w reaches rows 32 * (w % 4) .. + 31 of the
+// tile, and takes lanes (columns) 4 * (w / 4) .. + 3 of every group's accumulator.
+// A pass = up to four stages: wait for them, unpack them, one proxy fence and one barrier,
+// sixteen MMAs, one commit; then every thread reads its accumulators and the stages are
+// refilled for the pass after the next.
+__global__ void __launch_bounds__(I4_THREADS)
+k_gemm_i4_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcP p) {
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) unsigned long long full_bar[I4_STAGES];
+    __shared__ __align__(8) unsigned long long pass_bar;
+    __shared__ uint32_t s_tmem;
+    __shared__ unsigned s_fail;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int b0 = blockIdx.y * BN;
+    const long m0 = (long)blockIdx.x * TM;
+    const int nchunks = (int)(p.k / KC);                    // k is a multiple of 128 here
+    unsigned char *base = smem_raw + ((1024u - (saddr(smem_raw) & 1023u)) & 1023u);
+    unsigned char *Ap = base;                                   // [4][128 rows][128 B] unpacked, swizzled
+    unsigned char *Bs = Ap + (size_t)I4_PASS_CHUNKS * A_BYTES;  // [stage][16 lanes][128 B] swizzled
+    unsigned char *Pk = Bs + (size_t)I4_STAGES * B_BYTES;       // [stage][128 rows][64 B] packed
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < I4_STAGES; ++s) bar_init(&full_bar[s], 1u);
+        bar_init(&pass_bar, 1u);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        s_fail = 0u;
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(saddr(&s_tmem)), "r"(I4_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = s_tmem;
+    const unsigned stage_bytes = (unsigned)(P_BYTES + B_BYTES);
+    const int first = min(nchunks, I4_STAGES);
+    if (threadIdx.x == 0) {                                 // weights: before the dependency wait
+        for (int c = 0; c < first; ++c) {
+            bar_expect(&full_bar[c], stage_bytes);
+            tma_load_2d(Pk + (size_t)c * P_BYTES, &map_w, c * (KC / 2), (int)m0, &full_bar[c]);
+        }
+    }
+    mb_pdl_wait();
+    mb_pdl_trigger();
+    const int nb = p.n_active != nullptr ? min(p.batch, *p.n_active) : p.batch;
+    if (b0 >= nb) {
+        if (threadIdx.x == 0) {
+            for (int c = 0; c < first; ++c) {
+                tma_load_2d(Bs + (size_t)c * B_BYTES, &map_x, c * KC, b0, &full_bar[c]);
+                bar_wait(&full_bar[c], 0u, TC_SPIN);
+            }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        if (warp == 0)
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(I4_COLS) : "memory");
+        return;
+    }
+    if (threadIdx.x == 0)
+        for (int c = 0; c < first; ++c) tma_load_2d(Bs + (size_t)c * B_BYTES, &map_x, c * KC, b0, &full_bar[c]);
+    auto wait = [&](void *bar, unsigned parity, int bit) {
+        if (*reinterpret_cast<volatile unsigned *>(&s_fail) != 0u) return false;
+        if (bar_wait(bar, parity, TC_SPIN)) return true;
+        s_fail = 1u;
+        if (p.status != nullptr) atomicOr(p.status, bit);
+        return false;
+    };
+    // unpacking role
+    const int urow = threadIdx.x >> 2, uq = threadIdx.x & 3, usw = urow & 7;
+    // accumulation / epilogue role
+    const long row = m0 + (warp & 3) * 32 + lane;
+    const int col0 = (warp >> 2) * 4;                       // this thread's 4 lanes of the tile
+    const bool row_ok = row < p.n;
+    const long groups = p.k / 32;
+    const float *gscale = p.scales + (row_ok ? row : 0) * groups;
+    const uint32_t idesc = instr_desc_i8(TM, BN);
+    const uint32_t tbase = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)col0;
+    float accf[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    int pass = 0;
+    for (int p0 = 0; p0 < nchunks; p0 += I4_PASS_CHUNKS, ++pass) {
+        const int pend = min(nchunks, p0 + I4_PASS_CHUNKS);
+        for (int c = p0; c < pend; ++c) {
+            const int s = c % I4_STAGES;
+            if (wait(&full_bar[s], (unsigned)((c / I4_STAGES) & 1), 8)) {
+                // ---- unpack 16 packed bytes (32 elements) of row urow ----------------------
+                const int4 pk = *reinterpret_cast<const int4 *>(Pk + (size_t)s * P_BYTES + (size_t)urow * 64 + uq * 16);
+                unsigned char *dstrow = Ap + (size_t)(c - p0) * A_BYTES + (size_t)urow * 128;
+                const unsigned w[4] = {(unsigned)pk.x, (unsigned)pk.y, (unsigned)pk.z, (unsigned)pk.w};
+                unsigned o[8];
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    const unsigned lo = w[t] & 0x0f0f0f0fu, hi = (w[t] >> 4) & 0x0f0f0f0fu;
+                    o[2 * t] = __vsub4(__byte_perm(lo, hi, 0x5140), 0x08080808u);
+                    o[2 * t + 1] = __vsub4(__byte_perm(lo, hi, 0x7362), 0x08080808u);
+                }
+                *reinterpret_cast<int4 *>(dstrow + (((2 * uq) ^ usw) << 4)) = make_int4((int)o[0], (int)o[1], (int)o[2], (int)o[3]);
+                *reinterpret_cast<int4 *>(dstrow + (((2 * uq + 1) ^ usw) << 4)) = make_int4((int)o[4], (int)o[5], (int)o[6], (int)o[7]);
+            }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the MMAs read these bytes
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        if (threadIdx.x == 32) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (*reinterpret_cast<volatile unsigned *>(&s_fail) == 0u) {
+                for (int c = p0; c < pend; ++c) {
+                    const uint64_t da = smem_desc_sw128(saddr(Ap + (size_t)(c - p0) * A_BYTES));
+                    const uint64_t db = smem_desc_sw128(saddr(Bs + (size_t)(c % I4_STAGES) * B_BYTES));
+#pragma unroll
+                    for (int g = 0; g < KC / 32; ++g)
+                        mma_i8(tmem + (uint32_t)(((c - p0) * (KC / 32) + g) * BN), da + 2u * g, db + 2u * g, idesc, 0u);
+                }
+            }
+            mma_commit(&pass_bar);                           // arrives when every MMA so far has finished
+        }
+        const bool done = wait(&pass_bar, (unsigned)(pass & 1), 16);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (threadIdx.x == 0 && done) {
+            // the pass's stages are free: refill them for the pass after the next
+            for (int c = p0; c < pend; ++c) {
+                const int cn = c + I4_STAGES;
+                if (cn < nchunks) {
+                    const int s = c % I4_STAGES;
+                    bar_expect(&full_bar[s], stage_bytes);
+                    tma_load_2d(Pk + (size_t)s * P_BYTES, &map_w, cn * (KC / 2), (int)m0, &full_bar[s]);
+                    tma_load_2d(Bs + (size_t)s * B_BYTES, &map_x, cn * KC, b0, &full_bar[s]);
+                }
+            }
+        }
+        if (done) {
+            // all of the pass's accumulators for this thread's row and 4 lanes, then one wait;
+            // folded into the f32 sums in group order
+            const int ngroups = (pend - p0) * (KC / 32);
+            int v[I4_PASS_CHUNKS * (KC / 32)][4];
+#pragma unroll
+            for (int g = 0; g < I4_PASS_CHUNKS * (KC / 32); ++g)
+                if (g < ngroups) tmem_ld4_nowait(tbase + (uint32_t)(g * BN), v[g]);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (row_ok) {
+#pragma unroll
+                for (int g = 0; g < I4_PASS_CHUNKS * (KC / 32); ++g)
+                    if (g < ngroups) {
+                        const float gs = gscale[(long)p0 * (KC / 32) + g];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) accf[j] = __fadd_rn(accf[j], __fmul_rn((float)v[g][j], gs));
+                    }
+            }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();                                     // accumulators and the unpacked tiles are free
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    }
+    const bool good = *reinterpret_cast<volatile unsigned *>(&s_fail) == 0u;
+    if (!good) {
+        // a wait ran out: give copies still in flight one more bounded chance to land before
+        // this CTA's shared memory is released
+        if (threadIdx.x == 0)
+            for (int s = 0; s < I4_STAGES && s < nchunks; ++s) bar_wait(&full_bar[s], 0u, TC_SPIN >> 4);
+    } else if (row_ok) {
+        const float bias = p.bias != nullptr ? __ldg(p.bias + row) : 0.0f;
+        float prior[4], lane_scale[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int b = b0 + col0 + j;
+            lane_scale[j] = b < nb ? p.sx[b] : 0.0f;
+            prior[j] = (p.epilogue == MB_EPI_RESIDUAL && b < nb) ? p.out[(long)b * p.out_stride + row] : 0.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int b = b0 + col0 + j;
+            if (b < nb) {
+                float y = __fmul_rn(accf[j], lane_scale[j]);
+                if (p.bias != nullptr) y = __fadd_rn(y, bias);
+                float *dst = p.out + (long)b * p.out_stride + row;
+                if (p.epilogue == MB_EPI_RESIDUAL) *dst = __fadd_rn(prior[j], y);
+                else if (p.epilogue == MB_EPI_GELU)
+                    *dst = p.strict ? gelu_tanh<true>(y, p.tanh_tab) : gelu_tanh<false>(y, nullptr);
+                else *dst = y;
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(I4_COLS) : "memory");
+}
+
+constexpr size_t TC4_SMEM = (size_t)I4_PASS_CHUNKS * A_BYTES + (size_t)I4_STAGES * (B_BYTES + P_BYTES) + 1024;
+
 // [rows][k] bytes, row-major; box = 128 K-bytes x box_rows rows, 128-byte swizzle.
 bool make_map(CUtensorMap *map, const void *ptr, size_t rows, size_t k, unsigned box_rows) {
     return mb_make_map_2d(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, ptr, rows, k, k, (unsigned)KC, box_rows,
@@ -271,12 +488,17 @@ constexpr size_t TC_SMEM = (size_t)MAX_STAGES * (A_BYTES + B_BYTES) + 1024;
 }  // namespace
 
 extern "C" int mb_gemm_tc_init(void) {
-    return (int)cudaFuncSetAttribute(k_gemm_i8_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM);
+    int rc = (int)cudaFuncSetAttribute(k_gemm_i8_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM);
+    if (rc == 0) rc = (int)cudaFuncSetAttribute(k_gemm_i4_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC4_SMEM);
+    return rc;
 }
 
 // Shapes the tensor-core path takes: int8 weights, k a multiple of 16 (TMA row
 // stride), 16-byte aligned operands.
 extern "C" int mb_gemm_tc_supported(int qtype, size_t n, size_t k, size_t batch) {
+    // int4: whole 4-group stages; measured against the SIMT kernel the unpack-and-fold passes
+    // pay off from about 48 lanes (64 lanes: 1742 vs 1935 us per step; 32 lanes: 1624 vs 1488)
+    if (qtype == MB_INT4) return n > 0 && batch >= 48 && k >= 128 && (k % 128u) == 0;
     return qtype == MB_INT8 && n > 0 && batch >= 16 && k >= 16 && (k % 16u) == 0;
 }
 
@@ -288,8 +510,12 @@ extern "C" int mb_gemm_tc(const mb_gemv_args *a, size_t qx_rows_alloc, int *stat
         (((uintptr_t)a->w | (uintptr_t)a->qx) & 15u) != 0)
         return (int)cudaErrorInvalidValue;
     CUtensorMap map_w, map_x;
-    if (!make_map(&map_w, a->w, a->n, a->k, TM) ||
-        !make_map(&map_x, a->qx, qx_rows_alloc > a->batch ? qx_rows_alloc : a->batch, a->k, BN))
+    const bool int4 = a->qtype == MB_INT4;
+    // int4: [n][k/2] packed bytes, box = 64 bytes x 128 rows, unswizzled (the threads unpack it)
+    const bool w_ok = int4 ? mb_make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->w, a->n, a->k / 2u, a->k / 2u,
+                                            (unsigned)(KC / 2), TM, CU_TENSOR_MAP_SWIZZLE_NONE)
+                           : make_map(&map_w, a->w, a->n, a->k, TM);
+    if (!w_ok || !make_map(&map_x, a->qx, qx_rows_alloc > a->batch ? qx_rows_alloc : a->batch, a->k, BN))
         return (int)cudaErrorInvalidValue;
     TcP p;
     p.scales = a->scales; p.bias = a->bias; p.sx = a->sx; p.out = a->out;
@@ -299,6 +525,9 @@ extern "C" int mb_gemm_tc(const mb_gemv_args *a, size_t qx_rows_alloc, int *stat
     p.batch = (int)a->batch; p.epilogue = a->epilogue; p.strict = a->strict;
     const unsigned m_tiles = (unsigned)((a->n + TM - 1) / TM);
     const unsigned b_tiles = (unsigned)((a->batch + BN - 1) / BN);
-    mb_launch(k_gemm_i8_tc, dim3(dim3(m_tiles, b_tiles)), dim3(TC_THREADS), TC_SMEM, (cudaStream_t)stream, map_w, map_x, p);
+    if (int4)
+        mb_launch(k_gemm_i4_tc, dim3(dim3(m_tiles, b_tiles)), dim3(I4_THREADS), TC4_SMEM, (cudaStream_t)stream, map_w, map_x, p);
+    else
+        mb_launch(k_gemm_i8_tc, dim3(dim3(m_tiles, b_tiles)), dim3(TC_THREADS), TC_SMEM, (cudaStream_t)stream, map_w, map_x, p);
     return mb_check_launch();
 }

@@ -139,8 +139,9 @@ typedef struct {
 } mb_gemv_args;
 int mb_gemv(const mb_gemv_args *args, mb_stream stream);
 
-/* Tensor-core (tcgen05) form of the int8 product for 16+ lanes; same arguments
- * and same bits as mb_gemv.  qx_rows_alloc: rows the activation buffer holds. */
+/* Tensor-core (tcgen05) form of the product: int8 weights from 16 lanes, int4 (group 32)
+ * weights from 48 lanes; same arguments and same bits as mb_gemv.  qx_rows_alloc: rows
+ * the activation buffer holds. */
 int mb_gemm_tc_init(void);
 int mb_gemm_tc_supported(int qtype, size_t n, size_t k, size_t batch);
 int mb_gemm_tc(const mb_gemv_args *args, size_t qx_rows_alloc, int *status, mb_stream stream);

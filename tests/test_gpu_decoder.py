@@ -303,12 +303,14 @@ def golden_cross(sdec, be, model, seed):
     return _cross_cache[seed]
 
 
-def test_full_size_properties_64_streams(golden):
-    """At the benchmark's size (64 streams): every lane that starts from the same
-    codes and memory yields the same tokens as lane 0 and as the single-stream
-    run, and a lane's tokens do not change when the others stop early."""
+@pytest.mark.parametrize("name", ["int8", "int4"])
+def test_full_size_properties_64_streams(name, golden):
+    """At the benchmark's size (64 streams, products on the tensor cores): every lane
+    that starts from the same codes and memory yields the same tokens as lane 0 and as
+    the single-stream run (SIMT products), and a lane's tokens do not change when the
+    others stop early."""
     seed = 21
-    shape, model, start, be, dec = _full_setup(seed, "int8", False, 140, slots=64)
+    shape, model, start, be, dec = _full_setup(seed, name, False, 140, slots=64)
     slots = list(range(64))
     codes = np.repeat(start, 64, axis=0)
     tokens, eos, ms, _ = dec.greedy(slots, codes, 128, min_frames=10 ** 6)
@@ -316,6 +318,9 @@ def test_full_size_properties_64_streams(golden):
         assert np.array_equal(tokens[:, b], tokens[:, 0])
     for s in slots:
         dec.slot_set_length(s, 0)
+    solo, _, _, _ = dec.greedy([0], start, 128, min_frames=10 ** 6)     # one lane: the SIMT kernel
+    assert np.array_equal(solo[:, 0], tokens[:, 0])
+    dec.slot_set_length(0, 0)
     frames = [128 if b % 3 == 0 else 16 + b for b in range(64)]
     tokens2, _, _, _ = dec.greedy(slots, codes, frames, min_frames=10 ** 6)
     for b in range(64):
