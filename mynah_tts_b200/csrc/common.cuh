@@ -68,6 +68,85 @@ __device__ __forceinline__ int round_half_away(float v) {
     return __float2int_rz(v >= 0.0f ? __fadd_rn(v, 0.5f) : __fsub_rn(v, 0.5f));
 }
 
+// block_sum for a CTA that plays VT times its own size: thread t holds the partial sums of
+// virtual threads t, t + blockDim.x, ...; the result has the bits block_sum gives a CTA of
+// VT * blockDim.x threads (same butterflies, same order of the per-warp values).
+template <int VT>
+__device__ __forceinline__ float block_sum_vt(const float (&v)[VT], float *red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nrw = (blockDim.x + 31) >> 5;
+    float t[VT];
+#pragma unroll
+    for (int r = 0; r < VT; ++r) t[r] = warp_sum(v[r]);
+    __syncthreads();
+    if (lane == 0)
+#pragma unroll
+        for (int r = 0; r < VT; ++r) red[warp + r * nrw] = t[r];
+    __syncthreads();
+    if (warp == 0) {
+        float u = lane < VT * nrw ? red[lane] : 0.0f;
+        u = warp_sum(u);
+        if (lane == 0) red[32] = u;
+    }
+    __syncthreads();
+    return red[32];
+}
+
+// Non-strict layer norm of one row by one CTA, with optional int8 quantization of the
+// result (src/qmat.c:93-113): `row` holds the input in shared memory and receives y.  The
+// stand-alone kernel calls it with 256 threads and VT = 1, the products' fused prologue
+// with 128 threads and VT = 2 (each thread plays two): a row gets the same bits from
+// either.  Returns the quantization scale (0 when !quant) to every thread; q may be shared
+// or global memory.
+template <int VT>
+__device__ __forceinline__ float mb_ln_block(float *row, int width, const float *__restrict__ gain,
+                                             const float *__restrict__ bias, float eps, float *red,
+                                             float *y_out, bool quant, int8_t *q) {
+    const int stride = VT * blockDim.x;
+    float s[VT];
+#pragma unroll
+    for (int r = 0; r < VT; ++r) {
+        s[r] = 0.0f;
+        for (int i = threadIdx.x + r * blockDim.x; i < width; i += stride) s[r] += row[i];
+    }
+    const float mean = __fdiv_rn(block_sum_vt<VT>(s, red), (float)width);
+    float v[VT];
+#pragma unroll
+    for (int r = 0; r < VT; ++r) {
+        v[r] = 0.0f;
+        for (int i = threadIdx.x + r * blockDim.x; i < width; i += stride) {
+            const float d = row[i] - mean;
+            v[r] = fmaf(d, d, v[r]);
+        }
+    }
+    const float variance = block_sum_vt<VT>(v, red);
+    const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(variance, (float)width), eps)));
+    float amax = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float y = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(row[i], mean), scale), gain[i]),
+                                  bias == nullptr ? 0.0f : bias[i]);
+        if (y_out != nullptr) y_out[i] = y;
+        row[i] = y;                  // each thread rereads only its own elements below
+        amax = fmaxf(amax, fabsf(y));
+    }
+    if (!quant) return 0.0f;
+    amax = block_max(amax, red);
+    const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x)
+        q[i] = (int8_t)min(127, max(-127, round_half_away(__fmul_rn(row[i], inv))));
+    return amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 0.0f;
+}
+
+// int8 quantization of one f32 row held in shared memory by one CTA; returns the scale.
+__device__ __forceinline__ float mb_quant_block(const float *row, int width, float *red, int8_t *q) {
+    float amax = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) amax = fmaxf(amax, fabsf(row[i]));
+    amax = block_max(amax, red);
+    const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x)
+        q[i] = (int8_t)min(127, max(-127, round_half_away(__fmul_rn(row[i], inv))));
+    return amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 0.0f;
+}
+
 // tanh-form GELU of the reference's decode step (src/kernels.c:382-389):
 // 0.5*x*(1+tanhf(0.7978845608*(x+0.044715*x^3))), every operation rounded to
 // f32 in source order.  STRICT returns the host libm's tanhf bit for bit when

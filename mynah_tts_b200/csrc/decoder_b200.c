@@ -67,7 +67,7 @@ typedef struct mb_decoder {
     float *sx;
     float *partials;
     unsigned *counters;
-    int use_tc;
+    int use_tc, use_fuse1;
     /* lane state */
     int *d_lens, *d_slots, *d_n_active, *d_allow_eos, *d_eos_flag, *d_eos_frame, *d_frame_idx, *d_status;
     int *d_min_frames;
@@ -349,6 +349,8 @@ int mynah_b200_decoder_create(void *state, const mynah_b200_decoder_desc *desc, 
     {
         const char *no_tc = getenv("MYNAH_B200_NO_TC");
         d->use_tc = !(no_tc != NULL && strcmp(no_tc, "0") != 0);
+        const char *no_fuse = getenv("MYNAH_B200_NO_FUSE");
+        d->use_fuse1 = !(no_fuse != NULL && strcmp(no_fuse, "0") != 0);
     }
     D_TRY(dmalloc((void **)&d->partials, partial_floats * sizeof(float), error, cap));
     D_TRY(dmalloc((void **)&d->counters, n_counters * sizeof(unsigned), error, cap));
@@ -405,10 +407,17 @@ size_t mynah_b200_decoder_kv_bytes(const void *decoder, size_t length) {
 }
 
 /* ------------------------------------------------------------ the sequence */
-static int product(mb_decoder *d, const mb_dev_weight *w, const float *bias, const float *act_f32,
-                   float *out, size_t out_stride, size_t nb, int epilogue, unsigned *count) {
+/* fuse != MB_FUSE_NONE (one lane, int8, non-strict): the product makes its own quantized
+ * activations from the f32 row act_f32 (layer norm with `gain`, or plain quantization). */
+static int product_fused(mb_decoder *d, const mb_dev_weight *w, const float *bias, const float *act_f32,
+                         float *out, size_t out_stride, size_t nb, int epilogue, int fuse,
+                         const float *gain, unsigned *count) {
     mb_gemv_args g;
     memset(&g, 0, sizeof(g));
+    g.fuse = fuse;
+    g.fx = fuse != MB_FUSE_NONE ? act_f32 : NULL;
+    g.fuse_gain = gain;
+    g.fuse_eps = 1.0e-5f;
     mb_gemv_bind_weight(&g, w, bias);
     g.out = out;
     g.out_stride = out_stride;
@@ -427,6 +436,17 @@ static int product(mb_decoder *d, const mb_dev_weight *w, const float *bias, con
     if (d->use_tc && mb_gemm_tc_supported(w->qtype, w->n, w->k, nb))
         return mb_gemm_tc(&g, d->max_batch, d->d_status, d->st->stream);
     return mb_gemv(&g, d->st->stream);
+}
+
+static int product(mb_decoder *d, const mb_dev_weight *w, const float *bias, const float *act_f32,
+                   float *out, size_t out_stride, size_t nb, int epilogue, unsigned *count) {
+    return product_fused(d, w, bias, act_f32, out, out_stride, nb, epilogue, MB_FUSE_NONE, NULL, count);
+}
+
+/* One lane, int8 weights, non-strict: norms and the hidden-row quantization ride in the
+ * products that consume them (every launch saved is ~5 us of a ~790 us step). */
+static int fuse_one_lane(const mb_decoder *d, size_t nb) {
+    return nb == 1 && d->use_fuse1 && d->st->quant == MB_INT8 && !d->st->strict;
 }
 
 static int norm(mb_decoder *d, const float *in, float *out, const float *gain, size_t nb,
@@ -469,8 +489,15 @@ static int enqueue_local(mb_decoder *d, const float *first_rows, size_t nb, unsi
         *count += 1u;
         for (size_t l = 0; l < lt->layers && rc == 0; ++l) {
             const local_layer *L = &lt->L[l];
-            L_TRY(norm(d, d->x, d->nrm, L->norm_self, nb, count));
-            L_TRY(product(d, &L->qkv, NULL, d->nrm, d->qkv, 3u * W, nb, MB_EPI_STORE, count));
+            const int f1 = fuse_one_lane(d, nb) && L->qkv.qtype == MB_INT8 && L->ffn_up.qtype == MB_INT8 &&
+                           L->ffn_down.qtype == MB_INT8;
+            if (f1) {
+                L_TRY(product_fused(d, &L->qkv, NULL, d->x, d->qkv, 3u * W, nb, MB_EPI_STORE, MB_FUSE_LN,
+                                    L->norm_self, count));
+            } else {
+                L_TRY(norm(d, d->x, d->nrm, L->norm_self, nb, count));
+                L_TRY(product(d, &L->qkv, NULL, d->nrm, d->qkv, 3u * W, nb, MB_EPI_STORE, count));
+            }
             mb_attn_args a;
             memset(&a, 0, sizeof(a));
             a.q = d->qkv;
@@ -503,21 +530,33 @@ static int enqueue_local(mb_decoder *d, const float *first_rows, size_t nb, unsi
             L_TRY(mb_attention(&a, s));
             *count += (st->strict && q) ? 2u : 1u;
             L_TRY(product(d, &L->o, NULL, d->attn, d->x, W, nb, MB_EPI_RESIDUAL, count));
-            L_TRY(norm(d, d->x, d->nrm, L->norm_ff, nb, count));
-            L_TRY(product(d, &L->ffn_up, NULL, d->nrm, d->hidden, F, nb, MB_EPI_GELU, count));
-            if (q) {
-                L_TRY(mb_quant_rows(d->hidden, nb, F, d->qx, d->sx, d->d_n_active, s));
-                *count += 1u;
+            if (f1) {
+                L_TRY(product_fused(d, &L->ffn_up, NULL, d->x, d->hidden, F, nb, MB_EPI_GELU, MB_FUSE_LN,
+                                    L->norm_ff, count));
+                L_TRY(product_fused(d, &L->ffn_down, NULL, d->hidden, d->x, W, nb, MB_EPI_RESIDUAL,
+                                    MB_FUSE_QUANT, NULL, count));
+            } else {
+                L_TRY(norm(d, d->x, d->nrm, L->norm_ff, nb, count));
+                L_TRY(product(d, &L->ffn_up, NULL, d->nrm, d->hidden, F, nb, MB_EPI_GELU, count));
+                if (q) {
+                    L_TRY(mb_quant_rows(d->hidden, nb, F, d->qx, d->sx, d->d_n_active, s));
+                    *count += 1u;
+                }
+                L_TRY(product(d, &L->ffn_down, NULL, d->hidden, d->x, W, nb, MB_EPI_RESIDUAL, count));
             }
-            L_TRY(product(d, &L->ffn_down, NULL, d->hidden, d->x, W, nb, MB_EPI_RESIDUAL, count));
         }
         /* this table's projection (no norm in between: src/graph.c:1339-1341, 1538-1549) */
-        if (q) {
-            L_TRY(mb_quant_rows(d->x, nb, W, d->qx, d->sx, d->d_n_active, s));
-            *count += 1u;
-        }
         const mb_dev_weight head = weight_rows(&d->heads_w, t * d->vocab, d->vocab);
-        L_TRY(product(d, &head, d->heads_b + t * d->vocab, d->x, d->logits, d->vocab, nb, MB_EPI_STORE, count));
+        if (fuse_one_lane(d, nb) && head.qtype == MB_INT8) {
+            L_TRY(product_fused(d, &head, d->heads_b + t * d->vocab, d->x, d->logits, d->vocab, nb, MB_EPI_STORE,
+                                MB_FUSE_QUANT, NULL, count));
+        } else {
+            if (q) {
+                L_TRY(mb_quant_rows(d->x, nb, W, d->qx, d->sx, d->d_n_active, s));
+                *count += 1u;
+            }
+            L_TRY(product(d, &head, d->heads_b + t * d->vocab, d->x, d->logits, d->vocab, nb, MB_EPI_STORE, count));
+        }
         mb_sample_args sa;
         memset(&sa, 0, sizeof(sa));
         sa.logits = d->logits;
@@ -578,8 +617,15 @@ static int enqueue(mb_decoder *d, size_t bucket, int mode, unsigned *count) {
     *count += 1u;
     for (size_t l = 0; l < d->layers_run && rc == 0; ++l) {
         const dec_layer *L = &d->L[l];
-        P(PC_NORM, norm(d, d->x, d->nrm, L->norm_self, nb, count));
-        P(PC_QKV, product(d, &L->qkv, NULL, d->nrm, d->qkv, 3u * W, nb, MB_EPI_STORE, count));
+        const int f1 = fuse_one_lane(d, nb) && L->qkv.qtype == MB_INT8 && L->q_cross.qtype == MB_INT8 &&
+                       L->ffn_up.qtype == MB_INT8 && L->ffn_down.qtype == MB_INT8;
+        if (f1) {
+            P(PC_QKV, product_fused(d, &L->qkv, NULL, d->x, d->qkv, 3u * W, nb, MB_EPI_STORE, MB_FUSE_LN,
+                                    L->norm_self, count));
+        } else {
+            P(PC_NORM, norm(d, d->x, d->nrm, L->norm_self, nb, count));
+            P(PC_QKV, product(d, &L->qkv, NULL, d->nrm, d->qkv, 3u * W, nb, MB_EPI_STORE, count));
+        }
         mb_attn_args a;
         memset(&a, 0, sizeof(a));
         a.q = d->qkv;
@@ -613,8 +659,13 @@ static int enqueue(mb_decoder *d, size_t bucket, int mode, unsigned *count) {
         P(PC_ATTN_SELF, mb_attention(&a, s));
         *count += (st->strict && q) ? 2u : 1u;
         P(PC_O_SELF, product(d, &L->o_self, NULL, d->attn, d->x, W, nb, MB_EPI_RESIDUAL, count));
-        P(PC_NORM, norm(d, d->x, d->nrm, L->norm_xattn_query, nb, count));
-        P(PC_Q_CROSS, product(d, &L->q_cross, NULL, d->nrm, d->q_x, XW, nb, MB_EPI_STORE, count));
+        if (f1) {
+            P(PC_Q_CROSS, product_fused(d, &L->q_cross, NULL, d->x, d->q_x, XW, nb, MB_EPI_STORE, MB_FUSE_LN,
+                                        L->norm_xattn_query, count));
+        } else {
+            P(PC_NORM, norm(d, d->x, d->nrm, L->norm_xattn_query, nb, count));
+            P(PC_Q_CROSS, product(d, &L->q_cross, NULL, d->nrm, d->q_x, XW, nb, MB_EPI_STORE, count));
+        }
         memset(&a, 0, sizeof(a));
         a.q = d->q_x;
         a.q_stride = XW;
@@ -645,13 +696,20 @@ static int enqueue(mb_decoder *d, size_t bucket, int mode, unsigned *count) {
         P(PC_ATTN_CROSS, mb_attention(&a, s));
         *count += (st->strict && q) ? 2u : 1u;
         P(PC_O_CROSS, product(d, &L->o_cross, NULL, d->xctx, d->x, W, nb, MB_EPI_RESIDUAL, count));
-        P(PC_NORM, norm(d, d->x, d->nrm, L->norm_pos_ff, nb, count));
-        P(PC_FFN_UP, product(d, &L->ffn_up, NULL, d->nrm, d->hidden, F, nb, MB_EPI_GELU, count));
-        if (q) {
-            P(PC_QUANT, mb_quant_rows(d->hidden, nb, F, d->qx, d->sx, d->d_n_active, s));
-            *count += 1u;
+        if (f1) {
+            P(PC_FFN_UP, product_fused(d, &L->ffn_up, NULL, d->x, d->hidden, F, nb, MB_EPI_GELU, MB_FUSE_LN,
+                                       L->norm_pos_ff, count));
+            P(PC_FFN_DOWN, product_fused(d, &L->ffn_down, NULL, d->hidden, d->x, W, nb, MB_EPI_RESIDUAL,
+                                         MB_FUSE_QUANT, NULL, count));
+        } else {
+            P(PC_NORM, norm(d, d->x, d->nrm, L->norm_pos_ff, nb, count));
+            P(PC_FFN_UP, product(d, &L->ffn_up, NULL, d->nrm, d->hidden, F, nb, MB_EPI_GELU, count));
+            if (q) {
+                P(PC_QUANT, mb_quant_rows(d->hidden, nb, F, d->qx, d->sx, d->d_n_active, s));
+                *count += 1u;
+            }
+            P(PC_FFN_DOWN, product(d, &L->ffn_down, NULL, d->hidden, d->x, W, nb, MB_EPI_RESIDUAL, count));
         }
-        P(PC_FFN_DOWN, product(d, &L->ffn_down, NULL, d->hidden, d->x, W, nb, MB_EPI_RESIDUAL, count));
     }
     P(PC_NORM, norm(d, d->x, d->out, d->norm_out, nb, count));
     if (mode == MODE_FRAME) {

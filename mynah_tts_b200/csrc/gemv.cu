@@ -46,6 +46,9 @@ struct GemvP {
     int iters;          // consecutive row groups one warp walks
     long row_bytes;
     long w_gs, scale_gs, act_gs, out_gs;  // group strides (elements of the respective arrays)
+    int fuse;                             // MB_FUSE_*: make the activations from the f32 row fx
+    const float *fx, *fuse_gain;
+    float fuse_eps;
 };
 
 template <bool STRICT>
@@ -79,10 +82,35 @@ __global__ void __launch_bounds__(WARPS * 32) k_gemv(GemvP p) {
     unsigned char *act = smem;                         // [BT][act_bytes]
     float *pbuf = reinterpret_cast<float *>(smem + (size_t)BT * act_bytes);  // int4 only
 
+    __shared__ float fuse_red[33];
+    __shared__ float fuse_sx;
     // one batch tile per CTA (grid.z): tiles past the live lanes leave at once
     for (int b0 = blockIdx.z * BT; b0 < nb; b0 = nb) {
         // ---- stage the activation tile ------------------------------------
-        if (QUANT) {
+        if (QT == MB_INT8 && BT == 1 && p.fuse != MB_FUSE_NONE) {
+            // one lane: this CTA makes the quantized row itself from the f32 row (loads of a
+            // batch before its stores), with the routines the stand-alone kernels use
+            float *rowf = reinterpret_cast<float *>(smem + ((act_bytes + 15) & ~(long)15));
+            for (int base = threadIdx.x; base < k; base += blockDim.x * 8) {
+                float v[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int i = base + u * blockDim.x;
+                    if (i < k) v[u] = p.fx[i];
+                }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int i = base + u * blockDim.x;
+                    if (i < k) rowf[i] = v[u];
+                }
+            }
+            __syncthreads();
+            const float sxv = p.fuse == MB_FUSE_LN
+                                  ? mb_ln_block<2>(rowf, (int)k, p.fuse_gain, nullptr, p.fuse_eps, fuse_red, nullptr, true,
+                                                reinterpret_cast<int8_t *>(act))
+                                  : mb_quant_block(rowf, (int)k, fuse_red, reinterpret_cast<int8_t *>(act));
+            if (threadIdx.x == 0) fuse_sx = sxv;
+        } else if (QUANT) {
             const int8_t *src = p.qx + grp * p.act_gs;
             if (QT == MB_INT8) {
                 const int per = (int)(k / 16);
@@ -165,7 +193,8 @@ __global__ void __launch_bounds__(WARPS * 32) k_gemv(GemvP p) {
 #pragma unroll
                 for (int b = 0; b < BT; ++b) {
                     if (b0 + b < nb) {
-                        float v = __fmul_rn(__fmul_rn((float)acc[b], ws), p.sx[grp * p.batch + b0 + b]);
+                        const float lane_sx = (BT == 1 && p.fuse != MB_FUSE_NONE) ? fuse_sx : p.sx[grp * p.batch + b0 + b];
+                        float v = __fmul_rn(__fmul_rn((float)acc[b], ws), lane_sx);
                         if (p.bias != nullptr) v = __fadd_rn(v, bias);
                         store_out<STRICT>(p, out, row, b0 + b, v);
                     }
@@ -353,6 +382,7 @@ int launch_tiled(const GemvP &p, size_t groups, cudaStream_t s) {
     const bool quant = (QT == MB_INT8 || QT == MB_INT4);
     size_t smem = (size_t)BT * (quant ? p.k : p.k * 4);
     if (QT == MB_INT4) smem += (size_t)WARPS * 32 * p.cpl * BT * sizeof(float);
+    if (p.fuse != MB_FUSE_NONE) smem += 16u + (size_t)p.k * sizeof(float);
     if (smem > 160u * 1024u) return (int)cudaErrorInvalidValue;
     mb_launch(k_gemv<QT, BT, STRICT>, dim3(blocks, (unsigned)groups, (unsigned)btiles), dim3(WARPS * 32), smem, s, q);
     return mb_check_launch();
@@ -407,7 +437,11 @@ extern "C" int mb_gemv(const mb_gemv_args *a, mb_stream stream) {
         a->out == nullptr)
         return (int)cudaErrorInvalidValue;
     const bool quant = a->qtype == MB_INT8 || a->qtype == MB_INT4;
-    if (quant && (a->qx == nullptr || a->sx == nullptr || a->scales == nullptr))
+    const bool fused = a->fuse != MB_FUSE_NONE;
+    if (fused && (a->qtype != MB_INT8 || a->batch != 1 || a->strict || a->fx == nullptr || a->groups > 1 ||
+                  (a->fuse == MB_FUSE_LN && a->fuse_gain == nullptr)))
+        return (int)cudaErrorInvalidValue;
+    if (quant && ((!fused && (a->qx == nullptr || a->sx == nullptr)) || a->scales == nullptr))
         return (int)cudaErrorInvalidValue;
     if (!quant && a->x == nullptr) return (int)cudaErrorInvalidValue;
     if (a->qtype == MB_INT4 && (a->k % 32u) != 0) return (int)cudaErrorInvalidValue;
@@ -425,6 +459,7 @@ extern "C" int mb_gemv(const mb_gemv_args *a, mb_stream stream) {
     p.k = (long)a->k;
     p.out_stride = (long)a->out_stride;
     p.batch = (int)a->batch;
+    p.fuse = a->fuse; p.fx = a->fx; p.fuse_gain = a->fuse_gain; p.fuse_eps = a->fuse_eps;
     p.epilogue = a->epilogue;
     switch (a->qtype) {
         case MB_INT8: p.row_bytes = (long)a->k; break;
@@ -441,6 +476,7 @@ extern "C" int mb_gemv(const mb_gemv_args *a, mb_stream stream) {
     // row must be whole 16-byte chunks, else the scalar kernel takes the shape.
     const bool act_ok = quant ? (a->k % 16u) == 0 : (a->k % 4u) == 0;
     const bool tiled = act_ok && (p.row_bytes % 16) == 0;
+    if (fused && !tiled) return (int)cudaErrorInvalidValue;
     if (tiled) {
         const long cpr = p.row_bytes / 16;
         int lpr = 32;

@@ -57,15 +57,11 @@ k_layernorm(const float *__restrict__ in, float *__restrict__ out, const float *
         __syncthreads();
         variance = stat[1];
     } else {
-        float s = 0.0f;
-        for (int i = threadIdx.x; i < width; i += blockDim.x) s += row[i];
-        mean = __fdiv_rn(block_sum(s, red), (float)width);
-        float v = 0.0f;
-        for (int i = threadIdx.x; i < width; i += blockDim.x) {
-            const float d = row[i] - mean;
-            v = fmaf(d, d, v);
-        }
-        variance = block_sum(v, red);
+        // the routine shared with the products' fused prologue
+        const float sxv = mb_ln_block<1>(row, width, gain, bias, eps, red, out == nullptr ? nullptr : out + (size_t)r * width,
+                                      qx != nullptr, qx == nullptr ? nullptr : qx + (size_t)r * width);
+        if (qx != nullptr && threadIdx.x == 0) sx[r] = sxv;
+        return;
     }
     const float scale =
         __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(variance, (float)width), eps)));

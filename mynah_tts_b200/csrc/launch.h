@@ -20,6 +20,7 @@ enum { MB_F32 = 0, MB_INT8 = 1, MB_INT4 = 2, MB_F16 = 3 };
 
 /* GEMV epilogues. */
 enum { MB_EPI_STORE = 0, MB_EPI_RESIDUAL = 1, MB_EPI_GELU = 2 };
+enum { MB_FUSE_NONE = 0, MB_FUSE_LN = 1, MB_FUSE_QUANT = 2 };
 
 /* Device tables that make strict-mode expf/tanhf return the host libm's bits
  * (libm_parity.cuh); either pointer may be NULL (then: correctly rounded). */
@@ -134,6 +135,14 @@ typedef struct {
     int epilogue;         /* MB_EPI_* */
     int strict;           /* GELU epilogue: reference-order transcendental */
     const uint32_t *tanh_tab; /* strict GELU: host-libm correction table or NULL */
+    /* Fused prologue (int8 weights, batch == 1, non-strict): instead of reading qx/sx the
+     * kernel makes them from the f32 row fx: MB_FUSE_LN layer-normalizes (gain, eps) and
+     * quantizes it exactly as mb_layernorm with qx does, MB_FUSE_QUANT quantizes it as
+     * mb_quant_rows does.  Every CTA repeats the row work; the step loses a launch. */
+    int fuse;
+    const float *fx;
+    const float *fuse_gain;
+    float fuse_eps;
     size_t groups;        /* >1: independent problems; pointers advance by the strides below */
     size_t w_group_stride, scale_group_stride, act_group_stride, out_group_stride;
 } mb_gemv_args;
