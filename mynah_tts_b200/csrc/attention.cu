@@ -530,6 +530,134 @@ k_attn_rows(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CU
     quantize_shared_row(vals, width, p.qx + (long)b * width, p.sx + b, red);
 }
 
+// ------------------------------------------------------------- short caches
+// A cache short enough that every (head, chunk) pair gets its own warp of one CTA (cross
+// attention over the text memory: 1 head x 4 chunks): all K and V tiles are requested at
+// once, each warp makes its chunk's partial, and the partials meet in shared memory -- no
+// scratch in global memory, no arrival counter, no fence.  No row is appended (k_new is
+// null).  Per (head, chunk) and in the merge the operations and their order are those of
+// k_attn_rows: results are bit-identical.
+constexpr int SHORT_MAX_CHUNKS = 8;
+__global__ void __launch_bounds__(1024, 1)
+k_attn_short(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, AttnP p) {
+    extern __shared__ __align__(128) float sm[];
+    __shared__ float red[33];
+    __shared__ __align__(8) unsigned long long mbar[2 * SHORT_MAX_CHUNKS];   // K chunks, then V chunks
+    __shared__ unsigned s_bad;
+    if (!p.early) {
+        mb_pdl_wait();
+        mb_pdl_trigger();
+    }
+    const int b = blockIdx.x;
+    long pos, valid, slot;
+    float *kc, *vc;
+    if (!lane_setup(p, b, pos, valid, kc, vc, &slot)) return;
+    const int hw = p.hw, heads = p.heads, width = heads * hw;
+    const int cmax = p.max_chunks;
+    const int ns = (int)((valid + CHUNK - 1) / CHUNK);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int h = warp % heads, c = warp / heads;             // this warp's head and chunk
+    const int tpp = hw / 4, rps = 32 / tpp, sub = lane / tpp, li = lane % tpp;
+    const int tile_floats = CHUNK * width;
+    float *Kt = sm;                                           // [cmax] tiles
+    float *Vt = Kt + (long)cmax * tile_floats;
+    float *qs = Vt + (long)cmax * tile_floats;                // [width]
+    float *P = qs + width;                                    // [heads][cmax][hw + 2]
+    float *wts = P + (long)heads * cmax * (hw + 2) + (long)h * 2 * cmax;   // merge scratch of head h
+    float *vals = P + (long)heads * cmax * (hw + 2) + (long)heads * 2 * cmax;   // [width]
+    const unsigned tile_bytes = (unsigned)tile_floats * 4u;
+    if (threadIdx.x == 0) {
+        s_bad = 0u;
+        const unsigned long long stream_policy = mb_l2_evict_first();
+        for (int i = 0; i < 2 * cmax; ++i) mbar_init(&mbar[i], 1u);
+        for (int cc = 0; cc < ns; ++cc) {
+            const int y = (int)(slot * p.slot_rows + (long)cc * CHUNK);
+            mbar_expect_tx(&mbar[cc], tile_bytes);
+            mbar_expect_tx(&mbar[cmax + cc], tile_bytes);
+            for (int bx = 0; bx < p.nbox; ++bx) {
+                mb_tma_load_2d_hint(Kt + (long)cc * tile_floats + (long)bx * CHUNK * p.box_cols, &kmap, bx * p.box_cols, y,
+                                    &mbar[cc], stream_policy);
+                mb_tma_load_2d_hint(Vt + (long)cc * tile_floats + (long)bx * CHUNK * p.box_cols, &vmap, bx * p.box_cols, y,
+                                    &mbar[cmax + cc], stream_policy);
+            }
+        }
+    }
+    if (p.early) {
+        mb_pdl_wait();
+        mb_pdl_trigger();
+    }
+    for (int d = threadIdx.x; d < width; d += blockDim.x) qs[d] = p.q[(long)b * p.q_stride + d];
+    __syncthreads();
+    if (c < ns) {
+        const long slice = (long)((h * hw) / p.box_cols) * CHUNK * p.box_cols + (h * hw) % p.box_cols;
+        const int pitch = p.box_cols;
+        const float4 qv = reinterpret_cast<const float4 *>(qs + h * hw)[li];
+        const long s0 = (long)c * CHUNK;
+        const int cnt = (int)min((long)CHUNK, valid - s0);
+        const bool k_ok = mbar_wait(&mbar[c], 0u, SPIN_LIMIT);
+        const bool v_ok = k_ok && mbar_wait(&mbar[cmax + c], 0u, SPIN_LIMIT);
+        if (k_ok && v_ok) {
+            const float *Ks = Kt + (long)c * tile_floats + slice;
+            float dot;
+            switch (tpp) {
+            case 32: dot = chunk_scores<32>(Ks, pitch, qv, sub, li); break;
+            case 16: dot = chunk_scores<16>(Ks, pitch, qv, sub, li); break;
+            case 8: dot = chunk_scores<8>(Ks, pitch, qv, sub, li); break;
+            case 4: dot = chunk_scores<4>(Ks, pitch, qv, sub, li); break;
+            case 2: dot = chunk_scores<2>(Ks, pitch, qv, sub, li); break;
+            default: dot = chunk_scores<1>(Ks, pitch, qv, sub, li); break;
+            }
+            const int my_row = li * rps + sub;
+            const float mine = my_row < cnt ? dot * p.scale : -FLT_MAX;
+            const float m = warp_max(mine);
+            const float e = my_row < cnt ? exp_ref<false>(mine - m) : 0.0f;
+            const float l = warp_sum(e);
+            const float *Vs = Vt + (long)c * tile_floats + slice;
+            float4 acc;
+            switch (tpp) {
+            case 32: acc = chunk_values<32>(Vs, pitch, e, sub, li); break;
+            case 16: acc = chunk_values<16>(Vs, pitch, e, sub, li); break;
+            case 8: acc = chunk_values<8>(Vs, pitch, e, sub, li); break;
+            case 4: acc = chunk_values<4>(Vs, pitch, e, sub, li); break;
+            case 2: acc = chunk_values<2>(Vs, pitch, e, sub, li); break;
+            default: acc = chunk_values<1>(Vs, pitch, e, sub, li); break;
+            }
+            float *part = P + ((long)h * cmax + c) * (hw + 2);
+            if (sub == 0) {
+                part[2 + 4 * li] = acc.x; part[3 + 4 * li] = acc.y;
+                part[4 + 4 * li] = acc.z; part[5 + 4 * li] = acc.w;
+            }
+            if (lane == 0) { part[0] = m; part[1] = l; }
+        } else if (lane == 0) {
+            s_bad = 1u;
+            if (p.status != nullptr) atomicOr(p.status, 2);
+        }
+    }
+    __syncthreads();
+    if (s_bad != 0u) {
+        // a tile never landed: one more bounded wait per tile so that none is in flight when
+        // this CTA's shared memory is released
+        if (threadIdx.x == 0)
+            for (int cc = 0; cc < ns; ++cc) {
+                mbar_wait(&mbar[cc], 0u, SPIN_LIMIT);
+                mbar_wait(&mbar[cmax + cc], 0u, SPIN_LIMIT);
+            }
+        return;
+    }
+    const bool quant = p.qx != nullptr;
+    float *outrow = p.out == nullptr ? nullptr : p.out + (long)b * p.out_stride;
+    if (warp < heads) {
+        const long hoff = (long)h * hw;
+        merge_chunks<false>(P + (long)h * cmax * (hw + 2), ns, hw, lane, wts, [&](int d, float o) {
+            if (outrow != nullptr) outrow[hoff + d] = o;
+            if (quant) vals[hoff + d] = o;
+        });
+    }
+    if (!quant) return;
+    __syncthreads();
+    quantize_shared_row(vals, width, p.qx + (long)b * width, p.sx + b, red);
+}
+
 // Shapes the chunked kernel cannot take (head width not a power-of-two multiple
 // of 4, or unaligned rows): one CTA per (head, stream), plain loads, no split.
 __global__ void __launch_bounds__(FAST_THREADS) k_attn_scalar(AttnP p) {
@@ -596,6 +724,7 @@ size_t chunks_for(size_t max_valid) { return (max_valid + CHUNK - 1) / CHUNK; }
 extern "C" int mb_attention_init(void) {
     int rc = (int)cudaFuncSetAttribute(k_attn_strict, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (rc == 0) rc = (int)cudaFuncSetAttribute(k_attn_rows, cudaFuncAttributeMaxDynamicSharedMemorySize, ROWS_SMEM_MAX);
+    if (rc == 0) rc = (int)cudaFuncSetAttribute(k_attn_short, cudaFuncAttributeMaxDynamicSharedMemorySize, ROWS_SMEM_MAX - 1024);
     if (rc == 0) rc = (int)cudaFuncSetAttribute(k_attn_scalar, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     return rc;
 }
@@ -667,6 +796,37 @@ extern "C" int mb_attention(const mb_attn_args *a, mb_stream stream) {
                          (a->batch == 1 || a->cache_rows != 0) && (p.slot_stride % p.cache_stride) == 0 &&
                          (((uintptr_t)a->k_cache | (uintptr_t)a->v_cache | (uintptr_t)a->q |
                            (uintptr_t)a->k_new | (uintptr_t)a->v_new) & 15u) == 0;
+    // a cache of a few chunks that nothing is appended to: one CTA per stream, one warp per
+    // (head, chunk), partials merged in shared memory
+    {
+        int hpb_all = 0;
+        for (int c = p.hw > 0 ? 256 / p.hw : 0; c >= 1 && hpb_all == 0; --c)
+            if (c <= p.heads && p.heads % c == 0) hpb_all = c;
+        const size_t short_bytes =
+            (2u * (size_t)p.max_chunks * CHUNK * width + 2u * width + (size_t)p.heads * p.max_chunks * (p.hw + 2) +
+             2u * (size_t)p.heads * p.max_chunks) * sizeof(float);
+        if (chunked && a->k_new == nullptr && hpb_all > 0 && p.max_chunks <= SHORT_MAX_CHUNKS &&
+            p.heads * p.max_chunks <= 32 && short_bytes <= (size_t)ROWS_SMEM_MAX - 1024u &&
+            (a->batch == 1 || a->cache_rows != 0)) {
+            p.box_cols = hpb_all * p.hw;
+            p.nbox = p.heads / hpb_all;
+            p.slot_rows = p.slot_stride / p.cache_stride;
+            p.splits = 1;
+            p.depth = 1;
+            p.early = a->early_prefetch ? 1 : 0;
+            size_t rows = a->cache_rows;
+            if (rows == 0) rows = (size_t)p.valid;
+            CUtensorMap kmap, vmap;
+            if (!mb_make_map_2d(&kmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a->k_cache, rows, (size_t)p.cache_stride,
+                                (size_t)p.cache_stride * 4u, (unsigned)p.box_cols, CHUNK, CU_TENSOR_MAP_SWIZZLE_NONE) ||
+                !mb_make_map_2d(&vmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a->v_cache, rows, (size_t)p.cache_stride,
+                                (size_t)p.cache_stride * 4u, (unsigned)p.box_cols, CHUNK, CU_TENSOR_MAP_SWIZZLE_NONE))
+                return (int)cudaErrorInvalidValue;
+            mb_launch(k_attn_short, dim3((unsigned)p.batch), dim3((unsigned)(p.heads * p.max_chunks) * 32u), short_bytes, s,
+                      kmap, vmap, p);
+            return mb_check_launch();
+        }
+    }
     if (chunked) {
         if (a->partials == nullptr || a->counters == nullptr) return (int)cudaErrorInvalidValue;
         p.splits = (int)splits;
