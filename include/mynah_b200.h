@@ -386,7 +386,7 @@ size_t mynah_b200_decoder_kv_bytes(const void *decoder, size_t length);
  * every step runs as individual launches, each bracketed by two CUDA events on
  * the backend's stream, instead of a graph replay; _read synchronizes and
  * returns, per class, the launches seen and their summed device time. */
-#define MYNAH_B200_PROFILE_CLASSES 15
+#define MYNAH_B200_PROFILE_CLASSES 16
 int mynah_b200_decoder_profile(void *decoder, int enable, char *error, size_t cap);
 int mynah_b200_decoder_profile_read(void *decoder, unsigned long long *launches, double *ms,
                                     size_t n, char *error, size_t cap);

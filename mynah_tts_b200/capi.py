@@ -18,7 +18,7 @@ LIB_PATH = os.path.join(HERE, "libmynah_b200.so")
 F32, INT8, INT4, F16 = 0, 1, 2, 3
 QUANT = {"f32": F32, "int8": INT8, "int4": INT4, "f16": F16}
 ERR_CAP = 512
-PROFILE_CLASSES = 15
+PROFILE_CLASSES = 16
 
 c_float_p = C.POINTER(C.c_float)
 c_uint_p = C.POINTER(C.c_uint)

@@ -91,12 +91,36 @@ __device__ __forceinline__ float block_sum_vt(const float (&v)[VT], float *red) 
     return red[32];
 }
 
+// One-barrier forms of the block reductions: every warp repeats the butterfly over the
+// per-warp values (a butterfly leaves the same bits in every lane, and they are the bits
+// warp 0 gets in block_sum_vt / block_max), so nothing has to be broadcast.  `buf` holds 32
+// floats and must not be written again before the CTA has passed another barrier.
+template <int VT>
+__device__ __forceinline__ float block_sum_vt1(const float (&v)[VT], float *buf) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nrw = (blockDim.x + 31) >> 5;
+    float t[VT];
+#pragma unroll
+    for (int r = 0; r < VT; ++r) t[r] = warp_sum(v[r]);
+    if (lane == 0)
+#pragma unroll
+        for (int r = 0; r < VT; ++r) buf[warp + r * nrw] = t[r];
+    __syncthreads();
+    return warp_sum(lane < VT * nrw ? buf[lane] : 0.0f);
+}
+__device__ __forceinline__ float block_max1(float v, float *buf) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    if (lane == 0) buf[warp] = v;
+    __syncthreads();
+    return warp_max(lane < nw ? buf[lane] : -3.402823466e+38f);
+}
+
 // Non-strict layer norm of one row by one CTA, with optional int8 quantization of the
 // result (src/qmat.c:93-113): `row` holds the input in shared memory and receives y.  The
 // stand-alone kernel calls it with 256 threads and VT = 1, the products' fused prologue
 // with 128 threads and VT = 2 (each thread plays two): a row gets the same bits from
 // either.  Returns the quantization scale (0 when !quant) to every thread; q may be shared
-// or global memory.
+// or global memory.  `red` is scratch of 96 floats that no thread is still reading.
 template <int VT>
 __device__ __forceinline__ float mb_ln_block(float *row, int width, const float *__restrict__ gain,
                                              const float *__restrict__ bias, float eps, float *red,
@@ -108,7 +132,7 @@ __device__ __forceinline__ float mb_ln_block(float *row, int width, const float 
         s[r] = 0.0f;
         for (int i = threadIdx.x + r * blockDim.x; i < width; i += stride) s[r] += row[i];
     }
-    const float mean = __fdiv_rn(block_sum_vt<VT>(s, red), (float)width);
+    const float mean = __fdiv_rn(block_sum_vt1<VT>(s, red), (float)width);
     float v[VT];
 #pragma unroll
     for (int r = 0; r < VT; ++r) {
@@ -118,7 +142,7 @@ __device__ __forceinline__ float mb_ln_block(float *row, int width, const float 
             v[r] = fmaf(d, d, v[r]);
         }
     }
-    const float variance = block_sum_vt<VT>(v, red);
+    const float variance = block_sum_vt1<VT>(v, red + 32);
     const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(variance, (float)width), eps)));
     float amax = 0.0f;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
@@ -129,7 +153,7 @@ __device__ __forceinline__ float mb_ln_block(float *row, int width, const float 
         amax = fmaxf(amax, fabsf(y));
     }
     if (!quant) return 0.0f;
-    amax = block_max(amax, red);
+    amax = block_max1(amax, red + 64);
     const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
     for (int i = threadIdx.x; i < width; i += blockDim.x)
         q[i] = (int8_t)min(127, max(-127, round_half_away(__fmul_rn(row[i], inv))));

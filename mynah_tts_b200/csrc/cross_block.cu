@@ -1,0 +1,313 @@
+// The cross-attention block of a decoder layer as one launch, one CTA per stream
+// (src/graph.c:3213-3256 in mynah-tts):
+//
+//   x      = residual row (already holds x + o_self(...))
+//   h      = layer_norm(x, norm_xattn_query)          -> int8 row + scale
+//   q      = W_q h                                     (int8 x int8, int32 sums)
+//   ctx    = softmax(q K^T * scale) V                  over the stream's text states
+//   x     += W_o quant(ctx)
+//   h2     = layer_norm(x, norm_pos_ff)                -> int8 row + scale (feed-forward input)
+//
+// Everything here is per stream, so the five launches it replaces (norm, product,
+// attention, product, norm) only ever exchanged one row through global memory; each
+// dependent launch costs 4-7 us in the step and the block runs 12 times per step.  The
+// stream's K and V rows (constant after the slot is loaded) are requested as TMA tiles
+// before the wait on the preceding launch, so they land while the norm and the query
+// product run.
+//
+// Same bits as the separate launches: the norm is mb_ln_block<1> on 256 threads, the
+// products are exact int32 sums scaled as (float)s * ws * sx with each product rounded,
+// the attention is the chunked single-head form of k_attn_short (32-row chunks, ordered
+// merge), the quantizations round half away from zero.
+#include "attn_tiles.cuh"
+#include "launch.h"
+
+#include <string.h>
+
+namespace {
+
+constexpr int XB_THREADS = 256;
+constexpr int XB_WARPS = XB_THREADS / 32;
+constexpr int XB_MAX_CHUNKS = 8;
+
+struct CrossP {
+    float *x;
+    const float *gain_query, *gain_ff;
+    const int8_t *wq, *wo;
+    const float *wq_scales, *wo_scales;
+    const int *slots, *n_active;
+    int8_t *qx;
+    float *sx;
+    int *status;
+    long slot_rows;
+    int width, xw, rows, chunks;
+    float scale, eps;
+};
+
+__device__ __forceinline__ int dot16(const uint4 &a, const uint4 &b, int acc) {
+    acc = __dp4a((int)a.x, (int)b.x, acc);
+    acc = __dp4a((int)a.y, (int)b.y, acc);
+    acc = __dp4a((int)a.z, (int)b.z, acc);
+    acc = __dp4a((int)a.w, (int)b.w, acc);
+    return acc;
+}
+
+// RO = rows of the output weight one thread owns (width <= RO * 256); a thread of the query
+// product holds every other 16-byte piece of one weight row, 8 * RO of them.
+template <int RO>
+__global__ void __launch_bounds__(XB_THREADS, 1)
+k_cross_block(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, CrossP p) {
+    extern __shared__ __align__(128) float sm[];
+    __shared__ float red[96];
+    __shared__ __align__(8) unsigned long long mbar[2 * XB_MAX_CHUNKS];   // K chunks, then V chunks
+    __shared__ unsigned s_bad;
+    __shared__ float s_ctx_scale;
+    const int b = blockIdx.x;
+    // lane state was written by the previous step's last launch: readable before the wait
+    const int live = p.n_active != nullptr ? *p.n_active : 0x7fffffff;
+    const long slot = p.slots != nullptr ? (long)p.slots[b] : (long)b;
+    if (b >= live) return;
+    const int W = p.width, XW = p.xw, ns = p.chunks;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int tile_floats = CHUNK * XW;
+    float *Kt = sm;                                   // [ns] tiles of [32][XW]
+    float *Vt = Kt + (long)ns * tile_floats;
+    float *xres = Vt + (long)ns * tile_floats;        // [W] the residual row as it came in
+    float *row = xres + W;                            // [W] work row of the norms
+    float *qs = row + W;                              // [XW] query
+    float *P = qs + XW;                               // [ns][XW + 2] chunk partials
+    float *wts = P + (long)ns * (XW + 2);             // [32] merge scratch
+    float *vals = wts + 32;                           // [XW] merged context
+    float *gq = vals + XW;                            // [W] gain of the first norm
+    float *gf = gq + W;                               // [W] gain of the second norm
+    int8_t *qrow = reinterpret_cast<int8_t *>((reinterpret_cast<uintptr_t>(gf + W) + 15u) & ~(uintptr_t)15u);   // [W] quantized first norm
+    int8_t *ctxq = qrow + W;                                 // [XW] quantized context
+    const unsigned tile_bytes = (unsigned)tile_floats * 4u;
+    if (threadIdx.x == 0) {
+        s_bad = 0u;
+        const unsigned long long stream_policy = mb_l2_evict_first();
+        for (int i = 0; i < 2 * ns; ++i) mbar_init(&mbar[i], 1u);
+        for (int c = 0; c < ns; ++c) {
+            const int y = (int)(slot * p.slot_rows + (long)c * CHUNK);
+            mbar_expect_tx(&mbar[c], tile_bytes);
+            mbar_expect_tx(&mbar[ns + c], tile_bytes);
+            mb_tma_load_2d_hint(Kt + (long)c * tile_floats, &kmap, 0, y, &mbar[c], stream_policy);
+            mb_tma_load_2d_hint(Vt + (long)c * tile_floats, &vmap, 0, y, &mbar[ns + c], stream_policy);
+        }
+    }
+    // Constants, fetched while the preceding launch is still running: the norms' gains into
+    // shared memory, each thread's half of a query-weight row into registers, and the
+    // output weights into L2 (each CTA asks for its share of the lines).
+    for (int i = threadIdx.x; i < W; i += XB_THREADS) {
+        gq[i] = __ldg(p.gain_query + i);
+        gf[i] = __ldg(p.gain_ff + i);
+    }
+    const int npc = W / 16;
+    constexpr int PQ = 8 * RO;
+    const int oq = threadIdx.x >> 1, hq = threadIdx.x & 1;   // query row of this thread, and which pieces
+    uint4 wq0[PQ];
+#pragma unroll
+    for (int j = 0; j < PQ; ++j) {
+        const int pc = 2 * j + hq;
+        wq0[j] = (oq < XW && pc < npc) ? __ldg(reinterpret_cast<const uint4 *>(p.wq + (long)oq * W) + pc)
+                                       : make_uint4(0u, 0u, 0u, 0u);
+    }
+    const float wqs0 = oq < XW ? __ldg(p.wq_scales + oq) : 0.0f;
+    {
+        const long lines = ((long)W * XW + 127) / 128;
+        for (long ln = (long)blockIdx.x * XB_THREADS + threadIdx.x; ln < lines; ln += (long)gridDim.x * XB_THREADS)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(p.wo + ln * 128));
+    }
+    mb_pdl_wait();
+    mb_pdl_trigger();
+
+    // ---- first norm, quantized into shared memory
+    float *xg = p.x + (long)b * W;
+    for (int i = threadIdx.x; i < W; i += XB_THREADS) {
+        const float v = xg[i];
+        xres[i] = v;
+        row[i] = v;
+    }
+    __syncthreads();
+    const float sxq = mb_ln_block<1>(row, W, gq, nullptr, p.eps, red, nullptr, true, qrow);
+    __syncthreads();
+
+    // ---- query product: two threads per output row, pieces of the row interleaved
+    {
+        int acc = 0;
+#pragma unroll
+        for (int j = 0; j < PQ; ++j) {
+            const int pc = 2 * j + hq;
+            if (pc < npc) acc = dot16(wq0[j], reinterpret_cast<const uint4 *>(qrow)[pc], acc);
+        }
+        acc += __shfl_xor_sync(MB_FULL, acc, 1);
+        if (hq == 0 && oq < XW) qs[oq] = __fmul_rn(__fmul_rn((float)acc, wqs0), sxq);
+    }
+    // this thread's output-weight rows are requested now and land during the attention
+    const int lpr = XW / 16;                          // 16-byte pieces of an output-weight row
+    uint4 wo0[RO][8];
+    float wos0[RO];
+#pragma unroll
+    for (int k = 0; k < RO; ++k) {
+        const int r = threadIdx.x + k * XB_THREADS;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            wo0[k][j] = (r < W && j < lpr) ? __ldg(reinterpret_cast<const uint4 *>(p.wo + (long)r * XW) + j)
+                                           : make_uint4(0u, 0u, 0u, 0u);
+        wos0[k] = r < W ? __ldg(p.wo_scales + r) : 0.0f;
+    }
+    __syncthreads();
+
+    // ---- attention over the text states: warp c makes the partial of chunk c
+    const int tpp = XW / 4, rps = 32 / tpp, sub = lane / tpp, li = lane % tpp;
+    if (warp < ns) {
+        const int c = warp;
+        const float4 qv = reinterpret_cast<const float4 *>(qs)[li];
+        const int cnt = min(CHUNK, p.rows - c * CHUNK);
+        const bool k_ok = mbar_wait(&mbar[c], 0u, SPIN_LIMIT);
+        const bool v_ok = k_ok && mbar_wait(&mbar[ns + c], 0u, SPIN_LIMIT);
+        if (k_ok && v_ok) {
+            const float *Ks = Kt + (long)c * tile_floats;
+            float dot;
+            switch (tpp) {
+            case 32: dot = chunk_scores<32>(Ks, XW, qv, sub, li); break;
+            case 16: dot = chunk_scores<16>(Ks, XW, qv, sub, li); break;
+            case 8: dot = chunk_scores<8>(Ks, XW, qv, sub, li); break;
+            default: dot = chunk_scores<4>(Ks, XW, qv, sub, li); break;
+            }
+            const int my_row = li * rps + sub;
+            const float mine = my_row < cnt ? dot * p.scale : -FLT_MAX;
+            const float m = warp_max(mine);
+            const float e = my_row < cnt ? exp_ref<false>(mine - m) : 0.0f;
+            const float l = warp_sum(e);
+            const float *Vs = Vt + (long)c * tile_floats;
+            float4 acc;
+            switch (tpp) {
+            case 32: acc = chunk_values<32>(Vs, XW, e, sub, li); break;
+            case 16: acc = chunk_values<16>(Vs, XW, e, sub, li); break;
+            case 8: acc = chunk_values<8>(Vs, XW, e, sub, li); break;
+            default: acc = chunk_values<4>(Vs, XW, e, sub, li); break;
+            }
+            float *part = P + (long)c * (XW + 2);
+            if (sub == 0) {
+                part[2 + 4 * li] = acc.x; part[3 + 4 * li] = acc.y;
+                part[4 + 4 * li] = acc.z; part[5 + 4 * li] = acc.w;
+            }
+            if (lane == 0) { part[0] = m; part[1] = l; }
+        } else if (lane == 0) {
+            s_bad = 1u;
+            if (p.status != nullptr) atomicOr(p.status, 2);
+        }
+    }
+    __syncthreads();
+    if (s_bad != 0u) {
+        // a tile never landed: one more bounded wait per tile so that none is in flight when
+        // this CTA's shared memory is released
+        if (threadIdx.x == 0)
+            for (int c = 0; c < ns; ++c) {
+                mbar_wait(&mbar[c], 0u, SPIN_LIMIT);
+                mbar_wait(&mbar[ns + c], 0u, SPIN_LIMIT);
+            }
+        return;
+    }
+    if (warp == 0) {
+        merge_chunks<false>(P, ns, XW, lane, wts, [&](int d, float o) { vals[d] = o; });
+        __syncwarp();
+        quantize_row_warp(vals, XW, ctxq, &s_ctx_scale, lane);
+    }
+    __syncthreads();
+    const float sxc = s_ctx_scale;
+
+    // ---- output product added to the residual row: a thread per weight row
+    {
+        uint4 creg[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            creg[j] = j < lpr ? reinterpret_cast<const uint4 *>(ctxq)[j] : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+        for (int k = 0; k < RO; ++k) {
+            const int r = threadIdx.x + k * XB_THREADS;
+            int acc = 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc = dot16(wo0[k][j], creg[j], acc);
+            if (r < W) {
+                const float y = __fmul_rn(__fmul_rn((float)acc, wos0[k]), sxc);
+                const float xn = __fadd_rn(xres[r], y);
+                row[r] = xn;
+                xg[r] = xn;
+            }
+        }
+    }
+    __syncthreads();
+
+    // ---- second norm, quantized for the feed-forward product
+    const float sx2 = mb_ln_block<1>(row, W, gf, nullptr, p.eps, red, nullptr, true, p.qx + (long)b * W);
+    if (threadIdx.x == 0) p.sx[b] = sx2;
+}
+
+size_t cross_block_smem(size_t width, size_t xw, size_t chunks) {
+    const size_t floats = 2u * chunks * CHUNK * xw + 4u * width + xw + chunks * (xw + 2u) + 32u + xw;
+    return floats * sizeof(float) + width + xw + 16u;
+}
+
+bool is_pow2(size_t v) { return v != 0 && (v & (v - 1u)) == 0; }
+
+}  // namespace
+
+extern "C" int mb_cross_block_supported(size_t width, size_t xw, size_t rows) {
+    if (rows == 0 || width == 0 || xw == 0) return 0;
+    const size_t chunks = (rows + CHUNK - 1) / CHUNK;
+    return chunks <= (size_t)XB_MAX_CHUNKS && chunks <= (size_t)XB_WARPS && is_pow2(xw) && xw >= 16 && xw <= 128 &&
+           (width % 16u) == 0 && width <= 1024u && cross_block_smem(width, xw, chunks) <= 225u * 1024u;
+}
+
+extern "C" int mb_cross_block(const mb_cross_block_args *a, mb_stream stream) {
+    if (a == nullptr || a->x == nullptr || a->gain_query == nullptr || a->gain_ff == nullptr || a->wq == nullptr ||
+        a->wo == nullptr || a->wq_scales == nullptr || a->wo_scales == nullptr || a->k_cache == nullptr ||
+        a->v_cache == nullptr || a->qx == nullptr || a->sx == nullptr || a->batch == 0)
+        return (int)cudaErrorInvalidValue;
+    if (!mb_cross_block_supported(a->width, a->xw, a->rows)) return (int)cudaErrorInvalidValue;
+    if ((((uintptr_t)a->k_cache | (uintptr_t)a->v_cache | (uintptr_t)a->wq | (uintptr_t)a->wo | (uintptr_t)a->x |
+          (uintptr_t)a->qx) & 15u) != 0 ||
+        (a->slot_stride % a->xw) != 0 || (a->batch > 1 && a->cache_rows == 0))
+        return (int)cudaErrorInvalidValue;
+    CrossP p;
+    memset(&p, 0, sizeof(p));
+    p.x = a->x;
+    p.gain_query = a->gain_query; p.gain_ff = a->gain_ff;
+    p.wq = a->wq; p.wo = a->wo; p.wq_scales = a->wq_scales; p.wo_scales = a->wo_scales;
+    p.slots = a->slots; p.n_active = a->n_active;
+    p.qx = a->qx; p.sx = a->sx; p.status = a->status;
+    p.slot_rows = (long)(a->slot_stride / a->xw);
+    p.width = (int)a->width; p.xw = (int)a->xw; p.rows = (int)a->rows;
+    p.chunks = (int)((a->rows + CHUNK - 1) / CHUNK);
+    p.scale = a->scale; p.eps = a->eps;
+    const size_t rows = a->cache_rows != 0 ? a->cache_rows : a->rows;
+    CUtensorMap kmap, vmap;
+    if (!mb_make_map_2d(&kmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a->k_cache, rows, a->xw, a->xw * 4u, (unsigned)a->xw,
+                        CHUNK, CU_TENSOR_MAP_SWIZZLE_NONE) ||
+        !mb_make_map_2d(&vmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a->v_cache, rows, a->xw, a->xw * 4u, (unsigned)a->xw,
+                        CHUNK, CU_TENSOR_MAP_SWIZZLE_NONE))
+        return (int)cudaErrorInvalidValue;
+    const size_t smem = cross_block_smem(a->width, a->xw, (size_t)p.chunks);
+    const int ro = (int)((a->width + XB_THREADS - 1) / XB_THREADS);
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid((unsigned)a->batch), block(XB_THREADS);
+    switch (ro) {
+    case 1: mb_launch(k_cross_block<1>, grid, block, smem, s, kmap, vmap, p); break;
+    case 2: mb_launch(k_cross_block<2>, grid, block, smem, s, kmap, vmap, p); break;
+    case 3: mb_launch(k_cross_block<3>, grid, block, smem, s, kmap, vmap, p); break;
+    default: mb_launch(k_cross_block<4>, grid, block, smem, s, kmap, vmap, p); break;
+    }
+    return mb_check_launch();
+}
+
+extern "C" int mb_cross_block_init(void) {
+    int rc = 0;
+    const int bytes = 225 * 1024;
+    rc |= (int)cudaFuncSetAttribute(k_cross_block<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    rc |= (int)cudaFuncSetAttribute(k_cross_block<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    rc |= (int)cudaFuncSetAttribute(k_cross_block<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    rc |= (int)cudaFuncSetAttribute(k_cross_block<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    return rc;
+}

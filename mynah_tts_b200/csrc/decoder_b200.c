@@ -67,7 +67,7 @@ typedef struct mb_decoder {
     float *sx;
     float *partials;
     unsigned *counters;
-    int use_tc, use_fuse1;
+    int use_tc, use_fuse1, use_xblock;
     /* lane state */
     int *d_lens, *d_slots, *d_n_active, *d_allow_eos, *d_eos_flag, *d_eos_frame, *d_frame_idx, *d_status;
     int *d_min_frames;
@@ -97,12 +97,14 @@ typedef struct mb_decoder {
 
 #define PROF_POOL 4096u
 enum { PC_INPUT = 0, PC_NORM, PC_QKV, PC_ATTN_SELF, PC_O_SELF, PC_Q_CROSS, PC_ATTN_CROSS,
-       PC_O_CROSS, PC_FFN_UP, PC_QUANT, PC_FFN_DOWN, PC_HEADS, PC_ARGMAX, PC_ADVANCE, PC_LOCAL };
+       PC_O_CROSS, PC_FFN_UP, PC_QUANT, PC_FFN_DOWN, PC_HEADS, PC_ARGMAX, PC_ADVANCE, PC_LOCAL,
+       PC_XBLOCK };
 static const char *const prof_names[MYNAH_B200_PROFILE_CLASSES] = {
     "input(embed|position)", "layernorm(+quant)", "qkv product", "self attention", "o_self product",
     "q_cross product", "cross attention", "o_cross product", "ffn_up product(+gelu)",
     "hidden quant", "ffn_down product", "heads product", "argmax", "advance",
-    "local transformer frame (all tables)"};
+    "local transformer frame (all tables)",
+    "cross block (norm|q product|cross attention|o product|norm)"};
 
 static void prof_drain(mb_decoder *d) {
     if (d->prof_used == 0) return;
@@ -351,6 +353,8 @@ int mynah_b200_decoder_create(void *state, const mynah_b200_decoder_desc *desc, 
         d->use_tc = !(no_tc != NULL && strcmp(no_tc, "0") != 0);
         const char *no_fuse = getenv("MYNAH_B200_NO_FUSE");
         d->use_fuse1 = !(no_fuse != NULL && strcmp(no_fuse, "0") != 0);
+        const char *no_xb = getenv("MYNAH_B200_NO_CROSS_BLOCK");
+        d->use_xblock = !(no_xb != NULL && strcmp(no_xb, "0") != 0);
     }
     D_TRY(dmalloc((void **)&d->partials, partial_floats * sizeof(float), error, cap));
     D_TRY(dmalloc((void **)&d->counters, n_counters * sizeof(unsigned), error, cap));
@@ -659,6 +663,49 @@ static int enqueue(mb_decoder *d, size_t bucket, int mode, unsigned *count) {
         P(PC_ATTN_SELF, mb_attention(&a, s));
         *count += (st->strict && q) ? 2u : 1u;
         P(PC_O_SELF, product(d, &L->o_self, NULL, d->attn, d->x, W, nb, MB_EPI_RESIDUAL, count));
+        /* int8, non-strict: the whole cross-attention block, with the norm before the
+         * feed-forward product, is one launch with one CTA per stream */
+        const int xb = d->use_xblock && q && !st->strict && L->q_cross.qtype == MB_INT8 &&
+                       L->o_cross.qtype == MB_INT8 && L->ffn_up.qtype == MB_INT8 &&
+                       mb_cross_block_supported(W, XW, d->T);
+        if (xb) {
+            mb_cross_block_args cb;
+            memset(&cb, 0, sizeof(cb));
+            cb.x = d->x;
+            cb.gain_query = L->norm_xattn_query;
+            cb.gain_ff = L->norm_pos_ff;
+            cb.wq = (const int8_t *)L->q_cross.w;
+            cb.wq_scales = L->q_cross.scales;
+            cb.wo = (const int8_t *)L->o_cross.w;
+            cb.wo_scales = L->o_cross.scales;
+            cb.k_cache = d->cross_k + l * d->T * XW;
+            cb.v_cache = d->cross_v + l * d->T * XW;
+            cb.slot_stride = d->layers * d->T * XW;
+            cb.cache_rows = (d->slots - 1u) * d->layers * d->T + d->T;
+            cb.slots = d->d_slots;
+            cb.n_active = d->d_n_active;
+            cb.batch = nb;
+            cb.width = W;
+            cb.xw = XW;
+            cb.rows = d->T;
+            cb.scale = cross_scale;
+            cb.eps = 1.0e-5f;
+            cb.qx = d->qx;
+            cb.sx = d->sx;
+            cb.status = d->d_status;
+            P(PC_XBLOCK, mb_cross_block(&cb, s));
+            *count += 1u;
+            P(PC_FFN_UP, product(d, &L->ffn_up, NULL, d->nrm, d->hidden, F, nb, MB_EPI_GELU, count));
+            if (f1) {
+                P(PC_FFN_DOWN, product_fused(d, &L->ffn_down, NULL, d->hidden, d->x, W, nb, MB_EPI_RESIDUAL,
+                                             MB_FUSE_QUANT, NULL, count));
+            } else {
+                P(PC_QUANT, mb_quant_rows(d->hidden, nb, F, d->qx, d->sx, d->d_n_active, s));
+                *count += 1u;
+                P(PC_FFN_DOWN, product(d, &L->ffn_down, NULL, d->hidden, d->x, W, nb, MB_EPI_RESIDUAL, count));
+            }
+            continue;
+        }
         if (f1) {
             P(PC_Q_CROSS, product_fused(d, &L->q_cross, NULL, d->x, d->q_x, XW, nb, MB_EPI_STORE, MB_FUSE_LN,
                                         L->norm_xattn_query, count));

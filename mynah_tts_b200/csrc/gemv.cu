@@ -82,7 +82,7 @@ __global__ void __launch_bounds__(WARPS * 32) k_gemv(GemvP p) {
     unsigned char *act = smem;                         // [BT][act_bytes]
     float *pbuf = reinterpret_cast<float *>(smem + (size_t)BT * act_bytes);  // int4 only
 
-    __shared__ float fuse_red[33];
+    __shared__ float fuse_red[96];
     __shared__ float fuse_sx;
     // one batch tile per CTA (grid.z): tiles past the live lanes leave at once
     for (int b0 = blockIdx.z * BT; b0 < nb; b0 = nb) {

@@ -25,7 +25,7 @@ k_layernorm(const float *__restrict__ in, float *__restrict__ out, const float *
     mb_pdl_wait();
     mb_pdl_trigger();
     extern __shared__ float row[];
-    __shared__ float red[33];
+    __shared__ float red[96];
     __shared__ float stat[2];
     const int r = blockIdx.x;
     if (n_active != nullptr && r >= *n_active) return;
@@ -103,6 +103,40 @@ k_quant_rows(const float *__restrict__ in, int width, int8_t *__restrict__ qx,
     const int r = blockIdx.x;
     if (n_active != nullptr && r >= *n_active) return;
     const float *x = in + (size_t)r * width;
+    constexpr int VMAX = 4;                            // float4s a thread keeps in registers
+    if ((width & 3) == 0 && width <= 4 * VMAX * (int)blockDim.x && (reinterpret_cast<uintptr_t>(in) & 15u) == 0 &&
+        (reinterpret_cast<uintptr_t>(qx) & 3u) == 0) {
+        // the row is read once, four values per thread and load, and stays in registers
+        const float4 *x4 = reinterpret_cast<const float4 *>(x);
+        const int n4 = width >> 2;
+        float4 v[VMAX];
+        float vmax = 0.0f;
+#pragma unroll
+        for (int j = 0; j < VMAX; ++j) {
+            const int i = threadIdx.x + j * blockDim.x;
+            v[j] = i < n4 ? x4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int j = 0; j < VMAX; ++j)
+            vmax = fmaxf(fmaxf(vmax, fmaxf(fabsf(v[j].x), fabsf(v[j].y))), fmaxf(fabsf(v[j].z), fabsf(v[j].w)));
+        vmax = block_max1(vmax, red);
+        const float inv4 = vmax > 0.0f ? __fdiv_rn(127.0f, vmax) : 0.0f;
+        char4 *q4 = reinterpret_cast<char4 *>(qx + (size_t)r * width);
+#pragma unroll
+        for (int j = 0; j < VMAX; ++j) {
+            const int i = threadIdx.x + j * blockDim.x;
+            if (i < n4) {
+                char4 c;
+                c.x = (signed char)min(127, max(-127, round_half_away(__fmul_rn(v[j].x, inv4))));
+                c.y = (signed char)min(127, max(-127, round_half_away(__fmul_rn(v[j].y, inv4))));
+                c.z = (signed char)min(127, max(-127, round_half_away(__fmul_rn(v[j].z, inv4))));
+                c.w = (signed char)min(127, max(-127, round_half_away(__fmul_rn(v[j].w, inv4))));
+                q4[i] = c;
+            }
+        }
+        if (threadIdx.x == 0) sx[r] = vmax > 0.0f ? __fdiv_rn(vmax, 127.0f) : 0.0f;
+        return;
+    }
     float amax = 0.0f;
     for (int i = threadIdx.x; i < width; i += blockDim.x) amax = fmaxf(amax, fabsf(x[i]));
     amax = block_max(amax, red);

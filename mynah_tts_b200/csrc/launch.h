@@ -200,6 +200,37 @@ int mb_attention(const mb_attn_args *args, mb_stream stream);
 size_t mb_attention_scratch_floats(size_t batch, size_t heads, size_t max_valid, size_t head_width);
 size_t mb_attention_counters(size_t batch, size_t heads);
 
+/* The cross-attention block of one decoder layer for a batch of streams, one CTA per
+ * stream (src/graph.c:3213-3256): layer norm of the residual row (gain_query) with int8
+ * quantization, the query product, attention over the stream's constant cross K/V rows,
+ * int8 quantization of the context, the output product added to the residual row, and the
+ * next layer norm (gain_ff) with int8 quantization for the feed-forward product.  int8
+ * weights only; the arithmetic and its order are those of the separate launches
+ * (mb_layernorm, mb_gemv / mb_gemm_tc, mb_attention), so the bits are the same. */
+typedef struct {
+    float *x;                    /* [batch][width] residual rows, updated in place */
+    const float *gain_query;     /* [width] */
+    const float *gain_ff;        /* [width] */
+    const int8_t *wq;            /* [xw][width] row-major */
+    const float *wq_scales;      /* [xw] */
+    const int8_t *wo;            /* [width][xw] row-major */
+    const float *wo_scales;      /* [width] */
+    const float *k_cache;        /* cross K rows of this layer, slot 0 */
+    const float *v_cache;
+    size_t slot_stride;          /* floats between slots */
+    size_t cache_rows;           /* rows spanned by all slots (tensor-map extent) */
+    const int *slots;            /* [batch] or NULL (lane b uses slot b) */
+    const int *n_active;
+    size_t batch, width, xw, rows;   /* rows: text states attended over */
+    float scale, eps;
+    int8_t *qx;                  /* [batch][width] out: quantized second norm */
+    float *sx;                   /* [batch] */
+    int *status;
+} mb_cross_block_args;
+int mb_cross_block_init(void);
+int mb_cross_block_supported(size_t width, size_t xw, size_t rows);
+int mb_cross_block(const mb_cross_block_args *args, mb_stream stream);
+
 #ifdef __cplusplus
 }
 #endif

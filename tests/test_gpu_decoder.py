@@ -111,6 +111,47 @@ def test_stream_result_does_not_depend_on_batch(strict, tiny_model, tiny_memory)
     ps.close(); pm.close()
 
 
+@pytest.mark.parametrize("shape_name", ["tiny", "full"])
+def test_cross_block_launch_matches_separate_launches(shape_name, tiny_model, tiny_memory, monkeypatch):
+    """The one-launch cross-attention block (norm, query product, attention, output
+    product, norm) gives the bits of the five launches it replaces, at 2, 5, 16 and 64
+    streams with different rows and staggered positions."""
+    if shape_name == "tiny":
+        shape, model, memory = synth.TINY, tiny_model, tiny_memory
+    else:
+        shape = synth.MAGPIE_357M
+        model = synth.make_model(shape, seed=31)
+        memory = synth.make_memory(shape, seed=131)
+    pm = O.PortModel(model, O.INT8)
+    ps = pm.new_stream(memory, 4)
+    ck, cv = ps.cross_k.copy(), ps.cross_v.copy()
+    ps.close(); pm.close()
+    rng = np.random.default_rng(12)
+    rows = rng.normal(0, 0.05, size=(3, 64, shape.width)).astype(np.float32)
+    outs = {}
+    for mode in ("block", "separate"):
+        if mode == "separate":
+            monkeypatch.setenv("MYNAH_B200_NO_CROSS_BLOCK", "1")
+        else:
+            monkeypatch.delenv("MYNAH_B200_NO_CROSS_BLOCK", raising=False)
+        be = Backend("int8", strict=False)
+        dec = Decoder(be, model, capacity=16, slots=64)
+        for s in range(64):
+            # every slot its own text states: a rolled copy of the same cross K/V
+            dec.slot_load(s, np.roll(ck, s, axis=1), np.roll(cv, s, axis=1))
+        got = []
+        for batch in (2, 5, 16, 64):
+            for s in range(64):
+                dec.slot_set_length(s, s % 5)
+            lanes = list(range(64))[::-1][:batch]
+            for t in range(3):
+                got.append(dec.step_batch(lanes, rows[t, :batch]).copy())
+        outs[mode] = got
+        dec.close(); be.close()
+    for a, b in zip(outs["block"], outs["separate"]):
+        assert np.array_equal(a, b)
+
+
 def test_staggered_lengths_and_lane_masking(tiny_model, tiny_memory):
     """Streams at different positions in one step, and a batch that is not a
     power of two (lanes past the live count stay untouched)."""
