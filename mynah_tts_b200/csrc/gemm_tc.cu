@@ -18,8 +18,16 @@
 //     lanes (= weight rows) with tcgen05.ld and apply the epilogue.
 // Grid: (row tiles, lane tiles).  A CTA walks the whole K range through a ring of
 // eight stages: a stage is refilled as soon as tcgen05.commit reports that the
-// MMAs reading it have finished.  (Splitting K across CTAs with integer atomics
-// was measured at twice the time of an unsplit launch and was dropped.)
+// MMAs reading it have finished.
+//
+// Long K (more chunks than stages, the feed-forward down product): a thread-block
+// cluster of KS CTAs along K shares one output tile.  Each CTA walks 1/KS of the chunks,
+// few enough that all its weight stages are requested before the dependency wait, and the
+// CTAs of ranks 1.. write their int32 accumulators into rank 0's shared memory (distributed
+// shared memory, then a release-arrive on rank 0's mbarrier); rank 0 adds them to its own
+// and runs the epilogue.  Integer sums: the bits do not depend on the split.  (Splitting K
+// with integer atomics in global memory was measured at twice the time of an unsplit
+// launch and was dropped.)
 //
 // The first weight stages are requested BEFORE the programmatic-dependency wait: weights
 // are never written by a preceding launch, so they can land while it finishes.
@@ -31,6 +39,9 @@
 #include "launch.h"
 
 #include "tma.cuh"
+
+#include <stdlib.h>
+#include <string.h>
 
 namespace {
 
@@ -52,6 +63,7 @@ struct TcP {
     const uint32_t *tanh_tab;
     long n, k, out_stride;
     int batch, epilogue, strict;
+    int ksplit;          // CTAs of a cluster that share one output tile along K
 };
 
 __device__ __forceinline__ unsigned saddr(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -115,18 +127,59 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, int (&v)[16]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// ---- thread-block cluster helpers (split K)
+__device__ __forceinline__ unsigned cluster_rank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// address of `ptr` (this CTA's shared memory) in the shared memory of cluster rank `rank`
+__device__ __forceinline__ unsigned remote_saddr(const void *ptr, unsigned rank) {
+    unsigned r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr(ptr)), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void remote_store(unsigned raddr, int v) {
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(raddr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void remote_arrive(unsigned rbar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(rbar) : "memory");
+}
+__device__ __forceinline__ bool bar_wait_cluster(void *bar, unsigned parity, unsigned limit) {
+    for (unsigned i = 0; i < limit; ++i) {
+        unsigned done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(saddr(bar)), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
+template <bool SPLIT>
 __global__ void __launch_bounds__(TC_THREADS)
 k_gemm_i8_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcP p) {
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) unsigned long long full_bar[MAX_STAGES];
     __shared__ __align__(8) unsigned long long empty_bar[MAX_STAGES];
     __shared__ __align__(8) unsigned long long done_bar;
+    __shared__ __align__(8) unsigned long long part_bar;     // split K: arrivals of the other ranks
     __shared__ uint32_t s_tmem;
     __shared__ unsigned s_fail;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int b0 = blockIdx.y * BN;
     const long m0 = (long)blockIdx.x * TM;
-    const int nchunks = (int)((p.k + KC - 1) / KC);
+    const int all_chunks = (int)((p.k + KC - 1) / KC);
+    // split K: this CTA's share of the chunks (the launcher makes them divide evenly)
+    const int nks = SPLIT ? p.ksplit : 1;
+    const int ks = SPLIT ? (int)cluster_rank() : 0;
+    const int nchunks = all_chunks / nks, c_first = ks * nchunks;
     // operands need 1024-byte alignment for the 128-byte swizzle
     unsigned char *base = smem_raw + ((1024u - (saddr(smem_raw) & 1023u)) & 1023u);
     unsigned char *As = base;                               // [stage][128 rows][128 B]
@@ -137,6 +190,7 @@ k_gemm_i8_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
             bar_init(&empty_bar[s], 1u);
         }
         bar_init(&done_bar, 1u);
+        if (SPLIT) bar_init(&part_bar, (unsigned)((nks - 1) * TC_THREADS));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         s_fail = 0u;
     }
@@ -148,6 +202,8 @@ k_gemm_i8_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = s_tmem;
+    // split K: rank 0's arrival barrier is initialized before any rank can reach it
+    if (SPLIT) cluster_sync_all();
 
     // Weights do not depend on the launches before this one: their first stages are
     // requested before the dependency wait, so they land while the predecessor finishes.
@@ -156,7 +212,7 @@ k_gemm_i8_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
     if (warp == 0 && lane == 0) {
         for (int c = 0; c < first; ++c) {
             bar_expect(&full_bar[c], stage_bytes);
-            tma_load_2d(As + (size_t)c * A_BYTES, &map_w, c * KC, (int)m0, &full_bar[c]);
+            tma_load_2d(As + (size_t)c * A_BYTES, &map_w, (c_first + c) * KC, (int)m0, &full_bar[c]);
         }
     }
     mb_pdl_wait();
@@ -167,7 +223,7 @@ k_gemm_i8_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
         // halves are sent too, so each barrier completes), then give the TMEM back
         if (warp == 0 && lane == 0) {
             for (int c = 0; c < first; ++c) {
-                tma_load_2d(Bs + (size_t)c * B_BYTES, &map_x, c * KC, b0, &full_bar[c]);
+                tma_load_2d(Bs + (size_t)c * B_BYTES, &map_x, (c_first + c) * KC, b0, &full_bar[c]);
                 bar_wait(&full_bar[c], 0u, TC_SPIN);
             }
         }
@@ -180,7 +236,7 @@ k_gemm_i8_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
     if (warp == 0 && lane == 0) {
         // the activation halves of the first stages, then the rest of the K walk:
         // chunk c goes to stage c % 8 once the MMAs of chunk c - 8 released it
-        for (int c = 0; c < first; ++c) tma_load_2d(Bs + (size_t)c * B_BYTES, &map_x, c * KC, b0, &full_bar[c]);
+        for (int c = 0; c < first; ++c) tma_load_2d(Bs + (size_t)c * B_BYTES, &map_x, (c_first + c) * KC, b0, &full_bar[c]);
         for (int c = first; c < nchunks; ++c) {
             const int s = c % MAX_STAGES;
             if (!bar_wait(&empty_bar[s], (unsigned)((c / MAX_STAGES - 1) & 1), TC_SPIN)) {
@@ -189,8 +245,8 @@ k_gemm_i8_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
                 break;
             }
             bar_expect(&full_bar[s], stage_bytes);
-            tma_load_2d(As + (size_t)s * A_BYTES, &map_w, c * KC, (int)m0, &full_bar[s]);
-            tma_load_2d(Bs + (size_t)s * B_BYTES, &map_x, c * KC, b0, &full_bar[s]);
+            tma_load_2d(As + (size_t)s * A_BYTES, &map_w, (c_first + c) * KC, (int)m0, &full_bar[s]);
+            tma_load_2d(Bs + (size_t)s * B_BYTES, &map_x, (c_first + c) * KC, b0, &full_bar[s]);
         }
     } else if (warp == 1 && lane == 0) {
         const uint32_t idesc = instr_desc_i8(TM, BN);
@@ -235,10 +291,30 @@ k_gemm_i8_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
         // before this CTA's shared memory is released
         if (threadIdx.x == 0)
             for (int s = 0; s < MAX_STAGES && s < nchunks; ++s) bar_wait(&full_bar[s], 0u, TC_SPIN >> 4);
+        if (SPLIT && ks != 0) remote_arrive(remote_saddr(&part_bar, 0u));   // rank 0 need not wait for the limit
     } else {
         int v[16];
         tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16), v);
-        if (row_ok) {
+        bool whole = true;                                   // v holds the sum over all of K
+        if (SPLIT) {
+            // partial sums of ranks 1.. in rank 0's shared memory: [rank - 1][lane j][weight row]
+            int *parts = reinterpret_cast<int *>(Bs + (size_t)MAX_STAGES * B_BYTES);
+            if (ks != 0) {
+                const unsigned dst = remote_saddr(parts + ((size_t)(ks - 1) * BN) * TM + threadIdx.x, 0u);
+#pragma unroll
+                for (int j = 0; j < BN; ++j) remote_store(dst + (unsigned)(j * TM * 4), v[j]);
+                remote_arrive(remote_saddr(&part_bar, 0u));
+                whole = false;
+            } else if (bar_wait_cluster(&part_bar, 0u, TC_SPIN)) {
+                for (int z = 1; z < nks; ++z)
+#pragma unroll
+                    for (int j = 0; j < BN; ++j) v[j] += parts[((size_t)(z - 1) * BN + j) * TM + threadIdx.x];
+            } else {
+                whole = false;
+                if (p.status != nullptr) atomicOr(p.status, 16);
+            }
+        }
+        if (row_ok && whole) {
 #pragma unroll
             for (int j = 0; j < BN; ++j) {
                 const int b = b0 + j;
@@ -258,6 +334,8 @@ k_gemm_i8_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
     __syncthreads();
     if (warp == 0)
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    // split K: rank 0's shared memory stays allocated until every rank is past its stores
+    if (SPLIT) cluster_sync_all();
 }
 
 // ------------------------------------------------------------------ int4 weights
@@ -484,11 +562,20 @@ bool make_map(CUtensorMap *map, const void *ptr, size_t rows, size_t k, unsigned
 }
 
 constexpr size_t TC_SMEM = (size_t)MAX_STAGES * (A_BYTES + B_BYTES) + 1024;
+constexpr int KS_MAX = 4;            // most CTAs per cluster along K
+constexpr size_t TC_SMEM_SPLIT = TC_SMEM + (size_t)(KS_MAX - 1) * BN * TM * sizeof(int);
 
 }  // namespace
 
+// MYNAH_B200_NO_KSPLIT=1 keeps every product on one CTA per tile (for A/B measurements).
+static int mb_gemm_tc_split_enabled() {
+    const char *e = getenv("MYNAH_B200_NO_KSPLIT");
+    return (e != nullptr && strcmp(e, "0") != 0) ? 0 : 1;
+}
+
 extern "C" int mb_gemm_tc_init(void) {
-    int rc = (int)cudaFuncSetAttribute(k_gemm_i8_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM);
+    int rc = (int)cudaFuncSetAttribute(k_gemm_i8_tc<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM);
+    if (rc == 0) rc = (int)cudaFuncSetAttribute(k_gemm_i8_tc<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_SPLIT);
     if (rc == 0) rc = (int)cudaFuncSetAttribute(k_gemm_i4_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC4_SMEM);
     return rc;
 }
@@ -523,11 +610,39 @@ extern "C" int mb_gemm_tc(const mb_gemv_args *a, size_t qx_rows_alloc, int *stat
     p.tanh_tab = a->tanh_tab;
     p.n = (long)a->n; p.k = (long)a->k; p.out_stride = (long)a->out_stride;
     p.batch = (int)a->batch; p.epilogue = a->epilogue; p.strict = a->strict;
+    p.ksplit = 1;
     const unsigned m_tiles = (unsigned)((a->n + TM - 1) / TM);
     const unsigned b_tiles = (unsigned)((a->batch + BN - 1) / BN);
     if (int4)
         mb_launch(k_gemm_i4_tc, dim3(dim3(m_tiles, b_tiles)), dim3(I4_THREADS), TC4_SMEM, (cudaStream_t)stream, map_w, map_x, p);
-    else
-        mb_launch(k_gemm_i8_tc, dim3(dim3(m_tiles, b_tiles)), dim3(TC_THREADS), TC_SMEM, (cudaStream_t)stream, map_w, map_x, p);
+    else {
+        // more chunks than stages: the widest split along K (up to KS_MAX) that lets every CTA
+        // request all its weight stages at once, while the whole grid still fits the SMs
+        const unsigned chunks = (unsigned)((a->k + KC - 1) / KC);
+        unsigned ks = 1;
+        if (chunks > (unsigned)MAX_STAGES && (a->k % KC) == 0 && mb_gemm_tc_split_enabled())
+            for (unsigned c = (unsigned)KS_MAX; c >= 2 && ks == 1; --c)
+                if (chunks % c == 0 && chunks / c <= (unsigned)MAX_STAGES && m_tiles * b_tiles * c <= 132u) ks = c;
+        if (ks > 1) {
+            p.ksplit = (int)ks;
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(m_tiles, b_tiles, ks);
+            cfg.blockDim = dim3(TC_THREADS);
+            cfg.dynamicSmemBytes = TC_SMEM_SPLIT;
+            cfg.stream = (cudaStream_t)stream;
+            cudaLaunchAttribute attr[2];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = 1;
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = ks;
+            attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[1].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = mb_pdl_enabled() ? 2u : 1u;
+            const int rc = (int)cudaLaunchKernelEx(&cfg, k_gemm_i8_tc<true>, map_w, map_x, p);
+            return rc != 0 ? rc : mb_check_launch();
+        }
+        mb_launch(k_gemm_i8_tc<false>, dim3(dim3(m_tiles, b_tiles)), dim3(TC_THREADS), TC_SMEM, (cudaStream_t)stream, map_w, map_x, p);
+    }
     return mb_check_launch();
 }

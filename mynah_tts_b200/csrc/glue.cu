@@ -16,17 +16,26 @@
 namespace {
 
 // ---------------------------------------------------------------- LayerNorm
-// One CTA per row.  Dynamic shared memory: width floats (the row, then y).
+// One CTA per row.  Dynamic shared memory: the row, then the squares (strict form) or the
+// gain and the bias (fast form).
 template <bool STRICT>
 __global__ void __launch_bounds__(256)
 k_layernorm(const float *__restrict__ in, float *__restrict__ out, const float *__restrict__ gain,
             const float *__restrict__ bias, int width, float eps, int8_t *__restrict__ qx,
             float *__restrict__ sx, const int *__restrict__ n_active) {
-    mb_pdl_wait();
-    mb_pdl_trigger();
     extern __shared__ float row[];
     __shared__ float red[96];
     __shared__ float stat[2];
+    // gain and bias are constants: they are staged while the preceding launch still runs
+    float *gs = row + width, *bs = gs + width;
+    if (!STRICT) {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) {
+            gs[i] = __ldg(gain + i);
+            if (bias != nullptr) bs[i] = __ldg(bias + i);
+        }
+    }
+    mb_pdl_wait();
+    mb_pdl_trigger();
     const int r = blockIdx.x;
     if (n_active != nullptr && r >= *n_active) return;
     const float *x = in + (size_t)r * width;
@@ -58,7 +67,7 @@ k_layernorm(const float *__restrict__ in, float *__restrict__ out, const float *
         variance = stat[1];
     } else {
         // the routine shared with the products' fused prologue
-        const float sxv = mb_ln_block<1>(row, width, gain, bias, eps, red, out == nullptr ? nullptr : out + (size_t)r * width,
+        const float sxv = mb_ln_block<1>(row, width, gs, bias == nullptr ? nullptr : bs, eps, red, out == nullptr ? nullptr : out + (size_t)r * width,
                                       qx != nullptr, qx == nullptr ? nullptr : qx + (size_t)r * width);
         if (qx != nullptr && threadIdx.x == 0) sx[r] = sxv;
         return;
@@ -464,7 +473,8 @@ inline unsigned blocks_for(size_t n) { return (unsigned)((n + 255) / 256); }
 extern "C" int mb_layernorm(const float *in, float *out, const float *gain, const float *bias,
                             size_t rows, size_t width, float eps, int8_t *qx, float *sx,
                             const int *n_active, int strict, mb_stream stream) {
-    const size_t smem = width * sizeof(float) * (strict ? 2 : 1);
+    /* strict: the row and its squares; else the row, the gain and (if any) the bias */
+    const size_t smem = width * sizeof(float) * ((!strict && bias != NULL) ? 3u : 2u);
     if (rows == 0 || width == 0 || smem > 48u * 1024u) return (int)cudaErrorInvalidValue;
     cudaStream_t s = (cudaStream_t)stream;
     if (strict)

@@ -114,8 +114,9 @@ def test_stream_result_does_not_depend_on_batch(strict, tiny_model, tiny_memory)
 @pytest.mark.parametrize("shape_name", ["tiny", "full"])
 def test_cross_block_launch_matches_separate_launches(shape_name, tiny_model, tiny_memory, monkeypatch):
     """The one-launch cross-attention block (norm, query product, attention, output
-    product, norm) gives the bits of the five launches it replaces, at 2, 5, 16 and 64
-    streams with different rows and staggered positions."""
+    product, norm) gives the bits of the five launches it replaces, and the tensor-core
+    product split along K over a cluster the bits of the unsplit one, at 1, 2, 5, 16 and
+    64 streams with different rows and staggered positions."""
     if shape_name == "tiny":
         shape, model, memory = synth.TINY, tiny_model, tiny_memory
     else:
@@ -129,18 +130,20 @@ def test_cross_block_launch_matches_separate_launches(shape_name, tiny_model, ti
     rng = np.random.default_rng(12)
     rows = rng.normal(0, 0.05, size=(3, 64, shape.width)).astype(np.float32)
     outs = {}
-    for mode in ("block", "separate"):
+    for mode in ("block", "separate", "unsplit"):
+        monkeypatch.delenv("MYNAH_B200_NO_CROSS_BLOCK", raising=False)
+        monkeypatch.delenv("MYNAH_B200_NO_KSPLIT", raising=False)
         if mode == "separate":
             monkeypatch.setenv("MYNAH_B200_NO_CROSS_BLOCK", "1")
-        else:
-            monkeypatch.delenv("MYNAH_B200_NO_CROSS_BLOCK", raising=False)
+        if mode == "unsplit":
+            monkeypatch.setenv("MYNAH_B200_NO_KSPLIT", "1")
         be = Backend("int8", strict=False)
         dec = Decoder(be, model, capacity=16, slots=64)
         for s in range(64):
             # every slot its own text states: a rolled copy of the same cross K/V
             dec.slot_load(s, np.roll(ck, s, axis=1), np.roll(cv, s, axis=1))
         got = []
-        for batch in (2, 5, 16, 64):
+        for batch in (1, 2, 5, 16, 64):
             for s in range(64):
                 dec.slot_set_length(s, s % 5)
             lanes = list(range(64))[::-1][:batch]
@@ -148,8 +151,9 @@ def test_cross_block_launch_matches_separate_launches(shape_name, tiny_model, ti
                 got.append(dec.step_batch(lanes, rows[t, :batch]).copy())
         outs[mode] = got
         dec.close(); be.close()
-    for a, b in zip(outs["block"], outs["separate"]):
+    for a, b, c in zip(outs["block"], outs["separate"], outs["unsplit"]):
         assert np.array_equal(a, b)
+        assert np.array_equal(a, c)
 
 
 def test_staggered_lengths_and_lane_masking(tiny_model, tiny_memory):
