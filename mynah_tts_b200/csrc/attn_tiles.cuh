@@ -68,6 +68,21 @@ __device__ __forceinline__ void merge_chunks(const float *ph, int ns, int hw, in
     }
 }
 
+// merge_chunks for one dimension d by one thread: the same operations in the same order
+// (M, then per chunk w = exp(m - M), L and O as fma chains over the chunk index).
+__device__ __forceinline__ float merge_dim(const float *ph, int ns, int hw, int d) {
+    const int pitch = hw + 2;
+    float M = -FLT_MAX;
+    for (int s = 0; s < ns; ++s) M = fmaxf(M, ph[(long)s * pitch]);
+    float L = 0.0f, O = 0.0f;
+    for (int s = 0; s < ns; ++s) {
+        const float w = exp_ref<false>(ph[(long)s * pitch] - M);
+        L = fmaf(ph[(long)s * pitch + 1], w, L);
+        O = fmaf(ph[(long)s * pitch + 2 + d], w, O);
+    }
+    return L > 0.0f ? O / L : 0.0f;
+}
+
 // Quantize one merged row (already in `vals`, shared) to int8: shared by the
 // per-stream tail of the kernel below.
 __device__ __forceinline__ void quantize_shared_row(const float *vals, int width, int8_t *qrow,

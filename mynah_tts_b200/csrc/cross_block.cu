@@ -44,6 +44,15 @@ struct CrossP {
     float scale, eps;
 };
 
+// A read-only 16-byte load the compiler may not move: the constants fetched early must be
+// requested where the source says (before the dependency wait, before the attention), not
+// next to their first use.
+__device__ __forceinline__ uint4 ldg_pinned(const uint4 *ptr) {
+    uint4 v;
+    asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(ptr));
+    return v;
+}
+
 __device__ __forceinline__ int dot16(const uint4 &a, const uint4 &b, int acc) {
     acc = __dp4a((int)a.x, (int)b.x, acc);
     acc = __dp4a((int)a.y, (int)b.y, acc);
@@ -52,16 +61,16 @@ __device__ __forceinline__ int dot16(const uint4 &a, const uint4 &b, int acc) {
     return acc;
 }
 
-// RO = rows of the output weight one thread owns (width <= RO * 256); a thread of the query
-// product holds every other 16-byte piece of one weight row, 8 * RO of them.
-template <int RO>
+// RO = rows of the output weight one thread ends up owning (width <= RO * 256); a thread of
+// the query product holds every other 16-byte piece of one weight row, 8 * RO of them.
+// LPR = 16-byte pieces of an output-weight row (xw = 16 * LPR).
+template <int RO, int LPR>
 __global__ void __launch_bounds__(XB_THREADS, 1)
 k_cross_block(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, CrossP p) {
     extern __shared__ __align__(128) float sm[];
     __shared__ float red[96];
     __shared__ __align__(8) unsigned long long mbar[2 * XB_MAX_CHUNKS];   // K chunks, then V chunks
     __shared__ unsigned s_bad;
-    __shared__ float s_ctx_scale;
     const int b = blockIdx.x;
     // lane state was written by the previous step's last launch: readable before the wait
     const int live = p.n_active != nullptr ? *p.n_active : 0x7fffffff;
@@ -109,7 +118,7 @@ k_cross_block(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
 #pragma unroll
     for (int j = 0; j < PQ; ++j) {
         const int pc = 2 * j + hq;
-        wq0[j] = (oq < XW && pc < npc) ? __ldg(reinterpret_cast<const uint4 *>(p.wq + (long)oq * W) + pc)
+        wq0[j] = (oq < XW && pc < npc) ? ldg_pinned(reinterpret_cast<const uint4 *>(p.wq + (long)oq * W) + pc)
                                        : make_uint4(0u, 0u, 0u, 0u);
     }
     const float wqs0 = oq < XW ? __ldg(p.wq_scales + oq) : 0.0f;
@@ -134,27 +143,50 @@ k_cross_block(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
 
     // ---- query product: two threads per output row, pieces of the row interleaved
     {
-        int acc = 0;
+        int a0 = 0, a1 = 0, a2 = 0, a3 = 0;           // four chains instead of one of 4 * PQ steps
 #pragma unroll
         for (int j = 0; j < PQ; ++j) {
             const int pc = 2 * j + hq;
-            if (pc < npc) acc = dot16(wq0[j], reinterpret_cast<const uint4 *>(qrow)[pc], acc);
+            if (pc < npc) {
+                const uint4 h = reinterpret_cast<const uint4 *>(qrow)[pc];
+                a0 = __dp4a((int)wq0[j].x, (int)h.x, a0);
+                a1 = __dp4a((int)wq0[j].y, (int)h.y, a1);
+                a2 = __dp4a((int)wq0[j].z, (int)h.z, a2);
+                a3 = __dp4a((int)wq0[j].w, (int)h.w, a3);
+            }
         }
+        int acc = (a0 + a1) + (a2 + a3);
         acc += __shfl_xor_sync(MB_FULL, acc, 1);
         if (hq == 0 && oq < XW) qs[oq] = __fmul_rn(__fmul_rn((float)acc, wqs0), sxq);
     }
-    // this thread's output-weight rows are requested now and land during the attention
-    const int lpr = XW / 16;                          // 16-byte pieces of an output-weight row
-    uint4 wo0[RO][8];
+    // The output weights are requested now and land during the attention.  A warp owns
+    // 32 * RO consecutive weight rows and reads them LPR lanes to a row (whole 128-byte lines
+    // per load: a thread per row would touch 32 lines per load instruction).
+    constexpr int RPI = 32 / LPR;                     // rows per warp load
+    constexpr int NI = RO * LPR;                      // loads per lane
+    const int lr = lane / LPR, lp = lane % LPR;
+    const int wrow0 = warp * RO * 32;
+    uint4 wo0[NI];
+#pragma unroll
+    for (int u = 0; u < NI; ++u) {
+        const int r = wrow0 + u * RPI + lr;
+        wo0[u] = r < W ? ldg_pinned(reinterpret_cast<const uint4 *>(p.wo + (long)r * XW) + lp) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    // after the exchange below this lane holds the sums of loads ubase .. ubase + RO - 1
+    int ubase = 0;
+    {
+        int n = NI;
+#pragma unroll
+        for (int m = LPR / 2; m >= 1; m >>= 1) {
+            n >>= 1;
+            if (lp & m) ubase += n;
+        }
+    }
     float wos0[RO];
 #pragma unroll
-    for (int k = 0; k < RO; ++k) {
-        const int r = threadIdx.x + k * XB_THREADS;
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-            wo0[k][j] = (r < W && j < lpr) ? __ldg(reinterpret_cast<const uint4 *>(p.wo + (long)r * XW) + j)
-                                           : make_uint4(0u, 0u, 0u, 0u);
-        wos0[k] = r < W ? __ldg(p.wo_scales + r) : 0.0f;
+    for (int i = 0; i < RO; ++i) {
+        const int r = wrow0 + (ubase + i) * RPI + lr;
+        wos0[i] = r < W ? __ldg(p.wo_scales + r) : 0.0f;
     }
     __syncthreads();
 
@@ -210,28 +242,43 @@ k_cross_block(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
             }
         return;
     }
-    if (warp == 0) {
-        merge_chunks<false>(P, ns, XW, lane, wts, [&](int d, float o) { vals[d] = o; });
-        __syncwarp();
-        quantize_row_warp(vals, XW, ctxq, &s_ctx_scale, lane);
-    }
+    // merge of the chunk partials, a thread per dimension, and the int8 quantization of the
+    // merged row (one warp doing both in turn was a 4 us chain of dependent instructions)
+    float ctx = 0.0f;
+    if (threadIdx.x < XW) ctx = merge_dim(P, ns, XW, threadIdx.x);
+    const float cmax = block_max1(fabsf(ctx), red);
+    const float cinv = cmax > 0.0f ? __fdiv_rn(127.0f, cmax) : 0.0f;
+    if (threadIdx.x < XW) ctxq[threadIdx.x] = (int8_t)min(127, max(-127, round_half_away(__fmul_rn(ctx, cinv))));
+    const float sxc = cmax > 0.0f ? __fdiv_rn(cmax, 127.0f) : 0.0f;
     __syncthreads();
-    const float sxc = s_ctx_scale;
 
-    // ---- output product added to the residual row: a thread per weight row
+    // ---- output product added to the residual row
     {
-        uint4 creg[8];
+        const uint4 creg = reinterpret_cast<const uint4 *>(ctxq)[lp];
+        int part[NI];
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-            creg[j] = j < lpr ? reinterpret_cast<const uint4 *>(ctxq)[j] : make_uint4(0u, 0u, 0u, 0u);
+        for (int u = 0; u < NI; ++u) part[u] = dot16(wo0[u], creg, 0);
+        // the LPR lanes of a row exchange halves of their lists: log2(LPR) rounds, after which
+        // each lane holds RO complete sums (integers: the order does not matter)
+        int n = NI;
 #pragma unroll
-        for (int k = 0; k < RO; ++k) {
-            const int r = threadIdx.x + k * XB_THREADS;
-            int acc = 0;
+        for (int m = LPR / 2; m >= 1; m >>= 1) {
+            n >>= 1;
+            const bool upper = (lp & m) != 0;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) acc = dot16(wo0[k][j], creg[j], acc);
+            for (int i = 0; i < NI / 2; ++i) {
+                if (i < n) {
+                    const int send = upper ? part[i] : part[i + n];
+                    const int keep = upper ? part[i + n] : part[i];
+                    part[i] = keep + __shfl_xor_sync(MB_FULL, send, m);
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < RO; ++i) {
+            const int r = wrow0 + (ubase + i) * RPI + lr;
             if (r < W) {
-                const float y = __fmul_rn(__fmul_rn((float)acc, wos0[k]), sxc);
+                const float y = __fmul_rn(__fmul_rn((float)part[i], wos0[i]), sxc);
                 const float xn = __fadd_rn(xres[r], y);
                 row[r] = xn;
                 xg[r] = xn;
@@ -257,6 +304,9 @@ bool is_pow2(size_t v) { return v != 0 && (v & (v - 1u)) == 0; }
 extern "C" int mb_cross_block_supported(size_t width, size_t xw, size_t rows) {
     if (rows == 0 || width == 0 || xw == 0) return 0;
     const size_t chunks = (rows + CHUNK - 1) / CHUNK;
+    // instantiated: xw = 128 with any width up to 1024, and xw = 32 with width up to 256
+    const size_t ro = (width + XB_THREADS - 1) / XB_THREADS;
+    if (!(xw == 128 || (xw == 32 && ro == 1))) return 0;
     return chunks <= (size_t)XB_MAX_CHUNKS && chunks <= (size_t)XB_WARPS && is_pow2(xw) && xw >= 16 && xw <= 128 &&
            (width % 16u) == 0 && width <= 1024u && cross_block_smem(width, xw, chunks) <= 225u * 1024u;
 }
@@ -293,21 +343,21 @@ extern "C" int mb_cross_block(const mb_cross_block_args *a, mb_stream stream) {
     const int ro = (int)((a->width + XB_THREADS - 1) / XB_THREADS);
     cudaStream_t s = (cudaStream_t)stream;
     const dim3 grid((unsigned)a->batch), block(XB_THREADS);
-    switch (ro) {
-    case 1: mb_launch(k_cross_block<1>, grid, block, smem, s, kmap, vmap, p); break;
-    case 2: mb_launch(k_cross_block<2>, grid, block, smem, s, kmap, vmap, p); break;
-    case 3: mb_launch(k_cross_block<3>, grid, block, smem, s, kmap, vmap, p); break;
-    default: mb_launch(k_cross_block<4>, grid, block, smem, s, kmap, vmap, p); break;
-    }
+    const int lpr = (int)(a->xw / 16u);
+#define XB_CASE(RO_, LPR_) \
+    if (ro == RO_ && lpr == LPR_) mb_launch(k_cross_block<RO_, LPR_>, grid, block, smem, s, kmap, vmap, p)
+    XB_CASE(1, 2); XB_CASE(1, 8); XB_CASE(2, 8); XB_CASE(3, 8); XB_CASE(4, 8);
+#undef XB_CASE
     return mb_check_launch();
 }
 
 extern "C" int mb_cross_block_init(void) {
     int rc = 0;
     const int bytes = 225 * 1024;
-    rc |= (int)cudaFuncSetAttribute(k_cross_block<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    rc |= (int)cudaFuncSetAttribute(k_cross_block<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    rc |= (int)cudaFuncSetAttribute(k_cross_block<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    rc |= (int)cudaFuncSetAttribute(k_cross_block<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    rc |= (int)cudaFuncSetAttribute(k_cross_block<1, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    rc |= (int)cudaFuncSetAttribute(k_cross_block<1, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    rc |= (int)cudaFuncSetAttribute(k_cross_block<2, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    rc |= (int)cudaFuncSetAttribute(k_cross_block<3, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    rc |= (int)cudaFuncSetAttribute(k_cross_block<4, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     return rc;
 }
