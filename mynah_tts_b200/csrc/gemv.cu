@@ -62,18 +62,22 @@ __device__ __forceinline__ void store_out(const GemvP &p, float *out, long row, 
 __device__ __forceinline__ uint4 ldg16(const unsigned char *ptr) {
     return __ldg(reinterpret_cast<const uint4 *>(ptr));
 }
+// The same load, kept where the source puts it (the compiler may otherwise sink a read-only
+// load to its first use, behind the dependency wait).
+__device__ __forceinline__ uint4 ldg16_pinned(const unsigned char *ptr) {
+    uint4 v;
+    asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(ptr));
+    return v;
+}
 
 template <int QT, int BT, bool STRICT>
 __global__ void __launch_bounds__(WARPS * 32) k_gemv(GemvP p) {
-    mb_pdl_wait();
-    mb_pdl_trigger();
     extern __shared__ __align__(16) unsigned char smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const long grp = blockIdx.y;
     const unsigned char *w = p.w + grp * p.w_gs;
     const float *scales = p.scales == nullptr ? nullptr : p.scales + grp * p.scale_gs;
     float *out = p.out + grp * p.out_gs;
-    const int nb = p.n_active != nullptr ? min(p.batch, *p.n_active) : p.batch;
     const int LPR = p.lpr, CPL = p.cpl, RPW = 32 / LPR;
     const int sub = lane / LPR, li = lane % LPR;
     const long k = p.k;
@@ -84,6 +88,22 @@ __global__ void __launch_bounds__(WARPS * 32) k_gemv(GemvP p) {
 
     __shared__ float fuse_red[96];
     __shared__ float fuse_sx;
+    // Constants are requested before the dependency wait, so they land while the preceding
+    // launch finishes: this warp's first weight pieces (int8) and the fused norm's gain.
+    uint4 wpre[MAX_PRELOAD];
+    if (QT == MB_INT8) {
+        const long row0 = (((long)blockIdx.x * p.iters) * WARPS + warp) * RPW + sub;
+        const unsigned char *wrow0 = w + (row0 < p.n ? row0 : 0) * p.row_bytes;
+#pragma unroll
+        for (int u = 0; u < MAX_PRELOAD; ++u)
+            if (u < CPL) wpre[u] = ldg16_pinned(wrow0 + (long)(li + u * LPR) * 16);
+    }
+    float *fuse_gain_s = reinterpret_cast<float *>(smem + ((act_bytes + 15) & ~(long)15)) + k;
+    if (QT == MB_INT8 && BT == 1 && p.fuse == MB_FUSE_LN)
+        for (int i = threadIdx.x; i < k; i += blockDim.x) fuse_gain_s[i] = __ldg(p.fuse_gain + i);
+    mb_pdl_wait();
+    mb_pdl_trigger();
+    const int nb = p.n_active != nullptr ? min(p.batch, *p.n_active) : p.batch;
     // one batch tile per CTA (grid.z): tiles past the live lanes leave at once
     for (int b0 = blockIdx.z * BT; b0 < nb; b0 = nb) {
         // ---- stage the activation tile ------------------------------------
@@ -106,7 +126,7 @@ __global__ void __launch_bounds__(WARPS * 32) k_gemv(GemvP p) {
             }
             __syncthreads();
             const float sxv = p.fuse == MB_FUSE_LN
-                                  ? mb_ln_block<2>(rowf, (int)k, p.fuse_gain, nullptr, p.fuse_eps, fuse_red, nullptr, true,
+                                  ? mb_ln_block<2>(rowf, (int)k, fuse_gain_s, nullptr, p.fuse_eps, fuse_red, nullptr, true,
                                                 reinterpret_cast<int8_t *>(act))
                                   : mb_quant_block(rowf, (int)k, fuse_red, reinterpret_cast<int8_t *>(act));
             if (threadIdx.x == 0) fuse_sx = sxv;
@@ -164,8 +184,12 @@ __global__ void __launch_bounds__(WARPS * 32) k_gemv(GemvP p) {
                 for (int i0 = 0; i0 < CPL; i0 += MAX_PRELOAD) {
                     uint4 wv[MAX_PRELOAD];
 #pragma unroll
-                    for (int u = 0; u < MAX_PRELOAD; ++u)
-                        if (i0 + u < CPL) wv[u] = ldg16(wrow + (long)(li + (i0 + u) * LPR) * 16);
+                    for (int u = 0; u < MAX_PRELOAD; ++u) {
+                        if (i0 + u < CPL) {
+                            if (it == 0 && i0 == 0) wv[u] = wpre[u];
+                            else wv[u] = ldg16(wrow + (long)(li + (i0 + u) * LPR) * 16);
+                        }
+                    }
 #pragma unroll
                     for (int u = 0; u < MAX_PRELOAD; ++u) {
                         if (i0 + u < CPL) {
@@ -382,7 +406,7 @@ int launch_tiled(const GemvP &p, size_t groups, cudaStream_t s) {
     const bool quant = (QT == MB_INT8 || QT == MB_INT4);
     size_t smem = (size_t)BT * (quant ? p.k : p.k * 4);
     if (QT == MB_INT4) smem += (size_t)WARPS * 32 * p.cpl * BT * sizeof(float);
-    if (p.fuse != MB_FUSE_NONE) smem += 16u + (size_t)p.k * sizeof(float);
+    if (p.fuse != MB_FUSE_NONE) smem += 16u + 2u * (size_t)p.k * sizeof(float);   /* the f32 row and the gain */
     if (smem > 160u * 1024u) return (int)cudaErrorInvalidValue;
     mb_launch(k_gemv<QT, BT, STRICT>, dim3(blocks, (unsigned)groups, (unsigned)btiles), dim3(WARPS * 32), smem, s, q);
     return mb_check_launch();
