@@ -641,14 +641,11 @@ extern "C" int mb_attention(const mb_attn_args *a, mb_stream stream) {
     if (max_valid <= 0) return (int)cudaErrorInvalidValue;
     p.max_chunks = (int)chunks_for((size_t)max_valid);
     const size_t width = a->heads * a->head_width;
-    // heads per CTA (one warp each): all of them when many streams are stepped (whole cache
-    // rows per tile keep DRAM pages open), fewer when few streams must still fill the SMs
+    // heads per CTA (one warp each): all of them.  Whole cache rows per tile keep DRAM pages
+    // open, and one CTA per (stream, chunk subset) needs a single arrival counter per stream;
+    // head groups of 1 or 4 with more CTAs were measured slower at every batch size
+    // (one stream at position 256: 560 / 512 / 501 us per step for 1 / 4 / 12 heads per CTA).
     int hg = p.heads;
-    if (a->sm_count > 0 && p.heads <= 32) {
-        int want = p.batch >= 8 ? (p.heads + 2) / 3 : 1;
-        if (p.batch >= 32) want = p.heads;   // whole cache rows per tile (measured faster than half rows with a deeper ring)
-        for (hg = want < 1 ? 1 : want; hg < p.heads && p.heads % hg != 0; ++hg) {}
-    }
     int hpb = 0;   // heads per TMA box: a box holds whole heads and at most 256 columns
     for (int c = p.hw > 0 ? 256 / p.hw : 0; c >= 1 && hpb == 0; --c)
         if (c <= hg && hg % c == 0) hpb = c;
