@@ -23,6 +23,8 @@
 
 #include <cuda_fp16.h>
 
+#include <type_traits>
+
 namespace {
 
 constexpr int WARPS = 4;
@@ -70,7 +72,10 @@ __device__ __forceinline__ uint4 ldg16_pinned(const unsigned char *ptr) {
     return v;
 }
 
-template <int QT, int BT, bool STRICT>
+// EARLY (int8, one row group per warp): the first weight pieces are requested before the
+// dependency wait.  A kernel of its own: the extra registers would cost the streaming form
+// two resident CTAs per SM.
+template <int QT, int BT, bool STRICT, bool EARLY>
 __global__ void __launch_bounds__(WARPS * 32) k_gemv(GemvP p) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -91,7 +96,8 @@ __global__ void __launch_bounds__(WARPS * 32) k_gemv(GemvP p) {
     // Constants are requested before the dependency wait, so they land while the preceding
     // launch finishes: this warp's first weight pieces (int8) and the fused norm's gain.
     uint4 wpre[MAX_PRELOAD];
-    if (QT == MB_INT8) {
+    constexpr bool early_weights = EARLY && QT == MB_INT8;
+    if (early_weights) {
         const long row0 = (((long)blockIdx.x * p.iters) * WARPS + warp) * RPW + sub;
         const unsigned char *wrow0 = w + (row0 < p.n ? row0 : 0) * p.row_bytes;
 #pragma unroll
@@ -170,8 +176,10 @@ __global__ void __launch_bounds__(WARPS * 32) k_gemv(GemvP p) {
 
         // ---- dot products: a warp walks `iters` row groups; the unrolled loop keeps
         // the weight loads of two groups in flight -------------------------------
-#pragma unroll 2
-        for (int it = 0; it < p.iters; ++it) {
+        // PRE: the first weight pieces were requested before the dependency wait (a launch
+        // whose warps walk one row group each: latency bound; a streaming launch keeps the
+        // plain loop, whose loads of two groups overlap)
+        auto row_group = [&](int it, auto PRE) {
         const long wgroup = ((long)blockIdx.x * p.iters + it) * WARPS + warp;
         const long row = wgroup * RPW + sub;
         const bool row_ok = row < p.n;
@@ -186,7 +194,7 @@ __global__ void __launch_bounds__(WARPS * 32) k_gemv(GemvP p) {
 #pragma unroll
                     for (int u = 0; u < MAX_PRELOAD; ++u) {
                         if (i0 + u < CPL) {
-                            if (it == 0 && i0 == 0) wv[u] = wpre[u];
+                            if (decltype(PRE)::value && i0 == 0) wv[u] = wpre[u];
                             else wv[u] = ldg16(wrow + (long)(li + (i0 + u) * LPR) * 16);
                         }
                     }
@@ -336,7 +344,13 @@ __global__ void __launch_bounds__(WARPS * 32) k_gemv(GemvP p) {
                 }
             }
         }
-        }   // row groups
+        };   // row_group
+        if (early_weights) {
+            row_group(0, std::true_type{});   // the launcher gives this form iters == 1
+        } else {
+#pragma unroll 2
+            for (int it = 0; it < p.iters; ++it) row_group(it, std::false_type{});
+        }
     }
 }
 
@@ -408,7 +422,10 @@ int launch_tiled(const GemvP &p, size_t groups, cudaStream_t s) {
     if (QT == MB_INT4) smem += (size_t)WARPS * 32 * p.cpl * BT * sizeof(float);
     if (p.fuse != MB_FUSE_NONE) smem += 16u + 2u * (size_t)p.k * sizeof(float);   /* the f32 row and the gain */
     if (smem > 160u * 1024u) return (int)cudaErrorInvalidValue;
-    mb_launch(k_gemv<QT, BT, STRICT>, dim3(blocks, (unsigned)groups, (unsigned)btiles), dim3(WARPS * 32), smem, s, q);
+    if (QT == MB_INT8 && it == 1)
+        mb_launch(k_gemv<QT, BT, STRICT, QT == MB_INT8>, dim3(blocks, (unsigned)groups, (unsigned)btiles), dim3(WARPS * 32), smem, s, q);
+    else
+        mb_launch(k_gemv<QT, BT, STRICT, false>, dim3(blocks, (unsigned)groups, (unsigned)btiles), dim3(WARPS * 32), smem, s, q);
     return mb_check_launch();
 }
 
@@ -436,7 +453,10 @@ int set_attrs() {
     int rc = 0;
 #define MB_ATTR(BT, ST)                                                                         \
     if (rc == 0)                                                                                \
-        rc = (int)cudaFuncSetAttribute(k_gemv<QT, BT, ST>,                                      \
+        rc = (int)cudaFuncSetAttribute(k_gemv<QT, BT, ST, false>,                               \
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024); \
+    if (rc == 0 && QT == MB_INT8)                                                               \
+        rc = (int)cudaFuncSetAttribute(k_gemv<QT, BT, ST, QT == MB_INT8>,                       \
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024)
     MB_ATTR(1, false); MB_ATTR(2, false); MB_ATTR(4, false); MB_ATTR(8, false);
     MB_ATTR(1, true); MB_ATTR(2, true); MB_ATTR(4, true); MB_ATTR(8, true);
