@@ -425,8 +425,11 @@ def main():
     barrier()
     e2e_s = reduce_max(time.perf_counter() - t0, world)
     e2e_value = total_streams * frames * args.steps / e2e_s
-    h2d = frames * (B * shape.tables * 4 + 3 * B * 4 + 4)
-    d2h = frames * (B * shape.tables * 4)
+    # per frame the call copies one staging block in (slots, positions, EOS rule, EOS flags:
+    # 4 ints per lane of the decoder's batch capacity; 4 ints of lane count and frame index;
+    # the codes) and one block out (4 ints of status, the tokens)
+    h2d = frames * (4 * B * 4 + 16 + B * shape.tables * 4)
+    d2h = frames * (16 + B * shape.tables * 4)
 
     result = None
     if rank == 0:

@@ -77,6 +77,13 @@ typedef struct mb_decoder {
     float *h_rows, *h_out;
     int *h_lens, *h_slots, *h_ints, *h_table;
     unsigned *h_codes, *h_tokens;
+    /* One block on each side for everything a per-frame call stages (lane state, codes) and
+     * one for everything it reads back (status, tokens): a call is one copy in, one graph,
+     * one copy out.  d_slots .. d_codes, d_status, d_tokens and their h_ twins point into them. */
+    int *d_stage_in, *h_stage_in, *h_frame_idx;
+    unsigned *d_stage_out, *h_stage_out;
+    int *h_status;
+    size_t stage_in_ints;
     size_t *slot_len;           /* host mirror of every slot's length */
     mb_local local;             /* layers == 0: not attached */
     cudaGraphExec_t graph[MODE_COUNT][MAX_BUCKETS];
@@ -185,12 +192,10 @@ void mynah_b200_decoder_destroy(void *decoder) {
     void *dev[] = {d->position, d->norm_out, d->emb, (void *)d->d_tables, d->heads_b, d->self_k,
                    d->self_v, d->cross_k, d->cross_v, d->x, d->nrm, d->qkv, d->attn, d->q_x,
                    d->xctx, d->hidden, d->out, d->rows_in, d->logits, d->qx, d->sx, d->partials,
-                   d->counters, d->d_lens, d->d_slots, d->d_n_active, d->d_allow_eos,
-                   d->d_eos_flag, d->d_eos_frame, d->d_frame_idx, d->d_status, d->d_min_frames, d->d_codes,
-                   d->d_tokens, d->d_history};
+                   d->counters, d->d_stage_in, d->d_stage_out, d->d_eos_frame, d->d_min_frames,
+                   d->d_history};
     for (size_t i = 0; i < sizeof(dev) / sizeof(dev[0]); ++i) cudaFree(dev[i]);
-    void *pinned[] = {d->h_rows, d->h_out, d->h_lens, d->h_slots, d->h_ints, d->h_table,
-                      d->h_codes, d->h_tokens};
+    void *pinned[] = {d->h_rows, d->h_out, d->h_stage_in, d->h_stage_out, d->h_ints, d->h_table};
     for (size_t i = 0; i < sizeof(pinned) / sizeof(pinned[0]); ++i)
         if (pinned[i] != NULL) cudaFreeHost(pinned[i]);
     if (d->prof_ev != NULL) {
@@ -336,8 +341,6 @@ int mynah_b200_decoder_create(void *state, const mynah_b200_decoder_desc *desc, 
     D_TRY(dmalloc((void **)&d->sx, MB * sizeof(float), error, cap));
     if (d->tables != 0) {
         D_TRY(dmalloc((void **)&d->logits, MB * d->tables * d->vocab * sizeof(float), error, cap));
-        D_TRY(dmalloc((void **)&d->d_codes, MB * d->tables * sizeof(unsigned), error, cap));
-        D_TRY(dmalloc((void **)&d->d_tokens, MB * d->tables * sizeof(unsigned), error, cap));
         d->history_frames = d->capacity;
         D_TRY(dmalloc((void **)&d->d_history, d->history_frames * MB * d->tables * sizeof(unsigned), error, cap));
     }
@@ -358,32 +361,49 @@ int mynah_b200_decoder_create(void *state, const mynah_b200_decoder_desc *desc, 
     }
     D_TRY(dmalloc((void **)&d->partials, partial_floats * sizeof(float), error, cap));
     D_TRY(dmalloc((void **)&d->counters, n_counters * sizeof(unsigned), error, cap));
-    int **ints[] = {&d->d_lens, &d->d_slots, &d->d_allow_eos, &d->d_eos_flag, &d->d_eos_frame};
-    for (size_t i = 0; i < sizeof(ints) / sizeof(ints[0]); ++i)
-        D_TRY(dmalloc((void **)ints[i], MB * sizeof(int), error, cap));
-    D_TRY(dmalloc((void **)&d->d_n_active, sizeof(int), error, cap));
-    D_TRY(dmalloc((void **)&d->d_frame_idx, sizeof(int), error, cap));
-    D_TRY(dmalloc((void **)&d->d_status, sizeof(int), error, cap));
+    /* staged in: [slots MB | lens MB | allow_eos MB | eos_flag MB | n_active, frame_idx, 0, 0 | codes MB x tables];
+     * read back: [status, 0, 0, 0 | tokens MB x tables] */
+    d->stage_in_ints = 4u * MB + 4u + MB * d->tables;
+    D_TRY(dmalloc((void **)&d->d_stage_in, d->stage_in_ints * sizeof(int), error, cap));
+    D_TRY(dmalloc((void **)&d->d_stage_out, (4u + MB * d->tables) * sizeof(unsigned), error, cap));
+    D_TRY(dmalloc((void **)&d->d_eos_frame, MB * sizeof(int), error, cap));
+    if (ok) {
+        D_TRY(mb_cuda((int)cudaMemset(d->d_stage_in, 0, d->stage_in_ints * sizeof(int)), "memset", error, cap));
+        D_TRY(mb_cuda((int)cudaMemset(d->d_stage_out, 0, (4u + MB * d->tables) * sizeof(unsigned)), "memset", error, cap));
+        d->d_slots = d->d_stage_in;
+        d->d_lens = d->d_stage_in + MB;
+        d->d_allow_eos = d->d_stage_in + 2u * MB;
+        d->d_eos_flag = d->d_stage_in + 3u * MB;
+        d->d_n_active = d->d_stage_in + 4u * MB;
+        d->d_frame_idx = d->d_stage_in + 4u * MB + 1u;
+        d->d_codes = (unsigned *)(d->d_stage_in + 4u * MB + 4u);
+        d->d_status = (int *)d->d_stage_out;
+        d->d_tokens = d->d_stage_out + 4u;
+    }
     D_TRY(dmalloc((void **)&d->d_min_frames, sizeof(int), error, cap));
     if (ok) {
         D_TRY(mb_cuda((int)cudaMemset(d->counters, 0, n_counters * sizeof(unsigned)), "memset", error, cap));
-        D_TRY(mb_cuda((int)cudaMemset(d->d_status, 0, sizeof(int)), "memset", error, cap));
         D_TRY(mb_cuda((int)cudaMemset(d->d_min_frames, 0, sizeof(int)), "memset", error, cap));
-        D_TRY(mb_cuda((int)cudaMemset(d->d_eos_flag, 0, MB * sizeof(int)), "memset", error, cap));
         D_TRY(mb_cuda((int)cudaMemset(d->self_k, 0, self_n * sizeof(float)), "memset", error, cap));
         D_TRY(mb_cuda((int)cudaMemset(d->self_v, 0, self_n * sizeof(float)), "memset", error, cap));
     }
     /* pinned staging */
     D_TRY(mb_cuda((int)cudaMallocHost((void **)&d->h_rows, MB * W * sizeof(float)), "cudaMallocHost", error, cap));
     D_TRY(mb_cuda((int)cudaMallocHost((void **)&d->h_out, MB * W * sizeof(float)), "cudaMallocHost", error, cap));
-    D_TRY(mb_cuda((int)cudaMallocHost((void **)&d->h_lens, MB * sizeof(int)), "cudaMallocHost", error, cap));
-    D_TRY(mb_cuda((int)cudaMallocHost((void **)&d->h_slots, MB * sizeof(int)), "cudaMallocHost", error, cap));
+    D_TRY(mb_cuda((int)cudaMallocHost((void **)&d->h_stage_in, d->stage_in_ints * sizeof(int)), "cudaMallocHost", error, cap));
+    D_TRY(mb_cuda((int)cudaMallocHost((void **)&d->h_stage_out, (4u + MB * d->tables) * sizeof(unsigned)), "cudaMallocHost", error, cap));
+    if (ok) {
+        memset(d->h_stage_in, 0, d->stage_in_ints * sizeof(int));
+        memset(d->h_stage_out, 0, (4u + MB * d->tables) * sizeof(unsigned));
+        d->h_slots = d->h_stage_in;
+        d->h_lens = d->h_stage_in + MB;
+        d->h_frame_idx = d->h_stage_in + 4u * MB + 1u;
+        d->h_codes = (unsigned *)(d->h_stage_in + 4u * MB + 4u);
+        d->h_status = (int *)d->h_stage_out;
+        d->h_tokens = d->h_stage_out + 4u;
+    }
     D_TRY(mb_cuda((int)cudaMallocHost((void **)&d->h_ints, 4u * MB * sizeof(int)), "cudaMallocHost", error, cap));
     D_TRY(mb_cuda((int)cudaMallocHost((void **)&d->h_table, (MB + 1u) * sizeof(int)), "cudaMallocHost", error, cap));
-    if (d->tables != 0) {
-        D_TRY(mb_cuda((int)cudaMallocHost((void **)&d->h_codes, MB * d->tables * sizeof(unsigned)), "cudaMallocHost", error, cap));
-        D_TRY(mb_cuda((int)cudaMallocHost((void **)&d->h_tokens, MB * d->tables * sizeof(unsigned)), "cudaMallocHost", error, cap));
-    }
     D_TRY(mb_cuda((int)cudaEventCreate(&d->ev0), "cudaEventCreate", error, cap));
     D_TRY(mb_cuda((int)cudaEventCreate(&d->ev1), "cudaEventCreate", error, cap));
 #undef D_TRY
@@ -981,7 +1001,9 @@ int mynah_b200_decoder_set_layers(void *decoder, size_t n, char *error, size_t c
 
 /* ----------------------------------------------------------------- stepping */
 /* Validate the slot list and stage slot ids and positions for the lanes. */
-static int stage_lanes(mb_decoder *d, const unsigned *slots, size_t batch, char *error, size_t cap) {
+/* Validates the lanes of a call and writes their slots and positions to the pinned staging
+ * block (the caller copies them to the device). */
+static int fill_lanes(mb_decoder *d, const unsigned *slots, size_t batch, char *error, size_t cap) {
     if (d == NULL || slots == NULL || batch == 0 || batch > d->max_batch) {
         mb_set_error(error, cap, "decoder batch exceeds max_batch");   /* src/graph.c:3133-3136 */
         return -1;
@@ -1004,6 +1026,11 @@ static int stage_lanes(mb_decoder *d, const unsigned *slots, size_t batch, char 
         d->h_slots[b] = (int)slots[b];
         d->h_lens[b] = (int)d->slot_len[slots[b]];
     }
+    return 0;
+}
+
+static int stage_lanes(mb_decoder *d, const unsigned *slots, size_t batch, char *error, size_t cap) {
+    if (fill_lanes(d, slots, batch, error, cap) != 0) return -1;
     cudaStream_t s = d->st->stream;
     MB_TRY(cudaMemcpyAsync(d->d_slots, d->h_slots, batch * sizeof(int), cudaMemcpyHostToDevice, s), "stage slots");
     MB_TRY(cudaMemcpyAsync(d->d_lens, d->h_lens, batch * sizeof(int), cudaMemcpyHostToDevice, s), "stage positions");
@@ -1056,23 +1083,31 @@ int mynah_b200_decoder_frame_batch(void *decoder, const unsigned *slots, const u
         mb_set_error(error, cap, "decoder has no embedding tables or heads");
         return -1;
     }
-    if (stage_lanes(d, slots, batch, error, cap) != 0) return -1;
-    const size_t nt = batch * d->tables;
+    if (fill_lanes(d, slots, batch, error, cap) != 0) return -1;
+    const size_t nt = batch * d->tables, MB = d->max_batch;
     cudaStream_t s = d->st->stream;
+    /* One copy in: slots and positions (fill_lanes), the EOS rule, cleared EOS flags, the lane
+     * count, frame index 0 (history row 0 is scratch for this entry point; the allow_eos
+     * flags written by frame_advance are restaged on every call) and the codes.  Lanes past
+     * `batch` carry what the block held before: every kernel masks them by the lane count. */
+    int *in = d->h_stage_in;
+    for (size_t b = 0; b < batch; ++b) {
+        in[2u * MB + b] = allow_eos == NULL ? 1 : (allow_eos[b] != 0);
+        in[3u * MB + b] = 0;
+    }
+    in[4u * MB] = (int)batch;
+    in[4u * MB + 1u] = 0;
     memcpy(d->h_codes, codes, nt * sizeof(unsigned));
-    for (size_t b = 0; b < batch; ++b) d->h_ints[b] = allow_eos == NULL ? 1 : (allow_eos[b] != 0);
-    MB_TRY(cudaMemcpyAsync(d->d_codes, d->h_codes, nt * sizeof(unsigned), cudaMemcpyHostToDevice, s), "stage codes");
-    MB_TRY(cudaMemcpyAsync(d->d_allow_eos, d->h_ints, batch * sizeof(int), cudaMemcpyHostToDevice, s), "stage eos rule");
-    MB_TRY(cudaMemsetAsync(d->d_eos_flag, 0, batch * sizeof(int), s), "clear eos flags");
-    /* history row 0 is scratch for this entry point; the allow_eos flags written
-     * by frame_advance are restaged on every call */
-    MB_TRY(cudaMemsetAsync(d->d_frame_idx, 0, sizeof(int), s), "clear frame index");
+    MB_TRY(cudaMemcpyAsync(d->d_stage_in, d->h_stage_in, (4u * MB + 4u + nt) * sizeof(int), cudaMemcpyHostToDevice, s),
+           "stage the frame");
     if (run(d, batch, MODE_FRAME, error, cap) != 0) return -1;
-    MB_TRY(cudaMemcpyAsync(d->h_tokens, d->d_tokens, nt * sizeof(unsigned), cudaMemcpyDeviceToHost, s), "read tokens");
+    /* one copy out: the status word and the tokens */
+    MB_TRY(cudaMemcpyAsync(d->h_stage_out, d->d_stage_out, (4u + nt) * sizeof(unsigned), cudaMemcpyDeviceToHost, s),
+           "read tokens");
     if (hidden != NULL)
         MB_TRY(cudaMemcpyAsync(d->h_out, d->out, batch * d->width * sizeof(float), cudaMemcpyDeviceToHost, s), "read hidden");
     MB_TRY(cudaStreamSynchronize(s), "cudaStreamSynchronize");
-    if (check_status(d, error, cap) != 0) return -1;
+    if (*d->h_status != 0 && check_status(d, error, cap) != 0) return -1;
     memcpy(tokens, d->h_tokens, nt * sizeof(unsigned));
     if (hidden != NULL) memcpy(hidden, d->h_out, batch * d->width * sizeof(float));
     for (size_t b = 0; b < batch; ++b) d->slot_len[slots[b]] += 1u;
