@@ -202,6 +202,16 @@ static inline int mb_check_launch() { return (int)cudaGetLastError(); }
 __device__ __forceinline__ void mb_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void mb_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// The live-lane count of a step.  No kernel writes it (the host stages it before the step's
+// first launch), so it may be read before mb_pdl_wait(); the load is volatile asm so that it
+// stays there, off the chain of dependent round trips behind the wait.
+__device__ __forceinline__ int mb_lane_count(const int *n_active) {
+    if (n_active == nullptr) return 0x7fffffff;
+    int v;
+    asm volatile("ld.global.cg.b32 %0, [%1];" : "=r"(v) : "l"(n_active));
+    return v;
+}
+
 extern "C" int mb_pdl_enabled(void);   // glue.cu: MYNAH_B200_PDL, default on
 
 template <typename... KArgs, typename... Args>

@@ -215,9 +215,9 @@ k_gemm_i8_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
             tma_load_2d(As + (size_t)c * A_BYTES, &map_w, (c_first + c) * KC, (int)m0, &full_bar[c]);
         }
     }
+    const int nb = min(p.batch, mb_lane_count(p.n_active));
     mb_pdl_wait();
     mb_pdl_trigger();
-    const int nb = p.n_active != nullptr ? min(p.batch, *p.n_active) : p.batch;
     if (b0 >= nb) {
         // no live lane in this tile: let the requested weight stages land (the activation
         // halves are sent too, so each barrier completes), then give the TMEM back

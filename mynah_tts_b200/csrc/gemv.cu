@@ -107,9 +107,9 @@ __global__ void __launch_bounds__(WARPS * 32) k_gemv(GemvP p) {
     float *fuse_gain_s = reinterpret_cast<float *>(smem + ((act_bytes + 15) & ~(long)15)) + k;
     if (QT == MB_INT8 && BT == 1 && p.fuse == MB_FUSE_LN)
         for (int i = threadIdx.x; i < k; i += blockDim.x) fuse_gain_s[i] = __ldg(p.fuse_gain + i);
+    const int nb = min(p.batch, mb_lane_count(p.n_active));
     mb_pdl_wait();
     mb_pdl_trigger();
-    const int nb = p.n_active != nullptr ? min(p.batch, *p.n_active) : p.batch;
     // one batch tile per CTA (grid.z): tiles past the live lanes leave at once
     for (int b0 = blockIdx.z * BT; b0 < nb; b0 = nb) {
         // ---- stage the activation tile ------------------------------------

@@ -34,10 +34,11 @@ k_layernorm(const float *__restrict__ in, float *__restrict__ out, const float *
             if (bias != nullptr) bs[i] = __ldg(bias + i);
         }
     }
+    const int live = mb_lane_count(n_active);
     mb_pdl_wait();
     mb_pdl_trigger();
     const int r = blockIdx.x;
-    if (n_active != nullptr && r >= *n_active) return;
+    if (r >= live) return;
     const float *x = in + (size_t)r * width;
     for (int i = threadIdx.x; i < width; i += blockDim.x) row[i] = x[i];
     __syncthreads();
@@ -106,11 +107,12 @@ k_layernorm(const float *__restrict__ in, float *__restrict__ out, const float *
 __global__ void __launch_bounds__(256)
 k_quant_rows(const float *__restrict__ in, int width, int8_t *__restrict__ qx,
              float *__restrict__ sx, const int *__restrict__ n_active) {
+    const int live = mb_lane_count(n_active);
     mb_pdl_wait();
     mb_pdl_trigger();
     __shared__ float red[33];
     const int r = blockIdx.x;
-    if (n_active != nullptr && r >= *n_active) return;
+    if (r >= live) return;
     const float *x = in + (size_t)r * width;
     constexpr int VMAX = 4;                            // float4s a thread keeps in registers
     if ((width & 3) == 0 && width <= 4 * VMAX * (int)blockDim.x && (reinterpret_cast<uintptr_t>(in) & 15u) == 0 &&
