@@ -216,6 +216,8 @@ k_gemm_i8_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
         }
     }
     const int nb = min(p.batch, mb_lane_count(p.n_active));
+    // the activation map is first used behind the wait: its descriptor is fetched now
+    if (warp == 0 && lane == 0) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
     mb_pdl_wait();
     mb_pdl_trigger();
     if (b0 >= nb) {

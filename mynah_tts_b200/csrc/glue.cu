@@ -266,18 +266,56 @@ k_embed_frames(const float *const *__restrict__ tables, int n_tables, int vocab,
     const int b = blockIdx.x;
     if (n_active != nullptr && b >= *n_active) return;
     const float *pe = position + (size_t)lens[b] * width;
-    for (int d = threadIdx.x; d < width; d += blockDim.x) {
-        float row = 0.0f;
-        for (int t = 0; t < n_tables; ++t) {
-            unsigned code = codes[(size_t)b * n_tables + t];
-            if (code >= (unsigned)vocab) {
-                if (status != nullptr) atomicOr(status, 1);
-                code = 0;
+    // codes and table bases of up to ET tables at a time, all fetched before any row: the
+    // three loads behind each table row (code, base, row) otherwise run one after another
+    constexpr int ET = 8;
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};          // this thread's elements d, d + 256, ...
+    const int per_thread = (width + (int)blockDim.x - 1) / (int)blockDim.x;
+    if (per_thread > 4) {                             // wide rows: the plain loop
+        for (int d = threadIdx.x; d < width; d += blockDim.x) {
+            float row = 0.0f;
+            for (int t = 0; t < n_tables; ++t) {
+                unsigned code = codes[(size_t)b * n_tables + t];
+                if (code >= (unsigned)vocab) {
+                    if (status != nullptr) atomicOr(status, 1);
+                    code = 0;
+                }
+                row = __fadd_rn(row, tables[t][(size_t)code * width + d]);
             }
-            row = __fadd_rn(row, tables[t][(size_t)code * width + d]);
+            row = __fdiv_rn(row, (float)n_tables);
+            x[(size_t)b * width + d] = __fadd_rn(row, pe[d]);
         }
-        row = __fdiv_rn(row, (float)n_tables);
-        x[(size_t)b * width + d] = __fadd_rn(row, pe[d]);
+        return;
+    }
+    bool bad = false;
+    for (int t0 = 0; t0 < n_tables; t0 += ET) {
+        const float *base[ET];
+#pragma unroll
+        for (int u = 0; u < ET; ++u) {
+            const int t = t0 + u;
+            unsigned code = t < n_tables ? codes[(size_t)b * n_tables + t] : 0u;
+            if (code >= (unsigned)vocab) { bad = true; code = 0u; }
+            base[u] = t < n_tables ? tables[t] + (size_t)code * width : nullptr;
+        }
+        float v[ET][4];
+#pragma unroll
+        for (int u = 0; u < ET; ++u)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int d = threadIdx.x + j * blockDim.x;
+                v[u][j] = (t0 + u < n_tables && d < width) ? base[u][d] : 0.0f;
+            }
+#pragma unroll
+        for (int u = 0; u < ET; ++u)
+            if (t0 + u < n_tables)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[j] = __fadd_rn(acc[j], v[u][j]);   // table order
+    }
+    if (bad && threadIdx.x == 0 && status != nullptr) atomicOr(status, 1);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int d = threadIdx.x + j * blockDim.x;
+        if (d < width) x[(size_t)b * width + d] = __fadd_rn(__fdiv_rn(acc[j], (float)n_tables), pe[d]);
     }
 }
 
