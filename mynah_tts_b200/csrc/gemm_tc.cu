@@ -162,7 +162,10 @@ __device__ __forceinline__ bool bar_wait_cluster(void *bar, unsigned parity, uns
     return false;
 }
 
-template <bool SPLIT>
+// NS = stages of the ring (compile time: a run-time count was measured 30 us per step slower).
+// Six stages (109 KB) hold all of k = 768 and let two CTAs share an SM: used for grids of
+// more CTAs than SMs (the 512-CTA logit-head product), where it halves the waves.
+template <bool SPLIT, int NS = MAX_STAGES>
 __global__ void __launch_bounds__(TC_THREADS)
 k_gemm_i8_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcP p) {
     extern __shared__ unsigned char smem_raw[];
@@ -183,7 +186,7 @@ k_gemm_i8_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
     // operands need 1024-byte alignment for the 128-byte swizzle
     unsigned char *base = smem_raw + ((1024u - (saddr(smem_raw) & 1023u)) & 1023u);
     unsigned char *As = base;                               // [stage][128 rows][128 B]
-    unsigned char *Bs = base + (size_t)MAX_STAGES * A_BYTES; // [stage][BN rows][128 B]
+    unsigned char *Bs = base + (size_t)NS * A_BYTES; // [stage][BN rows][128 B]
     if (threadIdx.x == 0) {
         for (int s = 0; s < MAX_STAGES; ++s) {
             bar_init(&full_bar[s], 1u);
@@ -208,7 +211,7 @@ k_gemm_i8_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
     // Weights do not depend on the launches before this one: their first stages are
     // requested before the dependency wait, so they land while the predecessor finishes.
     const unsigned stage_bytes = (unsigned)(A_BYTES + B_BYTES);
-    const int first = min(nchunks, MAX_STAGES);             // stages that need no release to fill
+    const int first = min(nchunks, NS);             // stages that need no release to fill
     if (warp == 0 && lane == 0) {
         for (int c = 0; c < first; ++c) {
             bar_expect(&full_bar[c], stage_bytes);
@@ -240,8 +243,8 @@ k_gemm_i8_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
         // chunk c goes to stage c % 8 once the MMAs of chunk c - 8 released it
         for (int c = 0; c < first; ++c) tma_load_2d(Bs + (size_t)c * B_BYTES, &map_x, (c_first + c) * KC, b0, &full_bar[c]);
         for (int c = first; c < nchunks; ++c) {
-            const int s = c % MAX_STAGES;
-            if (!bar_wait(&empty_bar[s], (unsigned)((c / MAX_STAGES - 1) & 1), TC_SPIN)) {
+            const int s = c % NS;
+            if (!bar_wait(&empty_bar[s], (unsigned)((c / NS - 1) & 1), TC_SPIN)) {
                 s_fail = 1u;
                 if (p.status != nullptr) atomicOr(p.status, 8);
                 break;
@@ -253,8 +256,8 @@ k_gemm_i8_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
     } else if (warp == 1 && lane == 0) {
         const uint32_t idesc = instr_desc_i8(TM, BN);
         for (int c = 0; c < nchunks; ++c) {
-            const int s = c % MAX_STAGES;
-            if (!bar_wait(&full_bar[s], (unsigned)((c / MAX_STAGES) & 1), TC_SPIN)) {
+            const int s = c % NS;
+            if (!bar_wait(&full_bar[s], (unsigned)((c / NS) & 1), TC_SPIN)) {
                 s_fail = 1u;
                 if (p.status != nullptr) atomicOr(p.status, 8);
                 break;
@@ -292,7 +295,7 @@ k_gemm_i8_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
         // a wait ran out: give copies still in flight one more bounded chance to land
         // before this CTA's shared memory is released
         if (threadIdx.x == 0)
-            for (int s = 0; s < MAX_STAGES && s < nchunks; ++s) bar_wait(&full_bar[s], 0u, TC_SPIN >> 4);
+            for (int s = 0; s < NS && s < nchunks; ++s) bar_wait(&full_bar[s], 0u, TC_SPIN >> 4);
         if (SPLIT && ks != 0) remote_arrive(remote_saddr(&part_bar, 0u));   // rank 0 need not wait for the limit
     } else {
         int v[16];
@@ -300,7 +303,7 @@ k_gemm_i8_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
         bool whole = true;                                   // v holds the sum over all of K
         if (SPLIT) {
             // partial sums of ranks 1.. in rank 0's shared memory: [rank - 1][lane j][weight row]
-            int *parts = reinterpret_cast<int *>(Bs + (size_t)MAX_STAGES * B_BYTES);
+            int *parts = reinterpret_cast<int *>(Bs + (size_t)NS * B_BYTES);
             if (ks != 0) {
                 const unsigned dst = remote_saddr(parts + ((size_t)(ks - 1) * BN) * TM + threadIdx.x, 0u);
 #pragma unroll
@@ -577,6 +580,7 @@ static int mb_gemm_tc_split_enabled() {
 
 extern "C" int mb_gemm_tc_init(void) {
     int rc = (int)cudaFuncSetAttribute(k_gemm_i8_tc<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM);
+    if (rc == 0) rc = (int)cudaFuncSetAttribute(k_gemm_i8_tc<false, 6>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM);
     if (rc == 0) rc = (int)cudaFuncSetAttribute(k_gemm_i8_tc<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_SPLIT);
     if (rc == 0) rc = (int)cudaFuncSetAttribute(k_gemm_i4_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC4_SMEM);
     return rc;
@@ -644,7 +648,11 @@ extern "C" int mb_gemm_tc(const mb_gemv_args *a, size_t qx_rows_alloc, int *stat
             const int rc = (int)cudaLaunchKernelEx(&cfg, k_gemm_i8_tc<true>, map_w, map_x, p);
             return rc != 0 ? rc : mb_check_launch();
         }
-        mb_launch(k_gemm_i8_tc<false>, dim3(dim3(m_tiles, b_tiles)), dim3(TC_THREADS), TC_SMEM, (cudaStream_t)stream, map_w, map_x, p);
+        if (m_tiles * b_tiles > 148u && chunks <= 6u)
+            mb_launch(k_gemm_i8_tc<false, 6>, dim3(dim3(m_tiles, b_tiles)), dim3(TC_THREADS),
+                      (size_t)6 * (A_BYTES + B_BYTES) + 1024, (cudaStream_t)stream, map_w, map_x, p);
+        else
+            mb_launch(k_gemm_i8_tc<false>, dim3(dim3(m_tiles, b_tiles)), dim3(TC_THREADS), TC_SMEM, (cudaStream_t)stream, map_w, map_x, p);
     }
     return mb_check_launch();
 }
