@@ -509,8 +509,10 @@ static int enqueue_local(mb_decoder *d, const float *first_rows, size_t nb, unsi
     int rc = 0;
 #define L_TRY(expr) do { if (rc == 0) rc = (expr); } while (0)
     for (size_t t = 0; t < d->tables && rc == 0; ++t) {
-        L_TRY(mb_add_row(t == 0 ? first_rows : lt->row_in, lt->position + t * W, d->x, nb, W, d->d_n_active, s));
-        *count += 1u;
+        if (t == 0) {   /* later positions: the sampler of the table before wrote x = token row + position row */
+            L_TRY(mb_add_row(first_rows, lt->position, d->x, nb, W, d->d_n_active, s));
+            *count += 1u;
+        }
         for (size_t l = 0; l < lt->layers && rc == 0; ++l) {
             const local_layer *L = &lt->L[l];
             const int f1 = fuse_one_lane(d, nb) && L->qkv.qtype == MB_INT8 && L->ffn_up.qtype == MB_INT8 &&
@@ -602,6 +604,8 @@ static int enqueue_local(mb_decoder *d, const float *first_rows, size_t nb, unsi
         sa.eos_sub = lt->d_eos_sub;
         sa.emb_table = d->emb + t * d->vocab * W;
         sa.row_in = lt->row_in;
+        sa.next_row = t + 1u < d->tables ? lt->position + (t + 1u) * W : NULL;
+        sa.x_out = d->x;
         sa.width = W;
         sa.strict = st->strict;
         sa.exp_tab = st->libm.exp_tab;

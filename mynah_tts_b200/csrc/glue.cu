@@ -351,8 +351,10 @@ k_add_row(const float *__restrict__ rows, const float *__restrict__ row, float *
 //     -FLT_MAX;
 //   * greedy pick: largest logit, first index on ties;
 //   * when temperature > 0 and topk > 1: the top-k in the reference's insertion order
-//     (higher logit first, earlier index first among equals) is produced by a bitonic sort
-//     of (logit, index) keys; weights exp((l - max) / T) are summed in that order by one
+//     (higher logit first, earlier index first among equals) is produced by sorting
+//     (logit, index) keys: for k <= 128 and 1024..4096 keys each warp sorts its share in
+//     registers and three rounds of pairwise merges keep the 128 largest (block_top128);
+//     otherwise a bitonic sort of all keys in shared memory; weights exp((l - max) / T) are summed in that order by one
 //     thread, the lane's xorshift64 state advances once, and the drawn token is the first
 //     whose running sum reaches draw = (top 24 bits / 2^24) * total (the last one if none);
 //   * EOS is reported if the greedy or the drawn token is EOS; the stored code collapses
@@ -367,6 +369,92 @@ __device__ __forceinline__ float from_ordered_bits(unsigned o) {
     return __uint_as_float((o & 0x80000000u) ? (o & 0x7fffffffu) : ~o);
 }
 
+// ---- top 128 of the sampler's keys without block-wide sorting steps
+// Bitonic sort of 32 * R keys held by one warp, largest first: element e = r * 32 + lane is
+// register r of lane `lane`.  Strides of 32 and more exchange registers of one lane, smaller
+// strides exchange lanes by shuffle; no shared memory, no barrier.
+template <int R>
+__device__ __forceinline__ void warp_sort_desc(unsigned long long (&v)[R], int lane) {
+#pragma unroll
+    for (int size = 2; size <= 32 * R; size <<= 1) {
+#pragma unroll
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            if (stride >= 32) {
+                const int rs = stride >> 5;
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    if ((r & rs) == 0) {
+                        const bool desc = (((r * 32 + lane) & size) == 0);
+                        const unsigned long long a = v[r], c = v[r | rs];
+                        if ((a < c) == desc) { v[r] = c; v[r | rs] = a; }
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    const unsigned long long other = __shfl_xor_sync(MB_FULL, v[r], stride);
+                    const bool desc = (((r * 32 + lane) & size) == 0);
+                    const bool keep_max = (((lane & stride) == 0) == desc);
+                    v[r] = keep_max ? (v[r] > other ? v[r] : other) : (v[r] < other ? v[r] : other);
+                }
+            }
+        }
+    }
+}
+
+// Two lists of 128 keys sorted largest first -> the 128 largest of both, sorted, by one warp:
+// max(A[e], B[127 - e]) is a bitonic sequence holding them; seven merge steps sort it.
+__device__ __forceinline__ void warp_merge_top128(const unsigned long long *A, const unsigned long long *B,
+                                                  unsigned long long *out, int lane) {
+    unsigned long long v[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const int e = r * 32 + lane;
+        const unsigned long long a = A[e], c = B[127 - e];
+        v[r] = a > c ? a : c;
+    }
+    __syncwarp();                                            // `out` may be A: all reads are done
+#pragma unroll
+    for (int rs = 2; rs >= 1; rs >>= 1)
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+            if ((r & rs) == 0) {
+                const unsigned long long a = v[r], c = v[r | rs];
+                if (a < c) { v[r] = c; v[r | rs] = a; }
+            }
+#pragma unroll
+    for (int stride = 16; stride > 0; stride >>= 1)
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const unsigned long long other = __shfl_xor_sync(MB_FULL, v[r], stride);
+            v[r] = ((lane & stride) == 0) ? (v[r] > other ? v[r] : other) : (v[r] < other ? v[r] : other);
+        }
+#pragma unroll
+    for (int r = 0; r < 4; ++r) out[r * 32 + lane] = v[r];
+}
+
+// keys[0 .. 256 * R) (256 threads, R keys each) -> keys[0 .. 128) = the 128 largest, sorted.
+// Each of the eight warps sorts its 32 * R keys in registers and keeps 128; three rounds of
+// pairwise merges (four, two, one warp) leave the result in place.
+template <int R>
+__device__ __forceinline__ void block_top128(unsigned long long *keys) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    unsigned long long v[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) v[r] = keys[r * 256 + threadIdx.x];
+    __syncthreads();
+    warp_sort_desc<R>(v, lane);
+#pragma unroll
+    for (int r = 0; r < 4; ++r) keys[warp * 128 + r * 32 + lane] = v[r];
+    __syncthreads();
+    if (warp < 4) warp_merge_top128(keys + 256 * warp, keys + 256 * warp + 128, keys + 256 * warp, lane);
+    __syncthreads();
+    if (warp < 2) warp_merge_top128(keys + 512 * warp, keys + 512 * warp + 256, keys + 512 * warp, lane);
+    __syncthreads();
+    if (warp == 0) warp_merge_top128(keys, keys + 512, keys, lane);
+    __syncthreads();
+}
+
 template <bool STRICT>
 __global__ void __launch_bounds__(256)
 k_local_sample(const float *__restrict__ logits, int ld, int vocab, int n2, int codebook_size, int eos_id,
@@ -374,7 +462,8 @@ k_local_sample(const float *__restrict__ logits, int ld, int vocab, int n2, int 
                const unsigned *__restrict__ topk, unsigned long long *__restrict__ rng, int table, int tables,
                int codebooks, unsigned *__restrict__ tokens, unsigned *__restrict__ codes,
                int *__restrict__ eos_flag, int *__restrict__ eos_sub, const float *__restrict__ emb_table,
-               float *__restrict__ row_in, int width, const uint32_t *__restrict__ exp_tab,
+               float *__restrict__ row_in, const float *__restrict__ next_row, float *__restrict__ x_out, int width,
+               const uint32_t *__restrict__ exp_tab,
                const int *__restrict__ n_active) {
     mb_pdl_wait();
     mb_pdl_trigger();
@@ -412,7 +501,12 @@ k_local_sample(const float *__restrict__ logits, int ld, int vocab, int n2, int 
     }
     if ((threadIdx.x & 31) == 0) { s_best[threadIdx.x >> 5] = best; s_idx[threadIdx.x >> 5] = best_i; }
     __syncthreads();
-    if (sampling) {
+    if (sampling && k <= 128u && blockDim.x == 256 && (n2 == 1024 || n2 == 2048 || n2 == 4096)) {
+        // only the first k keys are read below: the 128 largest, sorted, are enough
+        if (n2 == 1024) block_top128<4>(keys);
+        else if (n2 == 2048) block_top128<8>(keys);
+        else block_top128<16>(keys);
+    } else if (sampling) {
         for (int size = 2; size <= n2; size <<= 1)
             for (int stride = size >> 1; stride > 0; stride >>= 1) {
                 for (int i = threadIdx.x; i < (n2 >> 1); i += blockDim.x) {
@@ -423,6 +517,8 @@ k_local_sample(const float *__restrict__ logits, int ld, int vocab, int n2, int 
                 }
                 __syncthreads();
             }
+    }
+    if (sampling) {
         const int used = (int)min(k, (unsigned)vocab);
         const float maximum = from_ordered_bits((unsigned)(keys[0] >> 32));
         for (int q = threadIdx.x; q < used; q += blockDim.x) {
@@ -469,7 +565,11 @@ k_local_sample(const float *__restrict__ logits, int ld, int vocab, int n2, int 
     }
     __syncthreads();
     const float *e = emb_table + (size_t)s_emit * width;
-    for (int d = threadIdx.x; d < width; d += blockDim.x) row_in[(size_t)b * width + d] = e[d];
+    for (int d = threadIdx.x; d < width; d += blockDim.x) {
+        const float v = e[d];
+        row_in[(size_t)b * width + d] = v;
+        if (x_out != nullptr) x_out[(size_t)b * width + d] = __fadd_rn(v, next_row[d]);
+    }
 }
 
 __global__ void k_advance_lens(int *lens, int batch, const int *n_active) {
@@ -628,12 +728,14 @@ extern "C" int mb_local_sample(const mb_sample_args *a, mb_stream stream) {
         mb_launch(k_local_sample<true>, dim3((unsigned)a->batch), dim3(256), smem, s, a->logits, (int)a->logits_stride,
                   (int)a->vocab, (int)n2, (int)a->codebook_size, (int)a->eos_id, a->allow_eos, a->temperature, a->topk,
                   a->rng, (int)a->table, (int)a->tables, (int)a->codebooks, a->tokens, a->codes, a->eos_flag,
-                  a->eos_sub, a->emb_table, a->row_in, (int)a->width, a->exp_tab, a->n_active);
+                  a->eos_sub, a->emb_table, a->row_in, a->next_row, a->next_row == nullptr ? nullptr : a->x_out, (int)a->width,
+                  a->exp_tab, a->n_active);
     else
         mb_launch(k_local_sample<false>, dim3((unsigned)a->batch), dim3(256), smem, s, a->logits, (int)a->logits_stride,
                   (int)a->vocab, (int)n2, (int)a->codebook_size, (int)a->eos_id, a->allow_eos, a->temperature, a->topk,
                   a->rng, (int)a->table, (int)a->tables, (int)a->codebooks, a->tokens, a->codes, a->eos_flag,
-                  a->eos_sub, a->emb_table, a->row_in, (int)a->width, a->exp_tab, a->n_active);
+                  a->eos_sub, a->emb_table, a->row_in, a->next_row, a->next_row == nullptr ? nullptr : a->x_out, (int)a->width,
+                  a->exp_tab, a->n_active);
     return mb_check_launch();
 }
 

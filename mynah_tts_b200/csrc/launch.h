@@ -99,6 +99,8 @@ typedef struct {
     int *eos_sub;             /* [batch] min(table / codebooks) over EOS tables, or NULL */
     const float *emb_table;   /* [vocab][width]: audio_embeddings.<table>.weight */
     float *row_in;            /* [batch][width] */
+    const float *next_row;    /* [width] or NULL: the next position's embedding row ... */
+    float *x_out;             /* ... added to the fed-back row into x_out[batch][width] (mb_add_row's sum) */
     size_t width;
     int strict;
     const uint32_t *exp_tab;  /* strict: host-libm expf correction table or NULL */
