@@ -536,8 +536,17 @@ k_local_sample(const float *__restrict__ logits, int ld, int vocab, int n2, int 
         unsigned value = argmax;
         if (sampling) {
             const int used = (int)min(k, (unsigned)vocab);
+            // sequential sums in list order (the reference's), sixteen weights fetched at a
+            // time so that the chain is the additions, not a shared-memory load per step
             float total = 0.0f;
-            for (int q = 0; q < used; ++q) total = __fadd_rn(total, weights[q]);
+            for (int q0 = 0; q0 < used; q0 += 16) {
+                float w[16];
+#pragma unroll
+                for (int u = 0; u < 16; ++u) w[u] = q0 + u < used ? weights[q0 + u] : 0.0f;
+#pragma unroll
+                for (int u = 0; u < 16; ++u)
+                    if (q0 + u < used) total = __fadd_rn(total, w[u]);
+            }
             unsigned long long state = rng[b];
             state ^= state << 13;
             state ^= state >> 7;
@@ -546,13 +555,20 @@ k_local_sample(const float *__restrict__ logits, int ld, int vocab, int n2, int 
             rng[b] = state;
             const float draw = __fmul_rn(__fdiv_rn((float)((state >> 40) & 0xffffffull), 16777216.0f), total);
             float cumulative = 0.0f;
-            for (int q = 0; q < used; ++q) {
-                cumulative = __fadd_rn(cumulative, weights[q]);
-                if (draw <= cumulative || q + 1 == used) {
-                    value = 0xffffffffu - (unsigned)(keys[q] & 0xffffffffull);
-                    break;
+            int pick = used - 1;                             // the last one if no running sum reaches the draw
+            for (int q0 = 0; q0 < used && pick == used - 1; q0 += 16) {
+                float w[16];
+#pragma unroll
+                for (int u = 0; u < 16; ++u) w[u] = q0 + u < used ? weights[q0 + u] : 0.0f;
+#pragma unroll
+                for (int u = 0; u < 16; ++u) {
+                    if (q0 + u < used && pick == used - 1) {
+                        cumulative = __fadd_rn(cumulative, w[u]);
+                        if (draw <= cumulative) pick = q0 + u;
+                    }
                 }
             }
+            value = 0xffffffffu - (unsigned)(keys[pick] & 0xffffffffull);
         }
         const bool eos = argmax == (unsigned)eos_id || value == (unsigned)eos_id;
         if (eos) {
