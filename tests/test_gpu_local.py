@@ -142,6 +142,41 @@ def test_full_size_generation_matches_reference_fixture(gl):
     dec.close(); be.close()
 
 
+def test_full_size_top_k_with_tied_logits_matches_port():
+    """The sampler's top-k on 2048 candidates (register-resident warp sorts and top-128
+    merges) against the CPU port, strict, with exact ties among the logits: half of every
+    table's projection rows are copies of other rows, so equal logits sit inside and at the
+    edge of the top k and the earlier index has to win.  k = 2, 40, 80, 128 take the
+    merge path, k = 200 the block-wide sort."""
+    import copy
+    shape = synth.MAGPIE_357M_LOCAL
+    model = copy.copy(synth.make_model(shape, seed=33))
+    model.tensors = dict(model.tensors)
+    rng = np.random.default_rng(5)
+    for t in range(shape.tables):
+        w = model.tensors[f"local_transformer_out_projections.{t}.weight"].copy()
+        b = model.tensors[f"local_transformer_out_projections.{t}.bias"].copy()
+        src = rng.permutation(shape.codebook_size)[:1000]
+        dst = rng.permutation(shape.codebook_size)[:1000]
+        w[dst] = w[src]
+        b[dst] = b[src]
+        model.tensors[f"local_transformer_out_projections.{t}.weight"] = w
+        model.tensors[f"local_transformer_out_projections.{t}.bias"] = b
+    rows = rng.normal(0, 1, size=(5, shape.width)).astype(np.float32)
+    lanes = [(0.7, 80, 11, 1), (1.0, 128, 12, 1), (0.5, 40, 13, 0), (1.3, 200, 14, 1), (0.9, 2, 15, 1)]
+    be, dec = make("int8", model, strict=True, slots=5, capacity=8)
+    codes, values, saw, eos, states = dec.local_frame(rows, lanes)
+    pm = O.PortModel(model, O.INT8)
+    pl = O.PortLocal(pm, 256)         # room for the largest top-k of the lanes
+    for b in range(5):
+        c, v, s_, e, r = pl.frame(rows[b], *lanes[b][:3], bool(lanes[b][3]))
+        assert np.array_equal(codes[b], c), b
+        assert np.array_equal(values[b], v), b
+        assert bool(saw[b]) == s_ and eos[b] == e and states[b] == r, b
+    pl.close(); pm.close()
+    dec.close(); be.close()
+
+
 def test_local_requests_are_refused_without_local_weights(tiny_model):
     from mynah_tts_b200.backend import Backend, Decoder
     from mynah_tts_b200.capi import MynahB200Error
