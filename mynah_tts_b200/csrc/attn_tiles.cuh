@@ -89,7 +89,7 @@ __device__ __forceinline__ void quantize_shared_row(const float *vals, int width
                                                     float *sx_out, float *red) {
     float amax = 0.0f;
     for (int i = threadIdx.x; i < width; i += blockDim.x) amax = fmaxf(amax, fabsf(vals[i]));
-    amax = block_max(amax, red);
+    amax = block_max1(amax, red);   // callers pass scratch no thread is still reading
     const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
         const int v = round_half_away(__fmul_rn(vals[i], inv));
