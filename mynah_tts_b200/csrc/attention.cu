@@ -139,7 +139,12 @@ __global__ void __launch_bounds__(256) k_attn_strict(AttnP p) {
 // K and V tiles each go through a ring of p.depth slots, so while the warps work on one
 // tile the next 2 * depth - 1 are landing.
 constexpr int RING_MAX = 4;
-__global__ void __launch_bounds__(1024, 1)
+// MAXT: most threads of a launch (32 per head).  The 1024-thread bound caps the kernel at 64
+// registers; an instantiation bounded at 384 threads (twelve heads) gets 160 and is faster
+// where the launch is bound by bandwidth (64 streams: 882 against 889 us per step) but slower
+// for a few streams (one stream: 497 against 486), so it is taken from 32 streams.
+template <int MAXT>
+__global__ void __launch_bounds__(MAXT, 1)
 k_attn_rows(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, AttnP p) {
     // With p.early the dependency wait comes AFTER the first tiles are requested.  The caller
     // then vouches that what is read before it (lane state, cache rows below `pos`) was
@@ -601,7 +606,8 @@ size_t chunks_for(size_t max_valid) { return (max_valid + CHUNK - 1) / CHUNK; }
 // per device at backend open, outside any stream capture.
 extern "C" int mb_attention_init(void) {
     int rc = (int)cudaFuncSetAttribute(k_attn_strict, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    if (rc == 0) rc = (int)cudaFuncSetAttribute(k_attn_rows, cudaFuncAttributeMaxDynamicSharedMemorySize, ROWS_SMEM_MAX);
+    if (rc == 0) rc = (int)cudaFuncSetAttribute(k_attn_rows<1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, ROWS_SMEM_MAX);
+    if (rc == 0) rc = (int)cudaFuncSetAttribute(k_attn_rows<384>, cudaFuncAttributeMaxDynamicSharedMemorySize, ROWS_SMEM_MAX);
     if (rc == 0) rc = (int)cudaFuncSetAttribute(k_attn_short, cudaFuncAttributeMaxDynamicSharedMemorySize, ROWS_SMEM_MAX - 1024);
     if (rc == 0) rc = (int)cudaFuncSetAttribute(k_attn_scalar, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     return rc;
@@ -718,8 +724,12 @@ extern "C" int mb_attention(const mb_attn_args *a, mb_stream stream) {
             !mb_make_map_2d(&vmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a->v_cache, rows, (size_t)p.cache_stride,
                             (size_t)p.cache_stride * 4u, (unsigned)p.box_cols, CHUNK, CU_TENSOR_MAP_SWIZZLE_NONE))
             return (int)cudaErrorInvalidValue;
-        mb_launch(k_attn_rows, dim3((unsigned)splits, (unsigned)p.batch, (unsigned)groups),
-                  dim3((unsigned)hg * 32u), rows_bytes, s, kmap, vmap, p);
+        if (hg * 32 <= 384 && p.batch >= 32)
+            mb_launch(k_attn_rows<384>, dim3((unsigned)splits, (unsigned)p.batch, (unsigned)groups),
+                      dim3((unsigned)hg * 32u), rows_bytes, s, kmap, vmap, p);
+        else
+            mb_launch(k_attn_rows<1024>, dim3((unsigned)splits, (unsigned)p.batch, (unsigned)groups),
+                      dim3((unsigned)hg * 32u), rows_bytes, s, kmap, vmap, p);
         return mb_check_launch();
     }
     if (a->out == nullptr) return (int)cudaErrorInvalidValue;
@@ -820,7 +830,7 @@ int mynah_b200_self_attention_static(const float *dev_qkv, float *dev_k_cache, f
         }
         // the chunk kernel stages two chunks of K and V: above 48 KB of dynamic shared
         // memory for wide heads, which a kernel must opt into once per device
-        rc = cudaFuncSetAttribute(k_attn_rows, cudaFuncAttributeMaxDynamicSharedMemorySize, ROWS_SMEM_MAX);
+        rc = cudaFuncSetAttribute(k_attn_rows<1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, ROWS_SMEM_MAX);
         if (rc != cudaSuccess) {
             static_error(error, cap, cudaGetErrorString(rc));
             return -1;
@@ -878,7 +888,7 @@ int mynah_b200_self_attention_static(const float *dev_qkv, float *dev_k_cache, f
         static_error(error, cap, "could not describe the KV cache to the copy engine");
         return -1;
     }
-    k_attn_rows<<<dim3((unsigned)p.splits, 1u), (unsigned)p.heads * 32u, floats * sizeof(float), s>>>(kmap, vmap, p);
+    k_attn_rows<1024><<<dim3((unsigned)p.splits, 1u), (unsigned)p.heads * 32u, floats * sizeof(float), s>>>(kmap, vmap, p);
     rc = cudaGetLastError();
     if (rc != cudaSuccess) {
         static_error(error, cap, cudaGetErrorString(rc));
