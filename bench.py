@@ -279,7 +279,7 @@ def workload_config(args, shape):
 
 # ------------------------------------------------------------------- own arm
 # measured DRAM bytes / algorithmic bytes of one launch, from an ncu capture of that kernel
-NCU_TRAFFIC_RATIO = {"self attention": 1.146}
+NCU_TRAFFIC_RATIO = {"self attention": 1.132}
 
 
 def algorithmic_bytes(shape, name: str, batch: int, mean_len: float, qbytes: dict) -> float:
