@@ -155,7 +155,10 @@ k_attn_rows(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CU
         mb_pdl_wait();
         mb_pdl_trigger();
     }
-    extern __shared__ __align__(128) float sm[];
+    // a name of its own: a redeclaration of another kernel's array would take that one's alignment,
+    // and the TMA tiles need 128 bytes
+    extern __shared__ __align__(128) float sm_rows[];
+    float *sm = sm_rows;
     __shared__ float red[33];
     __shared__ unsigned s_last;
     __shared__ __align__(8) unsigned long long mbar[2 * RING_MAX];   // K slots, then V slots
@@ -421,9 +424,13 @@ k_attn_rows(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CU
 // null).  Per (head, chunk) and in the merge the operations and their order are those of
 // k_attn_rows: results are bit-identical.
 constexpr int SHORT_MAX_CHUNKS = 8;
-__global__ void __launch_bounds__(1024, 1)
+// MAXT: most threads of a launch; the cross attention's four warps get an instantiation
+// bounded at 128 threads (the 1024-thread bound caps the registers at 64).
+template <int MAXT>
+__global__ void __launch_bounds__(MAXT, 1)
 k_attn_short(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, AttnP p) {
-    extern __shared__ __align__(128) float sm[];
+    extern __shared__ __align__(128) float sm_short[];      // (own name: see k_attn_rows)
+    float *sm = sm_short;
     __shared__ float red[33];
     __shared__ __align__(8) unsigned long long mbar[2 * SHORT_MAX_CHUNKS];   // K chunks, then V chunks
     __shared__ unsigned s_bad;
@@ -608,7 +615,8 @@ extern "C" int mb_attention_init(void) {
     int rc = (int)cudaFuncSetAttribute(k_attn_strict, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (rc == 0) rc = (int)cudaFuncSetAttribute(k_attn_rows<1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, ROWS_SMEM_MAX);
     if (rc == 0) rc = (int)cudaFuncSetAttribute(k_attn_rows<384>, cudaFuncAttributeMaxDynamicSharedMemorySize, ROWS_SMEM_MAX);
-    if (rc == 0) rc = (int)cudaFuncSetAttribute(k_attn_short, cudaFuncAttributeMaxDynamicSharedMemorySize, ROWS_SMEM_MAX - 1024);
+    if (rc == 0) rc = (int)cudaFuncSetAttribute(k_attn_short<1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, ROWS_SMEM_MAX - 1024);
+    if (rc == 0) rc = (int)cudaFuncSetAttribute(k_attn_short<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, ROWS_SMEM_MAX - 1024);
     if (rc == 0) rc = (int)cudaFuncSetAttribute(k_attn_scalar, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     return rc;
 }
@@ -703,8 +711,12 @@ extern "C" int mb_attention(const mb_attn_args *a, mb_stream stream) {
                 !mb_make_map_2d(&vmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a->v_cache, rows, (size_t)p.cache_stride,
                                 (size_t)p.cache_stride * 4u, (unsigned)p.box_cols, CHUNK, CU_TENSOR_MAP_SWIZZLE_NONE))
                 return (int)cudaErrorInvalidValue;
-            mb_launch(k_attn_short, dim3((unsigned)p.batch), dim3((unsigned)(p.heads * p.max_chunks) * 32u), short_bytes, s,
-                      kmap, vmap, p);
+            if (p.heads * p.max_chunks * 32 <= 128)
+                mb_launch(k_attn_short<128>, dim3((unsigned)p.batch), dim3((unsigned)(p.heads * p.max_chunks) * 32u), short_bytes, s,
+                          kmap, vmap, p);
+            else
+                mb_launch(k_attn_short<1024>, dim3((unsigned)p.batch), dim3((unsigned)(p.heads * p.max_chunks) * 32u), short_bytes, s,
+                          kmap, vmap, p);
             return mb_check_launch();
         }
     }
