@@ -30,6 +30,7 @@
 
 #include <float.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 namespace {
@@ -125,6 +126,10 @@ __global__ void __launch_bounds__(256) k_attn_strict(AttnP p) {
     }
 }
 
+
+}  // namespace
+#include "attn_exact.cuh"
+namespace {
 
 // -------------------------------------------------------------------- fast
 // Positions are cut into fixed chunks of CHUNK rows: the partition depends only on
@@ -607,6 +612,69 @@ bool is_pow2(long v) { return v > 0 && (v & (v - 1)) == 0; }
 
 size_t chunks_for(size_t max_valid) { return (max_valid + CHUNK - 1) / CHUNK; }
 
+
+int env_int(const char *name) {
+    const char *v = getenv(name);
+    return v == nullptr ? 0 : atoi(v);
+}
+
+// The streaming reference-order kernel (attn_exact.cuh) where the shape allows it: heads are
+// dealt to CTAs in groups whose columns fill whole 32-float boxes; about one CTA per SM.
+// Returns false (nothing launched) when the shape needs the plain strict kernel.
+bool launch_exact(const mb_attn_args *a, AttnP &p, cudaStream_t s) {
+    static const int force_groups = env_int("MYNAH_B200_ATTN_GROUPS");
+    static const int force_depth = env_int("MYNAH_B200_ATTN_DEPTH");
+    static const int off = env_int("MYNAH_B200_NO_EXACT_ATTN");
+    if (off || (p.hw % 4) != 0 || (p.cache_stride % 4) != 0 || (p.q_stride % 4) != 0 ||
+        (p.slot_stride % 4) != 0 || (p.cache_stride != 0 && (p.slot_stride % p.cache_stride) != 0) ||
+        !(a->batch == 1 || a->cache_rows != 0) ||
+        (((uintptr_t)a->k_cache | (uintptr_t)a->v_cache) & 15u) != 0 ||
+        (a->qx != nullptr && (a->counters == nullptr || a->sx == nullptr)))
+        return false;
+    const int sms = a->sm_count > 0 ? a->sm_count : 148;
+    int best_g = 0, best_depth = 0;
+    for (int g = 1; g <= p.heads; ++g) {
+        if (p.heads % g != 0) continue;
+        if (force_groups > 0 && g != force_groups) continue;
+        const int hg = p.heads / g, cw = hg * p.hw;
+        const int threads = cw > hg * 32 ? cw : hg * 32;
+        if ((cw % EX_BOX) != 0 || threads > 1024) continue;
+        // more CTAs than SMs: two of them share an SM
+        const size_t room = (long)p.batch * g > sms ? (size_t)110 * 1024 : (size_t)ROWS_SMEM_MAX;
+        int depth = 0;
+        for (int d = EX_RING_MAX; d >= 1 && depth == 0; --d)
+            if (exact_smem(hg, p.hw, p.max_chunks, d) + 1024u <= room) depth = d;
+        if (depth > 2 * p.max_chunks) depth = 2 * p.max_chunks;
+        if (force_depth > 0 && force_depth < depth) depth = force_depth;
+        if (depth < 1) continue;
+        best_g = g;
+        best_depth = depth;
+        if (force_groups > 0 || (long)p.batch * g >= sms) break;   // enough CTAs to cover the SMs
+    }
+    if (best_g == 0) return false;
+    const int hg = p.heads / best_g, cw = hg * p.hw;
+    const int threads = cw > hg * 32 ? cw : hg * 32;
+    p.depth = best_depth;
+    p.splits = 1;
+    p.early = a->early_prefetch ? 1 : 0;
+    p.slot_rows = p.cache_stride != 0 ? p.slot_stride / p.cache_stride : 0;
+    p.box_cols = EX_BOX;
+    p.nbox = cw / EX_BOX;
+    size_t rows = a->cache_rows;
+    if (rows == 0) rows = (size_t)(p.valid > p.position + 1 ? p.valid : p.position + 1);
+    CUtensorMap kmap, vmap;
+    if (!mb_make_map_2d(&kmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a->k_cache, rows, (size_t)p.cache_stride,
+                        (size_t)p.cache_stride * 4u, EX_BOX, CHUNK, CU_TENSOR_MAP_SWIZZLE_128B) ||
+        !mb_make_map_2d(&vmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a->v_cache, rows, (size_t)p.cache_stride,
+                        (size_t)p.cache_stride * 4u, EX_BOX, CHUNK, CU_TENSOR_MAP_SWIZZLE_128B))
+        return false;
+    const size_t smem = exact_smem(hg, p.hw, p.max_chunks, best_depth);
+    const dim3 grid((unsigned)best_g, (unsigned)p.batch), block((unsigned)threads);
+    if (threads <= 384) mb_launch(k_attn_exact<384>, grid, block, smem, s, kmap, vmap, p);
+    else mb_launch(k_attn_exact<1024>, grid, block, smem, s, kmap, vmap, p);
+    return true;
+}
+
 }  // namespace
 
 // Opt the kernels into large dynamic shared memory on the current device; once
@@ -618,6 +686,8 @@ extern "C" int mb_attention_init(void) {
     if (rc == 0) rc = (int)cudaFuncSetAttribute(k_attn_short<1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, ROWS_SMEM_MAX - 1024);
     if (rc == 0) rc = (int)cudaFuncSetAttribute(k_attn_short<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, ROWS_SMEM_MAX - 1024);
     if (rc == 0) rc = (int)cudaFuncSetAttribute(k_attn_scalar, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (rc == 0) rc = (int)cudaFuncSetAttribute(k_attn_exact<384>, cudaFuncAttributeMaxDynamicSharedMemorySize, ROWS_SMEM_MAX);
+    if (rc == 0) rc = (int)cudaFuncSetAttribute(k_attn_exact<1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, ROWS_SMEM_MAX);
     return rc;
 }
 
@@ -717,6 +787,7 @@ extern "C" int mb_attention(const mb_attn_args *a, mb_stream stream) {
             else
                 mb_launch(k_attn_short<1024>, dim3((unsigned)p.batch), dim3((unsigned)(p.heads * p.max_chunks) * 32u), short_bytes, s,
                           kmap, vmap, p);
+            if (a->launched != nullptr) *a->launched += 1u;
             return mb_check_launch();
         }
     }
@@ -742,17 +813,25 @@ extern "C" int mb_attention(const mb_attn_args *a, mb_stream stream) {
         else
             mb_launch(k_attn_rows<1024>, dim3((unsigned)splits, (unsigned)p.batch, (unsigned)groups),
                       dim3((unsigned)hg * 32u), rows_bytes, s, kmap, vmap, p);
+        if (a->launched != nullptr) *a->launched += 1u;
         return mb_check_launch();
     }
     if (a->out == nullptr) return (int)cudaErrorInvalidValue;
+    if (a->strict && launch_exact(a, p, s)) {
+        if (a->launched != nullptr) *a->launched += 1u;
+        return mb_check_launch();
+    }
     const size_t smem = (size_t)(p.hw + max_valid) * sizeof(float);
     if (smem > 200u * 1024u) return (int)cudaErrorInvalidValue;
     dim3 grid((unsigned)p.heads, (unsigned)p.batch);
     if (a->strict) mb_launch(k_attn_strict, dim3(grid), dim3(256), smem, s, p);
     else mb_launch(k_attn_scalar, dim3(grid), dim3(FAST_THREADS), smem, s, p);
     int rc = mb_check_launch();
-    if (rc == 0 && a->qx != nullptr)
+    if (a->launched != nullptr) *a->launched += 1u;
+    if (rc == 0 && a->qx != nullptr) {
         rc = mb_quant_rows(a->out, a->batch, width, a->qx, a->sx, a->n_active, stream);
+        if (a->launched != nullptr) *a->launched += 1u;
+    }
     return rc;
 }
 

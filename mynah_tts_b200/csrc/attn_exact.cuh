@@ -1,0 +1,219 @@
+// Reference-order ("strict") single-query attention at streaming speed.  Included by
+// attention.cu after AttnP and lane_setup.
+//
+// The reference's loops (src/graph.c:3182-3202 self, 3221-3244 cross) fix the ORDER of
+// three kinds of sums -- a score's 64 products over d, the denominator over s, an output's
+// products over s -- but nothing else: scores of different rows, outputs of different
+// dimensions, heads and streams are independent.  k_attn_exact keeps every such sum one
+// sequential chain of separately rounded products and adds, in index order, and runs the
+// chains side by side while the cache streams through shared memory:
+//
+//   CTA = one stream (lane) and a group of its heads.  K rows, then V rows, of the group's
+//   columns arrive as 32-row TMA tiles through one ring of mbarrier-guarded slots (every
+//   wait bounded, status bit 2).  A tile is a set of [32 rows][32 floats] boxes with the
+//   128-byte swizzle, so that the threads of a warp, which read the same column piece of 32
+//   different rows in the score pass, hit 32 different banks.
+//   pass 1 (K tiles): thread (head, row) forms its row's score, d = 0 .. hw-1 in order.
+//   middle: max per head (exact in any order), e = expf(score - max) with the host libm's
+//           bits, the denominator by one thread per head in row order, weights e / den.
+//   pass 2 (V tiles): thread (head, d) adds weight[s] * v[s][d] for s = 0 .. valid-1 in order.
+//   tail: the stream's last CTA (arrival counter; none when one CTA owns the stream)
+//         quantizes the row to int8 when the next product wants that.
+//
+// Same bits as k_attn_strict and as the CPU loop, whatever the batch or the head grouping.
+#pragma once
+
+namespace {
+
+constexpr int EX_RING_MAX = 8;
+constexpr int EX_BOX = 32;                     // columns (floats) and rows of a TMA box
+constexpr int EX_BOX_FLOATS = EX_BOX * EX_BOX;
+
+template <int MAXT>
+__global__ void __launch_bounds__(MAXT, 1)
+k_attn_exact(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, AttnP p) {
+    if (!p.early) {
+        mb_pdl_wait();
+        mb_pdl_trigger();
+    }
+    extern __shared__ __align__(1024) float sm_exact[];
+    __shared__ float red[33];
+    __shared__ unsigned s_last, s_fail;
+    __shared__ __align__(8) unsigned long long mbar[EX_RING_MAX];
+    const int b = blockIdx.y;
+    long pos, valid, slot;
+    float *kc, *vc;
+    if (!lane_setup(p, b, pos, valid, kc, vc, &slot)) return;
+    const int hw = p.hw, heads = p.heads, width = heads * hw;
+    const int groups = (int)gridDim.x, hg = heads / groups;
+    const int h0 = blockIdx.x * hg, cw = hg * hw, c0 = h0 * hw;     // this CTA's heads and columns
+    const int nbox = cw / EX_BOX, tile_floats = CHUNK * cw;
+    const int ns = (int)((valid + CHUNK - 1) / CHUNK), ntiles = 2 * ns;
+    const int depth = p.depth, scap = p.max_chunks * CHUNK;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    float *tiles = sm_exact;                                  // [depth][nbox][32][32], swizzled
+    float *qs = tiles + (long)depth * tile_floats;            // [cw]
+    float *kn = qs + cw;                                      // [cw] the row appended now
+    float *vn = kn + cw;
+    float *sc = vn + cw;                                      // [hg][scap] scores, then weights
+    float *stat = sc + (long)hg * scap;                       // [hg] max, [hg] denominator
+    const unsigned tile_bytes = (unsigned)tile_floats * 4u;
+    const unsigned long long stream_policy = mb_l2_evict_first();
+    // tile t of this CTA: K chunk t for t < ns, then V chunk t - ns; ring slot t % depth
+    auto issue = [&](int t) {
+        const int c = t < ns ? t : t - ns, rs = t % depth;
+        const CUtensorMap *map = t < ns ? &kmap : &vmap;
+        const int y = (int)(slot * p.slot_rows + (long)c * CHUNK);
+        float *tile = tiles + (long)rs * tile_floats;
+        mbar_expect_tx(&mbar[rs], tile_bytes);
+        for (int bx = 0; bx < nbox; ++bx)
+            mb_tma_load_2d_hint(tile + (long)bx * EX_BOX_FLOATS, map, c0 + bx * EX_BOX, y, &mbar[rs], stream_policy);
+    };
+    if (tid == 0) {
+        s_fail = 0u;
+        for (int i = 0; i < depth; ++i) mbar_init(&mbar[i], 1u);
+        for (int t = 0; t < depth && t < ntiles; ++t) issue(t);
+    }
+    if (p.early) {
+        mb_pdl_wait();
+        mb_pdl_trigger();
+    }
+    const bool append = p.k_new != nullptr;
+    for (int d = tid; d < cw; d += blockDim.x) {
+        qs[d] = p.q[(long)b * p.q_stride + c0 + d];
+        if (append) {
+            const float kk = p.k_new[(long)b * p.q_stride + c0 + d], vv = p.v_new[(long)b * p.q_stride + c0 + d];
+            kn[d] = kk;
+            vn[d] = vv;
+            kc[pos * p.cache_stride + c0 + d] = kk;
+            vc[pos * p.cache_stride + c0 + d] = vv;
+        }
+    }
+    __syncthreads();
+    const bool p1 = warp < hg;                                // pass-1 thread: head h0 + warp, row `lane` of a chunk
+    const int col = tid;                                      // pass-2 thread: column c0 + col
+    const bool p2 = col < cw;
+    const int h2 = p2 ? col / hw : 0;
+    const float *box2 = tiles + (long)(col >> 5) * EX_BOX_FLOATS;
+    const int j2c = (col & 31) >> 2, j2e = col & 3;
+    float lmax = -FLT_MAX, acc = 0.0f;
+    int done = 0;                                             // tiles consumed
+    for (int t = 0; t < ntiles; ++t) {
+        const int rs = t % depth;
+        const unsigned parity = (unsigned)((t / depth) & 1);
+        if (t == ns) {
+            // ---- all scores are in: max, exp, denominator, weights -------------------------
+            if (p1) {
+                const float m = warp_max(lmax);
+                if (lane == 0) stat[warp] = m;
+            }
+            __syncthreads();
+            for (int h = 0; h < hg; ++h) {
+                const float m = stat[h];
+                for (long s = tid; s < valid; s += blockDim.x)
+                    sc[(long)h * scap + s] = exp_ref<true>(__fsub_rn(sc[(long)h * scap + s], m), p.exp_tab);
+            }
+            __syncthreads();
+            if (p1 && lane == 0) {
+                const float *e = sc + (long)warp * scap;
+                float den = 0.0f;
+                for (long s = 0; s < valid; ++s) den = __fadd_rn(den, e[s]);
+                stat[hg + warp] = den;
+            }
+            __syncthreads();
+            for (int h = 0; h < hg; ++h) {
+                const float den = stat[hg + h];
+                for (long s = tid; s < valid; s += blockDim.x)
+                    sc[(long)h * scap + s] = __fdiv_rn(sc[(long)h * scap + s], den);
+            }
+            __syncthreads();
+        }
+        if (!mbar_wait(&mbar[rs], parity, SPIN_LIMIT)) s_fail = 1u;
+        else if (t < ns) {
+            // ---- pass 1: this thread's row of chunk t ----------------------------------------
+            const long s = (long)t * CHUNK + lane;
+            if (p1 && s < valid) {
+                const float *tile = tiles + (long)rs * tile_floats;
+                const float *qh = qs + warp * hw;
+                float a = 0.0f;
+                if (append && s == pos) {
+                    const float *kr = kn + warp * hw;
+                    for (int d = 0; d < hw; ++d) a = __fadd_rn(a, __fmul_rn(qh[d], kr[d]));
+                } else {
+                    for (int d4 = 0; d4 < hw; d4 += 4) {
+                        const int cc = warp * hw + d4;
+                        const float4 kv = *reinterpret_cast<const float4 *>(
+                            tile + (long)(cc >> 5) * EX_BOX_FLOATS + lane * EX_BOX + (((((cc & 31) >> 2)) ^ (lane & 7)) << 2));
+                        const float4 qv = *reinterpret_cast<const float4 *>(qh + d4);
+                        a = __fadd_rn(a, __fmul_rn(qv.x, kv.x));
+                        a = __fadd_rn(a, __fmul_rn(qv.y, kv.y));
+                        a = __fadd_rn(a, __fmul_rn(qv.z, kv.z));
+                        a = __fadd_rn(a, __fmul_rn(qv.w, kv.w));
+                    }
+                }
+                a = __fmul_rn(a, p.scale);
+                sc[(long)warp * scap + s] = a;
+                if (a > lmax) lmax = a;
+            }
+        } else if (p2) {
+            // ---- pass 2: this thread's column over the rows of chunk t - ns -------------------
+            const int c = t - ns;
+            const long s0 = (long)c * CHUNK;
+            const int cnt = (int)min((long)CHUNK, valid - s0);
+            const float *tile = box2 + (long)rs * tile_floats;
+            const float *w = sc + (long)h2 * scap + s0;
+            const int fresh = (append && pos >= s0 && pos < s0 + cnt) ? (int)(pos - s0) : -1;
+#pragma unroll 8
+            for (int r = 0; r < cnt; ++r) {
+                const float v = r == fresh ? vn[col] : tile[r * EX_BOX + (((j2c ^ (r & 7)) << 2) | j2e)];
+                acc = __fadd_rn(acc, __fmul_rn(w[r], v));
+            }
+        }
+        __syncthreads();                                     // every thread is done with the slot
+        done = t + 1;
+        if (s_fail != 0u) break;
+        if (tid == 0 && t + depth < ntiles) issue(t + depth);
+    }
+    if (s_fail != 0u) {
+        // a tile never landed: flag it and give every copy still in flight one more bounded wait,
+        // so that none lands after this CTA's shared memory is released
+        if (tid == 0) {
+            if (p.status != nullptr) atomicOr(p.status, 2);
+            const int issued = min(ntiles, done - 1 + depth);
+            for (int t = done - 1; t < issued; ++t) mbar_wait(&mbar[t % depth], (unsigned)((t / depth) & 1), SPIN_LIMIT);
+        }
+        return;
+    }
+    float *outrow = p.out + (long)b * p.out_stride;
+    if (p2) outrow[c0 + col] = acc;
+    if (p.qx == nullptr) return;
+    // ---- the stream's last CTA quantizes the whole row ------------------------------------
+    float *vals = tiles;                                      // every tile has been consumed
+    if (groups > 1) {
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+            unsigned *ctr = p.counters + b;
+            const unsigned prev = atomicAdd(ctr, 1u);
+            s_last = prev == (unsigned)groups - 1u;
+            if (s_last) *ctr = 0u;
+        }
+        __syncthreads();
+        if (!s_last) return;
+        __threadfence();
+        for (int i = tid; i < width; i += blockDim.x) vals[i] = __ldcg(outrow + i);
+    } else if (p2) {
+        vals[col] = acc;
+    }
+    __syncthreads();
+    quantize_shared_row(vals, width, p.qx + (long)b * width, p.sx + b, red);
+}
+
+// Shared memory of one CTA of k_attn_exact: `depth` tiles, q and the appended K/V row, the
+// scores of the group's heads, two statistics per head.
+inline size_t exact_smem(int hg, int hw, int max_chunks, int depth) {
+    const size_t cw = (size_t)hg * hw;
+    return ((size_t)depth * CHUNK * cw + 3u * cw + (size_t)hg * max_chunks * CHUNK + 2u * hg) * sizeof(float);
+}
+
+}  // namespace

@@ -553,8 +553,8 @@ static int enqueue_local(mb_decoder *d, const float *first_rows, size_t nb, unsi
             a.status = d->d_status;
             a.sm_count = st->sm_count;
             a.early_prefetch = 1;   /* rows below t were appended at earlier positions of this frame */
+            a.launched = count;
             L_TRY(mb_attention(&a, s));
-            *count += (st->strict && q) ? 2u : 1u;
             L_TRY(product(d, &L->o, NULL, d->attn, d->x, W, nb, MB_EPI_RESIDUAL, count));
             if (f1) {
                 L_TRY(product_fused(d, &L->ffn_up, NULL, d->x, d->hidden, F, nb, MB_EPI_GELU, MB_FUSE_LN,
@@ -684,8 +684,8 @@ static int enqueue(mb_decoder *d, size_t bucket, int mode, unsigned *count) {
         a.status = d->d_status;
         a.sm_count = st->sm_count;
         a.early_prefetch = 1;   /* lane state: previous step; cache rows below the position: earlier steps */
+        a.launched = count;
         P(PC_ATTN_SELF, mb_attention(&a, s));
-        *count += (st->strict && q) ? 2u : 1u;
         P(PC_O_SELF, product(d, &L->o_self, NULL, d->attn, d->x, W, nb, MB_EPI_RESIDUAL, count));
         /* int8, non-strict: the whole cross-attention block, with the norm before the
          * feed-forward product, is one launch with one CTA per stream */
@@ -764,8 +764,8 @@ static int enqueue(mb_decoder *d, size_t bucket, int mode, unsigned *count) {
         a.status = d->d_status;
         a.sm_count = st->sm_count;
         a.early_prefetch = 1;   /* the cross cache is written once, when the slot is loaded */
+        a.launched = count;
         P(PC_ATTN_CROSS, mb_attention(&a, s));
-        *count += (st->strict && q) ? 2u : 1u;
         P(PC_O_CROSS, product(d, &L->o_cross, NULL, d->xctx, d->x, W, nb, MB_EPI_RESIDUAL, count));
         if (f1) {
             P(PC_FFN_UP, product_fused(d, &L->ffn_up, NULL, d->x, d->hidden, F, nb, MB_EPI_GELU, MB_FUSE_LN,

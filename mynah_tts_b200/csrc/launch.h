@@ -197,6 +197,7 @@ typedef struct {
     int early_prefetch;   /* 1: lane state and cache rows below the position were written at least two
                            * launches before this one, so the kernel may request its first cache tiles
                            * before it waits for its predecessor (programmatic dependent launch) */
+    unsigned *launched;   /* optional: incremented by the number of kernels the call enqueued */
 } mb_attn_args;
 int mb_attention(const mb_attn_args *args, mb_stream stream);
 size_t mb_attention_scratch_floats(size_t batch, size_t heads, size_t max_valid, size_t head_width);
