@@ -115,10 +115,7 @@ k_attn_exact(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ C
             }
             __syncthreads();
             if (p1 && lane == 0) {
-                const float *e = sc + (long)warp * scap;
-                float den = 0.0f;
-                for (long s = 0; s < valid; ++s) den = __fadd_rn(den, e[s]);
-                stat[hg + warp] = den;
+                stat[hg + warp] = mb_seq_sum(sc + (long)warp * scap, (int)valid);
             }
             __syncthreads();
             for (int h = 0; h < hg; ++h) {
@@ -140,6 +137,7 @@ k_attn_exact(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ C
                     const float *kr = kn + warp * hw;
                     for (int d = 0; d < hw; ++d) a = __fadd_rn(a, __fmul_rn(qh[d], kr[d]));
                 } else {
+#pragma unroll 4
                     for (int d4 = 0; d4 < hw; d4 += 4) {
                         const int cc = warp * hw + d4;
                         const float4 kv = *reinterpret_cast<const float4 *>(

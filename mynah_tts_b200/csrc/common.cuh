@@ -160,6 +160,77 @@ __device__ __forceinline__ float mb_ln_block(float *row, int width, const float 
     return amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 0.0f;
 }
 
+// ((..(v[0] + v[1]) + v[2]) ..) + v[n-1], every add rounded: the reference's `sum += v[i]`
+// loop by ONE thread over shared memory.  The chain costs an add latency per element; the
+// loads run a batch of 32 floats ahead in registers so that they never sit in the chain.
+// (An array that is not 16-byte aligned is walked with plain loads.)
+__device__ __forceinline__ float mb_seq_sum(const float *v, int n) {
+    float s = 0.0f;
+    if ((reinterpret_cast<uintptr_t>(v) & 15u) != 0) {
+        for (int i = 0; i < n; ++i) s = __fadd_rn(s, v[i]);
+        return s;
+    }
+    const int n4 = n >> 2;
+    const float4 *v4 = reinterpret_cast<const float4 *>(v);
+    float4 cur[8], nxt[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) cur[j] = j < n4 ? v4[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int base = 0; base < n4; base += 8) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) nxt[j] = base + 8 + j < n4 ? v4[base + 8 + j] : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            if (base + j < n4) {
+                s = __fadd_rn(s, cur[j].x);
+                s = __fadd_rn(s, cur[j].y);
+                s = __fadd_rn(s, cur[j].z);
+                s = __fadd_rn(s, cur[j].w);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) cur[j] = nxt[j];
+    }
+    for (int i = n4 << 2; i < n; ++i) s = __fadd_rn(s, v[i]);
+    return s;
+}
+
+// Reference-order layer norm of one row by one CTA (src/kernels.c:186-244, portable branch:
+// the mean and the variance are each ONE sequential chain of rounded adds over the row, the
+// squares are rounded once each), with optional int8 quantization (src/qmat.c:93-113).
+// `row` (shared, 16-byte aligned) holds the input and receives y; `sq` is scratch of `width`
+// floats (16-byte aligned), `stat` of
+// two, `red` of 32 that no thread is still reading.  Returns the quantization scale (0 when
+// !quant) to every thread.  Same bits as k_layernorm<true>.
+__device__ __forceinline__ float mb_ln_block_strict(float *row, int width, const float *__restrict__ gain,
+                                                    const float *__restrict__ bias, float eps, float *sq, float *stat,
+                                                    float *red, float *y_out, bool quant, int8_t *q) {
+    if (threadIdx.x == 0) stat[0] = __fdiv_rn(mb_seq_sum(row, width), (float)width);
+    __syncthreads();
+    const float mean = stat[0];
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float d = __fsub_rn(row[i], mean);
+        sq[i] = __fmul_rn(d, d);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) stat[1] = mb_seq_sum(sq, width);
+    __syncthreads();
+    const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(stat[1], (float)width), eps)));
+    float amax = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float y = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(row[i], mean), scale), gain[i]),
+                                  bias == nullptr ? 0.0f : bias[i]);
+        if (y_out != nullptr) y_out[i] = y;
+        row[i] = y;                  // each thread rereads only its own elements below
+        amax = fmaxf(amax, fabsf(y));
+    }
+    if (!quant) return 0.0f;
+    amax = block_max1(amax, red);
+    const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x)
+        q[i] = (int8_t)min(127, max(-127, round_half_away(__fmul_rn(row[i], inv))));
+    return amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 0.0f;
+}
+
 // int8 quantization of one f32 row held in shared memory by one CTA; returns the scale.
 __device__ __forceinline__ float mb_quant_block(const float *row, int width, float *red, int8_t *q) {
     float amax = 0.0f;
@@ -182,6 +253,16 @@ __device__ __forceinline__ float gelu_tanh(float x, const uint32_t *tanh_tab) {
     const float c = __fmul_rn(0.7978845608f, __fadd_rn(x, __fmul_rn(0.044715f, cubic)));
     const float t = STRICT ? mb_tanhf_host(c, tanh_tab) : tanhf(c);
     return __fmul_rn(__fmul_rn(0.5f, x), __fadd_rn(1.0f, t));
+}
+
+// The strict GELU in two steps (see mb_tanh_fetch): the argument of tanhf, and the result
+// from the argument's fetched table word.
+__device__ __forceinline__ float gelu_tanh_arg(float x) {
+    const float cubic = __fmul_rn(__fmul_rn(x, x), x);
+    return __fmul_rn(0.7978845608f, __fadd_rn(x, __fmul_rn(0.044715f, cubic)));
+}
+__device__ __forceinline__ float gelu_tanh_finish(float x, float c, uint32_t word, bool have_tab) {
+    return __fmul_rn(__fmul_rn(0.5f, x), __fadd_rn(1.0f, mb_tanhf_host_with(c, word, have_tab)));
 }
 
 template <bool STRICT>

@@ -39,6 +39,7 @@ struct CrossP {
     int8_t *qx;
     float *sx;
     int *status;
+    const uint32_t *exp_tab;
     long slot_rows;
     int width, xw, rows, chunks;
     float scale, eps;
@@ -64,11 +65,16 @@ __device__ __forceinline__ int dot16(const uint4 &a, const uint4 &b, int acc) {
 // RO = rows of the output weight one thread ends up owning (width <= RO * 256); a thread of
 // the query product holds every other 16-byte piece of one weight row, 8 * RO of them.
 // LPR = 16-byte pieces of an output-weight row (xw = 16 * LPR).
-template <int RO, int LPR>
+// STRICT: the reference's summation orders (mb_ln_block_strict; scores, denominator and
+// context as sequential chains, as k_attn_exact forms them) and the host libm's expf; the
+// K/V tiles then arrive as 128-byte-swizzled [32][32] boxes so that a warp whose threads
+// each walk one row reads 32 different banks.  Same bits as the separate strict launches.
+template <int RO, int LPR, bool STRICT>
 __global__ void __launch_bounds__(XB_THREADS, 1)
 k_cross_block(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, CrossP p) {
-    extern __shared__ __align__(128) float sm[];
+    extern __shared__ __align__(1024) float sm[];
     __shared__ float red[96];
+    __shared__ float stat[2];
     __shared__ __align__(8) unsigned long long mbar[2 * XB_MAX_CHUNKS];   // K chunks, then V chunks
     __shared__ unsigned s_bad;
     const int b = blockIdx.x;
@@ -89,7 +95,8 @@ k_cross_block(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
     float *vals = wts + 32;                           // [XW] merged context
     float *gq = vals + XW;                            // [W] gain of the first norm
     float *gf = gq + W;                               // [W] gain of the second norm
-    int8_t *qrow = reinterpret_cast<int8_t *>((reinterpret_cast<uintptr_t>(gf + W) + 15u) & ~(uintptr_t)15u);   // [W] quantized first norm
+    float *sq = gf + W;                               // [W] squares of the strict norms
+    int8_t *qrow = reinterpret_cast<int8_t *>((reinterpret_cast<uintptr_t>(sq + W) + 15u) & ~(uintptr_t)15u);   // [W] quantized first norm
     int8_t *ctxq = qrow + W;                                 // [XW] quantized context
     const unsigned tile_bytes = (unsigned)tile_floats * 4u;
     if (threadIdx.x == 0) {
@@ -100,8 +107,15 @@ k_cross_block(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
             const int y = (int)(slot * p.slot_rows + (long)c * CHUNK);
             mbar_expect_tx(&mbar[c], tile_bytes);
             mbar_expect_tx(&mbar[ns + c], tile_bytes);
-            mb_tma_load_2d_hint(Kt + (long)c * tile_floats, &kmap, 0, y, &mbar[c], stream_policy);
-            mb_tma_load_2d_hint(Vt + (long)c * tile_floats, &vmap, 0, y, &mbar[ns + c], stream_policy);
+            if (STRICT) {
+                for (int bx = 0; bx < XW / 32; ++bx) {
+                    mb_tma_load_2d_hint(Kt + (long)c * tile_floats + bx * 1024, &kmap, bx * 32, y, &mbar[c], stream_policy);
+                    mb_tma_load_2d_hint(Vt + (long)c * tile_floats + bx * 1024, &vmap, bx * 32, y, &mbar[ns + c], stream_policy);
+                }
+            } else {
+                mb_tma_load_2d_hint(Kt + (long)c * tile_floats, &kmap, 0, y, &mbar[c], stream_policy);
+                mb_tma_load_2d_hint(Vt + (long)c * tile_floats, &vmap, 0, y, &mbar[ns + c], stream_policy);
+            }
         }
     }
     // Constants, fetched while the preceding launch is still running: the norms' gains into
@@ -138,7 +152,8 @@ k_cross_block(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
         row[i] = v;
     }
     __syncthreads();
-    const float sxq = mb_ln_block<1>(row, W, gq, nullptr, p.eps, red, nullptr, true, qrow);
+    const float sxq = STRICT ? mb_ln_block_strict(row, W, gq, nullptr, p.eps, sq, stat, red, nullptr, true, qrow)
+                             : mb_ln_block<1>(row, W, gq, nullptr, p.eps, red, nullptr, true, qrow);
     __syncthreads();
 
     // ---- query product: two threads per output row, pieces of the row interleaved
@@ -190,9 +205,63 @@ k_cross_block(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
     }
     __syncthreads();
 
+    float ctx = 0.0f;
     // ---- attention over the text states: warp c makes the partial of chunk c
     const int tpp = XW / 4, rps = 32 / tpp, sub = lane / tpp, li = lane % tpp;
-    if (warp < ns) {
+    if (STRICT) {
+        // reference order (src/graph.c:3221-3244): thread s forms the score of text state s as
+        // one chain over d; the denominator is one chain over s; thread d forms context
+        // element d as one chain over s
+        float *scs = P;                               // [ns * 32] scores, then weights
+        const int s = threadIdx.x, c = s >> 5, r = s & 31;
+        float a = -FLT_MAX;
+        if (s < p.rows) {
+            if (mbar_wait(&mbar[c], 0u, SPIN_LIMIT)) {
+                const float *tile = Kt + (long)c * tile_floats + r * 32;
+                float dot = 0.0f;
+#pragma unroll 4
+                for (int d4 = 0; d4 < XW; d4 += 4) {
+                    const float4 kv = *reinterpret_cast<const float4 *>(tile + (d4 >> 5) * 1024 + (((((d4 & 31) >> 2)) ^ (r & 7)) << 2));
+                    const float4 qv = *reinterpret_cast<const float4 *>(qs + d4);
+                    dot = __fadd_rn(dot, __fmul_rn(qv.x, kv.x));
+                    dot = __fadd_rn(dot, __fmul_rn(qv.y, kv.y));
+                    dot = __fadd_rn(dot, __fmul_rn(qv.z, kv.z));
+                    dot = __fadd_rn(dot, __fmul_rn(qv.w, kv.w));
+                }
+                a = __fmul_rn(dot, p.scale);
+            } else {
+                s_bad = 1u;
+                if (p.status != nullptr) atomicOr(p.status, 2);
+            }
+        }
+        const float m = block_max1(a, red);
+        if (s < p.rows) scs[s] = exp_ref<true>(__fsub_rn(a, m), p.exp_tab);
+        __syncthreads();
+        if (threadIdx.x == 0) stat[0] = mb_seq_sum(scs, p.rows);
+        __syncthreads();
+        if (s < p.rows) scs[s] = __fdiv_rn(scs[s], stat[0]);
+        __syncthreads();
+        if (threadIdx.x < XW && s_bad == 0u) {
+            const int d = threadIdx.x;
+            const float *col = Vt + (d >> 5) * 1024 + (d & 3);
+            const int jc = (d & 31) >> 2;
+            float acc = 0.0f;
+            for (int cc = 0; cc < ns; ++cc) {
+                if (!mbar_wait(&mbar[ns + cc], 0u, SPIN_LIMIT)) {
+                    s_bad = 1u;
+                    if (p.status != nullptr) atomicOr(p.status, 2);
+                    break;
+                }
+                const int cnt = min(CHUNK, p.rows - cc * CHUNK);
+                const float *tile = col + (long)cc * tile_floats;
+                const float *w = scs + cc * CHUNK;
+#pragma unroll 8
+                for (int rr = 0; rr < cnt; ++rr)
+                    acc = __fadd_rn(acc, __fmul_rn(w[rr], tile[rr * 32 + ((jc ^ (rr & 7)) << 2)]));
+            }
+            ctx = acc;
+        }
+    } else if (warp < ns) {
         const int c = warp;
         const float4 qv = reinterpret_cast<const float4 *>(qs)[li];
         const int cnt = min(CHUNK, p.rows - c * CHUNK);
@@ -244,8 +313,7 @@ k_cross_block(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
     }
     // merge of the chunk partials, a thread per dimension, and the int8 quantization of the
     // merged row (one warp doing both in turn was a 4 us chain of dependent instructions)
-    float ctx = 0.0f;
-    if (threadIdx.x < XW) ctx = merge_dim(P, ns, XW, threadIdx.x);
+    if (!STRICT && threadIdx.x < XW) ctx = merge_dim(P, ns, XW, threadIdx.x);
     const float cmax = block_max1(fabsf(ctx), red);
     const float cinv = cmax > 0.0f ? __fdiv_rn(127.0f, cmax) : 0.0f;
     if (threadIdx.x < XW) ctxq[threadIdx.x] = (int8_t)min(127, max(-127, round_half_away(__fmul_rn(ctx, cinv))));
@@ -288,12 +356,13 @@ k_cross_block(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
     __syncthreads();
 
     // ---- second norm, quantized for the feed-forward product
-    const float sx2 = mb_ln_block<1>(row, W, gf, nullptr, p.eps, red, nullptr, true, p.qx + (long)b * W);
+    const float sx2 = STRICT ? mb_ln_block_strict(row, W, gf, nullptr, p.eps, sq, stat, red, nullptr, true, p.qx + (long)b * W)
+                             : mb_ln_block<1>(row, W, gf, nullptr, p.eps, red, nullptr, true, p.qx + (long)b * W);
     if (threadIdx.x == 0) p.sx[b] = sx2;
 }
 
 size_t cross_block_smem(size_t width, size_t xw, size_t chunks) {
-    const size_t floats = 2u * chunks * CHUNK * xw + 4u * width + xw + chunks * (xw + 2u) + 32u + xw;
+    const size_t floats = 2u * chunks * CHUNK * xw + 5u * width + xw + chunks * (xw + 2u) + 32u + xw;
     return floats * sizeof(float) + width + xw + 16u;
 }
 
@@ -332,12 +401,13 @@ extern "C" int mb_cross_block(const mb_cross_block_args *a, mb_stream stream) {
     p.width = (int)a->width; p.xw = (int)a->xw; p.rows = (int)a->rows;
     p.chunks = (int)((a->rows + CHUNK - 1) / CHUNK);
     p.scale = a->scale; p.eps = a->eps;
+    p.exp_tab = a->exp_tab;
     const size_t rows = a->cache_rows != 0 ? a->cache_rows : a->rows;
+    const unsigned box_cols = a->strict ? 32u : (unsigned)a->xw;
+    const CUtensorMapSwizzle swz = a->strict ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE;
     CUtensorMap kmap, vmap;
-    if (!mb_make_map_2d(&kmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a->k_cache, rows, a->xw, a->xw * 4u, (unsigned)a->xw,
-                        CHUNK, CU_TENSOR_MAP_SWIZZLE_NONE) ||
-        !mb_make_map_2d(&vmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a->v_cache, rows, a->xw, a->xw * 4u, (unsigned)a->xw,
-                        CHUNK, CU_TENSOR_MAP_SWIZZLE_NONE))
+    if (!mb_make_map_2d(&kmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a->k_cache, rows, a->xw, a->xw * 4u, box_cols, CHUNK, swz) ||
+        !mb_make_map_2d(&vmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a->v_cache, rows, a->xw, a->xw * 4u, box_cols, CHUNK, swz))
         return (int)cudaErrorInvalidValue;
     const size_t smem = cross_block_smem(a->width, a->xw, (size_t)p.chunks);
     const int ro = (int)((a->width + XB_THREADS - 1) / XB_THREADS);
@@ -345,7 +415,10 @@ extern "C" int mb_cross_block(const mb_cross_block_args *a, mb_stream stream) {
     const dim3 grid((unsigned)a->batch), block(XB_THREADS);
     const int lpr = (int)(a->xw / 16u);
 #define XB_CASE(RO_, LPR_) \
-    if (ro == RO_ && lpr == LPR_) mb_launch(k_cross_block<RO_, LPR_>, grid, block, smem, s, kmap, vmap, p)
+    if (ro == RO_ && lpr == LPR_) { \
+        if (a->strict) mb_launch(k_cross_block<RO_, LPR_, true>, grid, block, smem, s, kmap, vmap, p); \
+        else mb_launch(k_cross_block<RO_, LPR_, false>, grid, block, smem, s, kmap, vmap, p); \
+    }
     XB_CASE(1, 2); XB_CASE(1, 8); XB_CASE(2, 8); XB_CASE(3, 8); XB_CASE(4, 8);
 #undef XB_CASE
     return mb_check_launch();
@@ -354,10 +427,15 @@ extern "C" int mb_cross_block(const mb_cross_block_args *a, mb_stream stream) {
 extern "C" int mb_cross_block_init(void) {
     int rc = 0;
     const int bytes = 225 * 1024;
-    rc |= (int)cudaFuncSetAttribute(k_cross_block<1, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    rc |= (int)cudaFuncSetAttribute(k_cross_block<1, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    rc |= (int)cudaFuncSetAttribute(k_cross_block<2, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    rc |= (int)cudaFuncSetAttribute(k_cross_block<3, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    rc |= (int)cudaFuncSetAttribute(k_cross_block<4, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    rc |= (int)cudaFuncSetAttribute(k_cross_block<1, 2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    rc |= (int)cudaFuncSetAttribute(k_cross_block<1, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    rc |= (int)cudaFuncSetAttribute(k_cross_block<1, 8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    rc |= (int)cudaFuncSetAttribute(k_cross_block<1, 8, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    rc |= (int)cudaFuncSetAttribute(k_cross_block<2, 8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    rc |= (int)cudaFuncSetAttribute(k_cross_block<2, 8, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    rc |= (int)cudaFuncSetAttribute(k_cross_block<3, 8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    rc |= (int)cudaFuncSetAttribute(k_cross_block<3, 8, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    rc |= (int)cudaFuncSetAttribute(k_cross_block<4, 8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    rc |= (int)cudaFuncSetAttribute(k_cross_block<4, 8, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     return rc;
 }

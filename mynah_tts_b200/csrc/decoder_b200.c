@@ -687,9 +687,9 @@ static int enqueue(mb_decoder *d, size_t bucket, int mode, unsigned *count) {
         a.launched = count;
         P(PC_ATTN_SELF, mb_attention(&a, s));
         P(PC_O_SELF, product(d, &L->o_self, NULL, d->attn, d->x, W, nb, MB_EPI_RESIDUAL, count));
-        /* int8, non-strict: the whole cross-attention block, with the norm before the
-         * feed-forward product, is one launch with one CTA per stream */
-        const int xb = d->use_xblock && q && !st->strict && L->q_cross.qtype == MB_INT8 &&
+        /* int8: the whole cross-attention block, with the norm before the feed-forward
+         * product, is one launch with one CTA per stream */
+        const int xb = d->use_xblock && q && L->q_cross.qtype == MB_INT8 &&
                        L->o_cross.qtype == MB_INT8 && L->ffn_up.qtype == MB_INT8 &&
                        mb_cross_block_supported(W, XW, d->T);
         if (xb) {
@@ -717,6 +717,8 @@ static int enqueue(mb_decoder *d, size_t bucket, int mode, unsigned *count) {
             cb.qx = d->qx;
             cb.sx = d->sx;
             cb.status = d->d_status;
+            cb.strict = st->strict;
+            cb.exp_tab = st->libm.exp_tab;
             P(PC_XBLOCK, mb_cross_block(&cb, s));
             *count += 1u;
             P(PC_FFN_UP, product(d, &L->ffn_up, NULL, d->nrm, d->hidden, F, nb, MB_EPI_GELU, count));

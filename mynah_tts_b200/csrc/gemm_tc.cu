@@ -319,7 +319,22 @@ k_gemm_i8_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
                 if (p.status != nullptr) atomicOr(p.status, 16);
             }
         }
-        if (row_ok && whole) {
+        if (row_ok && whole && p.epilogue == MB_EPI_GELU && p.strict) {
+            // host-libm GELU: the table words of all lanes are requested before the first
+            // double-precision tanh, so the lookups overlap instead of queueing one by one
+            float y[BN], c[BN];
+            uint32_t word[BN];
+#pragma unroll
+            for (int j = 0; j < BN; ++j) {
+                y[j] = __fmul_rn(__fmul_rn((float)v[j], ws), lane_scale[j]);
+                if (p.bias != nullptr) y[j] = __fadd_rn(y[j], bias);
+                c[j] = gelu_tanh_arg(y[j]);
+                word[j] = b0 + j < nb ? mb_tanh_fetch(c[j], p.tanh_tab) : 0x88888888u;
+            }
+#pragma unroll
+            for (int j = 0; j < BN; ++j)
+                if (b0 + j < nb) p.out[(long)(b0 + j) * p.out_stride + row] = gelu_tanh_finish(y[j], c[j], word[j], p.tanh_tab != nullptr);
+        } else if (row_ok && whole) {
 #pragma unroll
             for (int j = 0; j < BN; ++j) {
                 const int b = b0 + j;
@@ -328,8 +343,7 @@ k_gemm_i8_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
                     if (p.bias != nullptr) y = __fadd_rn(y, bias);
                     float *dst = p.out + (long)b * p.out_stride + row;
                     if (p.epilogue == MB_EPI_RESIDUAL) *dst = __fadd_rn(prior[j], y);
-                    else if (p.epilogue == MB_EPI_GELU)
-                        *dst = p.strict ? gelu_tanh<true>(y, p.tanh_tab) : gelu_tanh<false>(y, nullptr);
+                    else if (p.epilogue == MB_EPI_GELU) *dst = gelu_tanh<false>(y, nullptr);
                     else *dst = y;
                 }
             }
@@ -538,16 +552,26 @@ k_gemm_i4_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
             lane_scale[j] = b < nb ? p.sx[b] : 0.0f;
             prior[j] = (p.epilogue == MB_EPI_RESIDUAL && b < nb) ? p.out[(long)b * p.out_stride + row] : 0.0f;
         }
+        float y4[4], c4[4];
+        uint32_t word4[4];
+        const bool gelu_host = p.epilogue == MB_EPI_GELU && p.strict;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            y4[j] = __fmul_rn(accf[j], lane_scale[j]);
+            if (p.bias != nullptr) y4[j] = __fadd_rn(y4[j], bias);
+            c4[j] = gelu_tanh_arg(y4[j]);
+            // the four table words are requested together (see the int8 kernel)
+            word4[j] = (gelu_host && b0 + col0 + j < nb) ? mb_tanh_fetch(c4[j], p.tanh_tab) : 0x88888888u;
+        }
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int b = b0 + col0 + j;
             if (b < nb) {
-                float y = __fmul_rn(accf[j], lane_scale[j]);
-                if (p.bias != nullptr) y = __fadd_rn(y, bias);
+                const float y = y4[j];
                 float *dst = p.out + (long)b * p.out_stride + row;
                 if (p.epilogue == MB_EPI_RESIDUAL) *dst = __fadd_rn(prior[j], y);
                 else if (p.epilogue == MB_EPI_GELU)
-                    *dst = p.strict ? gelu_tanh<true>(y, p.tanh_tab) : gelu_tanh<false>(y, nullptr);
+                    *dst = p.strict ? gelu_tanh_finish(y, c4[j], word4[j], p.tanh_tab != nullptr) : gelu_tanh<false>(y, nullptr);
                 else *dst = y;
             }
         }

@@ -23,7 +23,7 @@ __global__ void __launch_bounds__(256)
 k_layernorm(const float *__restrict__ in, float *__restrict__ out, const float *__restrict__ gain,
             const float *__restrict__ bias, int width, float eps, int8_t *__restrict__ qx,
             float *__restrict__ sx, const int *__restrict__ n_active) {
-    extern __shared__ float row[];
+    extern __shared__ __align__(16) float row[];
     __shared__ float red[96];
     __shared__ float stat[2];
     // gain and bias are constants: they are staged while the preceding launch still runs
@@ -42,65 +42,17 @@ k_layernorm(const float *__restrict__ in, float *__restrict__ out, const float *
     const float *x = in + (size_t)r * width;
     for (int i = threadIdx.x; i < width; i += blockDim.x) row[i] = x[i];
     __syncthreads();
-    float mean, variance;
+    float *y_out = out == nullptr ? nullptr : out + (size_t)r * width;
+    int8_t *q = qx == nullptr ? nullptr : qx + (size_t)r * width;
+    float sxv;
     if (STRICT) {
-        // mean: one sequential chain over the row, as `mean += x[i]` does.
-        if (threadIdx.x == 0) {
-            float m = 0.0f;
-            for (int i = 0; i < width; ++i) m = __fadd_rn(m, row[i]);
-            stat[0] = __fdiv_rn(m, (float)width);
-        }
-        __syncthreads();
-        mean = stat[0];
-        // squares in parallel (each rounded once), then one sequential chain.
-        float *sq = row + width;
-        for (int i = threadIdx.x; i < width; i += blockDim.x) {
-            const float d = __fsub_rn(row[i], mean);
-            sq[i] = __fmul_rn(d, d);
-        }
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            float v = 0.0f;
-            for (int i = 0; i < width; ++i) v = __fadd_rn(v, sq[i]);
-            stat[1] = v;
-        }
-        __syncthreads();
-        variance = stat[1];
+        // the reference's two sequential chains (mean, variance); the squares sit behind the row
+        sxv = mb_ln_block_strict(row, width, gain, bias, eps, gs, stat, red, y_out, qx != nullptr, q);
     } else {
         // the routine shared with the products' fused prologue
-        const float sxv = mb_ln_block<1>(row, width, gs, bias == nullptr ? nullptr : bs, eps, red, out == nullptr ? nullptr : out + (size_t)r * width,
-                                      qx != nullptr, qx == nullptr ? nullptr : qx + (size_t)r * width);
-        if (qx != nullptr && threadIdx.x == 0) sx[r] = sxv;
-        return;
+        sxv = mb_ln_block<1>(row, width, gs, bias == nullptr ? nullptr : bs, eps, red, y_out, qx != nullptr, q);
     }
-    const float scale =
-        __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(variance, (float)width), eps)));
-    float amax = 0.0f;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        const float y = __fadd_rn(
-            __fmul_rn(__fmul_rn(__fsub_rn(row[i], mean), scale), gain[i]),
-            bias == nullptr ? 0.0f : bias[i]);
-        if (out != nullptr) out[(size_t)r * width + i] = y;
-        if (qx != nullptr) {
-            row[i] = y;  // each thread rereads only its own elements below
-            amax = fmaxf(amax, fabsf(y));
-        }
-    }
-    if (qx == nullptr) return;
-    amax = block_max(amax, red);
-    int8_t *q = qx + (size_t)r * width;
-    if (amax == 0.0f) {
-        for (int i = threadIdx.x; i < width; i += blockDim.x) q[i] = 0;
-        if (threadIdx.x == 0) sx[r] = 0.0f;
-        return;
-    }
-    const float inv = __fdiv_rn(127.0f, amax);
-    for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        int v = round_half_away(__fmul_rn(row[i], inv));
-        v = min(127, max(-127, v));
-        q[i] = (int8_t)v;
-    }
-    if (threadIdx.x == 0) sx[r] = __fdiv_rn(amax, 127.0f);
+    if (qx != nullptr && threadIdx.x == 0) sx[r] = sxv;
 }
 
 // Per-row int8 activation quantization (src/qmat.c:93-113).
@@ -629,8 +581,8 @@ inline unsigned blocks_for(size_t n) { return (unsigned)((n + 255) / 256); }
 extern "C" int mb_layernorm(const float *in, float *out, const float *gain, const float *bias,
                             size_t rows, size_t width, float eps, int8_t *qx, float *sx,
                             const int *n_active, int strict, mb_stream stream) {
-    /* strict: the row and its squares; else the row, the gain and (if any) the bias */
-    const size_t smem = width * sizeof(float) * ((!strict && bias != NULL) ? 3u : 2u);
+    /* strict: the row and its squares; else the row, the gain and the bias slot */
+    const size_t smem = width * sizeof(float) * (strict ? 2u : 3u);
     if (rows == 0 || width == 0 || smem > 48u * 1024u) return (int)cudaErrorInvalidValue;
     cudaStream_t s = (cudaStream_t)stream;
     if (strict)

@@ -209,7 +209,8 @@ size_t mb_attention_counters(size_t batch, size_t heads);
  * int8 quantization of the context, the output product added to the residual row, and the
  * next layer norm (gain_ff) with int8 quantization for the feed-forward product.  int8
  * weights only; the arithmetic and its order are those of the separate launches
- * (mb_layernorm, mb_gemv / mb_gemm_tc, mb_attention), so the bits are the same. */
+ * (mb_layernorm, mb_gemv / mb_gemm_tc, mb_attention) in the same mode (strict or not), so the
+ * bits are the same. */
 typedef struct {
     float *x;                    /* [batch][width] residual rows, updated in place */
     const float *gain_query;     /* [width] */
@@ -229,6 +230,8 @@ typedef struct {
     int8_t *qx;                  /* [batch][width] out: quantized second norm */
     float *sx;                   /* [batch] */
     int *status;
+    int strict;                  /* reference summation order and host-libm expf (any lane count) */
+    const uint32_t *exp_tab;     /* strict: host-libm correction table or NULL */
 } mb_cross_block_args;
 int mb_cross_block_init(void);
 int mb_cross_block_supported(size_t width, size_t xw, size_t rows);

@@ -18,7 +18,8 @@ __global__ void k_libm_delta(const float *__restrict__ host_vals, uint32_t first
         const size_t i = t * 8 + j;
         if (i >= count) break;
         const float a = __int_as_float((int)(first_bits + (uint32_t)i));
-        const float base = is_exp ? (float)exp(-(double)a) : (float)tanh((double)a);
+        const uint32_t bits = first_bits + (uint32_t)i;
+        const float base = is_exp ? mb_exp_base(a, bits, true) : mb_tanh_base(a, bits, true);
         const int delta = __float_as_int(host_vals[i]) - __float_as_int(base);
         if (delta < -8 || delta > 7) {
             atomicOr(status, 4);   // the table format cannot express this libm

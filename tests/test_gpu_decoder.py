@@ -111,8 +111,9 @@ def test_stream_result_does_not_depend_on_batch(strict, tiny_model, tiny_memory)
     ps.close(); pm.close()
 
 
+@pytest.mark.parametrize("strict", [False, True])
 @pytest.mark.parametrize("shape_name", ["tiny", "full"])
-def test_cross_block_launch_matches_separate_launches(shape_name, tiny_model, tiny_memory, monkeypatch):
+def test_cross_block_launch_matches_separate_launches(shape_name, strict, tiny_model, tiny_memory, monkeypatch):
     """The one-launch cross-attention block (norm, query product, attention, output
     product, norm) gives the bits of the five launches it replaces, and the tensor-core
     product split along K over a cluster the bits of the unsplit one, at 1, 2, 5, 16 and
@@ -137,7 +138,7 @@ def test_cross_block_launch_matches_separate_launches(shape_name, tiny_model, ti
             monkeypatch.setenv("MYNAH_B200_NO_CROSS_BLOCK", "1")
         if mode == "unsplit":
             monkeypatch.setenv("MYNAH_B200_NO_KSPLIT", "1")
-        be = Backend("int8", strict=False)
+        be = Backend("int8", strict=strict)
         dec = Decoder(be, model, capacity=16, slots=64)
         for s in range(64):
             # every slot its own text states: a rolled copy of the same cross K/V
