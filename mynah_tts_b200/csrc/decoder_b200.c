@@ -467,10 +467,11 @@ static int product(mb_decoder *d, const mb_dev_weight *w, const float *bias, con
     return product_fused(d, w, bias, act_f32, out, out_stride, nb, epilogue, MB_FUSE_NONE, NULL, count);
 }
 
-/* One lane, int8 weights, non-strict: norms and the hidden-row quantization ride in the
- * products that consume them (every launch saved is ~5 us of a ~790 us step). */
+/* One lane, int8 weights: norms and the hidden-row quantization ride in the products that
+ * consume them (every launch saved is ~5 us of the step), in strict mode with the
+ * reference's summation order. */
 static int fuse_one_lane(const mb_decoder *d, size_t nb) {
-    return nb == 1 && d->use_fuse1 && d->st->quant == MB_INT8 && !d->st->strict;
+    return nb == 1 && d->use_fuse1 && d->st->quant == MB_INT8;
 }
 
 static int norm(mb_decoder *d, const float *in, float *out, const float *gain, size_t nb,

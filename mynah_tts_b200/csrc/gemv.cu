@@ -93,6 +93,7 @@ __global__ void __launch_bounds__(WARPS * 32) k_gemv(GemvP p) {
 
     __shared__ float fuse_red[96];
     __shared__ float fuse_sx;
+    __shared__ float fuse_stat[2];
     // Constants are requested before the dependency wait, so they land while the preceding
     // launch finishes: this warp's first weight pieces (int8) and the fused norm's gain.
     uint4 wpre[MAX_PRELOAD];
@@ -131,9 +132,13 @@ __global__ void __launch_bounds__(WARPS * 32) k_gemv(GemvP p) {
                 }
             }
             __syncthreads();
+            // (strict: the reference's sequential sums, squares behind the gain; the plain
+            // quantization is exact in either mode)
             const float sxv = p.fuse == MB_FUSE_LN
-                                  ? mb_ln_block<2>(rowf, (int)k, fuse_gain_s, nullptr, p.fuse_eps, fuse_red, nullptr, true,
-                                                reinterpret_cast<int8_t *>(act))
+                                  ? (STRICT ? mb_ln_block_strict(rowf, (int)k, fuse_gain_s, nullptr, p.fuse_eps, fuse_gain_s + k,
+                                                                 fuse_stat, fuse_red, nullptr, true, reinterpret_cast<int8_t *>(act))
+                                            : mb_ln_block<2>(rowf, (int)k, fuse_gain_s, nullptr, p.fuse_eps, fuse_red, nullptr, true,
+                                                             reinterpret_cast<int8_t *>(act)))
                                   : mb_quant_block(rowf, (int)k, fuse_red, reinterpret_cast<int8_t *>(act));
             if (threadIdx.x == 0) fuse_sx = sxv;
         } else if (QUANT) {
@@ -420,7 +425,7 @@ int launch_tiled(const GemvP &p, size_t groups, cudaStream_t s) {
     const bool quant = (QT == MB_INT8 || QT == MB_INT4);
     size_t smem = (size_t)BT * (quant ? p.k : p.k * 4);
     if (QT == MB_INT4) smem += (size_t)WARPS * 32 * p.cpl * BT * sizeof(float);
-    if (p.fuse != MB_FUSE_NONE) smem += 16u + 2u * (size_t)p.k * sizeof(float);   /* the f32 row and the gain */
+    if (p.fuse != MB_FUSE_NONE) smem += 16u + (STRICT ? 3u : 2u) * (size_t)p.k * sizeof(float);   /* the f32 row, the gain, (strict) the squares */
     if (smem > 160u * 1024u) return (int)cudaErrorInvalidValue;
     if (QT == MB_INT8 && it == 1)
         mb_launch(k_gemv<QT, BT, STRICT, QT == MB_INT8>, dim3(blocks, (unsigned)groups, (unsigned)btiles), dim3(WARPS * 32), smem, s, q);
@@ -482,7 +487,7 @@ extern "C" int mb_gemv(const mb_gemv_args *a, mb_stream stream) {
         return (int)cudaErrorInvalidValue;
     const bool quant = a->qtype == MB_INT8 || a->qtype == MB_INT4;
     const bool fused = a->fuse != MB_FUSE_NONE;
-    if (fused && (a->qtype != MB_INT8 || a->batch != 1 || a->strict || a->fx == nullptr || a->groups > 1 ||
+    if (fused && (a->qtype != MB_INT8 || a->batch != 1 || a->fx == nullptr || a->groups > 1 || (a->k % 4u) != 0 ||
                   (a->fuse == MB_FUSE_LN && a->fuse_gain == nullptr)))
         return (int)cudaErrorInvalidValue;
     if (quant && ((!fused && (a->qx == nullptr || a->sx == nullptr)) || a->scales == nullptr))

@@ -137,7 +137,7 @@ typedef struct {
     int epilogue;         /* MB_EPI_* */
     int strict;           /* GELU epilogue: reference-order transcendental */
     const uint32_t *tanh_tab; /* strict GELU: host-libm correction table or NULL */
-    /* Fused prologue (int8 weights, batch == 1, non-strict): instead of reading qx/sx the
+    /* Fused prologue (int8 weights, batch == 1): instead of reading qx/sx the
      * kernel makes them from the f32 row fx: MB_FUSE_LN layer-normalizes (gain, eps) and
      * quantizes it exactly as mb_layernorm with qx does, MB_FUSE_QUANT quantizes it as
      * mb_quant_rows does.  Every CTA repeats the row work; the step loses a launch. */

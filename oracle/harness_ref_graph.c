@@ -24,6 +24,10 @@ typedef struct {
 
 #define REF_EXPORT __attribute__((visibility("default")))
 
+/* Defined only in the build that binds the reference's CUDA device to libmynah_b200.so
+ * (harness_ref_cuda.c); absent (NULL) in the CPU builds. */
+extern int ref_backend_light_up(mynah_backend *backend) __attribute__((weak));
+
 /* hidden_dim/layers fill mynah_tts_model_info the way model.json would
  * (src/mynah_tts.c:214-266); qtype is the enum of src/qmat.c:36
  * (0 f32, 1 int8, 2 int4, 3 f16). */
@@ -40,8 +44,16 @@ REF_EXPORT ref_model *ref_model_open(const char *safetensors_path, unsigned hidd
     r->model.info.codebook_size = codebook_size;
     r->model.info.audio_vocab_size = vocab;
     r->model.info.audio_eos_id = eos_id;
+    /* the B200 build opens the reference's CUDA device (device ordinal, weight format and
+     * strictness come from the environment, as for mynah_backend_open in the application) */
+    const mynah_tts_device device = ref_backend_light_up != NULL ? MYNAH_TTS_DEVICE_CUDA : MYNAH_TTS_DEVICE_CPU;
     if (mynah_weights_open(safetensors_path, &r->model.tts, error, cap) != 0 ||
-        mynah_backend_open(MYNAH_TTS_DEVICE_CPU, &r->model.backend, error, cap) != 0) {
+        mynah_backend_open(device, &r->model.backend, error, cap) != 0) {
+        free(r);
+        return NULL;
+    }
+    if (ref_backend_light_up != NULL && ref_backend_light_up(r->model.backend) != 0) {
+        snprintf(error, cap, "could not wire the resident-attention ops");
         free(r);
         return NULL;
     }
@@ -119,6 +131,29 @@ REF_EXPORT int ref_decoder_step_batch(ref_model *r, ref_decoder **decoders, cons
 REF_EXPORT int ref_decoder_run(ref_model *r, ref_decoder *d, const float *rows, size_t count,
                                float *out_last, char *error, size_t cap) {
     return decoder_run(&r->model, &d->cache, rows, count, out_last, NULL, error, cap);
+}
+
+/* 1 when decoder_run's resident path (src/graph.c:3363-3368) is open for this model. */
+REF_EXPORT int ref_model_resident(const ref_model *r) {
+    return mynah_backend_has_dev_ops(r->model.backend) && mynah_backend_has_attention_dev(r->model.backend);
+}
+REF_EXPORT const char *ref_model_backend_name(const ref_model *r) { return mynah_backend_name(r->model.backend); }
+
+/* The resident path keeps the self K/V on the device (src/graph.c:2901-2961): copy rows
+ * [0, length) of every layer back into the host cache so a test can read them.  Returns -1
+ * when the cache has no device copy. */
+REF_EXPORT int ref_decoder_download_kv(ref_model *r, ref_decoder *d, char *error, size_t cap) {
+    decoder_cache *c = &d->cache;
+    if (!c->dev_attention_allocated) return -1;
+    if (mynah_backend_sync(r->model.backend, error, cap) != 0) return -1;
+    for (size_t layer = 0; layer < c->layers; ++layer) {
+        const size_t off = layer * c->capacity * c->width;
+        if (c->length > 0 &&
+            (mynah_backend_d2h(r->model.backend, c->dev_self_k + off, c->self_k + off, c->length * c->width, error, cap) != 0 ||
+             mynah_backend_d2h(r->model.backend, c->dev_self_v + off, c->self_v + off, c->length * c->width, error, cap) != 0))
+            return -1;
+    }
+    return 0;
 }
 
 /* codes are [codebooks][code_stride] as in src/graph.c:760-766. */

@@ -21,7 +21,9 @@ import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 PORT_SO = os.path.join(HERE, "liboracle_port.so")
-REF_SO = {kind: os.path.join(HERE, "_ref", f"libmynah_ref_{kind}.so") for kind in ("strict", "fast")}
+# "b200": the reference's graph.c + backend.c (CUDA branch) linked against libmynah_b200.so,
+# i.e. the reference's own decoder_run driving the library under test (needs a GPU to open)
+REF_SO = {kind: os.path.join(HERE, "_ref", f"libmynah_ref_{kind}.so") for kind in ("strict", "fast", "b200")}
 
 F32, INT8, INT4, F16 = 0, 1, 2, 3
 QTYPES = {"f32": F32, "int8": INT8, "int4": INT4, "f16": F16}
@@ -418,6 +420,10 @@ class Ref:
                                                c_float_p, sz, C.c_char_p, sz]
         lib.ref_decoder_run.argtypes = [C.c_void_p, C.c_void_p, c_float_p, sz, c_float_p,
                                         C.c_char_p, sz]
+        lib.ref_model_resident.argtypes = [C.c_void_p]
+        lib.ref_model_backend_name.restype = C.c_char_p
+        lib.ref_model_backend_name.argtypes = [C.c_void_p]
+        lib.ref_decoder_download_kv.argtypes = [C.c_void_p, C.c_void_p, C.c_char_p, sz]
         lib.ref_heads_argmax.argtypes = [C.c_void_p, c_float_p, sz, C.c_int, c_uint_p, c_float_p,
                                          C.c_char_p, sz]
         lib.ref_greedy_decode.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), sz, c_uint_p, sz, sz,
@@ -585,6 +591,15 @@ class RefModel:
     def new_decoder(self, memory: np.ndarray, capacity: int) -> "RefDecoder":
         return RefDecoder(self, memory, capacity)
 
+    @property
+    def resident(self) -> bool:
+        """True when decoder_run takes its resident device path (src/graph.c:3363-3368)."""
+        return bool(self.ref.lib.ref_model_resident(self.handle))
+
+    @property
+    def backend_name(self) -> str:
+        return self.ref.lib.ref_model_backend_name(self.handle).decode()
+
     def step_batch(self, decoders, rows: np.ndarray) -> np.ndarray:
         rows = np.ascontiguousarray(rows, np.float32)
         outs = np.empty_like(rows)
@@ -694,3 +709,19 @@ class RefDecoder:
 
     def step(self, row: np.ndarray) -> np.ndarray:
         return self.model.step_batch([self], row.reshape(1, -1))[0]
+
+    def run(self, rows: np.ndarray) -> np.ndarray:
+        """decoder_run (src/graph.c:3286-3654) over `rows` new rows; the output-norm row of
+        the last one."""
+        rows = np.ascontiguousarray(rows, np.float32).reshape(-1, self.model.synth.shape.width)
+        out = np.empty((rows.shape[1],), np.float32)
+        err = C.create_string_buffer(256)
+        rc = self.lib.ref_decoder_run(self.model.handle, self.handle, _fp(rows), rows.shape[0], _fp(out), err, 256)
+        assert rc == 0, err.value
+        return out
+
+    def download_kv(self):
+        """Resident path only: copy the device self K/V back into the host cache arrays."""
+        err = C.create_string_buffer(256)
+        rc = self.lib.ref_decoder_download_kv(self.model.handle, self.handle, err, 256)
+        assert rc == 0, err.value or b"no device cache"

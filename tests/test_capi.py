@@ -47,3 +47,15 @@ def test_library_exports_every_declared_symbol():
     assert declared <= exported
     # nothing but the declared ABI leaks out of the library
     assert {e for e in exported if not e.startswith("_")} == declared
+
+
+def test_reference_seam_build_links_against_this_library():
+    """oracle/_ref/libmynah_ref_b200.so -- the reference's graph.c and backend.c (CUDA branch)
+    -- resolves every mynah_cuda_* symbol it binds from libmynah_b200.so (no compute here)."""
+    import ctypes
+    from oracle import oracle as O
+    if not O.have_ref("b200"):
+        import pytest
+        pytest.skip("compiled reference absent")
+    lib = ctypes.CDLL(O.REF_SO["b200"])          # RTLD_NOW: fails on any unresolved symbol
+    assert hasattr(lib, "ref_backend_light_up") and hasattr(lib, "ref_decoder_run")

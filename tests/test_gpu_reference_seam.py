@@ -1,0 +1,76 @@
+"""The reference's own decoder_run driving this library through the backend seam.
+
+oracle/_ref/libmynah_ref_b200.so is the reference's src/graph.c and src/backend.c (its CUDA
+branch, -DMYNAH_ENABLE_CUDA) linked against libmynah_b200.so, plus the seven assignments
+that wire the resident-attention ops (oracle/harness_ref_cuda.c).  decoder_run(count = 1)
+then takes its resident path (src/graph.c:3363-3491): h2d, batch_begin, layer_norm_inplace,
+matmul_d2d, self_attention_dev, residual_inplace, cross_attention_dev, gelu_inplace, sync,
+d2h -- every one of them served by this library, with MYNAH_QUANT quantizing behind the
+seam.  The same rows go through the reference's CPU build (decoder_run ->
+decoder_step_batch); in strict mode hidden rows and KV must agree bit for bit for the
+integer formats.
+"""
+import os
+
+import numpy as np
+import pytest
+
+from conftest import rel_err
+from mynah_tts_b200 import synth
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+NAMES = {O.F32: "f32", O.INT8: "int8", O.INT4: "int4"}
+
+
+def _open_pair(model, qtype, strict, monkeypatch):
+    monkeypatch.setenv("MYNAH_QUANT", NAMES[qtype])
+    monkeypatch.setenv("MYNAH_B200_STRICT", "1" if strict else "0")
+    monkeypatch.delenv("MYNAH_GPU_RESIDENT", raising=False)
+    gpu = O.RefModel(model, qtype, "b200")
+    cpu = O.RefModel(model, qtype, "strict")
+    return gpu, cpu
+
+
+@pytest.mark.skipif(not (O.have_ref("b200") and O.have_ref("strict")), reason="compiled reference absent")
+@pytest.mark.parametrize("shape_name,qtype,strict", [("tiny", O.INT8, True), ("tiny", O.INT4, True),
+                                                     ("tiny", O.F32, True), ("tiny", O.INT8, False),
+                                                     ("full", O.INT8, True)])
+def test_reference_decoder_run_resident_path(shape_name, qtype, strict, tiny_model, tiny_memory, monkeypatch):
+    if shape_name == "tiny":
+        shape, model, memory, frames = synth.TINY, tiny_model, tiny_memory, 16
+    else:
+        shape = synth.MAGPIE_357M
+        model = synth.make_model(shape, seed=41)
+        memory = synth.make_memory(shape, seed=141)
+        frames = 8
+    gpu, cpu = _open_pair(model, qtype, strict, monkeypatch)
+    assert gpu.backend_name == "cuda" and gpu.resident          # the resident step is open ...
+    assert cpu.backend_name != "cuda" and not cpu.resident      # ... and only there
+    dg, dc = gpu.new_decoder(memory, frames + 4), cpu.new_decoder(memory, frames + 4)
+    exact = strict and qtype in (O.INT8, O.INT4)
+    tol = 2e-5 if strict else {O.INT8: 1e-2, O.INT4: 2e-2, O.F32: 1e-3}[qtype]
+    # decoder_cache_init ran its kv_net products through the seam's host matmul (f32 whatever
+    # MYNAH_QUANT says, src/graph.c:3002-3027)
+    assert rel_err(dg.cross_k, dc.cross_k) < 1e-5 and rel_err(dg.cross_v, dc.cross_v) < 1e-5
+    if strict:
+        assert np.array_equal(dg.cross_k, dc.cross_k) and np.array_equal(dg.cross_v, dc.cross_v)
+    codes = synth.make_codes(shape, seed=17, frames=frames)
+    for f in range(frames):
+        row = cpu.embed_frame(codes[f])
+        want = dc.run(row)
+        got = dg.run(row)
+        assert rel_err(got, want) < tol, (shape_name, f)
+        if exact:
+            assert np.array_equal(got, want), (shape_name, NAMES[qtype], f)
+    assert dg.length == frames and dc.length == frames
+    # the resident path keeps K/V on the device: the host arrays of the GPU-backed cache were
+    # never written, the device copy holds what the CPU build appended
+    assert not dg.self_k[:, :frames].any()
+    dg.download_kv()
+    assert rel_err(dg.self_k[:, :frames], dc.self_k[:, :frames]) < tol
+    assert rel_err(dg.self_v[:, :frames], dc.self_v[:, :frames]) < tol
+    if exact:
+        assert np.array_equal(dg.self_k[:, :frames], dc.self_k[:, :frames])
+        assert np.array_equal(dg.self_v[:, :frames], dc.self_v[:, :frames])
+    dg.close(); dc.close(); gpu.close(); cpu.close()
