@@ -14,6 +14,13 @@ the data path; NCCL is used only for the barrier and the max over ranks).
     python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...
     python bench.py --impl reference
 
+The timed mode is the strict one (reference summation order, the host libm's
+expf/tanhf): the mode whose greedy token streams equal the reference's.  Lane 0
+of rank 0 carries the fixture request of tests/golden/golden.npz (seed 21) inside
+the timed job, and the line says whether its 512 tokens came out identical
+(`token_parity`).  `--mode fast` times the tolerance-parity mode instead; by
+default its throughput is reported beside the headline as `fast`.
+
 Prints ONE JSON line on rank 0.
 """
 from __future__ import annotations
@@ -126,25 +133,39 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------- reference arm
-def cpu_reference_job(shape, model, streams: int, frames: int, threads: int | None):
+def cpu_model_name() -> str:
+    try:
+        with open("/proc/cpuinfo") as f:
+            for line in f:
+                if line.startswith("model name"):
+                    return line.split(":", 1)[1].strip()
+    except OSError:
+        pass
+    return "unknown"
+
+
+def cpu_reference_job(shape, model, streams: int, frames: int, threads: int | None, start: int = 0):
     """`streams` greedy streams x `frames` frames through the reference's own CPU
     code (oracle/_ref, its default x86 flags) in groups of at most 16 (its batch
-    cap, src/graph.c:12); falls back to the C restatement where the compiled
-    reference is absent.  Returns (frames/s, seconds, kind, cores)."""
+    cap, src/graph.c:12), every stream starting with `start` rows already in its KV
+    cache (zero rows: the cost of a step depends on how many rows it attends, not on
+    what they hold); falls back to the C restatement where the compiled reference is
+    absent.  Returns (frames/s, seconds, kind, cores)."""
     from oracle import oracle as O
     cores = threads or os.cpu_count() or 1
     memory = synth.make_memory(shape, seed=SEED + 100)
-    start = synth.make_codes(shape, seed=SEED + 200, frames=1)
+    codes = synth.make_codes(shape, seed=SEED + 200, frames=1)
     if O.have_ref("fast"):
         rm = O.RefModel(model, O.INT8, "fast", threads=cores)
         groups = [min(16, streams - g) for g in range(0, streams, 16)]
-        decs = [[rm.new_decoder(memory, frames + 2) for _ in range(n)] for n in groups]
-        rm.greedy_decode(decs[0][:1], start, 1, 10 ** 6)          # packs the weights (first use)
-        for d in decs[0][:1]:
-            d.length = 0
+        decs = [[rm.new_decoder(memory, start + frames + 2) for _ in range(n)] for n in groups]
+        rm.greedy_decode(decs[0][:1], codes, 1, 10 ** 6)          # packs the weights (first use)
+        for group in decs:
+            for d in group:
+                d.length = start
         t0 = time.perf_counter()
         for group in decs:
-            rm.greedy_decode(group, np.repeat(start, len(group), axis=0), frames, 10 ** 6)
+            rm.greedy_decode(group, np.repeat(codes, len(group), axis=0), frames, 10 ** 6)
         dt = time.perf_counter() - t0
         for group in decs:
             for d in group:
@@ -152,15 +173,41 @@ def cpu_reference_job(shape, model, streams: int, frames: int, threads: int | No
         rm.close()
         return streams * frames / dt, dt, "reference", cores
     pm = O.PortModel(model, O.INT8)
-    ps = [pm.new_stream(memory, frames + 2) for _ in range(streams)]
+    ps = [pm.new_stream(memory, start + frames + 2) for _ in range(streams)]
+    for s in ps:
+        s.length = start
     t0 = time.perf_counter()
     for s in ps:
-        s.greedy_decode(start[0], frames, 10 ** 6)
+        s.greedy_decode(codes[0], frames, 10 ** 6)
     dt = time.perf_counter() - t0
     for s in ps:
         s.close()
     pm.close()
     return streams * frames / dt, dt, "port", 1
+
+
+def reference_sample(args):
+    """The bounded sample of the workload the CPU arm times: at most 16 streams (the
+    reference's batch cap) x --ref-frames frames centred on the job's mean position."""
+    streams = min(args.streams, 16)
+    mean_pos = args.start_position + (args.frames - 1) / 2.0
+    start = max(0, int(round(mean_pos - (args.ref_frames - 1) / 2.0)))
+    return streams, args.ref_frames, start
+
+
+def one_thread_reference(args) -> dict | None:
+    """The same sample on ONE host thread, in a process of its own (the reference sizes its
+    thread pool once per process)."""
+    cmd = [sys.executable, os.path.abspath(__file__), "--impl", "reference", "--steps", "1", "--warmup", "0",
+           "--streams", str(args.streams), "--frames", str(args.frames), "--start-position", str(args.start_position),
+           "--ref-frames", str(max(2, args.ref_frames // 4)), "--ref-threads", "1"]
+    try:
+        out = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+        line = [l for l in out.stdout.splitlines() if l.startswith("{")][-1]
+        d = json.loads(line)
+        return {"value": d["value"], "unit": "frames/s", "cores": 1, "sample": d["cpu_baseline"]["sample"]}
+    except Exception as exc:  # noqa: BLE001 - a missing 1-thread figure must not lose the line
+        return {"value": None, "error": str(exc)[:200]}
 
 
 def local_generate_extra(backend, streams: int, args) -> dict:
@@ -245,24 +292,29 @@ def run_reference(args, rank: int):
         return
     shape = synth.MAGPIE_357M
     model = synth.make_model(shape, seed=SEED)
-    streams, frames = min(args.streams, 16), args.ref_frames
+    streams, frames, start = reference_sample(args)
+    threads = args.ref_threads or None
     times = []
-    value = kind = cores = None
+    kind = cores = None
     for step in range(args.warmup + args.steps):
-        value, dt, kind, cores = cpu_reference_job(shape, model, streams, frames, None)
+        _, dt, kind, cores = cpu_reference_job(shape, model, streams, frames, threads, start)
         if step >= args.warmup:
             times.append(dt)
     ms = 1000.0 * float(np.mean(times))
     value = streams * frames / (ms / 1000.0)
-    sample = (f"{streams} streams stepped together x {frames} frames from empty KV per step "
-              f"(the reference's batch cap is 16)")
+    sample = (f"{streams} streams stepped together x {frames} frames per step, positions {start}..{start + frames - 1} "
+              f"(centred on the job's mean position; the reference's batch cap is 16), {cores} thread(s), "
+              f"{cpu_model_name()}")
+    config = workload_config(args, shape)
+    config["sampled"] = sample
     print(json.dumps({
         "impl": "reference", "metric": "frames_per_s", "value": value, "unit": "frames/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
         "data": "synthetic",
-        "config": workload_config(args, shape),
-        "cpu_baseline": {"value": value, "unit": "frames/s", "cores": cores, "kind": kind, "sample": sample},
+        "config": config,
+        "cpu_baseline": {"value": value, "unit": "frames/s", "cores": cores, "kind": kind, "sample": sample,
+                         "cpu": cpu_model_name()},
         "e2e": {"value": value, "unit": "frames/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
@@ -273,13 +325,34 @@ def workload_config(args, shape):
                          f"{'empty KV' if not args.start_position else str(args.start_position) + ' cached rows'}, Magpie-357M-shaped decoder "
                          f"(12L d768 12x64 heads, xw128 over 128 text states, ffn3072, 8 tables/heads x 2048)"),
             "streams_per_gpu": args.streams, "frames": args.frames, "quant": args.quant,
+            "mode": args.mode + (" (reference summation order and host-libm bits: token-identical to the reference)"
+                                 if args.mode == "strict" else " (tree reductions, CUDA expf/tanhf: tolerance parity)"),
             "l2": "working set (weights + f32 KV of all streams) exceeds the 126 MB L2",
             "parallelism": f"dp{args.gpus} replicas, no collective"}
 
 
 # ------------------------------------------------------------------- own arm
-# measured DRAM bytes / algorithmic bytes of one launch, from an ncu capture of that kernel
-NCU_TRAFFIC_RATIO = {"self attention": 1.132}
+def traffic_ratio(name: str):
+    """Measured DRAM bytes / algorithmic bytes of one launch of call site `name`, from the ncu
+    capture recorded in profiles/traffic.json -- valid only while the kernel's source is the
+    one that was captured (the record carries its hash).  Returns (ratio or None, provenance)."""
+    import hashlib
+    path = os.path.join(ROOT, "profiles", "traffic.json")
+    try:
+        with open(path) as f:
+            rec = json.load(f).get(name)
+    except (OSError, ValueError):
+        rec = None
+    if not rec:
+        return None, None
+    h = hashlib.sha256()
+    for rel in rec["sources"]:
+        with open(os.path.join(ROOT, rel), "rb") as f:
+            h.update(f.read())
+    if h.hexdigest() != rec["sources_sha256"]:
+        return None, f"stale: {rec['sources']} changed since the capture at commit {rec['commit']}"
+    return rec["ratio"], (f"ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch ({rec['case']}), captured at "
+                          f"commit {rec['commit']}, scaled by algorithmic bytes")
 
 
 def algorithmic_bytes(shape, name: str, batch: int, mean_len: float, qbytes: dict) -> float:
@@ -293,6 +366,8 @@ def algorithmic_bytes(shape, name: str, batch: int, mean_len: float, qbytes: dic
         return batch * (2 * (mean_len + 1) * W * 4 + 2 * W * 4 + 3 * W * 4 + W * (4 + act))
     if name == "cross attention":
         return batch * (2 * T * XW * 4 + XW * 4 + XW * (4 + act))
+    if name.startswith("cross block"):
+        return batch * (2 * T * XW * 4 + W * (4 + 4 + act)) + qbytes["q_cross"] + qbytes["o_cross"] + 2 * W * 4
     table = {"qkv product": (3 * W, W, "qkv"), "o_self product": (W, W, "o_self"),
              "q_cross product": (XW, W, "q_cross"), "o_cross product": (W, XW, "o_cross"),
              "ffn_up product(+gelu)": (F, W, "ffn_up"), "ffn_down product": (W, F, "ffn_down"),
@@ -321,20 +396,38 @@ def weight_bytes_table(shape, quant: str) -> dict:
             "quantized": quant in ("int8", "int4")}
 
 
+def step_bytes(shape, quant: str, batch: int, mean_len: float) -> float:
+    """Algorithmic bytes of one whole decoder step for `batch` streams at mean position
+    mean_len: every weight once, per stream its self K/V rows, cross K/V and row I/O."""
+    q = weight_bytes_table(shape, quant)
+    per_layer = q["qkv"] + q["o_self"] + q["q_cross"] + q["o_cross"] + q["ffn_up"] + q["ffn_down"] + 3 * shape.width * 4
+    weights = shape.layers * per_layer + q["heads"] + shape.width * 4
+    per_stream = shape.layers * (2 * (mean_len + 1) * shape.width * 4 + 2 * shape.width * 4 +
+                                 2 * shape.memory_length * shape.xattn_width * 4) + shape.tables * shape.width * 4
+    return weights + batch * per_stream
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--mode", default="strict", choices=["strict", "fast"],
+                    help="strict: reference summation order and host-libm bits (token-identical); "
+                         "fast: tree reductions and CUDA expf/tanhf (tolerance parity)")
     ap.add_argument("--streams", type=int, default=64, help="concurrent streams per GPU")
     ap.add_argument("--total-streams", type=int, default=0,
-                    help="strong scaling: this many streams in all, dealt round-robin to the ranks")
+                    help="strong scaling headline: this many streams in all, dealt round-robin to the ranks")
     ap.add_argument("--frames", type=int, default=512)
     ap.add_argument("--quant", default="int8", choices=["int8", "int4", "f16", "f32"])
     ap.add_argument("--ref-frames", type=int, default=24, help="frames per step of the CPU reference arm")
+    ap.add_argument("--ref-threads", type=int, default=0, help="host threads of the CPU reference arm (0: all)")
     ap.add_argument("--cpu-frames", type=int, default=24, help="frames of the CPU baseline sample")
-    ap.add_argument("--no-extras", action="store_true", help="skip batch-1 and matrix-pool measurements")
+    ap.add_argument("--no-extras", action="store_true", help="only the headline job (no other mode, batch-1, "
+                    "matrix-pool, partition sweep, f32 step, sampled loop, ragged int4, CPU baseline)")
+    ap.add_argument("--only", default="", choices=["", "gemv_pool", "batch1"],
+                    help="profiling aid: run only this small case (a few launches, no JSON contract)")
     ap.add_argument("--start-position", type=int, default=0,
                     help="profiling aid: every job starts with this many (zero) rows already in each "
                          "stream's KV cache, so a few frames exercise long-context launches")
@@ -363,6 +456,69 @@ def main():
     shape = synth.MAGPIE_357M
     model = synth.make_model(shape, seed=SEED)
     frames = args.frames
+    strict = args.mode == "strict"
+    peak, peak_kind = load_peaks()
+
+    def gemv_pool_case(backend):
+        """The single [3072,768] op (LayerNorm + quantization + product) streamed over 512
+        distinct matrices (1.2 GB > L2) per pass."""
+        x, w, gain, bias = synth.make_linear_case(seed=1)
+        groups = 512
+        pool = MatrixPool(backend, w, groups, bias=bias, gain=gain)
+        xs = np.repeat(x, groups, axis=0)
+        dx = backend.to_device(xs)
+        dy = backend.dev_alloc(groups * w.shape[0])
+        for _ in range(3):
+            pool.linear(dx, dy)
+        backend.timer_start()
+        passes = 10
+        for _ in range(passes):
+            pool.linear(dx, dy)
+        pool_ms = backend.timer_stop() / passes
+        gbs = pool.bytes_per_pass / (pool_ms / 1000.0) / 1e9
+        out = {"matrix": "[3072,768] " + args.quant, "matrices_per_pass": groups,
+               "bytes_per_pass": pool.bytes_per_pass, "ms_per_pass": pool_ms,
+               "gbs": gbs, "frac_of_measured_hbm": gbs / peak, "frac_of_8tbs": gbs / 8000.0,
+               "note": "LayerNorm+quant launch plus product launch per pass; cold (pool > L2)"}
+        pool.close(); dx.free(); dy.free()
+        return out
+
+    if args.only == "gemv_pool":
+        backend = Backend(args.quant, strict=strict, device=local_rank)
+        print(json.dumps({"gemv_pool": gemv_pool_case(backend)}))
+        backend.close()
+        return
+
+    def make_decoder(backend, stream_ids, capacity, golden_lane=False):
+        """A decoder holding one slot per stream of this rank; the cross K/V are synthetic except
+        for the fixture request, whose cross K/V are made on the device from its text memory."""
+        n = max(len(stream_ids), 1)
+        dec = Decoder(backend, model, capacity=capacity, slots=n, max_batch=n)
+        for slot, gid in enumerate(stream_ids):
+            if golden_lane and gid == 0:
+                dec.slot_prefill(slot, synth.make_memory(shape, seed=SEED + 100))
+            else:
+                ck, cv = synthetic_cross_kv(shape, gid)
+                dec.slot_load(slot, ck, cv)
+        return dec
+
+    def start_codes_of(stream_ids):
+        return np.stack([synth.make_codes(shape, seed=SEED + 200 + gid, frames=1)[0] for gid in stream_ids]) \
+            if stream_ids else np.zeros((0, shape.tables), np.uint32)
+
+    def timed_jobs(dec, slots, codes, n_frames, repeats, warmups, start=0):
+        """Device time (CUDA events inside the library) of `repeats` jobs after `warmups`."""
+        total = 0.0
+        toks = None
+        for it in range(warmups + repeats):
+            for sl in slots:
+                dec.slot_set_length(sl, start)
+            if slots:
+                toks, _, ms, _ = dec.greedy(slots, codes, n_frames, min_frames=10 ** 6)
+                if it >= warmups:
+                    total += ms
+        return total, toks
+
     if args.total_streams:
         # strong scaling: a fixed set of streams dealt round-robin to the ranks
         my_streams = partition_streams(args.total_streams, world, rank)
@@ -371,13 +527,17 @@ def main():
         my_streams = [rank * args.streams + i for i in range(args.streams)]
         scaling, total_streams = "weak", world * args.streams
     B = len(my_streams)
-    backend = Backend(args.quant, strict=False, device=local_rank)
-    dec = Decoder(backend, model, capacity=args.start_position + frames + 8, slots=B, max_batch=B)
-    for slot, gid in enumerate(my_streams):
-        ck, cv = synthetic_cross_kv(shape, gid)
-        dec.slot_load(slot, ck, cv)
+    backend = Backend(args.quant, strict=strict, device=local_rank)
+    golden_ok = strict and args.quant in ("int8", "int4", "f32") and frames == 512 and args.start_position == 0
+    dec = make_decoder(backend, my_streams, args.start_position + frames + 8, golden_lane=golden_ok)
     slots = list(range(B))
-    start_codes = np.stack([synth.make_codes(shape, seed=SEED + 200 + gid, frames=1)[0] for gid in my_streams])
+    start_codes = start_codes_of(my_streams)
+
+    if args.only == "batch1":
+        ms, _ = timed_jobs(dec, [0], start_codes[:1], frames, 1, 1, args.start_position)
+        print(json.dumps({"batch1": {"us_per_frame": ms * 1000.0 / frames, "mode": args.mode}}))
+        dec.close(); backend.close()
+        return
 
     def reset():
         for s in slots:
@@ -431,10 +591,29 @@ def main():
     h2d = frames * (4 * B * 4 + 16 + B * shape.tables * 4)
     d2h = frames * (16 + B * shape.tables * 4)
 
+    # ---- the partition sweep: 8, 64 and 256 streams in all, dealt over the ranks -----------
+    # (every rank takes part: the time of a total is the max over ranks)
+    strong = None
+    if not args.no_extras and not args.total_streams and args.start_position == 0:
+        strong = {}
+        for total in (8, 64, 256):
+            mine = partition_streams(total, world, rank)
+            if total == args.streams and world == 1:
+                job_ms = ms_per_step                      # the headline job itself
+            else:
+                sdec = make_decoder(backend, mine, frames + 8) if mine else None
+                ms_rank, _ = timed_jobs(sdec, list(range(len(mine))), start_codes_of(mine), frames, 1, 1) if mine else (0.0, None)
+                if sdec is not None:
+                    sdec.close()
+                barrier()
+                job_ms = reduce_max(ms_rank, world)
+            strong[str(total)] = {"streams_per_gpu": [len(partition_streams(total, world, r)) for r in range(world)],
+                                  "frames_per_s": total * frames / (job_ms / 1000.0), "ms_per_job": job_ms,
+                                  "rtf_per_stream": (job_ms / 1000.0 / frames) * FRAME_RATE}
+
     result = None
     if rank == 0:
         # ---- per-call-site device times over one more job -> roofline of the dominant kernel
-        peak, peak_kind = load_peaks()
         reset()
         dec.profile(True)
         dec.greedy(slots, start_codes, frames, min_frames=10 ** 6)
@@ -443,63 +622,84 @@ def main():
         total = sum(v[1] for v in prof.values()) or 1.0
         name, (n_launch, t_ms) = max(prof.items(), key=lambda kv: kv[1][1])
         qbytes = weight_bytes_table(shape, args.quant)
-        bytes_per_launch = algorithmic_bytes(shape, name, B, args.start_position + (frames - 1) / 2.0, qbytes)
+        mean_len = args.start_position + (frames - 1) / 2.0
+        bytes_per_launch = algorithmic_bytes(shape, name, B, mean_len, qbytes)
         avg_s = t_ms / 1000.0 / max(n_launch, 1)
         achieved = bytes_per_launch / avg_s / 1e9
-        # DRAM traffic per launch.  One ncu capture of the self-attention launch of 64 streams at
-        # position ~258 read 113.50 MB and wrote 4.66 MB for 103.1 MB of algorithmic bytes (whole
-        # 32-row cache tiles are fetched, and the per-chunk partials travel through L2); traffic
-        # grows in proportion to the rows attended, so that ratio scales this job's mean launch.
-        traffic = bytes_per_launch * NCU_TRAFFIC_RATIO[name] if name in NCU_TRAFFIC_RATIO else None
+        ratio, provenance = traffic_ratio(name)
         roofline = {"bound": "hbm", "kernel": name, "achieved": achieved, "peak": peak, "unit": "GB/s",
-                    "frac": achieved / peak, "of": peak_kind, "traffic": traffic,
-                    "traffic_source": ("ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch "
-                                       "(64 streams, position ~258), scaled by algorithmic bytes")
-                    if traffic is not None else None,
+                    "frac": achieved / peak, "of": peak_kind,
+                    "traffic": bytes_per_launch * ratio if ratio is not None else None,
+                    "traffic_source": provenance,
                     "bytes_per_launch": bytes_per_launch, "avg_launch_us": avg_s * 1e6,
                     "share_of_step": t_ms / total,
                     "timing": "CUDA events around each launch, eager replay of one job"}
         shares = {k: {"launches": v[0], "ms": round(v[1], 3), "share": round(v[1] / total, 4)}
                   for k, v in prof.items() if v[0]}
+        # the whole step against HBM: algorithmic bytes of a step at the job's mean position
+        step_b = step_bytes(shape, args.quant, B, mean_len)
+        step_us = ms_per_step * 1000.0 / frames
+        step_roof = {"bytes_per_step": step_b, "us_per_step": step_us, "gbs": step_b / (step_us * 1e-6) / 1e9,
+                     "frac_of_measured_hbm": step_b / (step_us * 1e-6) / 1e9 / peak}
+        token_parity = None
+        if golden_ok and my_streams and my_streams[0] == 0:
+            gold = os.path.join(ROOT, "tests", "golden", "golden.npz")
+            key = f"full_{args.quant}_s{SEED}_tokens"
+            with np.load(gold) as g:
+                if key in g:
+                    want = g[key].astype(np.uint32)
+                    got = np.asarray(tokens)[:, 0]
+                    bad = np.nonzero((got != want).any(axis=-1))[0]
+                    token_parity = {"lane": 0, "frames": int(frames), "fixture": f"tests/golden/golden.npz:{key}",
+                                    "identical_to_reference": bool(len(bad) == 0),
+                                    "first_divergence": int(bad[0]) if len(bad) else -1,
+                                    "where": "inside the timed job"}
         extras = {}
         if not args.no_extras:
             # batch-1 decode (weights stay L2-resident between steps: labelled so)
-            reset()
-            dec.greedy([0], start_codes[:1], frames, min_frames=10 ** 6)
-            dec.slot_set_length(0, 0)
-            _, _, ms1, _ = dec.greedy([0], start_codes[:1], frames, min_frames=10 ** 6)
-            step_us = ms1 * 1000.0 / frames
-            extras["batch1"] = {"frames_per_s": frames / (ms1 / 1000.0), "us_per_frame": step_us,
-                                "rtf": (ms1 / 1000.0 / frames) * FRAME_RATE, "note": "weights L2-resident"}
-            # the single [3072,768] op streamed over 512 distinct matrices (1.2 GB > L2) per pass
-            x, w, gain, bias = synth.make_linear_case(seed=1)
-            groups = 512
-            pool = MatrixPool(backend, w, groups, bias=bias, gain=gain)
-            xs = np.repeat(x, groups, axis=0)
-            dx = backend.to_device(xs)
-            dy = backend.dev_alloc(groups * w.shape[0])
-            for _ in range(3):
-                pool.linear(dx, dy)
-            backend.timer_start()
-            passes = 10
-            for _ in range(passes):
-                pool.linear(dx, dy)
-            pool_ms = backend.timer_stop() / passes
-            gbs = pool.bytes_per_pass / (pool_ms / 1000.0) / 1e9
-            extras["gemv_pool"] = {"matrix": "[3072,768] " + args.quant, "matrices_per_pass": groups,
-                                   "bytes_per_pass": pool.bytes_per_pass, "ms_per_pass": pool_ms,
-                                   "gbs": gbs, "frac_of_measured_hbm": gbs / peak,
-                                   "frac_of_8tbs": gbs / 8000.0,
-                                   "note": "LayerNorm+quant launch plus product launch per pass; cold (pool > L2)"}
-            pool.close(); dx.free(); dy.free()
+            ms1, _ = timed_jobs(dec, [0], start_codes[:1], frames, 1, 1, args.start_position)
+            b1_bytes = step_bytes(shape, args.quant, 1, mean_len)
+            extras["batch1"] = {"frames_per_s": frames / (ms1 / 1000.0), "us_per_frame": ms1 * 1000.0 / frames,
+                                "rtf": (ms1 / 1000.0 / frames) * FRAME_RATE, "mode": args.mode,
+                                "frac_of_measured_hbm": b1_bytes / (ms1 * 1e-3 / frames) / 1e9 / peak,
+                                "note": "weights L2-resident"}
+            # the other mode on the same jobs
+            other = "fast" if strict else "strict"
+            obe = Backend(args.quant, strict=not strict, device=local_rank)
+            odec = make_decoder(obe, my_streams, args.start_position + frames + 8)
+            oms, _ = timed_jobs(odec, slots, start_codes, frames, max(1, min(args.steps, 3)), 1, args.start_position)
+            oms /= max(1, min(args.steps, 3))
+            oms1, _ = timed_jobs(odec, [0], start_codes[:1], frames, 1, 1, args.start_position)
+            extras[other] = {"frames_per_s": B * frames / (oms / 1000.0), "ms_per_step": oms,
+                             "batch1_us_per_frame": oms1 * 1000.0 / frames,
+                             "ratio_to_headline": (B * frames / (oms / 1000.0)) / (value / world),
+                             "parity": ("tolerance (hidden rows within 1e-3 f32/f16, 2e-2 int8/int4; picks may part at "
+                                        "narrow margins)" if other == "fast" else "token-identical to the reference")}
+            odec.close(); obe.close()
+            extras["gemv_pool"] = gemv_pool_case(backend)
+            # one f32 decoder step at position 256, batch 1
+            fbe = Backend("f32", strict=strict, device=local_rank)
+            fdec = make_decoder(fbe, [0], 256 + 40)
+            fms, _ = timed_jobs(fdec, [0], start_codes_of([0]), 32, 1, 1, 256)
+            fbytes = step_bytes(shape, "f32", 1, 256 + 15.5)
+            extras["f32_step_position_256"] = {"us_per_step": fms * 1000.0 / 32, "mode": args.mode,
+                                               "gbs": fbytes / (fms * 1e-3 / 32) / 1e9,
+                                               "frac_of_measured_hbm": fbytes / (fms * 1e-3 / 32) / 1e9 / peak,
+                                               "bytes_per_step": fbytes,
+                                               "note": "f32 weights (349 MB) exceed L2: every step streams them from HBM; "
+                                                       "32 steps from position 256, batch 1"}
+            fdec.close(); fbe.close()
             extras["generate"] = local_generate_extra(backend, B, args)
             extras["ragged_int4"] = ragged_int4_extra(shape, model, local_rank, B)
         cpu = None
-        if world == 1:
-            v, dt, kind, cores = cpu_reference_job(shape, model, min(B, 16), args.cpu_frames, None)
-            cpu = {"value": v, "unit": "frames/s", "cores": cores, "kind": kind,
-                   "sample": f"{min(B, 16)} streams stepped together x {args.cpu_frames} frames from empty KV "
-                             f"({dt:.1f} s; the reference's batch cap is 16)"}
+        if world == 1 and not args.no_extras:
+            n_cpu, f_cpu, start_cpu = reference_sample(args)
+            f_cpu = args.cpu_frames
+            v, dt, kind, cores = cpu_reference_job(shape, model, n_cpu, f_cpu, None, start_cpu)
+            cpu = {"value": v, "unit": "frames/s", "cores": cores, "kind": kind, "cpu": cpu_model_name(),
+                   "sample": f"{n_cpu} streams stepped together x {f_cpu} frames, positions {start_cpu}..{start_cpu + f_cpu - 1} "
+                             f"({dt:.1f} s; the reference's batch cap is 16)",
+                   "one_thread": one_thread_reference(args)}
         result = {
             "metric": "frames_per_s", "value": value, "unit": "frames/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
@@ -511,9 +711,12 @@ def main():
             "e2e": {"value": e2e_value, "unit": "frames/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "call": "mynah_b200_decoder_frame_batch per frame, pinned host codes in / tokens out"},
             "gpu_launches": int(gpu_launches),
-            "roofline": roofline, "call_sites": shares, "cpu_baseline": cpu,
+            "roofline": roofline, "step_vs_hbm": step_roof, "call_sites": shares, "cpu_baseline": cpu,
+            "token_parity": token_parity,
             "tokens_checksum": int(np.asarray(tokens, np.uint64).sum()),
         }
+        if strong is not None:
+            result["strong"] = strong
         result.update(extras)
     dec.close()
     backend.close()

@@ -219,7 +219,9 @@ typedef struct {
 
 typedef struct {
     size_t layers, width, heads, xattn_width; /* head_width = width/heads, ffn = 4*width */
-    size_t memory_length;  /* rows of cross K/V per slot */
+    size_t memory_length;  /* most text states (rows of cross K/V) a request may have; each slot
+                            * keeps its own request's count (decoder_cache.memory_length,
+                            * src/graph.c:2820) */
     size_t capacity;       /* self-KV rows per slot (src/graph.c:3804-3806) */
     size_t slots;          /* resident requests (each owns KV) */
     size_t max_batch;      /* most slots stepped together */
@@ -241,19 +243,24 @@ int mynah_b200_decoder_create(void *state, const mynah_b200_decoder_desc *desc, 
                               char *error, size_t cap);
 void mynah_b200_decoder_destroy(void *decoder);
 
-/* Load one request into a slot: cross K/V [layers][memory_length][xattn_width]
- * as decoder_cache_init leaves them (src/graph.c:3012-3027), and optionally
- * `length` rows of existing self K/V [layers][capacity][width] (what
- * decoder_gpu_attention_init uploads, src/graph.c:2929-2953). */
+/* Load one request into a slot: its cross K/V [layers][memory_length][xattn_width]
+ * as decoder_cache_init leaves them (src/graph.c:3012-3027; memory_length is the
+ * REQUEST's own text length, 1 .. the decoder's, and also the layer stride of the
+ * two arrays), and optionally `length` rows of existing self K/V
+ * [layers][capacity][width] (what decoder_gpu_attention_init uploads,
+ * src/graph.c:2929-2953).  Cross attention of the slot then covers exactly its
+ * memory_length rows, whatever the other slots of a batch hold. */
 int mynah_b200_decoder_slot_load(void *decoder, size_t slot, const float *cross_k,
-                                 const float *cross_v, const float *self_k, const float *self_v,
-                                 size_t length, char *error, size_t cap);
+                                 const float *cross_v, size_t memory_length, const float *self_k,
+                                 const float *self_v, size_t length, char *error, size_t cap);
 /* Make a slot's cross K/V on the device from the text-encoder memory
- * [memory_length][width] (HOST): what decoder_cache_init computes on the CPU
- * (src/graph.c:3002-3027).  The slot starts at length 0. */
+ * [memory_length][width] (HOST; 1 .. the decoder's memory_length rows): what
+ * decoder_cache_init computes on the CPU (src/graph.c:3002-3027).  The slot starts
+ * at length 0. */
 int mynah_b200_decoder_slot_prefill(void *decoder, size_t slot, const float *memory,
                                     size_t memory_length, char *error, size_t cap);
-/* Copy a slot's cross K/V back: host arrays [layers][memory_length][xattn_width]. */
+/* Copy a slot's cross K/V back: host arrays [layers][M][xattn_width] with M the DECODER's
+ * memory_length; rows at and beyond the slot's own count are not part of the request. */
 int mynah_b200_decoder_slot_read_cross(void *decoder, size_t slot, float *cross_k, float *cross_v,
                                        char *error, size_t cap);
 int mynah_b200_decoder_slot_length(void *decoder, size_t slot, size_t *length, char *error, size_t cap);
@@ -366,6 +373,7 @@ int mynah_b200_decoder_frame_batch_local(void *decoder, const unsigned *slots, c
  * produces alone. */
 typedef struct {
     const float *memory;         /* [memory_length][width] text-encoder states (HOST) */
+    size_t memory_length;        /* this request's text states, 1 .. the decoder's memory_length */
     const unsigned *start_codes; /* [tables]: the frame embedded before the first step */
     size_t max_frames, min_frames;
     mynah_b200_sampler sampler;  /* advanced; allow_eos is ignored */

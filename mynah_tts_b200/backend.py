@@ -307,11 +307,14 @@ class Decoder:
         return {names[i]: (int(launches[i]), float(ms[i])) for i in range(n)}
 
     def slot_load(self, slot: int, cross_k, cross_v, self_k=None, self_v=None, length: int = 0):
+        """cross_k / cross_v: [layers, memory_length, xattn_width] of THIS request (its own
+        text length, at most the decoder's); self_k / self_v: [layers, capacity, width]."""
         ck = np.ascontiguousarray(cross_k, np.float32)
         cv = np.ascontiguousarray(cross_v, np.float32)
+        assert ck.ndim == 3 and ck.shape == cv.shape
         sk = None if self_k is None else np.ascontiguousarray(self_k, np.float32)
         sv = None if self_v is None else np.ascontiguousarray(self_v, np.float32)
-        call(capi.lib().mynah_b200_decoder_slot_load, self.handle, slot, fp(ck), fp(cv),
+        call(capi.lib().mynah_b200_decoder_slot_load, self.handle, slot, fp(ck), fp(cv), ck.shape[1],
              None if sk is None else fp(sk), None if sv is None else fp(sv), length)
 
     def slot_prefill(self, slot: int, memory: np.ndarray):
@@ -439,6 +442,7 @@ class Decoder:
             out = np.zeros((r["max_frames"], self.shape.tables), np.uint32)
             keep.append((mem, start, out))
             arr[i].memory, arr[i].start_codes = fp(mem), start.ctypes.data_as(capi.c_uint_p)
+            arr[i].memory_length = mem.shape[0]
             arr[i].max_frames, arr[i].min_frames = r["max_frames"], r.get("min_frames", 0)
             t = r.get("sampler", (0.0, 0, 0))
             arr[i].sampler.temperature, arr[i].sampler.topk, arr[i].sampler.rng_state = float(t[0]), int(t[1]), int(t[2])

@@ -72,7 +72,7 @@ class Sampler(C.Structure):
 
 
 class Request(C.Structure):
-    _fields_ = [("memory", c_float_p), ("start_codes", c_uint_p), ("max_frames", sz), ("min_frames", sz),
+    _fields_ = [("memory", c_float_p), ("memory_length", sz), ("start_codes", c_uint_p), ("max_frames", sz), ("min_frames", sz),
                 ("sampler", Sampler), ("codes", c_uint_p), ("frames_done", sz), ("eos_frame", C.c_long),
                 ("admitted_at", sz)]
 
@@ -148,7 +148,7 @@ SIGNATURES = {
     "mynah_b200_pool_bytes_per_pass": (sz, [C.c_void_p]),
     "mynah_b200_decoder_create": (C.c_int, [C.c_void_p, C.POINTER(DecoderDesc), C.POINTER(C.c_void_p), _E]),
     "mynah_b200_decoder_destroy": (None, [C.c_void_p]),
-    "mynah_b200_decoder_slot_load": (C.c_int, [C.c_void_p, sz, c_float_p, c_float_p, c_float_p, c_float_p, sz, _E]),
+    "mynah_b200_decoder_slot_load": (C.c_int, [C.c_void_p, sz, c_float_p, c_float_p, sz, c_float_p, c_float_p, sz, _E]),
     "mynah_b200_decoder_slot_prefill": (C.c_int, [C.c_void_p, sz, c_float_p, sz, _E]),
     "mynah_b200_decoder_slot_read_cross": (C.c_int, [C.c_void_p, sz, c_float_p, c_float_p, _E]),
     "mynah_b200_decoder_slot_length": (C.c_int, [C.c_void_p, sz, C.POINTER(sz), _E]),

@@ -39,6 +39,7 @@ struct AttnP {
     const float *q, *k_new, *v_new;
     float *k_cache, *v_cache;
     const int *slots, *lens, *n_active;
+    const int *valids;   // lens == nullptr: rows attended by the lane in slot s, or nullptr (p.valid)
     float *out;
     int8_t *qx;
     float *sx;
@@ -52,6 +53,7 @@ struct AttnP {
     long slot_rows;      // cache rows between consecutive slots (slot_stride / cache_stride)
     int box_cols, nbox;  // a 32-row tile is nbox TMA boxes of box_cols columns
     int depth;           // ring slots per tile kind (K, V)
+    int ps, map4d;       // k_attn_exact: 128-byte segments per tile row (odd), rank of its tensor maps
     int early;           // first tiles are requested before the dependency wait
     float scale;
 };
@@ -65,7 +67,11 @@ __device__ __forceinline__ bool lane_setup(const AttnP &p, int b, long &pos, lon
     if (b >= live) return false;
     if (slot_out != nullptr) *slot_out = slot;
     if (p.lens != nullptr) { pos = len; valid = pos + 1; }
-    else { pos = p.position; valid = p.valid; }
+    else {
+        pos = p.position;
+        valid = p.valid;
+        if (p.valids != nullptr) valid = min((long)max(p.valids[slot], 1), p.valid);
+    }
     kc = p.k_cache + slot * p.slot_stride;
     vc = p.v_cache + slot * p.slot_stride;
     return true;
@@ -632,25 +638,36 @@ bool launch_exact(const mb_attn_args *a, AttnP &p, cudaStream_t s) {
         (a->qx != nullptr && (a->counters == nullptr || a->sx == nullptr)))
         return false;
     const int sms = a->sm_count > 0 ? a->sm_count : 148;
-    int best_g = 0, best_depth = 0;
+    // Head groups per stream: enough CTAs to cover the SMs about one and a half times with
+    // groups of three or more heads (cache rows are then read in runs of 768 bytes or more),
+    // else the first count that covers them once, else as many groups as the shape allows.
+    int best_g = 0, best_depth = 0, cover_g = 0, cover_depth = 0;
     for (int g = 1; g <= p.heads; ++g) {
         if (p.heads % g != 0) continue;
         if (force_groups > 0 && g != force_groups) continue;
         const int hg = p.heads / g, cw = hg * p.hw;
         const int threads = cw > hg * 32 ? cw : hg * 32;
-        if ((cw % EX_BOX) != 0 || threads > 1024) continue;
-        // more CTAs than SMs: two of them share an SM
-        const size_t room = (long)p.batch * g > sms ? (size_t)110 * 1024 : (size_t)ROWS_SMEM_MAX;
-        int depth = 0;
-        for (int d = EX_RING_MAX; d >= 1 && depth == 0; --d)
-            if (exact_smem(hg, p.hw, p.max_chunks, d) + 1024u <= room) depth = d;
+        if ((cw % EX_SEG) != 0 || threads > 1024) continue;
+        auto depth_for = [&](size_t room) {
+            int depth = 0;
+            for (int d = EX_RING_MAX; d >= 1 && depth == 0; --d)
+                if (exact_smem(hg, p.hw, p.max_chunks, d) + 1024u <= room) depth = d;
+            return depth;
+        };
+        // more CTAs than SMs: two of them share an SM if each still gets a ring of two tiles
+        int depth = (long)p.batch * g > sms ? depth_for((size_t)110 * 1024) : 0;
+        if (depth < 2) depth = depth_for((size_t)ROWS_SMEM_MAX);
         if (depth > 2 * p.max_chunks) depth = 2 * p.max_chunks;
         if (force_depth > 0 && force_depth < depth) depth = force_depth;
         if (depth < 1) continue;
         best_g = g;
         best_depth = depth;
-        if (force_groups > 0 || (long)p.batch * g >= sms) break;   // enough CTAs to cover the SMs
+        if (force_groups > 0) break;
+        if (cover_g == 0 && (long)p.batch * g >= sms) { cover_g = g; cover_depth = depth; }
+        if (2L * p.batch * g >= 3L * sms && hg >= 3) { cover_g = g; cover_depth = depth; break; }
+        if (hg < 3 && cover_g != 0) break;
     }
+    if (cover_g != 0 && force_groups <= 0) { best_g = cover_g; best_depth = cover_depth; }
     if (best_g == 0) return false;
     const int hg = p.heads / best_g, cw = hg * p.hw;
     const int threads = cw > hg * 32 ? cw : hg * 32;
@@ -658,16 +675,32 @@ bool launch_exact(const mb_attn_args *a, AttnP &p, cudaStream_t s) {
     p.splits = 1;
     p.early = a->early_prefetch ? 1 : 0;
     p.slot_rows = p.cache_stride != 0 ? p.slot_stride / p.cache_stride : 0;
-    p.box_cols = EX_BOX;
-    p.nbox = cw / EX_BOX;
+    p.box_cols = EX_SEG;
+    p.nbox = 1;
+    p.ps = exact_pitch_segments(hg, p.hw);
     size_t rows = a->cache_rows;
     if (rows == 0) rows = (size_t)(p.valid > p.position + 1 ? p.valid : p.position + 1);
+    const size_t nseg = (size_t)cw / EX_SEG, row_bytes = (size_t)p.cache_stride * 4u;
     CUtensorMap kmap, vmap;
-    if (!mb_make_map_2d(&kmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a->k_cache, rows, (size_t)p.cache_stride,
-                        (size_t)p.cache_stride * 4u, EX_BOX, CHUNK, CU_TENSOR_MAP_SWIZZLE_128B) ||
-        !mb_make_map_2d(&vmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a->v_cache, rows, (size_t)p.cache_stride,
-                        (size_t)p.cache_stride * 4u, EX_BOX, CHUNK, CU_TENSOR_MAP_SWIZZLE_128B))
-        return false;
+    // (float of a segment, segment of the group, group, cache row): a box of ps segments is
+    // one wider than the group's when that count is even; the extra one is never fetched
+    const size_t dims4[4] = {EX_SEG, nseg, (size_t)best_g, rows};
+    const size_t strides4[3] = {EX_SEG * 4u, (size_t)cw * 4u, row_bytes};
+    const unsigned box4[4] = {EX_SEG, (unsigned)p.ps, 1u, CHUNK};
+    p.map4d = 1;
+    if (!mb_make_map_nd(&kmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a->k_cache, 4, dims4, strides4, box4, CU_TENSOR_MAP_SWIZZLE_128B) ||
+        !mb_make_map_nd(&vmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a->v_cache, 4, dims4, strides4, box4, CU_TENSOR_MAP_SWIZZLE_128B)) {
+        // (float, segment of the row, cache row): the extra segment of an even group is then
+        // the next group's first one (fetched and ignored) or lies outside the row
+        const size_t dims3[3] = {EX_SEG, (size_t)p.cache_stride / EX_SEG, rows};
+        const size_t strides3[2] = {EX_SEG * 4u, row_bytes};
+        const unsigned box3[3] = {EX_SEG, (unsigned)p.ps, CHUNK};
+        p.map4d = 0;
+        if ((size_t)p.heads * p.hw > dims3[1] * EX_SEG ||
+            !mb_make_map_nd(&kmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a->k_cache, 3, dims3, strides3, box3, CU_TENSOR_MAP_SWIZZLE_128B) ||
+            !mb_make_map_nd(&vmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a->v_cache, 3, dims3, strides3, box3, CU_TENSOR_MAP_SWIZZLE_128B))
+            return false;
+    }
     const size_t smem = exact_smem(hg, p.hw, p.max_chunks, best_depth);
     const dim3 grid((unsigned)best_g, (unsigned)p.batch), block((unsigned)threads);
     if (threads <= 384) mb_launch(k_attn_exact<384>, grid, block, smem, s, kmap, vmap, p);
@@ -710,6 +743,7 @@ extern "C" int mb_attention(const mb_attn_args *a, mb_stream stream) {
     p.q = a->q; p.k_new = a->k_new; p.v_new = a->v_new;
     p.k_cache = a->k_cache; p.v_cache = a->v_cache;
     p.slots = a->slots; p.lens = a->lens; p.n_active = a->n_active;
+    p.valids = a->lens == nullptr ? a->valid_per_slot : nullptr;
     p.out = a->out; p.qx = a->qx; p.sx = a->sx;
     p.partials = a->partials; p.counters = a->counters; p.status = a->status;
     p.exp_tab = a->exp_tab;

@@ -10,9 +10,15 @@
 //
 //   CTA = one stream (lane) and a group of its heads.  K rows, then V rows, of the group's
 //   columns arrive as 32-row TMA tiles through one ring of mbarrier-guarded slots (every
-//   wait bounded, status bit 2).  A tile is a set of [32 rows][32 floats] boxes with the
-//   128-byte swizzle, so that the threads of a warp, which read the same column piece of 32
-//   different rows in the score pass, hit 32 different banks.
+//   wait bounded, status bit 2), one copy per tile.  The copy reads each cache row's piece
+//   as one contiguous run (segments of 128 bytes, innermost), and lays the tile out as
+//   [32 rows][ps segments][32 floats] with the 128-byte swizzle, where ps is the group's
+//   segment count made odd: when it is even the box is one segment wider than the array's
+//   segment dimension, and that segment is zero-filled without being fetched.  With ps odd
+//   the swizzle key (row * ps + segment) mod 8 differs between any 8 consecutive rows, so
+//   the threads of a warp, which read the same column piece of 32 different rows in the
+//   score pass, hit 32 different banks; the value pass reads along a row and is conflict
+//   free anyway.
 //   pass 1 (K tiles): thread (head, row) forms its row's score, d = 0 .. hw-1 in order.
 //   middle: max per head (exact in any order), e = expf(score - max) with the host libm's
 //           bits, the denominator by one thread per head in row order, weights e / den.
@@ -26,8 +32,13 @@
 namespace {
 
 constexpr int EX_RING_MAX = 8;
-constexpr int EX_BOX = 32;                     // columns (floats) and rows of a TMA box
-constexpr int EX_BOX_FLOATS = EX_BOX * EX_BOX;
+constexpr int EX_SEG = 32;                     // floats of a 128-byte segment
+
+// float offset of element (row r, column col) of a tile with ps segments per row
+__device__ __forceinline__ int ex_offset(int r, int col, int ps) {
+    const int line = r * ps + (col >> 5), j = col & 31;
+    return line * EX_SEG + ((((j >> 2) ^ (line & 7)) << 2) | (j & 3));
+}
 
 template <int MAXT>
 __global__ void __launch_bounds__(MAXT, 1)
@@ -47,11 +58,11 @@ k_attn_exact(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ C
     const int hw = p.hw, heads = p.heads, width = heads * hw;
     const int groups = (int)gridDim.x, hg = heads / groups;
     const int h0 = blockIdx.x * hg, cw = hg * hw, c0 = h0 * hw;     // this CTA's heads and columns
-    const int nbox = cw / EX_BOX, tile_floats = CHUNK * cw;
+    const int ps = p.ps, tile_floats = CHUNK * ps * EX_SEG;
     const int ns = (int)((valid + CHUNK - 1) / CHUNK), ntiles = 2 * ns;
     const int depth = p.depth, scap = p.max_chunks * CHUNK;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    float *tiles = sm_exact;                                  // [depth][nbox][32][32], swizzled
+    float *tiles = sm_exact;                                  // [depth][32 rows][ps][32], swizzled
     float *qs = tiles + (long)depth * tile_floats;            // [cw]
     float *kn = qs + cw;                                      // [cw] the row appended now
     float *vn = kn + cw;
@@ -66,8 +77,9 @@ k_attn_exact(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ C
         const int y = (int)(slot * p.slot_rows + (long)c * CHUNK);
         float *tile = tiles + (long)rs * tile_floats;
         mbar_expect_tx(&mbar[rs], tile_bytes);
-        for (int bx = 0; bx < nbox; ++bx)
-            mb_tma_load_2d_hint(tile + (long)bx * EX_BOX_FLOATS, map, c0 + bx * EX_BOX, y, &mbar[rs], stream_policy);
+        // 4-D map: (float, segment of the group, group, row); 3-D: (float, segment of the row, row)
+        if (p.map4d) mb_tma_load_4d_hint(tile, map, 0, 0, (int)blockIdx.x, y, &mbar[rs], stream_policy);
+        else mb_tma_load_3d_hint(tile, map, 0, c0 / EX_SEG, y, &mbar[rs], stream_policy);
     };
     if (tid == 0) {
         s_fail = 0u;
@@ -94,8 +106,7 @@ k_attn_exact(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ C
     const int col = tid;                                      // pass-2 thread: column c0 + col
     const bool p2 = col < cw;
     const int h2 = p2 ? col / hw : 0;
-    const float *box2 = tiles + (long)(col >> 5) * EX_BOX_FLOATS;
-    const int j2c = (col & 31) >> 2, j2e = col & 3;
+    const int seg2 = col >> 5, j2c = (col & 31) >> 2, j2e = col & 3;
     float lmax = -FLT_MAX, acc = 0.0f;
     int done = 0;                                             // tiles consumed
     for (int t = 0; t < ntiles; ++t) {
@@ -139,9 +150,7 @@ k_attn_exact(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ C
                 } else {
 #pragma unroll 4
                     for (int d4 = 0; d4 < hw; d4 += 4) {
-                        const int cc = warp * hw + d4;
-                        const float4 kv = *reinterpret_cast<const float4 *>(
-                            tile + (long)(cc >> 5) * EX_BOX_FLOATS + lane * EX_BOX + (((((cc & 31) >> 2)) ^ (lane & 7)) << 2));
+                        const float4 kv = *reinterpret_cast<const float4 *>(tile + ex_offset(lane, warp * hw + d4, ps));
                         const float4 qv = *reinterpret_cast<const float4 *>(qh + d4);
                         a = __fadd_rn(a, __fmul_rn(qv.x, kv.x));
                         a = __fadd_rn(a, __fmul_rn(qv.y, kv.y));
@@ -158,12 +167,13 @@ k_attn_exact(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ C
             const int c = t - ns;
             const long s0 = (long)c * CHUNK;
             const int cnt = (int)min((long)CHUNK, valid - s0);
-            const float *tile = box2 + (long)rs * tile_floats;
+            const float *tile = tiles + (long)rs * tile_floats;
             const float *w = sc + (long)h2 * scap + s0;
             const int fresh = (append && pos >= s0 && pos < s0 + cnt) ? (int)(pos - s0) : -1;
 #pragma unroll 8
             for (int r = 0; r < cnt; ++r) {
-                const float v = r == fresh ? vn[col] : tile[r * EX_BOX + (((j2c ^ (r & 7)) << 2) | j2e)];
+                const int line = r * ps + seg2;
+                const float v = r == fresh ? vn[col] : tile[line * EX_SEG + (((j2c ^ (line & 7)) << 2) | j2e)];
                 acc = __fadd_rn(acc, __fmul_rn(w[r], v));
             }
         }
@@ -207,11 +217,15 @@ k_attn_exact(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ C
     quantize_shared_row(vals, width, p.qx + (long)b * width, p.sx + b, red);
 }
 
+// Segments per tile row: the group's column count in 128-byte segments, made odd.
+inline int exact_pitch_segments(int hg, int hw) { return ((hg * hw) / EX_SEG) | 1; }
+
 // Shared memory of one CTA of k_attn_exact: `depth` tiles, q and the appended K/V row, the
 // scores of the group's heads, two statistics per head.
 inline size_t exact_smem(int hg, int hw, int max_chunks, int depth) {
     const size_t cw = (size_t)hg * hw;
-    return ((size_t)depth * CHUNK * cw + 3u * cw + (size_t)hg * max_chunks * CHUNK + 2u * hg) * sizeof(float);
+    return ((size_t)depth * CHUNK * exact_pitch_segments(hg, hw) * EX_SEG + 3u * cw + (size_t)hg * max_chunks * CHUNK + 2u * hg) *
+           sizeof(float);
 }
 
 }  // namespace

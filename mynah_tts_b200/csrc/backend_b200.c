@@ -648,6 +648,15 @@ int mynah_cuda_sync(void *state, char *error, size_t cap) {
     if (st == NULL) return -1;
     if (use_device(st, error, cap) != 0) return -1;
     MB_TRY(cudaStreamSynchronize(st->stream), "cudaStreamSynchronize");
+    /* the seam ops enqueue and return: a bounded device wait that ran out since the last
+     * sync is reported here, where the caller collects the step's result */
+    int status = 0;
+    MB_TRY(cudaMemcpy(&status, st->d_status, sizeof(int), cudaMemcpyDeviceToHost), "read status");
+    if (status != 0) {
+        cudaMemset(st->d_status, 0, sizeof(int));
+        mb_set_error(error, cap, mb_status_message(status));
+        return -1;
+    }
     mb_clear_error(error, cap);
     return 0;
 }

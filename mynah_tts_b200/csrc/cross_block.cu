@@ -35,7 +35,7 @@ struct CrossP {
     const float *gain_query, *gain_ff;
     const int8_t *wq, *wo;
     const float *wq_scales, *wo_scales;
-    const int *slots, *n_active;
+    const int *slots, *n_active, *rows_per_slot;
     int8_t *qx;
     float *sx;
     int *status;
@@ -82,16 +82,19 @@ k_cross_block(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
     const int live = p.n_active != nullptr ? *p.n_active : 0x7fffffff;
     const long slot = p.slots != nullptr ? (long)p.slots[b] : (long)b;
     if (b >= live) return;
-    const int W = p.width, XW = p.xw, ns = p.chunks;
+    // text states of this stream (the slot's request), and the 32-row chunks they fill
+    const int rows = p.rows_per_slot != nullptr ? min(max(p.rows_per_slot[slot], 1), p.rows) : p.rows;
+    const int W = p.width, XW = p.xw, ns = (rows + CHUNK - 1) / CHUNK;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int tile_floats = CHUNK * XW;
-    float *Kt = sm;                                   // [ns] tiles of [32][XW]
-    float *Vt = Kt + (long)ns * tile_floats;
-    float *xres = Vt + (long)ns * tile_floats;        // [W] the residual row as it came in
+    const int nsmax = p.chunks;                       // the layout is sized for the longest request
+    float *Kt = sm;                                   // [nsmax] tiles of [32][XW]
+    float *Vt = Kt + (long)nsmax * tile_floats;
+    float *xres = Vt + (long)nsmax * tile_floats;     // [W] the residual row as it came in
     float *row = xres + W;                            // [W] work row of the norms
     float *qs = row + W;                              // [XW] query
-    float *P = qs + XW;                               // [ns][XW + 2] chunk partials
-    float *wts = P + (long)ns * (XW + 2);             // [32] merge scratch
+    float *P = qs + XW;                               // [nsmax][XW + 2] chunk partials
+    float *wts = P + (long)nsmax * (XW + 2);          // [32] merge scratch
     float *vals = wts + 32;                           // [XW] merged context
     float *gq = vals + XW;                            // [W] gain of the first norm
     float *gf = gq + W;                               // [W] gain of the second norm
@@ -102,19 +105,19 @@ k_cross_block(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
     if (threadIdx.x == 0) {
         s_bad = 0u;
         const unsigned long long stream_policy = mb_l2_evict_first();
-        for (int i = 0; i < 2 * ns; ++i) mbar_init(&mbar[i], 1u);
+        for (int i = 0; i < 2 * XB_MAX_CHUNKS; ++i) mbar_init(&mbar[i], 1u);
         for (int c = 0; c < ns; ++c) {
             const int y = (int)(slot * p.slot_rows + (long)c * CHUNK);
             mbar_expect_tx(&mbar[c], tile_bytes);
-            mbar_expect_tx(&mbar[ns + c], tile_bytes);
+            mbar_expect_tx(&mbar[XB_MAX_CHUNKS + c], tile_bytes);
             if (STRICT) {
                 for (int bx = 0; bx < XW / 32; ++bx) {
                     mb_tma_load_2d_hint(Kt + (long)c * tile_floats + bx * 1024, &kmap, bx * 32, y, &mbar[c], stream_policy);
-                    mb_tma_load_2d_hint(Vt + (long)c * tile_floats + bx * 1024, &vmap, bx * 32, y, &mbar[ns + c], stream_policy);
+                    mb_tma_load_2d_hint(Vt + (long)c * tile_floats + bx * 1024, &vmap, bx * 32, y, &mbar[XB_MAX_CHUNKS + c], stream_policy);
                 }
             } else {
                 mb_tma_load_2d_hint(Kt + (long)c * tile_floats, &kmap, 0, y, &mbar[c], stream_policy);
-                mb_tma_load_2d_hint(Vt + (long)c * tile_floats, &vmap, 0, y, &mbar[ns + c], stream_policy);
+                mb_tma_load_2d_hint(Vt + (long)c * tile_floats, &vmap, 0, y, &mbar[XB_MAX_CHUNKS + c], stream_policy);
             }
         }
     }
@@ -215,7 +218,7 @@ k_cross_block(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
         float *scs = P;                               // [ns * 32] scores, then weights
         const int s = threadIdx.x, c = s >> 5, r = s & 31;
         float a = -FLT_MAX;
-        if (s < p.rows) {
+        if (s < rows) {
             if (mbar_wait(&mbar[c], 0u, SPIN_LIMIT)) {
                 const float *tile = Kt + (long)c * tile_floats + r * 32;
                 float dot = 0.0f;
@@ -235,11 +238,11 @@ k_cross_block(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
             }
         }
         const float m = block_max1(a, red);
-        if (s < p.rows) scs[s] = exp_ref<true>(__fsub_rn(a, m), p.exp_tab);
+        if (s < rows) scs[s] = exp_ref<true>(__fsub_rn(a, m), p.exp_tab);
         __syncthreads();
-        if (threadIdx.x == 0) stat[0] = mb_seq_sum(scs, p.rows);
+        if (threadIdx.x == 0) stat[0] = mb_seq_sum(scs, rows);
         __syncthreads();
-        if (s < p.rows) scs[s] = __fdiv_rn(scs[s], stat[0]);
+        if (s < rows) scs[s] = __fdiv_rn(scs[s], stat[0]);
         __syncthreads();
         if (threadIdx.x < XW && s_bad == 0u) {
             const int d = threadIdx.x;
@@ -247,12 +250,12 @@ k_cross_block(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
             const int jc = (d & 31) >> 2;
             float acc = 0.0f;
             for (int cc = 0; cc < ns; ++cc) {
-                if (!mbar_wait(&mbar[ns + cc], 0u, SPIN_LIMIT)) {
+                if (!mbar_wait(&mbar[XB_MAX_CHUNKS + cc], 0u, SPIN_LIMIT)) {
                     s_bad = 1u;
                     if (p.status != nullptr) atomicOr(p.status, 2);
                     break;
                 }
-                const int cnt = min(CHUNK, p.rows - cc * CHUNK);
+                const int cnt = min(CHUNK, rows - cc * CHUNK);
                 const float *tile = col + (long)cc * tile_floats;
                 const float *w = scs + cc * CHUNK;
 #pragma unroll 8
@@ -264,9 +267,9 @@ k_cross_block(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
     } else if (warp < ns) {
         const int c = warp;
         const float4 qv = reinterpret_cast<const float4 *>(qs)[li];
-        const int cnt = min(CHUNK, p.rows - c * CHUNK);
+        const int cnt = min(CHUNK, rows - c * CHUNK);
         const bool k_ok = mbar_wait(&mbar[c], 0u, SPIN_LIMIT);
-        const bool v_ok = k_ok && mbar_wait(&mbar[ns + c], 0u, SPIN_LIMIT);
+        const bool v_ok = k_ok && mbar_wait(&mbar[XB_MAX_CHUNKS + c], 0u, SPIN_LIMIT);
         if (k_ok && v_ok) {
             const float *Ks = Kt + (long)c * tile_floats;
             float dot;
@@ -307,7 +310,7 @@ k_cross_block(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
         if (threadIdx.x == 0)
             for (int c = 0; c < ns; ++c) {
                 mbar_wait(&mbar[c], 0u, SPIN_LIMIT);
-                mbar_wait(&mbar[ns + c], 0u, SPIN_LIMIT);
+                mbar_wait(&mbar[XB_MAX_CHUNKS + c], 0u, SPIN_LIMIT);
             }
         return;
     }
@@ -395,7 +398,7 @@ extern "C" int mb_cross_block(const mb_cross_block_args *a, mb_stream stream) {
     p.x = a->x;
     p.gain_query = a->gain_query; p.gain_ff = a->gain_ff;
     p.wq = a->wq; p.wo = a->wo; p.wq_scales = a->wq_scales; p.wo_scales = a->wo_scales;
-    p.slots = a->slots; p.n_active = a->n_active;
+    p.slots = a->slots; p.n_active = a->n_active; p.rows_per_slot = a->rows_per_slot;
     p.qx = a->qx; p.sx = a->sx; p.status = a->status;
     p.slot_rows = (long)(a->slot_stride / a->xw);
     p.width = (int)a->width; p.xw = (int)a->xw; p.rows = (int)a->rows;

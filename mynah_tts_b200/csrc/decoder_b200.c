@@ -85,6 +85,9 @@ typedef struct mb_decoder {
     int *h_status;
     size_t stage_in_ints;
     size_t *slot_len;           /* host mirror of every slot's length */
+    int *d_mem_len;             /* [slots] text states of the request in each slot (<= T) */
+    size_t *slot_mem;           /* host mirror */
+    float *pf_mem, *pf_nrm, *pf_kv;   /* prefill scratch: [T][W], [T][W], [T][2xw] */
     mb_local local;             /* layers == 0: not attached */
     cudaGraphExec_t graph[MODE_COUNT][MAX_BUCKETS];
     unsigned graph_launches[MODE_COUNT][MAX_BUCKETS];
@@ -193,7 +196,7 @@ void mynah_b200_decoder_destroy(void *decoder) {
                    d->self_v, d->cross_k, d->cross_v, d->x, d->nrm, d->qkv, d->attn, d->q_x,
                    d->xctx, d->hidden, d->out, d->rows_in, d->logits, d->qx, d->sx, d->partials,
                    d->counters, d->d_stage_in, d->d_stage_out, d->d_eos_frame, d->d_min_frames,
-                   d->d_history};
+                   d->d_history, d->d_mem_len, d->pf_mem, d->pf_nrm, d->pf_kv};
     for (size_t i = 0; i < sizeof(dev) / sizeof(dev[0]); ++i) cudaFree(dev[i]);
     void *pinned[] = {d->h_rows, d->h_out, d->h_stage_in, d->h_stage_out, d->h_ints, d->h_table};
     for (size_t i = 0; i < sizeof(pinned) / sizeof(pinned[0]); ++i)
@@ -207,6 +210,7 @@ void mynah_b200_decoder_destroy(void *decoder) {
     if (d->ev0 != NULL) cudaEventDestroy(d->ev0);
     if (d->ev1 != NULL) cudaEventDestroy(d->ev1);
     free(d->slot_len);
+    free(d->slot_mem);
     free(d);
 }
 
@@ -268,7 +272,8 @@ int mynah_b200_decoder_create(void *state, const mynah_b200_decoder_desc *desc, 
 #define D_TRY(expr) do { if (ok && (expr) != 0) ok = 0; } while (0)
     d->L = (dec_layer *)calloc(d->layers, sizeof(dec_layer));
     d->slot_len = (size_t *)calloc(d->slots, sizeof(size_t));
-    if (d->L == NULL || d->slot_len == NULL) { mb_set_error(error, cap, "out of memory"); ok = 0; }
+    d->slot_mem = (size_t *)calloc(d->slots, sizeof(size_t));
+    if (d->L == NULL || d->slot_len == NULL || d->slot_mem == NULL) { mb_set_error(error, cap, "out of memory"); ok = 0; }
     for (size_t l = 0; ok && l < d->layers; ++l) {
         const mynah_b200_layer_weights *s = &desc->layer[l];
         dec_layer *L = &d->L[l];
@@ -327,6 +332,28 @@ int mynah_b200_decoder_create(void *state, const mynah_b200_decoder_desc *desc, 
     D_TRY(dmalloc((void **)&d->self_v, self_n * sizeof(float), error, cap));
     D_TRY(dmalloc((void **)&d->cross_k, cross_n * sizeof(float), error, cap));
     D_TRY(dmalloc((void **)&d->cross_v, cross_n * sizeof(float), error, cap));
+    D_TRY(dmalloc((void **)&d->d_mem_len, d->slots * sizeof(int), error, cap));
+    if (ok) {
+        /* every slot starts as a request of the full memory length over zeroed cross rows */
+        int *full = (int *)malloc(d->slots * sizeof(int));
+        if (full == NULL) { mb_set_error(error, cap, "out of memory"); ok = 0; }
+        for (size_t i = 0; ok && i < d->slots; ++i) { full[i] = (int)d->T; d->slot_mem[i] = d->T; }
+        D_TRY(mb_cuda((int)cudaMemcpy(d->d_mem_len, full, d->slots * sizeof(int), cudaMemcpyHostToDevice), "upload", error, cap));
+        free(full);
+        D_TRY(mb_cuda((int)cudaMemset(d->cross_k, 0, cross_n * sizeof(float)), "memset", error, cap));
+        D_TRY(mb_cuda((int)cudaMemset(d->cross_v, 0, cross_n * sizeof(float)), "memset", error, cap));
+    }
+    {
+        int have_kv = 1;
+        for (size_t l = 0; l < d->layers; ++l)
+            if (d->L[l].norm_xattn_memory == NULL || d->L[l].kv_cross.w == NULL) have_kv = 0;
+        if (ok && have_kv) {
+            /* scratch of slot_prefill, allocated once: admissions allocate and free nothing */
+            D_TRY(dmalloc((void **)&d->pf_mem, d->T * W * sizeof(float), error, cap));
+            D_TRY(dmalloc((void **)&d->pf_nrm, d->T * W * sizeof(float), error, cap));
+            D_TRY(dmalloc((void **)&d->pf_kv, d->T * 2u * XW * sizeof(float), error, cap));
+        }
+    }
     /* activations */
     D_TRY(dmalloc((void **)&d->x, MB * W * sizeof(float), error, cap));
     D_TRY(dmalloc((void **)&d->nrm, MB * W * sizeof(float), error, cap));
@@ -713,6 +740,7 @@ static int enqueue(mb_decoder *d, size_t bucket, int mode, unsigned *count) {
             cb.width = W;
             cb.xw = XW;
             cb.rows = d->T;
+            cb.rows_per_slot = d->d_mem_len;
             cb.scale = cross_scale;
             cb.eps = 1.0e-5f;
             cb.qx = d->qx;
@@ -749,6 +777,7 @@ static int enqueue(mb_decoder *d, size_t bucket, int mode, unsigned *count) {
         a.slots = d->d_slots;
         a.position = 0;
         a.valid = d->T;
+        a.valid_per_slot = d->d_mem_len;
         a.cache_rows = (d->slots - 1u) * d->layers * d->T + d->T;
         a.cache_stride = XW;
         a.heads = 1;
@@ -856,9 +885,18 @@ static int check_slot(const mb_decoder *d, size_t slot, char *error, size_t cap)
     return mb_cuda((int)cudaSetDevice(d->st->device), "cudaSetDevice", error, cap);
 }
 
+/* One slot's text-state count to the device (kernels read it per lane). */
+static int set_slot_memory(mb_decoder *d, size_t slot, size_t rows, char *error, size_t cap) {
+    const int v = (int)rows;
+    MB_TRY(cudaMemcpyAsync(d->d_mem_len + slot, &v, sizeof(int), cudaMemcpyHostToDevice, d->st->stream), "stage memory length");
+    MB_TRY(cudaStreamSynchronize(d->st->stream), "cudaStreamSynchronize");   /* &v leaves scope */
+    d->slot_mem[slot] = rows;
+    return 0;
+}
+
 int mynah_b200_decoder_slot_load(void *decoder, size_t slot, const float *cross_k,
-                                 const float *cross_v, const float *self_k, const float *self_v,
-                                 size_t length, char *error, size_t cap) {
+                                 const float *cross_v, size_t memory_length, const float *self_k,
+                                 const float *self_v, size_t length, char *error, size_t cap) {
     mb_decoder *d = (mb_decoder *)decoder;
     if (check_slot(d, slot, error, cap) != 0) return -1;
     if (cross_k == NULL || cross_v == NULL || length > d->capacity ||
@@ -866,12 +904,19 @@ int mynah_b200_decoder_slot_load(void *decoder, size_t slot, const float *cross_
         mb_set_error(error, cap, "invalid slot contents");
         return -1;
     }
+    if (memory_length == 0 || memory_length > d->T) {
+        mb_set_error(error, cap, "slot memory length must be 1 .. the decoder's memory_length");
+        return -1;
+    }
     cudaStream_t s = d->st->stream;
-    const size_t cross_n = d->layers * d->T * d->xw;
-    MB_TRY(cudaMemcpyAsync(d->cross_k + slot * cross_n, cross_k, cross_n * sizeof(float),
-                           cudaMemcpyHostToDevice, s), "upload cross K");
-    MB_TRY(cudaMemcpyAsync(d->cross_v + slot * cross_n, cross_v, cross_n * sizeof(float),
-                           cudaMemcpyHostToDevice, s), "upload cross V");
+    const size_t cross_n = d->layers * d->T * d->xw, rows_n = memory_length * d->xw;
+    /* the request's arrays are [layers][memory_length][xw]; a slot keeps [layers][T][xw] */
+    for (size_t l = 0; l < d->layers; ++l) {
+        MB_TRY(cudaMemcpyAsync(d->cross_k + slot * cross_n + l * d->T * d->xw, cross_k + l * rows_n,
+                               rows_n * sizeof(float), cudaMemcpyHostToDevice, s), "upload cross K");
+        MB_TRY(cudaMemcpyAsync(d->cross_v + slot * cross_n + l * d->T * d->xw, cross_v + l * rows_n,
+                               rows_n * sizeof(float), cudaMemcpyHostToDevice, s), "upload cross V");
+    }
     const size_t per_layer = d->capacity * d->width;
     for (size_t l = 0; l < d->layers && length > 0; ++l) {
         const size_t off = (slot * d->layers + l) * per_layer;
@@ -880,7 +925,7 @@ int mynah_b200_decoder_slot_load(void *decoder, size_t slot, const float *cross_
         MB_TRY(cudaMemcpyAsync(d->self_v + off, self_v + l * per_layer, length * d->width * sizeof(float),
                                cudaMemcpyHostToDevice, s), "upload self V");
     }
-    MB_TRY(cudaStreamSynchronize(s), "cudaStreamSynchronize");
+    if (set_slot_memory(d, slot, memory_length, error, cap) != 0) return -1;
     d->slot_len[slot] = length;
     mb_clear_error(error, cap);
     return 0;
@@ -893,28 +938,24 @@ int mynah_b200_decoder_slot_prefill(void *decoder, size_t slot, const float *mem
                                     size_t memory_length, char *error, size_t cap) {
     mb_decoder *d = (mb_decoder *)decoder;
     if (check_slot(d, slot, error, cap) != 0) return -1;
-    if (memory == NULL || memory_length != d->T) {
-        mb_set_error(error, cap, "prefill: memory must have the decoder's memory_length rows");
+    if (memory == NULL || memory_length == 0 || memory_length > d->T) {
+        mb_set_error(error, cap, "prefill: memory must have 1 .. the decoder's memory_length rows");
         return -1;
     }
-    for (size_t l = 0; l < d->layers; ++l)
-        if (d->L[l].norm_xattn_memory == NULL || d->L[l].kv_cross.w == NULL) {
-            mb_set_error(error, cap, "prefill: the decoder was created without norm_xattn_memory / kv_net weights");
-            return -1;
-        }
+    if (d->pf_mem == NULL) {
+        mb_set_error(error, cap, "prefill: the decoder was created without norm_xattn_memory / kv_net weights");
+        return -1;
+    }
     mb_state *st = d->st;
     cudaStream_t s = st->stream;
-    const size_t W = d->width, XW = d->xw, T = d->T;
-    float *mem = NULL, *nrm = NULL, *kv = NULL;
+    const size_t W = d->width, XW = d->xw, T = d->T, M = memory_length;
+    float *mem = d->pf_mem, *nrm = d->pf_nrm, *kv = d->pf_kv;
     int rc = 0;
 #define F_TRY(expr, what) do { if (rc == 0 && mb_cuda((int)(expr), (what), error, cap) != 0) rc = -1; } while (0)
-    F_TRY(cudaMalloc((void **)&mem, T * W * sizeof(float)), "cudaMalloc(prefill)");
-    F_TRY(cudaMalloc((void **)&nrm, T * W * sizeof(float)), "cudaMalloc(prefill)");
-    F_TRY(cudaMalloc((void **)&kv, T * 2u * XW * sizeof(float)), "cudaMalloc(prefill)");
-    F_TRY(cudaMemcpyAsync(mem, memory, T * W * sizeof(float), cudaMemcpyHostToDevice, s), "upload memory");
+    F_TRY(cudaMemcpyAsync(mem, memory, M * W * sizeof(float), cudaMemcpyHostToDevice, s), "upload memory");
     const size_t cross_n = d->layers * T * XW;
     for (size_t l = 0; l < d->layers && rc == 0; ++l) {
-        F_TRY(mb_layernorm(mem, nrm, d->L[l].norm_xattn_memory, NULL, T, W, 1.0e-5f, NULL, NULL, NULL,
+        F_TRY(mb_layernorm(mem, nrm, d->L[l].norm_xattn_memory, NULL, M, W, 1.0e-5f, NULL, NULL, NULL,
                            st->strict, s), "layer norm of the memory");
         mb_gemv_args g;
         memset(&g, 0, sizeof(g));
@@ -922,22 +963,22 @@ int mynah_b200_decoder_slot_prefill(void *decoder, size_t slot, const float *mem
         g.x = nrm;
         g.out = kv;
         g.out_stride = 2u * XW;
-        g.batch = T;
+        g.batch = M;
         g.epilogue = MB_EPI_STORE;
         g.strict = st->strict;
         F_TRY(mb_gemv(&g, s), "kv_net product");
         float *ck = d->cross_k + slot * cross_n + l * T * XW;
         float *cv = d->cross_v + slot * cross_n + l * T * XW;
-        F_TRY(cudaMemcpy2DAsync(ck, XW * sizeof(float), kv, 2u * XW * sizeof(float), XW * sizeof(float), T,
+        F_TRY(cudaMemcpy2DAsync(ck, XW * sizeof(float), kv, 2u * XW * sizeof(float), XW * sizeof(float), M,
                                 cudaMemcpyDeviceToDevice, s), "split K");
-        F_TRY(cudaMemcpy2DAsync(cv, XW * sizeof(float), kv + XW, 2u * XW * sizeof(float), XW * sizeof(float), T,
+        F_TRY(cudaMemcpy2DAsync(cv, XW * sizeof(float), kv + XW, 2u * XW * sizeof(float), XW * sizeof(float), M,
                                 cudaMemcpyDeviceToDevice, s), "split V");
         st->launches += 2u;
     }
-    F_TRY(cudaStreamSynchronize(s), "cudaStreamSynchronize");
+    F_TRY(cudaStreamSynchronize(s), "cudaStreamSynchronize");   /* the caller's memory may go away */
 #undef F_TRY
-    cudaFree(mem); cudaFree(nrm); cudaFree(kv);
     if (rc != 0) return -1;
+    if (set_slot_memory(d, slot, M, error, cap) != 0) return -1;
     d->slot_len[slot] = 0;
     mb_clear_error(error, cap);
     return 0;
@@ -1050,7 +1091,7 @@ static int check_status(mb_decoder *d, char *error, size_t cap) {
     MB_TRY(cudaMemcpy(&status, d->d_status, sizeof(int), cudaMemcpyDeviceToHost), "read status");
     if (status != 0) {
         cudaMemset(d->d_status, 0, sizeof(int));
-        mb_set_error(error, cap, "audio token id is outside vocabulary");   /* src/graph.c:794-797 */
+        mb_set_error(error, cap, mb_status_message(status));
         return -1;
     }
     return 0;
@@ -1443,8 +1484,10 @@ int mynah_b200_decoder_serve(void *decoder, mynah_b200_request *requests, size_t
     }
     for (size_t i = 0; rc == 0 && i < count; ++i) {
         if (requests[i].memory == NULL || requests[i].start_codes == NULL || requests[i].codes == NULL ||
-            requests[i].max_frames > d->capacity) {
-            mb_set_error(error, cap, "serve: a request lacks buffers or exceeds the cache capacity");
+            requests[i].max_frames > d->capacity || requests[i].memory_length == 0 ||
+            requests[i].memory_length > d->T) {
+            mb_set_error(error, cap, "serve: a request lacks buffers, exceeds the cache capacity or has more text "
+                                     "states than the decoder's memory_length");
             rc = -1;
         }
         requests[i].frames_done = 0;
@@ -1458,7 +1501,7 @@ int mynah_b200_decoder_serve(void *decoder, mynah_b200_request *requests, size_t
             if (owner[s] != SIZE_MAX) continue;
             mynah_b200_request *r = &requests[waiting];
             if (r->max_frames == 0) { ++waiting; --s; continue; }
-            if (mynah_b200_decoder_slot_prefill(d, s, r->memory, d->T, error, cap) != 0) { rc = -1; break; }
+            if (mynah_b200_decoder_slot_prefill(d, s, r->memory, r->memory_length, error, cap) != 0) { rc = -1; break; }
             owner[s] = waiting++;
             r->admitted_at = step;
             ++live;

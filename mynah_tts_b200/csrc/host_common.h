@@ -70,6 +70,19 @@ static inline int mb_cuda(int rc, const char *what, char *error, size_t cap) {
         if (mb_cuda((int)(expr), (what), error, cap) != 0) return -1;   \
     } while (0)
 
+/* What a nonzero device status word says.  Bits: 1 a token id outside the embedding tables
+ * (src/graph.c:794-797); 2 a cache tile of an attention kernel never arrived (bounded TMA
+ * wait ran out); 8 / 16 a tensor-core product's operand copy / its MMAs never completed
+ * (bounded waits ran out).  Several bits: the message of the lowest hardware bit wins, since
+ * the outputs of that step are then stale whatever the tokens were. */
+static inline const char *mb_status_message(int status) {
+    if (status & 2) return "an attention kernel's wait for a cache tile ran out; the step's outputs are stale";
+    if (status & 8) return "a tensor-core product's wait for an operand copy ran out; the step's outputs are stale";
+    if (status & 16) return "a tensor-core product's wait for its MMAs ran out; the step's outputs are stale";
+    if (status & 1) return "audio token id is outside vocabulary";
+    return "device status word is set";
+}
+
 /* Upload a host f32 weight [n,k] and pack it as `qtype` (falls back to f32
  * when int4 cannot represent k).  The caller owns *out (mb_weight_release). */
 int mb_weight_build(mb_state *st, const float *host_w, size_t n, size_t k, int qtype,

@@ -175,6 +175,7 @@ typedef struct {
     const int *slots;     /* [batch] slot of each lane, NULL = identity */
     const int *lens;      /* [batch] position of each lane (valid = len+1); NULL = scalars below */
     size_t position, valid;
+    const int *valid_per_slot; /* lens == NULL only: rows attended by the lane in slot s (<= valid), or NULL */
     size_t cache_stride, heads, head_width;
     size_t cache_rows;    /* rows addressable from k_cache/v_cache (all slots); 0 = up to valid/position */
     float scale;
@@ -225,7 +226,8 @@ typedef struct {
     size_t cache_rows;           /* rows spanned by all slots (tensor-map extent) */
     const int *slots;            /* [batch] or NULL (lane b uses slot b) */
     const int *n_active;
-    size_t batch, width, xw, rows;   /* rows: text states attended over */
+    size_t batch, width, xw, rows;   /* rows: most text states a stream attends over */
+    const int *rows_per_slot;    /* [slots] text states of the stream in each slot (1 .. rows), or NULL: rows */
     float scale, eps;
     int8_t *qx;                  /* [batch][width] out: quantized second norm */
     float *sx;                   /* [batch] */

@@ -40,6 +40,27 @@ static inline bool mb_make_map_2d(CUtensorMap *map, CUtensorMapDataType type, co
                swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// General form: `rank` dimensions (innermost first) with byte strides for dimensions 1..rank-1
+// and a box extent per dimension.  Elements outside the array read as zero and are not
+// fetched, which lets a box be wider than the array in a dimension on purpose (padding rows
+// of the shared-memory tile).
+static inline bool mb_make_map_nd(CUtensorMap *map, CUtensorMapDataType type, const void *ptr, unsigned rank,
+                                  const size_t *dims, const size_t *strides_bytes, const unsigned *box,
+                                  CUtensorMapSwizzle swizzle) {
+    mb_encode_fn enc = mb_tensor_map_encoder();
+    if (enc == nullptr || rank < 2 || rank > 5) return false;
+    cuuint64_t d[5], st[4];
+    cuuint32_t b[5], estr[5];
+    for (unsigned i = 0; i < rank; ++i) {
+        d[i] = (cuuint64_t)dims[i];
+        b[i] = box[i];
+        estr[i] = 1;
+        if (i > 0) st[i - 1] = (cuuint64_t)strides_bytes[i - 1];
+    }
+    return enc(map, type, rank, const_cast<void *>(ptr), d, st, b, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 #ifdef __CUDACC__
 // Tile whose first element is (x, y) -> this CTA's shared memory; completion is
 // counted in bytes on the mbarrier.  x * element size must be a multiple of 16.
@@ -70,6 +91,22 @@ __device__ __forceinline__ void mb_tma_load_2d_hint(void *dst, const CUtensorMap
         "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint "
         "[%0], [%1, {%2, %3}], [%4], %5;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(map), "r"(x), "r"(y),
         "r"((unsigned)__cvta_generic_to_shared(bar)), "l"(policy)
+        : "memory");
+}
+__device__ __forceinline__ void mb_tma_load_3d_hint(void *dst, const CUtensorMap *map, int c0, int c1, int c2, void *bar,
+                                                    unsigned long long policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint "
+        "[%0], [%1, {%2, %3, %4}], [%5], %6;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(map), "r"(c0), "r"(c1),
+        "r"(c2), "r"((unsigned)__cvta_generic_to_shared(bar)), "l"(policy)
+        : "memory");
+}
+__device__ __forceinline__ void mb_tma_load_4d_hint(void *dst, const CUtensorMap *map, int c0, int c1, int c2, int c3,
+                                                    void *bar, unsigned long long policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint "
+        "[%0], [%1, {%2, %3, %4, %5}], [%6], %7;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(map), "r"(c0), "r"(c1),
+        "r"(c2), "r"(c3), "r"((unsigned)__cvta_generic_to_shared(bar)), "l"(policy)
         : "memory");
 }
 #endif
