@@ -869,6 +869,17 @@ extern "C" int mb_attention(const mb_attn_args *a, mb_stream stream) {
     return rc;
 }
 
+#ifdef MB_PHASE_TICKS
+// Profiling builds only (make TICKS=1): the phase timestamps of the last k_attn_exact launch,
+// eight per CTA (see attn_exact.cuh), copied to `host` (n values).
+extern "C" __attribute__((visibility("default")))
+int mynah_b200_debug_attention_ticks(unsigned long long *host, size_t n) {
+    if (n > 8u * 8192u) n = 8u * 8192u;
+    cudaDeviceSynchronize();
+    return (int)cudaMemcpyFromSymbol(host, g_exact_ticks, n * sizeof(unsigned long long));
+}
+#endif
+
 // ---------------------------------------------------------------------------
 // Allocation-free self-attention for callers that must not allocate.
 //

@@ -40,9 +40,29 @@ __device__ __forceinline__ int ex_offset(int r, int col, int ps) {
     return line * EX_SEG + ((((j >> 2) ^ (line & 7)) << 2) | (j & 3));
 }
 
+// Phase timestamps for profiling, compiled in with -DMB_PHASE_TICKS (make TICKS=1): thread 0
+// of every CTA records the global nanosecond timer at its phase boundaries -- 0 entry, 1
+// prologue done, 2 score pass done, 3 weights ready, 4 value pass done, 5 exit -- into a
+// device array that mynah_b200_debug_attention_ticks copies out.  Absent from normal builds.
+#ifdef MB_PHASE_TICKS
+__device__ unsigned long long g_exact_ticks[8 * 8192];
+__device__ __forceinline__ void mb_tick(int i) {
+    if (threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        const unsigned cta = blockIdx.y * gridDim.x + blockIdx.x;
+        if (cta < 8192u) g_exact_ticks[cta * 8 + i] = t;
+    }
+}
+#define MB_TICK(i) mb_tick(i)
+#else
+#define MB_TICK(i)
+#endif
+
 template <int MAXT>
 __global__ void __launch_bounds__(MAXT, 1)
 k_attn_exact(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, AttnP p) {
+    MB_TICK(0);
     if (!p.early) {
         mb_pdl_wait();
         mb_pdl_trigger();
@@ -102,6 +122,7 @@ k_attn_exact(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ C
         }
     }
     __syncthreads();
+    MB_TICK(1);
     const bool p1 = warp < hg;                                // pass-1 thread: head h0 + warp, row `lane` of a chunk
     const int col = tid;                                      // pass-2 thread: column c0 + col
     const bool p2 = col < cw;
@@ -113,16 +134,38 @@ k_attn_exact(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ C
         const int rs = t % depth;
         const unsigned parity = (unsigned)((t / depth) & 1);
         if (t == ns) {
+            MB_TICK(2);
             // ---- all scores are in: max, exp, denominator, weights -------------------------
             if (p1) {
                 const float m = warp_max(lmax);
                 if (lane == 0) stat[warp] = m;
             }
             __syncthreads();
-            for (int h = 0; h < hg; ++h) {
-                const float m = stat[h];
-                for (long s = tid; s < valid; s += blockDim.x)
-                    sc[(long)h * scap + s] = exp_ref<true>(__fsub_rn(sc[(long)h * scap + s], m), p.exp_tab);
+            // e = expf(score - max) with the host libm's bits, over the (head, row) pairs of the
+            // group six at a time per thread: the table words of a batch are requested
+            // together, so a batch costs one memory round trip, not six
+            {
+                constexpr int EXB = 6;
+                const int total = hg * (int)valid;
+                for (int i0 = tid; i0 < total; i0 += EXB * blockDim.x) {
+                    float arg[EXB];
+                    uint32_t word[EXB];
+                    int at[EXB];
+#pragma unroll
+                    for (int j = 0; j < EXB; ++j) {
+                        const int i = i0 + j * blockDim.x;
+                        at[j] = -1;
+                        if (i < total) {
+                            const int h = i / (int)valid, s = i - h * (int)valid;
+                            at[j] = h * scap + s;
+                            arg[j] = __fsub_rn(sc[at[j]], stat[h]);
+                            word[j] = mb_exp_fetch(arg[j], p.exp_tab);
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j < EXB; ++j)
+                        if (at[j] >= 0) sc[at[j]] = mb_expf_host_with(arg[j], word[j], p.exp_tab != nullptr);
+                }
             }
             __syncthreads();
             if (p1 && lane == 0) {
@@ -135,6 +178,7 @@ k_attn_exact(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ C
                     sc[(long)h * scap + s] = __fdiv_rn(sc[(long)h * scap + s], den);
             }
             __syncthreads();
+            MB_TICK(3);
         }
         if (!mbar_wait(&mbar[rs], parity, SPIN_LIMIT)) s_fail = 1u;
         else if (t < ns) {
@@ -192,6 +236,7 @@ k_attn_exact(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ C
         }
         return;
     }
+    MB_TICK(4);
     float *outrow = p.out + (long)b * p.out_stride;
     if (p2) outrow[c0 + col] = acc;
     if (p.qx == nullptr) return;
@@ -215,6 +260,7 @@ k_attn_exact(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ C
     }
     __syncthreads();
     quantize_shared_row(vals, width, p.qx + (long)b * width, p.sx + b, red);
+    MB_TICK(5);
 }
 
 // Segments per tile row: the group's column count in 128-byte segments, made odd.

@@ -317,6 +317,7 @@ int mynah_b200_open(void **state, int device, int quant, int strict, char *error
         mb_cuda(mb_gemv_init(), "kernel attributes (gemv)", error, cap) != 0 ||
         mb_cuda(mb_attention_init(), "kernel attributes (attention)", error, cap) != 0 ||
         mb_cuda(mb_gemm_tc_init(), "kernel attributes (tensor-core product)", error, cap) != 0 ||
+        mb_cuda(mb_gemm_tc_f16_init(), "kernel attributes (f16 tensor-core product)", error, cap) != 0 ||
         mb_cuda(mb_cross_block_init(), "kernel attributes (cross-attention block)", error, cap) != 0 ||
         mb_cuda((int)cudaMalloc((void **)&st->d_token, sizeof(unsigned)), "cudaMalloc", error, cap) != 0 ||
         mb_cuda((int)cudaMalloc((void **)&st->d_status, sizeof(int)), "cudaMalloc", error, cap) != 0 ||

@@ -65,6 +65,7 @@ typedef struct mb_decoder {
     float *x, *nrm, *qkv, *attn, *q_x, *xctx, *hidden, *out, *rows_in, *logits;
     int8_t *qx;
     float *sx;
+    void *xsplit;               /* f16 weights: the activations' two f16 planes for the tensor-core product */
     float *partials;
     unsigned *counters;
     int use_tc, use_fuse1, use_xblock;
@@ -194,7 +195,7 @@ void mynah_b200_decoder_destroy(void *decoder) {
     }
     void *dev[] = {d->position, d->norm_out, d->emb, (void *)d->d_tables, d->heads_b, d->self_k,
                    d->self_v, d->cross_k, d->cross_v, d->x, d->nrm, d->qkv, d->attn, d->q_x,
-                   d->xctx, d->hidden, d->out, d->rows_in, d->logits, d->qx, d->sx, d->partials,
+                   d->xctx, d->hidden, d->out, d->rows_in, d->logits, d->qx, d->sx, d->xsplit, d->partials,
                    d->counters, d->d_stage_in, d->d_stage_out, d->d_eos_frame, d->d_min_frames,
                    d->d_history, d->d_mem_len, d->pf_mem, d->pf_nrm, d->pf_kv};
     for (size_t i = 0; i < sizeof(dev) / sizeof(dev[0]); ++i) cudaFree(dev[i]);
@@ -366,6 +367,8 @@ int mynah_b200_decoder_create(void *state, const mynah_b200_decoder_desc *desc, 
     D_TRY(dmalloc((void **)&d->rows_in, MB * W * sizeof(float), error, cap));
     D_TRY(dmalloc((void **)&d->qx, MB * F, error, cap));
     D_TRY(dmalloc((void **)&d->sx, MB * sizeof(float), error, cap));
+    if (q == MB_F16)
+        D_TRY(dmalloc(&d->xsplit, mb_gemm_tc_f16_split_halves(MB, F) * 2u, error, cap));
     if (d->tables != 0) {
         D_TRY(dmalloc((void **)&d->logits, MB * d->tables * d->vocab * sizeof(float), error, cap));
         d->history_frames = d->capacity;
@@ -486,6 +489,11 @@ static int product_fused(mb_decoder *d, const mb_dev_weight *w, const float *bia
     *count += 1u;
     if (d->use_tc && mb_gemm_tc_supported(w->qtype, w->n, w->k, nb))
         return mb_gemm_tc(&g, d->max_batch, d->d_status, d->st->stream);
+    if (d->use_tc && w->qtype == MB_F16 && d->xsplit != NULL && w->k <= d->ffn &&
+        mb_gemm_tc_f16_supported(w->n, w->k, nb)) {
+        *count += 1u;   /* the activation split is a launch of its own */
+        return mb_gemm_tc_f16(&g, d->xsplit, d->max_batch, d->d_status, d->st->stream);
+    }
     return mb_gemv(&g, d->st->stream);
 }
 

@@ -39,6 +39,7 @@
 #include "launch.h"
 
 #include "tma.cuh"
+#include "tc_common.cuh"
 
 #include <stdlib.h>
 #include <string.h>
@@ -53,7 +54,6 @@ constexpr int MAX_STAGES = 8;
 constexpr int A_BYTES = TM * KC;    // 16 KB
 constexpr int B_BYTES = BN * KC;    // 2 KB
 constexpr int TMEM_COLS = 32;       // smallest allocation; BN <= 32 columns used
-constexpr unsigned TC_SPIN = 1u << 24;
 
 struct TcP {
     const float *scales, *bias, *sx;
@@ -65,102 +65,6 @@ struct TcP {
     int batch, epilogue, strict;
     int ksplit;          // CTAs of a cluster that share one output tile along K
 };
-
-__device__ __forceinline__ unsigned saddr(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void bar_init(void *bar, unsigned count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(saddr(bar)), "r"(count));
-}
-__device__ __forceinline__ void bar_expect(void *bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(saddr(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool bar_wait(void *bar, unsigned parity, unsigned limit) {
-    for (unsigned i = 0; i < limit; ++i) {
-        unsigned done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(done) : "r"(saddr(bar)), "r"(parity) : "memory");
-        if (done) return true;
-    }
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, void *bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
-        "[%0], [%1, {%2, %3}], [%4];" ::"r"(saddr(dst)), "l"(map), "r"(x), "r"(y), "r"(saddr(bar))
-        : "memory");
-}
-
-// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of
-// 128 bytes, 8-row groups 1024 bytes apart.
-__device__ __forceinline__ uint64_t smem_desc_sw128(unsigned addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((addr & 0x3ffffu) >> 4);          // start address, 16-byte units
-    d |= (uint64_t)1 << 16;                           // leading byte offset (unused with swizzle)
-    d |= (uint64_t)(1024u >> 4) << 32;                // stride byte offset between 8-row groups
-    d |= (uint64_t)1 << 46;                           // descriptor version of this architecture
-    d |= (uint64_t)2 << 61;                           // 128-byte swizzle
-    return d;
-}
-// Instruction descriptor: int32 accumulate, signed 8-bit A and B, both K-major.
-__device__ __forceinline__ uint32_t instr_desc_i8(int m, int n) {
-    return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-__device__ __forceinline__ void mma_i8(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void mma_commit(void *bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(saddr(bar)) : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, int (&v)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-        : "r"(taddr) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// ---- thread-block cluster helpers (split K)
-__device__ __forceinline__ unsigned cluster_rank() {
-    unsigned r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// address of `ptr` (this CTA's shared memory) in the shared memory of cluster rank `rank`
-__device__ __forceinline__ unsigned remote_saddr(const void *ptr, unsigned rank) {
-    unsigned r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr(ptr)), "r"(rank));
-    return r;
-}
-__device__ __forceinline__ void remote_store(unsigned raddr, int v) {
-    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(raddr), "r"(v) : "memory");
-}
-__device__ __forceinline__ void remote_arrive(unsigned rbar) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(rbar) : "memory");
-}
-__device__ __forceinline__ bool bar_wait_cluster(void *bar, unsigned parity, unsigned limit) {
-    for (unsigned i = 0; i < limit; ++i) {
-        unsigned done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(done) : "r"(saddr(bar)), "r"(parity) : "memory");
-        if (done) return true;
-    }
-    return false;
-}
 
 // NS = stages of the ring (compile time: a run-time count was measured 30 us per step slower).
 // Six stages (109 KB) hold all of k = 768 and let two CTAs share an SM: used for grids of

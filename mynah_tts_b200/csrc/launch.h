@@ -157,6 +157,15 @@ int mb_gemm_tc_init(void);
 int mb_gemm_tc_supported(int qtype, size_t n, size_t k, size_t batch);
 int mb_gemm_tc(const mb_gemv_args *args, size_t qx_rows_alloc, int *status, mb_stream stream);
 
+/* f16 weights on the tensor cores from 16 lanes (gemm_tc_f16.cu): the f32 activations a->x
+ * are first split into two f16 planes in `split` (mb_gemm_tc_f16_split_halves() halves, rows
+ * of `rows_alloc` streams), then one tcgen05 product reads both.  Two launches.  Agrees with
+ * mb_gemv to f32 rounding of the sums, not bit for bit. */
+int mb_gemm_tc_f16_init(void);
+int mb_gemm_tc_f16_supported(size_t n, size_t k, size_t batch);
+size_t mb_gemm_tc_f16_split_halves(size_t rows_alloc, size_t k_max);
+int mb_gemm_tc_f16(const mb_gemv_args *args, void *split, size_t rows_alloc, int *status, mb_stream stream);
+
 /* Plain f32 row-major sgemm for the non-hot seam entries (prefill, codec):
  * C = alpha*op(A)*op(B) + beta*C. */
 int mb_sgemm(int trans_a, int trans_b, size_t m, size_t n, size_t k, float alpha,

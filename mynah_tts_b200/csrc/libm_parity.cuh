@@ -85,4 +85,18 @@ __device__ __forceinline__ float mb_expf_host(float x, const uint32_t *tab) {
         r = mb_apply_nibble(r, __ldg(tab + ((bits - MB_EXP_LO_BITS) >> 3)), bits - MB_EXP_LO_BITS);
     return r;
 }
+// Two-step form of mb_expf_host (x <= 0), as for tanhf: fetch the table word first.
+__device__ __forceinline__ uint32_t mb_exp_fetch(float x, const uint32_t *tab) {
+    const uint32_t bits = (uint32_t)__float_as_int(-x);
+    if (tab == nullptr || !(x <= 0.0f) || bits < MB_EXP_LO_BITS || bits >= MB_EXP_HI_BITS) return 0x88888888u;   // delta 0
+    return __ldg(tab + ((bits - MB_EXP_LO_BITS) >> 3));
+}
+__device__ __forceinline__ float mb_expf_host_with(float x, uint32_t word, bool have_tab) {
+    if (!(x <= 0.0f)) return (float)exp((double)x);
+    const float a = -x;
+    const uint32_t bits = (uint32_t)__float_as_int(a);
+    float r = mb_exp_base(a, bits, have_tab);
+    if (have_tab && bits >= MB_EXP_LO_BITS && bits < MB_EXP_HI_BITS) r = mb_apply_nibble(r, word, bits - MB_EXP_LO_BITS);
+    return r;
+}
 #endif

@@ -496,8 +496,9 @@ def test_full_size_distinct_lanes_match_oracle(name, monkeypatch):
     for three greedy frames against the CPU checker lane by lane: in strict mode every hidden
     row and pick must be the checker's bit for bit, on the tensor-core products (K = 768 and
     the K = 3072 ring with its cluster split, the six-stage logit-head product, the int4
-    tile) and again with MYNAH_B200_NO_TC=1 (the SIMT products); fast mode is held to its
-    tolerance, and its tensor-core and SIMT runs to each other bit for bit."""
+    tile) and again with MYNAH_B200_NO_TC=1 (the SIMT products); fast mode is held to rounding
+    on the typical lane and to its drift bound on every lane, and its tensor-core and SIMT
+    runs to each other bit for bit."""
     shape = synth.MAGPIE_357M
     qtype = QT[name]
     model = synth.make_model(shape, seed=51)
@@ -538,9 +539,60 @@ def test_full_size_distinct_lanes_match_oracle(name, monkeypatch):
             assert np.array_equal(h[:, b], want_hidden[:, b]), (name, "strict", no_tc, b)
         assert np.array_equal(t, want_tokens), (name, "strict", no_tc)
     hf, tf = got[(False, False)]
-    # frame 0 starts from the checker's exact state; later frames follow the lane's own picks
-    assert rel_err(hf[0], want_hidden[0]) < FAST_TOL[name]
+    # frame 0 starts from the checker's exact state (later frames follow the lane's own picks):
+    # a lane is within rounding unless one of its ~75k int8 activations rounded the other way,
+    # which twelve random-init layers amplify to the order of 1e-2 of the row
+    per_lane = np.array([rel_err(hf[0, b], want_hidden[0, b]) for b in range(lanes)])
+    assert np.median(per_lane) < 1e-4 and per_lane.max() < 5e-2, per_lane
     assert np.array_equal(hf, got[(False, True)][0]) and np.array_equal(tf, got[(False, True)][1])
+
+
+@pytest.mark.parametrize("shape_name,lanes", [("tiny", 16), ("tiny", 64), ("full", 17)])
+def test_f16_weights_on_the_tensor_cores_match_oracle(shape_name, lanes, tiny_model, monkeypatch):
+    """f16 weights at 16 or more lanes run on tcgen05 tiles (kind::f16, activations split into
+    two f16 halves): lanes that all differ, staggered positions, two frames, every lane
+    against the CPU restatement of the reference's f16 product (f32 activations, f16 weights,
+    src/qmat.c:319-377) within its 1e-3 bound, and against the same decoder on the SIMT
+    products (MYNAH_B200_NO_TC=1) to f32 rounding of the sums."""
+    if shape_name == "tiny":
+        shape, model = synth.TINY, tiny_model
+    else:
+        shape, model = synth.MAGPIE_357M, synth.make_model(synth.MAGPIE_357M, seed=61)
+    capacity, frames = 48, 2
+    pm = O.PortModel(model, O.F16)
+    streams, cross = [], []
+    positions = [(5 * b) % 37 for b in range(lanes)]
+    for b in range(lanes):
+        st = pm.new_stream(synth.make_memory(shape, seed=70 + b % 3), capacity)
+        st.length = positions[b]
+        streams.append(st)
+        cross.append((st.cross_k.copy(), st.cross_v.copy()))
+    rng = np.random.default_rng(23)
+    rows = rng.normal(0, 0.05, size=(frames, lanes, shape.width)).astype(np.float32)
+    want = np.stack([np.stack([streams[b].step(rows[f, b]) for b in range(lanes)]) for f in range(frames)])
+    got = {}
+    for no_tc in (False, True):
+        monkeypatch.delenv("MYNAH_B200_NO_TC", raising=False)
+        if no_tc:
+            monkeypatch.setenv("MYNAH_B200_NO_TC", "1")
+        be = Backend("f16", strict=False)
+        dec = Decoder(be, model, capacity=capacity, slots=lanes)
+        for b in range(lanes):
+            dec.slot_load(b, cross[b][0], cross[b][1])
+            dec.slot_set_length(b, positions[b])
+        launches0 = be.launch_count
+        got[no_tc] = np.stack([dec.step_batch(list(range(lanes)), rows[f]).copy() for f in range(frames)])
+        got[(no_tc, "launches")] = be.launch_count - launches0
+        dec.close(); be.close()
+    for st in streams:
+        st.close()
+    pm.close()
+    for f in range(frames):
+        for b in range(lanes):
+            assert rel_err(got[False][f, b], want[f, b]) < 1e-3, (f, b)
+            assert rel_err(got[False][f, b], got[True][f, b]) < 2e-5, (f, b)
+    # the tensor-core run really took the other path: a split launch rides with every product
+    assert got[(False, "launches")] > got[(True, "launches")]
 
 
 @pytest.mark.parametrize("strict", [True, False])
