@@ -54,6 +54,7 @@ struct AttnP {
     int box_cols, nbox;  // a 32-row tile is nbox TMA boxes of box_cols columns
     int depth;           // ring slots per tile kind (K, V)
     int ps, map4d;       // k_attn_exact: 128-byte segments per tile row (odd), rank of its tensor maps
+    int mchunks;         // k_attn_exact: 32-row chunks per copy
     int early;           // first tiles are requested before the dependency wait
     float scale;
 };
@@ -648,16 +649,17 @@ bool launch_exact(const mb_attn_args *a, AttnP &p, cudaStream_t s) {
         const int hg = p.heads / g, cw = hg * p.hw;
         const int threads = cw > hg * 32 ? cw : hg * 32;
         if ((cw % EX_SEG) != 0 || threads > 1024) continue;
+        const int mch = exact_chunks_per_copy(hg, p.hw, p.max_chunks);
         auto depth_for = [&](size_t room) {
             int depth = 0;
             for (int d = EX_RING_MAX; d >= 1 && depth == 0; --d)
-                if (exact_smem(hg, p.hw, p.max_chunks, d) + 1024u <= room) depth = d;
+                if (exact_smem(hg, p.hw, p.max_chunks, d, mch) + 1024u <= room) depth = d;
             return depth;
         };
         // more CTAs than SMs: two of them share an SM if each still gets a ring of two tiles
         int depth = (long)p.batch * g > sms ? depth_for((size_t)110 * 1024) : 0;
         if (depth < 2) depth = depth_for((size_t)ROWS_SMEM_MAX);
-        if (depth > 2 * p.max_chunks) depth = 2 * p.max_chunks;
+        if (depth > 2 * ((p.max_chunks + mch - 1) / mch)) depth = 2 * ((p.max_chunks + mch - 1) / mch);
         if (force_depth > 0 && force_depth < depth) depth = force_depth;
         if (depth < 1) continue;
         best_g = g;
@@ -678,6 +680,7 @@ bool launch_exact(const mb_attn_args *a, AttnP &p, cudaStream_t s) {
     p.box_cols = EX_SEG;
     p.nbox = 1;
     p.ps = exact_pitch_segments(hg, p.hw);
+    p.mchunks = exact_chunks_per_copy(hg, p.hw, p.max_chunks);
     size_t rows = a->cache_rows;
     if (rows == 0) rows = (size_t)(p.valid > p.position + 1 ? p.valid : p.position + 1);
     const size_t nseg = (size_t)cw / EX_SEG, row_bytes = (size_t)p.cache_stride * 4u;
@@ -686,7 +689,7 @@ bool launch_exact(const mb_attn_args *a, AttnP &p, cudaStream_t s) {
     // one wider than the group's when that count is even; the extra one is never fetched
     const size_t dims4[4] = {EX_SEG, nseg, (size_t)best_g, rows};
     const size_t strides4[3] = {EX_SEG * 4u, (size_t)cw * 4u, row_bytes};
-    const unsigned box4[4] = {EX_SEG, (unsigned)p.ps, 1u, CHUNK};
+    const unsigned box4[4] = {EX_SEG, (unsigned)p.ps, 1u, (unsigned)(CHUNK * p.mchunks)};
     p.map4d = 1;
     if (!mb_make_map_nd(&kmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a->k_cache, 4, dims4, strides4, box4, CU_TENSOR_MAP_SWIZZLE_128B) ||
         !mb_make_map_nd(&vmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a->v_cache, 4, dims4, strides4, box4, CU_TENSOR_MAP_SWIZZLE_128B)) {
@@ -694,14 +697,14 @@ bool launch_exact(const mb_attn_args *a, AttnP &p, cudaStream_t s) {
         // the next group's first one (fetched and ignored) or lies outside the row
         const size_t dims3[3] = {EX_SEG, (size_t)p.cache_stride / EX_SEG, rows};
         const size_t strides3[2] = {EX_SEG * 4u, row_bytes};
-        const unsigned box3[3] = {EX_SEG, (unsigned)p.ps, CHUNK};
+        const unsigned box3[3] = {EX_SEG, (unsigned)p.ps, (unsigned)(CHUNK * p.mchunks)};
         p.map4d = 0;
         if ((size_t)p.heads * p.hw > dims3[1] * EX_SEG ||
             !mb_make_map_nd(&kmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a->k_cache, 3, dims3, strides3, box3, CU_TENSOR_MAP_SWIZZLE_128B) ||
             !mb_make_map_nd(&vmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a->v_cache, 3, dims3, strides3, box3, CU_TENSOR_MAP_SWIZZLE_128B))
             return false;
     }
-    const size_t smem = exact_smem(hg, p.hw, p.max_chunks, best_depth);
+    const size_t smem = exact_smem(hg, p.hw, p.max_chunks, best_depth, p.mchunks);
     const dim3 grid((unsigned)best_g, (unsigned)p.batch), block((unsigned)threads);
     if (threads <= 384) mb_launch(k_attn_exact<384>, grid, block, smem, s, kmap, vmap, p);
     else mb_launch(k_attn_exact<1024>, grid, block, smem, s, kmap, vmap, p);

@@ -18,7 +18,9 @@
 //   the swizzle key (row * ps + segment) mod 8 differs between any 8 consecutive rows, so
 //   the threads of a warp, which read the same column piece of 32 different rows in the
 //   score pass, hit 32 different banks; the value pass reads along a row and is conflict
-//   free anyway.
+//   free anyway.  A copy brings p.mchunks chunks of 32 rows at once (one when a chunk is tens
+//   of KB, several for narrow head groups): copies of one CTA complete about one per memory
+//   round trip, so a copy should carry 30 KB or more.
 //   pass 1 (K tiles): thread (head, row) forms its row's score, d = 0 .. hw-1 in order.
 //   middle: max per head (exact in any order), e = expf(score - max) with the host libm's
 //           bits, the denominator by one thread per head in row order, weights e / den.
@@ -78,11 +80,12 @@ k_attn_exact(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ C
     const int hw = p.hw, heads = p.heads, width = heads * hw;
     const int groups = (int)gridDim.x, hg = heads / groups;
     const int h0 = blockIdx.x * hg, cw = hg * hw, c0 = h0 * hw;     // this CTA's heads and columns
-    const int ps = p.ps, tile_floats = CHUNK * ps * EX_SEG;
-    const int ns = (int)((valid + CHUNK - 1) / CHUNK), ntiles = 2 * ns;
+    const int ps = p.ps, chunk_floats = CHUNK * ps * EX_SEG, mch = p.mchunks, tile_floats = mch * chunk_floats;
+    const int ns = (int)((valid + CHUNK - 1) / CHUNK);      // chunks of this stream
+    const int nk = (ns + mch - 1) / mch, ntiles = 2 * nk;   // copies per pass, and in all
     const int depth = p.depth, scap = p.max_chunks * CHUNK;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    float *tiles = sm_exact;                                  // [depth][32 rows][ps][32], swizzled
+    float *tiles = sm_exact;                                  // [depth][mch * 32 rows][ps][32], swizzled
     float *qs = tiles + (long)depth * tile_floats;            // [cw]
     float *kn = qs + cw;                                      // [cw] the row appended now
     float *vn = kn + cw;
@@ -90,10 +93,11 @@ k_attn_exact(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ C
     float *stat = sc + (long)hg * scap;                       // [hg] max, [hg] denominator
     const unsigned tile_bytes = (unsigned)tile_floats * 4u;
     const unsigned long long stream_policy = mb_l2_evict_first();
-    // tile t of this CTA: K chunk t for t < ns, then V chunk t - ns; ring slot t % depth
+    // copy t of this CTA: K chunks [t * mch, (t + 1) * mch) for t < nk, then the V chunks
+    // likewise; ring slot t % depth
     auto issue = [&](int t) {
-        const int c = t < ns ? t : t - ns, rs = t % depth;
-        const CUtensorMap *map = t < ns ? &kmap : &vmap;
+        const int c = (t < nk ? t : t - nk) * mch, rs = t % depth;
+        const CUtensorMap *map = t < nk ? &kmap : &vmap;
         const int y = (int)(slot * p.slot_rows + (long)c * CHUNK);
         float *tile = tiles + (long)rs * tile_floats;
         mbar_expect_tx(&mbar[rs], tile_bytes);
@@ -133,7 +137,7 @@ k_attn_exact(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ C
     for (int t = 0; t < ntiles; ++t) {
         const int rs = t % depth;
         const unsigned parity = (unsigned)((t / depth) & 1);
-        if (t == ns) {
+        if (t == nk) {
             MB_TICK(2);
             // ---- all scores are in: max, exp, denominator, weights -------------------------
             if (p1) {
@@ -181,16 +185,35 @@ k_attn_exact(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ C
             MB_TICK(3);
         }
         if (!mbar_wait(&mbar[rs], parity, SPIN_LIMIT)) s_fail = 1u;
-        else if (t < ns) {
-            // ---- pass 1: this thread's row of chunk t ----------------------------------------
-            const long s = (long)t * CHUNK + lane;
+        else if (t < nk) {
+          for (int sub = 0; sub < mch; ++sub) {
+            // ---- pass 1: this thread's row of chunk t * mch + sub ----------------------------
+            const long s = ((long)t * mch + sub) * CHUNK + lane;
             if (p1 && s < valid) {
-                const float *tile = tiles + (long)rs * tile_floats;
+                const float *tile = tiles + (long)rs * tile_floats + (long)sub * chunk_floats;
                 const float *qh = qs + warp * hw;
                 float a = 0.0f;
                 if (append && s == pos) {
                     const float *kr = kn + warp * hw;
                     for (int d = 0; d < hw; ++d) a = __fadd_rn(a, __fmul_rn(qh[d], kr[d]));
+                } else if (hw == 64) {
+                    // the row's 64 floats first (sixteen independent 16-byte loads), then the chain:
+                    // a loop that loads inside the chain pays a shared-memory round trip per step
+                    // when few warps share a scheduler (measured 117 cycles per four elements)
+                    float4 kr[16];
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) {
+                        const int line = lane * ps + 2 * warp + (c >> 3);
+                        kr[c] = *reinterpret_cast<const float4 *>(tile + line * EX_SEG + (((c & 7) ^ (line & 7)) << 2));
+                    }
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) {
+                        const float4 qv = *reinterpret_cast<const float4 *>(qh + 4 * c);
+                        a = __fadd_rn(a, __fmul_rn(qv.x, kr[c].x));
+                        a = __fadd_rn(a, __fmul_rn(qv.y, kr[c].y));
+                        a = __fadd_rn(a, __fmul_rn(qv.z, kr[c].z));
+                        a = __fadd_rn(a, __fmul_rn(qv.w, kr[c].w));
+                    }
                 } else {
 #pragma unroll 4
                     for (int d4 = 0; d4 < hw; d4 += 4) {
@@ -206,20 +229,38 @@ k_attn_exact(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ C
                 sc[(long)warp * scap + s] = a;
                 if (a > lmax) lmax = a;
             }
+          }
         } else if (p2) {
-            // ---- pass 2: this thread's column over the rows of chunk t - ns -------------------
-            const int c = t - ns;
+          for (int sub = 0; sub < mch; ++sub) {
+            // ---- pass 2: this thread's column over the rows of chunk (t - nk) * mch + sub ------
+            const int c = (t - nk) * mch + sub;
+            if (c >= ns) break;
             const long s0 = (long)c * CHUNK;
             const int cnt = (int)min((long)CHUNK, valid - s0);
-            const float *tile = tiles + (long)rs * tile_floats;
+            const float *tile = tiles + (long)rs * tile_floats + (long)sub * chunk_floats;
             const float *w = sc + (long)h2 * scap + s0;
             const int fresh = (append && pos >= s0 && pos < s0 + cnt) ? (int)(pos - s0) : -1;
-#pragma unroll 8
-            for (int r = 0; r < cnt; ++r) {
+            // the chunk's 32 values of this column and its 32 weights first, then the chain
+            float vr[CHUNK], wr[CHUNK];
+#pragma unroll
+            for (int r = 0; r < CHUNK; ++r) {
                 const int line = r * ps + seg2;
-                const float v = r == fresh ? vn[col] : tile[line * EX_SEG + (((j2c ^ (line & 7)) << 2) | j2e)];
-                acc = __fadd_rn(acc, __fmul_rn(w[r], v));
+                vr[r] = tile[line * EX_SEG + (((j2c ^ (line & 7)) << 2) | j2e)];
             }
+#pragma unroll
+            for (int r4 = 0; r4 < CHUNK / 4; ++r4) {
+                const float4 w4 = *reinterpret_cast<const float4 *>(w + 4 * r4);
+                wr[4 * r4] = w4.x; wr[4 * r4 + 1] = w4.y; wr[4 * r4 + 2] = w4.z; wr[4 * r4 + 3] = w4.w;
+            }
+            if (fresh >= 0) {
+                const float vf = vn[col];
+#pragma unroll
+                for (int r = 0; r < CHUNK; ++r) vr[r] = r == fresh ? vf : vr[r];
+            }
+#pragma unroll
+            for (int r = 0; r < CHUNK; ++r)
+                if (r < cnt) acc = __fadd_rn(acc, __fmul_rn(wr[r], vr[r]));
+          }
         }
         __syncthreads();                                     // every thread is done with the slot
         done = t + 1;
@@ -268,10 +309,19 @@ inline int exact_pitch_segments(int hg, int hw) { return ((hg * hw) / EX_SEG) | 
 
 // Shared memory of one CTA of k_attn_exact: `depth` tiles, q and the appended K/V row, the
 // scores of the group's heads, two statistics per head.
-inline size_t exact_smem(int hg, int hw, int max_chunks, int depth) {
+inline size_t exact_smem(int hg, int hw, int max_chunks, int depth, int mchunks) {
     const size_t cw = (size_t)hg * hw;
-    return ((size_t)depth * CHUNK * exact_pitch_segments(hg, hw) * EX_SEG + 3u * cw + (size_t)hg * max_chunks * CHUNK + 2u * hg) *
-           sizeof(float);
+    return ((size_t)depth * mchunks * CHUNK * exact_pitch_segments(hg, hw) * EX_SEG + 3u * cw + (size_t)hg * max_chunks * CHUNK +
+            2u * hg) * sizeof(float);
+}
+// Chunks per copy: as many as fit in 40 KB, at least one, at most four (and no more than the
+// longest stream has).
+inline int exact_chunks_per_copy(int hg, int hw, int max_chunks) {
+    const size_t chunk_bytes = (size_t)CHUNK * exact_pitch_segments(hg, hw) * EX_SEG * sizeof(float);
+    int m = (int)((40u * 1024u) / chunk_bytes);
+    if (m > 4) m = 4;
+    if (m > max_chunks) m = max_chunks;
+    return m < 1 ? 1 : m;
 }
 
 }  // namespace

@@ -222,14 +222,27 @@ k_cross_block(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
             if (mbar_wait(&mbar[c], 0u, SPIN_LIMIT)) {
                 const float *tile = Kt + (long)c * tile_floats + r * 32;
                 float dot = 0.0f;
-#pragma unroll 4
-                for (int d4 = 0; d4 < XW; d4 += 4) {
-                    const float4 kv = *reinterpret_cast<const float4 *>(tile + (d4 >> 5) * 1024 + (((((d4 & 31) >> 2)) ^ (r & 7)) << 2));
-                    const float4 qv = *reinterpret_cast<const float4 *>(qs + d4);
-                    dot = __fadd_rn(dot, __fmul_rn(qv.x, kv.x));
-                    dot = __fadd_rn(dot, __fmul_rn(qv.y, kv.y));
-                    dot = __fadd_rn(dot, __fmul_rn(qv.z, kv.z));
-                    dot = __fadd_rn(dot, __fmul_rn(qv.w, kv.w));
+                // sixteen 16-byte pieces of the row at a time into registers, then their part of
+                // the chain (loads inside the chain would each cost a shared-memory round trip)
+                for (int d0 = 0; d0 < XW; d0 += 64) {
+                    float4 kr[16];
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) {
+                        const int d4 = d0 + 4 * c;
+                        kr[c] = d4 < XW ? *reinterpret_cast<const float4 *>(tile + (d4 >> 5) * 1024 + (((((d4 & 31) >> 2)) ^ (r & 7)) << 2))
+                                        : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) {
+                        const int d4 = d0 + 4 * c;
+                        if (d4 < XW) {
+                            const float4 qv = *reinterpret_cast<const float4 *>(qs + d4);
+                            dot = __fadd_rn(dot, __fmul_rn(qv.x, kr[c].x));
+                            dot = __fadd_rn(dot, __fmul_rn(qv.y, kr[c].y));
+                            dot = __fadd_rn(dot, __fmul_rn(qv.z, kr[c].z));
+                            dot = __fadd_rn(dot, __fmul_rn(qv.w, kr[c].w));
+                        }
+                    }
                 }
                 a = __fmul_rn(dot, p.scale);
             } else {
@@ -258,9 +271,17 @@ k_cross_block(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
                 const int cnt = min(CHUNK, rows - cc * CHUNK);
                 const float *tile = col + (long)cc * tile_floats;
                 const float *w = scs + cc * CHUNK;
-#pragma unroll 8
-                for (int rr = 0; rr < cnt; ++rr)
-                    acc = __fadd_rn(acc, __fmul_rn(w[rr], tile[rr * 32 + ((jc ^ (rr & 7)) << 2)]));
+                float vr[CHUNK], wr[CHUNK];
+#pragma unroll
+                for (int rr = 0; rr < CHUNK; ++rr) vr[rr] = tile[rr * 32 + ((jc ^ (rr & 7)) << 2)];
+#pragma unroll
+                for (int r4 = 0; r4 < CHUNK / 4; ++r4) {
+                    const float4 w4 = *reinterpret_cast<const float4 *>(w + 4 * r4);
+                    wr[4 * r4] = w4.x; wr[4 * r4 + 1] = w4.y; wr[4 * r4 + 2] = w4.z; wr[4 * r4 + 3] = w4.w;
+                }
+#pragma unroll
+                for (int rr = 0; rr < CHUNK; ++rr)
+                    if (rr < cnt) acc = __fadd_rn(acc, __fmul_rn(wr[rr], vr[rr]));
             }
             ctx = acc;
         }
