@@ -677,18 +677,20 @@ def main():
                                         "narrow margins)" if other == "fast" else "token-identical to the reference")}
             odec.close(); obe.close()
             extras["gemv_pool"] = gemv_pool_case(backend)
-            # one f32 decoder step at position 256, batch 1
-            fbe = Backend("f32", strict=strict, device=local_rank)
-            fdec = make_decoder(fbe, [0], 256 + 40)
-            fms, _ = timed_jobs(fdec, [0], start_codes_of([0]), 32, 1, 1, 256)
+            # one f32 decoder step at position 256, batch 1 (BASELINE config 2), in both modes:
+            # strict f32 products keep the reference's sequential sum (one thread per output)
             fbytes = step_bytes(shape, "f32", 1, 256 + 15.5)
-            extras["f32_step_position_256"] = {"us_per_step": fms * 1000.0 / 32, "mode": args.mode,
-                                               "gbs": fbytes / (fms * 1e-3 / 32) / 1e9,
-                                               "frac_of_measured_hbm": fbytes / (fms * 1e-3 / 32) / 1e9 / peak,
-                                               "bytes_per_step": fbytes,
-                                               "note": "f32 weights (349 MB) exceed L2: every step streams them from HBM; "
-                                                       "32 steps from position 256, batch 1"}
-            fdec.close(); fbe.close()
+            f32 = {"bytes_per_step": fbytes,
+                   "note": "f32 weights (349 MB) exceed L2: every step streams them from HBM; 32 steps from "
+                           "position 256, batch 1"}
+            for fmode in ("fast", "strict"):
+                fbe = Backend("f32", strict=fmode == "strict", device=local_rank)
+                fdec = make_decoder(fbe, [0], 256 + 40)
+                fms, _ = timed_jobs(fdec, [0], start_codes_of([0]), 32, 1, 1, 256)
+                f32[fmode] = {"us_per_step": fms * 1000.0 / 32, "gbs": fbytes / (fms * 1e-3 / 32) / 1e9,
+                              "frac_of_measured_hbm": fbytes / (fms * 1e-3 / 32) / 1e9 / peak}
+                fdec.close(); fbe.close()
+            extras["f32_step_position_256"] = f32
             extras["generate"] = local_generate_extra(backend, B, args)
             extras["ragged_int4"] = ragged_int4_extra(shape, model, local_rank, B)
         cpu = None
