@@ -691,6 +691,24 @@ def main():
                               "frac_of_measured_hbm": fbytes / (fms * 1e-3 / 32) / 1e9 / peak}
                 fdec.close(); fbe.close()
             extras["f32_step_position_256"] = f32
+            # the context prefill (decoder_run with count > 1): 217 rows of one request at once,
+            # the real model's context length (src/graph.c:2786-2787); a quantized model
+            # multiplies them with its f32 weights, as the reference does
+            pre = {"rows": 217, "note": "217 rows pushed through the stack together (f32 weights for more than 16 "
+                                        "rows, as in the reference); strict keeps sequential f32 sums"}
+            prows = np.random.default_rng([SEED, 0x707265]).normal(0, 0.05, size=(217, shape.width)).astype(np.float32)
+            for pmode in ("fast", "strict"):
+                pbe = Backend(args.quant, strict=pmode == "strict", device=local_rank)
+                pdec = Decoder(pbe, model, capacity=256, slots=1, max_batch=217, keep_f32_weights=True)
+                ck, cv = synthetic_cross_kv(shape, 0)
+                pdec.slot_load(0, ck, cv)
+                pdec.prefill(0, prows)
+                pdec.slot_set_length(0, 0)
+                t0 = time.perf_counter()
+                pdec.prefill(0, prows)
+                pre[pmode + "_ms"] = (time.perf_counter() - t0) * 1000.0
+                pdec.close(); pbe.close()
+            extras["prefill"] = pre
             extras["generate"] = local_generate_extra(backend, B, args)
             extras["ragged_int4"] = ragged_int4_extra(shape, model, local_rank, B)
         cpu = None

@@ -224,7 +224,8 @@ typedef struct {
                             * src/graph.c:2820) */
     size_t capacity;       /* self-KV rows per slot (src/graph.c:3804-3806) */
     size_t slots;          /* resident requests (each owns KV) */
-    size_t max_batch;      /* most slots stepped together */
+    size_t max_batch;      /* most lanes of one launch sequence: slots stepped together, or rows of one
+                            * request prefilled together (may exceed slots for the latter) */
     size_t max_positions;  /* rows of the position table */
     const mynah_b200_layer_weights *layer; /* [layers] */
     const float *position;  /* decoder.position_embeddings.weight [max_positions, width] */
@@ -234,6 +235,9 @@ typedef struct {
     const float *const *embeddings; /* tables x [vocab, width]  (audio_embeddings.N.weight) */
     const float *const *head_w;     /* tables x [vocab, width] */
     const float *const *head_b;     /* tables x [vocab] */
+    /* nonzero: a quantized decoder also keeps f32 copies of the layer weights, which
+     * _prefill of more than 16 rows multiplies with (as the reference does) */
+    int keep_f32_weights;
 } mynah_b200_decoder_desc;
 
 /* Uploads and packs every weight once (format and strictness of `state`) and
@@ -270,6 +274,16 @@ int mynah_b200_decoder_slot_read_kv(void *decoder, size_t slot, float *self_k, f
                                     char *error, size_t cap);
 /* Run only the first n layers (then the output norm); n = layers restores. */
 int mynah_b200_decoder_set_layers(void *decoder, size_t n, char *error, size_t cap);
+
+/* Push `count` new rows [count][width] (HOST) of the request in `slot` through the stack
+ * together: the contract of decoder_run with count > 1 (src/graph.c:3286-3654, the context
+ * prefill) -- position embedding, all layers with causal attention among the new rows and
+ * over the rows already cached, K/V appended, the slot's length advanced by count, and the
+ * output-norm row of the LAST new row in out_last [width] (HOST).  count <= max_batch.
+ * As in the reference, a quantized model multiplies more than 16 rows with its f32 weights
+ * (keep_f32_weights) and at most 16 with the packed ones.  Synchronous. */
+int mynah_b200_decoder_prefill(void *decoder, size_t slot, const float *rows, size_t count,
+                               float *out_last, char *error, size_t cap);
 
 /* One decoder step for `batch` slots: the contract of decoder_step_batch
  * (src/graph.c:3127-3284) with HOST rows -- inputs[b] and outs[b] are `width`

@@ -228,7 +228,7 @@ class Decoder:
     same accessors)."""
 
     def __init__(self, backend: Backend, model, capacity: int, slots: int, max_batch: int | None = None,
-                 with_heads: bool = True):
+                 with_heads: bool = True, keep_f32_weights: bool = False):
         self.backend = backend
         self.model = model
         s = model.shape
@@ -256,6 +256,7 @@ class Decoder:
         desc.max_batch, desc.max_positions = self.max_batch, s.max_positions
         desc.layer = layers
         desc.position, desc.norm_out = fp(model.position), fp(model.norm_out)
+        desc.keep_f32_weights = int(keep_f32_weights)
         if with_heads:
             tabs = (capi.c_float_p * s.tables)(*[fp(model.embedding(t)) for t in range(s.tables)])
             hw = (capi.c_float_p * s.tables)(*[fp(model.head_weight(t)) for t in range(s.tables)])
@@ -321,6 +322,14 @@ class Decoder:
         """Cross K/V of a request made on the device from its text-encoder memory."""
         mem = np.ascontiguousarray(memory, np.float32)
         call(capi.lib().mynah_b200_decoder_slot_prefill, self.handle, slot, fp(mem), mem.shape[0])
+
+    def prefill(self, slot: int, rows: np.ndarray) -> np.ndarray:
+        """decoder_run with count > 1: rows [count, width] of one request pushed through the
+        stack together; returns the output-norm row of the last one."""
+        rows = np.ascontiguousarray(rows, np.float32)
+        out = np.empty((self.shape.width,), np.float32)
+        call(capi.lib().mynah_b200_decoder_prefill, self.handle, slot, fp(rows), rows.shape[0], fp(out))
+        return out
 
     def slot_read_cross(self, slot: int):
         s = self.shape

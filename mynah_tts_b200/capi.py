@@ -53,6 +53,7 @@ class DecoderDesc(C.Structure):
         ("tables", sz), ("vocab", sz), ("codebook_size", sz), ("eos_id", sz),
         ("embeddings", C.POINTER(c_float_p)), ("head_w", C.POINTER(c_float_p)),
         ("head_b", C.POINTER(c_float_p)),
+        ("keep_f32_weights", C.c_int),
     ]
 
 
@@ -150,6 +151,7 @@ SIGNATURES = {
     "mynah_b200_decoder_destroy": (None, [C.c_void_p]),
     "mynah_b200_decoder_slot_load": (C.c_int, [C.c_void_p, sz, c_float_p, c_float_p, sz, c_float_p, c_float_p, sz, _E]),
     "mynah_b200_decoder_slot_prefill": (C.c_int, [C.c_void_p, sz, c_float_p, sz, _E]),
+    "mynah_b200_decoder_prefill": (C.c_int, [C.c_void_p, sz, c_float_p, sz, c_float_p, _E]),
     "mynah_b200_decoder_slot_read_cross": (C.c_int, [C.c_void_p, sz, c_float_p, c_float_p, _E]),
     "mynah_b200_decoder_slot_length": (C.c_int, [C.c_void_p, sz, C.POINTER(sz), _E]),
     "mynah_b200_decoder_slot_set_length": (C.c_int, [C.c_void_p, sz, sz, _E]),

@@ -55,6 +55,7 @@ struct AttnP {
     int depth;           // ring slots per tile kind (K, V)
     int ps, map4d;       // k_attn_exact: 128-byte segments per tile row (odd), rank of its tensor maps
     int mchunks;         // k_attn_exact: 32-row chunks per copy
+    int inv_norm;        // strict kernels: weights e * (1 / den) (the reference's multi-row softmax) instead of e / den
     int early;           // first tiles are requested before the dependency wait
     float scale;
 };
@@ -123,7 +124,12 @@ __global__ void __launch_bounds__(256) k_attn_strict(AttnP p) {
     }
     __syncthreads();
     const float den = s_denom;
-    for (long s = threadIdx.x; s < valid; s += blockDim.x) sc[s] = __fdiv_rn(sc[s], den);
+    if (p.inv_norm) {
+        const float inv = den > 0.0f ? __fdiv_rn(1.0f, den) : 0.0f;
+        for (long s = threadIdx.x; s < valid; s += blockDim.x) sc[s] = __fmul_rn(sc[s], inv);
+    } else {
+        for (long s = threadIdx.x; s < valid; s += blockDim.x) sc[s] = __fdiv_rn(sc[s], den);
+    }
     __syncthreads();
     for (int d = threadIdx.x; d < hw; d += blockDim.x) {
         float a = 0.0f;
@@ -755,6 +761,7 @@ extern "C" int mb_attention(const mb_attn_args *a, mb_stream stream) {
     p.position = (long)a->position; p.valid = (long)a->valid;
     p.heads = (int)a->heads; p.hw = (int)a->head_width; p.batch = (int)a->batch;
     p.scale = a->scale;
+    p.inv_norm = a->softmax_inverse ? 1 : 0;
     cudaStream_t s = (cudaStream_t)stream;
     // Longest row any lane can attend over: callers with per-lane positions pass
     // the cache capacity in `valid`.

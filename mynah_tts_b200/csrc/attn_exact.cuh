@@ -178,8 +178,14 @@ k_attn_exact(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ C
             __syncthreads();
             for (int h = 0; h < hg; ++h) {
                 const float den = stat[hg + h];
-                for (long s = tid; s < valid; s += blockDim.x)
-                    sc[(long)h * scap + s] = __fdiv_rn(sc[(long)h * scap + s], den);
+                if (p.inv_norm) {     // softmax_row_inplace of the multi-row path: values *= 1 / total
+                    const float inv = den > 0.0f ? __fdiv_rn(1.0f, den) : 0.0f;
+                    for (long s = tid; s < valid; s += blockDim.x)
+                        sc[(long)h * scap + s] = __fmul_rn(sc[(long)h * scap + s], inv);
+                } else {
+                    for (long s = tid; s < valid; s += blockDim.x)
+                        sc[(long)h * scap + s] = __fdiv_rn(sc[(long)h * scap + s], den);
+                }
             }
             __syncthreads();
             MB_TICK(3);

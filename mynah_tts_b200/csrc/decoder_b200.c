@@ -26,6 +26,9 @@ enum { MODE_STEP = 0, MODE_FRAME = 1, MODE_LOCAL = 2, MODE_LOCAL_ONLY = 3, MODE_
 typedef struct {
     float *norm_self, *norm_xattn_query, *norm_pos_ff;
     mb_dev_weight qkv, o_self, q_cross, o_cross, ffn_up, ffn_down;
+    /* optional f32 copies (a quantized decoder that prefills more than 16 rows at once: the
+     * reference then multiplies with the f32 weights, src/qmat.c:773-788) */
+    mb_dev_weight qkv32, o_self32, q_cross32, o_cross32, ffn_up32, ffn_down32;
     float *norm_xattn_memory;   /* optional: with kv_cross, lets a slot's cross K/V be made here */
     mb_dev_weight kv_cross;     /* f32 [2*xw, width]; the reference runs it unquantized */
 } dec_layer;
@@ -179,6 +182,9 @@ void mynah_b200_decoder_destroy(void *decoder) {
             mb_weight_release(&L->qkv); mb_weight_release(&L->o_self);
             mb_weight_release(&L->q_cross); mb_weight_release(&L->o_cross);
             mb_weight_release(&L->ffn_up); mb_weight_release(&L->ffn_down);
+            mb_weight_release(&L->qkv32); mb_weight_release(&L->o_self32);
+            mb_weight_release(&L->q_cross32); mb_weight_release(&L->o_cross32);
+            mb_weight_release(&L->ffn_up32); mb_weight_release(&L->ffn_down32);
         }
         free(d->L);
     }
@@ -231,7 +237,7 @@ int mynah_b200_decoder_create(void *state, const mynah_b200_decoder_desc *desc, 
     *decoder = NULL;
     if (desc->layers == 0 || desc->width == 0 || desc->heads == 0 || desc->width % desc->heads != 0 ||
         desc->xattn_width == 0 || desc->memory_length == 0 || desc->capacity == 0 ||
-        desc->slots == 0 || desc->max_batch == 0 || desc->max_batch > desc->slots ||
+        desc->slots == 0 || desc->max_batch == 0 ||
         desc->max_batch > 1024u || desc->layer == NULL || desc->position == NULL ||
         desc->norm_out == NULL || desc->max_positions < desc->capacity) {
         mb_set_error(error, cap, "invalid decoder shape");
@@ -291,6 +297,14 @@ int mynah_b200_decoder_create(void *state, const mynah_b200_decoder_desc *desc, 
         D_TRY(mb_weight_build(st, s->o_cross_w, W, XW, q, &L->o_cross, error, cap));
         D_TRY(mb_weight_build(st, s->ffn_up_w, F, W, q, &L->ffn_up, error, cap));
         D_TRY(mb_weight_build(st, s->ffn_down_w, W, F, q, &L->ffn_down, error, cap));
+        if (desc->keep_f32_weights && q != MB_F32) {
+            D_TRY(mb_weight_build(st, s->qkv_w, 3u * W, W, MB_F32, &L->qkv32, error, cap));
+            D_TRY(mb_weight_build(st, s->o_self_w, W, W, MB_F32, &L->o_self32, error, cap));
+            D_TRY(mb_weight_build(st, s->q_cross_w, XW, W, MB_F32, &L->q_cross32, error, cap));
+            D_TRY(mb_weight_build(st, s->o_cross_w, W, XW, MB_F32, &L->o_cross32, error, cap));
+            D_TRY(mb_weight_build(st, s->ffn_up_w, F, W, MB_F32, &L->ffn_up32, error, cap));
+            D_TRY(mb_weight_build(st, s->ffn_down_w, W, F, MB_F32, &L->ffn_down32, error, cap));
+        }
         if (ok)
             d->weight_bytes += L->qkv.bytes + L->o_self.bytes + L->q_cross.bytes + L->o_cross.bytes +
                                L->ffn_up.bytes + L->ffn_down.bytes + 3u * W * sizeof(float);
@@ -1289,6 +1303,184 @@ int mynah_b200_decoder_generate(void *decoder, const unsigned *slots, size_t bat
                                 float *elapsed_ms, char *error, size_t cap) {
     return decode_loop((mb_decoder *)decoder, MODE_LOCAL, samplers, slots, batch, codes, frames,
                        min_frames, tokens, eos_frame, elapsed_ms, error, cap);
+}
+
+/* ------------------------------------------------------------------ prefill */
+/* One product of the prefill: through the decoder's packed weight with quantized rows
+ * (d->qx/d->sx) when `packed`, else through the f32 weight with the f32 rows. */
+static int prefill_product(mb_decoder *d, const mb_dev_weight *wq, const mb_dev_weight *w32, int packed,
+                           const float *act_f32, float *out, size_t out_stride, size_t nb, int epilogue,
+                           unsigned *count) {
+    if (packed) return product(d, wq, NULL, act_f32, out, out_stride, nb, epilogue, count);
+    mb_gemv_args g;
+    memset(&g, 0, sizeof(g));
+    mb_gemv_bind_weight(&g, w32, NULL);
+    g.x = act_f32;
+    g.out = out;
+    g.out_stride = out_stride;
+    g.batch = nb;
+    g.n_active = d->d_n_active;
+    g.epilogue = epilogue;
+    g.strict = d->st->strict;
+    g.tanh_tab = d->st->libm.tanh_tab;
+    *count += 1u;
+    return mb_gemv(&g, d->st->stream);
+}
+
+/* decoder_run with count > 1 (src/graph.c:3506-3641): `count` new rows of ONE request go
+ * through the stack together; row i attends the request's cached rows and the new rows up
+ * to itself.  The rows ride as `count` lanes that share the slot at consecutive positions:
+ * the new K/V rows of a layer are appended first (they lie back to back in the cache), then
+ * every lane attends up to its own position.  As in the reference, more than 16 rows of a
+ * quantized model are multiplied with the f32 weights (src/qmat.c:773-788: the quantized
+ * product is taken for at most 16 rows), at most 16 with the packed weights row by row; the
+ * self-attention weights are e * (1 / sum) (softmax_row_inplace, src/graph.c:245-257).  The
+ * output-norm row of the last new row is returned (src/graph.c:3640-3642). */
+int mynah_b200_decoder_prefill(void *decoder, size_t slot, const float *rows, size_t count,
+                               float *out_last, char *error, size_t cap) {
+    mb_decoder *d = (mb_decoder *)decoder;
+    if (check_slot(d, slot, error, cap) != 0) return -1;
+    if (rows == NULL || out_last == NULL || count == 0) {
+        mb_set_error(error, cap, "invalid prefill buffers");
+        return -1;
+    }
+    const size_t start = d->slot_len[slot];
+    if (start + count > d->capacity || start + count > d->max_positions) {
+        mb_set_error(error, cap, "decoder cache capacity exceeded");          /* src/graph.c:3309-3312 */
+        return -1;
+    }
+    if (count > d->max_batch) {
+        mb_set_error(error, cap, "prefill: more rows than the decoder's max_batch");   /* src/graph.c:3313-3316 */
+        return -1;
+    }
+    mb_state *st = d->st;
+    const int q = quantized_mode(d);
+    const int f32_model = st->quant == MB_F32;
+    /* packed weights: an f32 or f16 model always; a quantized one for at most 16 rows */
+    const int packed = f32_model || st->quant == MB_F16 || count <= 16u;
+    if (!packed && d->L[0].qkv32.w == NULL) {
+        mb_set_error(error, cap, "prefill of more than 16 rows of a quantized model uses the f32 weights: "
+                                 "create the decoder with keep_f32_weights");
+        return -1;
+    }
+    const int quant_rows = q && packed;      /* products read int8 rows */
+    cudaStream_t s = st->stream;
+    const size_t W = d->width, F = d->ffn, XW = d->xw;
+    const float self_scale = 1.0f / sqrtf((float)d->hw), cross_scale = 1.0f / sqrtf((float)XW);
+    for (size_t b = 0; b < count; ++b) {
+        d->h_slots[b] = (int)slot;
+        d->h_lens[b] = (int)(start + b);
+    }
+    MB_TRY(cudaMemcpyAsync(d->d_slots, d->h_slots, count * sizeof(int), cudaMemcpyHostToDevice, s), "stage slots");
+    MB_TRY(cudaMemcpyAsync(d->d_lens, d->h_lens, count * sizeof(int), cudaMemcpyHostToDevice, s), "stage positions");
+    MB_TRY(cudaMemcpyAsync(d->d_n_active, &d->h_table[count], sizeof(int), cudaMemcpyHostToDevice, s), "stage lane count");
+    memcpy(d->h_rows, rows, count * W * sizeof(float));
+    MB_TRY(cudaMemcpyAsync(d->rows_in, d->h_rows, count * W * sizeof(float), cudaMemcpyHostToDevice, s), "stage rows");
+    unsigned launches = 0;
+    int rc = 0;
+#define R_TRY(expr) do { if (rc == 0) rc = (int)(expr); } while (0)
+    R_TRY(mb_add_position(d->rows_in, d->position, d->d_lens, d->x, count, W, d->d_n_active, s));
+    launches += 1u;
+    for (size_t l = 0; l < d->layers_run && rc == 0; ++l) {
+        const dec_layer *L = &d->L[l];
+        mb_attn_args a;
+        R_TRY(mb_layernorm(d->x, d->nrm, L->norm_self, NULL, count, W, 1.0e-5f, quant_rows ? d->qx : NULL,
+                           quant_rows ? d->sx : NULL, d->d_n_active, st->strict, s));
+        launches += 1u;
+        R_TRY(prefill_product(d, &L->qkv, &L->qkv32, packed, d->nrm, d->qkv, 3u * W, count, MB_EPI_STORE, &launches));
+        /* the new rows' K and V into the cache: rows start .. start + count - 1 of this layer */
+        float *kc = d->self_k + ((slot * d->layers + l) * d->capacity + start) * W;
+        float *vc = d->self_v + ((slot * d->layers + l) * d->capacity + start) * W;
+        R_TRY(cudaMemcpy2DAsync(kc, W * sizeof(float), d->qkv + W, 3u * W * sizeof(float), W * sizeof(float), count,
+                                cudaMemcpyDeviceToDevice, s));
+        R_TRY(cudaMemcpy2DAsync(vc, W * sizeof(float), d->qkv + 2u * W, 3u * W * sizeof(float), W * sizeof(float), count,
+                                cudaMemcpyDeviceToDevice, s));
+        memset(&a, 0, sizeof(a));
+        a.q = d->qkv;
+        a.q_stride = 3u * W;
+        a.k_cache = d->self_k + l * d->capacity * W;
+        a.v_cache = d->self_v + l * d->capacity * W;
+        a.slot_stride = d->layers * d->capacity * W;
+        a.slots = d->d_slots;
+        a.lens = d->d_lens;                 /* lane b attends rows 0 .. start + b */
+        a.valid = d->capacity;
+        a.cache_rows = (d->slots - 1u) * d->layers * d->capacity + d->capacity;
+        a.cache_stride = W;
+        a.heads = d->heads;
+        a.head_width = d->hw;
+        a.scale = self_scale;
+        a.out = d->attn;
+        a.out_stride = W;
+        a.qx = quant_rows ? d->qx : NULL;
+        a.sx = quant_rows ? d->sx : NULL;
+        a.batch = count;
+        a.n_active = d->d_n_active;
+        a.strict = st->strict;
+        a.exp_tab = st->libm.exp_tab;
+        a.partials = d->partials;
+        a.counters = d->counters;
+        a.status = d->d_status;
+        a.sm_count = st->sm_count;
+        a.softmax_inverse = 1;
+        a.launched = &launches;
+        R_TRY(mb_attention(&a, s));
+        R_TRY(prefill_product(d, &L->o_self, &L->o_self32, packed, d->attn, d->x, W, count, MB_EPI_RESIDUAL, &launches));
+        R_TRY(mb_layernorm(d->x, d->nrm, L->norm_xattn_query, NULL, count, W, 1.0e-5f, quant_rows ? d->qx : NULL,
+                           quant_rows ? d->sx : NULL, d->d_n_active, st->strict, s));
+        launches += 1u;
+        R_TRY(prefill_product(d, &L->q_cross, &L->q_cross32, packed, d->nrm, d->q_x, XW, count, MB_EPI_STORE, &launches));
+        memset(&a, 0, sizeof(a));
+        a.q = d->q_x;
+        a.q_stride = XW;
+        a.k_cache = d->cross_k + l * d->T * XW;
+        a.v_cache = d->cross_v + l * d->T * XW;
+        a.slot_stride = d->layers * d->T * XW;
+        a.slots = d->d_slots;
+        a.valid = d->T;
+        a.valid_per_slot = d->d_mem_len;
+        a.cache_rows = (d->slots - 1u) * d->layers * d->T + d->T;
+        a.cache_stride = XW;
+        a.heads = 1;
+        a.head_width = XW;
+        a.scale = cross_scale;
+        a.out = d->xctx;
+        a.out_stride = XW;
+        a.qx = quant_rows ? d->qx : NULL;
+        a.sx = quant_rows ? d->sx : NULL;
+        a.batch = count;
+        a.n_active = d->d_n_active;
+        a.strict = st->strict;
+        a.exp_tab = st->libm.exp_tab;
+        a.partials = d->partials;
+        a.counters = d->counters;
+        a.status = d->d_status;
+        a.sm_count = st->sm_count;
+        a.launched = &launches;
+        R_TRY(mb_attention(&a, s));
+        R_TRY(prefill_product(d, &L->o_cross, &L->o_cross32, packed, d->xctx, d->x, W, count, MB_EPI_RESIDUAL, &launches));
+        R_TRY(mb_layernorm(d->x, d->nrm, L->norm_pos_ff, NULL, count, W, 1.0e-5f, quant_rows ? d->qx : NULL,
+                           quant_rows ? d->sx : NULL, d->d_n_active, st->strict, s));
+        launches += 1u;
+        R_TRY(prefill_product(d, &L->ffn_up, &L->ffn_up32, packed, d->nrm, d->hidden, F, count, MB_EPI_GELU, &launches));
+        if (quant_rows) {
+            R_TRY(mb_quant_rows(d->hidden, count, F, d->qx, d->sx, d->d_n_active, s));
+            launches += 1u;
+        }
+        R_TRY(prefill_product(d, &L->ffn_down, &L->ffn_down32, packed, d->hidden, d->x, W, count, MB_EPI_RESIDUAL, &launches));
+    }
+    /* the output norm of the last new row only */
+    R_TRY(mb_layernorm(d->x + (count - 1u) * W, d->out, d->norm_out, NULL, 1u, W, 1.0e-5f, NULL, NULL, NULL, st->strict, s));
+    launches += 1u;
+#undef R_TRY
+    if (rc != 0) return mb_cuda(rc, "decoder prefill", error, cap);
+    st->launches += launches;
+    MB_TRY(cudaMemcpyAsync(d->h_out, d->out, W * sizeof(float), cudaMemcpyDeviceToHost, s), "read output");
+    MB_TRY(cudaStreamSynchronize(s), "cudaStreamSynchronize");
+    if (check_status(d, error, cap) != 0) return -1;
+    memcpy(out_last, d->h_out, W * sizeof(float));
+    d->slot_len[slot] += count;
+    mb_clear_error(error, cap);
+    return 0;
 }
 
 /* ------------------------------------------------------- local transformer */

@@ -208,6 +208,8 @@ typedef struct {
                            * launches before this one, so the kernel may request its first cache tiles
                            * before it waits for its predecessor (programmatic dependent launch) */
     unsigned *launched;   /* optional: incremented by the number of kernels the call enqueued */
+    int softmax_inverse;  /* strict: weights e * (1 / sum) as the reference's multi-row self attention forms
+                           * them (softmax_row_inplace, src/graph.c:245-257), not e / sum */
 } mb_attn_args;
 int mb_attention(const mb_attn_args *args, mb_stream stream);
 size_t mb_attention_scratch_floats(size_t batch, size_t heads, size_t max_valid, size_t head_width);

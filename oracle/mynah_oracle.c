@@ -648,6 +648,110 @@ int orc_decoder_step(orc_stream *s, const float *input, float *out) {
     return 0;
 }
 
+/* decoder_run with count > 1, the multi-row prefill: src/graph.c:3286-3654 in the
+ * reference's scalar build (scalar sgemm src/backend.c:343-354, scalar GELU
+ * src/kernels.c:374-380).  Products of more than 16 rows use the f32 weights whatever the
+ * cache's format (src/qmat.c:773-788: quantized only for count <= 16), at most 16 rows go
+ * row by row through the packed weights.  Self attention per head: scores = scale * (q . k)
+ * over ALL cached and new rows (src/graph.c:3532-3534), softmax_row_inplace over the first
+ * start + i + 1 of them (values *= 1 / total, src/graph.c:245-257), zeros behind, then the
+ * weighted sum over all rows in order (src/graph.c:3541).  Cross attention is the decode
+ * step's loop (src/graph.c:3593-3611).  out_last receives the output norm of the last row. */
+int orc_decoder_prefill(orc_stream *s, const float *rows, size_t count, float *out_last) {
+    const orc_model *m = s->m;
+    const size_t w = m->width, heads = m->heads, hw = m->head_width;
+    const size_t ffn = m->ffn_width, xw = m->xattn_width, start = s->length;
+    if (count == 0 || start + count > s->capacity) return -1;
+    const size_t total_kv = start + count;
+    const int packed = count <= 16u;
+    float *x = (float *)malloc(count * w * sizeof(float));
+    float *nrm = (float *)malloc(count * w * sizeof(float));
+    float *qkv = (float *)malloc(count * 3u * w * sizeof(float));
+    float *attn = (float *)malloc(count * w * sizeof(float));
+    float *proj = (float *)malloc(count * w * sizeof(float));
+    float *q_x = (float *)malloc(count * xw * sizeof(float));
+    float *xctx = (float *)malloc(count * xw * sizeof(float));
+    float *hidden = (float *)malloc(count * ffn * sizeof(float));
+    float *score = (float *)malloc((total_kv > s->memory_length ? total_kv : s->memory_length) * sizeof(float));
+    if (!x || !nrm || !qkv || !attn || !proj || !q_x || !xctx || !hidden || !score) {
+        free(x); free(nrm); free(qkv); free(attn); free(proj); free(q_x); free(xctx); free(hidden); free(score);
+        return -1;
+    }
+    const float self_scale = 1.0f / sqrtf((float)hw);
+    const float cross_scale = 1.0f / sqrtf((float)xw);
+    for (size_t i = 0; i < count; ++i) {
+        const float *pe = m->position + (start + i) * w;
+        for (size_t d = 0; d < w; ++d) x[i * w + d] = rows[i * w + d] + pe[d];
+    }
+/* rows through one weight: packed row by row, or the f32 product (src/backend.c:283-291) */
+#define ORC_LINEAR(W_, in_, iw_, out_, ow_)                                                     \
+    for (size_t i_ = 0; i_ < count; ++i_) {                                                     \
+        if (packed) orc_linear_row(&(W_), (in_) + i_ * (iw_), (out_) + i_ * (ow_), NULL);       \
+        else for (size_t r_ = 0; r_ < (ow_); ++r_)                                               \
+            (out_)[i_ * (ow_) + r_] = orc_dot_f32((W_).w + r_ * (iw_), (in_) + i_ * (iw_), (iw_)); \
+    }
+    for (size_t l = 0; l < s->layers_run; ++l) {
+        const orc_layer *L = &m->layer[l];
+        orc_layernorm(x, L->norm_self, NULL, nrm, count, w, 1.0e-5f);
+        ORC_LINEAR(L->qkv, nrm, w, qkv, 3u * w);
+        float *kbase = s->self_k + l * s->capacity * w;
+        float *vbase = s->self_v + l * s->capacity * w;
+        for (size_t i = 0; i < count; ++i) {
+            memcpy(kbase + (start + i) * w, qkv + i * 3u * w + w, w * sizeof(float));
+            memcpy(vbase + (start + i) * w, qkv + i * 3u * w + 2u * w, w * sizeof(float));
+        }
+        for (size_t h = 0; h < heads; ++h) {
+            for (size_t i = 0; i < count; ++i) {
+                const float *qh = qkv + i * 3u * w + h * hw;
+                const size_t valid = start + i + 1u;
+                /* one row of the score matrix: alpha * sum (+ 0 * c, which changes nothing) */
+                for (size_t sidx = 0; sidx < total_kv; ++sidx) {
+                    const float *k = kbase + sidx * w + h * hw;
+                    float sum = 0.0f;
+                    for (size_t d = 0; d < hw; ++d) sum += qh[d] * k[d];
+                    score[sidx] = self_scale * sum;
+                }
+                float maximum = -FLT_MAX;
+                for (size_t sidx = 0; sidx < valid; ++sidx)
+                    if (score[sidx] > maximum) maximum = score[sidx];
+                float total = 0.0f;
+                for (size_t sidx = 0; sidx < valid; ++sidx) {
+                    score[sidx] = expf(score[sidx] - maximum);
+                    total += score[sidx];
+                }
+                const float inverse = total > 0.0f ? 1.0f / total : 0.0f;
+                for (size_t sidx = 0; sidx < valid; ++sidx) score[sidx] *= inverse;
+                for (size_t sidx = valid; sidx < total_kv; ++sidx) score[sidx] = 0.0f;
+                for (size_t d = 0; d < hw; ++d) {
+                    float sum = 0.0f;
+                    for (size_t sidx = 0; sidx < total_kv; ++sidx) sum += score[sidx] * vbase[sidx * w + h * hw + d];
+                    attn[i * w + h * hw + d] = 1.0f * sum;
+                }
+            }
+        }
+        ORC_LINEAR(L->o_self, attn, w, proj, w);
+        for (size_t k = 0; k < count * w; ++k) x[k] += proj[k];
+        orc_layernorm(x, L->norm_xattn_query, NULL, nrm, count, w, 1.0e-5f);
+        ORC_LINEAR(L->q_cross, nrm, w, q_x, xw);
+        for (size_t i = 0; i < count; ++i)
+            orc_cross_attention(q_x + i * xw, s->cross_k + l * s->memory_length * xw,
+                                s->cross_v + l * s->memory_length * xw, s->memory_length, xw, 1u, xw,
+                                cross_scale, xctx + i * xw, score);
+        ORC_LINEAR(L->o_cross, xctx, xw, proj, w);
+        for (size_t k = 0; k < count * w; ++k) x[k] += proj[k];
+        orc_layernorm(x, L->norm_pos_ff, NULL, nrm, count, w, 1.0e-5f);
+        ORC_LINEAR(L->ffn_up, nrm, w, hidden, ffn);
+        orc_gelu_scalar(hidden, count * ffn);
+        ORC_LINEAR(L->ffn_down, hidden, ffn, proj, w);
+        for (size_t k = 0; k < count * w; ++k) x[k] += proj[k];
+    }
+#undef ORC_LINEAR
+    orc_layernorm(x + (count - 1u) * w, m->norm_out, NULL, out_last, 1u, w, 1.0e-5f);
+    s->length += count;
+    free(x); free(nrm); free(qkv); free(attn); free(proj); free(q_x); free(xctx); free(hidden); free(score);
+    return 0;
+}
+
 /* src/graph.c:760-804 with the table index flattened: the reference walks
  * stream = fs * codebooks + codebook over stacking * codebooks tables and
  * divides the sum by their count. */

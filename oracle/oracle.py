@@ -98,6 +98,7 @@ class Port:
         lib.orc_stream_set_length.argtypes = [C.c_void_p, sz]
         lib.orc_stream_set_layers.argtypes = [C.c_void_p, sz]
         lib.orc_decoder_step.argtypes = [C.c_void_p, c_float_p, c_float_p]
+        lib.orc_decoder_prefill.argtypes = [C.c_void_p, c_float_p, C.c_size_t, c_float_p]
         lib.orc_embed_frame.argtypes = [C.c_void_p, c_uint_p, c_float_p]
         lib.orc_heads_argmax.argtypes = [C.c_void_p, c_float_p, C.c_int, c_uint_p, c_float_p]
         lib.orc_greedy_frame.argtypes = [C.c_void_p, c_uint_p, C.c_int, c_uint_p, c_float_p]
@@ -370,6 +371,13 @@ class PortStream:
     def step(self, row: np.ndarray) -> np.ndarray:
         out = np.empty_like(row)
         assert self.lib.orc_decoder_step(self.handle, _fp(row), _fp(out)) == 0
+        return out
+
+    def prefill(self, rows: np.ndarray) -> np.ndarray:
+        """decoder_run with count > 1 (src/graph.c:3506-3641): rows [count, width] at once."""
+        rows = np.ascontiguousarray(rows, np.float32)
+        out = np.empty((rows.shape[1],), np.float32)
+        assert self.lib.orc_decoder_prefill(self.handle, _fp(rows), rows.shape[0], _fp(out)) == 0
         return out
 
     def greedy_frame(self, codes: np.ndarray, allow_eos: bool):

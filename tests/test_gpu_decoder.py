@@ -595,6 +595,66 @@ def test_f16_weights_on_the_tensor_cores_match_oracle(shape_name, lanes, tiny_mo
     assert got[(False, "launches")] > got[(True, "launches")]
 
 
+@pytest.mark.parametrize("shape_name,name,count,strict", [
+    ("tiny", "int8", 20, True), ("tiny", "int8", 9, True), ("tiny", "f32", 20, True), ("tiny", "int4", 17, True),
+    ("tiny", "int8", 16, True), ("tiny", "int8", 20, False), ("tiny", "f16", 20, False), ("full", "int8", 24, True)])
+def test_multi_row_prefill_matches_decoder_run(shape_name, name, count, strict, tiny_model, tiny_memory):
+    """decoder_run with count > 1 (src/graph.c:3506-3641): a few rows stepped one by one, then
+    `count` rows pushed at once, then a step on top, against the CPU restatement (itself equal
+    to the reference's decoder_run bit for bit, tests/test_oracle.py).  More than 16 rows of a
+    quantized model take the f32 weights, as in the reference.  Strict mode: hidden rows and
+    the appended KV rows bit for bit for the integer and f32-weight paths."""
+    if shape_name == "tiny":
+        shape, model, memory = synth.TINY, tiny_model, tiny_memory
+    else:
+        shape = synth.MAGPIE_357M
+        model = synth.make_model(shape, seed=71)
+        memory = synth.make_memory(shape, seed=171)
+    capacity = 48
+    rng = np.random.default_rng(37)
+    first = rng.normal(0, 0.05, size=(3, shape.width)).astype(np.float32)
+    rows = rng.normal(0, 0.05, size=(count, shape.width)).astype(np.float32)
+    after = rng.normal(0, 0.05, size=(shape.width,)).astype(np.float32)
+    pm = O.PortModel(model, QT[name])
+    ps = pm.new_stream(memory, capacity)
+    be = Backend(name, strict=strict)
+    dec = Decoder(be, model, capacity=capacity, slots=2, max_batch=max(count, 2), keep_f32_weights=True)
+    dec.slot_load(1, ps.cross_k, ps.cross_v)
+    # strict: exact wherever every sum is an integer or a reference-order chain (f32 products
+    # of more than 16 rows are sequential sums in strict mode)
+    exact = strict and (name in ("int8", "int4") or (name == "f32"))
+    tol = STRICT_TOL if strict else FAST_TOL[name]
+    for r in first:
+        want, got = ps.step(r), dec.step_batch([1], r[None, :])[0]
+        assert rel_err(got, want) < tol
+    want, got = ps.prefill(rows), dec.prefill(1, rows)
+    assert rel_err(got, want) < tol, (name, count, strict)
+    if exact:
+        assert np.array_equal(got, want), (name, count)
+    assert dec.slot_length(1) == 3 + count
+    k, v = dec.slot_read_kv(1)
+    n = 3 + count
+    assert rel_err(k[:, :n], ps.self_k[:, :n]) < tol and rel_err(v[:, :n], ps.self_v[:, :n]) < tol
+    if exact:
+        assert np.array_equal(k[:, :n], ps.self_k[:, :n]) and np.array_equal(v[:, :n], ps.self_v[:, :n])
+    assert not k[:, n:].any()
+    want, got = ps.step(after), dec.step_batch([1], after[None, :])[0]
+    assert rel_err(got, want) < tol
+    if exact:
+        assert np.array_equal(got, want)
+    with pytest.raises(MynahB200Error, match="capacity"):
+        dec.prefill(1, np.zeros((capacity, shape.width), np.float32))
+    dec.close(); be.close(); ps.close(); pm.close()
+
+
+def test_prefill_of_a_quantized_model_needs_its_f32_weights(tiny_model, tiny_memory):
+    be = Backend("int8", strict=True)
+    dec = Decoder(be, tiny_model, capacity=48, slots=1, max_batch=20)
+    with pytest.raises(MynahB200Error, match="f32 weights"):
+        dec.prefill(0, np.zeros((20, synth.TINY.width), np.float32))
+    dec.close(); be.close()
+
+
 @pytest.mark.parametrize("strict", [True, False])
 def test_slot_prefill_makes_the_reference_cross_kv(strict, tiny_model, tiny_memory, golden):
     """Cross K/V made on the device from the text memory (decoder_cache_init,

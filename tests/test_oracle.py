@@ -255,3 +255,31 @@ def test_fast_reference_build_is_close_to_strict(tiny_model, tiny_memory):
     row = pm.embed_frame(synth.make_codes(shape, seed=2, frames=1)[0])
     assert rel_err(df.step(row), ds.step(row)) < 1e-5
     df.close(); ds.close(); fast.close(); strict.close(); pm.close()
+
+
+@pytest.mark.parametrize("qtype,count", [(O.INT8, 20), (O.INT8, 9), (O.F32, 20), (O.INT4, 17)])
+def test_port_prefill_equals_reference_decoder_run(qtype, count, tiny_model, tiny_memory):
+    """The restated multi-row prefill (decoder_run with count > 1, src/graph.c:3506-3641)
+    against the reference's own, bit for bit: hidden row of the last new row, the KV rows it
+    appended, and a decode step on top; more than 16 rows take the f32 weights in both."""
+    if not O.have_ref("strict"):
+        pytest.skip("compiled reference absent")
+    from mynah_tts_b200 import synth
+    shape = synth.TINY
+    rng = np.random.default_rng(31)
+    first = rng.normal(0, 0.05, size=(3, shape.width)).astype(np.float32)
+    rows = rng.normal(0, 0.05, size=(count, shape.width)).astype(np.float32)
+    after = rng.normal(0, 0.05, size=(shape.width,)).astype(np.float32)
+    rm = O.RefModel(tiny_model, qtype, "strict")
+    rd = rm.new_decoder(tiny_memory, 40)
+    pm = O.PortModel(tiny_model, qtype)
+    ps = pm.new_stream(tiny_memory, 40)
+    for r in first:                                   # a few cached rows first
+        assert np.array_equal(ps.step(r), rd.step(r))
+    want, got = rd.run(rows), ps.prefill(rows)
+    assert np.array_equal(got, want)
+    assert rd.length == ps.length == 3 + count
+    assert np.array_equal(ps.self_k[:, :3 + count], rd.self_k[:, :3 + count])
+    assert np.array_equal(ps.self_v[:, :3 + count], rd.self_v[:, :3 + count])
+    assert np.array_equal(ps.step(after), rd.step(after))
+    rd.close(); rm.close(); ps.close(); pm.close()
