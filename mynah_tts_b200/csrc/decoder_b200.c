@@ -723,8 +723,11 @@ static int enqueue(mb_decoder *d, size_t bucket, int mode, unsigned *count) {
         a.scale = self_scale;
         a.out = d->attn;
         a.out_stride = W;
-        a.qx = q ? d->qx : NULL;
-        a.sx = q ? d->sx : NULL;
+        /* one lane: the output product quantizes the row in its own prologue, which spares the
+         * attention's head groups their arrival counter and the gathering tail */
+        const int o_fused = f1 && L->o_self.qtype == MB_INT8;
+        a.qx = (q && !o_fused) ? d->qx : NULL;
+        a.sx = (q && !o_fused) ? d->sx : NULL;
         a.batch = nb;
         a.n_active = d->d_n_active;
         a.strict = st->strict;
@@ -736,7 +739,11 @@ static int enqueue(mb_decoder *d, size_t bucket, int mode, unsigned *count) {
         a.early_prefetch = 1;   /* lane state: previous step; cache rows below the position: earlier steps */
         a.launched = count;
         P(PC_ATTN_SELF, mb_attention(&a, s));
-        P(PC_O_SELF, product(d, &L->o_self, NULL, d->attn, d->x, W, nb, MB_EPI_RESIDUAL, count));
+        if (o_fused) {
+            P(PC_O_SELF, product_fused(d, &L->o_self, NULL, d->attn, d->x, W, nb, MB_EPI_RESIDUAL, MB_FUSE_QUANT, NULL, count));
+        } else {
+            P(PC_O_SELF, product(d, &L->o_self, NULL, d->attn, d->x, W, nb, MB_EPI_RESIDUAL, count));
+        }
         /* int8: the whole cross-attention block, with the norm before the feed-forward
          * product, is one launch with one CTA per stream */
         const int xb = d->use_xblock && q && L->q_cross.qtype == MB_INT8 &&

@@ -434,10 +434,101 @@ int launch_tiled(const GemvP &p, size_t groups, cudaStream_t s) {
     return mb_check_launch();
 }
 
+// Strict f32 product at streaming speed: out[b][r] = ((w[r][0]*x[b][0] + w[r][1]*x[b][1]) + ...)
+// with every product and sum rounded, in index order -- the reference's scalar build
+// (src/backend.c:283-291, src/kernels.c:40-44).  The order binds each output's own sum, not
+// how the weights reach the threads: a CTA owns 32 weight rows and up to 4 lanes; the rows'
+// next 64 floats are fetched by all 128 threads with coalesced 16-byte loads into registers
+// while the chains run over the current 64 (shared memory, row pitch 65 so that the 32 rows
+// a warp reads fall into 32 banks), sixteen values staged in registers ahead of their adds.
+constexpr int SEQ_ROWS = 32, SEQ_LANES = 4, SEQ_KC = 64, SEQ_PITCH = SEQ_KC + 1;
+__global__ void __launch_bounds__(SEQ_ROWS * SEQ_LANES) k_gemv_f32_seq(GemvP p) {
+    __shared__ float ws[SEQ_ROWS * SEQ_PITCH];
+    __shared__ __align__(16) float xs[SEQ_LANES * SEQ_KC];
+    const int nb = min(p.batch, mb_lane_count(p.n_active));
+    mb_pdl_wait();
+    mb_pdl_trigger();
+    const int b0 = blockIdx.y * SEQ_LANES;
+    if (b0 >= nb) return;
+    const long r0 = (long)blockIdx.x * SEQ_ROWS;
+    const int tid = threadIdx.x, r = tid % SEQ_ROWS, lb = tid / SEQ_ROWS;
+    const long k = p.k;
+    const float *w = reinterpret_cast<const float *>(p.w);
+    const int nchunks = (int)((k + SEQ_KC - 1) / SEQ_KC);
+    // this thread's share of a weight chunk: 32 rows x 16 pieces of 16 bytes = 512 pieces, 4 each
+    float4 wreg[4], xreg;
+    auto fetch = [&](int c) {
+        const long k0 = (long)c * SEQ_KC;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = tid + u * SEQ_ROWS * SEQ_LANES, rr = i >> 4, pc = i & 15;
+            const long row = r0 + rr, col = k0 + 4 * pc;
+            wreg[u] = (row < p.n && col < k) ? __ldg(reinterpret_cast<const float4 *>(w + row * k + col))
+                                             : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        // activations of the CTA's lanes: 4 lanes x 16 pieces = 64 pieces, threads 0..63
+        xreg = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (tid < SEQ_LANES * 16) {
+            const int l = tid >> 4, pc = tid & 15;
+            const long col = k0 + 4 * pc;
+            if (b0 + l < nb && col < k) xreg = *reinterpret_cast<const float4 *>(p.x + (long)(b0 + l) * k + col);
+        }
+    };
+    auto stash = [&]() {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = tid + u * SEQ_ROWS * SEQ_LANES, rr = i >> 4, pc = i & 15;
+            float *dst = ws + rr * SEQ_PITCH + 4 * pc;
+            dst[0] = wreg[u].x; dst[1] = wreg[u].y; dst[2] = wreg[u].z; dst[3] = wreg[u].w;
+        }
+        if (tid < SEQ_LANES * 16) *reinterpret_cast<float4 *>(xs + 4 * tid) = xreg;
+    };
+    fetch(0);
+    stash();
+    __syncthreads();
+    float a = 0.0f;
+    const bool mine = r0 + r < p.n && b0 + lb < nb;
+    for (int c = 0; c < nchunks; ++c) {
+        if (c + 1 < nchunks) fetch(c + 1);              // in flight while the chains run
+        const int len = (int)min((long)SEQ_KC, k - (long)c * SEQ_KC);
+        if (mine) {
+            const float *wr = ws + r * SEQ_PITCH;
+            const float *xr = xs + lb * SEQ_KC;
+            for (int j0 = 0; j0 < len; j0 += 16) {
+                float wv[16], xv[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) wv[j] = wr[j0 + j];
+#pragma unroll
+                for (int j4 = 0; j4 < 4; ++j4) {
+                    const float4 t = *reinterpret_cast<const float4 *>(xr + j0 + 4 * j4);
+                    xv[4 * j4] = t.x; xv[4 * j4 + 1] = t.y; xv[4 * j4 + 2] = t.z; xv[4 * j4 + 3] = t.w;
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    if (j0 + j < len) a = __fadd_rn(a, __fmul_rn(wv[j], xv[j]));
+            }
+        }
+        __syncthreads();
+        if (c + 1 < nchunks) {
+            stash();
+            __syncthreads();
+        }
+    }
+    if (!mine) return;
+    if (p.bias != nullptr) a = __fadd_rn(a, p.bias[r0 + r]);
+    store_out<true>(p, p.out, r0 + r, b0 + lb, a);
+}
+
 template <int QT, bool STRICT>
 int launch_qt(const GemvP &p, size_t groups, bool tiled, cudaStream_t s) {
     // Strict f32: the reference's scalar build sums a row's products one after another
     // (src/kernels.c:40-44); only the one-thread-per-output kernel keeps that order.
+    if (STRICT && QT == MB_F32 && groups == 1 && (p.k % 4) == 0 &&
+        ((reinterpret_cast<uintptr_t>(p.w) | reinterpret_cast<uintptr_t>(p.x)) & 15u) == 0) {
+        const dim3 grid((unsigned)((p.n + SEQ_ROWS - 1) / SEQ_ROWS), (unsigned)((p.batch + SEQ_LANES - 1) / SEQ_LANES));
+        mb_launch(k_gemv_f32_seq, grid, dim3(SEQ_ROWS * SEQ_LANES), 0, s, p);
+        return mb_check_launch();
+    }
     if (!tiled || (STRICT && QT == MB_F32 && groups == 1)) {
         if (groups != 1) return (int)cudaErrorInvalidValue;
         const long total = p.n * p.batch;
