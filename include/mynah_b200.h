@@ -399,6 +399,40 @@ typedef struct {
 int mynah_b200_decoder_serve(void *decoder, mynah_b200_request *requests, size_t count,
                              size_t *steps, char *error, size_t cap);
 
+/* ---- text encoder (src/graph.c:709-748) -------------------------------------------
+ * encode_text: token ids -> the text-encoder states the decoder cross-attends (the
+ * `memory` of _slot_prefill and of mynah_b200_request).  Host weight pointers of one
+ * layer, names as the reference resolves them (src/graph.c:662-699, 291-296, 386-391): */
+typedef struct {
+    const float *norm_self;    /* encoder.layers.N.norm_self.weight [width] */
+    const float *norm_pos_ff;  /* ...norm_pos_ff.weight [width] */
+    const float *qkv_w;        /* ...self_attention.qkv_net.weight [3*width, width] */
+    const float *o_w;          /* ...self_attention.o_net.weight [width, width] */
+    const float *ffn_proj_w;   /* ...pos_ff.proj.conv.weight [4*width, width, kernel] */
+    const float *ffn_out_w;    /* ...pos_ff.o_net.conv.weight [width, 4*width, kernel] */
+} mynah_b200_encoder_layer_weights;
+
+typedef struct {
+    size_t layers, width, heads, kernel;   /* the reference runs 12 heads and kernel 3 (src/graph.c:735) */
+    size_t vocab;              /* rows of text_embedding.weight */
+    size_t max_length;         /* text_max_length: rows of encoder.position_embeddings.weight, <= 1024 */
+    const mynah_b200_encoder_layer_weights *layer;   /* [layers] */
+    const float *embedding;    /* text_embedding.weight [vocab, width] */
+    const float *position;     /* encoder.position_embeddings.weight [max_length, width] */
+    const float *norm_out;     /* encoder.norm_out.weight [width] */
+} mynah_b200_encoder_desc;
+
+/* Uploads the weights (kept in f32 whatever the backend's format: the reference's encoder
+ * never takes the quantized path).  Host pointers need only be valid during the call. */
+int mynah_b200_encoder_create(void *state, const mynah_b200_encoder_desc *desc, void **encoder,
+                              char *error, size_t cap);
+void mynah_b200_encoder_destroy(void *encoder);
+/* ids [count] (HOST) -> out [count][width] (HOST): the contract of encode_text; ids outside
+ * the vocabulary and count outside 1..max_length are refused with the reference's messages.
+ * Synchronous. */
+int mynah_b200_encoder_encode(void *encoder, const int *ids, size_t count, float *out, char *error,
+                              size_t cap);
+
 /* Bytes of weights one step reads, and of KV one slot at `length` reads. */
 size_t mynah_b200_decoder_weight_bytes(const void *decoder);
 size_t mynah_b200_decoder_kv_bytes(const void *decoder, size_t length);

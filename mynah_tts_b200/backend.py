@@ -223,6 +223,44 @@ class MatrixPool:
             self.handle = None
 
 
+class TextEncoder:
+    """encode_text over the reference-named tensors of synth.add_encoder (or a real pack)."""
+
+    def __init__(self, backend: Backend, tensors: dict, shape):
+        self.backend, self.shape = backend, shape
+        self._keep = [np.ascontiguousarray(v, np.float32) for v in tensors.values()]
+        t = {k: self._keep[i] for i, k in enumerate(tensors)}
+        layers = (capi.EncoderLayerWeights * shape.layers)()
+        for i in range(shape.layers):
+            pre = f"encoder.layers.{i}."
+            layers[i].norm_self = fp(t[pre + "norm_self.weight"])
+            layers[i].norm_pos_ff = fp(t[pre + "norm_pos_ff.weight"])
+            layers[i].qkv_w = fp(t[pre + "self_attention.qkv_net.weight"])
+            layers[i].o_w = fp(t[pre + "self_attention.o_net.weight"])
+            layers[i].ffn_proj_w = fp(t[pre + "pos_ff.proj.conv.weight"])
+            layers[i].ffn_out_w = fp(t[pre + "pos_ff.o_net.conv.weight"])
+        desc = capi.EncoderDesc()
+        desc.layers, desc.width, desc.heads, desc.kernel = shape.layers, shape.width, shape.heads, shape.kernel
+        desc.vocab, desc.max_length = shape.vocab, shape.max_length
+        desc.layer = layers
+        desc.embedding = fp(t["text_embedding.weight"])
+        desc.position = fp(t["encoder.position_embeddings.weight"])
+        desc.norm_out = fp(t["encoder.norm_out.weight"])
+        self.handle = C.c_void_p()
+        call(capi.lib().mynah_b200_encoder_create, backend.state, C.byref(desc), C.byref(self.handle))
+
+    def encode(self, ids) -> np.ndarray:
+        ids = np.ascontiguousarray(ids, np.int32)
+        out = np.empty((len(ids), self.shape.width), np.float32)
+        call(capi.lib().mynah_b200_encoder_encode, self.handle, ids.ctypes.data_as(capi.c_int_p), len(ids), fp(out))
+        return out
+
+    def close(self):
+        if self.handle:
+            capi.lib().mynah_b200_encoder_destroy(self.handle)
+            self.handle = None
+
+
 class Decoder:
     """The whole-step decoder over a synth.SynthModel (or any object with the
     same accessors)."""

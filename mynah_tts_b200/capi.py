@@ -67,6 +67,16 @@ class LocalDesc(C.Structure):
                 ("position_rows", sz), ("codebooks", sz)]
 
 
+class EncoderLayerWeights(C.Structure):
+    _fields_ = [(n, c_float_p) for n in ("norm_self", "norm_pos_ff", "qkv_w", "o_w", "ffn_proj_w", "ffn_out_w")]
+
+
+class EncoderDesc(C.Structure):
+    _fields_ = [("layers", sz), ("width", sz), ("heads", sz), ("kernel", sz), ("vocab", sz), ("max_length", sz),
+                ("layer", C.POINTER(EncoderLayerWeights)), ("embedding", c_float_p), ("position", c_float_p),
+                ("norm_out", c_float_p)]
+
+
 class Sampler(C.Structure):
     _fields_ = [("temperature", C.c_float), ("topk", C.c_uint), ("rng_state", C.c_ulonglong),
                 ("allow_eos", C.c_int)]
@@ -152,6 +162,9 @@ SIGNATURES = {
     "mynah_b200_decoder_slot_load": (C.c_int, [C.c_void_p, sz, c_float_p, c_float_p, sz, c_float_p, c_float_p, sz, _E]),
     "mynah_b200_decoder_slot_prefill": (C.c_int, [C.c_void_p, sz, c_float_p, sz, _E]),
     "mynah_b200_decoder_prefill": (C.c_int, [C.c_void_p, sz, c_float_p, sz, c_float_p, _E]),
+    "mynah_b200_encoder_create": (C.c_int, [C.c_void_p, C.POINTER(EncoderDesc), C.POINTER(C.c_void_p), _E]),
+    "mynah_b200_encoder_destroy": (None, [C.c_void_p]),
+    "mynah_b200_encoder_encode": (C.c_int, [C.c_void_p, c_int_p, sz, c_float_p, _E]),
     "mynah_b200_decoder_slot_read_cross": (C.c_int, [C.c_void_p, sz, c_float_p, c_float_p, _E]),
     "mynah_b200_decoder_slot_length": (C.c_int, [C.c_void_p, sz, C.POINTER(sz), _E]),
     "mynah_b200_decoder_slot_set_length": (C.c_int, [C.c_void_p, sz, sz, _E]),

@@ -69,6 +69,23 @@ __device__ __forceinline__ int dot16(const uint4 &a, const uint4 &b, int acc) {
 // context as sequential chains, as k_attn_exact forms them) and the host libm's expf; the
 // K/V tiles then arrive as 128-byte-swizzled [32][32] boxes so that a warp whose threads
 // each walk one row reads 32 different banks.  Same bits as the separate strict launches.
+// Phase timestamps of profiling builds (make TICKS=1): see attn_exact.cuh.  0 entry, 1 after
+// the dependency wait, 2 row loaded, 3 first norm, 4 query product, 5 attention, 6 context
+// quantized, 7 output product, 8 second norm.
+#ifdef MB_PHASE_TICKS
+__device__ unsigned long long g_xb_ticks[16 * 1024];
+__device__ __forceinline__ void xb_tick(int i) {
+    if (threadIdx.x == 0 && blockIdx.x < 1024u) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        g_xb_ticks[blockIdx.x * 16 + i] = t;
+    }
+}
+#define XB_TICK(i) xb_tick(i)
+#else
+#define XB_TICK(i)
+#endif
+
 template <int RO, int LPR, bool STRICT>
 __global__ void __launch_bounds__(XB_THREADS, 1)
 k_cross_block(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, CrossP p) {
@@ -77,6 +94,7 @@ k_cross_block(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
     __shared__ float stat[2];
     __shared__ __align__(8) unsigned long long mbar[2 * XB_MAX_CHUNKS];   // K chunks, then V chunks
     __shared__ unsigned s_bad;
+    XB_TICK(0);
     const int b = blockIdx.x;
     // lane state was written by the previous step's last launch: readable before the wait
     const int live = p.n_active != nullptr ? *p.n_active : 0x7fffffff;
@@ -146,6 +164,7 @@ k_cross_block(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
     }
     mb_pdl_wait();
     mb_pdl_trigger();
+    XB_TICK(1);
 
     // ---- first norm, quantized into shared memory
     float *xg = p.x + (long)b * W;
@@ -155,10 +174,12 @@ k_cross_block(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
         row[i] = v;
     }
     __syncthreads();
+    XB_TICK(2);
     const float sxq = STRICT ? mb_ln_block_strict(row, W, gq, nullptr, p.eps, sq, stat, red, nullptr, true, qrow)
                              : mb_ln_block<1>(row, W, gq, nullptr, p.eps, red, nullptr, true, qrow);
     __syncthreads();
 
+    XB_TICK(3);
     // ---- query product: two threads per output row, pieces of the row interleaved
     {
         int a0 = 0, a1 = 0, a2 = 0, a3 = 0;           // four chains instead of one of 4 * PQ steps
@@ -208,6 +229,7 @@ k_cross_block(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
     }
     __syncthreads();
 
+    XB_TICK(4);
     float ctx = 0.0f;
     // ---- attention over the text states: warp c makes the partial of chunk c
     const int tpp = XW / 4, rps = 32 / tpp, sub = lane / tpp, li = lane % tpp;
@@ -337,6 +359,7 @@ k_cross_block(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
     }
     // merge of the chunk partials, a thread per dimension, and the int8 quantization of the
     // merged row (one warp doing both in turn was a 4 us chain of dependent instructions)
+    XB_TICK(5);
     if (!STRICT && threadIdx.x < XW) ctx = merge_dim(P, ns, XW, threadIdx.x);
     const float cmax = block_max1(fabsf(ctx), red);
     const float cinv = cmax > 0.0f ? __fdiv_rn(127.0f, cmax) : 0.0f;
@@ -344,6 +367,7 @@ k_cross_block(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
     const float sxc = cmax > 0.0f ? __fdiv_rn(cmax, 127.0f) : 0.0f;
     __syncthreads();
 
+    XB_TICK(6);
     // ---- output product added to the residual row
     {
         const uint4 creg = reinterpret_cast<const uint4 *>(ctxq)[lp];
@@ -379,10 +403,12 @@ k_cross_block(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
     }
     __syncthreads();
 
+    XB_TICK(7);
     // ---- second norm, quantized for the feed-forward product
     const float sx2 = STRICT ? mb_ln_block_strict(row, W, gf, nullptr, p.eps, sq, stat, red, nullptr, true, p.qx + (long)b * W)
                              : mb_ln_block<1>(row, W, gf, nullptr, p.eps, red, nullptr, true, p.qx + (long)b * W);
     if (threadIdx.x == 0) p.sx[b] = sx2;
+    XB_TICK(8);
 }
 
 size_t cross_block_smem(size_t width, size_t xw, size_t chunks) {
@@ -447,6 +473,15 @@ extern "C" int mb_cross_block(const mb_cross_block_args *a, mb_stream stream) {
 #undef XB_CASE
     return mb_check_launch();
 }
+
+#ifdef MB_PHASE_TICKS
+extern "C" __attribute__((visibility("default")))
+int mynah_b200_debug_cross_block_ticks(unsigned long long *host, size_t n) {
+    if (n > 16u * 1024u) n = 16u * 1024u;
+    cudaDeviceSynchronize();
+    return (int)cudaMemcpyFromSymbol(host, g_xb_ticks, n * sizeof(unsigned long long));
+}
+#endif
 
 extern "C" int mb_cross_block_init(void) {
     int rc = 0;

@@ -540,6 +540,34 @@ k_local_sample(const float *__restrict__ logits, int ld, int vocab, int n2, int 
     }
 }
 
+// out[t] = table[ids[t]] + position[t]   (encode_text, src/graph.c:728-733 and 651-653)
+__global__ void __launch_bounds__(256)
+k_gather_rows(const float *__restrict__ table, const int *__restrict__ ids, const float *__restrict__ position,
+              float *__restrict__ out, int width) {
+    mb_pdl_wait();
+    mb_pdl_trigger();
+    const int t = blockIdx.x;
+    const float *row = table + (size_t)ids[t] * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x)
+        out[(size_t)t * width + i] = __fadd_rn(row[i], position[(size_t)t * width + i]);
+}
+
+// Causal unfold of `length` rows over a convolution window (unfold_causal,
+// src/graph.c:267-286): col[t][i * kernel + k] = in[t - (kernel - 1) + k][i], zero before
+// the first row.
+__global__ void __launch_bounds__(256)
+k_unfold_causal(const float *__restrict__ in, float *__restrict__ col, int channels, int kernel) {
+    mb_pdl_wait();
+    mb_pdl_trigger();
+    const int t = blockIdx.x;
+    const int total = channels * kernel;
+    for (int j = threadIdx.x; j < total; j += blockDim.x) {
+        const int i = j / kernel, k = j - i * kernel;
+        const int src = t - (kernel - 1) + k;
+        col[(size_t)t * total + j] = src < 0 ? 0.0f : in[(size_t)src * channels + i];
+    }
+}
+
 __global__ void k_advance_lens(int *lens, int batch, const int *n_active) {
     mb_pdl_wait();
     mb_pdl_trigger();
@@ -704,6 +732,19 @@ extern "C" int mb_local_sample(const mb_sample_args *a, mb_stream stream) {
                   a->rng, (int)a->table, (int)a->tables, (int)a->codebooks, a->tokens, a->codes, a->eos_flag,
                   a->eos_sub, a->emb_table, a->row_in, a->next_row, a->next_row == nullptr ? nullptr : a->x_out, (int)a->width,
                   a->exp_tab, a->n_active);
+    return mb_check_launch();
+}
+
+extern "C" int mb_gather_rows(const float *table, const int *ids, const float *position, float *out, size_t rows,
+                              size_t width, mb_stream stream) {
+    if (rows == 0 || width == 0) return (int)cudaErrorInvalidValue;
+    mb_launch(k_gather_rows, dim3((unsigned)rows), dim3(256), 0, (cudaStream_t)stream, table, ids, position, out, (int)width);
+    return mb_check_launch();
+}
+
+extern "C" int mb_unfold_causal(const float *in, float *col, size_t rows, size_t channels, size_t kernel, mb_stream stream) {
+    if (rows == 0 || channels == 0 || kernel == 0) return (int)cudaErrorInvalidValue;
+    mb_launch(k_unfold_causal, dim3((unsigned)rows), dim3(256), 0, (cudaStream_t)stream, in, col, (int)channels, (int)kernel);
     return mb_check_launch();
 }
 

@@ -109,6 +109,11 @@ typedef struct {
 int mb_local_sample(const mb_sample_args *args, mb_stream stream);
 size_t mb_local_sample_smem(size_t vocab);
 
+/* out[t] = table[ids[t]] + position[t] for `rows` rows of `width` (ids checked by the caller). */
+int mb_gather_rows(const float *table, const int *ids, const float *position, float *out, size_t rows,
+                   size_t width, mb_stream stream);
+/* col[t][i * kernel + k] = in[t - (kernel - 1) + k][i], zero before the first row. */
+int mb_unfold_causal(const float *in, float *col, size_t rows, size_t channels, size_t kernel, mb_stream stream);
 int mb_advance_lens(int *lens, size_t batch, const int *n_active, mb_stream stream);
 /* End of one greedy frame for lanes below n_active: lens[b] += 1; append
  * tokens_cur[b][:] to history[*frame_idx][b][:] (rows of lane_stride lanes); record the first frame whose

@@ -167,6 +167,53 @@ def make_model(shape: DecoderShape = MAGPIE_357M, seed: int = 0) -> SynthModel:
     return SynthModel(shape=shape, seed=seed, tensors=t)
 
 
+@dataclass(frozen=True)
+class EncoderShape:
+    """The text encoder (src/graph.c:709-748: `transformer_stack` over the "encoder" tensors):
+    12 heads, FFN 4 x width with a causal convolution of kernel 3, no cross attention."""
+    layers: int = 6
+    width: int = 768
+    heads: int = 12            # fixed in the reference (src/graph.c:735)
+    kernel: int = 3            # fixed in the reference (src/graph.c:735)
+    vocab: int = 96            # rows of text_embedding.weight (synthetic)
+    max_length: int = 256      # rows of encoder.position_embeddings.weight / text_max_length
+
+    @property
+    def ffn_width(self) -> int:
+        return 4 * self.width
+
+
+TINY_ENCODER = EncoderShape(layers=2, width=192, vocab=40, max_length=48)
+
+
+def add_encoder(model: "SynthModel | None", shape: EncoderShape, seed: int) -> dict[str, np.ndarray]:
+    """Draws the text encoder's tensors (reference names) and returns them; with a model they
+    also go into `model.tensors`, and the width must be the decoder's (the reference shares
+    `hidden_dim`)."""
+    assert model is None or shape.width == model.shape.width
+    rng = np.random.default_rng([seed, 0x656E63])
+    t: dict[str, np.ndarray] = {}
+
+    def normal(mean, std, dims):
+        return np.ascontiguousarray(rng.normal(mean, std, size=dims).astype(np.float32))
+
+    W, F, K = shape.width, shape.ffn_width, shape.kernel
+    t["text_embedding.weight"] = normal(0.0, 0.02, (shape.vocab, W))
+    t["encoder.position_embeddings.weight"] = normal(0.0, 0.02, (shape.max_length, W))
+    t["encoder.norm_out.weight"] = normal(1.0, 0.01, (W,))
+    for layer in range(shape.layers):
+        pre = f"encoder.layers.{layer}."
+        t[pre + "norm_self.weight"] = normal(1.0, 0.01, (W,))
+        t[pre + "norm_pos_ff.weight"] = normal(1.0, 0.01, (W,))
+        t[pre + "self_attention.qkv_net.weight"] = normal(0.0, 0.02, (3 * W, W))
+        t[pre + "self_attention.o_net.weight"] = normal(0.0, 0.02, (W, W))
+        t[pre + "pos_ff.proj.conv.weight"] = normal(0.0, 0.02, (F, W, K))
+        t[pre + "pos_ff.o_net.conv.weight"] = normal(0.0, 0.02, (W, F, K))
+    if model is not None:
+        model.tensors.update(t)
+    return t
+
+
 def make_memory(shape: DecoderShape, seed: int) -> np.ndarray:
     """Text-encoder output for one request: [memory_length, width] ~ N(0,1)."""
     rng = np.random.default_rng([seed, 0x6D656D])

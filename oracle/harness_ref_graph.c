@@ -246,6 +246,21 @@ REF_EXPORT int ref_greedy_decode(ref_model *r, ref_decoder **decoders, size_t ba
     return rc;
 }
 
+/* encode_text (src/graph.c:709-748) on the model's "encoder" tensors; encoder_layers and
+ * text_max_length stand for the manifest fields of src/mynah_tts.c:228-233.  out is
+ * [count][hidden_dim]. */
+REF_EXPORT int ref_encode_text(ref_model *r, unsigned encoder_layers, unsigned text_max_length,
+                               const int *ids, size_t count, float *out, char *error, size_t cap) {
+    r->model.info.encoder_layers = encoder_layers;
+    r->model.info.text_max_length = text_max_length;
+    float *encoded = NULL;
+    if (cap > 0) error[0] = '\0';
+    if (encode_text(&r->model, ids, count, &encoded, error, cap) != 0) return -1;
+    memcpy(out, encoded, count * r->model.info.hidden_dim * sizeof(float));
+    free(encoded);
+    return 0;
+}
+
 /* ------------------------------------------------------ local transformer */
 typedef struct {
     local_frame_state state;

@@ -752,6 +752,103 @@ int orc_decoder_prefill(orc_stream *s, const float *rows, size_t count, float *o
     return 0;
 }
 
+/* ------------------------------------------------------------ text encoder */
+/* encode_text (src/graph.c:709-748): token embedding rows, then transformer_stack over the
+ * "encoder" tensors (src/graph.c:634-707) with 12 heads, no cross attention, the output norm
+ * applied -- in the reference's scalar build: every `linear` is the f32 product of
+ * src/backend.c:283-291 (never quantized: `linear` bypasses qmat, src/graph.c:259-265); the
+ * self attention is causal, per head scores = (1/sqrt(hw)) * (q . k) for ALL pairs
+ * (src/graph.c:442-444), softmax_row_inplace over the first t + 1 (values *= 1 / total),
+ * zeros behind, weighted sum over all rows in order (src/graph.c:450); the feed-forward is
+ * the causal convolution of kernel K as ONE product over the unfolded input
+ * (unfold_causal, src/graph.c:267-286: col[t][i * K + k] = in[t - (K - 1) + k][i], zero
+ * before the start), the scalar tanh GELU, and the same for the output convolution
+ * (src/graph.c:333-350).  Per-layer weights are passed as pointer arrays of `layers`
+ * entries: norm_self [W], qkv [3W][W], o [W][W], norm_ff [W], proj [F][W*K], out [W][F*K]. */
+int orc_encode_text(const int *ids, size_t count, size_t layers, size_t width, size_t heads,
+                    size_t kernel, size_t vocab, const float *embedding, const float *position,
+                    const float *norm_out, const float *const *norm_self, const float *const *qkv_w,
+                    const float *const *o_w, const float *const *norm_ff, const float *const *proj_w,
+                    const float *const *out_w, float *out) {
+    const size_t w = width, ffn = 4u * width, hw = width / heads;
+    float *x = (float *)malloc(count * w * sizeof(float));
+    float *nrm = (float *)malloc(count * w * sizeof(float));
+    float *qkv = (float *)malloc(count * 3u * w * sizeof(float));
+    float *ctx = (float *)malloc(count * w * sizeof(float));
+    float *res = (float *)malloc(count * w * sizeof(float));
+    float *hidden = (float *)malloc(count * ffn * sizeof(float));
+    float *col = (float *)malloc(count * ffn * kernel * sizeof(float));
+    float *score = (float *)malloc(count * sizeof(float));
+    int rc = -1;
+    if (!x || !nrm || !qkv || !ctx || !res || !hidden || !col || !score) goto done;
+    for (size_t t = 0; t < count; ++t) {
+        if (ids[t] < 0 || (size_t)ids[t] >= vocab) goto done;
+        for (size_t d = 0; d < w; ++d) x[t * w + d] = embedding[(size_t)ids[t] * w + d];
+    }
+    for (size_t t = 0; t < count; ++t)
+        for (size_t d = 0; d < w; ++d) x[t * w + d] += position[t * w + d];
+    const float scale = 1.0f / sqrtf((float)hw);
+    for (size_t l = 0; l < layers; ++l) {
+        orc_layernorm(x, norm_self[l], NULL, nrm, count, w, 1.0e-5f);
+        for (size_t t = 0; t < count; ++t)
+            for (size_t r = 0; r < 3u * w; ++r) qkv[t * 3u * w + r] = orc_dot_f32(qkv_w[l] + r * w, nrm + t * w, w);
+        for (size_t h = 0; h < heads; ++h) {
+            for (size_t t = 0; t < count; ++t) {
+                const float *q = qkv + t * 3u * w + h * hw;
+                for (size_t sidx = 0; sidx < count; ++sidx) {
+                    const float *k = qkv + sidx * 3u * w + w + h * hw;
+                    float sum = 0.0f;
+                    for (size_t d = 0; d < hw; ++d) sum += q[d] * k[d];
+                    score[sidx] = scale * sum;
+                }
+                const size_t valid = t + 1u;
+                float maximum = -FLT_MAX;
+                for (size_t sidx = 0; sidx < valid; ++sidx) if (score[sidx] > maximum) maximum = score[sidx];
+                float total = 0.0f;
+                for (size_t sidx = 0; sidx < valid; ++sidx) { score[sidx] = expf(score[sidx] - maximum); total += score[sidx]; }
+                const float inverse = total > 0.0f ? 1.0f / total : 0.0f;
+                for (size_t sidx = 0; sidx < valid; ++sidx) score[sidx] *= inverse;
+                for (size_t sidx = valid; sidx < count; ++sidx) score[sidx] = 0.0f;
+                for (size_t d = 0; d < hw; ++d) {
+                    float sum = 0.0f;
+                    for (size_t sidx = 0; sidx < count; ++sidx) sum += score[sidx] * qkv[sidx * 3u * w + 2u * w + h * hw + d];
+                    ctx[t * w + h * hw + d] = 1.0f * sum;
+                }
+            }
+        }
+        for (size_t t = 0; t < count; ++t)
+            for (size_t r = 0; r < w; ++r) res[t * w + r] = orc_dot_f32(o_w[l] + r * w, ctx + t * w, w);
+        for (size_t i = 0; i < count * w; ++i) x[i] += res[i];
+        orc_layernorm(x, norm_ff[l], NULL, nrm, count, w, 1.0e-5f);
+        /* unfold, product, GELU, unfold, product */
+        for (size_t t = 0; t < count; ++t)
+            for (size_t i = 0; i < w; ++i)
+                for (size_t k = 0; k < kernel; ++k) {
+                    const long src = (long)t - (long)(kernel - 1u) + (long)k;
+                    col[(t * w + i) * kernel + k] = src < 0 ? 0.0f : nrm[(size_t)src * w + i];
+                }
+        for (size_t t = 0; t < count; ++t)
+            for (size_t r = 0; r < ffn; ++r)
+                hidden[t * ffn + r] = 1.0f * orc_dot_f32(col + t * w * kernel, proj_w[l] + r * w * kernel, w * kernel);
+        orc_gelu_scalar(hidden, count * ffn);
+        for (size_t t = 0; t < count; ++t)
+            for (size_t i = 0; i < ffn; ++i)
+                for (size_t k = 0; k < kernel; ++k) {
+                    const long src = (long)t - (long)(kernel - 1u) + (long)k;
+                    col[(t * ffn + i) * kernel + k] = src < 0 ? 0.0f : hidden[(size_t)src * ffn + i];
+                }
+        for (size_t t = 0; t < count; ++t)
+            for (size_t r = 0; r < w; ++r)
+                res[t * w + r] = 1.0f * orc_dot_f32(col + t * ffn * kernel, out_w[l] + r * ffn * kernel, ffn * kernel);
+        for (size_t i = 0; i < count * w; ++i) x[i] += res[i];
+    }
+    orc_layernorm(x, norm_out, NULL, out, count, w, 1.0e-5f);
+    rc = 0;
+done:
+    free(x); free(nrm); free(qkv); free(ctx); free(res); free(hidden); free(col); free(score);
+    return rc;
+}
+
 /* src/graph.c:760-804 with the table index flattened: the reference walks
  * stream = fs * codebooks + codebook over stacking * codebooks tables and
  * divides the sum by their count. */

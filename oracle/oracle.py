@@ -99,6 +99,10 @@ class Port:
         lib.orc_stream_set_layers.argtypes = [C.c_void_p, sz]
         lib.orc_decoder_step.argtypes = [C.c_void_p, c_float_p, c_float_p]
         lib.orc_decoder_prefill.argtypes = [C.c_void_p, c_float_p, C.c_size_t, c_float_p]
+        fpp = C.POINTER(c_float_p)
+        lib.orc_encode_text.argtypes = [C.POINTER(C.c_int), C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t,
+                                        C.c_size_t, c_float_p, c_float_p, c_float_p, fpp, fpp, fpp, fpp, fpp, fpp,
+                                        c_float_p]
         lib.orc_embed_frame.argtypes = [C.c_void_p, c_uint_p, c_float_p]
         lib.orc_heads_argmax.argtypes = [C.c_void_p, c_float_p, C.c_int, c_uint_p, c_float_p]
         lib.orc_greedy_frame.argtypes = [C.c_void_p, c_uint_p, C.c_int, c_uint_p, c_float_p]
@@ -171,6 +175,30 @@ class Port:
         rc = self.lib.orc_qmat_linear(qtype, _fp(w), _fp(x2), _fp(out), x2.shape[0], k, n,
                                       None if bias is None else _fp(bias),
                                       None if ln_gain is None else _fp(ln_gain))
+        assert rc == 0
+        return out
+
+    def encode_text(self, tensors: dict, shape, ids) -> np.ndarray:
+        """The text encoder over the reference-named tensors of synth.add_encoder:
+        ids [count] -> states [count, width]."""
+        ids = np.ascontiguousarray(ids, np.int32)
+        L = shape.layers
+
+        def arr(fmt):
+            keep = [np.ascontiguousarray(tensors[fmt.format(l)], np.float32) for l in range(L)]
+            return keep, (c_float_p * L)(*[_fp(a) for a in keep])
+        keeps = []
+        ptrs = []
+        for fmt in ("encoder.layers.{}.norm_self.weight", "encoder.layers.{}.self_attention.qkv_net.weight",
+                    "encoder.layers.{}.self_attention.o_net.weight", "encoder.layers.{}.norm_pos_ff.weight",
+                    "encoder.layers.{}.pos_ff.proj.conv.weight", "encoder.layers.{}.pos_ff.o_net.conv.weight"):
+            k, p = arr(fmt)
+            keeps.append(k); ptrs.append(p)
+        out = np.empty((len(ids), shape.width), np.float32)
+        rc = self.lib.orc_encode_text(ids.ctypes.data_as(C.POINTER(C.c_int)), len(ids), L, shape.width, shape.heads,
+                                      shape.kernel, shape.vocab, _fp(tensors["text_embedding.weight"]),
+                                      _fp(tensors["encoder.position_embeddings.weight"]),
+                                      _fp(tensors["encoder.norm_out.weight"]), *ptrs, _fp(out))
         assert rc == 0
         return out
 
@@ -428,6 +456,7 @@ class Ref:
                                                c_float_p, sz, C.c_char_p, sz]
         lib.ref_decoder_run.argtypes = [C.c_void_p, C.c_void_p, c_float_p, sz, c_float_p,
                                         C.c_char_p, sz]
+        lib.ref_encode_text.argtypes = [C.c_void_p, C.c_uint, C.c_uint, C.POINTER(C.c_int), sz, c_float_p, C.c_char_p, sz]
         lib.ref_model_resident.argtypes = [C.c_void_p]
         lib.ref_model_backend_name.restype = C.c_char_p
         lib.ref_model_backend_name.argtypes = [C.c_void_p]
@@ -598,6 +627,16 @@ class RefModel:
 
     def new_decoder(self, memory: np.ndarray, capacity: int) -> "RefDecoder":
         return RefDecoder(self, memory, capacity)
+
+    def encode_text(self, shape, ids) -> np.ndarray:
+        """encode_text (src/graph.c:709-748) over the model file's "encoder" tensors."""
+        ids = np.ascontiguousarray(ids, np.int32)
+        out = np.empty((len(ids), shape.width), np.float32)
+        err = C.create_string_buffer(256)
+        rc = self.ref.lib.ref_encode_text(self.handle, shape.layers, shape.max_length,
+                                          ids.ctypes.data_as(C.POINTER(C.c_int)), len(ids), _fp(out), err, 256)
+        assert rc == 0, err.value
+        return out
 
     @property
     def resident(self) -> bool:

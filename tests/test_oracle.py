@@ -283,3 +283,25 @@ def test_port_prefill_equals_reference_decoder_run(qtype, count, tiny_model, tin
     assert np.array_equal(ps.self_v[:, :3 + count], rd.self_v[:, :3 + count])
     assert np.array_equal(ps.step(after), rd.step(after))
     rd.close(); rm.close(); ps.close(); pm.close()
+
+
+def test_port_text_encoder_equals_reference(tiny_model):
+    """The restated text encoder (encode_text, src/graph.c:709-748: embedding rows, six-tensor
+    layers with causal self attention and the kernel-3 causal convolution feed-forward, output
+    norm) against the reference's own, bit for bit."""
+    if not O.have_ref("strict"):
+        pytest.skip("compiled reference absent")
+    import copy
+    from mynah_tts_b200 import synth
+    model = copy.copy(tiny_model)
+    model = type(tiny_model)(shape=tiny_model.shape, seed=tiny_model.seed, tensors=dict(tiny_model.tensors))
+    enc = synth.TINY_ENCODER
+    tensors = synth.add_encoder(model, enc, seed=91)
+    rm = O.RefModel(model, O.INT8, "strict")          # the cache format must not matter: linear() is f32
+    rng = np.random.default_rng(5)
+    for count in (1, 2, 19, 40):
+        ids = rng.integers(0, enc.vocab, size=count).astype(np.int32)
+        want = rm.encode_text(enc, ids)
+        got = O.Port.get().encode_text(tensors, enc, ids)
+        assert np.array_equal(got, want), count
+    rm.close()
