@@ -214,6 +214,75 @@ def add_encoder(model: "SynthModel | None", shape: EncoderShape, seed: int) -> d
     return t
 
 
+@dataclass(frozen=True)
+class CodecShape:
+    """The NanoCodec decoder (src/graph.c:2640-2780): 8 FSQ groups of 4 latent channels, a first
+    convolution to `base` channels, five up-sampling stages that halve the channels.  The
+    reference hard-codes base = 864; smaller multiples of 32 serve as test shapes."""
+    base: int = 864
+    rates: tuple = (8, 8, 4, 2, 2)
+    kernels: tuple = (3, 7, 11)      # one residual branch per kernel
+    dilations: tuple = (1, 3, 5)     # three blocks per branch
+    groups: int = 8
+    latent: int = 32
+    fsq_codes: int = 2016            # 8 * 7 * 6 * 6 indices per group
+
+    @property
+    def samples_per_frame(self) -> int:
+        return int(np.prod(self.rates))
+
+
+TINY_CODEC = CodecShape(base=96)
+
+
+def add_codec(model: "SynthModel | None", shape: CodecShape, seed: int) -> dict[str, np.ndarray]:
+    """Draws the codec decoder's tensors under the names decode_codec resolves
+    (src/graph.c:2545-2626, 2360-2395).  Convolution weights ~ N(0, 1/fan_in) so activations
+    keep unit scale through the 19 convolutions of a stage; Snake alphas ~ N(1, 0.1)."""
+    rng = np.random.default_rng([seed, 0x636463])
+    t: dict[str, np.ndarray] = {}
+
+    def conv(name, oc, ic, k, fan_in=None):
+        std = 1.0 / np.sqrt(fan_in or ic * k)
+        t[name + ".weight"] = np.ascontiguousarray(rng.normal(0.0, std, size=(oc, ic, k)).astype(np.float32))
+        t[name + ".bias"] = np.ascontiguousarray(rng.normal(0.0, 0.02, size=(oc,)).astype(np.float32))
+
+    def alpha(name, channels):
+        t[name + ".activation.snake_act.alpha"] = np.ascontiguousarray(
+            rng.normal(1.0, 0.1, size=(channels,)).astype(np.float32))
+
+    conv("audio_decoder.pre_conv.conv", shape.base, shape.latent, 7)
+    ch = shape.base
+    for s, rate in enumerate(shape.rates):
+        alpha(f"audio_decoder.activations.{s}", ch)
+        nch = ch // 2
+        # transposed convolution weight [in][out per group = 1][kernel]; every output sample
+        # sums 2 channels x 2 taps
+        conv(f"audio_decoder.up_sample_conv_layers.{s}.conv", ch, 1, 2 * rate, fan_in=4)
+        t[f"audio_decoder.up_sample_conv_layers.{s}.conv.bias"] = np.ascontiguousarray(
+            rng.normal(0.0, 0.02, size=(nch,)).astype(np.float32))
+        for b, k in enumerate(shape.kernels):
+            for d in range(len(shape.dilations)):
+                pre = f"audio_decoder.res_layers.{s}.res_blocks.{b}.res_blocks.{d}."
+                alpha(pre + "input_activation", nch)
+                conv(pre + "input_conv.conv", nch, nch, k)
+                alpha(pre + "skip_activation", nch)
+                # the skip convolution's output joins the residual: keep it small
+                conv(pre + "skip_conv.conv", nch, nch, k, fan_in=9 * nch * k)
+        ch = nch
+    alpha("audio_decoder.post_activation", ch)
+    conv("audio_decoder.post_conv.conv", 1, ch, 3)
+    if model is not None:
+        model.tensors.update(t)
+    return t
+
+
+def make_codec_codes(shape: CodecShape, seed: int, frames: int) -> np.ndarray:
+    """FSQ indices [groups, frames] uint32, uniform over the group's code space."""
+    rng = np.random.default_rng([seed, 0x667371])
+    return np.ascontiguousarray(rng.integers(0, shape.fsq_codes, size=(shape.groups, frames), dtype=np.uint32))
+
+
 def make_memory(shape: DecoderShape, seed: int) -> np.ndarray:
     """Text-encoder output for one request: [memory_length, width] ~ N(0,1)."""
     rng = np.random.default_rng([seed, 0x6D656D])

@@ -261,6 +261,21 @@ REF_EXPORT int ref_encode_text(ref_model *r, unsigned encoder_layers, unsigned t
     return 0;
 }
 
+/* decode_codec (src/graph.c:2640-2780) over codec tensors that live in the same synthetic
+ * file as the rest (the reference keeps them in a second file, model->codec).  codes are
+ * [8][raw_length]; out receives raw_length * 1024 samples.  Returns the count or -1. */
+REF_EXPORT long ref_decode_codec(ref_model *r, const unsigned *codes, size_t raw_length, float *out,
+                                 char *error, size_t cap) {
+    if (r->model.codec == NULL) r->model.codec = r->model.tts;
+    float *samples = NULL;
+    size_t count = 0;
+    if (cap > 0) error[0] = '\0';
+    if (decode_codec(&r->model, codes, raw_length, &samples, &count, error, cap) != 0) return -1;
+    memcpy(out, samples, count * sizeof(float));
+    free(samples);
+    return (long)count;
+}
+
 /* ------------------------------------------------------ local transformer */
 typedef struct {
     local_frame_state state;

@@ -1144,3 +1144,159 @@ int orc_local_frame(orc_local *s, const float *decoder_last, float temperature, 
     if (eos_frame != NULL) *eos_frame = first;
     return saw_eos;
 }
+
+/* ------------------------------------------------------------------ NanoCodec decoder
+ * decode_codec in the reference's scalar build (src/graph.c:2640-2780): FSQ de-index of the
+ * 8 codebook indices into 32 latent channels (levels 8,7,6,6 per group), a causal
+ * convolution 32 -> base (kernel 7), five stages of { half-Snake, grouped causal transposed
+ * convolution (kernel 2r, stride r, two input channels per output channel), residual layer },
+ * half-Snake, a causal convolution to one channel (kernel 3), clip to [-1, 1].  Activations
+ * are [channels][length], time contiguous.  base is 864 in the reference (hard-coded); it is
+ * a parameter here so small shapes can be checked too. */
+typedef struct {
+    const float *in_alpha, *in_w, *in_b, *skip_alpha, *skip_w, *skip_b;
+} orc_codec_block;
+typedef struct {
+    const float *alpha, *up_w, *up_b;
+    orc_codec_block block[3][3];      /* [kernel 3,7,11][dilation 1,3,5] */
+} orc_codec_stage;
+typedef struct {
+    size_t base;                      /* channels after the first convolution */
+    const float *pre_w, *pre_b;       /* [base][32][7], [base] */
+    orc_codec_stage stage[5];
+    const float *post_alpha, *post_w, *post_b;   /* [base/32], [1][base/32][3], [1] */
+} orc_codec;
+
+/* conv1d_causal without BLAS (src/graph.c:2059-2096): the output is seeded with the bias,
+ * the input is unfolded into columns[(i * kernel + k)][t] = in[i][t - (kernel-1-k) * dilation]
+ * (zero before the start) and one scalar sgemm with beta = 1 adds the product: per output
+ * c = 1.0f * sum + 1.0f * c with sum over p = i * kernel + k in order (src/backend.c:343-354). */
+static void orc_conv1d_causal(const float *w, const float *b, const float *in, float *out, size_t ic,
+                              size_t oc, size_t length, size_t kernel, size_t dilation) {
+    for (size_t o = 0; o < oc; ++o)
+        for (size_t t = 0; t < length; ++t) {
+            float sum = 0.0f;
+            for (size_t i = 0; i < ic; ++i)
+                for (size_t k = 0; k < kernel; ++k) {
+                    const size_t shift = (kernel - 1u - k) * dilation;
+                    const float x = t >= shift ? in[i * length + (t - shift)] : 0.0f;
+                    sum += w[(o * ic + i) * kernel + k] * x;
+                }
+            out[o * length + t] = 1.0f * sum + 1.0f * b[o];
+        }
+}
+
+/* conv_transpose_causal / convt_channel (src/graph.c:2179-2231) with groups = out channels. */
+static void orc_conv_transpose(const float *w, const float *b, const float *in, float *out, size_t ic,
+                               size_t oc, size_t length, size_t kernel, size_t stride) {
+    const size_t out_len = (length - 1u) * stride + kernel - (kernel - stride);
+    const size_t ipg = ic / oc;
+    for (size_t o = 0; o < oc; ++o) {
+        float *row = out + o * out_len;
+        for (size_t t = 0; t < out_len; ++t) row[t] = b[o];
+        for (size_t i = o * ipg; i < (o + 1u) * ipg; ++i)
+            for (size_t t = 0; t < length; ++t) {
+                const float v = in[i * length + t];
+                for (size_t k = 0; k < kernel; ++k) {
+                    const size_t pos = t * stride + k;
+                    if (pos < out_len) row[pos] += v * w[i * kernel + k];
+                }
+            }
+    }
+}
+
+/* Snake on the first half of the channels, leaky ReLU (0.01) on the rest.  half_snake
+ * (src/graph.c:2250-2323) hands the signal to mynah_backend_snake_dev whenever a backend
+ * exists, and the CPU backend's form is snake_row (src/backend.c:643-658): v + sn * sn *
+ * (1 / (a + 1e-9)) -- a product with the reciprocal, not the division of graph.c's own
+ * snake_channel, which no CPU synthesis reaches. */
+static void orc_half_snake(float *x, const float *alpha, size_t channels, size_t length) {
+    const size_t snake = channels / 2u;
+    for (size_t c = 0; c < channels; ++c) {
+        float *row = x + c * length;
+        if (c < snake) {
+            const float a = alpha[c];
+            const float inv_a = 1.0f / (a + 1e-9f);
+            for (size_t t = 0; t < length; ++t) {
+                const float v = row[t];
+                const float sn = sinf(a * v);
+                row[t] = v + sn * sn * inv_a;
+            }
+        } else {
+            for (size_t t = 0; t < length; ++t)
+                if (row[t] < 0.0f) row[t] *= 0.01f;
+        }
+    }
+}
+
+/* res_layer (src/graph.c:2325-2421). */
+static int orc_res_layer(const orc_codec_stage *s, const float *in, float *out, size_t channels, size_t length) {
+    static const size_t kernels[3] = {3u, 7u, 11u}, dilations[3] = {1u, 3u, 5u};
+    const size_t n = channels * length;
+    float *branch = (float *)malloc(n * sizeof(float)), *cur = (float *)malloc(n * sizeof(float));
+    float *act = (float *)malloc(n * sizeof(float)), *res = (float *)malloc(n * sizeof(float));
+    if (!branch || !cur || !act || !res) { free(branch); free(cur); free(act); free(res); return -1; }
+    memset(out, 0, n * sizeof(float));
+    for (size_t bi = 0; bi < 3u; ++bi) {
+        memcpy(cur, in, n * sizeof(float));
+        for (size_t di = 0; di < 3u; ++di) {
+            const orc_codec_block *b = &s->block[bi][di];
+            memcpy(act, cur, n * sizeof(float));
+            orc_half_snake(act, b->in_alpha, channels, length);
+            orc_conv1d_causal(b->in_w, b->in_b, act, res, channels, channels, length, kernels[bi], dilations[di]);
+            orc_half_snake(res, b->skip_alpha, channels, length);
+            orc_conv1d_causal(b->skip_w, b->skip_b, res, branch, channels, channels, length, kernels[bi], 1u);
+            for (size_t i = 0; i < n; ++i) cur[i] += branch[i];
+        }
+        for (size_t i = 0; i < n; ++i) out[i] += cur[i];
+    }
+    for (size_t i = 0; i < n; ++i) out[i] /= 3.0f;
+    free(branch); free(cur); free(act); free(res);
+    return 0;
+}
+
+/* codes [8][raw_length] -> samples [raw_length * 1024].  Returns the sample count or -1.
+ * stop_after: 0 = whole codec; 1 = only the first convolution (out = [base][raw_length]);
+ * 2 + s = through stage s (out = [base >> (s+1)][length of that stage]) -- for stage-wise
+ * comparisons. */
+long orc_codec_decode(const orc_codec *c, const unsigned *codes, size_t raw_length, int stop_after, float *out) {
+    static const size_t levels[4] = {8u, 7u, 6u, 6u}, bases[4] = {1u, 8u, 56u, 336u}, rates[5] = {8u, 8u, 4u, 2u, 2u};
+    if (raw_length == 0u) return -1;
+    float *latent = (float *)malloc(32u * raw_length * sizeof(float));
+    float *cur = (float *)malloc(c->base * raw_length * sizeof(float));
+    if (!latent || !cur) { free(latent); free(cur); return -1; }
+    for (size_t t = 0; t < raw_length; ++t)
+        for (size_t g = 0; g < 8u; ++g) {
+            const unsigned index = codes[g * raw_length + t];
+            for (size_t d = 0; d < 4u; ++d) {
+                const size_t digit = (index / bases[d]) % levels[d];
+                const float den = (float)(levels[d] / 2u);
+                latent[(g * 4u + d) * raw_length + t] = ((float)digit - (float)(levels[d] / 2u)) / den;
+            }
+        }
+    orc_conv1d_causal(c->pre_w, c->pre_b, latent, cur, 32u, c->base, raw_length, 7u, 1u);
+    free(latent);
+    size_t ch = c->base, len = raw_length;
+    if (stop_after == 1) { memcpy(out, cur, ch * len * sizeof(float)); free(cur); return (long)(ch * len); }
+    for (size_t s = 0; s < 5u; ++s) {
+        orc_half_snake(cur, c->stage[s].alpha, ch, len);
+        const size_t nch = ch / 2u, nlen = len * rates[s];
+        float *up = (float *)malloc(nch * nlen * sizeof(float));
+        float *next = (float *)malloc(nch * nlen * sizeof(float));
+        if (!up || !next) { free(up); free(next); free(cur); return -1; }
+        orc_conv_transpose(c->stage[s].up_w, c->stage[s].up_b, cur, up, ch, nch, len, rates[s] * 2u, rates[s]);
+        free(cur);
+        if (orc_res_layer(&c->stage[s], up, next, nch, nlen) != 0) { free(up); free(next); return -1; }
+        free(up);
+        cur = next; ch = nch; len = nlen;
+        if (stop_after == 2 + (int)s) { memcpy(out, cur, ch * len * sizeof(float)); free(cur); return (long)(ch * len); }
+    }
+    orc_half_snake(cur, c->post_alpha, ch, len);
+    orc_conv1d_causal(c->post_w, c->post_b, cur, out, ch, 1u, len, 3u, 1u);
+    for (size_t i = 0; i < len; ++i) {
+        if (out[i] > 1.0f) out[i] = 1.0f;
+        if (out[i] < -1.0f) out[i] = -1.0f;
+    }
+    free(cur);
+    return (long)len;
+}

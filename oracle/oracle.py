@@ -53,6 +53,47 @@ def _ptr_array(arrays):
     return arr
 
 
+class CodecBlock(C.Structure):
+    _fields_ = [(n, C.POINTER(C.c_float)) for n in ("in_alpha", "in_w", "in_b", "skip_alpha", "skip_w", "skip_b")]
+
+
+class CodecStage(C.Structure):
+    _fields_ = [("alpha", C.POINTER(C.c_float)), ("up_w", C.POINTER(C.c_float)), ("up_b", C.POINTER(C.c_float)),
+                ("block", (CodecBlock * 3) * 3)]
+
+
+class CodecDesc(C.Structure):
+    """orc_codec of mynah_oracle.c."""
+    _fields_ = [("base", C.c_size_t), ("pre_w", C.POINTER(C.c_float)), ("pre_b", C.POINTER(C.c_float)),
+                ("stage", CodecStage * 5), ("post_alpha", C.POINTER(C.c_float)),
+                ("post_w", C.POINTER(C.c_float)), ("post_b", C.POINTER(C.c_float))]
+
+
+def fill_codec_desc(desc, tensors: dict, keep: list):
+    """Points a codec descriptor (this module's CodecDesc or any structure with the same field
+    names) at the reference-named tensors of synth.add_codec."""
+    def p(name):
+        a = np.ascontiguousarray(tensors[name], np.float32)
+        keep.append(a)
+        return a.ctypes.data_as(C.POINTER(C.c_float))
+    desc.pre_w, desc.pre_b = p("audio_decoder.pre_conv.conv.weight"), p("audio_decoder.pre_conv.conv.bias")
+    for s in range(5):
+        st = desc.stage[s]
+        st.alpha = p(f"audio_decoder.activations.{s}.activation.snake_act.alpha")
+        st.up_w = p(f"audio_decoder.up_sample_conv_layers.{s}.conv.weight")
+        st.up_b = p(f"audio_decoder.up_sample_conv_layers.{s}.conv.bias")
+        for b in range(3):
+            for d in range(3):
+                pre = f"audio_decoder.res_layers.{s}.res_blocks.{b}.res_blocks.{d}."
+                blk = st.block[b][d]
+                blk.in_alpha = p(pre + "input_activation.activation.snake_act.alpha")
+                blk.in_w, blk.in_b = p(pre + "input_conv.conv.weight"), p(pre + "input_conv.conv.bias")
+                blk.skip_alpha = p(pre + "skip_activation.activation.snake_act.alpha")
+                blk.skip_w, blk.skip_b = p(pre + "skip_conv.conv.weight"), p(pre + "skip_conv.conv.bias")
+    desc.post_alpha = p("audio_decoder.post_activation.activation.snake_act.alpha")
+    desc.post_w, desc.post_b = p("audio_decoder.post_conv.conv.weight"), p("audio_decoder.post_conv.conv.bias")
+
+
 class Port:
     """Typed access to liboracle_port.so."""
 
@@ -103,6 +144,8 @@ class Port:
         lib.orc_encode_text.argtypes = [C.POINTER(C.c_int), C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t,
                                         C.c_size_t, c_float_p, c_float_p, c_float_p, fpp, fpp, fpp, fpp, fpp, fpp,
                                         c_float_p]
+        lib.orc_codec_decode.restype = C.c_long
+        lib.orc_codec_decode.argtypes = [C.POINTER(CodecDesc), c_uint_p, C.c_size_t, C.c_int, c_float_p]
         lib.orc_embed_frame.argtypes = [C.c_void_p, c_uint_p, c_float_p]
         lib.orc_heads_argmax.argtypes = [C.c_void_p, c_float_p, C.c_int, c_uint_p, c_float_p]
         lib.orc_greedy_frame.argtypes = [C.c_void_p, c_uint_p, C.c_int, c_uint_p, c_float_p]
@@ -200,6 +243,27 @@ class Port:
                                       _fp(tensors["encoder.position_embeddings.weight"]),
                                       _fp(tensors["encoder.norm_out.weight"]), *ptrs, _fp(out))
         assert rc == 0
+        return out
+
+    def codec_decode(self, tensors: dict, shape, codes, stop_after: int = 0) -> np.ndarray:
+        """The codec decoder over the reference-named tensors of synth.add_codec: codes
+        [8, frames] -> samples [frames * 1024]; stop_after = 1: the first convolution's output
+        [base, frames]; 2 + s: stage s's output [channels, length]."""
+        codes = np.ascontiguousarray(codes, np.uint32)
+        frames = codes.shape[1]
+        desc, keep = CodecDesc(), []
+        desc.base = shape.base
+        fill_codec_desc(desc, tensors, keep)
+        if stop_after == 0:
+            dims = (frames * shape.samples_per_frame,)
+        elif stop_after == 1:
+            dims = (shape.base, frames)
+        else:
+            s = stop_after - 2
+            dims = (shape.base >> (s + 1), frames * int(np.prod(shape.rates[:s + 1])))
+        out = np.empty(dims, np.float32)
+        n = self.lib.orc_codec_decode(C.byref(desc), codes.ctypes.data_as(c_uint_p), frames, stop_after, _fp(out))
+        assert n == out.size, n
         return out
 
     def argmax_constrained(self, logits, codebook_size, eos_id, allow_eos) -> int:
@@ -457,6 +521,8 @@ class Ref:
         lib.ref_decoder_run.argtypes = [C.c_void_p, C.c_void_p, c_float_p, sz, c_float_p,
                                         C.c_char_p, sz]
         lib.ref_encode_text.argtypes = [C.c_void_p, C.c_uint, C.c_uint, C.POINTER(C.c_int), sz, c_float_p, C.c_char_p, sz]
+        lib.ref_decode_codec.restype = C.c_long
+        lib.ref_decode_codec.argtypes = [C.c_void_p, c_uint_p, sz, c_float_p, C.c_char_p, sz]
         lib.ref_model_resident.argtypes = [C.c_void_p]
         lib.ref_model_backend_name.restype = C.c_char_p
         lib.ref_model_backend_name.argtypes = [C.c_void_p]
@@ -585,6 +651,16 @@ class RefModel:
                                                 _fp(row), err, 256)
         assert rc == 0, err.value
         return row
+
+    def decode_codec(self, codes) -> np.ndarray:
+        """decode_codec (src/graph.c:2640-2780): codes [8, frames] -> samples [frames * 1024];
+        the model's tensors must include synth.add_codec's at base 864."""
+        codes = np.ascontiguousarray(codes, np.uint32)
+        out = np.empty((codes.shape[1] * 1024,), np.float32)
+        err = C.create_string_buffer(256)
+        n = self.ref.lib.ref_decode_codec(self.handle, codes.ctypes.data_as(c_uint_p), codes.shape[1], _fp(out), err, 256)
+        assert n == out.size, err.value
+        return out
 
     def new_local(self, top_count: int = 0) -> "RefLocal":
         return RefLocal(self, top_count)
