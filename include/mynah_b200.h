@@ -125,8 +125,11 @@ int mynah_cuda_argmax_dev(void *state, const float *dev_logits, size_t vocab, si
 int mynah_cuda_gelu_host(void *state, float *host_data, size_t n, char *error, size_t cap);
 int mynah_cuda_gelu_host_f64(void *state, float *host_data, size_t n, char *error, size_t cap);
 
-/* NanoCodec ops (src/backend.h:59-62,128-133) are outside this library's
- * scope; they return -1 with a message so the caller keeps its CPU path. */
+/* NanoCodec ops (src/backend.h:59-60,128-133).  snake_dev: device signal in place, HOST alpha.
+ * im2col: device pointers.  conv1d: HOST input/output and host weight/bias as cache keys,
+ * synchronous -- the contract of the reference's CUDA backend (gpu/cuda/backend_cuda.cu:
+ * 746-810); kernels other than 3, 7, 11 return -1 so the caller keeps its CPU path.  The whole
+ * codec as one device-resident pass is mynah_b200_codec_decode below. */
 int mynah_cuda_snake_dev(void *state, float *dev_data, const float *alpha, size_t channels,
                          size_t length, size_t snake_channels, char *error, size_t cap);
 int mynah_cuda_im2col(void *state, const float *in, float *cols, int in_ch, int length, int kernel,
@@ -432,6 +435,46 @@ void mynah_b200_encoder_destroy(void *encoder);
  * Synchronous. */
 int mynah_b200_encoder_encode(void *encoder, const int *ids, size_t count, float *out, char *error,
                               size_t cap);
+
+/* ---- codec decoder (src/graph.c:2640-2780) -----------------------------------------
+ * decode_codec: FSQ indices -> audio samples.  Host weight pointers under the names the
+ * reference resolves (src/graph.c:2545-2626, 2360-2395): */
+typedef struct {
+    const float *in_alpha;    /* ...res_blocks.B.res_blocks.D.input_activation.activation.snake_act.alpha [C] */
+    const float *in_w, *in_b; /* ...input_conv.conv.{weight [C, C, kernel], bias [C]} */
+    const float *skip_alpha;  /* ...skip_activation.activation.snake_act.alpha [C] */
+    const float *skip_w, *skip_b; /* ...skip_conv.conv.{weight [C, C, kernel], bias [C]} */
+} mynah_b200_codec_block;
+
+typedef struct {
+    const float *alpha;       /* audio_decoder.activations.S.activation.snake_act.alpha [2C] */
+    const float *up_w, *up_b; /* audio_decoder.up_sample_conv_layers.S.conv.{weight [2C, 1, 2 * rate], bias [C]} */
+    mynah_b200_codec_block block[3][3];   /* audio_decoder.res_layers.S: [kernel 3, 7, 11][dilation 1, 3, 5] */
+} mynah_b200_codec_stage;
+
+typedef struct {
+    size_t base;              /* channels after the first convolution: 864 in the reference; a multiple of 32 */
+    size_t max_frames;        /* longest request, <= 4096; activations take base * 32 * 5 * 4 bytes per frame */
+    const float *pre_w, *pre_b;       /* audio_decoder.pre_conv.conv.{weight [base, 32, 7], bias} */
+    mynah_b200_codec_stage stage[5];  /* rates 8, 8, 4, 2, 2; channels halve per stage */
+    const float *post_alpha;          /* audio_decoder.post_activation.activation.snake_act.alpha [base / 32] */
+    const float *post_w, *post_b;     /* audio_decoder.post_conv.conv.{weight [1, base / 32, 3], bias [1]} */
+} mynah_b200_codec_desc;
+
+int mynah_b200_codec_create(void *state, const mynah_b200_codec_desc *desc, void **codec, char *error, size_t cap);
+void mynah_b200_codec_destroy(void *codec);
+size_t mynah_b200_codec_samples_per_frame(void);   /* 1024 */
+/* codes [8][frames] (HOST, FSQ index per group and frame) -> samples [frames * 1024] (HOST),
+ * clipped to [-1, 1]: the contract of decode_codec.  Synchronous. */
+int mynah_b200_codec_decode(void *codec, const unsigned *codes, size_t frames, float *samples,
+                            size_t *sample_count, char *error, size_t cap);
+/* For stage-wise checks: stop_after = 1 returns the first convolution's output [base][frames],
+ * 2 + s the output of stage s [base >> (s + 1)][its length]; 0 = the samples. */
+int mynah_b200_codec_decode_partial(void *codec, const unsigned *codes, size_t frames, int stop_after,
+                                    float *out, size_t out_capacity, size_t *count, char *error, size_t cap);
+/* Device time of one decode, averaged over `repeats` back-to-back decodes after one warm-up. */
+int mynah_b200_codec_time(void *codec, const unsigned *codes, size_t frames, int repeats,
+                          float *ms_per_decode, char *error, size_t cap);
 
 /* Bytes of weights one step reads, and of KV one slot at `length` reads. */
 size_t mynah_b200_decoder_weight_bytes(const void *decoder);

@@ -261,6 +261,73 @@ class TextEncoder:
             self.handle = None
 
 
+class Codec:
+    """decode_codec over the reference-named tensors of synth.add_codec (or a real pack)."""
+
+    def __init__(self, backend: Backend, tensors: dict, shape, max_frames: int):
+        self.backend, self.shape, self.max_frames = backend, shape, max_frames
+        self._keep = []
+
+        def p(name):
+            a = np.ascontiguousarray(tensors[name], np.float32)
+            self._keep.append(a)
+            return fp(a)
+        desc = capi.CodecDesc()
+        desc.base, desc.max_frames = shape.base, max_frames
+        desc.pre_w, desc.pre_b = p("audio_decoder.pre_conv.conv.weight"), p("audio_decoder.pre_conv.conv.bias")
+        for s in range(5):
+            st = desc.stage[s]
+            st.alpha = p(f"audio_decoder.activations.{s}.activation.snake_act.alpha")
+            st.up_w = p(f"audio_decoder.up_sample_conv_layers.{s}.conv.weight")
+            st.up_b = p(f"audio_decoder.up_sample_conv_layers.{s}.conv.bias")
+            for b in range(3):
+                for d in range(3):
+                    pre = f"audio_decoder.res_layers.{s}.res_blocks.{b}.res_blocks.{d}."
+                    blk = st.block[b][d]
+                    blk.in_alpha = p(pre + "input_activation.activation.snake_act.alpha")
+                    blk.in_w, blk.in_b = p(pre + "input_conv.conv.weight"), p(pre + "input_conv.conv.bias")
+                    blk.skip_alpha = p(pre + "skip_activation.activation.snake_act.alpha")
+                    blk.skip_w, blk.skip_b = p(pre + "skip_conv.conv.weight"), p(pre + "skip_conv.conv.bias")
+        desc.post_alpha = p("audio_decoder.post_activation.activation.snake_act.alpha")
+        desc.post_w, desc.post_b = p("audio_decoder.post_conv.conv.weight"), p("audio_decoder.post_conv.conv.bias")
+        self.handle = C.c_void_p()
+        call(capi.lib().mynah_b200_codec_create, backend.state, C.byref(desc), C.byref(self.handle))
+        self._keep = []          # the weights were uploaded during the call
+
+    def decode(self, codes, stop_after: int = 0) -> np.ndarray:
+        """codes [8, frames] -> samples [frames * 1024]; stop_after as in
+        mynah_b200_codec_decode_partial (1: first convolution, 2 + s: stage s)."""
+        codes = np.ascontiguousarray(codes, np.uint32)
+        frames = codes.shape[1]
+        n = C.c_size_t()
+        if stop_after == 0:
+            out = np.empty((frames * int(capi.lib().mynah_b200_codec_samples_per_frame()),), np.float32)
+            call(capi.lib().mynah_b200_codec_decode, self.handle, codes.ctypes.data_as(capi.c_uint_p), frames, fp(out),
+                 C.byref(n))
+        else:
+            s = stop_after - 2
+            dims = (self.shape.base, frames) if stop_after == 1 else \
+                (self.shape.base >> (s + 1), frames * int(np.prod(self.shape.rates[:s + 1])))
+            out = np.empty(dims, np.float32)
+            call(capi.lib().mynah_b200_codec_decode_partial, self.handle, codes.ctypes.data_as(capi.c_uint_p), frames,
+                 stop_after, fp(out), out.size, C.byref(n))
+        assert n.value == out.size
+        return out
+
+    def time(self, codes, repeats: int = 5) -> float:
+        """Device milliseconds of one decode."""
+        codes = np.ascontiguousarray(codes, np.uint32)
+        ms = C.c_float()
+        call(capi.lib().mynah_b200_codec_time, self.handle, codes.ctypes.data_as(capi.c_uint_p), codes.shape[1], repeats,
+             C.byref(ms))
+        return float(ms.value)
+
+    def close(self):
+        if self.handle:
+            capi.lib().mynah_b200_codec_destroy(self.handle)
+            self.handle = None
+
+
 class Decoder:
     """The whole-step decoder over a synth.SynthModel (or any object with the
     same accessors)."""

@@ -77,6 +77,19 @@ class EncoderDesc(C.Structure):
                 ("norm_out", c_float_p)]
 
 
+class CodecBlock(C.Structure):
+    _fields_ = [(n, c_float_p) for n in ("in_alpha", "in_w", "in_b", "skip_alpha", "skip_w", "skip_b")]
+
+
+class CodecStage(C.Structure):
+    _fields_ = [("alpha", c_float_p), ("up_w", c_float_p), ("up_b", c_float_p), ("block", (CodecBlock * 3) * 3)]
+
+
+class CodecDesc(C.Structure):
+    _fields_ = [("base", sz), ("max_frames", sz), ("pre_w", c_float_p), ("pre_b", c_float_p),
+                ("stage", CodecStage * 5), ("post_alpha", c_float_p), ("post_w", c_float_p), ("post_b", c_float_p)]
+
+
 class Sampler(C.Structure):
     _fields_ = [("temperature", C.c_float), ("topk", C.c_uint), ("rng_state", C.c_ulonglong),
                 ("allow_eos", C.c_int)]
@@ -162,6 +175,12 @@ SIGNATURES = {
     "mynah_b200_decoder_slot_load": (C.c_int, [C.c_void_p, sz, c_float_p, c_float_p, sz, c_float_p, c_float_p, sz, _E]),
     "mynah_b200_decoder_slot_prefill": (C.c_int, [C.c_void_p, sz, c_float_p, sz, _E]),
     "mynah_b200_decoder_prefill": (C.c_int, [C.c_void_p, sz, c_float_p, sz, c_float_p, _E]),
+    "mynah_b200_codec_create": (C.c_int, [C.c_void_p, C.POINTER(CodecDesc), C.POINTER(C.c_void_p), _E]),
+    "mynah_b200_codec_destroy": (None, [C.c_void_p]),
+    "mynah_b200_codec_samples_per_frame": (sz, []),
+    "mynah_b200_codec_decode": (C.c_int, [C.c_void_p, c_uint_p, sz, c_float_p, C.POINTER(sz), _E]),
+    "mynah_b200_codec_decode_partial": (C.c_int, [C.c_void_p, c_uint_p, sz, C.c_int, c_float_p, sz, C.POINTER(sz), _E]),
+    "mynah_b200_codec_time": (C.c_int, [C.c_void_p, c_uint_p, sz, C.c_int, c_float_p, _E]),
     "mynah_b200_encoder_create": (C.c_int, [C.c_void_p, C.POINTER(EncoderDesc), C.POINTER(C.c_void_p), _E]),
     "mynah_b200_encoder_destroy": (None, [C.c_void_p]),
     "mynah_b200_encoder_encode": (C.c_int, [C.c_void_p, c_int_p, sz, c_float_p, _E]),

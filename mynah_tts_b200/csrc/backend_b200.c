@@ -176,10 +176,12 @@ static int grow(void **ptr, size_t *have, size_t want, size_t elem, char *error,
 #define TANH_HI_BITS 0x41800000u
 #define EXP_LO_BITS 0x38000000u
 #define EXP_HI_BITS 0x43800000u
+#define SIN_LO_BITS 0x39800000u
+#define SIN_HI_BITS 0x42800000u
 static struct { mb_libm_tables tables; int state; /* 0 none, 1 exact, -1 failed */ } g_libm[LIBM_MAX_DEVICES];
 static pthread_mutex_t g_libm_lock = PTHREAD_MUTEX_INITIALIZER;
 
-typedef struct { float *out; uint32_t first_bits; size_t begin, end; int is_exp; } libm_job;
+typedef struct { float *out; uint32_t first_bits; size_t begin, end; int kind; /* 0 tanhf, 1 expf(-a), 2 sinf */ } libm_job;
 
 static void *libm_worker(void *arg) {
     const libm_job *j = (const libm_job *)arg;
@@ -187,12 +189,12 @@ static void *libm_worker(void *arg) {
         const uint32_t bits = j->first_bits + (uint32_t)i;
         float a;
         memcpy(&a, &bits, sizeof(a));
-        j->out[i] = j->is_exp ? expf(-a) : tanhf(a);   /* the HOST libm, which the reference links */
+        j->out[i] = j->kind == 1 ? expf(-a) : j->kind == 2 ? sinf(a) : tanhf(a);   /* the HOST libm, which the reference links */
     }
     return NULL;
 }
 
-static int build_libm_table(mb_state *st, int is_exp, uint32_t lo, uint32_t hi, uint32_t **table_out,
+static int build_libm_table(mb_state *st, int kind, uint32_t lo, uint32_t hi, uint32_t **table_out,
                             char *error, size_t cap) {
     enum { RUN = 1 << 23, MAX_THREADS = 64 };
     const size_t total = (size_t)(hi - lo);
@@ -218,7 +220,7 @@ static int build_libm_table(mb_state *st, int is_exp, uint32_t lo, uint32_t hi, 
             jobs[t].first_bits = lo + (uint32_t)off;
             jobs[t].begin = count * t / threads;
             jobs[t].end = count * (t + 1) / threads;
-            jobs[t].is_exp = is_exp;
+            jobs[t].kind = kind;
             if (t + 1 == threads || pthread_create(&tid[t], NULL, libm_worker, &jobs[t]) != 0) {
                 jobs[t].end = count;           /* this thread takes the rest */
                 libm_worker(&jobs[t]);
@@ -228,7 +230,7 @@ static int build_libm_table(mb_state *st, int is_exp, uint32_t lo, uint32_t hi, 
         }
         for (size_t t = 0; t < started; ++t) pthread_join(tid[t], NULL);
         rc = (int)cudaMemcpyAsync(dev, host, count * sizeof(float), cudaMemcpyHostToDevice, st->stream);
-        if (rc == 0) rc = mb_libm_delta(dev, lo + (uint32_t)off, count, is_exp, table + off / 8u, status, st->stream);
+        if (rc == 0) rc = mb_libm_delta(dev, lo + (uint32_t)off, count, kind, table + off / 8u, status, st->stream);
         if (rc == 0) rc = (int)cudaStreamSynchronize(st->stream);   /* host buffer is reused */
         st->launches += 1;
     }
@@ -268,6 +270,25 @@ static void libm_tables_for(mb_state *st) {
         st->libm_exact = 1;
     }
     pthread_mutex_unlock(&g_libm_lock);
+}
+
+/* The sinf table (the codec's Snake activation), built on first use: strict backends that
+ * never decode audio do not pay its 76 MB.  Returns NULL when strict mode is off or the
+ * build failed (the codec then uses the correctly rounded value). */
+const uint32_t *mb_libm_sin_table(mb_state *st) {
+    if (!st->strict || !st->libm_exact || st->device < 0 || st->device >= LIBM_MAX_DEVICES) return NULL;
+    pthread_mutex_lock(&g_libm_lock);
+    static int tried[LIBM_MAX_DEVICES];
+    if (g_libm[st->device].tables.sin_tab == NULL && g_libm[st->device].state == 1 && !tried[st->device]) {
+        char msg[128];
+        uint32_t *tab = NULL;
+        tried[st->device] = 1;
+        if (build_libm_table(st, 2, SIN_LO_BITS, SIN_HI_BITS, &tab, msg, sizeof(msg)) == 0)
+            g_libm[st->device].tables.sin_tab = tab;
+    }
+    st->libm.sin_tab = g_libm[st->device].tables.sin_tab;
+    pthread_mutex_unlock(&g_libm_lock);
+    return st->libm.sin_tab;
 }
 
 /* 1 when strict mode reproduces the host libm's expf/tanhf bit for bit. */
@@ -895,27 +916,68 @@ int mynah_cuda_cross_attention_dev(void *state, const float *dev_q, const float 
                             scale, dev_out, error, cap);
 }
 
-/* ------------------------------------------------------------- codec stubs */
-static int out_of_scope(char *error, size_t cap) {
-    mb_set_error(error, cap, "codec op is not part of the B200 decode backend; use the CPU path");
-    return -1;
-}
+/* ------------------------------------------------------------- codec ops */
+/* snake_dev (src/backend.h:128-133): device signal [channels][length] in place, HOST alpha
+ * (cached by pointer like the weights). */
 int mynah_cuda_snake_dev(void *state, float *dev_data, const float *alpha, size_t channels,
                          size_t length, size_t snake_channels, char *error, size_t cap) {
-    (void)state; (void)dev_data; (void)alpha; (void)channels; (void)length; (void)snake_channels;
-    return out_of_scope(error, cap);
+    SEAM_PROLOGUE();
+    if (dev_data == NULL || alpha == NULL || channels == 0u || length == 0u || snake_channels > channels) return -1;
+    const float *d_alpha = NULL;
+    if (snake_channels > 0u && mb_vector_cached(st, alpha, snake_channels, &d_alpha, error, cap) != 0) return -1;
+    MB_TRY(mb_codec_half_snake(dev_data, dev_data, d_alpha, channels, length, snake_channels, st->strict,
+                               mb_libm_sin_table(st), st->stream), "snake");
+    st->launches += 1;
+    mb_clear_error(error, cap);
+    return 0;
 }
+
+/* im2col (src/backend.h:59): device input [in_ch][length] -> device columns
+ * [in_ch * kernel][length]. */
 int mynah_cuda_im2col(void *state, const float *in, float *cols, int in_ch, int length, int kernel,
                       int dilation, char *error, size_t cap) {
-    (void)state; (void)in; (void)cols; (void)in_ch; (void)length; (void)kernel; (void)dilation;
-    return out_of_scope(error, cap);
+    SEAM_PROLOGUE();
+    if (in == NULL || cols == NULL || in_ch <= 0 || length <= 0 || kernel <= 0 || dilation <= 0) return -1;
+    MB_TRY(mb_codec_im2col(in, cols, (size_t)in_ch, (size_t)length, (size_t)kernel, (size_t)dilation, st->stream), "im2col");
+    st->launches += 1;
+    mb_clear_error(error, cap);
+    return 0;
 }
+
+/* conv1d (src/backend.h:60) as the reference's CUDA backend serves it: HOST input
+ * [in_ch][length] and HOST output [out_ch][length], host weight [out_ch][in_ch * kernel] and
+ * bias as cache keys, synchronous.  Shapes the convolution kernel does not take (a kernel
+ * other than 3, 7, 11) return -1 and the caller keeps its CPU path. */
 int mynah_cuda_conv1d(void *state, const float *in, float *out, int in_ch, int out_ch, int length,
                       int kernel, int dilation, const float *weight, const float *bias,
                       char *error, size_t cap) {
-    (void)state; (void)in; (void)out; (void)in_ch; (void)out_ch; (void)length; (void)kernel;
-    (void)dilation; (void)weight; (void)bias;
-    return out_of_scope(error, cap);
+    SEAM_PROLOGUE();
+    if (in == NULL || out == NULL || weight == NULL || bias == NULL || in_ch <= 0 || out_ch <= 0 || length <= 0 ||
+        dilation <= 0 || (kernel != 3 && kernel != 7 && kernel != 11) || (kernel - 1) * dilation > 50) {
+        mb_set_error(error, cap, "conv1d shape is not served by the B200 backend; use the CPU path");
+        return -1;
+    }
+    const size_t ic = (size_t)in_ch, oc = (size_t)out_ch, L = (size_t)length, K = (size_t)kernel;
+    const float *d_w = NULL, *d_b = NULL;
+    if (mb_vector_cached(st, weight, oc * ic * K, &d_w, error, cap) != 0 ||
+        mb_vector_cached(st, bias, oc, &d_b, error, cap) != 0) return -1;
+    const size_t packed = mb_codec_conv_packed_floats(oc, ic, K);
+    if (grow((void **)&st->d_in, &st->d_in_cap, ic * L + packed, sizeof(float), error, cap) != 0 ||
+        grow((void **)&st->d_out, &st->d_out_cap, oc * L, sizeof(float), error, cap) != 0) return -1;
+    float *d_packed = st->d_in + ic * L;
+    MB_TRY(cudaMemcpyAsync(st->d_in, in, ic * L * sizeof(float), cudaMemcpyHostToDevice, st->stream), "host to device copy");
+    MB_TRY(mb_codec_pack_conv_weight(d_w, d_packed, oc, ic, K, st->stream), "pack weight");
+    mb_codec_conv_args g;
+    memset(&g, 0, sizeof(g));
+    g.in = st->d_in; g.w_packed = d_packed; g.bias = d_b; g.out = st->d_out;
+    g.ic = ic; g.oc = oc; g.length = L; g.kernel = K; g.dilation = (size_t)dilation;
+    g.strict = st->strict; g.sm_count = st->sm_count;
+    MB_TRY(mb_codec_conv1d(&g, st->stream), "conv1d");
+    st->launches += 2;
+    MB_TRY(cudaMemcpyAsync(out, st->d_out, oc * L * sizeof(float), cudaMemcpyDeviceToHost, st->stream), "device to host copy");
+    MB_TRY(cudaStreamSynchronize(st->stream), "cudaStreamSynchronize");
+    mb_clear_error(error, cap);
+    return 0;
 }
 
 /* ------------------------------------------------ packing / single-op extension */

@@ -83,6 +83,9 @@ static inline const char *mb_status_message(int status) {
     return "device status word is set";
 }
 
+/* Strict mode: the host-libm sinf correction table of this device, built on first call. */
+const uint32_t *mb_libm_sin_table(mb_state *st);
+
 /* Upload a host f32 weight [n,k] and pack it as `qtype` (falls back to f32
  * when int4 cannot represent k).  The caller owns *out (mb_weight_release). */
 int mb_weight_build(mb_state *st, const float *host_w, size_t n, size_t k, int qtype,

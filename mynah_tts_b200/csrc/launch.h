@@ -27,12 +27,13 @@ enum { MB_FUSE_NONE = 0, MB_FUSE_LN = 1, MB_FUSE_QUANT = 2 };
 typedef struct {
     const uint32_t *tanh_tab;
     const uint32_t *exp_tab;
+    const uint32_t *sin_tab;   /* built on first use by a strict codec */
 } mb_libm_tables;
-/* One run of the table build: host_vals_dev[i] is the host's tanhf(a) (or
- * expf(-a) when is_exp) for the float a with bit pattern first_bits + i; packs
- * count/8 words at table_words.  status gets bit 4 if a difference does not fit
+/* One run of the table build: host_vals_dev[i] is the host's tanhf(a) (kind 0),
+ * expf(-a) (kind 1) or sinf(a) (kind 2) for the float a with bit pattern first_bits + i;
+ * packs count/8 words at table_words.  status gets bit 4 if a difference does not fit
  * 4 bits. */
-int mb_libm_delta(const float *host_vals_dev, uint32_t first_bits, size_t count, int is_exp,
+int mb_libm_delta(const float *host_vals_dev, uint32_t first_bits, size_t count, int kind,
                   uint32_t *table_words, int *status, mb_stream stream);
 
 /* Per-device one-time kernel attribute setup (call with the device current,
@@ -176,6 +177,45 @@ int mb_gemm_tc_f16(const mb_gemv_args *args, void *split, size_t rows_alloc, int
 int mb_sgemm(int trans_a, int trans_b, size_t m, size_t n, size_t k, float alpha,
              const float *a, size_t lda, const float *b, size_t ldb, float beta, float *c,
              size_t ldc, mb_stream stream);
+
+/* ---- codec decoder (codec.cu) ------------------------------------------- */
+/* Causal convolution out[o][t] = bias[o] + sum_{i,k} w[o][i][k] * in[i][t - (kernel-1-k) * dilation]
+ * over [channels][length] rows, summed per output in the order p = i * kernel + k, with the
+ * epilogues the codec's residual layers need.  kernel is 3, 7 or 11; (kernel-1)*dilation <= 50. */
+typedef struct {
+    const float *in;          /* [ic][length] */
+    const float *w_packed;    /* mb_codec_pack_conv_weight's layout */
+    const float *bias;        /* [oc] */
+    const float *res;         /* optional [oc][length]: v = res + v (may be `out`) */
+    float *out;               /* optional [oc][length] */
+    const float *alpha;       /* optional [oc]: out_act = half-Snake(v), Snake on channels < oc / 2 */
+    float *out_act;
+    float *acc;               /* acc_mode != 0: the residual layer's branch sum */
+    const float *alpha2;      /* acc_mode 3: half-Snake applied to the finished sum, or NULL */
+    const uint32_t *sin_tab;  /* strict: host-libm sinf correction table or NULL */
+    size_t ic, oc, length, kernel, dilation;
+    int acc_mode;             /* 0 none; 1 acc = v; 2 acc += v; 3 acc = (acc + v) / 3 */
+    int clip;                 /* clamp v to [-1, 1] */
+    int strict;
+    int sm_count;
+} mb_codec_conv_args;
+size_t mb_codec_conv_groups_alloc(size_t oc);
+size_t mb_codec_conv_packed_floats(size_t oc, size_t ic, size_t kernel);
+/* [oc][ic][kernel] (device) -> the packed layout (device). */
+int mb_codec_pack_conv_weight(const float *w, float *packed, size_t oc, size_t ic, size_t kernel, mb_stream stream);
+int mb_codec_conv1d(const mb_codec_conv_args *args, mb_stream stream);
+/* FSQ de-index: codes [8][frames] -> latent [32][frames]. */
+int mb_codec_fsq_latent(const unsigned *codes, float *latent, size_t frames, mb_stream stream);
+/* Grouped causal transposed convolution, kernel = 2 * stride, ic / oc input channels per output
+ * channel: in [ic][length] -> out [oc][length * stride]; w [ic][2 * stride]. */
+int mb_codec_conv_transpose(const float *in, const float *w, const float *bias, float *out, size_t ic, size_t oc,
+                            size_t length, size_t stride, int strict, mb_stream stream);
+/* out = half-Snake(in) (in place when out == in). */
+int mb_codec_half_snake(const float *in, float *out, const float *alpha, size_t channels, size_t length,
+                        size_t snake_channels, int strict, const uint32_t *sin_tab, mb_stream stream);
+/* columns[(i * kernel + k)][t] = in[i][t - (kernel-1-k) * dilation], zero before the start. */
+int mb_codec_im2col(const float *in, float *col, size_t ic, size_t length, size_t kernel, size_t dilation,
+                    mb_stream stream);
 
 /* ---- attention ----------------------------------------------------------- */
 typedef struct {

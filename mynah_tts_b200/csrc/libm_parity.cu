@@ -1,5 +1,5 @@
 // Builds the libm correction tables described in libm_parity.cuh: the host
-// hands over its own expf/tanhf results for a run of consecutive float bit
+// hands over its own expf/tanhf/sinf results for a run of consecutive float bit
 // patterns, the device compares them with its base values and packs the
 // differences, 4 bits each.
 #include "common.cuh"
@@ -10,7 +10,7 @@ namespace {
 
 // Thread t packs values [8t, 8t+8) of this run into one table word.
 __global__ void k_libm_delta(const float *__restrict__ host_vals, uint32_t first_bits, size_t count,
-                             int is_exp, uint32_t *__restrict__ table_words, int *__restrict__ status) {
+                             int kind, uint32_t *__restrict__ table_words, int *__restrict__ status) {
     const size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (t * 8 >= count) return;
     uint32_t word = 0;
@@ -19,7 +19,8 @@ __global__ void k_libm_delta(const float *__restrict__ host_vals, uint32_t first
         if (i >= count) break;
         const float a = __int_as_float((int)(first_bits + (uint32_t)i));
         const uint32_t bits = first_bits + (uint32_t)i;
-        const float base = is_exp ? mb_exp_base(a, bits, true) : mb_tanh_base(a, bits, true);
+        const float base = kind == MB_LIBM_EXP ? mb_exp_base(a, bits, true)
+                           : kind == MB_LIBM_SIN ? mb_sin_base(a) : mb_tanh_base(a, bits, true);
         const int delta = __float_as_int(host_vals[i]) - __float_as_int(base);
         if (delta < -8 || delta > 7) {
             atomicOr(status, 4);   // the table format cannot express this libm
@@ -32,11 +33,11 @@ __global__ void k_libm_delta(const float *__restrict__ host_vals, uint32_t first
 
 }  // namespace
 
-extern "C" int mb_libm_delta(const float *host_vals_dev, uint32_t first_bits, size_t count, int is_exp,
+extern "C" int mb_libm_delta(const float *host_vals_dev, uint32_t first_bits, size_t count, int kind,
                              uint32_t *table_words, int *status, mb_stream stream) {
     if (count == 0 || (count % 8u) != 0) return (int)cudaErrorInvalidValue;
     const size_t threads = count / 8;
     k_libm_delta<<<(unsigned)((threads + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
-        host_vals_dev, first_bits, count, is_exp, table_words, status);
+        host_vals_dev, first_bits, count, kind, table_words, status);
     return mb_check_launch();
 }

@@ -1,4 +1,4 @@
-// Bit-for-bit reproduction of the HOST libm's expf and tanhf on the device.
+// Bit-for-bit reproduction of the HOST libm's expf, tanhf and sinf on the device.
 //
 // The reference's decode step calls libm's expf (softmax, src/graph.c:3195) and
 // tanhf (GELU, src/kernels.c:382-389).  Neither is correctly rounded, so no
@@ -32,6 +32,13 @@
 // expf arguments from here on (results below 2^-92) keep the double-precision base: the
 // single-precision function is not held to a few ulp among denormal results
 #define MB_EXP_FLOAT_HI_BITS 0x42800000u   // 64
+// sinf (the codec's Snake activation, src/backend.c:643-658): below 2^-12 the host returns its
+// argument, which is also the correctly rounded value; the table covers 2^-12 .. 64
+#define MB_SIN_LO_BITS 0x39800000u    // 2^-12
+#define MB_SIN_HI_BITS 0x42800000u    // 64
+#define MB_LIBM_TANH 0
+#define MB_LIBM_EXP 1
+#define MB_LIBM_SIN 2
 
 
 #ifdef __CUDACC__
@@ -42,10 +49,11 @@ __device__ __forceinline__ float mb_tanh_base(float a, uint32_t bits, bool have_
 __device__ __forceinline__ float mb_exp_base(float a, uint32_t bits, bool have_tab) {   // exp(-a), a >= 0
     return (have_tab && bits >= MB_EXP_LO_BITS && bits < MB_EXP_FLOAT_HI_BITS) ? expf(-a) : (float)exp(-(double)a);
 }
+__device__ __forceinline__ float mb_sin_base(float a) { return (float)sin((double)a); }   // a >= 0
 __device__ __forceinline__ float mb_apply_nibble(float base, uint32_t word, uint32_t idx) {
     const uint32_t d = (word >> ((idx & 7u) * 4u)) & 15u;
     const int delta = (int)(d ^ 8u) - 8;   // sign-extend the nibble
-    return __int_as_float(__float_as_int(base) + delta);   // base >= 0 here
+    return __int_as_float(__float_as_int(base) + delta);   // raw bit patterns, as the builder subtracts them
 }
 
 // tanhf as the host computes it (tables present) or correctly rounded (absent).
@@ -73,6 +81,17 @@ __device__ __forceinline__ float mb_tanhf_host_with(float x, uint32_t word, bool
     float r = mb_tanh_base(a, bits, have_tab);
     if (have_tab && bits >= MB_TANH_LO_BITS && bits < MB_TANH_HI_BITS) r = mb_apply_nibble(r, word, bits - MB_TANH_LO_BITS);
     return copysignf(r, x);
+}
+
+// sinf as the host computes it (table present) or correctly rounded (absent).  The table
+// holds host - base as a difference of raw bit patterns, whatever the base's sign.
+__device__ __forceinline__ float mb_sinf_host(float x, const uint32_t *tab) {
+    const float a = fabsf(x);
+    const uint32_t bits = (uint32_t)__float_as_int(a);
+    float r = mb_sin_base(a);
+    if (tab != nullptr && bits >= MB_SIN_LO_BITS && bits < MB_SIN_HI_BITS)
+        r = mb_apply_nibble(r, __ldg(tab + ((bits - MB_SIN_LO_BITS) >> 3)), bits - MB_SIN_LO_BITS);
+    return x < 0.0f ? -r : r;
 }
 
 // expf(x) for x <= 0 as the host computes it.
