@@ -261,6 +261,61 @@ def local_generate_extra(backend, streams: int, args) -> dict:
     return out
 
 
+def frontend_extra(device: int) -> dict:
+    """The two ends of a request around the decoder loop: the text encoder (encode_text, 6 layers
+    x 768, 128 ids) and the codec decoder (decode_codec at the reference's fixed size, 256 frames =
+    11.9 s of audio), both modes, with the CPU code beside them on a bounded sample."""
+    import ctypes as C
+    from mynah_tts_b200.backend import Backend, Codec, TextEncoder
+    out = {}
+    eshape = synth.EncoderShape()
+    etensors = synth.add_encoder(None, eshape, seed=SEED)
+    ids = np.random.default_rng([SEED, 0x696473]).integers(0, eshape.vocab, size=128).astype(np.int32)
+    cshape = synth.CodecShape()
+    ctensors = synth.add_codec(None, cshape, seed=SEED)
+    frames = 256
+    codes = synth.make_codec_codes(cshape, SEED, frames)
+    flop = 0.0          # multiply-adds of the codec's convolutions per frame, x2
+    ch, length = cshape.base, 1
+    flop += 2.0 * cshape.base * cshape.latent * 7
+    for rate in cshape.rates:
+        ch, length = ch // 2, length * rate
+        flop += 2.0 * ch * 4 * length + 2.0 * 2 * 3 * sum(cshape.kernels) * ch * ch * length
+    flop += 2.0 * ch * 3 * length
+    enc = {"ids": 128, "shape": "6 layers x 768, 12 heads, kernel-3 causal convolution feed-forward, f32"}
+    cod = {"frames": frames, "audio_s": frames / FRAME_RATE, "gflop_per_frame": flop / 1e9,
+           "shape": "base 864, rates 8/8/4/2/2, f32; strict keeps one sequential f32 sum per output sample and "
+                    "the host libm's sinf bits (bit-identical samples), fast contracts to FMAs"}
+    for mode in ("strict", "fast"):
+        be = Backend("int8", strict=mode == "strict", device=device)
+        te = TextEncoder(be, etensors, eshape)
+        te.encode(ids)
+        t0 = time.perf_counter()
+        for _ in range(3):
+            te.encode(ids)
+        enc[mode + "_ms"] = (time.perf_counter() - t0) * 1000.0 / 3
+        te.close()
+        cd = Codec(be, ctensors, cshape, max_frames=frames)
+        ms = cd.time(codes, 3)
+        t0 = time.perf_counter()
+        cd.decode(codes)
+        cod[mode] = {"device_ms": ms, "tflops": flop * frames / (ms * 1e-3) / 1e12, "x_realtime": frames / FRAME_RATE / (ms * 1e-3),
+                     "host_call_ms": (time.perf_counter() - t0) * 1000.0}
+        cd.close(); be.close()
+    # CPU beside it: the restatement (pinned bit for bit against the reference) on one core
+    from oracle import oracle as O
+    t0 = time.perf_counter()
+    O.Port.get().encode_text(etensors, eshape, ids[:32])
+    enc["cpu_port_ms_32_ids"] = (time.perf_counter() - t0) * 1000.0
+    t0 = time.perf_counter()
+    O.Port.get().codec_decode(ctensors, cshape, codes[:, :2])
+    cod["cpu_port_ms_per_frame"] = (time.perf_counter() - t0) * 1000.0 / 2
+    cod["cpu_note"] = "scalar restatement of decode_codec, one core, 2 frames"
+    out["text_encoder"] = enc
+    out["codec"] = cod
+    return out
+
+
 def ragged_int4_extra(shape, model, device: int, streams: int) -> dict:
     """int4 (group 32) weights, `streams` greedy streams whose lengths are uniform in
     [128, 1024] from the seed; a stream leaves the batch at its length.  Aggregate frames/s
@@ -426,7 +481,7 @@ def main():
     ap.add_argument("--cpu-frames", type=int, default=24, help="frames of the CPU baseline sample")
     ap.add_argument("--no-extras", action="store_true", help="only the headline job (no other mode, batch-1, "
                     "matrix-pool, partition sweep, f32 step, sampled loop, ragged int4, CPU baseline)")
-    ap.add_argument("--only", default="", choices=["", "gemv_pool", "batch1"],
+    ap.add_argument("--only", default="", choices=["", "gemv_pool", "batch1", "frontend", "codec"],
                     help="profiling aid: run only this small case (a few launches, no JSON contract)")
     ap.add_argument("--start-position", type=int, default=0,
                     help="profiling aid: every job starts with this many (zero) rows already in each "
@@ -483,6 +538,18 @@ def main():
         pool.close(); dx.free(); dy.free()
         return out
 
+    if args.only == "frontend":
+        print(json.dumps({"frontend": frontend_extra(local_rank)}))
+        return
+    if args.only == "codec":          # profiling aid: one small decode (64 frames) in the chosen mode
+        from mynah_tts_b200.backend import Codec
+        cshape = synth.CodecShape()
+        cbe = Backend("f32", strict=strict, device=local_rank)
+        cd = Codec(cbe, synth.add_codec(None, cshape, seed=SEED), cshape, max_frames=64)
+        samples = cd.decode(synth.make_codec_codes(cshape, SEED, 64))
+        print(json.dumps({"codec": {"frames": 64, "samples": int(samples.size), "rms": float(samples.std())}}))
+        cd.close(); cbe.close()
+        return
     if args.only == "gemv_pool":
         backend = Backend(args.quant, strict=strict, device=local_rank)
         print(json.dumps({"gemv_pool": gemv_pool_case(backend)}))
@@ -711,6 +778,7 @@ def main():
             extras["prefill"] = pre
             extras["generate"] = local_generate_extra(backend, B, args)
             extras["ragged_int4"] = ragged_int4_extra(shape, model, local_rank, B)
+            extras["frontend"] = frontend_extra(local_rank)
         cpu = None
         if world == 1 and not args.no_extras:
             n_cpu, f_cpu, start_cpu = reference_sample(args)
