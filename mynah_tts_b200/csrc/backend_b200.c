@@ -340,6 +340,7 @@ int mynah_b200_open(void **state, int device, int quant, int strict, char *error
         mb_cuda(mb_gemm_tc_init(), "kernel attributes (tensor-core product)", error, cap) != 0 ||
         mb_cuda(mb_gemm_tc_f16_init(), "kernel attributes (f16 tensor-core product)", error, cap) != 0 ||
         mb_cuda(mb_cross_block_init(), "kernel attributes (cross-attention block)", error, cap) != 0 ||
+        mb_cuda(mb_codec_tc_init(), "kernel attributes (codec tensor-core convolution)", error, cap) != 0 ||
         mb_cuda((int)cudaMalloc((void **)&st->d_token, sizeof(unsigned)), "cudaMalloc", error, cap) != 0 ||
         mb_cuda((int)cudaMalloc((void **)&st->d_status, sizeof(int)), "cudaMalloc", error, cap) != 0 ||
         mb_cuda((int)cudaMemset(st->d_status, 0, sizeof(int)), "cudaMemset", error, cap) != 0) {

@@ -8,7 +8,9 @@
  * convolution's epilogue: the Snake in front of the next convolution, the residual add, the
  * sum of the three branches with its division by three, the next stage's activation, the clip.
  * A residual layer is then 21 launches (3 x (Snake + 6 convolutions)) instead of the 57
- * calls of res_layer_device (src/graph.c:2423-2509).
+ * calls of res_layer_device (src/graph.c:2423-2509).  In fast mode the 90 residual-layer
+ * convolutions run on the tensor cores (codec_tc.cu) over f16 hi/lo planes that the
+ * epilogues write for one another; strict mode keeps the sequential f32 sums of codec.cu.
  *
  * Convolution weights are repacked once at create ([in * kernel][groups of 7 output
  * channels][8]) so that a CTA's tile is a run of 16-byte copies; everything stays f32.
@@ -16,6 +18,7 @@
 #include "host_common.h"
 #include "../../include/mynah_b200.h"
 
+#include <math.h>
 #include <stdlib.h>
 #include <string.h>
 
@@ -26,6 +29,8 @@ static const size_t codec_dilations[CODEC_BLOCKS] = {1u, 3u, 5u};
 
 typedef struct {
     float *w, *bias;          /* packed weights, bias */
+    void *w_tc;               /* tensor-core layout (fast mode), or NULL */
+    float scale;              /* power of two the tensor-core weights carry */
 } dev_conv;
 
 typedef struct {
@@ -48,6 +53,9 @@ typedef struct {
     /* activations */
     unsigned *d_codes;
     float *latent, *a, *up, *cur, *act, *res, *audio;
+    int use_tc;               /* fast mode: residual-layer convolutions on the tensor cores */
+    void *act_planes, *res_planes;   /* f16 hi/lo planes [2][length][cp] of the widest stage */
+    size_t plane_halves;
     unsigned *h_codes;   /* pinned */
     float *h_audio;      /* pinned */
     float *staging;      /* device scratch for weight uploads */
@@ -70,7 +78,7 @@ static int c_upload(float **dst, const float *host, size_t n, char *error, size_
 
 /* [oc][ic][kernel] host weights -> packed device weights. */
 static int c_conv(mb_codec *c, dev_conv *dst, const float *host_w, const float *host_b, size_t oc, size_t ic,
-                  size_t kernel, char *error, size_t cap) {
+                  size_t kernel, int tensor_core, char *error, size_t cap) {
     if (host_w == NULL || host_b == NULL) {
         mb_set_error(error, cap, "codec tensor is missing");
         return -1;
@@ -86,8 +94,28 @@ static int c_conv(mb_codec *c, dev_conv *dst, const float *host_w, const float *
     if (c_malloc((void **)&dst->w, mb_codec_conv_packed_floats(oc, ic, kernel) * sizeof(float), error, cap) != 0) return -1;
     MB_TRY(cudaMemcpyAsync(c->staging, host_w, n * sizeof(float), cudaMemcpyHostToDevice, c->st->stream), "upload weight");
     MB_TRY(mb_codec_pack_conv_weight(c->staging, dst->w, oc, ic, kernel, c->st->stream), "pack weight");
-    MB_TRY(cudaStreamSynchronize(c->st->stream), "cudaStreamSynchronize");    /* host_w may be pageable; staging is reused */
     c->st->launches += 1u;
+    if (c->use_tc && tensor_core) {
+        /* a power of two that brings the largest weight just under 2^14: the f16 lo halves
+         * of all but the smallest weights are then normal numbers */
+        float amax = 0.0f;
+        for (size_t i = 0; i < n; ++i) {
+            const float v = fabsf(host_w[i]);
+            if (v > amax) amax = v;
+        }
+        int e = 0;
+        if (amax > 0.0f) {
+            (void)frexpf(amax, &e);          /* amax = f * 2^e, 0.5 <= f < 1 */
+            e = 14 - e;
+        }
+        if (e > 30) e = 30;
+        if (e < -30) e = -30;
+        dst->scale = ldexpf(1.0f, e);
+        if (c_malloc(&dst->w_tc, mb_codec_tc_packed_halves(oc, ic, kernel) * 2u, error, cap) != 0) return -1;
+        MB_TRY(mb_codec_tc_pack_weight(c->staging, dst->w_tc, oc, ic, kernel, dst->scale, c->st->stream), "pack weight");
+        c->st->launches += 1u;
+    }
+    MB_TRY(cudaStreamSynchronize(c->st->stream), "cudaStreamSynchronize");    /* host_w may be pageable; staging is reused */
     return c_upload(&dst->bias, host_b, oc, error, cap);
 }
 
@@ -104,11 +132,11 @@ void mynah_b200_codec_destroy(void *codec) {
             for (size_t d = 0; d < CODEC_BLOCKS; ++d) {
                 dev_block *B = &S->block[b][d];
                 cudaFree(B->in_alpha); cudaFree(B->skip_alpha);
-                cudaFree(B->in_conv.w); cudaFree(B->in_conv.bias);
-                cudaFree(B->skip_conv.w); cudaFree(B->skip_conv.bias);
+                cudaFree(B->in_conv.w); cudaFree(B->in_conv.bias); cudaFree(B->in_conv.w_tc);
+                cudaFree(B->skip_conv.w); cudaFree(B->skip_conv.bias); cudaFree(B->skip_conv.w_tc);
             }
     }
-    void *dev[] = {c->d_codes, c->latent, c->a, c->up, c->cur, c->act, c->res, c->audio, c->staging};
+    void *dev[] = {c->d_codes, c->latent, c->a, c->up, c->cur, c->act, c->res, c->audio, c->staging, c->act_planes, c->res_planes};
     for (size_t i = 0; i < sizeof(dev) / sizeof(dev[0]); ++i) cudaFree(dev[i]);
     if (c->h_codes != NULL) cudaFreeHost(c->h_codes);
     if (c->h_audio != NULL) cudaFreeHost(c->h_audio);
@@ -142,9 +170,13 @@ int mynah_b200_codec_create(void *state, const mynah_b200_codec_desc *desc, void
     c->base = desc->base;
     c->max_frames = desc->max_frames;
     c->sin_tab = mb_libm_sin_table(st);
+    {
+        const char *no_tc = getenv("MYNAH_B200_NO_TC");
+        c->use_tc = !st->strict && !(no_tc != NULL && strcmp(no_tc, "0") != 0);
+    }
     int ok = 1;
 #define C_TRY(expr) do { if (ok && (expr) != 0) ok = 0; } while (0)
-    C_TRY(c_conv(c, &c->pre, desc->pre_w, desc->pre_b, c->base, CODEC_LATENT, 7u, error, cap));
+    C_TRY(c_conv(c, &c->pre, desc->pre_w, desc->pre_b, c->base, CODEC_LATENT, 7u, 0, error, cap));
     size_t ch = c->base;
     for (size_t s = 0; ok && s < CODEC_STAGES; ++s) {
         const mynah_b200_codec_stage *S = &desc->stage[s];
@@ -159,13 +191,13 @@ int mynah_b200_codec_create(void *state, const mynah_b200_codec_desc *desc, void
                 dev_block *DB = &D->block[b][d];
                 C_TRY(c_upload(&DB->in_alpha, B->in_alpha, nch, error, cap));
                 C_TRY(c_upload(&DB->skip_alpha, B->skip_alpha, nch, error, cap));
-                C_TRY(c_conv(c, &DB->in_conv, B->in_w, B->in_b, nch, nch, codec_kernels[b], error, cap));
-                C_TRY(c_conv(c, &DB->skip_conv, B->skip_w, B->skip_b, nch, nch, codec_kernels[b], error, cap));
+                C_TRY(c_conv(c, &DB->in_conv, B->in_w, B->in_b, nch, nch, codec_kernels[b], 1, error, cap));
+                C_TRY(c_conv(c, &DB->skip_conv, B->skip_w, B->skip_b, nch, nch, codec_kernels[b], 1, error, cap));
             }
         ch = nch;
     }
     C_TRY(c_upload(&c->post_alpha, desc->post_alpha, ch, error, cap));
-    C_TRY(c_conv(c, &c->post, desc->post_w, desc->post_b, 1u, ch, 3u, error, cap));
+    C_TRY(c_conv(c, &c->post, desc->post_w, desc->post_b, 1u, ch, 3u, 0, error, cap));
     /* the widest activation: stages 2..4 hold base * 32 floats per frame */
     const size_t T = c->max_frames, act_floats = c->base * 32u * T, samples = mynah_b200_codec_samples_per_frame() * T;
     C_TRY(c_malloc((void **)&c->d_codes, CODEC_GROUPS * T * sizeof(unsigned), error, cap));
@@ -176,6 +208,21 @@ int mynah_b200_codec_create(void *state, const mynah_b200_codec_desc *desc, void
     C_TRY(c_malloc((void **)&c->act, act_floats * sizeof(float), error, cap));
     C_TRY(c_malloc((void **)&c->res, act_floats * sizeof(float), error, cap));
     C_TRY(c_malloc((void **)&c->audio, samples * sizeof(float), error, cap));
+    if (c->use_tc) {
+        /* the widest plane: the last stage, 1024 times per frame x its channels rounded up to 64 */
+        size_t widest = 0, pch = c->base, plen = T;
+        for (size_t s = 0; s < CODEC_STAGES; ++s) {
+            pch /= 2u;
+            plen *= codec_rates[s];
+            const size_t cp = (pch + 63u) / 64u * 64u;
+            if (plen * cp > widest) widest = plen * cp;
+        }
+        c->plane_halves = widest;
+        C_TRY(c_malloc(&c->act_planes, 2u * widest * 2u, error, cap));
+        C_TRY(c_malloc(&c->res_planes, 2u * widest * 2u, error, cap));
+        if (ok) C_TRY(mb_cuda((int)cudaMemset(c->act_planes, 0, 2u * widest * 2u), "cudaMemset", error, cap));
+        if (ok) C_TRY(mb_cuda((int)cudaMemset(c->res_planes, 0, 2u * widest * 2u), "cudaMemset", error, cap));
+    }
     C_TRY(mb_cuda((int)cudaMallocHost((void **)&c->h_codes, CODEC_GROUPS * T * sizeof(unsigned)), "cudaMallocHost", error, cap));
     C_TRY(mb_cuda((int)cudaMallocHost((void **)&c->h_audio, samples * sizeof(float)), "cudaMallocHost", error, cap));
 #undef C_TRY
@@ -232,7 +279,40 @@ static int codec_enqueue(mb_codec *c, size_t frames, int stop_after, size_t *res
         R_TRY(mb_codec_conv_transpose(c->a, D->up_w, D->up_b, c->up, ch, nch, len, codec_rates[si], st->strict, s));
         const int raw_stage_out = stop_after == 2 + (int)si;
         const float *next_alpha = raw_stage_out ? NULL : (si + 1u < CODEC_STAGES ? c->stage[si + 1u].alpha : c->post_alpha);
-        for (size_t b = 0; b < CODEC_BRANCHES && rc == 0; ++b) {
+        for (size_t b = 0; c->use_tc && b < CODEC_BRANCHES && rc == 0; ++b) {
+            /* tensor-core form: the activations between convolutions are f16 hi/lo planes */
+            const size_t cp = (nch + 63u) / 64u * 64u, pstride = nlen * cp;
+            unsigned short *actp = (unsigned short *)c->act_planes, *resp = (unsigned short *)c->res_planes;
+            R_TRY(mb_codec_snake_planes(c->up, D->block[b][0].in_alpha, actp, actp + pstride, nch, nlen, s));
+            for (size_t d = 0; d < CODEC_BLOCKS && rc == 0; ++d) {
+                const dev_block *B = &D->block[b][d];
+                mb_codec_conv_tc_args t;
+                memset(&t, 0, sizeof(t));
+                t.x_planes = actp; t.x_plane_stride = pstride;
+                t.w_packed = B->in_conv.w_tc; t.scale = B->in_conv.scale; t.bias = B->in_conv.bias;
+                t.alpha = B->skip_alpha; t.act_planes = resp; t.act_plane_stride = pstride;
+                t.ic = nch; t.oc = nch; t.length = nlen; t.kernel = codec_kernels[b]; t.dilation = codec_dilations[d];
+                t.status = st->d_status;
+                R_TRY(mb_codec_conv1d_tc(&t, s));
+                memset(&t, 0, sizeof(t));
+                t.x_planes = resp; t.x_plane_stride = pstride;
+                t.w_packed = B->skip_conv.w_tc; t.scale = B->skip_conv.scale; t.bias = B->skip_conv.bias;
+                t.res = d == 0 ? c->up : c->cur;
+                t.ic = nch; t.oc = nch; t.length = nlen; t.kernel = codec_kernels[b]; t.dilation = 1u;
+                t.status = st->d_status;
+                if (d + 1u < CODEC_BLOCKS) {
+                    t.out = c->cur;
+                    t.alpha = D->block[b][d + 1u].in_alpha;
+                    t.act_planes = actp; t.act_plane_stride = pstride;
+                } else {
+                    t.acc = c->a;
+                    t.acc_mode = b == 0 ? 1 : (b + 1u < CODEC_BRANCHES ? 2 : 3);
+                    t.alpha2 = next_alpha;
+                }
+                R_TRY(mb_codec_conv1d_tc(&t, s));
+            }
+        }
+        for (size_t b = 0; !c->use_tc && b < CODEC_BRANCHES && rc == 0; ++b) {
             R_TRY(mb_codec_half_snake(c->up, c->act, D->block[b][0].in_alpha, nch, nlen, nch / 2u, st->strict, c->sin_tab, s));
             for (size_t d = 0; d < CODEC_BLOCKS && rc == 0; ++d) {
                 const dev_block *B = &D->block[b][d];
@@ -303,6 +383,15 @@ static int codec_run(mb_codec *c, const unsigned *codes, size_t frames, int stop
     } else {
         MB_TRY(cudaMemcpyAsync(out, result, n * sizeof(float), cudaMemcpyDeviceToHost, st->stream), "read activations");
         MB_TRY(cudaStreamSynchronize(st->stream), "cudaStreamSynchronize");
+    }
+    if (c->use_tc) {
+        int status = 0;
+        MB_TRY(cudaMemcpy(&status, st->d_status, sizeof(int), cudaMemcpyDeviceToHost), "read status");
+        if (status != 0) {
+            cudaMemset(st->d_status, 0, sizeof(int));
+            mb_set_error(error, cap, mb_status_message(status));
+            return -1;
+        }
     }
     if (count != NULL) *count = n;
     mb_clear_error(error, cap);

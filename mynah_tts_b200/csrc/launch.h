@@ -217,6 +217,38 @@ int mb_codec_half_snake(const float *in, float *out, const float *alpha, size_t 
 int mb_codec_im2col(const float *in, float *col, size_t ic, size_t length, size_t kernel, size_t dilation,
                     mb_stream stream);
 
+/* The same convolution on tcgen05 tensor cores (codec_tc.cu), fast mode: operands are f16
+ * hi/lo planes, channels contiguous.  x_planes: [2][length][cp_in] halves (plane stride
+ * x_plane_stride halves), cp = channels rounded up to 64, pad columns zero or finite under
+ * zero weights.  act_planes receive half-Snake(v) in the same layout for the next convolution. */
+typedef struct {
+    const void *x_planes;
+    size_t x_plane_stride;
+    const void *w_packed;     /* mb_codec_tc_pack_weight's layout */
+    float scale;              /* the power of two the packed weights carry */
+    const float *bias;
+    const float *res;
+    float *out;
+    const float *alpha;
+    void *act_planes;
+    size_t act_plane_stride;
+    float *acc;
+    const float *alpha2;
+    size_t ic, oc, length, kernel, dilation;
+    int acc_mode;
+    int *status;              /* device status word: bits 8 / 16 on a bounded wait running out */
+} mb_codec_conv_tc_args;
+int mb_codec_tc_init(void);
+void mb_codec_tc_shape(size_t oc, size_t *n_tile, size_t *tiles, size_t *cp);
+size_t mb_codec_tc_packed_halves(size_t oc, size_t ic, size_t kernel);
+/* [oc][ic][kernel] f32 (device) -> f16 hi/lo planes of scale * w in the tensor-core layout. */
+int mb_codec_tc_pack_weight(const float *w, void *packed, size_t oc, size_t ic, size_t kernel, float scale,
+                            mb_stream stream);
+/* f32 [channels][length] -> half-Snake -> f16 hi/lo planes [length][cp]. */
+int mb_codec_snake_planes(const float *in, const float *alpha, void *hi, void *lo, size_t channels, size_t length,
+                          mb_stream stream);
+int mb_codec_conv1d_tc(const mb_codec_conv_tc_args *args, mb_stream stream);
+
 /* ---- attention ----------------------------------------------------------- */
 typedef struct {
     const float *q;       /* [batch][q_stride], head h at h*head_width */
