@@ -22,8 +22,8 @@
 //
 // One CTA = 128 times x N output channels (N <= 112, a multiple of 16) through a ring of
 // stages of { X hi, X lo: 16 KB each; W hi, W lo: N x 128 B each }, each filled by two TMA
-// copies; one thread issues 12 tcgen05.mma (M128 N K16) per stage; the four warps read their
-// 32 accumulator rows with tcgen05.ld and run the same epilogue as the SIMT kernel (bias,
+// copies; one thread issues 12 tcgen05.mma (M128 N K16) per stage; sixteen warps (four per 32
+// accumulator rows, each a quarter of the columns) read them with tcgen05.ld and run the same epilogue as the SIMT kernel (bias,
 // residual, half-Snake copy for the next convolution, branch sum).  Every wait is bounded
 // (status bits 8 and 16).
 #include "common.cuh"
@@ -37,7 +37,7 @@
 
 namespace {
 
-constexpr int CT_THREADS = 128;
+constexpr int CT_THREADS = 512;            // 16 warps: warp w reads accumulator rows 32 (w % 4) .. +31, column groups w / 4, w / 4 + 4, ..
 constexpr int CT_TM = 128;                 // times per tile
 constexpr int CT_KC = 128;                 // bytes of channels per stage row: 64 halves
 constexpr int CT_A_BYTES = CT_TM * CT_KC;  // one plane of the activation tile
@@ -168,13 +168,24 @@ k_conv1d_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
         if (threadIdx.x == 0)
             for (int s = 0; s < S && s < nsteps; ++s) bar_wait(&full_bar[s], 0u, TC_SPIN >> 4);
     } else {
-        const int t = t0 + warp * 32 + lane;
+        const int quad = warp & 3;
+        const int t = t0 + quad * 32 + lane;
         const bool t_ok = t < p.L;
         const int snake_ch = p.oc / 2;
-        for (int g = 0; g < N / 16; ++g) {
+        for (int g = warp >> 2; g < N / 16; g += CT_THREADS / 128) {
             float v[16];
-            tmem_ld16f(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(g * 16), v);
+            tmem_ld16f(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)(g * 16), v);
             const int o0 = ntile * N + g * 16;
+            // every global read of the group first (the pointers may alias, so the compiler
+            // would otherwise keep each read behind the previous column's store)
+            float r[16], s[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const bool ok = t_ok && o0 + j < p.oc;
+                const size_t at = (size_t)(o0 + j) * p.L + t;
+                r[j] = (ok && p.res != nullptr) ? p.res[at] : 0.0f;
+                s[j] = (ok && p.acc_mode >= 2) ? p.acc[at] : 0.0f;
+            }
             __align__(16) __half hi[16], lo[16];
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
@@ -182,16 +193,15 @@ k_conv1d_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
                 float a = 0.0f;
                 if (o < p.oc && t_ok) {
                     const size_t at = (size_t)o * p.L + t;
-                    float y = v[j] * p.inv_scale + p.bias[o];
-                    if (p.res != nullptr) y = p.res[at] + y;
+                    const float y = r[j] + (v[j] * p.inv_scale + p.bias[o]);
                     if (p.out != nullptr) p.out[at] = y;
                     if (p.alpha != nullptr) a = snake_fast(y, o, snake_ch, p.alpha);
                     if (p.acc_mode == 1) {
                         p.acc[at] = y;
                     } else if (p.acc_mode == 2) {
-                        p.acc[at] = p.acc[at] + y;
+                        p.acc[at] = s[j] + y;
                     } else if (p.acc_mode == 3) {
-                        float s3 = (p.acc[at] + y) / 3.0f;
+                        float s3 = (s[j] + y) / 3.0f;
                         if (p.alpha2 != nullptr) s3 = snake_fast(s3, o, snake_ch, p.alpha2);
                         p.acc[at] = s3;
                     }
