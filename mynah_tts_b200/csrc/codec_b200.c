@@ -36,6 +36,7 @@ typedef struct {
 typedef struct {
     float *in_alpha, *skip_alpha;
     dev_conv in_conv, skip_conv;
+    float *in_table, *skip_table;   /* tensor-core epilogue constants per output channel */
 } dev_block;
 
 typedef struct {
@@ -131,7 +132,7 @@ void mynah_b200_codec_destroy(void *codec) {
         for (size_t b = 0; b < CODEC_BRANCHES; ++b)
             for (size_t d = 0; d < CODEC_BLOCKS; ++d) {
                 dev_block *B = &S->block[b][d];
-                cudaFree(B->in_alpha); cudaFree(B->skip_alpha);
+                cudaFree(B->in_alpha); cudaFree(B->skip_alpha); cudaFree(B->in_table); cudaFree(B->skip_table);
                 cudaFree(B->in_conv.w); cudaFree(B->in_conv.bias); cudaFree(B->in_conv.w_tc);
                 cudaFree(B->skip_conv.w); cudaFree(B->skip_conv.bias); cudaFree(B->skip_conv.w_tc);
             }
@@ -197,6 +198,23 @@ int mynah_b200_codec_create(void *state, const mynah_b200_codec_desc *desc, void
         ch = nch;
     }
     C_TRY(c_upload(&c->post_alpha, desc->post_alpha, ch, error, cap));
+    /* epilogue constants of the tensor-core convolutions: the first convolution of a block is
+     * followed by the block's skip activation; the second by the next block's input activation,
+     * or, as the last of its branch, by the next stage's activation on the finished sum */
+    for (size_t s = 0, tch = c->base / 2u; ok && c->use_tc && s < CODEC_STAGES; ++s, tch /= 2u)
+        for (size_t b = 0; ok && b < CODEC_BRANCHES; ++b)
+            for (size_t d = 0; ok && d < CODEC_BLOCKS; ++d) {
+                dev_block *DB = &c->stage[s].block[b][d];
+                const float *after = d + 1u < CODEC_BLOCKS ? c->stage[s].block[b][d + 1u].in_alpha : NULL;
+                const float *next_stage = s + 1u < CODEC_STAGES ? c->stage[s + 1u].alpha : c->post_alpha;
+                C_TRY(c_malloc((void **)&DB->in_table, tch * 4u * sizeof(float), error, cap));
+                C_TRY(c_malloc((void **)&DB->skip_table, tch * 4u * sizeof(float), error, cap));
+                if (ok) C_TRY(mb_cuda(mb_codec_tc_channel_table(DB->in_conv.bias, DB->skip_alpha, NULL, DB->in_table, tch, st->stream),
+                                      "channel table", error, cap));
+                if (ok) C_TRY(mb_cuda(mb_codec_tc_channel_table(DB->skip_conv.bias, after, d + 1u < CODEC_BLOCKS ? NULL : next_stage,
+                                                                DB->skip_table, tch, st->stream), "channel table", error, cap));
+            }
+    if (ok && c->use_tc) C_TRY(mb_cuda((int)cudaStreamSynchronize(st->stream), "cudaStreamSynchronize", error, cap));
     C_TRY(c_conv(c, &c->post, desc->post_w, desc->post_b, 1u, ch, 3u, 0, error, cap));
     /* the widest activation: stages 2..4 hold base * 32 floats per frame */
     const size_t T = c->max_frames, act_floats = c->base * 32u * T, samples = mynah_b200_codec_samples_per_frame() * T;
@@ -289,25 +307,25 @@ static int codec_enqueue(mb_codec *c, size_t frames, int stop_after, size_t *res
                 mb_codec_conv_tc_args t;
                 memset(&t, 0, sizeof(t));
                 t.x_planes = actp; t.x_plane_stride = pstride;
-                t.w_packed = B->in_conv.w_tc; t.scale = B->in_conv.scale; t.bias = B->in_conv.bias;
-                t.alpha = B->skip_alpha; t.act_planes = resp; t.act_plane_stride = pstride;
+                t.w_packed = B->in_conv.w_tc; t.scale = B->in_conv.scale; t.channel_table = B->in_table;
+                t.has_alpha = 1; t.act_planes = resp; t.act_plane_stride = pstride;
                 t.ic = nch; t.oc = nch; t.length = nlen; t.kernel = codec_kernels[b]; t.dilation = codec_dilations[d];
                 t.status = st->d_status;
                 R_TRY(mb_codec_conv1d_tc(&t, s));
                 memset(&t, 0, sizeof(t));
                 t.x_planes = resp; t.x_plane_stride = pstride;
-                t.w_packed = B->skip_conv.w_tc; t.scale = B->skip_conv.scale; t.bias = B->skip_conv.bias;
+                t.w_packed = B->skip_conv.w_tc; t.scale = B->skip_conv.scale; t.channel_table = B->skip_table;
                 t.res = d == 0 ? c->up : c->cur;
                 t.ic = nch; t.oc = nch; t.length = nlen; t.kernel = codec_kernels[b]; t.dilation = 1u;
                 t.status = st->d_status;
                 if (d + 1u < CODEC_BLOCKS) {
                     t.out = c->cur;
-                    t.alpha = D->block[b][d + 1u].in_alpha;
+                    t.has_alpha = 1;
                     t.act_planes = actp; t.act_plane_stride = pstride;
                 } else {
                     t.acc = c->a;
                     t.acc_mode = b == 0 ? 1 : (b + 1u < CODEC_BRANCHES ? 2 : 3);
-                    t.alpha2 = next_alpha;
+                    t.has_alpha2 = next_alpha != NULL;
                 }
                 R_TRY(mb_codec_conv1d_tc(&t, s));
             }

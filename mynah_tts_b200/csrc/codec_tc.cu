@@ -4,10 +4,14 @@
 //
 //   out[o][t] = bias[o] + sum_k sum_i W[o][i][k] * x[i][t - (K-1-k) * dilation]
 //
-// is one accumulation over (tap k, channel chunk) of products  X_k [128 times x 64 channels]
+// is one accumulation over (channel chunk, tap k) of products  X_k [128 times x 64 channels]
 // . W_k^T [64 channels x N output channels]: the tile of X for tap k is the same channel-major
-// slab of the activation shifted by the tap's delay, so TMA fetches it at row t0 - delay and
-// fills rows before the start of the signal with zeros (the causal padding).  Operands are
+// slab of the activation shifted by the tap's delay.  TMA fetches the slab once per chunk with
+// its halo (rows t0 - (K-1) * dilation .. t0 + 127; rows before the start of the signal arrive
+// as zeros, the causal padding) and every tap's MMA reads it through a descriptor that starts
+// k * dilation rows further down: rows of a 128-byte-swizzled K-major tile lie 128 bytes
+// apart and the swizzle is a function of the shared-memory address, so a descriptor may
+// start at any row of a 1024-byte-aligned buffer (base offset 0).  Operands are
 // f16, so both sides are split in two halves that add up to the f32 value to about 22 bits,
 //   hi = f16(v), lo = f16(v - hi),
 // and three MMAs per K step (hi.hi + lo.hi + hi.lo) accumulate in f32 in tensor memory.  The
@@ -20,9 +24,9 @@
 // [plane][tap][rows = tiles * N][Cp] f16.  Everything else (residual stream, branch sum) stays
 // f32 [channels][time] as in codec.cu.
 //
-// One CTA = 128 times x N output channels (N <= 112, a multiple of 16) through a ring of
-// stages of { X hi, X lo: 16 KB each; W hi, W lo: N x 128 B each }, each filled by two TMA
-// copies; one thread issues 12 tcgen05.mma (M128 N K16) per stage; sixteen warps (four per 32
+// One CTA = 128 times x N output channels (N <= 112, a multiple of 16): two buffers of
+// { X hi, X lo: (128 + halo) x 128 B each } filled once per chunk and a ring of stages of
+// { W hi, W lo: N x 128 B each } filled once per (chunk, tap); one thread issues 12 tcgen05.mma (M128 N K16) per stage; sixteen warps (four per 32
 // accumulator rows, each a quarter of the columns) read them with tcgen05.ld and run the same epilogue as the SIMT kernel (bias,
 // residual, half-Snake copy for the next convolution, branch sum).  Every wait is bounded
 // (status bits 8 and 16).
@@ -40,23 +44,41 @@ namespace {
 constexpr int CT_THREADS = 512;            // 16 warps: warp w reads accumulator rows 32 (w % 4) .. +31, column groups w / 4, w / 4 + 4, ..
 constexpr int CT_TM = 128;                 // times per tile
 constexpr int CT_KC = 128;                 // bytes of channels per stage row: 64 halves
-constexpr int CT_A_BYTES = CT_TM * CT_KC;  // one plane of the activation tile
-constexpr int CT_MAX_STAGES = 6;
+constexpr int CT_MAX_STAGES = 8;           // weight stages
+constexpr int CT_HALO_MAX = 50;            // (kernel - 1) * dilation
 
 struct ConvTcP {
-    const float *bias, *res, *alpha, *alpha2;
+    const float4 *chan;          // per output channel: {bias, alpha, 1 / (alpha + 1e-9), alpha2} (mb_codec_tc_channel_table)
+    const float *res;
+    int has_alpha, has_alpha2;
     float *out, *acc;
     __half *act_hi, *act_lo;     // planes [L][cp_out] of half-Snake(v), or NULL
     int *status;
     float inv_scale;             // 1 / the power of two the weights were scaled by
     int oc, L, K, dil, n_tile, chunks, stages, cp_out, acc_mode;
+    int xrows;                   // 128 + (K - 1) * dil rows per activation tile
+    int x_plane_bytes;           // xrows * 128 rounded up to 1024
+    int xbufs;                   // activation buffers: 2, or 1 where two do not fit beside two weight stages
 };
+
+// Descriptor of a 128-byte-swizzled K-major tile that starts at any 128-byte row of a
+// 1024-byte-aligned buffer that TMA filled: both TMA and the MMA swizzle by address bits,
+// so the base-offset field stays 0 (measured: setting it to the row's phase reads wrong rows).
+__device__ __forceinline__ uint64_t smem_desc_sw128_row(unsigned addr) { return smem_desc_sw128(addr); }
 
 __device__ __forceinline__ float snake_fast(float v, int c, int snake_ch, const float *alpha) {
     if (c < snake_ch) {
         const float a = alpha[c];
         const float sn = sinf(a * v);
         return v + sn * sn * (1.0f / (a + 1e-9f));
+    }
+    return v < 0.0f ? v * 0.01f : v;
+}
+// The same with the channel's constants at hand.
+__device__ __forceinline__ float snake_with(float v, bool snake, float a, float inv_a) {
+    if (snake) {
+        const float sn = sinf(a * v);
+        return fmaf(sn * sn, inv_a, v);
     }
     return v < 0.0f ? v * 0.01f : v;
 }
@@ -68,11 +90,13 @@ __device__ __forceinline__ void tmem_ld16f(uint32_t taddr, float (&v)[16]) {
     for (int i = 0; i < 16; ++i) v[i] = __int_as_float(r[i]);
 }
 
-__global__ void __launch_bounds__(CT_THREADS)
+__global__ void __launch_bounds__(CT_THREADS, 2)
 k_conv1d_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, ConvTcP p) {
     extern __shared__ unsigned char smem_ct[];
     __shared__ __align__(8) unsigned long long full_bar[CT_MAX_STAGES];
     __shared__ __align__(8) unsigned long long empty_bar[CT_MAX_STAGES];
+    __shared__ __align__(8) unsigned long long xfull_bar[2];
+    __shared__ __align__(8) unsigned long long xempty_bar[2];
     __shared__ __align__(8) unsigned long long done_bar;
     __shared__ uint32_t s_tmem;
     __shared__ unsigned s_fail;
@@ -81,15 +105,22 @@ k_conv1d_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
     const int ntile = blockIdx.y;
     const int N = p.n_tile;
     const int b_bytes = N * CT_KC;                           // one plane of the weight tile
-    const unsigned stage_bytes = (unsigned)(2 * CT_A_BYTES + 2 * b_bytes);
-    const int nsteps = p.K * p.chunks;
+    const unsigned w_stage_bytes = (unsigned)(2 * b_bytes);
+    const unsigned x_buf_bytes = (unsigned)(2 * p.x_plane_bytes);
     const int S = p.stages;
+    const int halo = (p.K - 1) * p.dil;
     const uint32_t tmem_cols = N <= 32 ? 32u : (N <= 64 ? 64u : 128u);
     unsigned char *base = smem_ct + ((1024u - (saddr(smem_ct) & 1023u)) & 1023u);
+    unsigned char *xbuf = base;                               // [xbufs][hi plane | lo plane]
+    unsigned char *wring = base + (size_t)p.xbufs * x_buf_bytes;   // [S][hi N x 128 | lo N x 128]
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; ++s) {
             bar_init(&full_bar[s], 1u);
             bar_init(&empty_bar[s], 1u);
+        }
+        for (int s = 0; s < 2; ++s) {
+            bar_init(&xfull_bar[s], 1u);
+            bar_init(&xempty_bar[s], 1u);
         }
         bar_init(&done_bar, 1u);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -105,55 +136,76 @@ k_conv1d_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
     const uint32_t tmem = s_tmem;
     mb_pdl_wait();
     mb_pdl_trigger();
-    // stage s: [X hi 16 KB][X lo 16 KB][W hi N*128][W lo N*128]
-    auto load_step = [&](int c, int s) {
-        const int tap = c / p.chunks, chunk = c - tap * p.chunks;
-        const int delay = (p.K - 1 - tap) * p.dil;
-        unsigned char *dst = base + (size_t)s * stage_bytes;
-        bar_expect(&full_bar[s], stage_bytes);
-        asm volatile(
-            "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
-            "[%0], [%1, {%2, %3, %4}], [%5];" ::"r"(saddr(dst)), "l"(&map_x), "r"(chunk * CT_KC), "r"(t0 - delay), "r"(0),
-            "r"(saddr(&full_bar[s]))
-            : "memory");
-        asm volatile(
-            "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
-            "[%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(saddr(dst + 2 * CT_A_BYTES)), "l"(&map_w), "r"(chunk * CT_KC),
-            "r"(ntile * N), "r"(tap), "r"(0), "r"(saddr(&full_bar[s]))
-            : "memory");
-    };
     if (warp == 0 && lane == 0) {
-        for (int c = 0; c < nsteps; ++c) {
-            const int s = c % S;
-            if (c >= S && !bar_wait(&empty_bar[s], (unsigned)((c / S - 1) & 1), TC_SPIN)) {
-                s_fail = 1u;
-                if (p.status != nullptr) atomicOr(p.status, 8);
-                break;
+        int wstep = 0;
+        bool ok = true;
+        for (int chunk = 0; chunk < p.chunks && ok; ++chunk) {
+            const int xb = chunk % p.xbufs;
+            if (chunk >= p.xbufs && !bar_wait(&xempty_bar[xb], (unsigned)((chunk / p.xbufs - 1) & 1), TC_SPIN)) ok = false;
+            if (!ok) break;
+            bar_expect(&xfull_bar[xb], 2u * (unsigned)(p.xrows * CT_KC));
+            for (int plane = 0; plane < 2; ++plane)
+                asm volatile(
+                    "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+                    "[%0], [%1, {%2, %3, %4}], [%5];" ::"r"(saddr(xbuf + (size_t)xb * x_buf_bytes + (size_t)plane * p.x_plane_bytes)),
+                    "l"(&map_x), "r"(chunk * CT_KC), "r"(t0 - halo), "r"(plane), "r"(saddr(&xfull_bar[xb]))
+                    : "memory");
+            for (int tap = 0; tap < p.K; ++tap, ++wstep) {
+                const int s = wstep % S;
+                if (wstep >= S && !bar_wait(&empty_bar[s], (unsigned)((wstep / S - 1) & 1), TC_SPIN)) {
+                    ok = false;
+                    break;
+                }
+                bar_expect(&full_bar[s], w_stage_bytes);
+                asm volatile(
+                    "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+                    "[%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(saddr(wring + (size_t)s * w_stage_bytes)), "l"(&map_w),
+                    "r"(chunk * CT_KC), "r"(ntile * N), "r"(tap), "r"(0), "r"(saddr(&full_bar[s]))
+                    : "memory");
             }
-            load_step(c, s);
+        }
+        if (!ok) {
+            s_fail = 1u;
+            if (p.status != nullptr) atomicOr(p.status, 8);
         }
     } else if (warp == 1 && lane == 0) {
         const uint32_t idesc = instr_desc_f16(CT_TM, N);
-        for (int c = 0; c < nsteps; ++c) {
-            const int s = c % S;
-            if (!bar_wait(&full_bar[s], (unsigned)((c / S) & 1), TC_SPIN)) {
-                s_fail = 1u;
-                if (p.status != nullptr) atomicOr(p.status, 8);
+        int wstep = 0;
+        bool ok = true;
+        for (int chunk = 0; chunk < p.chunks && ok; ++chunk) {
+            const int xb = chunk % p.xbufs;
+            if (!bar_wait(&xfull_bar[xb], (unsigned)((chunk / p.xbufs) & 1), TC_SPIN)) {
+                ok = false;
                 break;
             }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            unsigned char *st = base + (size_t)s * stage_bytes;
-            const uint64_t xh = smem_desc_sw128(saddr(st));
-            const uint64_t xl = smem_desc_sw128(saddr(st + CT_A_BYTES));
-            const uint64_t wh = smem_desc_sw128(saddr(st + 2 * CT_A_BYTES));
-            const uint64_t wl = smem_desc_sw128(saddr(st + 2 * CT_A_BYTES + b_bytes));
+            unsigned char *xh_base = xbuf + (size_t)xb * x_buf_bytes;
+            for (int tap = 0; tap < p.K; ++tap, ++wstep) {
+                const int s = wstep % S;
+                if (!bar_wait(&full_bar[s], (unsigned)((wstep / S) & 1), TC_SPIN)) {
+                    ok = false;
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                // tap k reads times t - (K-1-k) * dil: rows k * dil .. k * dil + 127 of the slab
+                const unsigned row_bytes = (unsigned)(tap * p.dil) * (unsigned)CT_KC;
+                const uint64_t xh = smem_desc_sw128_row(saddr(xh_base) + row_bytes);
+                const uint64_t xl = smem_desc_sw128_row(saddr(xh_base + p.x_plane_bytes) + row_bytes);
+                unsigned char *wst = wring + (size_t)s * w_stage_bytes;
+                const uint64_t wh = smem_desc_sw128(saddr(wst));
+                const uint64_t wl = smem_desc_sw128(saddr(wst + b_bytes));
 #pragma unroll
-            for (int kk = 0; kk < CT_KC / 32; ++kk) {            // 16 halves = 32 K-bytes per instruction
-                mma_f16(tmem, xh + 2u * kk, wh + 2u * kk, idesc, (c | kk) != 0 ? 1u : 0u);
-                mma_f16(tmem, xl + 2u * kk, wh + 2u * kk, idesc, 1u);
-                mma_f16(tmem, xh + 2u * kk, wl + 2u * kk, idesc, 1u);
+                for (int kk = 0; kk < CT_KC / 32; ++kk) {            // 16 halves = 32 K-bytes per instruction
+                    mma_f16(tmem, xh + 2u * kk, wh + 2u * kk, idesc, (wstep | kk) != 0 ? 1u : 0u);
+                    mma_f16(tmem, xl + 2u * kk, wh + 2u * kk, idesc, 1u);
+                    mma_f16(tmem, xh + 2u * kk, wl + 2u * kk, idesc, 1u);
+                }
+                mma_commit(&empty_bar[s]);
             }
-            mma_commit(&empty_bar[s]);
+            if (ok) mma_commit(&xempty_bar[xb]);
+        }
+        if (!ok) {
+            s_fail = 1u;
+            if (p.status != nullptr) atomicOr(p.status, 8);
         }
         mma_commit(&done_bar);
     }
@@ -165,8 +217,10 @@ k_conv1d_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
     if (!good) {
         // a wait ran out: give copies still in flight one more bounded chance to land before
         // this CTA's shared memory is released
-        if (threadIdx.x == 0)
-            for (int s = 0; s < S && s < nsteps; ++s) bar_wait(&full_bar[s], 0u, TC_SPIN >> 4);
+        if (threadIdx.x == 0) {
+            for (int s = 0; s < S; ++s) bar_wait(&full_bar[s], 0u, TC_SPIN >> 4);
+            for (int s = 0; s < p.xbufs && s < p.chunks; ++s) bar_wait(&xfull_bar[s], 0u, TC_SPIN >> 4);
+        }
     } else {
         const int quad = warp & 3;
         const int t = t0 + quad * 32 + lane;
@@ -179,10 +233,11 @@ k_conv1d_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
             // every global read of the group first (the pointers may alias, so the compiler
             // would otherwise keep each read behind the previous column's store)
             float r[16], s[16];
+            const unsigned at0 = (unsigned)o0 * (unsigned)p.L + (unsigned)t;
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
                 const bool ok = t_ok && o0 + j < p.oc;
-                const size_t at = (size_t)(o0 + j) * p.L + t;
+                const unsigned at = at0 + (unsigned)j * (unsigned)p.L;
                 r[j] = (ok && p.res != nullptr) ? p.res[at] : 0.0f;
                 s[j] = (ok && p.acc_mode >= 2) ? p.acc[at] : 0.0f;
             }
@@ -192,17 +247,19 @@ k_conv1d_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
                 const int o = o0 + j;
                 float a = 0.0f;
                 if (o < p.oc && t_ok) {
-                    const size_t at = (size_t)o * p.L + t;
-                    const float y = r[j] + (v[j] * p.inv_scale + p.bias[o]);
+                    const unsigned at = at0 + (unsigned)j * (unsigned)p.L;
+                    const float4 ch = __ldg(p.chan + o);
+                    const bool snake = o < snake_ch;
+                    const float y = r[j] + fmaf(v[j], p.inv_scale, ch.x);
                     if (p.out != nullptr) p.out[at] = y;
-                    if (p.alpha != nullptr) a = snake_fast(y, o, snake_ch, p.alpha);
+                    if (p.has_alpha) a = snake_with(y, snake, ch.y, ch.z);
                     if (p.acc_mode == 1) {
                         p.acc[at] = y;
                     } else if (p.acc_mode == 2) {
                         p.acc[at] = s[j] + y;
                     } else if (p.acc_mode == 3) {
-                        float s3 = (s[j] + y) / 3.0f;
-                        if (p.alpha2 != nullptr) s3 = snake_fast(s3, o, snake_ch, p.alpha2);
+                        float s3 = (s[j] + y) * (1.0f / 3.0f);
+                        if (p.has_alpha2) s3 = snake_with(s3, snake, ch.w, 1.0f / (ch.w + 1e-9f));
                         p.acc[at] = s3;
                     }
                 }
@@ -248,6 +305,16 @@ k_snake_planes(const float *__restrict__ in, const float *__restrict__ alpha, __
             lo[(size_t)t * cp + c] = __float2half_rn(v - __half2float(h));
         }
     }
+}
+
+// Per output channel {bias, alpha, 1 / (alpha + 1e-9), alpha2}: what the epilogue needs of a
+// channel in one 16-byte read.
+__global__ void k_channel_table(const float *__restrict__ bias, const float *__restrict__ alpha,
+                                const float *__restrict__ alpha2, float4 *__restrict__ table, int oc) {
+    const int o = blockIdx.x * blockDim.x + threadIdx.x;
+    if (o >= oc) return;
+    const float a = alpha != nullptr ? alpha[o] : 1.0f;
+    table[o] = make_float4(bias[o], a, 1.0f / (a + 1e-9f), alpha2 != nullptr ? alpha2[o] : 1.0f);
 }
 
 // [oc][ic][K] f32 -> planes [2][K][rows][cp] f16 of scale * w (zero where no channel).
@@ -296,6 +363,14 @@ extern "C" int mb_codec_tc_pack_weight(const float *w, void *packed, size_t oc, 
     return mb_check_launch();
 }
 
+extern "C" int mb_codec_tc_channel_table(const float *bias, const float *alpha, const float *alpha2, float *table, size_t oc,
+                                         mb_stream stream) {
+    if (bias == nullptr || table == nullptr || oc == 0 || ((uintptr_t)table & 15u) != 0) return (int)cudaErrorInvalidValue;
+    k_channel_table<<<(unsigned)((oc + 127u) / 128u), 128, 0, (cudaStream_t)stream>>>(bias, alpha, alpha2,
+                                                                                     reinterpret_cast<float4 *>(table), (int)oc);
+    return mb_check_launch();
+}
+
 extern "C" int mb_codec_snake_planes(const float *in, const float *alpha, void *hi, void *lo, size_t channels, size_t length,
                                      mb_stream stream) {
     if (channels == 0 || length == 0) return (int)cudaErrorInvalidValue;
@@ -306,8 +381,9 @@ extern "C" int mb_codec_snake_planes(const float *in, const float *alpha, void *
 }
 
 extern "C" int mb_codec_conv1d_tc(const mb_codec_conv_tc_args *a, mb_stream stream) {
-    if (a == nullptr || a->x_planes == nullptr || a->w_packed == nullptr || a->bias == nullptr || a->ic == 0 || a->oc == 0 ||
-        a->length == 0 || a->kernel == 0 || a->dilation == 0 || (a->alpha != nullptr && a->act_planes == nullptr) ||
+    if (a == nullptr || a->x_planes == nullptr || a->w_packed == nullptr || a->channel_table == nullptr || a->ic == 0 || a->oc == 0 ||
+        a->length == 0 || a->kernel == 0 || a->dilation == 0 || (a->has_alpha && a->act_planes == nullptr) ||
+        a->oc * a->length > 0xffffffffull ||
         (a->acc_mode != 0 && a->acc == nullptr) || a->scale <= 0.0f ||
         (((uintptr_t)a->x_planes | (uintptr_t)a->w_packed | (uintptr_t)a->act_planes) & 15u) != 0)
         return (int)cudaErrorInvalidValue;
@@ -315,10 +391,13 @@ extern "C" int mb_codec_conv1d_tc(const mb_codec_conv_tc_args *a, mb_stream stre
     mb_codec_tc_shape(a->oc, &n, &tiles, &cp_o);
     const size_t cp_i = (a->ic + 63u) / 64u * 64u, L = a->length, rows = tiles * n;
     CUtensorMap map_x, map_w;
-    // activations: (channel bytes, time, plane); box 128 B x 128 times x both planes
+    // activations: (channel bytes, time, plane); box 128 B x (128 + halo) times of one plane
     const size_t xdims[3] = {cp_i * 2u, L, 2u};
     const size_t xstrides[2] = {cp_i * 2u, a->x_plane_stride * 2u};
-    const unsigned xbox[3] = {(unsigned)CT_KC, (unsigned)CT_TM, 2u};
+    const size_t halo = (a->kernel - 1u) * a->dilation;
+    if (halo > (size_t)CT_HALO_MAX) return (int)cudaErrorInvalidValue;
+    const size_t xrows = (size_t)CT_TM + halo;
+    const unsigned xbox[3] = {(unsigned)CT_KC, (unsigned)xrows, 1u};
     // weights: (channel bytes, output row, tap, plane); box 128 B x N rows x 1 tap x both planes
     const size_t wdims[4] = {cp_i * 2u, rows, a->kernel, 2u};
     const size_t wstrides[3] = {cp_i * 2u, rows * cp_i * 2u, a->kernel * rows * cp_i * 2u};
@@ -328,7 +407,9 @@ extern "C" int mb_codec_conv1d_tc(const mb_codec_conv_tc_args *a, mb_stream stre
         return (int)cudaErrorInvalidValue;
     ConvTcP p;
     memset(&p, 0, sizeof(p));
-    p.bias = a->bias; p.res = a->res; p.alpha = a->alpha; p.alpha2 = a->alpha2; p.out = a->out; p.acc = a->acc;
+    p.chan = reinterpret_cast<const float4 *>(a->channel_table);
+    p.has_alpha = a->has_alpha; p.has_alpha2 = a->has_alpha2;
+    p.res = a->res; p.out = a->out; p.acc = a->acc;
     p.act_hi = static_cast<__half *>(a->act_planes);
     p.act_lo = p.act_hi != nullptr ? p.act_hi + a->act_plane_stride : nullptr;
     p.status = a->status;
@@ -337,14 +418,20 @@ extern "C" int mb_codec_conv1d_tc(const mb_codec_conv_tc_args *a, mb_stream stre
     p.chunks = (int)(cp_i / 64u);
     p.cp_out = (int)cp_o;
     p.acc_mode = a->acc_mode;
-    const size_t stage_bytes = 2u * CT_A_BYTES + 2u * n * CT_KC;
-    size_t stages = (224u * 1024u) / stage_bytes;
+    p.xrows = (int)xrows;
+    p.x_plane_bytes = (int)((xrows * CT_KC + 1023u) / 1024u * 1024u);
+    // two CTAs per SM (one's epilogue runs beside the other's MMAs): 111 KB each
+    const size_t budget = 111u * 1024u, stage_bytes = 2u * n * CT_KC;
+    const size_t steps = a->kernel * (cp_i / 64u), chunks = cp_i / 64u;
+    size_t xbufs = chunks > 1 && 4u * (size_t)p.x_plane_bytes + 2u * stage_bytes <= budget ? 2u : 1u;
+    const size_t x_bytes = xbufs * 2u * (size_t)p.x_plane_bytes;
+    if (x_bytes + stage_bytes > budget) return (int)cudaErrorInvalidValue;
+    size_t stages = (budget - x_bytes) / stage_bytes;
     if (stages > CT_MAX_STAGES) stages = CT_MAX_STAGES;
-    const size_t steps = a->kernel * (cp_i / 64u);
     if (stages > steps) stages = steps;
-    if (stages < 1) return (int)cudaErrorInvalidValue;
     p.stages = (int)stages;
-    const size_t smem = stages * stage_bytes + 1024u;
+    p.xbufs = (int)xbufs;
+    const size_t smem = x_bytes + stages * stage_bytes + 1024u;
     mb_launch(k_conv1d_tc, dim3((unsigned)((L + CT_TM - 1) / CT_TM), (unsigned)tiles), dim3(CT_THREADS), smem, (cudaStream_t)stream,
               map_x, map_w, p);
     return mb_check_launch();

@@ -226,14 +226,14 @@ typedef struct {
     size_t x_plane_stride;
     const void *w_packed;     /* mb_codec_tc_pack_weight's layout */
     float scale;              /* the power of two the packed weights carry */
-    const float *bias;
+    const float *channel_table; /* mb_codec_tc_channel_table: bias, the Snake constants of the epilogue */
+    int has_alpha;            /* act_planes = half-Snake(v) with the table's alpha */
+    int has_alpha2;           /* acc_mode 3: half-Snake with the table's alpha2 on the finished sum */
     const float *res;
     float *out;
-    const float *alpha;
     void *act_planes;
     size_t act_plane_stride;
     float *acc;
-    const float *alpha2;
     size_t ic, oc, length, kernel, dilation;
     int acc_mode;
     int *status;              /* device status word: bits 8 / 16 on a bounded wait running out */
@@ -244,6 +244,10 @@ size_t mb_codec_tc_packed_halves(size_t oc, size_t ic, size_t kernel);
 /* [oc][ic][kernel] f32 (device) -> f16 hi/lo planes of scale * w in the tensor-core layout. */
 int mb_codec_tc_pack_weight(const float *w, void *packed, size_t oc, size_t ic, size_t kernel, float scale,
                             mb_stream stream);
+/* table[o] = {bias[o], alpha[o], 1 / (alpha[o] + 1e-9), alpha2[o]} (4 floats per channel, 16-byte
+ * aligned); alpha / alpha2 may be NULL. */
+int mb_codec_tc_channel_table(const float *bias, const float *alpha, const float *alpha2, float *table, size_t oc,
+                              mb_stream stream);
 /* f32 [channels][length] -> half-Snake -> f16 hi/lo planes [length][cp]. */
 int mb_codec_snake_planes(const float *in, const float *alpha, void *hi, void *lo, size_t channels, size_t length,
                           mb_stream stream);
