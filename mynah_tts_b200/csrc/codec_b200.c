@@ -310,14 +310,14 @@ static int codec_enqueue(mb_codec *c, size_t frames, int stop_after, size_t *res
                 t.w_packed = B->in_conv.w_tc; t.scale = B->in_conv.scale; t.channel_table = B->in_table;
                 t.has_alpha = 1; t.act_planes = resp; t.act_plane_stride = pstride;
                 t.ic = nch; t.oc = nch; t.length = nlen; t.kernel = codec_kernels[b]; t.dilation = codec_dilations[d];
-                t.status = st->d_status;
+                t.status = st->d_status; t.sm_count = st->sm_count;
                 R_TRY(mb_codec_conv1d_tc(&t, s));
                 memset(&t, 0, sizeof(t));
                 t.x_planes = resp; t.x_plane_stride = pstride;
                 t.w_packed = B->skip_conv.w_tc; t.scale = B->skip_conv.scale; t.channel_table = B->skip_table;
                 t.res = d == 0 ? c->up : c->cur;
                 t.ic = nch; t.oc = nch; t.length = nlen; t.kernel = codec_kernels[b]; t.dilation = 1u;
-                t.status = st->d_status;
+                t.status = st->d_status; t.sm_count = st->sm_count;
                 if (d + 1u < CODEC_BLOCKS) {
                     t.out = c->cur;
                     t.has_alpha = 1;

@@ -390,6 +390,17 @@ extern "C" int mb_codec_conv1d_tc(const mb_codec_conv_tc_args *a, mb_stream stre
     size_t n, tiles, cp_o;
     mb_codec_tc_shape(a->oc, &n, &tiles, &cp_o);
     const size_t cp_i = (a->ic + 63u) / 64u * 64u, L = a->length, rows = tiles * n;
+    // a short signal leaves SMs without a tile: narrower tiles of output channels then (each
+    // re-reads the activation slab, which stays in L2); rows past the packed matrix read as zeros
+    {
+        const size_t m_tiles = (L + CT_TM - 1) / CT_TM, sms = a->sm_count > 0 ? (size_t)a->sm_count : 148u;
+        static const size_t narrower[] = {64u, 48u, 32u, 16u};
+        for (size_t i = 0; i < 4 && m_tiles * tiles < sms; ++i)
+            if (narrower[i] < n) {
+                n = narrower[i];
+                tiles = (a->oc + n - 1u) / n;
+            }
+    }
     CUtensorMap map_x, map_w;
     // activations: (channel bytes, time, plane); box 128 B x (128 + halo) times of one plane
     const size_t xdims[3] = {cp_i * 2u, L, 2u};

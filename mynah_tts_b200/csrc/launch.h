@@ -237,6 +237,7 @@ typedef struct {
     size_t ic, oc, length, kernel, dilation;
     int acc_mode;
     int *status;              /* device status word: bits 8 / 16 on a bounded wait running out */
+    int sm_count;
 } mb_codec_conv_tc_args;
 int mb_codec_tc_init(void);
 void mb_codec_tc_shape(size_t oc, size_t *n_tile, size_t *tiles, size_t *cp);
