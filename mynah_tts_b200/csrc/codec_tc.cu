@@ -56,6 +56,8 @@ struct ConvTcP {
     int *status;
     float inv_scale;             // 1 / the power of two the weights were scaled by
     int oc, L, K, dil, n_tile, chunks, stages, cp_out, acc_mode;
+    float *rows_out;             // row-major form: out[t][o] with row stride rows_stride (the codec's form: NULL)
+    int rows_stride, rows_epi;   // MB_EPI_STORE / MB_EPI_RESIDUAL / MB_EPI_GELU
     int xrows;                   // 128 + (K - 1) * dil rows per activation tile
     int x_plane_bytes;           // xrows * 128 rounded up to 1024
     int xbufs;                   // activation buffers: 2, or 1 where two do not fit beside two weight stages
@@ -230,6 +232,35 @@ k_conv1d_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
             float v[16];
             tmem_ld16f(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)(g * 16), v);
             const int o0 = ntile * N + g * 16;
+            if (p.rows_out != nullptr) {
+                // products over rows (text encoder, context prefill): out[t][o0 .. o0 + 15], 64 bytes per thread
+                if (t_ok && o0 < p.oc) {
+                    float *dst = p.rows_out + (size_t)t * p.rows_stride + o0;
+                    float y[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) y[j] = v[j] * p.inv_scale;
+                    if (p.rows_epi == MB_EPI_GELU) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) y[j] = gelu_tanh<false>(y[j], nullptr);
+                    }
+                    if (o0 + 16 <= p.oc) {
+                        float4 *d4 = reinterpret_cast<float4 *>(dst);
+                        if (p.rows_epi == MB_EPI_RESIDUAL) {
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                const float4 old = d4[q];
+                                y[4 * q] += old.x; y[4 * q + 1] += old.y; y[4 * q + 2] += old.z; y[4 * q + 3] += old.w;
+                            }
+                        }
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) d4[q] = make_float4(y[4 * q], y[4 * q + 1], y[4 * q + 2], y[4 * q + 3]);
+                    } else {
+                        for (int j = 0; j < 16 && o0 + j < p.oc; ++j)
+                            dst[j] = p.rows_epi == MB_EPI_RESIDUAL ? dst[j] + y[j] : y[j];
+                    }
+                }
+                continue;
+            }
             // every global read of the group first (the pointers may alias, so the compiler
             // would otherwise keep each read behind the previous column's store)
             float r[16], s[16];
@@ -307,6 +338,20 @@ k_snake_planes(const float *__restrict__ in, const float *__restrict__ alpha, __
     }
 }
 
+// f32 rows [rows][k] (row stride ld) -> f16 hi/lo planes [rows][k].
+__global__ void __launch_bounds__(256)
+k_split_rows(const float *__restrict__ x, __half *__restrict__ hi, __half *__restrict__ lo, int k, int ld) {
+    mb_pdl_wait();
+    mb_pdl_trigger();
+    const int r = blockIdx.x;
+    for (int i = threadIdx.x; i < k; i += blockDim.x) {
+        const float v = x[(size_t)r * ld + i];
+        const __half h = __float2half_rn(v);
+        hi[(size_t)r * k + i] = h;
+        lo[(size_t)r * k + i] = __float2half_rn(v - __half2float(h));
+    }
+}
+
 // Per output channel {bias, alpha, 1 / (alpha + 1e-9), alpha2}: what the epilogue needs of a
 // channel in one 16-byte read.
 __global__ void k_channel_table(const float *__restrict__ bias, const float *__restrict__ alpha,
@@ -371,6 +416,13 @@ extern "C" int mb_codec_tc_channel_table(const float *bias, const float *alpha, 
     return mb_check_launch();
 }
 
+extern "C" int mb_split_rows_f16(const float *x, void *hi, void *lo, size_t rows, size_t k, size_t ld, mb_stream stream) {
+    if (rows == 0 || k == 0 || ld < k) return (int)cudaErrorInvalidValue;
+    mb_launch(k_split_rows, dim3((unsigned)rows), dim3(256), 0, (cudaStream_t)stream, x, static_cast<__half *>(hi),
+              static_cast<__half *>(lo), (int)k, (int)ld);
+    return mb_check_launch();
+}
+
 extern "C" int mb_codec_snake_planes(const float *in, const float *alpha, void *hi, void *lo, size_t channels, size_t length,
                                      mb_stream stream) {
     if (channels == 0 || length == 0) return (int)cudaErrorInvalidValue;
@@ -381,7 +433,9 @@ extern "C" int mb_codec_snake_planes(const float *in, const float *alpha, void *
 }
 
 extern "C" int mb_codec_conv1d_tc(const mb_codec_conv_tc_args *a, mb_stream stream) {
-    if (a == nullptr || a->x_planes == nullptr || a->w_packed == nullptr || a->channel_table == nullptr || a->ic == 0 || a->oc == 0 ||
+    if (a == nullptr || a->x_planes == nullptr || a->w_packed == nullptr ||
+        (a->channel_table == nullptr && a->rows_out == nullptr) || a->ic == 0 || a->oc == 0 ||
+        (a->rows_out != nullptr && ((a->rows_stride % 4u) != 0 || ((uintptr_t)a->rows_out & 15u) != 0)) ||
         a->length == 0 || a->kernel == 0 || a->dilation == 0 || (a->has_alpha && a->act_planes == nullptr) ||
         a->oc * a->length > 0xffffffffull ||
         (a->acc_mode != 0 && a->acc == nullptr) || a->scale <= 0.0f ||
@@ -421,6 +475,7 @@ extern "C" int mb_codec_conv1d_tc(const mb_codec_conv_tc_args *a, mb_stream stre
     p.chan = reinterpret_cast<const float4 *>(a->channel_table);
     p.has_alpha = a->has_alpha; p.has_alpha2 = a->has_alpha2;
     p.res = a->res; p.out = a->out; p.acc = a->acc;
+    p.rows_out = a->rows_out; p.rows_stride = (int)a->rows_stride; p.rows_epi = a->rows_epilogue;
     p.act_hi = static_cast<__half *>(a->act_planes);
     p.act_lo = p.act_hi != nullptr ? p.act_hi + a->act_plane_stride : nullptr;
     p.status = a->status;

@@ -1533,6 +1533,7 @@ int mynah_b200_decoder_local_attach(void *decoder, const mynah_b200_local_desc *
     A_TRY(dmalloc((void **)&lt->d_topk, MB * sizeof(unsigned), error, cap));
     A_TRY(dmalloc((void **)&lt->d_rng, MB * sizeof(unsigned long long), error, cap));
     A_TRY(dmalloc((void **)&lt->d_eos_sub, MB * sizeof(int), error, cap));
+    if (ok) A_TRY(mb_cuda((int)cudaMemset(lt->d_eos_sub, 0xff, MB * sizeof(int)), "cudaMemset", error, cap));   /* -1: none yet */
     if (ok) {
         A_TRY(mb_cuda((int)cudaMemset(lt->k, 0, kv * sizeof(float)), "memset", error, cap));
         A_TRY(mb_cuda((int)cudaMemset(lt->v, 0, kv * sizeof(float)), "memset", error, cap));

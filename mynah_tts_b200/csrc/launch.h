@@ -238,7 +238,15 @@ typedef struct {
     int acc_mode;
     int *status;              /* device status word: bits 8 / 16 on a bounded wait running out */
     int sm_count;
+    /* Products over rows (text encoder, context prefill) use the same kernel with time = row:
+     * x_planes [2][rows][ic], result row-major out[row][o] with row stride rows_stride (a multiple
+     * of 4 floats), epilogue MB_EPI_STORE / _RESIDUAL / _GELU (fast form); no bias, no table. */
+    float *rows_out;
+    size_t rows_stride;
+    int rows_epilogue;
 } mb_codec_conv_tc_args;
+/* f32 rows [rows][k] with row stride ld -> f16 hi/lo planes [rows][k] each. */
+int mb_split_rows_f16(const float *x, void *hi, void *lo, size_t rows, size_t k, size_t ld, mb_stream stream);
 int mb_codec_tc_init(void);
 void mb_codec_tc_shape(size_t oc, size_t *n_tile, size_t *tiles, size_t *cp);
 size_t mb_codec_tc_packed_halves(size_t oc, size_t ic, size_t kernel);

@@ -15,8 +15,15 @@ WIDE = synth.EncoderShape(layers=2, width=768, vocab=96, max_length=160)
 
 @pytest.mark.parametrize("shape,counts", [(synth.TINY_ENCODER, (1, 2, 19, 33, 48)), (WIDE, (1, 31, 97, 160))],
                          ids=["tiny", "width768"])
-@pytest.mark.parametrize("strict", [True, False], ids=["strict", "fast"])
-def test_text_encoder_matches_oracle(shape, counts, strict):
+@pytest.mark.parametrize("strict,no_tc", [pytest.param(True, False, id="strict"),
+                                           pytest.param(False, False, id="fast-tensor-core"),
+                                           pytest.param(False, True, id="fast-simt")])
+def test_text_encoder_matches_oracle(shape, counts, strict, no_tc, monkeypatch):
+    """Strict: sequential f32 sums, bit for bit.  Fast: the layer's products on the tensor cores
+    over split f16 planes (the kernel-3 convolutions without an unfolded copy), or SIMT FMAs
+    with MYNAH_B200_NO_TC."""
+    if no_tc:
+        monkeypatch.setenv("MYNAH_B200_NO_TC", "1")
     tensors = synth.add_encoder(None, shape, seed=91)
     be = Backend("int8", strict=strict)          # the weight format must not matter: the encoder is f32
     enc = TextEncoder(be, tensors, shape)
