@@ -29,6 +29,10 @@ typedef struct {
     /* optional f32 copies (a quantized decoder that prefills more than 16 rows at once: the
      * reference then multiplies with the f32 weights, src/qmat.c:773-788) */
     mb_dev_weight qkv32, o_self32, q_cross32, o_cross32, ffn_up32, ffn_down32;
+    /* fast mode, with the f32 copies: the same weights as f16 hi/lo planes for the tensor-core
+     * product of many rows (codec_tc.cu), and the power of two they carry */
+    void *tc_w[6];
+    float tc_scale[6];
     float *norm_xattn_memory;   /* optional: with kv_cross, lets a slot's cross K/V be made here */
     mb_dev_weight kv_cross;     /* f32 [2*xw, width]; the reference runs it unquantized */
 } dec_layer;
@@ -68,6 +72,7 @@ typedef struct mb_decoder {
     float *x, *nrm, *qkv, *attn, *q_x, *xctx, *hidden, *out, *rows_in, *logits;
     int8_t *qx;
     float *sx;
+    void *row_planes;           /* prefill on the tensor cores: f16 hi/lo planes of the rows feeding a product */
     void *xsplit;               /* f16 weights: the activations' two f16 planes for the tensor-core product */
     float *partials;
     unsigned *counters;
@@ -168,6 +173,14 @@ static void destroy_graphs(mb_decoder *d) {
             }
 }
 
+/* Tensor-core planes of the f32 weights are worth building: not switched off, and every
+ * product's input width is a whole number of 64-column chunks. */
+static int prefill_tc_wanted(size_t width, size_t xattn_width) {
+    const char *no_tc = getenv("MYNAH_B200_NO_TC");
+    if (no_tc != NULL && strcmp(no_tc, "0") != 0) return 0;
+    return width % 64u == 0 && xattn_width % 64u == 0;
+}
+
 void mynah_b200_decoder_destroy(void *decoder) {
     mb_decoder *d = (mb_decoder *)decoder;
     if (d == NULL) return;
@@ -185,6 +198,7 @@ void mynah_b200_decoder_destroy(void *decoder) {
             mb_weight_release(&L->qkv32); mb_weight_release(&L->o_self32);
             mb_weight_release(&L->q_cross32); mb_weight_release(&L->o_cross32);
             mb_weight_release(&L->ffn_up32); mb_weight_release(&L->ffn_down32);
+            for (int t = 0; t < 6; ++t) cudaFree(L->tc_w[t]);
         }
         free(d->L);
     }
@@ -201,7 +215,7 @@ void mynah_b200_decoder_destroy(void *decoder) {
     }
     void *dev[] = {d->position, d->norm_out, d->emb, (void *)d->d_tables, d->heads_b, d->self_k,
                    d->self_v, d->cross_k, d->cross_v, d->x, d->nrm, d->qkv, d->attn, d->q_x,
-                   d->xctx, d->hidden, d->out, d->rows_in, d->logits, d->qx, d->sx, d->xsplit, d->partials,
+                   d->xctx, d->hidden, d->out, d->rows_in, d->logits, d->qx, d->sx, d->xsplit, d->row_planes, d->partials,
                    d->counters, d->d_stage_in, d->d_stage_out, d->d_eos_frame, d->d_min_frames,
                    d->d_history, d->d_mem_len, d->pf_mem, d->pf_nrm, d->pf_kv};
     for (size_t i = 0; i < sizeof(dev) / sizeof(dev[0]); ++i) cudaFree(dev[i]);
@@ -305,6 +319,31 @@ int mynah_b200_decoder_create(void *state, const mynah_b200_decoder_desc *desc, 
             D_TRY(mb_weight_build(st, s->ffn_up_w, F, W, MB_F32, &L->ffn_up32, error, cap));
             D_TRY(mb_weight_build(st, s->ffn_down_w, W, F, MB_F32, &L->ffn_down32, error, cap));
         }
+        if (ok && desc->keep_f32_weights && !st->strict && prefill_tc_wanted(W, XW)) {
+            /* the f32 weights once more as tensor-core planes (fast mode's many-row products) */
+            const float *host[6] = {s->qkv_w, s->o_self_w, s->q_cross_w, s->o_cross_w, s->ffn_up_w, s->ffn_down_w};
+            const mb_dev_weight *dev[6] = {q != MB_F32 ? &L->qkv32 : &L->qkv, q != MB_F32 ? &L->o_self32 : &L->o_self,
+                                           q != MB_F32 ? &L->q_cross32 : &L->q_cross, q != MB_F32 ? &L->o_cross32 : &L->o_cross,
+                                           q != MB_F32 ? &L->ffn_up32 : &L->ffn_up, q != MB_F32 ? &L->ffn_down32 : &L->ffn_down};
+            for (int t = 0; ok && t < 6; ++t) {
+                const size_t n = dev[t]->n, k = dev[t]->k;
+                float amax = 0.0f;
+                for (size_t i = 0; i < n * k; ++i) {
+                    const float v = fabsf(host[t][i]);
+                    if (v > amax) amax = v;
+                }
+                int ex = 0;
+                if (amax > 0.0f) {
+                    (void)frexpf(amax, &ex);
+                    ex = 14 - ex;
+                }
+                ex = ex > 30 ? 30 : (ex < -30 ? -30 : ex);
+                L->tc_scale[t] = ldexpf(1.0f, ex);
+                D_TRY(dmalloc(&L->tc_w[t], mb_codec_tc_packed_halves(n, k, 1u) * 2u, error, cap));
+                if (ok) D_TRY(mb_cuda(mb_codec_tc_pack_weight((const float *)dev[t]->w, L->tc_w[t], n, k, 1u, L->tc_scale[t], st->stream),
+                                      "pack weight", error, cap));
+            }
+        }
         if (ok)
             d->weight_bytes += L->qkv.bytes + L->o_self.bytes + L->q_cross.bytes + L->o_cross.bytes +
                                L->ffn_up.bytes + L->ffn_down.bytes + 3u * W * sizeof(float);
@@ -383,6 +422,7 @@ int mynah_b200_decoder_create(void *state, const mynah_b200_decoder_desc *desc, 
     D_TRY(dmalloc((void **)&d->sx, MB * sizeof(float), error, cap));
     if (q == MB_F16)
         D_TRY(dmalloc(&d->xsplit, mb_gemm_tc_f16_split_halves(MB, F) * 2u, error, cap));
+    if (d->L != NULL && d->L[0].tc_w[0] != NULL) D_TRY(dmalloc(&d->row_planes, 2u * MB * F * 2u, error, cap));
     if (d->tables != 0) {
         D_TRY(dmalloc((void **)&d->logits, MB * d->tables * d->vocab * sizeof(float), error, cap));
         d->history_frames = d->capacity;
@@ -1314,11 +1354,27 @@ int mynah_b200_decoder_generate(void *decoder, const unsigned *slots, size_t bat
 
 /* ------------------------------------------------------------------ prefill */
 /* One product of the prefill: through the decoder's packed weight with quantized rows
- * (d->qx/d->sx) when `packed`, else through the f32 weight with the f32 rows. */
+ * (d->qx/d->sx) when `packed`, else through the f32 weight with the f32 rows -- in fast mode
+ * on the tensor cores when the decoder holds the weight's f16 planes (tc_w != NULL). */
 static int prefill_product(mb_decoder *d, const mb_dev_weight *wq, const mb_dev_weight *w32, int packed,
                            const float *act_f32, float *out, size_t out_stride, size_t nb, int epilogue,
-                           unsigned *count) {
+                           unsigned *count, const void *tc_w, float tc_scale) {
     if (packed) return product(d, wq, NULL, act_f32, out, out_stride, nb, epilogue, count);
+    if (tc_w != NULL && d->row_planes != NULL && d->use_tc) {
+        const size_t k = w32->k;
+        unsigned short *hi = (unsigned short *)d->row_planes, *lo = hi + d->max_batch * k;
+        int rc = mb_split_rows_f16(act_f32, hi, lo, nb, k, k, d->st->stream);
+        if (rc != 0) return rc;
+        mb_codec_conv_tc_args t;
+        memset(&t, 0, sizeof(t));
+        t.x_planes = hi; t.x_plane_stride = d->max_batch * k;
+        t.w_packed = tc_w; t.scale = tc_scale;
+        t.ic = k; t.oc = w32->n; t.length = nb; t.kernel = 1u; t.dilation = 1u;
+        t.rows_out = out; t.rows_stride = out_stride; t.rows_epilogue = epilogue;
+        t.status = d->d_status; t.sm_count = d->st->sm_count;
+        *count += 2u;
+        return mb_codec_conv1d_tc(&t, d->st->stream);
+    }
     mb_gemv_args g;
     memset(&g, 0, sizeof(g));
     mb_gemv_bind_weight(&g, w32, NULL);
@@ -1364,8 +1420,10 @@ int mynah_b200_decoder_prefill(void *decoder, size_t slot, const float *rows, si
     const int q = quantized_mode(d);
     const int f32_model = st->quant == MB_F32;
     /* packed weights: an f32 or f16 model always; a quantized one for at most 16 rows */
-    const int packed = f32_model || st->quant == MB_F16 || count <= 16u;
-    if (!packed && d->L[0].qkv32.w == NULL) {
+    /* fast mode with the weights' f16 planes at hand: more than 16 rows go through the tensor cores */
+    const int tc_rows = !st->strict && d->use_tc && d->row_planes != NULL && count > 16u && st->quant != MB_F16;
+    const int packed = !tc_rows && (f32_model || st->quant == MB_F16 || count <= 16u);
+    if (!packed && !f32_model && d->L[0].qkv32.w == NULL) {
         mb_set_error(error, cap, "prefill of more than 16 rows of a quantized model uses the f32 weights: "
                                  "create the decoder with keep_f32_weights");
         return -1;
@@ -1394,7 +1452,7 @@ int mynah_b200_decoder_prefill(void *decoder, size_t slot, const float *rows, si
         R_TRY(mb_layernorm(d->x, d->nrm, L->norm_self, NULL, count, W, 1.0e-5f, quant_rows ? d->qx : NULL,
                            quant_rows ? d->sx : NULL, d->d_n_active, st->strict, s));
         launches += 1u;
-        R_TRY(prefill_product(d, &L->qkv, &L->qkv32, packed, d->nrm, d->qkv, 3u * W, count, MB_EPI_STORE, &launches));
+        R_TRY(prefill_product(d, &L->qkv, f32_model ? &L->qkv : &L->qkv32, packed, d->nrm, d->qkv, 3u * W, count, MB_EPI_STORE, &launches, L->tc_w[0], L->tc_scale[0]));
         /* the new rows' K and V into the cache: rows start .. start + count - 1 of this layer */
         float *kc = d->self_k + ((slot * d->layers + l) * d->capacity + start) * W;
         float *vc = d->self_v + ((slot * d->layers + l) * d->capacity + start) * W;
@@ -1431,11 +1489,11 @@ int mynah_b200_decoder_prefill(void *decoder, size_t slot, const float *rows, si
         a.softmax_inverse = 1;
         a.launched = &launches;
         R_TRY(mb_attention(&a, s));
-        R_TRY(prefill_product(d, &L->o_self, &L->o_self32, packed, d->attn, d->x, W, count, MB_EPI_RESIDUAL, &launches));
+        R_TRY(prefill_product(d, &L->o_self, f32_model ? &L->o_self : &L->o_self32, packed, d->attn, d->x, W, count, MB_EPI_RESIDUAL, &launches, L->tc_w[1], L->tc_scale[1]));
         R_TRY(mb_layernorm(d->x, d->nrm, L->norm_xattn_query, NULL, count, W, 1.0e-5f, quant_rows ? d->qx : NULL,
                            quant_rows ? d->sx : NULL, d->d_n_active, st->strict, s));
         launches += 1u;
-        R_TRY(prefill_product(d, &L->q_cross, &L->q_cross32, packed, d->nrm, d->q_x, XW, count, MB_EPI_STORE, &launches));
+        R_TRY(prefill_product(d, &L->q_cross, f32_model ? &L->q_cross : &L->q_cross32, packed, d->nrm, d->q_x, XW, count, MB_EPI_STORE, &launches, L->tc_w[2], L->tc_scale[2]));
         memset(&a, 0, sizeof(a));
         a.q = d->q_x;
         a.q_stride = XW;
@@ -1464,16 +1522,16 @@ int mynah_b200_decoder_prefill(void *decoder, size_t slot, const float *rows, si
         a.sm_count = st->sm_count;
         a.launched = &launches;
         R_TRY(mb_attention(&a, s));
-        R_TRY(prefill_product(d, &L->o_cross, &L->o_cross32, packed, d->xctx, d->x, W, count, MB_EPI_RESIDUAL, &launches));
+        R_TRY(prefill_product(d, &L->o_cross, f32_model ? &L->o_cross : &L->o_cross32, packed, d->xctx, d->x, W, count, MB_EPI_RESIDUAL, &launches, L->tc_w[3], L->tc_scale[3]));
         R_TRY(mb_layernorm(d->x, d->nrm, L->norm_pos_ff, NULL, count, W, 1.0e-5f, quant_rows ? d->qx : NULL,
                            quant_rows ? d->sx : NULL, d->d_n_active, st->strict, s));
         launches += 1u;
-        R_TRY(prefill_product(d, &L->ffn_up, &L->ffn_up32, packed, d->nrm, d->hidden, F, count, MB_EPI_GELU, &launches));
+        R_TRY(prefill_product(d, &L->ffn_up, f32_model ? &L->ffn_up : &L->ffn_up32, packed, d->nrm, d->hidden, F, count, MB_EPI_GELU, &launches, L->tc_w[4], L->tc_scale[4]));
         if (quant_rows) {
             R_TRY(mb_quant_rows(d->hidden, count, F, d->qx, d->sx, d->d_n_active, s));
             launches += 1u;
         }
-        R_TRY(prefill_product(d, &L->ffn_down, &L->ffn_down32, packed, d->hidden, d->x, W, count, MB_EPI_RESIDUAL, &launches));
+        R_TRY(prefill_product(d, &L->ffn_down, f32_model ? &L->ffn_down : &L->ffn_down32, packed, d->hidden, d->x, W, count, MB_EPI_RESIDUAL, &launches, L->tc_w[5], L->tc_scale[5]));
     }
     /* the output norm of the last new row only */
     R_TRY(mb_layernorm(d->x + (count - 1u) * W, d->out, d->norm_out, NULL, 1u, W, 1.0e-5f, NULL, NULL, NULL, st->strict, s));

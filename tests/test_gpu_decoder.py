@@ -597,7 +597,9 @@ def test_f16_weights_on_the_tensor_cores_match_oracle(shape_name, lanes, tiny_mo
 
 @pytest.mark.parametrize("shape_name,name,count,strict", [
     ("tiny", "int8", 20, True), ("tiny", "int8", 9, True), ("tiny", "f32", 20, True), ("tiny", "int4", 17, True),
-    ("tiny", "int8", 16, True), ("tiny", "int8", 20, False), ("tiny", "f16", 20, False), ("full", "int8", 24, True)])
+    ("tiny", "int8", 16, True), ("tiny", "int8", 20, False), ("tiny", "f16", 20, False), ("full", "int8", 24, True),
+    # fast mode at full size: more than 16 rows run on the tensor cores over split f16 planes
+    ("full", "int8", 40, False), ("full", "f32", 19, False)])
 def test_multi_row_prefill_matches_decoder_run(shape_name, name, count, strict, tiny_model, tiny_memory):
     """decoder_run with count > 1 (src/graph.c:3506-3641): a few rows stepped one by one, then
     `count` rows pushed at once, then a step on top, against the CPU restatement (itself equal
@@ -610,9 +612,12 @@ def test_multi_row_prefill_matches_decoder_run(shape_name, name, count, strict, 
         shape = synth.MAGPIE_357M
         model = synth.make_model(shape, seed=71)
         memory = synth.make_memory(shape, seed=171)
-    capacity = 48
+    capacity = 64
     rng = np.random.default_rng(37)
-    first = rng.normal(0, 0.05, size=(3, shape.width)).astype(np.float32)
+    # the full-size fast cases isolate the many-row products (f32 weights on the tensor cores):
+    # no quantized single steps in front, whose rounding flips would ride into the cache
+    tc_case = shape_name == "full" and not strict
+    first = rng.normal(0, 0.05, size=(0 if tc_case else 3, shape.width)).astype(np.float32)
     rows = rng.normal(0, 0.05, size=(count, shape.width)).astype(np.float32)
     after = rng.normal(0, 0.05, size=(shape.width,)).astype(np.float32)
     pm = O.PortModel(model, QT[name])
@@ -628,13 +633,17 @@ def test_multi_row_prefill_matches_decoder_run(shape_name, name, count, strict, 
         want, got = ps.step(r), dec.step_batch([1], r[None, :])[0]
         assert rel_err(got, want) < tol
     want, got = ps.prefill(rows), dec.prefill(1, rows)
+    if tc_case:
+        tol = 1e-4          # f32 weights as split f16 planes: measured 9e-6
     assert rel_err(got, want) < tol, (name, count, strict)
     if exact:
         assert np.array_equal(got, want), (name, count)
-    assert dec.slot_length(1) == 3 + count
+    assert dec.slot_length(1) == len(first) + count
     k, v = dec.slot_read_kv(1)
-    n = 3 + count
+    n = len(first) + count
     assert rel_err(k[:, :n], ps.self_k[:, :n]) < tol and rel_err(v[:, :n], ps.self_v[:, :n]) < tol
+    if tc_case:
+        tol = 2e-2 if name != "f32" else 1e-3          # the single step on top is quantized again
     if exact:
         assert np.array_equal(k[:, :n], ps.self_k[:, :n]) and np.array_equal(v[:, :n], ps.self_v[:, :n])
     assert not k[:, n:].any()
