@@ -86,7 +86,27 @@ __device__ __forceinline__ void xb_tick(int i) {
 #define XB_TICK(i)
 #endif
 
-template <int RO, int LPR, bool STRICT>
+// One group of 32 int4 weights (16 packed bytes, even index in the low nibble, +8 offset) times
+// 32 int8 activations (two 16-byte pieces in natural order): the exact int32 sum.
+__device__ __forceinline__ int dot_q4_group(uint4 w, uint4 x0, uint4 x1) {
+    const unsigned ww[4] = {w.x, w.y, w.z, w.w};
+    const unsigned xe[4] = {__byte_perm(x0.x, x0.y, 0x6420), __byte_perm(x0.z, x0.w, 0x6420),
+                            __byte_perm(x1.x, x1.y, 0x6420), __byte_perm(x1.z, x1.w, 0x6420)};
+    const unsigned xo[4] = {__byte_perm(x0.x, x0.y, 0x7531), __byte_perm(x0.z, x0.w, 0x7531),
+                            __byte_perm(x1.x, x1.y, 0x7531), __byte_perm(x1.z, x1.w, 0x7531)};
+    int gi = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        gi = __dp4a((int)__vsub4(ww[j] & 0x0f0f0f0fu, 0x08080808u), (int)xe[j], gi);
+        gi = __dp4a((int)__vsub4((ww[j] >> 4) & 0x0f0f0f0fu, 0x08080808u), (int)xo[j], gi);
+    }
+    return gi;
+}
+
+// INT4: the two weights are int4 in groups of 32 with f32 group scales (src/qmat.c:154-185:
+// per group an exact int32 sum times the group's scale, added in group order, then times the
+// activation scale); otherwise int8 with one scale per row.
+template <int RO, int LPR, bool STRICT, bool INT4>
 __global__ void __launch_bounds__(XB_THREADS, 1)
 k_cross_block(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, CrossP p) {
     extern __shared__ __align__(1024) float sm[];
@@ -146,19 +166,21 @@ k_cross_block(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
         gq[i] = __ldg(p.gain_query + i);
         gf[i] = __ldg(p.gain_ff + i);
     }
-    const int npc = W / 16;
-    constexpr int PQ = 8 * RO;
+    const int npc = INT4 ? W / 32 : W / 16;           // 16-byte pieces of a query-weight row
+    constexpr int PQ = INT4 ? 4 * RO : 8 * RO;
     const int oq = threadIdx.x >> 1, hq = threadIdx.x & 1;   // query row of this thread, and which pieces
     uint4 wq0[PQ];
+    float wqg[INT4 ? PQ : 1];                         // int4: the group scale of each piece
 #pragma unroll
     for (int j = 0; j < PQ; ++j) {
         const int pc = 2 * j + hq;
-        wq0[j] = (oq < XW && pc < npc) ? ldg_pinned(reinterpret_cast<const uint4 *>(p.wq + (long)oq * W) + pc)
+        wq0[j] = (oq < XW && pc < npc) ? ldg_pinned(reinterpret_cast<const uint4 *>(p.wq + (long)oq * (INT4 ? W / 2 : W)) + pc)
                                        : make_uint4(0u, 0u, 0u, 0u);
+        if (INT4) wqg[j] = (oq < XW && pc < npc) ? __ldg(p.wq_scales + (long)oq * npc + pc) : 0.0f;
     }
-    const float wqs0 = oq < XW ? __ldg(p.wq_scales + oq) : 0.0f;
+    const float wqs0 = (!INT4 && oq < XW) ? __ldg(p.wq_scales + oq) : 0.0f;
     {
-        const long lines = ((long)W * XW + 127) / 128;
+        const long lines = ((long)W * XW / (INT4 ? 2 : 1) + 127) / 128;
         for (long ln = (long)blockIdx.x * XB_THREADS + threadIdx.x; ln < lines; ln += (long)gridDim.x * XB_THREADS)
             asm volatile("prefetch.global.L2 [%0];" ::"l"(p.wo + ln * 128));
     }
@@ -181,7 +203,31 @@ k_cross_block(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
 
     XB_TICK(3);
     // ---- query product: two threads per output row, pieces of the row interleaved
-    {
+    if (INT4) {
+        // a piece is one group: its exact sum times its scale; the two threads of a row then
+        // add the groups in order, each taking the other's from a shuffle
+        float gp[PQ];
+#pragma unroll
+        for (int j = 0; j < PQ; ++j) {
+            const int pc = 2 * j + hq;
+            gp[j] = 0.0f;
+            if (pc < npc) {
+                const uint4 x0 = reinterpret_cast<const uint4 *>(qrow)[2 * pc];
+                const uint4 x1 = reinterpret_cast<const uint4 *>(qrow)[2 * pc + 1];
+                gp[j] = __fmul_rn((float)dot_q4_group(wq0[j], x0, x1), wqg[j]);
+            }
+        }
+        float acc = 0.0f;
+#pragma unroll
+        for (int j = 0; j < PQ; ++j) {
+            const float mine = gp[j];
+            const float even = __shfl_sync(MB_FULL, mine, lane & ~1);     // group 2j
+            const float odd = __shfl_sync(MB_FULL, mine, lane | 1);       // group 2j + 1
+            if (2 * j < npc) acc = __fadd_rn(acc, even);
+            if (2 * j + 1 < npc) acc = __fadd_rn(acc, odd);
+        }
+        if (hq == 0 && oq < XW) qs[oq] = __fmul_rn(acc, sxq);
+    } else {
         int a0 = 0, a1 = 0, a2 = 0, a3 = 0;           // four chains instead of one of 4 * PQ steps
 #pragma unroll
         for (int j = 0; j < PQ; ++j) {
@@ -205,11 +251,28 @@ k_cross_block(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
     constexpr int NI = RO * LPR;                      // loads per lane
     const int lr = lane / LPR, lp = lane % LPR;
     const int wrow0 = warp * RO * 32;
-    uint4 wo0[NI];
+    uint4 wo0[INT4 ? 1 : NI];
+    constexpr int OG = 4;                             // int4: groups of an output-weight row (xw = 128), or fewer
+    uint4 wo4[INT4 ? RO * OG : 1];                    // int4: a thread owns rows threadIdx.x + 256 i
+    float wog[INT4 ? RO * OG : 1];
+    const int og = XW / 32;
+    if (INT4) {
 #pragma unroll
-    for (int u = 0; u < NI; ++u) {
-        const int r = wrow0 + u * RPI + lr;
-        wo0[u] = r < W ? ldg_pinned(reinterpret_cast<const uint4 *>(p.wo + (long)r * XW) + lp) : make_uint4(0u, 0u, 0u, 0u);
+        for (int i = 0; i < RO; ++i) {
+            const int r = (int)threadIdx.x + i * XB_THREADS;
+#pragma unroll
+            for (int g = 0; g < OG; ++g) {
+                const bool ok = r < W && g < og;
+                wo4[i * OG + g] = ok ? ldg_pinned(reinterpret_cast<const uint4 *>(p.wo + (long)r * (XW / 2)) + g) : make_uint4(0u, 0u, 0u, 0u);
+                wog[i * OG + g] = ok ? __ldg(p.wo_scales + (long)r * og + g) : 0.0f;
+            }
+        }
+    } else {
+#pragma unroll
+        for (int u = 0; u < NI; ++u) {
+            const int r = wrow0 + u * RPI + lr;
+            wo0[u] = r < W ? ldg_pinned(reinterpret_cast<const uint4 *>(p.wo + (long)r * XW) + lp) : make_uint4(0u, 0u, 0u, 0u);
+        }
     }
     // after the exchange below this lane holds the sums of loads ubase .. ubase + RO - 1
     int ubase = 0;
@@ -225,7 +288,7 @@ k_cross_block(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
 #pragma unroll
     for (int i = 0; i < RO; ++i) {
         const int r = wrow0 + (ubase + i) * RPI + lr;
-        wos0[i] = r < W ? __ldg(p.wo_scales + r) : 0.0f;
+        wos0[i] = (!INT4 && r < W) ? __ldg(p.wo_scales + r) : 0.0f;
     }
     __syncthreads();
 
@@ -369,7 +432,26 @@ k_cross_block(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
 
     XB_TICK(6);
     // ---- output product added to the residual row
-    {
+    if (INT4) {
+#pragma unroll
+        for (int i = 0; i < RO; ++i) {
+            const int r = (int)threadIdx.x + i * XB_THREADS;
+            if (r < W) {
+                float acc = 0.0f;
+#pragma unroll
+                for (int g = 0; g < OG; ++g) {
+                    if (g < og) {
+                        const uint4 x0 = reinterpret_cast<const uint4 *>(ctxq)[2 * g];
+                        const uint4 x1 = reinterpret_cast<const uint4 *>(ctxq)[2 * g + 1];
+                        acc = __fadd_rn(acc, __fmul_rn((float)dot_q4_group(wo4[i * OG + g], x0, x1), wog[i * OG + g]));
+                    }
+                }
+                const float xn = __fadd_rn(xres[r], __fmul_rn(acc, sxc));
+                row[r] = xn;
+                xg[r] = xn;
+            }
+        }
+    } else {
         const uint4 creg = reinterpret_cast<const uint4 *>(ctxq)[lp];
         int part[NI];
 #pragma unroll
@@ -436,6 +518,8 @@ extern "C" int mb_cross_block(const mb_cross_block_args *a, mb_stream stream) {
         a->v_cache == nullptr || a->qx == nullptr || a->sx == nullptr || a->batch == 0)
         return (int)cudaErrorInvalidValue;
     if (!mb_cross_block_supported(a->width, a->xw, a->rows)) return (int)cudaErrorInvalidValue;
+    if (a->qtype != MB_INT8 && a->qtype != MB_INT4) return (int)cudaErrorInvalidValue;
+    if (a->qtype == MB_INT4 && ((a->width % 32u) != 0 || (a->xw % 32u) != 0)) return (int)cudaErrorInvalidValue;
     if ((((uintptr_t)a->k_cache | (uintptr_t)a->v_cache | (uintptr_t)a->wq | (uintptr_t)a->wo | (uintptr_t)a->x |
           (uintptr_t)a->qx) & 15u) != 0 ||
         (a->slot_stride % a->xw) != 0 || (a->batch > 1 && a->cache_rows == 0))
@@ -464,10 +548,13 @@ extern "C" int mb_cross_block(const mb_cross_block_args *a, mb_stream stream) {
     cudaStream_t s = (cudaStream_t)stream;
     const dim3 grid((unsigned)a->batch), block(XB_THREADS);
     const int lpr = (int)(a->xw / 16u);
+    const bool int4 = a->qtype == MB_INT4;
 #define XB_CASE(RO_, LPR_) \
     if (ro == RO_ && lpr == LPR_) { \
-        if (a->strict) mb_launch(k_cross_block<RO_, LPR_, true>, grid, block, smem, s, kmap, vmap, p); \
-        else mb_launch(k_cross_block<RO_, LPR_, false>, grid, block, smem, s, kmap, vmap, p); \
+        if (a->strict && int4) mb_launch(k_cross_block<RO_, LPR_, true, true>, grid, block, smem, s, kmap, vmap, p); \
+        else if (a->strict) mb_launch(k_cross_block<RO_, LPR_, true, false>, grid, block, smem, s, kmap, vmap, p); \
+        else if (int4) mb_launch(k_cross_block<RO_, LPR_, false, true>, grid, block, smem, s, kmap, vmap, p); \
+        else mb_launch(k_cross_block<RO_, LPR_, false, false>, grid, block, smem, s, kmap, vmap, p); \
     }
     XB_CASE(1, 2); XB_CASE(1, 8); XB_CASE(2, 8); XB_CASE(3, 8); XB_CASE(4, 8);
 #undef XB_CASE
@@ -486,15 +573,12 @@ int mynah_b200_debug_cross_block_ticks(unsigned long long *host, size_t n) {
 extern "C" int mb_cross_block_init(void) {
     int rc = 0;
     const int bytes = 225 * 1024;
-    rc |= (int)cudaFuncSetAttribute(k_cross_block<1, 2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    rc |= (int)cudaFuncSetAttribute(k_cross_block<1, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    rc |= (int)cudaFuncSetAttribute(k_cross_block<1, 8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    rc |= (int)cudaFuncSetAttribute(k_cross_block<1, 8, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    rc |= (int)cudaFuncSetAttribute(k_cross_block<2, 8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    rc |= (int)cudaFuncSetAttribute(k_cross_block<2, 8, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    rc |= (int)cudaFuncSetAttribute(k_cross_block<3, 8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    rc |= (int)cudaFuncSetAttribute(k_cross_block<3, 8, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    rc |= (int)cudaFuncSetAttribute(k_cross_block<4, 8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    rc |= (int)cudaFuncSetAttribute(k_cross_block<4, 8, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+#define XB_ATTR(RO_, LPR_) \
+    rc |= (int)cudaFuncSetAttribute(k_cross_block<RO_, LPR_, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes); \
+    rc |= (int)cudaFuncSetAttribute(k_cross_block<RO_, LPR_, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes); \
+    rc |= (int)cudaFuncSetAttribute(k_cross_block<RO_, LPR_, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes); \
+    rc |= (int)cudaFuncSetAttribute(k_cross_block<RO_, LPR_, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    XB_ATTR(1, 2) XB_ATTR(1, 8) XB_ATTR(2, 8) XB_ATTR(3, 8) XB_ATTR(4, 8)
+#undef XB_ATTR
     return rc;
 }

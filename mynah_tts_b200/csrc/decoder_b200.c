@@ -784,10 +784,11 @@ static int enqueue(mb_decoder *d, size_t bucket, int mode, unsigned *count) {
         } else {
             P(PC_O_SELF, product(d, &L->o_self, NULL, d->attn, d->x, W, nb, MB_EPI_RESIDUAL, count));
         }
-        /* int8: the whole cross-attention block, with the norm before the feed-forward
+        /* int8 and int4: the whole cross-attention block, with the norm before the feed-forward
          * product, is one launch with one CTA per stream */
-        const int xb = d->use_xblock && q && L->q_cross.qtype == MB_INT8 &&
-                       L->o_cross.qtype == MB_INT8 && L->ffn_up.qtype == MB_INT8 &&
+        const int xq = L->q_cross.qtype;
+        const int xb = d->use_xblock && q && (xq == MB_INT8 || (xq == MB_INT4 && W % 32u == 0 && XW % 32u == 0)) &&
+                       L->o_cross.qtype == xq && (L->ffn_up.qtype == MB_INT8 || L->ffn_up.qtype == MB_INT4) &&
                        mb_cross_block_supported(W, XW, d->T);
         if (xb) {
             mb_cross_block_args cb;
@@ -795,6 +796,7 @@ static int enqueue(mb_decoder *d, size_t bucket, int mode, unsigned *count) {
             cb.x = d->x;
             cb.gain_query = L->norm_xattn_query;
             cb.gain_ff = L->norm_pos_ff;
+            cb.qtype = xq;
             cb.wq = (const int8_t *)L->q_cross.w;
             cb.wq_scales = L->q_cross.scales;
             cb.wo = (const int8_t *)L->o_cross.w;

@@ -317,10 +317,11 @@ typedef struct {
     float *x;                    /* [batch][width] residual rows, updated in place */
     const float *gain_query;     /* [width] */
     const float *gain_ff;        /* [width] */
-    const int8_t *wq;            /* [xw][width] row-major */
-    const float *wq_scales;      /* [xw] */
-    const int8_t *wo;            /* [width][xw] row-major */
-    const float *wo_scales;      /* [width] */
+    int qtype;                   /* MB_INT8 or MB_INT4: the format of both weights */
+    const int8_t *wq;            /* int8 [xw][width] row-major; int4 [xw][width / 2] */
+    const float *wq_scales;      /* int8 [xw]; int4 [xw][width / 32] */
+    const int8_t *wo;            /* int8 [width][xw] row-major; int4 [width][xw / 2] */
+    const float *wo_scales;      /* int8 [width]; int4 [width][xw / 32] */
     const float *k_cache;        /* cross K rows of this layer, slot 0 */
     const float *v_cache;
     size_t slot_stride;          /* floats between slots */

@@ -112,25 +112,25 @@ def test_stream_result_does_not_depend_on_batch(strict, tiny_model, tiny_memory)
 
 
 @pytest.mark.parametrize("strict", [False, True])
-@pytest.mark.parametrize("shape_name", ["tiny", "full"])
-def test_cross_block_launch_matches_separate_launches(shape_name, strict, tiny_model, tiny_memory, monkeypatch):
+@pytest.mark.parametrize("shape_name,name", [("tiny", "int8"), ("full", "int8"), ("tiny", "int4"), ("full", "int4")])
+def test_cross_block_launch_matches_separate_launches(shape_name, name, strict, tiny_model, tiny_memory, monkeypatch):
     """The one-launch cross-attention block (norm, query product, attention, output
-    product, norm) gives the bits of the five launches it replaces, and the tensor-core
-    product split along K over a cluster the bits of the unsplit one, at 1, 2, 5, 16 and
-    64 streams with different rows and staggered positions."""
+    product, norm; int8 or int4 weights) gives the bits of the five launches it replaces,
+    and the tensor-core product split along K over a cluster the bits of the unsplit one, at
+    1, 2, 5, 16 and 64 streams with different rows and staggered positions."""
     if shape_name == "tiny":
         shape, model, memory = synth.TINY, tiny_model, tiny_memory
     else:
         shape = synth.MAGPIE_357M
         model = synth.make_model(shape, seed=31)
         memory = synth.make_memory(shape, seed=131)
-    pm = O.PortModel(model, O.INT8)
+    pm = O.PortModel(model, QT[name])
     ps = pm.new_stream(memory, 4)
     ck, cv = ps.cross_k.copy(), ps.cross_v.copy()
     ps.close(); pm.close()
     rng = np.random.default_rng(12)
     rows = rng.normal(0, 0.05, size=(3, 64, shape.width)).astype(np.float32)
-    outs = {}
+    outs, launches = {}, {}
     for mode in ("block", "separate", "unsplit"):
         monkeypatch.delenv("MYNAH_B200_NO_CROSS_BLOCK", raising=False)
         monkeypatch.delenv("MYNAH_B200_NO_KSPLIT", raising=False)
@@ -138,12 +138,13 @@ def test_cross_block_launch_matches_separate_launches(shape_name, strict, tiny_m
             monkeypatch.setenv("MYNAH_B200_NO_CROSS_BLOCK", "1")
         if mode == "unsplit":
             monkeypatch.setenv("MYNAH_B200_NO_KSPLIT", "1")
-        be = Backend("int8", strict=strict)
+        be = Backend(name, strict=strict)
         dec = Decoder(be, model, capacity=16, slots=64)
         for s in range(64):
             # every slot its own text states: a rolled copy of the same cross K/V
             dec.slot_load(s, np.roll(ck, s, axis=1), np.roll(cv, s, axis=1))
         got = []
+        launches0 = be.launch_count
         for batch in (1, 2, 5, 16, 64):
             for s in range(64):
                 dec.slot_set_length(s, s % 5)
@@ -151,10 +152,12 @@ def test_cross_block_launch_matches_separate_launches(shape_name, strict, tiny_m
             for t in range(3):
                 got.append(dec.step_batch(lanes, rows[t, :batch]).copy())
         outs[mode] = got
+        launches[mode] = be.launch_count - launches0
         dec.close(); be.close()
     for a, b, c in zip(outs["block"], outs["separate"], outs["unsplit"]):
         assert np.array_equal(a, b)
         assert np.array_equal(a, c)
+    assert launches["block"] < launches["separate"]          # the block really replaced launches
 
 
 def test_staggered_lengths_and_lane_masking(tiny_model, tiny_memory):
