@@ -1,5 +1,5 @@
-"""GPU parity tests of the local transformer and its sampler (the survey's first
-"next" row: src/graph.c:806-1656 in mynah-tts) through the C ABI.
+"""GPU parity tests of the local transformer and its sampler (src/graph.c:806-1656 in
+mynah-tts) through the C ABI.
 
 Strict mode must reproduce the reference bit for bit: hidden rows, greedy picks,
 top-k draws (so the xorshift64 states too), stored codes and EOS reports, at any
