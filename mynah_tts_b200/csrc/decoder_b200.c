@@ -35,6 +35,8 @@ typedef struct {
     float tc_scale[6];
     float *norm_xattn_memory;   /* optional: with kv_cross, lets a slot's cross K/V be made here */
     mb_dev_weight kv_cross;     /* f32 [2*xw, width]; the reference runs it unquantized */
+    void *kv_tc;                /* fast mode: the same as f16 hi/lo planes for the tensor-core product */
+    float kv_tc_scale;
 } dec_layer;
 
 typedef struct {
@@ -97,6 +99,7 @@ typedef struct mb_decoder {
     int *d_mem_len;             /* [slots] text states of the request in each slot (<= T) */
     size_t *slot_mem;           /* host mirror */
     float *pf_mem, *pf_nrm, *pf_kv;   /* prefill scratch: [T][W], [T][W], [T][2xw] */
+    void *pf_planes;                  /* fast mode: f16 hi/lo planes of the normalized text states, [2][T][W] */
     mb_local local;             /* layers == 0: not attached */
     cudaGraphExec_t graph[MODE_COUNT][MAX_BUCKETS];
     unsigned graph_launches[MODE_COUNT][MAX_BUCKETS];
@@ -191,7 +194,7 @@ void mynah_b200_decoder_destroy(void *decoder) {
         for (size_t l = 0; l < d->layers; ++l) {
             dec_layer *L = &d->L[l];
             cudaFree(L->norm_self); cudaFree(L->norm_xattn_query); cudaFree(L->norm_pos_ff);
-            cudaFree(L->norm_xattn_memory); mb_weight_release(&L->kv_cross);
+            cudaFree(L->norm_xattn_memory); mb_weight_release(&L->kv_cross); cudaFree(L->kv_tc);
             mb_weight_release(&L->qkv); mb_weight_release(&L->o_self);
             mb_weight_release(&L->q_cross); mb_weight_release(&L->o_cross);
             mb_weight_release(&L->ffn_up); mb_weight_release(&L->ffn_down);
@@ -217,7 +220,7 @@ void mynah_b200_decoder_destroy(void *decoder) {
                    d->self_v, d->cross_k, d->cross_v, d->x, d->nrm, d->qkv, d->attn, d->q_x,
                    d->xctx, d->hidden, d->out, d->rows_in, d->logits, d->qx, d->sx, d->xsplit, d->row_planes, d->partials,
                    d->counters, d->d_stage_in, d->d_stage_out, d->d_eos_frame, d->d_min_frames,
-                   d->d_history, d->d_mem_len, d->pf_mem, d->pf_nrm, d->pf_kv};
+                   d->d_history, d->d_mem_len, d->pf_mem, d->pf_nrm, d->pf_kv, d->pf_planes};
     for (size_t i = 0; i < sizeof(dev) / sizeof(dev[0]); ++i) cudaFree(dev[i]);
     void *pinned[] = {d->h_rows, d->h_out, d->h_stage_in, d->h_stage_out, d->h_ints, d->h_table};
     for (size_t i = 0; i < sizeof(pinned) / sizeof(pinned[0]); ++i)
@@ -304,6 +307,24 @@ int mynah_b200_decoder_create(void *state, const mynah_b200_decoder_desc *desc, 
         if (s->norm_xattn_memory != NULL && s->kv_cross_w != NULL) {
             D_TRY(upload_vec(&L->norm_xattn_memory, s->norm_xattn_memory, W, error, cap));
             D_TRY(mb_weight_build(st, s->kv_cross_w, 2u * XW, W, MB_F32, &L->kv_cross, error, cap));
+            if (ok && !st->strict && prefill_tc_wanted(W, 64u)) {
+                /* fast mode: the text states' K/V product runs on the tensor cores */
+                float amax = 0.0f;
+                for (size_t i = 0; i < 2u * XW * W; ++i) {
+                    const float v = fabsf(s->kv_cross_w[i]);
+                    if (v > amax) amax = v;
+                }
+                int ex = 0;
+                if (amax > 0.0f) {
+                    (void)frexpf(amax, &ex);
+                    ex = 14 - ex;
+                }
+                ex = ex > 30 ? 30 : (ex < -30 ? -30 : ex);
+                L->kv_tc_scale = ldexpf(1.0f, ex);
+                D_TRY(dmalloc(&L->kv_tc, mb_codec_tc_packed_halves(2u * XW, W, 1u) * 2u, error, cap));
+                if (ok) D_TRY(mb_cuda(mb_codec_tc_pack_weight((const float *)L->kv_cross.w, L->kv_tc, 2u * XW, W, 1u, L->kv_tc_scale,
+                                                              st->stream), "pack weight", error, cap));
+            }
         }
         D_TRY(mb_weight_build(st, s->qkv_w, 3u * W, W, q, &L->qkv, error, cap));
         D_TRY(mb_weight_build(st, s->o_self_w, W, W, q, &L->o_self, error, cap));
@@ -406,6 +427,7 @@ int mynah_b200_decoder_create(void *state, const mynah_b200_decoder_desc *desc, 
             D_TRY(dmalloc((void **)&d->pf_mem, d->T * W * sizeof(float), error, cap));
             D_TRY(dmalloc((void **)&d->pf_nrm, d->T * W * sizeof(float), error, cap));
             D_TRY(dmalloc((void **)&d->pf_kv, d->T * 2u * XW * sizeof(float), error, cap));
+            if (d->L[0].kv_tc != NULL) D_TRY(dmalloc(&d->pf_planes, 2u * d->T * W * 2u, error, cap));
         }
     }
     /* activations */
@@ -1028,16 +1050,30 @@ int mynah_b200_decoder_slot_prefill(void *decoder, size_t slot, const float *mem
     for (size_t l = 0; l < d->layers && rc == 0; ++l) {
         F_TRY(mb_layernorm(mem, nrm, d->L[l].norm_xattn_memory, NULL, M, W, 1.0e-5f, NULL, NULL, NULL,
                            st->strict, s), "layer norm of the memory");
-        mb_gemv_args g;
-        memset(&g, 0, sizeof(g));
-        mb_gemv_bind_weight(&g, &d->L[l].kv_cross, NULL);
-        g.x = nrm;
-        g.out = kv;
-        g.out_stride = 2u * XW;
-        g.batch = M;
-        g.epilogue = MB_EPI_STORE;
-        g.strict = st->strict;
-        F_TRY(mb_gemv(&g, s), "kv_net product");
+        if (d->pf_planes != NULL && d->L[l].kv_tc != NULL && d->use_tc) {
+            unsigned short *hi = (unsigned short *)d->pf_planes, *lo = hi + T * W;
+            F_TRY(mb_split_rows_f16(nrm, hi, lo, M, W, W, s), "split rows");
+            mb_codec_conv_tc_args t;
+            memset(&t, 0, sizeof(t));
+            t.x_planes = hi; t.x_plane_stride = T * W;
+            t.w_packed = d->L[l].kv_tc; t.scale = d->L[l].kv_tc_scale;
+            t.ic = W; t.oc = 2u * XW; t.length = M; t.kernel = 1u; t.dilation = 1u;
+            t.rows_out = kv; t.rows_stride = 2u * XW; t.rows_epilogue = MB_EPI_STORE;
+            t.status = d->d_status; t.sm_count = st->sm_count;
+            F_TRY(mb_codec_conv1d_tc(&t, s), "kv_net product");
+            st->launches += 1u;
+        } else {
+            mb_gemv_args g;
+            memset(&g, 0, sizeof(g));
+            mb_gemv_bind_weight(&g, &d->L[l].kv_cross, NULL);
+            g.x = nrm;
+            g.out = kv;
+            g.out_stride = 2u * XW;
+            g.batch = M;
+            g.epilogue = MB_EPI_STORE;
+            g.strict = st->strict;
+            F_TRY(mb_gemv(&g, s), "kv_net product");
+        }
         float *ck = d->cross_k + slot * cross_n + l * T * XW;
         float *cv = d->cross_v + slot * cross_n + l * T * XW;
         F_TRY(cudaMemcpy2DAsync(ck, XW * sizeof(float), kv, 2u * XW * sizeof(float), XW * sizeof(float), M,
