@@ -74,6 +74,8 @@ typedef struct mb_decoder {
     float *x, *nrm, *qkv, *attn, *q_x, *xctx, *hidden, *out, *rows_in, *logits;
     int8_t *qx;
     float *sx;
+    float *cand_v;              /* f32 heads: candidates of the fused projection + argmax */
+    unsigned *cand_i, *cand_counters;
     void *row_planes;           /* prefill on the tensor cores: f16 hi/lo planes of the rows feeding a product */
     void *xsplit;               /* f16 weights: the activations' two f16 planes for the tensor-core product */
     float *partials;
@@ -218,7 +220,7 @@ void mynah_b200_decoder_destroy(void *decoder) {
     }
     void *dev[] = {d->position, d->norm_out, d->emb, (void *)d->d_tables, d->heads_b, d->self_k,
                    d->self_v, d->cross_k, d->cross_v, d->x, d->nrm, d->qkv, d->attn, d->q_x,
-                   d->xctx, d->hidden, d->out, d->rows_in, d->logits, d->qx, d->sx, d->xsplit, d->row_planes, d->partials,
+                   d->xctx, d->hidden, d->out, d->rows_in, d->logits, d->qx, d->sx, d->xsplit, d->row_planes, d->cand_v, d->cand_i, d->cand_counters, d->partials,
                    d->counters, d->d_stage_in, d->d_stage_out, d->d_eos_frame, d->d_min_frames,
                    d->d_history, d->d_mem_len, d->pf_mem, d->pf_nrm, d->pf_kv, d->pf_planes};
     for (size_t i = 0; i < sizeof(dev) / sizeof(dev[0]); ++i) cudaFree(dev[i]);
@@ -447,6 +449,13 @@ int mynah_b200_decoder_create(void *state, const mynah_b200_decoder_desc *desc, 
     if (d->L != NULL && d->L[0].tc_w[0] != NULL) D_TRY(dmalloc(&d->row_planes, 2u * MB * F * 2u, error, cap));
     if (d->tables != 0) {
         D_TRY(dmalloc((void **)&d->logits, MB * d->tables * d->vocab * sizeof(float), error, cap));
+        if (q == MB_F32 && mb_heads_argmax_f32_supported(d->vocab, W)) {
+            const size_t nc = mb_heads_argmax_candidates(MB, d->tables, d->vocab);
+            D_TRY(dmalloc((void **)&d->cand_v, nc * sizeof(float), error, cap));
+            D_TRY(dmalloc((void **)&d->cand_i, nc * sizeof(unsigned), error, cap));
+            D_TRY(dmalloc((void **)&d->cand_counters, MB * d->tables * sizeof(unsigned), error, cap));
+            if (ok) D_TRY(mb_cuda((int)cudaMemset(d->cand_counters, 0, MB * d->tables * sizeof(unsigned)), "cudaMemset", error, cap));
+        }
         d->history_frames = d->capacity;
         D_TRY(dmalloc((void **)&d->d_history, d->history_frames * MB * d->tables * sizeof(unsigned), error, cap));
     }
@@ -908,7 +917,23 @@ static int enqueue(mb_decoder *d, size_t bucket, int mode, unsigned *count) {
         }
     }
     P(PC_NORM, norm(d, d->x, d->out, d->norm_out, nb, count));
-    if (mode == MODE_FRAME) {
+    if (mode == MODE_FRAME && d->cand_v != NULL && d->use_fuse1 && d->heads_w.qtype == MB_F32) {
+        /* f32 heads: projection and constrained pick in one launch (src/qmat.c:453-536) */
+        mb_heads_argmax_args ha;
+        memset(&ha, 0, sizeof(ha));
+        ha.w = (const float *)d->heads_w.w; ha.bias = d->heads_b; ha.x = d->out;
+        ha.tables = d->tables; ha.vocab = d->vocab; ha.k = W; ha.batch = nb;
+        ha.codebook_size = d->codebook_size; ha.eos_id = d->eos_id;
+        ha.allow_eos = d->d_allow_eos; ha.n_active = d->d_n_active;
+        ha.cand_v = d->cand_v; ha.cand_i = d->cand_i; ha.counters = d->cand_counters;
+        ha.tokens = d->d_tokens; ha.codes = d->d_codes; ha.eos_flag = d->d_eos_flag;
+        P(PC_HEADS, mb_heads_argmax_f32(&ha, s));
+        P(PC_ADVANCE, mb_frame_advance(d->d_lens, d->d_tokens, d->d_history, d->d_frame_idx,
+                                       d->d_eos_flag, d->d_eos_frame, d->d_allow_eos, nb,
+                                       d->max_batch, d->tables, d->d_min_frames, d->history_frames,
+                                       d->d_n_active, s));
+        *count += 2u;
+    } else if (mode == MODE_FRAME) {
         P(PC_HEADS, product(d, &d->heads_w, d->heads_b, d->out, d->logits, d->tables * d->vocab, nb,
                             MB_EPI_STORE, count));
         P(PC_ARGMAX, mb_argmax_rows(d->logits, nb * d->tables, d->vocab, d->codebook_size, d->eos_id,

@@ -18,6 +18,8 @@
 // rows.  Activations of a tile of BT streams are staged in shared memory once
 // per CTA; batch tiles are spread over grid.z (the weight stream is read once per
 // tile, from L2 after the first).
+#include <float.h>
+
 #include "common.cuh"
 #include "launch.h"
 
@@ -442,7 +444,30 @@ int launch_tiled(const GemvP &p, size_t groups, cudaStream_t s) {
 // while the chains run over the current 64 (shared memory, row pitch 65 so that the 32 rows
 // a warp reads fall into 32 banks), sixteen values staged in registers ahead of their adds.
 constexpr int SEQ_ROWS = 32, SEQ_LANES = 4, SEQ_KC = 64, SEQ_PITCH = SEQ_KC + 1;
-__global__ void __launch_bounds__(SEQ_ROWS * SEQ_LANES) k_gemv_f32_seq(GemvP p) {
+
+// ARGMAX: the rows are the logit heads ([tables * vocab][k]) and nothing is stored: the
+// constrained first-on-ties pick of every (stream, table) is made on the fly, the fused
+// projection + argmax of the reference's f32 greedy path (mynah_qmat_greedy_argmax,
+// src/qmat.c:453-536; serial kernel src/kernels.c:116-139).  A warp holds 32 consecutive
+// vocabulary entries of one stream: it reduces them to one candidate, and the last of the
+// table's vocab / 32 warps to arrive (a counter per stream and table) reduces the candidates
+// in index order.
+struct SeqArgmaxP {
+    int vocab, codebook_size, eos_id, tables;
+    const int *allow_eos;
+    float *cand_v;            // [batch][tables][vocab / 32]
+    unsigned *cand_i;
+    unsigned *counters;       // [batch][tables], zero between launches
+    unsigned *tokens, *codes; // [batch][tables]
+    int *eos_flag;            // [batch]
+};
+
+__device__ __forceinline__ void seq_better(float &v, unsigned &i, float ov, unsigned oi) {
+    if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+}
+
+template <bool ARGMAX>
+__global__ void __launch_bounds__(SEQ_ROWS * SEQ_LANES) k_gemv_f32_seq(GemvP p, SeqArgmaxP q) {
     __shared__ float ws[SEQ_ROWS * SEQ_PITCH];
     __shared__ __align__(16) float xs[SEQ_LANES * SEQ_KC];
     const int nb = min(p.batch, mb_lane_count(p.n_active));
@@ -514,6 +539,51 @@ __global__ void __launch_bounds__(SEQ_ROWS * SEQ_LANES) k_gemv_f32_seq(GemvP p) 
             __syncthreads();
         }
     }
+    if (ARGMAX) {
+        // warp lb = stream b0 + lb, lane r = vocabulary entry (r0 + r) % vocab of table (r0 + r) / vocab
+        const int b = b0 + lb;
+        if (b >= nb) return;                               // whole warp
+        const long row = r0 + r;
+        const int table = (int)(r0 / q.vocab), chunk = (int)((r0 % q.vocab) / SEQ_ROWS), nchunk = q.vocab / SEQ_ROWS;
+        const int idx = (int)(row % q.vocab);
+        const int allow = q.allow_eos != nullptr ? q.allow_eos[b] : 0;
+        float v = -FLT_MAX;
+        unsigned vi = 0xffffffffu;
+        if (row < p.n && (idx < q.codebook_size || (allow && idx == q.eos_id))) {
+            float y = a;
+            if (p.bias != nullptr) y = __fadd_rn(y, p.bias[row]);
+            if (y > -FLT_MAX) { v = y; vi = (unsigned)idx; }
+        }
+#pragma unroll
+        for (int m = 16; m >= 1; m >>= 1)
+            seq_better(v, vi, __shfl_xor_sync(MB_FULL, v, m), __shfl_xor_sync(MB_FULL, vi, m));
+        const size_t slot = ((size_t)b * q.tables + table);
+        unsigned ticket = 0;
+        if (r == 0) {
+            q.cand_v[slot * nchunk + chunk] = v;
+            q.cand_i[slot * nchunk + chunk] = vi;
+            __threadfence();
+            ticket = atomicAdd(q.counters + slot, 1u);
+        }
+        ticket = __shfl_sync(MB_FULL, ticket, 0);
+        if (ticket != (unsigned)(nchunk - 1)) return;
+        __threadfence();
+        v = -FLT_MAX;
+        vi = 0xffffffffu;
+        for (int c = r; c < nchunk; c += 32)
+            seq_better(v, vi, __ldcg(q.cand_v + slot * nchunk + c), __ldcg(q.cand_i + slot * nchunk + c));
+#pragma unroll
+        for (int m = 16; m >= 1; m >>= 1)
+            seq_better(v, vi, __shfl_xor_sync(MB_FULL, v, m), __shfl_xor_sync(MB_FULL, vi, m));
+        if (r == 0) {
+            q.counters[slot] = 0u;
+            const unsigned tok = vi == 0xffffffffu ? 0u : vi;
+            q.tokens[slot] = tok;
+            if (q.codes != nullptr) q.codes[slot] = tok < (unsigned)q.codebook_size ? tok : 0u;
+            if (q.eos_flag != nullptr && tok == (unsigned)q.eos_id) atomicOr(&q.eos_flag[b], 1);
+        }
+        return;
+    }
     if (!mine) return;
     if (p.bias != nullptr) a = __fadd_rn(a, p.bias[r0 + r]);
     store_out<true>(p, p.out, r0 + r, b0 + lb, a);
@@ -526,7 +596,7 @@ int launch_qt(const GemvP &p, size_t groups, bool tiled, cudaStream_t s) {
     if (STRICT && QT == MB_F32 && groups == 1 && (p.k % 4) == 0 &&
         ((reinterpret_cast<uintptr_t>(p.w) | reinterpret_cast<uintptr_t>(p.x)) & 15u) == 0) {
         const dim3 grid((unsigned)((p.n + SEQ_ROWS - 1) / SEQ_ROWS), (unsigned)((p.batch + SEQ_LANES - 1) / SEQ_LANES));
-        mb_launch(k_gemv_f32_seq, grid, dim3(SEQ_ROWS * SEQ_LANES), 0, s, p);
+        mb_launch(k_gemv_f32_seq<false>, grid, dim3(SEQ_ROWS * SEQ_LANES), 0, s, p, SeqArgmaxP{});
         return mb_check_launch();
     }
     if (!tiled || (STRICT && QT == MB_F32 && groups == 1)) {
@@ -643,4 +713,35 @@ extern "C" int mb_gemv(const mb_gemv_args *a, mb_stream stream) {
         default: return (int)cudaErrorInvalidValue;
     }
 #undef MB_DISPATCH
+}
+
+// The fused f32 projection + constrained argmax (see k_gemv_f32_seq<true>).  Every output's
+// sum runs in index order in both modes, so the pick is the reference's in strict mode and
+// deterministic in fast mode.
+extern "C" size_t mb_heads_argmax_candidates(size_t batch, size_t tables, size_t vocab) {
+    return batch * tables * (vocab / SEQ_ROWS);
+}
+
+extern "C" int mb_heads_argmax_f32_supported(size_t vocab, size_t k) {
+    return vocab != 0 && (vocab % SEQ_ROWS) == 0 && (k % 4u) == 0;
+}
+
+extern "C" int mb_heads_argmax_f32(const mb_heads_argmax_args *a, mb_stream stream) {
+    if (a == nullptr || a->w == nullptr || a->x == nullptr || a->cand_v == nullptr || a->cand_i == nullptr ||
+        a->counters == nullptr || a->tokens == nullptr || a->batch == 0 || a->tables == 0 ||
+        !mb_heads_argmax_f32_supported(a->vocab, a->k) || a->codebook_size > a->vocab ||
+        ((reinterpret_cast<uintptr_t>(a->w) | reinterpret_cast<uintptr_t>(a->x)) & 15u) != 0)
+        return (int)cudaErrorInvalidValue;
+    GemvP p;
+    memset(&p, 0, sizeof(p));
+    p.w = reinterpret_cast<const unsigned char *>(a->w); p.bias = a->bias; p.x = a->x;
+    p.n = (long)(a->tables * a->vocab); p.k = (long)a->k;
+    p.batch = (int)a->batch; p.n_active = a->n_active;
+    SeqArgmaxP q;
+    q.vocab = (int)a->vocab; q.codebook_size = (int)a->codebook_size; q.eos_id = (int)a->eos_id; q.tables = (int)a->tables;
+    q.allow_eos = a->allow_eos; q.cand_v = a->cand_v; q.cand_i = a->cand_i; q.counters = a->counters;
+    q.tokens = a->tokens; q.codes = a->codes; q.eos_flag = a->eos_flag;
+    const dim3 grid((unsigned)(p.n / SEQ_ROWS), (unsigned)((a->batch + SEQ_LANES - 1) / SEQ_LANES));
+    mb_launch(k_gemv_f32_seq<true>, grid, dim3(SEQ_ROWS * SEQ_LANES), 0, (cudaStream_t)stream, p, q);
+    return mb_check_launch();
 }

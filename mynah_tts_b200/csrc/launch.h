@@ -156,6 +156,25 @@ typedef struct {
 } mb_gemv_args;
 int mb_gemv(const mb_gemv_args *args, mb_stream stream);
 
+/* The f32 logit heads and the constrained first-on-ties pick in one launch (the reference's
+ * fused f32 greedy path, src/qmat.c:453-536): w [tables * vocab][k] f32, x [batch][k] f32;
+ * candidates: ids below codebook_size, plus eos_id where allow_eos[stream]; writes
+ * tokens[stream][table], the stored code (non-codes collapse to 0) and ORs eos_flag[stream].
+ * cand_v / cand_i hold mb_heads_argmax_candidates() entries; counters [batch][tables] are zero
+ * before the first launch (the kernel leaves them zero).  vocab a multiple of 32, k of 4. */
+typedef struct {
+    const float *w, *bias, *x;
+    size_t tables, vocab, k, batch, codebook_size, eos_id;
+    const int *allow_eos, *n_active;
+    float *cand_v;
+    unsigned *cand_i, *counters;
+    unsigned *tokens, *codes;
+    int *eos_flag;
+} mb_heads_argmax_args;
+size_t mb_heads_argmax_candidates(size_t batch, size_t tables, size_t vocab);
+int mb_heads_argmax_f32_supported(size_t vocab, size_t k);
+int mb_heads_argmax_f32(const mb_heads_argmax_args *args, mb_stream stream);
+
 /* Tensor-core (tcgen05) form of the product: int8 weights from 16 lanes, int4 (group 32)
  * weights from 48 lanes; same arguments and same bits as mb_gemv.  qx_rows_alloc: rows
  * the activation buffer holds. */

@@ -689,3 +689,43 @@ def test_slot_prefill_makes_the_reference_cross_kv(strict, tiny_model, tiny_memo
     with pytest.raises(MynahB200Error):
         dec.slot_prefill(0, np.concatenate([tiny_memory, tiny_memory[:1]]))   # more rows than the slots hold
     dec.close(); be.close()
+
+
+@pytest.mark.parametrize("strict", [True, False])
+def test_f32_heads_and_pick_in_one_launch(strict, tiny_model, tiny_memory, golden, monkeypatch):
+    """f32 weights: the logit heads and the constrained first-on-ties pick run as one launch
+    (the reference's fused f32 greedy path, src/qmat.c:453-536).  Strict: the tokens of the
+    two-launch form (MYNAH_B200_NO_FUSE) at 1, 3 and 6 lanes with EOS allowed on some lanes;
+    fast: both forms keep one sequential sum per logit, so they agree there too."""
+    shape = synth.TINY
+    rng = np.random.default_rng(3)
+    got, launches = {}, {}
+    for mode in ("fused", "separate"):
+        monkeypatch.delenv("MYNAH_B200_NO_FUSE", raising=False)
+        if mode == "separate":
+            monkeypatch.setenv("MYNAH_B200_NO_FUSE", "1")
+        be = Backend("f32", strict=strict)
+        dec = Decoder(be, tiny_model, capacity=40, slots=6)
+        for s in range(6):
+            dec.slot_load(s, np.roll(golden["tiny_cross_k"], s, axis=1), np.roll(golden["tiny_cross_v"], s, axis=1))
+        out = []
+        l0 = be.launch_count
+        for lanes in ([0], [3, 1, 4], [5, 4, 3, 2, 1, 0]):
+            codes = rng.integers(0, shape.codebook_size, size=(len(lanes), shape.tables)).astype(np.uint32) \
+                if mode == "fused" else None
+            if mode == "fused":
+                got.setdefault("codes", []).append(codes)
+            codes = got["codes"][len(out) // 4]
+            for f in range(4):
+                tokens = dec.frame_batch(lanes, codes, [int((f + i) % 2) for i in range(len(lanes))])
+                out.append(tokens.copy())
+                codes = np.where(tokens < shape.codebook_size, tokens, 0).astype(np.uint32)
+        got[mode] = out
+        launches[mode] = be.launch_count - l0
+        dec.close(); be.close()
+    for a, b in zip(got["fused"], got["separate"]):
+        if strict:
+            assert np.array_equal(a, b)
+        else:
+            assert (a == b).mean() > 0.9          # the fast two-launch form sums its logits as a tree
+    assert launches["fused"] < launches["separate"]
