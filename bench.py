@@ -285,7 +285,9 @@ def frontend_extra(device: int) -> dict:
     enc = {"ids": 128, "shape": "6 layers x 768, 12 heads, kernel-3 causal convolution feed-forward, f32"}
     cod = {"frames": frames, "audio_s": frames / FRAME_RATE, "gflop_per_frame": flop / 1e9,
            "shape": "base 864, rates 8/8/4/2/2, f32; strict keeps one sequential f32 sum per output sample and "
-                    "the host libm's sinf bits (bit-identical samples), fast contracts to FMAs"}
+                    "the host libm's sinf bits (bit-identical samples, SIMT); fast runs the residual-layer "
+                    "convolutions on tcgen05 over split f16 planes (samples within 1e-4); a strict decoder may "
+                    "be paired with either (the codec's `arithmetic`)"}
     for mode in ("strict", "fast"):
         be = Backend("int8", strict=mode == "strict", device=device)
         te = TextEncoder(be, etensors, eshape)

@@ -459,6 +459,9 @@ typedef struct {
     mynah_b200_codec_stage stage[5];  /* rates 8, 8, 4, 2, 2; channels halve per stage */
     const float *post_alpha;          /* audio_decoder.post_activation.activation.snake_act.alpha [base / 32] */
     const float *post_w, *post_b;     /* audio_decoder.post_conv.conv.{weight [1, base / 32, 3], bias [1]} */
+    int arithmetic;           /* 0: the backend's mode; 1: reference order (bit-identical samples, SIMT);
+                                 2: tensor cores (samples within 1e-4) whatever the backend's mode -- the
+                                 audio comes after the token stream, so a strict decoder may pair with it */
 } mynah_b200_codec_desc;
 
 int mynah_b200_codec_create(void *state, const mynah_b200_codec_desc *desc, void **codec, char *error, size_t cap);

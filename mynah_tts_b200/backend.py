@@ -264,7 +264,8 @@ class TextEncoder:
 class Codec:
     """decode_codec over the reference-named tensors of synth.add_codec (or a real pack)."""
 
-    def __init__(self, backend: Backend, tensors: dict, shape, max_frames: int):
+    def __init__(self, backend: Backend, tensors: dict, shape, max_frames: int, arithmetic: int = 0):
+        """arithmetic: 0 the backend's mode, 1 reference order, 2 tensor cores."""
         self.backend, self.shape, self.max_frames = backend, shape, max_frames
         self._keep = []
 
@@ -273,7 +274,7 @@ class Codec:
             self._keep.append(a)
             return fp(a)
         desc = capi.CodecDesc()
-        desc.base, desc.max_frames = shape.base, max_frames
+        desc.base, desc.max_frames, desc.arithmetic = shape.base, max_frames, arithmetic
         desc.pre_w, desc.pre_b = p("audio_decoder.pre_conv.conv.weight"), p("audio_decoder.pre_conv.conv.bias")
         for s in range(5):
             st = desc.stage[s]

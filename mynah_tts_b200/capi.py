@@ -87,7 +87,8 @@ class CodecStage(C.Structure):
 
 class CodecDesc(C.Structure):
     _fields_ = [("base", sz), ("max_frames", sz), ("pre_w", c_float_p), ("pre_b", c_float_p),
-                ("stage", CodecStage * 5), ("post_alpha", c_float_p), ("post_w", c_float_p), ("post_b", c_float_p)]
+                ("stage", CodecStage * 5), ("post_alpha", c_float_p), ("post_w", c_float_p), ("post_b", c_float_p),
+                ("arithmetic", C.c_int)]
 
 
 class Sampler(C.Structure):

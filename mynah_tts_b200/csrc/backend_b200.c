@@ -272,14 +272,17 @@ static void libm_tables_for(mb_state *st) {
     pthread_mutex_unlock(&g_libm_lock);
 }
 
-/* The sinf table (the codec's Snake activation), built on first use: strict backends that
- * never decode audio do not pay its 76 MB.  Returns NULL when strict mode is off or the
- * build failed (the codec then uses the correctly rounded value). */
+/* The sinf table (the codec's Snake activation), built on first use by a reference-order
+ * codec: backends that never decode audio that way do not pay its 76 MB.  Returns NULL when
+ * the tables are switched off or the build failed (the codec then uses the correctly rounded
+ * value). */
 const uint32_t *mb_libm_sin_table(mb_state *st) {
-    if (!st->strict || !st->libm_exact || st->device < 0 || st->device >= LIBM_MAX_DEVICES) return NULL;
+    if (st->device < 0 || st->device >= LIBM_MAX_DEVICES) return NULL;
+    const char *env = getenv("MYNAH_B200_LIBM_TABLES");
+    if (env != NULL && strcmp(env, "0") == 0) return NULL;
     pthread_mutex_lock(&g_libm_lock);
     static int tried[LIBM_MAX_DEVICES];
-    if (g_libm[st->device].tables.sin_tab == NULL && g_libm[st->device].state == 1 && !tried[st->device]) {
+    if (g_libm[st->device].tables.sin_tab == NULL && !tried[st->device]) {
         char msg[128];
         uint32_t *tab = NULL;
         tried[st->device] = 1;

@@ -47,6 +47,7 @@ typedef struct {
 typedef struct {
     mb_state *st;
     size_t base, max_frames;
+    int strict;               /* this codec's arithmetic (the backend's unless the descriptor says otherwise) */
     dev_conv pre, post;
     dev_stage stage[CODEC_STAGES];
     float *post_alpha;
@@ -170,10 +171,16 @@ int mynah_b200_codec_create(void *state, const mynah_b200_codec_desc *desc, void
     c->st = st;
     c->base = desc->base;
     c->max_frames = desc->max_frames;
-    c->sin_tab = mb_libm_sin_table(st);
+    if (desc->arithmetic < 0 || desc->arithmetic > 2) {
+        free(c);
+        mb_set_error(error, cap, "invalid codec arithmetic");
+        return -1;
+    }
+    c->strict = desc->arithmetic == 0 ? st->strict : desc->arithmetic == 1;
+    c->sin_tab = c->strict ? mb_libm_sin_table(st) : NULL;
     {
         const char *no_tc = getenv("MYNAH_B200_NO_TC");
-        c->use_tc = !st->strict && !(no_tc != NULL && strcmp(no_tc, "0") != 0);
+        c->use_tc = !c->strict && !(no_tc != NULL && strcmp(no_tc, "0") != 0);
     }
     int ok = 1;
 #define C_TRY(expr) do { if (ok && (expr) != 0) ok = 0; } while (0)
@@ -263,7 +270,7 @@ static void conv_defaults(const mb_codec *c, mb_codec_conv_args *g, const dev_co
     g->w_packed = w->w;
     g->bias = w->bias;
     g->ic = ic; g->oc = oc; g->length = length; g->kernel = kernel; g->dilation = dilation;
-    g->strict = c->st->strict;
+    g->strict = c->strict;
     g->sin_tab = c->sin_tab;
     g->sm_count = c->st->sm_count;
 }
@@ -294,7 +301,7 @@ static int codec_enqueue(mb_codec *c, size_t frames, int stop_after, size_t *res
         const dev_stage *D = &c->stage[si];
         const size_t nch = ch / 2u, nlen = len * codec_rates[si];
         /* c->a holds half-Snake(previous output) */
-        R_TRY(mb_codec_conv_transpose(c->a, D->up_w, D->up_b, c->up, ch, nch, len, codec_rates[si], st->strict, s));
+        R_TRY(mb_codec_conv_transpose(c->a, D->up_w, D->up_b, c->up, ch, nch, len, codec_rates[si], c->strict, s));
         const int raw_stage_out = stop_after == 2 + (int)si;
         const float *next_alpha = raw_stage_out ? NULL : (si + 1u < CODEC_STAGES ? c->stage[si + 1u].alpha : c->post_alpha);
         for (size_t b = 0; c->use_tc && b < CODEC_BRANCHES && rc == 0; ++b) {
@@ -331,7 +338,7 @@ static int codec_enqueue(mb_codec *c, size_t frames, int stop_after, size_t *res
             }
         }
         for (size_t b = 0; !c->use_tc && b < CODEC_BRANCHES && rc == 0; ++b) {
-            R_TRY(mb_codec_half_snake(c->up, c->act, D->block[b][0].in_alpha, nch, nlen, nch / 2u, st->strict, c->sin_tab, s));
+            R_TRY(mb_codec_half_snake(c->up, c->act, D->block[b][0].in_alpha, nch, nlen, nch / 2u, c->strict, c->sin_tab, s));
             for (size_t d = 0; d < CODEC_BLOCKS && rc == 0; ++d) {
                 const dev_block *B = &D->block[b][d];
                 /* residual = half-Snake_skip(conv_in(activated)) */

@@ -95,6 +95,24 @@ def test_codec_long_request_is_causal(strict):
     codec.close(); be.close()
 
 
+def test_codec_arithmetic_is_the_codecs_choice():
+    """A strict backend (token-identical decoder) may carry a tensor-core codec, and a fast one
+    a reference-order codec."""
+    shape = synth.TINY_CODEC
+    tensors = synth.add_codec(None, shape, seed=2)
+    codes = synth.make_codec_codes(shape, 8, 3)
+    want = O.Port.get().codec_decode(tensors, shape, codes)
+    strict_be, fast_be = Backend("int8", strict=True), Backend("int8", strict=False)
+    exact = Codec(fast_be, tensors, shape, max_frames=4, arithmetic=1)
+    quick = Codec(strict_be, tensors, shape, max_frames=4, arithmetic=2)
+    assert np.array_equal(exact.decode(codes), want)
+    got = quick.decode(codes)
+    assert not np.array_equal(got, want) and np.abs(got - want).max() < 1e-4
+    with pytest.raises(RuntimeError, match="arithmetic"):
+        Codec(fast_be, tensors, shape, max_frames=4, arithmetic=3)
+    exact.close(); quick.close(); strict_be.close(); fast_be.close()
+
+
 def test_codec_refusals():
     shape = synth.TINY_CODEC
     tensors = synth.add_codec(None, shape, seed=2)
