@@ -139,6 +139,96 @@ __global__ void __launch_bounds__(256) k_attn_strict(AttnP p) {
     }
 }
 
+// ------------------------------------------------------------------ short caches
+// A cache of at most 32 rows (the local transformer's: one row per stacked stream of the
+// frame): one CTA per stream, a thread per column.  Everything a thread needs from global
+// memory -- its column of V, then the rows of K -- is requested up front, so the launch is a
+// few memory round trips, not a ring of copies with its set-up and tail.  Every sum runs in
+// the reference's order (scores as one chain over the head's width, the denominator and each
+// context element as one chain over the rows), so strict mode gives the bits of the other
+// strict kernels; fast mode only swaps expf.
+constexpr int SMALL_ROWS = 32;
+template <bool STRICT>
+__global__ void __launch_bounds__(1024) k_attn_small(AttnP p) {
+    extern __shared__ float sm_small[];
+    __shared__ float red[33];
+    mb_pdl_wait();
+    mb_pdl_trigger();
+    const int b = blockIdx.x;
+    long pos, valid_l;
+    float *kc, *vc;
+    if (!lane_setup(p, b, pos, valid_l, kc, vc)) return;
+    const int valid = (int)valid_l, hw = p.hw, W = p.heads * p.hw;
+    float *qs = sm_small;                       // [W]
+    float *sc = qs + W;                         // [heads][SMALL_ROWS]
+    float *row = sc + p.heads * SMALL_ROWS;     // [W] the context row (for the quantization)
+    const int c = threadIdx.x;                  // this thread's column
+    float vr[SMALL_ROWS];
+    if (c < W) {
+        qs[c] = p.q[(long)b * p.q_stride + c];
+        float vnew = 0.0f;
+        if (p.k_new != nullptr) {
+            kc[pos * p.cache_stride + c] = p.k_new[(long)b * p.q_stride + c];
+            vnew = p.v_new[(long)b * p.q_stride + c];
+            vc[pos * p.cache_stride + c] = vnew;
+        }
+#pragma unroll
+        for (int s = 0; s < SMALL_ROWS; ++s)
+            vr[s] = s < valid ? ((p.k_new != nullptr && s == (int)pos) ? vnew : vc[(long)s * p.cache_stride + c]) : 0.0f;
+    }
+    __syncthreads();
+    // scores: a thread per (head, row), the row's hw values in registers sixteen at a time
+    for (int idx = threadIdx.x; idx < p.heads * valid; idx += blockDim.x) {
+        const int h = idx / valid, s = idx - h * valid;
+        const float *k = kc + (long)s * p.cache_stride + h * hw;
+        const float *qh = qs + h * hw;
+        float dot = 0.0f;
+        for (int d0 = 0; d0 < hw; d0 += 16) {
+            float kr[16];
+#pragma unroll
+            for (int j4 = 0; j4 < 4; ++j4) {
+                const float4 f = d0 + 4 * j4 < hw ? *reinterpret_cast<const float4 *>(k + d0 + 4 * j4) : make_float4(0.f, 0.f, 0.f, 0.f);
+                kr[4 * j4] = f.x; kr[4 * j4 + 1] = f.y; kr[4 * j4 + 2] = f.z; kr[4 * j4 + 3] = f.w;
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                if (d0 + j < hw) dot = __fadd_rn(dot, __fmul_rn(qh[d0 + j], kr[j]));
+        }
+        sc[h * SMALL_ROWS + s] = __fmul_rn(dot, p.scale);
+    }
+    __syncthreads();
+    // softmax of a head by one warp: lane s holds row s
+    for (int h = threadIdx.x >> 5; h < p.heads; h += blockDim.x >> 5) {
+        const int lane = threadIdx.x & 31;
+        const float a = lane < valid ? sc[h * SMALL_ROWS + lane] : -FLT_MAX;
+        const float m = warp_max(a);
+        const float e = lane < valid ? exp_ref<STRICT>(__fsub_rn(a, m), p.exp_tab) : 0.0f;
+        float den = 0.0f;
+        for (int s = 0; s < valid; ++s) den = __fadd_rn(den, __shfl_sync(MB_FULL, e, s));   // rows in order
+        float w;
+        if (p.inv_norm) w = __fmul_rn(e, den > 0.0f ? __fdiv_rn(1.0f, den) : 0.0f);
+        else w = __fdiv_rn(e, den);
+        if (lane < valid) sc[h * SMALL_ROWS + lane] = w;
+    }
+    __syncthreads();
+    float acc = 0.0f;
+    if (c < W) {
+        const float *w = sc + (c / hw) * SMALL_ROWS;
+#pragma unroll
+        for (int s = 0; s < SMALL_ROWS; ++s)
+            if (s < valid) acc = __fadd_rn(acc, __fmul_rn(w[s], vr[s]));
+        if (p.out != nullptr) p.out[(long)b * p.out_stride + c] = acc;
+    }
+    if (p.qx != nullptr) {
+        // per-row int8 quantization of the context (src/qmat.c:93-113), as mb_quant_rows
+        const float amax = block_max(c < W ? fabsf(acc) : 0.0f, red);
+        const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+        if (c < W) p.qx[(long)b * W + c] = (int8_t)min(127, max(-127, round_half_away(__fmul_rn(acc, inv))));
+        if (threadIdx.x == 0) p.sx[b] = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 0.0f;
+    }
+    (void)row;
+}
+
 
 }  // namespace
 #include "attn_exact.cuh"
@@ -767,6 +857,20 @@ extern "C" int mb_attention(const mb_attn_args *a, mb_stream stream) {
     // the cache capacity in `valid`.
     const long max_valid = (long)a->valid;
     if (max_valid <= 0) return (int)cudaErrorInvalidValue;
+    {
+        // at most 32 rows per stream: one CTA per stream, a thread per column
+        static const int no_small = env_int("MYNAH_B200_NO_SMALL_ATTN");
+        const size_t w = a->heads * a->head_width;
+        if (!no_small && max_valid <= SMALL_ROWS && w <= 1024u && (a->head_width % 4u) == 0 && (p.cache_stride % 4) == 0 &&
+            (((uintptr_t)a->k_cache) & 15u) == 0 && (p.slot_stride % 4) == 0 && (a->qx == nullptr || a->sx != nullptr)) {
+            const unsigned threads = (unsigned)((w + 31u) / 32u * 32u);
+            const size_t smem = (2u * w + a->heads * SMALL_ROWS) * sizeof(float);
+            if (a->strict) mb_launch(k_attn_small<true>, dim3((unsigned)p.batch), dim3(threads), smem, s, p);
+            else mb_launch(k_attn_small<false>, dim3((unsigned)p.batch), dim3(threads), smem, s, p);
+            if (a->launched != nullptr) *a->launched += 1u;
+            return mb_check_launch();
+        }
+    }
     p.max_chunks = (int)chunks_for((size_t)max_valid);
     const size_t width = a->heads * a->head_width;
     // heads per CTA (one warp each): all of them.  Whole cache rows per tile keep DRAM pages
