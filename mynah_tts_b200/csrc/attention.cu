@@ -861,7 +861,7 @@ extern "C" int mb_attention(const mb_attn_args *a, mb_stream stream) {
         // at most 32 rows per stream: one CTA per stream, a thread per column
         static const int no_small = env_int("MYNAH_B200_NO_SMALL_ATTN");
         const size_t w = a->heads * a->head_width;
-        if (!no_small && max_valid <= SMALL_ROWS && w <= 1024u && (a->head_width % 4u) == 0 && (p.cache_stride % 4) == 0 &&
+        if (!no_small && a->short_cache && max_valid <= SMALL_ROWS && w <= 1024u && (a->head_width % 4u) == 0 && (p.cache_stride % 4) == 0 &&
             (((uintptr_t)a->k_cache) & 15u) == 0 && (p.slot_stride % 4) == 0 && (a->qx == nullptr || a->sx != nullptr)) {
             const unsigned threads = (unsigned)((w + 31u) / 32u * 32u);
             const size_t smem = (2u * w + a->heads * SMALL_ROWS) * sizeof(float);

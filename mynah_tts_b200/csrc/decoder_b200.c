@@ -674,6 +674,7 @@ static int enqueue_local(mb_decoder *d, const float *first_rows, size_t nb, unsi
             a.status = d->d_status;
             a.sm_count = st->sm_count;
             a.early_prefetch = 1;   /* rows below t were appended at earlier positions of this frame */
+            a.short_cache = lt->capacity <= 32u;
             a.launched = count;
             L_TRY(mb_attention(&a, s));
             L_TRY(product(d, &L->o, NULL, d->attn, d->x, W, nb, MB_EPI_RESIDUAL, count));

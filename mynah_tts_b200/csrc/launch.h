@@ -317,6 +317,9 @@ typedef struct {
                            * launches before this one, so the kernel may request its first cache tiles
                            * before it waits for its predecessor (programmatic dependent launch) */
     unsigned *launched;   /* optional: incremented by the number of kernels the call enqueued */
+    int short_cache;      /* 1: a cache that never holds more than 32 rows (the local transformer's): take the
+                           * one-CTA-per-stream kernel.  Strict mode: the same bits as the other kernels; fast
+                           * mode: its own (sequential) sums, so a caller must use it for every call on that cache */
     int softmax_inverse;  /* strict: weights e * (1 / sum) as the reference's multi-row self attention forms
                            * them (softmax_row_inplace, src/graph.c:245-257), not e / sum */
 } mb_attn_args;
