@@ -210,7 +210,7 @@ def one_thread_reference(args) -> dict | None:
         return {"value": None, "error": str(exc)[:200]}
 
 
-def local_generate_extra(backend, streams: int, args) -> dict:
+def local_generate_extra(backend, streams: int, args, cpu: bool = True) -> dict:
     """The sampled generation loop with the local transformer (16 stacked streams, 2 local
     layers): embed -> decoder step -> 16 local positions with top-k draws, per frame, for
     `streams` requests; plus the same loop through the reference's own CPU functions on a
@@ -219,7 +219,7 @@ def local_generate_extra(backend, streams: int, args) -> dict:
     from oracle import oracle as O
     shape = synth.MAGPIE_357M_LOCAL
     model = synth.make_model(shape, seed=SEED + 7)
-    frames = 64
+    frames = 64 if cpu else max(1, min(64, args.frames))
     dec = Decoder(backend, model, capacity=frames + 8, slots=streams, max_batch=streams)
     for slot in range(streams):
         ck, cv = synthetic_cross_kv(shape, slot)
@@ -235,7 +235,7 @@ def local_generate_extra(backend, streams: int, args) -> dict:
                        "temperature 0.7, top-k 80", "frames_per_s": streams * frames / (ms / 1000.0),
            "us_per_frame": ms * 1000.0 / frames, "rtf_per_stream": (ms / 1000.0 / frames) * FRAME_RATE}
     dec.close()
-    if O.have_ref("fast"):
+    if cpu and O.have_ref("fast"):
         n, cpu_frames = min(streams, 16), 6
         rm = O.RefModel(model, O.INT8, "fast", threads=os.cpu_count() or 1)
         memory = synth.make_memory(shape, seed=SEED + 100)
@@ -483,7 +483,7 @@ def main():
     ap.add_argument("--cpu-frames", type=int, default=24, help="frames of the CPU baseline sample")
     ap.add_argument("--no-extras", action="store_true", help="only the headline job (no other mode, batch-1, "
                     "matrix-pool, partition sweep, f32 step, sampled loop, ragged int4, CPU baseline)")
-    ap.add_argument("--only", default="", choices=["", "gemv_pool", "batch1", "frontend", "codec"],
+    ap.add_argument("--only", default="", choices=["", "gemv_pool", "batch1", "frontend", "codec", "generate"],
                     help="profiling aid: run only this small case (a few launches, no JSON contract)")
     ap.add_argument("--start-position", type=int, default=0,
                     help="profiling aid: every job starts with this many (zero) rows already in each "
@@ -542,6 +542,11 @@ def main():
 
     if args.only == "frontend":
         print(json.dumps({"frontend": frontend_extra(local_rank)}))
+        return
+    if args.only == "generate":       # profiling aid: the sampled loop with the local transformer, --frames frames
+        gbe = Backend(args.quant, strict=strict, device=local_rank)
+        print(json.dumps({"generate": local_generate_extra(gbe, args.streams, args, cpu=False)}))
+        gbe.close()
         return
     if args.only == "codec":          # profiling aid: one small decode (64 frames) in the chosen mode
         from mynah_tts_b200.backend import Codec
