@@ -125,11 +125,15 @@ int mynah_cuda_argmax_dev(void *state, const float *dev_logits, size_t vocab, si
 int mynah_cuda_gelu_host(void *state, float *host_data, size_t n, char *error, size_t cap);
 int mynah_cuda_gelu_host_f64(void *state, float *host_data, size_t n, char *error, size_t cap);
 
-/* NanoCodec ops (src/backend.h:59-60,128-133).  snake_dev: device signal in place, HOST alpha.
- * im2col: device pointers.  conv1d: HOST input/output and host weight/bias as cache keys,
- * synchronous -- the contract of the reference's CUDA backend (gpu/cuda/backend_cuda.cu:
- * 746-810); kernels other than 3, 7, 11 return -1 so the caller keeps its CPU path.  The whole
- * codec as one device-resident pass is mynah_b200_codec_decode below. */
+/* NanoCodec ops (src/backend.h:59-61,128-133).  snake_dev: device signal in place, HOST alpha.
+ * im2col: device pointers.  conv1d: host weight/bias as cache keys; HOST input/output served
+ * synchronously (the contract of the reference's CUDA backend, gpu/cuda/backend_cuda.cu:746-810)
+ * and DEVICE input/output enqueued without a sync (what decode_codec_resident passes,
+ * src/graph.c:2552-2556) -- the kind of `in` decides; kernels other than 3, 7, 11 return -1 so
+ * the caller keeps its CPU path.  conv_transpose_dev (wired only for Metal in the reference;
+ * an integrator who wires the resident-attention ops must wire it too, or decode_codec_resident
+ * fails instead of falling back): the codec's shape only (one output channel per group, kernel
+ * = 2 * stride).  The whole codec as one device-resident pass is mynah_b200_codec_decode. */
 int mynah_cuda_snake_dev(void *state, float *dev_data, const float *alpha, size_t channels,
                          size_t length, size_t snake_channels, char *error, size_t cap);
 int mynah_cuda_im2col(void *state, const float *in, float *cols, int in_ch, int length, int kernel,
@@ -137,6 +141,9 @@ int mynah_cuda_im2col(void *state, const float *in, float *cols, int in_ch, int 
 int mynah_cuda_conv1d(void *state, const float *in, float *out, int in_ch, int out_ch, int length,
                       int kernel, int dilation, const float *weight, const float *bias,
                       char *error, size_t cap);
+int mynah_cuda_conv_transpose_dev(void *state, const float *in, float *out, int in_ch, int out_ch,
+                                  int length, int output_length, int kernel, int stride, int groups,
+                                  const float *weight, const float *bias, char *error, size_t cap);
 
 /* ===================================================================== *
  * Part 2: extensions (no counterpart in the reference's seam)

@@ -152,6 +152,8 @@ SIGNATURES = {
     "mynah_cuda_im2col": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, _E]),
     "mynah_cuda_conv1d": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
                                     C.c_int, c_float_p, c_float_p, _E]),
+    "mynah_cuda_conv_transpose_dev": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
+                                                C.c_int, C.c_int, C.c_int, c_float_p, c_float_p, _E]),
     "mynah_b200_open": (C.c_int, [C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_int, _E]),
     "mynah_b200_close": (None, [C.c_void_p]),
     "mynah_b200_set_stream": (C.c_int, [C.c_void_p, C.c_void_p, _E]),

@@ -948,10 +948,12 @@ int mynah_cuda_im2col(void *state, const float *in, float *cols, int in_ch, int 
     return 0;
 }
 
-/* conv1d (src/backend.h:60) as the reference's CUDA backend serves it: HOST input
- * [in_ch][length] and HOST output [out_ch][length], host weight [out_ch][in_ch * kernel] and
- * bias as cache keys, synchronous.  Shapes the convolution kernel does not take (a kernel
- * other than 3, 7, 11) return -1 and the caller keeps its CPU path. */
+/* conv1d (src/backend.h:60).  The reference calls it two ways: conv1d_causal hands HOST
+ * input/output (what its CUDA backend serves, gpu/cuda/backend_cuda.cu:746-810: synchronous),
+ * decode_codec_resident hands DEVICE buffers from dev_alloc (what its Metal backend serves,
+ * src/graph.c:2552-2556: enqueued, no sync).  The kind of `in` decides; weight and bias are
+ * host pointers used as cache keys either way.  Shapes the convolution kernel does not take
+ * (a kernel other than 3, 7, 11) return -1 and the caller keeps its CPU path. */
 int mynah_cuda_conv1d(void *state, const float *in, float *out, int in_ch, int out_ch, int length,
                       int kernel, int dilation, const float *weight, const float *bias,
                       char *error, size_t cap) {
@@ -962,24 +964,56 @@ int mynah_cuda_conv1d(void *state, const float *in, float *out, int in_ch, int o
         return -1;
     }
     const size_t ic = (size_t)in_ch, oc = (size_t)out_ch, L = (size_t)length, K = (size_t)kernel;
+    struct cudaPointerAttributes attr;
+    const int on_device = cudaPointerGetAttributes(&attr, in) == cudaSuccess && attr.type == cudaMemoryTypeDevice;
+    if (!on_device) (void)cudaGetLastError();      /* an unregistered host pointer is not an error here */
     const float *d_w = NULL, *d_b = NULL;
     if (mb_vector_cached(st, weight, oc * ic * K, &d_w, error, cap) != 0 ||
         mb_vector_cached(st, bias, oc, &d_b, error, cap) != 0) return -1;
     const size_t packed = mb_codec_conv_packed_floats(oc, ic, K);
-    if (grow((void **)&st->d_in, &st->d_in_cap, ic * L + packed, sizeof(float), error, cap) != 0 ||
-        grow((void **)&st->d_out, &st->d_out_cap, oc * L, sizeof(float), error, cap) != 0) return -1;
-    float *d_packed = st->d_in + ic * L;
-    MB_TRY(cudaMemcpyAsync(st->d_in, in, ic * L * sizeof(float), cudaMemcpyHostToDevice, st->stream), "host to device copy");
+    const size_t staged_in = on_device ? 0u : ic * L;
+    if (grow((void **)&st->d_in, &st->d_in_cap, staged_in + packed, sizeof(float), error, cap) != 0) return -1;
+    if (!on_device && grow((void **)&st->d_out, &st->d_out_cap, oc * L, sizeof(float), error, cap) != 0) return -1;
+    float *d_packed = st->d_in + staged_in;
+    if (!on_device)
+        MB_TRY(cudaMemcpyAsync(st->d_in, in, ic * L * sizeof(float), cudaMemcpyHostToDevice, st->stream), "host to device copy");
     MB_TRY(mb_codec_pack_conv_weight(d_w, d_packed, oc, ic, K, st->stream), "pack weight");
     mb_codec_conv_args g;
     memset(&g, 0, sizeof(g));
-    g.in = st->d_in; g.w_packed = d_packed; g.bias = d_b; g.out = st->d_out;
+    g.in = on_device ? in : st->d_in; g.w_packed = d_packed; g.bias = d_b; g.out = on_device ? out : st->d_out;
     g.ic = ic; g.oc = oc; g.length = L; g.kernel = K; g.dilation = (size_t)dilation;
     g.strict = st->strict; g.sm_count = st->sm_count;
     MB_TRY(mb_codec_conv1d(&g, st->stream), "conv1d");
     st->launches += 2;
-    MB_TRY(cudaMemcpyAsync(out, st->d_out, oc * L * sizeof(float), cudaMemcpyDeviceToHost, st->stream), "device to host copy");
-    MB_TRY(cudaStreamSynchronize(st->stream), "cudaStreamSynchronize");
+    if (!on_device) {
+        MB_TRY(cudaMemcpyAsync(out, st->d_out, oc * L * sizeof(float), cudaMemcpyDeviceToHost, st->stream), "device to host copy");
+        MB_TRY(cudaStreamSynchronize(st->stream), "cudaStreamSynchronize");
+    }
+    mb_clear_error(error, cap);
+    return 0;
+}
+
+/* conv_transpose_dev (src/backend.h:61; the reference wires it for Metal only): device input
+ * [in_ch][length] -> device output [out_ch][output_length], host weight [in_ch][out_ch / groups]
+ * [kernel] and bias as cache keys.  Served: the codec's shape -- one output channel per group,
+ * kernel = 2 * stride, output_length = length * stride (src/graph.c:2596-2601); anything else
+ * returns -1. */
+int mynah_cuda_conv_transpose_dev(void *state, const float *in, float *out, int in_ch, int out_ch, int length,
+                                  int output_length, int kernel, int stride, int groups, const float *weight,
+                                  const float *bias, char *error, size_t cap) {
+    SEAM_PROLOGUE();
+    if (in == NULL || out == NULL || weight == NULL || bias == NULL || in_ch <= 0 || out_ch <= 0 || length <= 0 ||
+        stride <= 0 || groups != out_ch || in_ch % out_ch != 0 || kernel != 2 * stride ||
+        (long)output_length != (long)length * stride) {
+        mb_set_error(error, cap, "conv_transpose shape is not served by the B200 backend");
+        return -1;
+    }
+    const float *d_w = NULL, *d_b = NULL;
+    if (mb_vector_cached(st, weight, (size_t)in_ch * (size_t)kernel, &d_w, error, cap) != 0 ||
+        mb_vector_cached(st, bias, (size_t)out_ch, &d_b, error, cap) != 0) return -1;
+    MB_TRY(mb_codec_conv_transpose(in, d_w, d_b, out, (size_t)in_ch, (size_t)out_ch, (size_t)length, (size_t)stride,
+                                   st->strict, st->stream), "conv_transpose");
+    st->launches += 1;
     mb_clear_error(error, cap);
     return 0;
 }

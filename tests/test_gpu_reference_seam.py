@@ -74,3 +74,29 @@ def test_reference_decoder_run_resident_path(shape_name, qtype, strict, tiny_mod
         assert np.array_equal(dg.self_k[:, :frames], dc.self_k[:, :frames])
         assert np.array_equal(dg.self_v[:, :frames], dc.self_v[:, :frames])
     dg.close(); dc.close(); gpu.close(); cpu.close()
+
+
+@pytest.mark.skipif(not (O.have_ref("b200") and O.have_ref("strict")), reason="compiled reference absent")
+@pytest.mark.parametrize("strict", [True, False])
+def test_reference_decode_codec_resident_path(strict, monkeypatch):
+    """With the resident ops wired, the reference's decode_codec takes decode_codec_resident
+    (src/graph.c:2511-2638): dev_alloc, h2d, conv1d on DEVICE buffers, snake_dev,
+    conv_transpose_dev, copy_dev, residual_inplace, scale_dev, clip_dev, d2h -- all served by
+    this library.  Against the reference's CPU build on the same codes: the resident form
+    scales the branch sum by 1/3 where the CPU form divides by 3, so the samples agree to
+    rounding, not bit for bit."""
+    import sys
+    import os as _os
+    sys.path.insert(0, _os.path.join(_os.path.dirname(_os.path.abspath(__file__)), "golden"))
+    import make_golden_frontend as G
+    shape = synth.CodecShape()
+    model = G.bare_model(lambda m: synth.add_codec(m, shape, seed=61))
+    gpu, cpu = _open_pair(model, O.F32, strict, monkeypatch)
+    assert gpu.backend_name == "cuda" and gpu.resident
+    for frames in (1, 3):
+        codes = synth.make_codec_codes(shape, 62 + frames, frames)
+        want = cpu.decode_codec(codes)
+        got = gpu.decode_codec(codes)
+        assert got.shape == want.shape == (frames * 1024,)
+        assert np.abs(got - want).max() < (2e-6 if strict else 1e-4), frames
+    gpu.close(); cpu.close()
