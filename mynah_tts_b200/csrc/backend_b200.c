@@ -722,10 +722,30 @@ int mynah_cuda_gelu_dev(void *state, float *dev_data, size_t n, char *error, siz
     return mynah_cuda_gelu_inplace(state, dev_data, n, error, cap);
 }
 
+/* 1 when `p` is memory a kernel may read (device or managed / registered host memory), 0 for a
+ * plain host pointer.  The reference's resident paths were written for a unified-memory
+ * device and hand some operands as host pointers. */
+static int device_readable(const void *p) {
+    struct cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return 0;
+    }
+    return attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged || attr.type == cudaMemoryTypeHost;
+}
+
 int mynah_cuda_residual_inplace(void *state, float *dev_out, const float *dev_in, size_t n,
                                 char *error, size_t cap) {
     SEAM_PROLOGUE();
     if (dev_out == NULL || dev_in == NULL) return -1;
+    if (!device_readable(dev_in)) {
+        /* local_step_device adds a row of the position table straight from the weight file
+         * (src/graph.c:1119-1121: a host pointer, fine on the reference's unified-memory
+         * device): stage it */
+        if (grow((void **)&st->d_in, &st->d_in_cap, n, sizeof(float), error, cap) != 0) return -1;
+        MB_TRY(cudaMemcpyAsync(st->d_in, dev_in, n * sizeof(float), cudaMemcpyHostToDevice, st->stream), "host to device copy");
+        dev_in = st->d_in;
+    }
     MB_TRY(mb_residual_add(dev_out, dev_in, n, st->stream), "residual add");
     st->launches += 1;
     mb_clear_error(error, cap);

@@ -100,3 +100,28 @@ def test_reference_decode_codec_resident_path(strict, monkeypatch):
         assert got.shape == want.shape == (frames * 1024,)
         assert np.abs(got - want).max() < (2e-6 if strict else 1e-4), frames
     gpu.close(); cpu.close()
+
+
+@pytest.mark.skipif(not (O.have_ref("b200") and O.have_ref("strict")), reason="compiled reference absent")
+@pytest.mark.parametrize("qtype", [O.INT8, O.F32])
+def test_reference_local_frame_device_path(qtype, monkeypatch):
+    """One request's stacked frame through the reference's own local transformer: with the
+    resident ops wired its local_step_device runs (src/graph.c:1101-1159, 1403-1520: copy_dev,
+    residual_inplace, layer_norm_inplace, matmul_d2d, self_attention_dev, gelu_inplace, the
+    head's matmul_d2d with bias, argmax_dev or d2h of the logits) through this library.
+    Strict mode, greedy and sampling: the codes, EOS reports and RNG state of its CPU build."""
+    shape = synth.TINY_LOCAL
+    model = synth.make_model(shape, seed=3)
+    gpu, cpu = _open_pair(model, qtype, True, monkeypatch)
+    assert gpu.resident
+    rng = np.random.default_rng(43)
+    for temp, topk, seed, allow in ((0.0, 0, 1, 1), (0.7, 8, 0x1234, 1), (1.3, 5, 99, 0)):
+        rows = rng.normal(0.0, 1.0, size=(1, shape.width)).astype(np.float32)
+        lg, lc = gpu.new_local(shape.vocab), cpu.new_local(shape.vocab)
+        got = gpu.local_frame([lg], rows, [temp], [topk], [seed], [allow])
+        want = cpu.local_frame([lc], rows, [temp], [topk], [seed], [allow])
+        assert np.array_equal(got[0], want[0]), (temp, topk)          # codes
+        assert np.array_equal(got[1], want[1]) and np.array_equal(got[2], want[2])
+        assert got[3] == want[3]                                       # xorshift state
+        lg.close(); lc.close()
+    gpu.close(); cpu.close()
