@@ -77,6 +77,27 @@ def test_reference_decoder_run_resident_path(shape_name, qtype, strict, tiny_mod
 
 
 @pytest.mark.skipif(not (O.have_ref("b200") and O.have_ref("strict")), reason="compiled reference absent")
+def test_reference_decode_codec_cpu_path_with_seam_ops(monkeypatch):
+    """MYNAH_METAL_CPU_CODEC=1 keeps the reference on its CPU codec loop (src/graph.c:2517-2518),
+    which still hands every convolution to the backend as HOST buffers (conv1d_causal,
+    src/graph.c:2033-2046) and every Snake through upload / snake_dev / download (half_snake,
+    src/graph.c:2262-2280).  Strict mode: one sequential sum per output and the host libm's
+    sinf, so the samples are the CPU build's bit for bit."""
+    import sys
+    import os as _os
+    sys.path.insert(0, _os.path.join(_os.path.dirname(_os.path.abspath(__file__)), "golden"))
+    import make_golden_frontend as G
+    monkeypatch.setenv("MYNAH_METAL_CPU_CODEC", "1")
+    shape = synth.CodecShape()
+    model = G.bare_model(lambda m: synth.add_codec(m, shape, seed=61))
+    gpu, cpu = _open_pair(model, O.F32, True, monkeypatch)
+    codes = synth.make_codec_codes(shape, 64, 2)
+    got, want = gpu.decode_codec(codes), cpu.decode_codec(codes)
+    assert np.array_equal(got, want)
+    gpu.close(); cpu.close()
+
+
+@pytest.mark.skipif(not (O.have_ref("b200") and O.have_ref("strict")), reason="compiled reference absent")
 @pytest.mark.parametrize("strict", [True, False])
 def test_reference_decode_codec_resident_path(strict, monkeypatch):
     """With the resident ops wired, the reference's decode_codec takes decode_codec_resident
