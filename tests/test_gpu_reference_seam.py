@@ -146,3 +146,24 @@ def test_reference_local_frame_device_path(qtype, monkeypatch):
         assert got[3] == want[3]                                       # xorshift state
         lg.close(); lc.close()
     gpu.close(); cpu.close()
+
+
+@pytest.mark.skipif(not (O.have_ref("b200") and O.have_ref("strict")), reason="compiled reference absent")
+def test_reference_encode_text_and_prefill_through_host_matmul(tiny_model, tiny_memory, monkeypatch):
+    """The reference's many-row paths keep their host loops and hand only the products to the
+    backend: encode_text (linear -> matmul with host buffers, graph_sgemm for the attention,
+    src/graph.c:259-265, 446-452) and decoder_run with count > 1 (src/graph.c:3506-3641).
+    Strict mode: the seam's f32 matmul and sgemm keep one sequential sum per output, so both
+    equal the CPU build bit for bit."""
+    enc = synth.TINY_ENCODER
+    model = type(tiny_model)(shape=tiny_model.shape, seed=tiny_model.seed, tensors=dict(tiny_model.tensors))
+    synth.add_encoder(model, enc, seed=91)
+    gpu, cpu = _open_pair(model, O.F32, True, monkeypatch)
+    ids = np.random.default_rng(8).integers(0, enc.vocab, size=21).astype(np.int32)
+    assert np.array_equal(gpu.encode_text(enc, ids), cpu.encode_text(enc, ids))
+    rows = np.random.default_rng(9).normal(0, 0.05, size=(20, tiny_model.shape.width)).astype(np.float32)
+    dg, dc = gpu.new_decoder(tiny_memory, 32), cpu.new_decoder(tiny_memory, 32)
+    got, want = dg.run(rows), dc.run(rows)
+    assert np.array_equal(got, want)
+    assert dg.length == dc.length == 20
+    dg.close(); dc.close(); gpu.close(); cpu.close()
