@@ -738,7 +738,10 @@ bool launch_exact(const mb_attn_args *a, AttnP &p, cudaStream_t s) {
     // Head groups per stream: enough CTAs to cover the SMs about one and a half times with
     // groups of three or more heads (cache rows are then read in runs of 768 bytes or more),
     // else the first count that covers them once, else as many groups as the shape allows.
-    int best_g = 0, best_depth = 0, cover_g = 0, cover_depth = 0;
+    int best_g = 0, best_depth = 0, cover_g = 0, cover_depth = 0, many_g = 0, many_depth = 0;
+    double many_fill = 0.0;
+    long many_off = 0;
+    int many_per_sm = 0;
     for (int g = 1; g <= p.heads; ++g) {
         if (p.heads % g != 0) continue;
         if (force_groups > 0 && g != force_groups) continue;
@@ -754,18 +757,39 @@ bool launch_exact(const mb_attn_args *a, AttnP &p, cudaStream_t s) {
         };
         // more CTAs than SMs: two of them share an SM if each still gets a ring of two tiles
         int depth = (long)p.batch * g > sms ? depth_for((size_t)110 * 1024) : 0;
+        const int per_sm = depth >= 2 ? 2 : 1;
         if (depth < 2) depth = depth_for((size_t)ROWS_SMEM_MAX);
         if (depth > 2 * ((p.max_chunks + mch - 1) / mch)) depth = 2 * ((p.max_chunks + mch - 1) / mch);
         if (force_depth > 0 && force_depth < depth) depth = force_depth;
         if (depth < 1) continue;
+        // many streams (128 or more): among groups of three or more heads keep the split whose
+        // CTAs fill whole waves best; of equally full ones the split closest to three waves, then
+        // the one that puts two CTAs on an SM (measured at position 256: 256 streams 140 / 116 /
+        // 100 / 109 us for 1 / 2 / 3 / 4 groups; 128 streams 63 / 67 / 60 us for 2 / 3 / 4 groups)
+        if (p.batch >= 128 && hg >= 3 && force_groups <= 0) {
+            const long ctas = (long)p.batch * g, slots = (long)sms * per_sm;
+            const long waves = (ctas + slots - 1) / slots;
+            const double fill = (double)ctas / (double)(waves * slots);
+            const long off = waves > 3 ? waves - 3 : 3 - waves;
+            if (many_g == 0 || fill > many_fill + 0.05 ||
+                (fill > many_fill - 0.05 && (off < many_off || (off == many_off && per_sm > many_per_sm)))) {
+                many_g = g; many_depth = depth; many_fill = fill > many_fill ? fill : many_fill; many_off = off;
+                many_per_sm = per_sm;
+            }
+        }
         best_g = g;
         best_depth = depth;
         if (force_groups > 0) break;
         if (cover_g == 0 && (long)p.batch * g >= sms) { cover_g = g; cover_depth = depth; }
-        if (2L * p.batch * g >= 3L * sms && hg >= 3) { cover_g = g; cover_depth = depth; break; }
+        if (2L * p.batch * g >= 3L * sms && hg >= 3) {
+            cover_g = g;
+            cover_depth = depth;
+            if (p.batch < 128) break;          // many streams: every split of three or more heads is weighed above
+        }
         if (hg < 3 && cover_g != 0) break;
     }
     if (cover_g != 0 && force_groups <= 0) { best_g = cover_g; best_depth = cover_depth; }
+    if (many_g != 0 && force_groups <= 0) { best_g = many_g; best_depth = many_depth; }
     if (best_g == 0) return false;
     const int hg = p.heads / best_g, cw = hg * p.hw;
     const int threads = cw > hg * 32 ? cw : hg * 32;

@@ -729,3 +729,29 @@ def test_f32_heads_and_pick_in_one_launch(strict, tiny_model, tiny_memory, golde
         else:
             assert (a == b).mean() > 0.9          # the fast two-launch form sums its logits as a tree
     assert launches["fused"] < launches["separate"]
+
+
+@pytest.mark.parametrize("lanes", [128, 256])
+def test_many_streams_match_their_solo_runs(lanes):
+    """128 and 256 streams stepped together (the attention launcher splits the heads of a
+    stream over three or four CTAs there, several waves deep): strict mode, long staggered
+    positions, every sampled lane's tokens equal the same stream stepped alone."""
+    shape = synth.MAGPIE_357M
+    model = synth.make_model(shape, seed=81)
+    rng = np.random.default_rng(82)
+    ck = rng.normal(0, 1, size=(shape.layers, shape.memory_length, shape.xattn_width)).astype(np.float32)
+    be = Backend("int8", strict=True)
+    dec = Decoder(be, model, capacity=300, slots=lanes)
+    for s in range(lanes):
+        dec.slot_load(s, np.roll(ck, s, axis=1), np.roll(ck, s + 1, axis=1))
+    start = rng.integers(0, shape.codebook_size, size=(lanes, shape.tables)).astype(np.uint32)
+    frames = 5
+    for s in range(lanes):
+        dec.slot_set_length(s, 200 + (s * 7) % 90)          # cached rows are zeros: positions matter, not contents
+    together, _, _, _ = dec.greedy(list(range(lanes)), start, frames, min_frames=10 ** 6)
+    for s in (0, 1, lanes // 2 + 3, lanes - 1):
+        dec.slot_set_length(s, 200 + (s * 7) % 90)
+        # the rows appended by the joint run lie beyond the reset length and are overwritten
+        solo, _, _, _ = dec.greedy([s], start[s:s + 1], frames, min_frames=10 ** 6)
+        assert np.array_equal(solo[:, 0], together[:, s]), s
+    dec.close(); be.close()
