@@ -412,15 +412,17 @@ def traffic_ratio(name: str):
                           f"commit {rec['commit']}, scaled by algorithmic bytes")
 
 
-def algorithmic_bytes(shape, name: str, batch: int, mean_len: float, qbytes: dict) -> float:
-    """Bytes one launch of a call site must move, each counted once."""
+def algorithmic_bytes(shape, name: str, batch: int, mean_len: float, qbytes: dict, split_quant: bool = False) -> float:
+    """Bytes one launch of a call site must move, each counted once.  split_quant: the self
+    attention leaves f32 rows only and a launch of its own quantizes them (strict mode, two or
+    more lanes, quantized weights)."""
     W, F, XW, T = shape.width, shape.ffn_width, shape.xattn_width, shape.memory_length
     act = 1 if qbytes["quantized"] else 4
 
     def product(n, k, wname, out_f32=True):
         return qbytes[wname] + batch * (k * act + 4 + n * 4 * (2 if wname in ("o_self", "o_cross", "ffn_down") else 1))
     if name == "self attention":
-        return batch * (2 * (mean_len + 1) * W * 4 + 2 * W * 4 + 3 * W * 4 + W * (4 + act))
+        return batch * (2 * (mean_len + 1) * W * 4 + 2 * W * 4 + 3 * W * 4 + W * (4 + (0 if split_quant else act)))
     if name == "cross attention":
         return batch * (2 * T * XW * 4 + XW * 4 + XW * (4 + act))
     if name.startswith("cross block"):
@@ -434,8 +436,10 @@ def algorithmic_bytes(shape, name: str, batch: int, mean_len: float, qbytes: dic
         return product(n, k, wname)
     if name == "layernorm(+quant)":
         return batch * W * (4 + 4 + act) + W * 4
-    if name == "hidden quant":
-        return batch * F * (4 + 1)
+    if name.startswith("row quantization"):
+        # the feed-forward hidden rows, and in strict mode at 2+ lanes the self-attention rows
+        # (one launch each per layer: the mean of the two)
+        return batch * (F + W) / 2 * (4 + 1) if split_quant else batch * F * (4 + 1)
     return 0.0
 
 
@@ -697,7 +701,9 @@ def main():
         name, (n_launch, t_ms) = max(prof.items(), key=lambda kv: kv[1][1])
         qbytes = weight_bytes_table(shape, args.quant)
         mean_len = args.start_position + (frames - 1) / 2.0
-        bytes_per_launch = algorithmic_bytes(shape, name, B, mean_len, qbytes)
+        split_quant = (args.mode == "strict" and B >= 2 and qbytes["quantized"] and
+                       os.environ.get("MYNAH_B200_NO_SPLIT_QUANT", "0") in ("", "0"))
+        bytes_per_launch = algorithmic_bytes(shape, name, B, mean_len, qbytes, split_quant)
         avg_s = t_ms / 1000.0 / max(n_launch, 1)
         achieved = bytes_per_launch / avg_s / 1e9
         ratio, provenance = traffic_ratio(name)

@@ -81,6 +81,7 @@ typedef struct mb_decoder {
     float *partials;
     unsigned *counters;
     int use_tc, use_fuse1, use_xblock;
+    int use_split_quant; /* strict: quantize the self-attention rows in a launch of their own (MYNAH_B200_NO_SPLIT_QUANT=1: off) */
     /* lane state */
     int *d_lens, *d_slots, *d_n_active, *d_allow_eos, *d_eos_flag, *d_eos_frame, *d_frame_idx, *d_status;
     int *d_min_frames;
@@ -126,7 +127,7 @@ enum { PC_INPUT = 0, PC_NORM, PC_QKV, PC_ATTN_SELF, PC_O_SELF, PC_Q_CROSS, PC_AT
 static const char *const prof_names[MYNAH_B200_PROFILE_CLASSES] = {
     "input(embed|position)", "layernorm(+quant)", "qkv product", "self attention", "o_self product",
     "q_cross product", "cross attention", "o_cross product", "ffn_up product(+gelu)",
-    "hidden quant", "ffn_down product", "heads product", "argmax", "advance",
+    "row quantization (attention rows|hidden rows)", "ffn_down product", "heads product", "argmax", "advance",
     "local transformer frame (all tables)",
     "cross block (norm|q product|cross attention|o product|norm)"};
 
@@ -473,6 +474,8 @@ int mynah_b200_decoder_create(void *state, const mynah_b200_decoder_desc *desc, 
         d->use_fuse1 = !(no_fuse != NULL && strcmp(no_fuse, "0") != 0);
         const char *no_xb = getenv("MYNAH_B200_NO_CROSS_BLOCK");
         d->use_xblock = !(no_xb != NULL && strcmp(no_xb, "0") != 0);
+        const char *no_sq = getenv("MYNAH_B200_NO_SPLIT_QUANT");
+        d->use_split_quant = !(no_sq != NULL && strcmp(no_sq, "0") != 0);
     }
     D_TRY(dmalloc((void **)&d->partials, partial_floats * sizeof(float), error, cap));
     D_TRY(dmalloc((void **)&d->counters, n_counters * sizeof(unsigned), error, cap));
@@ -798,8 +801,14 @@ static int enqueue(mb_decoder *d, size_t bucket, int mode, unsigned *count) {
         /* one lane: the output product quantizes the row in its own prologue, which spares the
          * attention's head groups their arrival counter and the gathering tail */
         const int o_fused = f1 && L->o_self.qtype == MB_INT8;
-        a.qx = (q && !o_fused) ? d->qx : NULL;
-        a.sx = (q && !o_fused) ? d->sx : NULL;
+        /* strict mode, two or more lanes: the attention leaves its rows in f32 and a launch of
+         * its own quantizes them.  The attention's head groups then need no arrival counter and
+         * no gathering tail, which costs more than the extra launch, hidden as it is behind its
+         * neighbours (measured 1.7% to 4.9% per step between 8 and 256 streams; fast mode, whose
+         * attention kernel is another, loses 0.8% and keeps the tail) */
+        const int q_sep = !o_fused && q && st->strict && nb >= 2 && d->use_split_quant;
+        a.qx = (q && !o_fused && !q_sep) ? d->qx : NULL;
+        a.sx = (q && !o_fused && !q_sep) ? d->sx : NULL;
         a.batch = nb;
         a.n_active = d->d_n_active;
         a.strict = st->strict;
@@ -811,7 +820,11 @@ static int enqueue(mb_decoder *d, size_t bucket, int mode, unsigned *count) {
         a.early_prefetch = 1;   /* lane state: previous step; cache rows below the position: earlier steps */
         a.launched = count;
         P(PC_ATTN_SELF, mb_attention(&a, s));
-        if (o_fused) {
+        if (q_sep) {
+            P(PC_QUANT, mb_quant_rows(d->attn, nb, W, d->qx, d->sx, d->d_n_active, s));
+            *count += 1u;
+            P(PC_O_SELF, product(d, &L->o_self, NULL, d->attn, d->x, W, nb, MB_EPI_RESIDUAL, count));
+        } else if (o_fused) {
             P(PC_O_SELF, product_fused(d, &L->o_self, NULL, d->attn, d->x, W, nb, MB_EPI_RESIDUAL, MB_FUSE_QUANT, NULL, count));
         } else {
             P(PC_O_SELF, product(d, &L->o_self, NULL, d->attn, d->x, W, nb, MB_EPI_RESIDUAL, count));

@@ -116,8 +116,10 @@ def test_stream_result_does_not_depend_on_batch(strict, tiny_model, tiny_memory)
 def test_cross_block_launch_matches_separate_launches(shape_name, name, strict, tiny_model, tiny_memory, monkeypatch):
     """The one-launch cross-attention block (norm, query product, attention, output
     product, norm; int8 or int4 weights) gives the bits of the five launches it replaces,
-    and the tensor-core product split along K over a cluster the bits of the unsplit one, at
-    1, 2, 5, 16 and 64 streams with different rows and staggered positions."""
+    the tensor-core product split along K over a cluster the bits of the unsplit one, and the
+    strict self attention followed by a quantizing launch the bits of the attention that
+    quantizes its rows in its own tail (MYNAH_B200_NO_SPLIT_QUANT), at 1, 2, 5, 16 and 64
+    streams with different rows and staggered positions."""
     if shape_name == "tiny":
         shape, model, memory = synth.TINY, tiny_model, tiny_memory
     else:
@@ -131,9 +133,12 @@ def test_cross_block_launch_matches_separate_launches(shape_name, name, strict, 
     rng = np.random.default_rng(12)
     rows = rng.normal(0, 0.05, size=(3, 64, shape.width)).astype(np.float32)
     outs, launches = {}, {}
-    for mode in ("block", "separate", "unsplit"):
+    for mode in ("block", "separate", "unsplit", "tail"):
         monkeypatch.delenv("MYNAH_B200_NO_CROSS_BLOCK", raising=False)
         monkeypatch.delenv("MYNAH_B200_NO_KSPLIT", raising=False)
+        monkeypatch.delenv("MYNAH_B200_NO_SPLIT_QUANT", raising=False)
+        if mode == "tail":
+            monkeypatch.setenv("MYNAH_B200_NO_SPLIT_QUANT", "1")
         if mode == "separate":
             monkeypatch.setenv("MYNAH_B200_NO_CROSS_BLOCK", "1")
         if mode == "unsplit":
@@ -154,10 +159,13 @@ def test_cross_block_launch_matches_separate_launches(shape_name, name, strict, 
         outs[mode] = got
         launches[mode] = be.launch_count - launches0
         dec.close(); be.close()
-    for a, b, c in zip(outs["block"], outs["separate"], outs["unsplit"]):
+    for a, b, c, d in zip(outs["block"], outs["separate"], outs["unsplit"], outs["tail"]):
         assert np.array_equal(a, b)
         assert np.array_equal(a, c)
+        assert np.array_equal(a, d)
     assert launches["block"] < launches["separate"]          # the block really replaced launches
+    if strict:
+        assert launches["tail"] < launches["block"]          # the quantizing launch really ran
 
 
 def test_staggered_lengths_and_lane_masking(tiny_model, tiny_memory):
