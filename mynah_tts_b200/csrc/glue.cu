@@ -16,8 +16,8 @@
 namespace {
 
 // ---------------------------------------------------------------- LayerNorm
-// One CTA per row.  Dynamic shared memory: the row, then the squares (strict form) or the
-// gain and the bias (fast form).
+// One CTA per row.  Dynamic shared memory: the row, then the squares and the gain (strict
+// form) or the gain and the bias (fast form).
 template <bool STRICT>
 __global__ void __launch_bounds__(256)
 k_layernorm(const float *__restrict__ in, float *__restrict__ out, const float *__restrict__ gain,
@@ -33,6 +33,9 @@ k_layernorm(const float *__restrict__ in, float *__restrict__ out, const float *
             gs[i] = __ldg(gain + i);
             if (bias != nullptr) bs[i] = __ldg(bias + i);
         }
+    } else {
+        // strict: gs holds the squares, the gain sits behind them
+        for (int i = threadIdx.x; i < width; i += blockDim.x) bs[i] = __ldg(gain + i);
     }
     const int live = mb_lane_count(n_active);
     mb_pdl_wait();
@@ -47,7 +50,7 @@ k_layernorm(const float *__restrict__ in, float *__restrict__ out, const float *
     float sxv;
     if (STRICT) {
         // the reference's two sequential chains (mean, variance); the squares sit behind the row
-        sxv = mb_ln_block_strict(row, width, gain, bias, eps, gs, stat, red, y_out, qx != nullptr, q);
+        sxv = mb_ln_block_strict(row, width, bs, bias, eps, gs, stat, red, y_out, qx != nullptr, q);
     } else {
         // the routine shared with the products' fused prologue
         sxv = mb_ln_block<1>(row, width, gs, bias == nullptr ? nullptr : bs, eps, red, y_out, qx != nullptr, q);
@@ -609,8 +612,8 @@ inline unsigned blocks_for(size_t n) { return (unsigned)((n + 255) / 256); }
 extern "C" int mb_layernorm(const float *in, float *out, const float *gain, const float *bias,
                             size_t rows, size_t width, float eps, int8_t *qx, float *sx,
                             const int *n_active, int strict, mb_stream stream) {
-    /* strict: the row and its squares; else the row, the gain and the bias slot */
-    const size_t smem = width * sizeof(float) * (strict ? 2u : 3u);
+    /* strict: the row, its squares and the gain; else the row, the gain and the bias slot */
+    const size_t smem = width * sizeof(float) * 3u;
     if (rows == 0 || width == 0 || smem > 48u * 1024u) return (int)cudaErrorInvalidValue;
     cudaStream_t s = (cudaStream_t)stream;
     if (strict)
