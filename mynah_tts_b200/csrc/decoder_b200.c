@@ -590,9 +590,9 @@ static int product(mb_decoder *d, const mb_dev_weight *w, const float *bias, con
     return product_fused(d, w, bias, act_f32, out, out_stride, nb, epilogue, MB_FUSE_NONE, NULL, count);
 }
 
-/* One lane, int8 weights: norms and the hidden-row quantization ride in the products that
- * consume them (every launch saved is ~5 us of the step), in strict mode with the
- * reference's summation order. */
+/* One lane, int8 weights: the norms and the attention row's quantization ride in the
+ * products that consume them, in strict mode with the reference's summation order (the
+ * hidden row's quantization stays a launch: 192 CTAs would each repeat it). */
 static int fuse_one_lane(const mb_decoder *d, size_t nb) {
     return nb == 1 && d->use_fuse1 && d->st->quant == MB_INT8;
 }
@@ -867,14 +867,13 @@ static int enqueue(mb_decoder *d, size_t bucket, int mode, unsigned *count) {
             P(PC_XBLOCK, mb_cross_block(&cb, s));
             *count += 1u;
             P(PC_FFN_UP, product(d, &L->ffn_up, NULL, d->nrm, d->hidden, F, nb, MB_EPI_GELU, count));
-            if (f1) {
-                P(PC_FFN_DOWN, product_fused(d, &L->ffn_down, NULL, d->hidden, d->x, W, nb, MB_EPI_RESIDUAL,
-                                             MB_FUSE_QUANT, NULL, count));
-            } else {
-                P(PC_QUANT, mb_quant_rows(d->hidden, nb, F, d->qx, d->sx, d->d_n_active, s));
-                *count += 1u;
-                P(PC_FFN_DOWN, product(d, &L->ffn_down, NULL, d->hidden, d->x, W, nb, MB_EPI_RESIDUAL, count));
-            }
+            /* the hidden row is quantized by a launch of its own at every lane count: in the
+             * product's prologue each of its 192 CTAs would take the absmax of all 3072 values
+             * first (one lane, measured: 481 -> 443 us per frame in fast mode without that
+             * prologue, strict unchanged) */
+            P(PC_QUANT, mb_quant_rows(d->hidden, nb, F, d->qx, d->sx, d->d_n_active, s));
+            *count += 1u;
+            P(PC_FFN_DOWN, product(d, &L->ffn_down, NULL, d->hidden, d->x, W, nb, MB_EPI_RESIDUAL, count));
             continue;
         }
         if (f1) {
@@ -918,8 +917,9 @@ static int enqueue(mb_decoder *d, size_t bucket, int mode, unsigned *count) {
         if (f1) {
             P(PC_FFN_UP, product_fused(d, &L->ffn_up, NULL, d->x, d->hidden, F, nb, MB_EPI_GELU, MB_FUSE_LN,
                                        L->norm_pos_ff, count));
-            P(PC_FFN_DOWN, product_fused(d, &L->ffn_down, NULL, d->hidden, d->x, W, nb, MB_EPI_RESIDUAL,
-                                         MB_FUSE_QUANT, NULL, count));
+            P(PC_QUANT, mb_quant_rows(d->hidden, nb, F, d->qx, d->sx, d->d_n_active, s));
+            *count += 1u;
+            P(PC_FFN_DOWN, product(d, &L->ffn_down, NULL, d->hidden, d->x, W, nb, MB_EPI_RESIDUAL, count));
         } else {
             P(PC_NORM, norm(d, d->x, d->nrm, L->norm_pos_ff, nb, count));
             P(PC_FFN_UP, product(d, &L->ffn_up, NULL, d->nrm, d->hidden, F, nb, MB_EPI_GELU, count));
