@@ -684,8 +684,10 @@ static int enqueue_local(mb_decoder *d, const float *first_rows, size_t nb, unsi
             if (f1) {
                 L_TRY(product_fused(d, &L->ffn_up, NULL, d->x, d->hidden, F, nb, MB_EPI_GELU, MB_FUSE_LN,
                                     L->norm_ff, count));
-                L_TRY(product_fused(d, &L->ffn_down, NULL, d->hidden, d->x, W, nb, MB_EPI_RESIDUAL,
-                                    MB_FUSE_QUANT, NULL, count));
+                /* as in the decoder's layers: the hidden row is quantized once, by its own launch */
+                L_TRY(mb_quant_rows(d->hidden, nb, F, d->qx, d->sx, d->d_n_active, s));
+                *count += 1u;
+                L_TRY(product(d, &L->ffn_down, NULL, d->hidden, d->x, W, nb, MB_EPI_RESIDUAL, count));
             } else {
                 L_TRY(norm(d, d->x, d->nrm, L->norm_ff, nb, count));
                 L_TRY(product(d, &L->ffn_up, NULL, d->nrm, d->hidden, F, nb, MB_EPI_GELU, count));
