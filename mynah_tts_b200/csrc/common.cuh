@@ -192,19 +192,27 @@ __device__ __forceinline__ float mb_seq_sum(const float *v, int n) {
 // floats (16-byte aligned), `stat` of
 // two, `red` of 32 that no thread is still reading.  Returns the quantization scale (0 when
 // !quant) to every thread.  Same bits as k_layernorm<true>.
+// (MB_LN_TICK: a file of a profiling build may define it before this header to timestamp the
+// steps: 0 mean, 1 squares, 2 variance, 3 normalized, 4 absmax, 5 quantized.)
+#ifndef MB_LN_TICK
+#define MB_LN_TICK(i)
+#endif
 __device__ __forceinline__ float mb_ln_block_strict(float *row, int width, const float *__restrict__ gain,
                                                     const float *__restrict__ bias, float eps, float *sq, float *stat,
                                                     float *red, float *y_out, bool quant, int8_t *q) {
     if (threadIdx.x == 0) stat[0] = __fdiv_rn(mb_seq_sum(row, width), (float)width);
     __syncthreads();
+    MB_LN_TICK(0);
     const float mean = stat[0];
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
         const float d = __fsub_rn(row[i], mean);
         sq[i] = __fmul_rn(d, d);
     }
     __syncthreads();
+    MB_LN_TICK(1);
     if (threadIdx.x == 0) stat[1] = mb_seq_sum(sq, width);
     __syncthreads();
+    MB_LN_TICK(2);
     const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(stat[1], (float)width), eps)));
     float amax = 0.0f;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
@@ -214,11 +222,14 @@ __device__ __forceinline__ float mb_ln_block_strict(float *row, int width, const
         row[i] = y;                  // each thread rereads only its own elements below
         amax = fmaxf(amax, fabsf(y));
     }
+    MB_LN_TICK(3);
     if (!quant) return 0.0f;
     amax = block_max1(amax, red);
+    MB_LN_TICK(4);
     const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
     for (int i = threadIdx.x; i < width; i += blockDim.x)
         q[i] = (int8_t)min(127, max(-127, round_half_away(__fmul_rn(row[i], inv))));
+    MB_LN_TICK(5);
     return amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 0.0f;
 }
 

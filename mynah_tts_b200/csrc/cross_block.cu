@@ -19,6 +19,26 @@
 // products are exact int32 sums scaled as (float)s * ws * sx with each product rounded,
 // the attention is the chunked single-head form of k_attn_short (32-row chunks, ordered
 // merge), the quantizations round half away from zero.
+// Phase timestamps of profiling builds (make TICKS=1), 16 per CTA: 0 entry, 1 after the
+// dependency wait, 2 row loaded, 3 first norm, 4 query product, 5 attention, 6 context
+// quantized, 7 output product, 8 second norm; 9 .. 14 the steps inside the second norm (mean
+// chain, squares, variance chain, normalized, absmax, quantized: the first norm writes them
+// too and is overwritten).
+#ifdef MB_PHASE_TICKS
+__device__ unsigned long long g_xb_ticks[16 * 1024];
+__device__ __forceinline__ void xb_tick(int i) {
+    if (threadIdx.x == 0 && blockIdx.x < 1024u) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        g_xb_ticks[blockIdx.x * 16 + i] = t;
+    }
+}
+#define XB_TICK(i) xb_tick(i)
+#define MB_LN_TICK(i) xb_tick(9 + (i))
+#else
+#define XB_TICK(i)
+#endif
+
 #include "attn_tiles.cuh"
 #include "launch.h"
 
@@ -69,22 +89,6 @@ __device__ __forceinline__ int dot16(const uint4 &a, const uint4 &b, int acc) {
 // context as sequential chains, as k_attn_exact forms them) and the host libm's expf; the
 // K/V tiles then arrive as 128-byte-swizzled [32][32] boxes so that a warp whose threads
 // each walk one row reads 32 different banks.  Same bits as the separate strict launches.
-// Phase timestamps of profiling builds (make TICKS=1): see attn_exact.cuh.  0 entry, 1 after
-// the dependency wait, 2 row loaded, 3 first norm, 4 query product, 5 attention, 6 context
-// quantized, 7 output product, 8 second norm.
-#ifdef MB_PHASE_TICKS
-__device__ unsigned long long g_xb_ticks[16 * 1024];
-__device__ __forceinline__ void xb_tick(int i) {
-    if (threadIdx.x == 0 && blockIdx.x < 1024u) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        g_xb_ticks[blockIdx.x * 16 + i] = t;
-    }
-}
-#define XB_TICK(i) xb_tick(i)
-#else
-#define XB_TICK(i)
-#endif
 
 // One group of 32 int4 weights (16 packed bytes, even index in the low nibble, +8 offset) times
 // 32 int8 activations (two 16-byte pieces in natural order): the exact int32 sum.

@@ -625,6 +625,41 @@ extern "C" int mb_layernorm(const float *in, float *out, const float *gain, cons
     return mb_check_launch();
 }
 
+#ifdef MB_PHASE_TICKS
+// Profiling builds only (make TICKS=1): SM cycles per term of mb_seq_sum over `n` floats in
+// shared memory, one thread, `reps` sums in a row (n a multiple of 16, at most 4096).
+namespace {
+__global__ void k_seq_sum_cycles(int n, int reps, long long *cycles, float *sink) {
+    extern __shared__ __align__(16) float row[];
+    for (int i = threadIdx.x; i < n; i += blockDim.x) row[i] = (float)((i * 2654435761u) % 1000u) / 977.0f - 0.5f;
+    __syncthreads();
+    if (threadIdx.x != 0) return;
+    float acc = 0.0f;
+    const long long t0 = clock64();
+    for (int r = 0; r < reps; ++r) {
+        const float s = mb_seq_sum(row, n);
+        acc += s;
+        row[0] = row[0] + (s > 1e30f ? 1.0f : 0.0f);       // keeps the sums apart
+    }
+    *cycles = clock64() - t0;
+    *sink = acc;
+}
+}  // namespace
+extern "C" __attribute__((visibility("default")))
+int mynah_b200_debug_seq_sum_cycles(size_t n, size_t reps, double *cycles_per_term) {
+    if (n == 0 || (n % 16u) != 0 || n > 4096u || reps == 0 || cycles_per_term == nullptr) return -1;
+    long long *dc = nullptr;
+    float *ds = nullptr;
+    if (cudaMalloc((void **)&dc, sizeof(long long)) != cudaSuccess || cudaMalloc((void **)&ds, sizeof(float)) != cudaSuccess) return -1;
+    for (int pass = 0; pass < 2; ++pass) k_seq_sum_cycles<<<1, 256, n * sizeof(float)>>>((int)n, (int)reps, dc, ds);
+    long long c = 0;
+    const int rc = (int)cudaMemcpy(&c, dc, sizeof(c), cudaMemcpyDeviceToHost);
+    cudaFree(dc); cudaFree(ds);
+    *cycles_per_term = (double)c / (double)reps / (double)n;
+    return rc;
+}
+#endif
+
 extern "C" int mb_quant_rows(const float *in, size_t rows, size_t width, int8_t *qx, float *sx,
                              const int *n_active, mb_stream stream) {
     if (rows == 0 || width == 0) return (int)cudaErrorInvalidValue;
