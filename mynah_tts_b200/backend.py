@@ -487,6 +487,30 @@ class Decoder:
              None if hidden is None else fp(hidden), batch)
         return (tokens, hidden) if want_hidden else tokens
 
+    def bind_frame_batch(self, slots, codes: np.ndarray, allow_eos, tokens: np.ndarray):
+        """frame_batch for a loop that calls it every frame with the same buffers: the C
+        arguments (slot ids, EOS rule, the addresses of `codes` and `tokens`) are made once and
+        the returned function only makes the foreign call: it reads `codes` and fills `tokens`
+        as they are at that moment.  `codes` and `tokens` must be C-contiguous uint32 arrays of
+        [len(slots), tables] that outlive the returned function."""
+        batch = len(slots)
+        want = (batch, self.shape.tables)
+        for name, arr in (("codes", codes), ("tokens", tokens)):
+            if arr.dtype != np.uint32 or arr.shape != want or not arr.flags["C_CONTIGUOUS"]:
+                raise ValueError(f"{name} must be a C-contiguous uint32 array of shape {want}")
+        fn = capi.lib().mynah_b200_decoder_frame_batch
+        slot_arr = (C.c_uint * batch)(*slots)
+        allow = None if allow_eos is None else (C.c_int * batch)(*[int(a) for a in allow_eos])
+        codes_p, tokens_p = codes.ctypes.data_as(capi.c_uint_p), tokens.ctypes.data_as(capi.c_uint_p)
+        err = C.create_string_buffer(capi.ERR_CAP)
+        handle, keep = self.handle, (codes, tokens)
+
+        def step():
+            if fn(handle, slot_arr, codes_p, allow, tokens_p, None, batch, err, capi.ERR_CAP) != 0:
+                raise MynahB200Error(err.value.decode(errors="replace") or "frame_batch failed")
+            return keep[1]
+        return step
+
     @staticmethod
     def _samplers(batch, samplers):
         """samplers: None (greedy) or a list of (temperature, topk, rng_state[, allow_eos])."""

@@ -263,6 +263,36 @@ def test_decoder_errors(tiny_model, tiny_memory):
     dec.close(); be.close(); ps.close(); pm.close()
 
 
+def test_bound_frame_call_matches_frame_batch(golden, tiny_model):
+    """bind_frame_batch (arguments made once, one foreign call per frame on the caller's two
+    host buffers) gives frame_batch's tokens, frame after frame, and refuses buffers of the
+    wrong type or shape."""
+    shape = synth.TINY
+    start = np.concatenate([synth.make_codes(shape, seed=9 + g, frames=1) for g in range(3)])
+    be = Backend("int8", strict=True)
+    dec = Decoder(be, tiny_model, capacity=40, slots=6)
+    for s in range(6):
+        dec.slot_load(s, golden["tiny_cross_k"], golden["tiny_cross_v"])
+    codes = np.ascontiguousarray(start, np.uint32)
+    want = []
+    for f in range(12):
+        tokens = dec.frame_batch([0, 1, 2], codes, [0, 0, 0])
+        want.append(tokens.copy())
+        codes = tokens.copy()
+    buf_codes = np.ascontiguousarray(start, np.uint32).copy()
+    buf_tokens = np.zeros_like(buf_codes)
+    step = dec.bind_frame_batch([3, 4, 5], buf_codes, [0, 0, 0], buf_tokens)
+    for f in range(12):
+        assert step() is buf_tokens
+        assert np.array_equal(buf_tokens, want[f]), f
+        buf_codes[:] = buf_tokens
+    with pytest.raises(ValueError):
+        dec.bind_frame_batch([3, 4, 5], buf_codes.astype(np.int64), [0, 0, 0], buf_tokens)
+    with pytest.raises(ValueError):
+        dec.bind_frame_batch([3, 4], buf_codes, [0, 0], buf_tokens)
+    dec.close(); be.close()
+
+
 @pytest.mark.parametrize("name", ["f32", "int8", "int4"])
 def test_tiny_greedy_tokens_match_reference(name, golden, tiny_model, tiny_memory):
     """Free-running greedy decode (EOS allowed from frame 4) through both entry
