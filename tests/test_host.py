@@ -66,6 +66,15 @@ def test_algorithmic_bytes_match_the_documented_figures():
     # self-attention at batch 1, position 256: K and V rows 0..256 of 768 floats
     b = bench.algorithmic_bytes(shape, "self attention", 1, 256, q)
     assert b >= 2 * 257 * 768 * 4 and b < 2 * 257 * 768 * 4 + 40000
+    # 64 streams at position 257, the strict step's launch (f32 rows out, quantized by the next
+    # launch): the figure of profiles/traffic.json; with the int8 row, one byte per column more
+    split = bench.algorithmic_bytes(shape, "self attention", 64, 257, q, split_quant=True)
+    assert split == 64 * (2 * 258 * 3072 + 2 * 3072 + 3 * 3072 + 3072) == 102629376
+    assert bench.algorithmic_bytes(shape, "self attention", 64, 257, q) == split + 64 * 768
+    # the quantization launches: hidden rows alone, or the mean of hidden and attention rows
+    name = "row quantization (attention rows|hidden rows)"
+    assert bench.algorithmic_bytes(shape, name, 64, 257, q) == 64 * 3072 * 5
+    assert bench.algorithmic_bytes(shape, name, 64, 257, q, split_quant=True) == 64 * (3072 + 768) / 2 * 5
 
 
 def test_reduce_max_over_two_gloo_ranks(tmp_path):
